@@ -1,0 +1,150 @@
+/*
+ * rwkvq_b200.h -- C ABI of librwkvq_b200.so: sm_100a kernels for the quantized
+ * RWKV-7 forward path of `.rwkvq` checkpoints.
+ *
+ * The reference project has no FFI: its backend boundary is a set of Python
+ * classes in rwkv_quant/backends/metal/ that launch Metal kernels.  Each entry
+ * point below names the reference operator it stands behind (paths relative to
+ * the reference project root).  The Python classes in
+ * rwkv_quant_b200/backends/cuda/ bind these symbols through ctypes and expose
+ * the reference's class / function names on top of them.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer owned by the caller, unless the
+ *     parameter name ends in `_host`;
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it
+ *     and nothing synchronises;
+ *   - no entry point allocates or frees device memory;
+ *   - return value: 0 on success, a negative RWKVQ_E_* code otherwise
+ *     (rwkvq_strerror() gives the text, rwkvq_last_error_detail() the detail of
+ *     the calling thread's last failure);
+ *   - thread-safe when called on distinct streams.
+ */
+#ifndef RWKVQ_B200_H
+#define RWKVQ_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RWKVQ_OK          0
+#define RWKVQ_E_SHAPE    -1   /* a dimension violates a layout rule (IN % 256, ...)   */
+#define RWKVQ_E_ALIGN    -2   /* a pointer is not aligned as the kernel needs          */
+#define RWKVQ_E_DTYPE    -3   /* unsupported dtype / layout / bit width                */
+#define RWKVQ_E_ARCH     -4   /* device is not sm_100                                  */
+#define RWKVQ_E_LAUNCH   -5   /* the CUDA runtime refused the launch                   */
+#define RWKVQ_E_TIMEOUT  -6   /* a bounded device-side wait ran out                    */
+#define RWKVQ_E_NULL     -7   /* a required pointer is null                            */
+#define RWKVQ_E_LIMIT    -8   /* a size exceeds a documented maximum                   */
+
+/* element types of activation / output buffers */
+#define RWKVQ_F32   0
+#define RWKVQ_F16   1
+#define RWKVQ_BF16  2
+
+/* tensor layouts ("kind" in the .rwkvq manifest; formats/codec.py:28-41) */
+#define RWKVQ_KIND_DENSE 0    /* bf16 as stored                                         */
+#define RWKVQ_KIND_SB6   1    /* block 32, super-block 8, 6-bit scale/min codes         */
+#define RWKVQ_KIND_SYM   2    /* block 16, super-block 16, int8 scale code, no min      */
+#define RWKVQ_KIND_ASYM  3    /* block gs, fp32 scale/min per block, uint8 codes        */
+#define RWKVQ_KIND_RTN   4    /* per-row fp16 scale, int8 codes or biased nibbles       */
+
+/* epilogues of the GEMV family */
+#define RWKVQ_EPI_NONE      0   /* y = W x                                             */
+#define RWKVQ_EPI_RELU2     1   /* y = relu(W x)^2      (cmix key, quant_model.py:800) */
+#define RWKVQ_EPI_ADD       2   /* y = resid + W x      (residual add of a block)      */
+
+/*
+ * One quantized tensor in the FILE layout (no repack).  rows/cols are the stored
+ * shape; for linear weights rows = OUT, cols = IN.  Unused pointers are NULL.
+ * Field <-> file buffer (formats/schema.py:45-81):
+ *   codes   sb6/sym@6: codes_packed u8 [rows, cols/2];  sym@8/rtn@8: codes i8
+ *           [rows, cols];  asym: codes u8 [rows, cols];  rtn@<=4: codes_packed u8
+ *           [rows, ceil(cols/2)];  dense: bf16 [rows, cols]
+ *   qh,qh2  gw_qh / gw_qh2 u8 [rows, cols/8]
+ *   qsqm    gw_qsqm u8 [rows, cols/256, 12]              (sb6)
+ *   qs      gw_qs  i8 [rows, cols/16]                    (sym)
+ *   d,dm    gw_d / gw_dm f16 [rows, cols/256]
+ *   scale   asym: gw_scale f32 [rows, ceil(cols/gs)];  rtn: scale f16 [rows]
+ *   mn      asym: gw_min  f32 [rows, ceil(cols/gs)]
+ */
+typedef struct rwkvq_qtensor {
+    int32_t kind;
+    int32_t bits;
+    int32_t rows;
+    int32_t cols;
+    int32_t gs;
+    int32_t sb;
+    const void* codes;
+    const void* qh;
+    const void* qh2;
+    const void* qsqm;
+    const void* qs;
+    const void* d;
+    const void* dm;
+    const void* scale;
+    const void* mn;
+} rwkvq_qtensor;
+
+const char* rwkvq_strerror(int code);
+const char* rwkvq_last_error_detail(void);
+/* 0 when the current device is compute capability 10.x, RWKVQ_E_ARCH otherwise */
+int rwkvq_check_device(void);
+int rwkvq_abi_version(void);
+
+/*
+ * Dequantise a tensor to a dense [rows, cols] buffer.
+ * Stands behind codec.dequant_{sb6,sym,asym,rtn} (formats/codec.py:183-292) and
+ * the Metal dequant kernel SymQuantLinear._dequant_w
+ * (backends/metal/quant_linear_sym.py:275-363, 433-452).
+ * out_dtype RWKVQ_F32 is bit-exact against the numpy codec (separate multiply
+ * and add, fp16 round-trip of the block scale / min); F16 / BF16 round that
+ * value once.  `round_bf16` != 0 rounds the fp32 value to bf16 first (what
+ * reader._dequantize_one does, formats/reader.py:114-127) before the cast.
+ */
+int rwkvq_dequant(const rwkvq_qtensor* t, void* out, int out_dtype, int round_bf16,
+                  void* stream);
+
+/*
+ * Quantized matrix-vector product for N right-hand sides, weights streamed in
+ * the file layout and never materialised:  y[n, o] = epi( sum_c W[o, c] x[n, c] ).
+ * Stands behind GwQuantLinear.__call__ / _gemv1 / _gemv_nb
+ * (backends/metal/quant_linear_gw.py:842-940), SymQuantLinear._gemv
+ * (quant_linear_sym.py:498-516) and QuantLinearV2.__call__
+ * (quant_linear_v2.py:322-351).
+ *   x      [N, ldx] of x_dtype, y [N, ldy] fp32, resid [N, ldy] fp32 (EPI_ADD)
+ * fp32 accumulation.  Layout rules: sb6 / sym need cols % 256 == 0; the other
+ * kinds are unrestricted (a slower generic kernel serves ragged shapes).
+ */
+int rwkvq_gemv(const rwkvq_qtensor* t, const void* x, int x_dtype, int N, int64_t ldx,
+               float* y, int64_t ldy, int epilogue, const float* resid, void* stream);
+
+/*
+ * K same-shape matrices, K different inputs, one launch: y[k] = W_k x[k].
+ * Stands behind GwQuantLinearFused / SymQuantLinearFused
+ * (quant_linear_gw.py:943-1020, quant_linear_sym.py:519-574); results are
+ * bit-identical to K separate rwkvq_gemv calls with N = 1.
+ *   ts [K] host array of tensors (same kind, bits, rows, cols)
+ *   x  [K, cols] of x_dtype, y [K, rows] fp32
+ */
+int rwkvq_gemv_fused(const rwkvq_qtensor* ts_host, int K, const void* x, int x_dtype,
+                     float* y, void* stream);
+
+/*
+ * Matrix-vector product against a tensor stored [in, out] (world-naming LoRA
+ * matrices, formats/codec.py:514-535):  y[n, o] = act( sum_i x[n, i] Wt[i, o] ).
+ * Stands behind the dense LoRA matmuls of QuantTMix._lora
+ * (backends/metal/quant_model.py:462-526, _mm :204-208) with the weights read
+ * from the file bytes instead of an fp16 copy.  `round_w` != 0 applies the
+ * reference's load-time rounding fp16(bf16(w)) to every weight
+ * (quant_model.py:128-154).  act: 0 none, 1 tanh, 2 sigmoid.
+ */
+int rwkvq_gemv_t(const rwkvq_qtensor* t, const float* x, int N, int64_t ldx,
+                 float* y, int64_t ldy, int act, int round_w, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RWKVQ_B200_H */

@@ -1,0 +1,90 @@
+"""ctypes binding of ``librwkvq_b200.so`` (declared in ``include/rwkvq_b200.h``).
+
+There is no CPU or PyTorch fallback: if the library is missing or the device is
+not a B200-class GPU, loading fails with an error that says how to build it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "librwkvq_b200.so")
+
+F32, F16, BF16 = 0, 1, 2
+KIND = {"dense": 0, "sb6": 1, "sym": 2, "asym": 3, "rtn": 4}
+EPI_NONE, EPI_RELU2, EPI_ADD = 0, 1, 2
+DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+
+class QTensorStruct(C.Structure):
+    """``rwkvq_qtensor`` of the header."""
+    _fields_ = [("kind", C.c_int32), ("bits", C.c_int32), ("rows", C.c_int32),
+                ("cols", C.c_int32), ("gs", C.c_int32), ("sb", C.c_int32),
+                ("codes", C.c_void_p), ("qh", C.c_void_p), ("qh2", C.c_void_p),
+                ("qsqm", C.c_void_p), ("qs", C.c_void_p), ("d", C.c_void_p),
+                ("dm", C.c_void_p), ("scale", C.c_void_p), ("mn", C.c_void_p)]
+
+
+class RwkvqError(RuntimeError):
+    def __init__(self, code: int, name: str, detail: str):
+        super().__init__(f"{name} failed: {code} ({detail})")
+        self.code = code
+
+
+_lib = None
+
+# name -> (restype, argtypes); every symbol the header declares
+_PROTOS = {
+    "rwkvq_strerror": (C.c_char_p, [C.c_int]),
+    "rwkvq_last_error_detail": (C.c_char_p, []),
+    "rwkvq_check_device": (C.c_int, []),
+    "rwkvq_abi_version": (C.c_int, []),
+    "rwkvq_dequant": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "rwkvq_gemv": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_int, C.c_int64,
+                             C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
+    "rwkvq_gemv_fused": (C.c_int, [C.POINTER(QTensorStruct), C.c_int, C.c_void_p, C.c_int,
+                                   C.c_void_p, C.c_void_p]),
+    "rwkvq_gemv_t": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_int64,
+                               C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
+}
+
+
+def exported_symbols():
+    """Names the header declares (and the library must export)."""
+    return sorted(_PROTOS)
+
+
+def load(check_device: bool = False) -> C.CDLL:
+    """Load the library (once).  ``check_device`` additionally requires sm_100."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m rwkv_quant_b200.build` "
+                f"(nvcc, sm_100a). There is no CPU fallback.")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in _PROTOS.items():
+            fn = getattr(lib, name)         # AttributeError if the symbol is absent
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    if check_device:
+        check(_lib.rwkvq_check_device(), "rwkvq_check_device")
+    return _lib
+
+
+def check(code: int, name: str) -> None:
+    if code != 0:
+        lib = load()
+        detail = lib.rwkvq_last_error_detail().decode() or lib.rwkvq_strerror(code).decode()
+        raise RwkvqError(code, name, detail)
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream

@@ -1,0 +1,187 @@
+"""PyTorch custom ops (namespace ``rwkvq``) over the C ABI, and the device-side
+view of a quantized tensor.
+
+Every op takes the tensor's file buffers as a fixed-order list plus six
+integers, builds the ``rwkvq_qtensor`` descriptor and calls the library on the
+current CUDA stream.  Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import torch
+
+from ... import _lib
+from ..._lib import QTensorStruct
+
+_BUF_ORDER = ("codes", "qh", "qh2", "qsqm", "qs", "d", "dm", "scale", "mn")
+
+
+def _descr(bufs: Sequence[torch.Tensor], meta: Sequence[int]) -> QTensorStruct:
+    s = QTensorStruct()
+    s.kind, s.bits, s.rows, s.cols, s.gs, s.sb = (int(v) for v in meta)
+    for name, b in zip(_BUF_ORDER, bufs):
+        setattr(s, name, b.data_ptr() if b.numel() else None)
+    return s
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("rwkvq ops run on CUDA tensors only (there is no CPU path)")
+
+
+class DeviceQT:
+    """A QuantizedTensor uploaded to the GPU in the file layout (no repack).
+
+    Accepts this package's ``QuantizedTensor`` or the reference's (same field
+    names, formats/schema.py:45-81).  ``rows, cols`` is the stored 2-D shape."""
+
+    def __init__(self, qt, device="cuda"):
+        shape = tuple(qt.shape)
+        if len(shape) != 2:
+            raise ValueError(f"{getattr(qt, 'key', '?')}: only 2-D tensors, got {shape}")
+        oi = getattr(qt, "outlier_indices", None)
+        if oi is not None and oi.numel() > 0:
+            raise NotImplementedError(
+                f"{getattr(qt, 'key', '?')}: sparse outlier overrides are not supported")
+        self.key = getattr(qt, "key", "")
+        self.rows, self.cols = int(shape[0]), int(shape[1])
+        self.bits = int(qt.bits)
+        mode = getattr(qt, "gw_mode", "") or ""
+        self.kind = "dense" if self.bits >= 16 else (mode or "rtn")
+        self.gs, self.sb = int(getattr(qt, "gw_gs", 0) or 0), int(getattr(qt, "gw_sb", 0) or 0)
+        dev = torch.device(device)
+
+        def up(t, dtype=None):
+            if t is None:
+                return torch.empty(0, dtype=torch.uint8, device=dev)
+            t = t.to(dev, non_blocking=True)
+            if dtype is not None and t.dtype != dtype:
+                t = t.to(dtype)
+            return t.contiguous()
+
+        g = lambda f: getattr(qt, f, None)
+        none = up(None)
+        b = dict.fromkeys(_BUF_ORDER, none)
+        if self.kind == "dense":
+            b["codes"] = up(qt.dense, torch.bfloat16)
+        elif self.kind == "sb6":
+            b.update(codes=up(qt.codes_packed), qh=up(g("gw_qh")), qh2=up(g("gw_qh2")),
+                     qsqm=up(qt.gw_qsqm), d=up(qt.gw_d, torch.float16), dm=up(qt.gw_dm, torch.float16))
+        elif self.kind == "sym":
+            codes = qt.codes if g("codes") is not None else qt.codes_packed
+            b.update(codes=up(codes), qh=up(g("gw_qh")), qh2=up(g("gw_qh2")),
+                     qs=up(qt.gw_qs, torch.int8), d=up(qt.gw_d, torch.float16))
+        elif self.kind == "asym":
+            b.update(codes=up(qt.codes), scale=up(qt.gw_scale, torch.float32),
+                     mn=up(qt.gw_min, torch.float32))
+        elif self.kind == "rtn":
+            codes = qt.codes if g("codes") is not None else qt.codes_packed
+            b.update(codes=up(codes), scale=up(qt.scale.reshape(-1), torch.float16))
+        else:
+            raise NotImplementedError(f"{self.key}: layout {self.kind!r}")
+        self.bufs: List[torch.Tensor] = [b[n] for n in _BUF_ORDER]
+        self.meta: List[int] = [_lib.KIND[self.kind], self.bits, self.rows, self.cols, self.gs, self.sb]
+        self.struct = _descr(self.bufs, self.meta)
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.bufs)
+
+    def slice_rows(self, a: int, b: int) -> "DeviceQT":
+        """Rows [a, b) as a view: every layout stores rows first and blocks along
+        the columns, so any row range is a valid tensor (formats/reader.py:130-152)."""
+        out = object.__new__(DeviceQT)
+        out.__dict__.update(self.__dict__)
+        out.rows = b - a
+        out.bufs = [t[a:b] if t.numel() else t for t in self.bufs]
+        out.meta = list(self.meta)
+        out.meta[2] = b - a
+        out.struct = _descr(out.bufs, out.meta)
+        return out
+
+
+# ---------------------------------------------------------------------------
+# custom ops
+# ---------------------------------------------------------------------------
+
+@torch.library.custom_op("rwkvq::dequant", mutates_args=())
+def dequant(bufs: Sequence[torch.Tensor], meta: Sequence[int], out_dtype: torch.dtype,
+            round_bf16: bool) -> torch.Tensor:
+    _require_cuda(bufs[0])
+    lib = _lib.load()
+    d = _descr(bufs, meta)
+    out = torch.empty((meta[2], meta[3]), dtype=out_dtype, device=bufs[0].device)
+    _lib.check(lib.rwkvq_dequant(C.byref(d), out.data_ptr(), _lib.DTYPE_CODE[out_dtype],
+                                 int(round_bf16), _lib.stream_ptr()), "rwkvq_dequant")
+    return out
+
+
+@dequant.register_fake
+def _(bufs, meta, out_dtype, round_bf16):
+    return torch.empty((meta[2], meta[3]), dtype=out_dtype, device=bufs[0].device)
+
+
+@torch.library.custom_op("rwkvq::gemv", mutates_args=())
+def gemv(bufs: Sequence[torch.Tensor], meta: Sequence[int], x: torch.Tensor, epilogue: int,
+         resid: Optional[torch.Tensor]) -> torch.Tensor:
+    """x [N, IN] (fp32 / fp16 / bf16, contiguous rows) -> y [N, OUT] fp32."""
+    _require_cuda(bufs[0], x, resid)
+    lib = _lib.load()
+    d = _descr(bufs, meta)
+    n = x.shape[0]
+    y = torch.empty((n, meta[2]), dtype=torch.float32, device=x.device)
+    _lib.check(lib.rwkvq_gemv(C.byref(d), x.data_ptr(), _lib.DTYPE_CODE[x.dtype], n, x.stride(0),
+                              y.data_ptr(), y.stride(0), epilogue, _lib.ptr(resid),
+                              _lib.stream_ptr()), "rwkvq_gemv")
+    return y
+
+
+@gemv.register_fake
+def _(bufs, meta, x, epilogue, resid):
+    return torch.empty((x.shape[0], meta[2]), dtype=torch.float32, device=x.device)
+
+
+@torch.library.custom_op("rwkvq::gemv_t", mutates_args=())
+def gemv_t(bufs: Sequence[torch.Tensor], meta: Sequence[int], x: torch.Tensor, act: int,
+           round_w: bool) -> torch.Tensor:
+    """x [N, rows] fp32 against a tensor stored [rows=in, cols=out] -> [N, cols]."""
+    _require_cuda(bufs[0], x)
+    lib = _lib.load()
+    d = _descr(bufs, meta)
+    n = x.shape[0]
+    y = torch.empty((n, meta[3]), dtype=torch.float32, device=x.device)
+    _lib.check(lib.rwkvq_gemv_t(C.byref(d), x.data_ptr(), n, x.stride(0), y.data_ptr(),
+                                y.stride(0), act, int(round_w), _lib.stream_ptr()), "rwkvq_gemv_t")
+    return y
+
+
+@gemv_t.register_fake
+def _(bufs, meta, x, act, round_w):
+    return torch.empty((x.shape[0], meta[3]), dtype=torch.float32, device=x.device)
+
+
+def gemv_fused(dqts: Sequence[DeviceQT], xstack: torch.Tensor) -> torch.Tensor:
+    """K same-shape matrices, K inputs [K, IN] -> [K, OUT], one launch."""
+    _require_cuda(xstack)
+    lib = _lib.load()
+    k = len(dqts)
+    arr = (QTensorStruct * k)(*[d.struct for d in dqts])
+    y = torch.empty((k, dqts[0].rows), dtype=torch.float32, device=xstack.device)
+    _lib.check(lib.rwkvq_gemv_fused(arr, k, xstack.data_ptr(), _lib.DTYPE_CODE[xstack.dtype],
+                                    y.data_ptr(), _lib.stream_ptr()), "rwkvq_gemv_fused")
+    return y
+
+
+def as_rows(x: torch.Tensor, n_in: int):
+    """[..., IN] -> contiguous [N, IN] of a supported dtype plus the leading shape."""
+    if x.shape[-1] != n_in:
+        raise AssertionError(f"last dim {x.shape[-1]} != in_features {n_in}")
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, n_in)
+    if x2.dtype not in _lib.DTYPE_CODE:
+        x2 = x2.float()
+    if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16 or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+    return x2, lead

@@ -1,0 +1,204 @@
+"""CUDA kernels against the oracle, through the C ABI (via the rwkvq:: ops).
+
+  dequant  fp32 output equal BIT FOR BIT to the reference codec (digests of
+           tests/golden/codec_cases.npz, made by the reference's packers);
+  GEMV     relmax(|y - x @ dequant(W).T|) / max|ref| <= 1e-3 (the reference's own
+           kernel gates allow 3e-3: tests/test_gw_kernel.py:29), N in {1,2,3,8};
+  claims restated from the reference's equality gates: batch invariance
+  (tests/test_gw_nb_parity.py), fused == separate (tests/test_sym_fuse_parity.py),
+  poison-filled outputs to catch rows the grid does not cover.
+"""
+import zlib
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import case_to_qt, digest_f32, oracle_dequant_case, relmax
+from oracle import codec_np as oc
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+def _x(n, k, seed, dtype=torch.float32):
+    x = np.random.default_rng(seed).standard_normal((n, k)).astype(np.float32)
+    return torch.from_numpy(x).to("cuda", dtype)
+
+
+def test_dequant_bit_exact_all_golden_cases(cuda_lib, codec_cases):
+    from rwkv_quant_b200.backends.cuda import ops
+    for name, (meta, bufs, _) in codec_cases.items():
+        if "outlier_indices" in bufs:
+            continue
+        dq = ops.DeviceQT(case_to_qt(name, meta, bufs))
+        w = ops.dequant(dq.bufs, dq.meta, torch.float32, False).cpu().numpy()
+        assert digest_f32(w) == meta["digest"], f"{name}: device dequant differs from the codec"
+        ref = oracle_dequant_case(meta, bufs)
+        h = ops.dequant(dq.bufs, dq.meta, torch.float16, False).cpu().numpy()
+        np.testing.assert_array_equal(h, ref.astype(np.float16), err_msg=name)
+        b = ops.dequant(dq.bufs, dq.meta, torch.bfloat16, True).float().cpu().numpy()
+        np.testing.assert_array_equal(b, oc.f32_to_bf16_rne(ref), err_msg=name)
+
+
+@pytest.mark.parametrize("xdtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_gemv_golden_cases(cuda_lib, codec_cases, xdtype):
+    from rwkv_quant_b200.backends.cuda import ops
+    for name, (meta, bufs, _) in codec_cases.items():
+        if "outlier_indices" in bufs:
+            continue
+        dq = ops.DeviceQT(case_to_qt(name, meta, bufs))
+        w = oracle_dequant_case(meta, bufs).astype(np.float64)
+        for n in (1, 2, 3, 8):
+            x = _x(n, dq.cols, zlib.crc32(f"{name}-{n}".encode()), xdtype)
+            y = ops.gemv(dq.bufs, dq.meta, x, 0, None).cpu().numpy()
+            ref = x.float().cpu().numpy().astype(np.float64) @ w.T
+            assert relmax(y, ref) <= TOL, (name, n, relmax(y, ref))
+
+
+def _synth_linear(layout, bits, rows, cols, seed=0):
+    from rwkv_quant_b200 import synth
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(rows, cols, generator=g) * 0.02
+    fn = {"sb6": synth.quant_sb6, "sym": synth.quant_sym, "rtn": synth.quant_rtn}[layout]
+    return fn("w", "g", w, bits)
+
+
+def _oracle_w(qt):
+    n = lambda t: None if t is None else t.numpy()
+    if qt.gw_mode == "sb6":
+        return oc.dequant_sb6(n(qt.codes_packed), n(qt.gw_qsqm), n(qt.gw_d), n(qt.gw_dm), shape=qt.shape,
+                              qh=n(qt.gw_qh), qh2=n(qt.gw_qh2))
+    if qt.gw_mode == "sym":
+        return oc.dequant_sym(n(qt.gw_qs), n(qt.gw_d), shape=qt.shape, codes=n(qt.codes),
+                              codes_packed=n(qt.codes_packed), qh=n(qt.gw_qh), qh2=n(qt.gw_qh2))
+    return oc.dequant_rtn(n(qt.scale), shape=qt.shape, codes=n(qt.codes), codes_packed=n(qt.codes_packed))
+
+
+LAYOUTS = [("sb6", 4), ("sb6", 5), ("sb6", 6), ("sym", 6), ("sym", 8), ("rtn", 8), ("rtn", 4)]
+
+
+@pytest.mark.parametrize("layout,bits", LAYOUTS)
+@pytest.mark.parametrize("rows,cols", [(16, 256), (48, 512), (2048, 2048), (100, 2560), (2048, 8192)])
+def test_gemv_shapes_and_uncovered_rows(cuda_lib, layout, bits, rows, cols):
+    """Exhaustive small shapes plus model shapes; rows not a multiple of the CTA
+    tile; the output is NaN-filled first so an unwritten row cannot pass."""
+    from rwkv_quant_b200 import _lib
+    from rwkv_quant_b200.backends.cuda import ops
+    import ctypes as C
+    qt = _synth_linear(layout, bits, rows, cols, seed=rows + cols)
+    dq = ops.DeviceQT(qt)
+    w = _oracle_w(qt)
+    wd = ops.dequant(dq.bufs, dq.meta, torch.float32, False).cpu().numpy()
+    assert np.array_equal(wd.view(np.uint32), w.view(np.uint32)), "device dequant != oracle, bit level"
+    x = _x(1, cols, rows * 31 + cols)
+    y = torch.full((1, rows), float("nan"), device="cuda")
+    d = ops._descr(dq.bufs, dq.meta)
+    _lib.check(cuda_lib.rwkvq_gemv(C.byref(d), x.data_ptr(), 0, 1, cols, y.data_ptr(), rows, 0, None,
+                                   _lib.stream_ptr()), "rwkvq_gemv")
+    y = y.cpu().numpy()
+    assert np.isfinite(y).all(), "a row was not written"
+    ref = x.cpu().numpy().astype(np.float64) @ w.astype(np.float64).T
+    assert relmax(y, ref) <= TOL, relmax(y, ref)
+
+
+@pytest.mark.parametrize("layout,bits", LAYOUTS[:6])
+def test_batch_invariance_and_epilogues(cuda_lib, layout, bits):
+    """Column n of an N-column call equals the single-vector call bit for bit;
+    relu^2 and residual-add epilogues equal their unfused forms."""
+    from rwkv_quant_b200.backends.cuda import ops
+    qt = _synth_linear(layout, bits, 512, 1024, seed=bits)
+    dq = ops.DeviceQT(qt)
+    x = _x(7, 1024, 99)
+    y = ops.gemv(dq.bufs, dq.meta, x, 0, None)
+    for n in range(7):
+        y1 = ops.gemv(dq.bufs, dq.meta, x[n:n + 1].contiguous(), 0, None)
+        assert torch.equal(y1[0], y[n]), f"column {n} depends on the batch it was computed in"
+    assert torch.equal(ops.gemv(dq.bufs, dq.meta, x, 1, None), torch.relu(y) ** 2)
+    resid = _x(7, 512, 5)
+    assert torch.equal(ops.gemv(dq.bufs, dq.meta, x, 2, resid), resid + y)
+
+
+@pytest.mark.parametrize("layout,bits", [("sb6", 5), ("sym", 8), ("sb6", 4)])
+def test_fused_projections_equal_separate(cuda_lib, layout, bits):
+    from rwkv_quant_b200.backends import cuda as be
+    cls, fused = ((be.GwQuantLinear, be.GwQuantLinearFused) if layout == "sb6"
+                  else (be.SymQuantLinear, be.SymQuantLinearFused))
+    lins = [cls(_synth_linear(layout, bits, 768, 768, seed=s)) for s in (1, 2, 3)]
+    xs = _x(3, 768, 17)
+    out = fused(lins)(xs)
+    assert out.shape == (3, 768)
+    for k in range(3):
+        assert torch.equal(out[k], lins[k](xs[k])), f"matrix {k}"
+
+
+def test_linear_classes_contract(cuda_lib):
+    """Any leading shape, fp32 out, attributes, from_buffers, dispatch by layout."""
+    from rwkv_quant_b200.backends import cuda as be
+    qt = _synth_linear("sym", 6, 256, 512, seed=8)
+    lin = be.linear_for(qt)
+    assert isinstance(lin, be.SymQuantLinear) and (lin.in_features, lin.out_features) == (512, 256)
+    x = _x(6, 512, 3).reshape(2, 3, 512)
+    y = lin(x)
+    assert y.shape == (2, 3, 256) and y.dtype == torch.float32
+    n = lambda t: None if t is None else t.numpy()
+    lin2 = be.SymQuantLinear.from_buffers(shape=qt.shape, bits=6, qs=n(qt.gw_qs), d=n(qt.gw_d),
+                                          codes_packed=n(qt.codes_packed), qh=n(qt.gw_qh), qh2=n(qt.gw_qh2))
+    assert torch.equal(lin2(x), y)
+    w = lin._dequant_w(torch.float32).cpu().numpy()
+    assert np.array_equal(w.view(np.uint32), _oracle_w(qt).view(np.uint32))
+    assert not np.array_equal(lin._dequant_w(torch.float16).float().cpu().numpy(), w)   # control
+    assert isinstance(be.linear_for(_synth_linear("sb6", 4, 64, 256)), be.GwQuantLinear)
+    assert isinstance(be.linear_for(_synth_linear("rtn", 8, 64, 256)), be.QuantLinearV2)
+    with pytest.raises(AssertionError):
+        lin(_x(1, 256, 0))
+
+
+def test_gemv_t_lora_orientation(cuda_lib, codec_cases):
+    """Tensors stored [in, out]: y = act(x @ W) with the reference's load-time
+    rounding fp16(bf16(w)) of LoRA weights (quant_model.py:128-154)."""
+    from rwkv_quant_b200.backends.cuda import ops
+    for name in ("asym/ragged", "asym/wide", "rtn/8", "rtn/8wide", "rtn/4odd"):
+        meta, bufs, _ = codec_cases[name]
+        dq = ops.DeviceQT(case_to_qt(name, meta, bufs))
+        w = oracle_dequant_case(meta, bufs)
+        wr = oc.f32_to_bf16_rne(w).astype(np.float16).astype(np.float64)
+        for n in (1, 5, 11):
+            x = _x(n, dq.rows, zlib.crc32(name.encode()) + n)
+            xh = x.cpu().numpy().astype(np.float64)
+            y = ops.gemv_t(dq.bufs, dq.meta, x, 0, True).cpu().numpy()
+            assert relmax(y, xh @ wr) <= 2e-5, (name, n)
+            y = ops.gemv_t(dq.bufs, dq.meta, x, 0, False).cpu().numpy()
+            assert relmax(y, xh @ w.astype(np.float64)) <= 2e-5, (name, n)
+            y = ops.gemv_t(dq.bufs, dq.meta, x, 1, True).cpu().numpy()
+            assert relmax(y, np.tanh(xh @ wr)) <= 2e-5, (name, n)
+            y = ops.gemv_t(dq.bufs, dq.meta, x, 2, True).cpu().numpy()
+            assert relmax(y, 1 / (1 + np.exp(-(xh @ wr)))) <= 2e-5, (name, n)
+
+
+def test_config1_single_gemv(cuda_lib):
+    """W [8192, 2048] ~N(0, 0.02) int4 sb6 (9 437 184 packed bytes), x fp16 [1, 2048]:
+    dequantised W bit-exact, y relmax <= 1e-3."""
+    from rwkv_quant_b200.backends import cuda as be
+    qt = _synth_linear("sb6", 4, 8192, 2048, seed=0)
+    assert qt.nbytes() == 9437184
+    lin = be.GwQuantLinear(qt)
+    w = _oracle_w(qt)
+    assert np.array_equal(lin._dequant_w().cpu().numpy().view(np.uint32), w.view(np.uint32))
+    x = torch.from_numpy(np.random.default_rng(0).standard_normal((1, 2048)).astype(np.float16)).cuda()
+    y = lin(x).cpu().numpy()
+    ref = x.float().cpu().numpy().astype(np.float64) @ w.astype(np.float64).T
+    assert relmax(y, ref) <= TOL
+
+
+def test_errors_surface_as_exceptions(cuda_lib):
+    from rwkv_quant_b200 import _lib
+    from rwkv_quant_b200.backends.cuda import ops
+    qt = _synth_linear("sb6", 4, 64, 256)
+    dq = ops.DeviceQT(qt)
+    bad = list(dq.meta)
+    bad[3] = 250
+    with pytest.raises(_lib.RwkvqError):
+        ops.gemv(dq.bufs, bad, _x(1, 256, 0), 0, None)
+    with pytest.raises(RuntimeError):
+        ops.gemv(dq.bufs, dq.meta, torch.zeros(1, 256), 0, None)      # CPU tensor: no fallback
