@@ -86,6 +86,14 @@ typedef struct rwkvq_qtensor {
     const void* dm;
     const void* scale;
     const void* mn;
+    /* Optional device-side relayout of the small side streams (same byte count as
+     * the file buffers, made once at load by rwkvq_relayout_*; codes stay as in the
+     * file).  When both are NULL the kernels read the file buffers only.
+     *   dev_meta    sb6: [rows, cols/256] records of 16 B = qsqm (12 B) | d | dm
+     *   dev_planes  bit-planes regrouped per block so that one shift + mask yields
+     *               the high code bits of 4 weights (see rwkvq_relayout_planes) */
+    const void* dev_meta;
+    const void* dev_planes;
 } rwkvq_qtensor;
 
 const char* rwkvq_strerror(int code);
@@ -143,6 +151,18 @@ int rwkvq_gemv_fused(const rwkvq_qtensor* ts_host, int K, const void* x, int x_d
  */
 int rwkvq_gemv_t(const rwkvq_qtensor* t, const float* x, int N, int64_t ldx,
                  float* y, int64_t ldy, int act, int round_w, void* stream);
+
+/*
+ * Load-time relayout of the side streams of an sb6 / sym tensor for the decode
+ * kernels; pure byte / bit permutations, no value changes, same total size.
+ * No counterpart in the reference's file format; it plays the role of the Metal
+ * loader's K3 interleave (formats/codec.py:390-435) without growing the data.
+ *   meta    out [rows, cols/256, 16] u8           (sb6 only)
+ *   planes  out u32: sb6@5 [rows, cols/32]; sb6@6 [rows, cols/32, 2];
+ *           sym@6 [rows, cols/16]                 (not needed at 4 / 8 bits)
+ */
+int rwkvq_relayout_meta(const rwkvq_qtensor* t, void* meta_out, void* stream);
+int rwkvq_relayout_planes(const rwkvq_qtensor* t, void* planes_out, void* stream);
 
 #ifdef __cplusplus
 }

@@ -25,7 +25,8 @@ class QTensorStruct(C.Structure):
                 ("cols", C.c_int32), ("gs", C.c_int32), ("sb", C.c_int32),
                 ("codes", C.c_void_p), ("qh", C.c_void_p), ("qh2", C.c_void_p),
                 ("qsqm", C.c_void_p), ("qs", C.c_void_p), ("d", C.c_void_p),
-                ("dm", C.c_void_p), ("scale", C.c_void_p), ("mn", C.c_void_p)]
+                ("dm", C.c_void_p), ("scale", C.c_void_p), ("mn", C.c_void_p),
+                ("dev_meta", C.c_void_p), ("dev_planes", C.c_void_p)]
 
 
 class RwkvqError(RuntimeError):
@@ -47,6 +48,8 @@ _PROTOS = {
                              C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
     "rwkvq_gemv_fused": (C.c_int, [C.POINTER(QTensorStruct), C.c_int, C.c_void_p, C.c_int,
                                    C.c_void_p, C.c_void_p]),
+    "rwkvq_relayout_meta": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_void_p]),
+    "rwkvq_relayout_planes": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_void_p]),
     "rwkvq_gemv_t": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_int64,
                                C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
 }

@@ -15,12 +15,13 @@ import torch
 from ... import _lib
 from ..._lib import QTensorStruct
 
-_BUF_ORDER = ("codes", "qh", "qh2", "qsqm", "qs", "d", "dm", "scale", "mn")
+_BUF_ORDER = ("codes", "qh", "qh2", "qsqm", "qs", "d", "dm", "scale", "mn",
+              "dev_meta", "dev_planes")
 
 
 def _descr(bufs: Sequence[torch.Tensor], meta: Sequence[int]) -> QTensorStruct:
     s = QTensorStruct()
-    s.kind, s.bits, s.rows, s.cols, s.gs, s.sb = (int(v) for v in meta)
+    s.kind, s.bits, s.rows, s.cols, s.gs, s.sb = (int(v) for v in meta[:6])
     for name, b in zip(_BUF_ORDER, bufs):
         setattr(s, name, b.data_ptr() if b.numel() else None)
     return s
@@ -38,7 +39,7 @@ class DeviceQT:
     Accepts this package's ``QuantizedTensor`` or the reference's (same field
     names, formats/schema.py:45-81).  ``rows, cols`` is the stored 2-D shape."""
 
-    def __init__(self, qt, device="cuda"):
+    def __init__(self, qt, device="cuda", relayout=True):
         shape = tuple(qt.shape)
         if len(shape) != 2:
             raise ValueError(f"{getattr(qt, 'key', '?')}: only 2-D tensors, got {shape}")
@@ -84,6 +85,29 @@ class DeviceQT:
             raise NotImplementedError(f"{self.key}: layout {self.kind!r}")
         self.bufs: List[torch.Tensor] = [b[n] for n in _BUF_ORDER]
         self.meta: List[int] = [_lib.KIND[self.kind], self.bits, self.rows, self.cols, self.gs, self.sb]
+        self.struct = _descr(self.bufs, self.meta)
+        if relayout and dev.type == "cuda":
+            self._relayout()
+
+    def _relayout(self):
+        """Regroup the scale records / bit-planes for the decode kernels (same bytes,
+        done once at load on the device)."""
+        lib = _lib.load()
+        dev = self.bufs[0].device
+        i_meta, i_planes = _BUF_ORDER.index("dev_meta"), _BUF_ORDER.index("dev_planes")
+        with torch.cuda.device(dev):
+            if self.kind == "sb6":
+                m = torch.empty((self.rows, self.cols // 256, 16), dtype=torch.uint8, device=dev)
+                _lib.check(lib.rwkvq_relayout_meta(C.byref(self.struct), m.data_ptr(), _lib.stream_ptr()),
+                           "rwkvq_relayout_meta")
+                self.bufs[i_meta] = m
+            words = {("sb6", 5): self.cols // 32, ("sb6", 6): self.cols // 16,
+                     ("sym", 6): self.cols // 16}.get((self.kind, self.bits))
+            if words:
+                p = torch.empty((self.rows, words), dtype=torch.int32, device=dev)
+                _lib.check(lib.rwkvq_relayout_planes(C.byref(self.struct), p.data_ptr(), _lib.stream_ptr()),
+                           "rwkvq_relayout_planes")
+                self.bufs[i_planes] = p
         self.struct = _descr(self.bufs, self.meta)
 
     def nbytes(self) -> int:

@@ -126,6 +126,8 @@ struct QView {
     const __half* dm;
     const void* scale;
     const float* mn;
+    const uint8_t* dev_meta;
+    const uint32_t* dev_planes;
 };
 
 __host__ inline QView make_view(const rwkvq_qtensor& t) {
@@ -140,6 +142,8 @@ __host__ inline QView make_view(const rwkvq_qtensor& t) {
     v.dm = static_cast<const __half*>(t.dm);
     v.scale = t.scale;
     v.mn = static_cast<const float*>(t.mn);
+    v.dev_meta = static_cast<const uint8_t*>(t.dev_meta);
+    v.dev_planes = static_cast<const uint32_t*>(t.dev_planes);
     return v;
 }
 
@@ -217,5 +221,12 @@ __device__ __forceinline__ float decode_element(const QView& t, int r, int c) {
 }
 
 int validate_qtensor(const rwkvq_qtensor* t, const char* who);
+
+// Single-vector tensor-core GEMV (rwkvq_gemv_mma.cu): layout id >= 0 when the
+// tensor carries what that kernel needs, and its launcher.
+int mma_layout_of(const rwkvq_qtensor& t);
+int launch_gemv_mma(int layout, const rwkvq_qtensor* ts, int n_mats, const void* x, int x_dtype,
+                    long long ldx, float* y, long long ldy, int epilogue, const float* resid,
+                    int fused, cudaStream_t s);
 
 }  // namespace rwkvq

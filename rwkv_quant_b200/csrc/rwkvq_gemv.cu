@@ -36,7 +36,7 @@ __device__ __forceinline__ float apply_epilogue(float v, int epi, const float* r
         v = fmaxf(v, 0.0f);
         return v * v;
     }
-    if (epi == RWKVQ_EPI_ADD) return v + resid[idx];
+    if (epi == RWKVQ_EPI_ADD) return __fadd_rn(v, resid[idx]);
     return v;
 }
 
@@ -300,7 +300,7 @@ gemv_chunk_kernel(const GemvArgs a) {
             for (int n = 0; n < NC; ++n) {
                 if (n >= a.n_cols) break;
                 const long long idx = (a.fused ? blockIdx.y : n) * a.ldy + row;
-                a.y[idx] = apply_epilogue(acc[r][n] * rs, a.epilogue, a.resid, idx);
+                a.y[idx] = apply_epilogue(__fmul_rn(acc[r][n], rs), a.epilogue, a.resid, idx);
             }
         }
     }
@@ -377,6 +377,10 @@ static int check_x(const void* x, int x_dtype, long long ldx, const char* who) {
     RWKVQ_REQUIRE(x != nullptr, RWKVQ_E_NULL, "%s: x is null", who);
     RWKVQ_REQUIRE(x_dtype == RWKVQ_F32 || x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_DTYPE,
                   "%s: x_dtype %d", who, x_dtype);
+    return RWKVQ_OK;
+}
+
+static int check_x_vector_loads(const void* x, int x_dtype, long long ldx, const char* who) {
     const size_t esz = x_dtype == RWKVQ_F32 ? 4 : 2;
     RWKVQ_REQUIRE(aligned(x, 16) && (ldx * esz) % 16 == 0, RWKVQ_E_ALIGN,
                   "%s: x and its row stride must be 16-byte aligned", who);
@@ -413,6 +417,18 @@ int rwkvq_gemv(const rwkvq_qtensor* t, const void* x, int x_dtype, int N, int64_
         gemv_generic_kernel<<<(t->rows + kWarpsPerCta - 1) / kWarpsPerCta, kWarpsPerCta * 32, 0, s>>>(a);
         return check_launch("rwkvq_gemv(generic)");
     }
+    rc = check_x_vector_loads(x, x_dtype, ldx, "rwkvq_gemv");
+    if (rc) return rc;
+    const int ml = mma_layout_of(*t);
+    if (ml >= 0) {      // one launch per right-hand side: each column's result is independent of N
+        for (int n = 0; n < N; ++n) {
+            rc = launch_gemv_mma(ml, t, 1, static_cast<const char*>(x) + static_cast<size_t>(n) * ldx * esz, x_dtype,
+                                 ldx, y + static_cast<size_t>(n) * ldy, ldy, epilogue,
+                                 resid ? resid + static_cast<size_t>(n) * ldy : nullptr, 0, s);
+            if (rc) return rc;
+        }
+        return check_launch("rwkvq_gemv(mma)");
+    }
     const int R = rows_per_warp(*t, 1);
     for (int n0 = 0; n0 < N;) {
         const int left = N - n0;
@@ -445,7 +461,17 @@ int rwkvq_gemv_fused(const rwkvq_qtensor* ts, int K, const void* x, int x_dtype,
     }
     int rc = check_x(x, x_dtype, ts[0].cols, "rwkvq_gemv_fused");
     if (rc) return rc;
+    rc = check_x_vector_loads(x, x_dtype, ts[0].cols, "rwkvq_gemv_fused");
+    if (rc) return rc;
     RWKVQ_REQUIRE(y != nullptr, RWKVQ_E_NULL, "rwkvq_gemv_fused: y is null");
+    int ml = mma_layout_of(ts[0]);
+    for (int k = 1; k < K; ++k)
+        if (mma_layout_of(ts[k]) != ml) ml = -1;
+    if (ml >= 0) {
+        rc = launch_gemv_mma(ml, ts, K, x, x_dtype, ts[0].cols, y, ts[0].rows, RWKVQ_EPI_NONE, nullptr, 1,
+                             static_cast<cudaStream_t>(stream));
+        return rc ? rc : check_launch("rwkvq_gemv_fused(mma)");
+    }
     const int ck = chunk_kind_of(ts[0]);
     RWKVQ_REQUIRE(ck >= 0, RWKVQ_E_DTYPE, "rwkvq_gemv_fused: layout has no chunk kernel");
     GemvArgs a{};

@@ -1,0 +1,494 @@
+// Single-vector decode GEMV on the integer tensor-core path.
+//
+// The codes of the .rwkvq layouts are small integers, so the inner products
+// sum_c q_c * X_c are computed EXACTLY in int32 by mma.sync.m16n8k32 (u8/s8 x s8):
+//   * the activation vector is turned once per CTA into a 21-bit fixed-point
+//     vector X = round(x * 2^e) (2^e chosen from max|x|) and split into three
+//     signed 7-bit digits  X = d1*2^14 + d2*2^7 + d3  kept in shared memory;
+//   * a warp owns 16 output rows; thread (g, t) of the warp streams the codes of
+//     rows g and g+8 for blocks 2t and 2t+1 of each group of 8 blocks with
+//     128-bit loads straight from the file layout (a quad reads 128 contiguous
+//     bytes of a row), turns nibbles into bytes with one AND per 4 weights and
+//     feeds them to the MMA as the A operand;
+//   * the 8 MMA columns are (block of the quad lane, digit): the B operand of
+//     column 2t+dg is digit dg of the activations of thread t's block and zero
+//     elsewhere, so C[row, 2t+dg] is the integer dot product of (row, block)
+//     with digit dg and every thread ends up holding the dot products of exactly
+//     the (row, block) pairs whose scale codes it loaded;
+//   * the per-block scale s = fp16(qs*d) (and min) is applied in fp32 per block,
+//     which is the arithmetic the codec defines; accumulation over blocks is fp32.
+// No dequantised copy of the weights ever exists; the only approximation is the
+// 21-bit fixed-point activation (relative error <= 2^-20 of max|x| per element).
+#include "rwkvq_common.cuh"
+
+namespace rwkvq {
+
+enum MmaLayout { ML_SB6_4 = 0, ML_SB6_5, ML_SB6_6, ML_SYM6, ML_SYM8 };
+
+constexpr int kMmaWarps = 8;
+constexpr int kMmaMaxFused = 4;
+
+struct MmaArgs {
+    QView t[kMmaMaxFused];
+    const void* x;      // [n_mats, ldx] (fused) or [ldx]
+    int x_dtype;
+    long long ldx;
+    float* y;
+    long long ldy;
+    const float* resid;
+    int epilogue;
+    int fused;
+};
+
+template <bool A_UNSIGNED>
+__device__ __forceinline__ void mma_i8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                       uint32_t b0, uint32_t b1) {
+    if (A_UNSIGNED) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        asm volatile(
+            "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+
+template <int L> struct Geo;   // K per iteration, bytes of codes per (row, thread, iteration)
+template <> struct Geo<ML_SB6_4> { static constexpr int KI = 256, BLK = 32, BITS = 4; };
+template <> struct Geo<ML_SB6_5> { static constexpr int KI = 256, BLK = 32, BITS = 5; };
+template <> struct Geo<ML_SB6_6> { static constexpr int KI = 256, BLK = 32, BITS = 6; };
+template <> struct Geo<ML_SYM6> { static constexpr int KI = 128, BLK = 16, BITS = 6; };
+template <> struct Geo<ML_SYM8> { static constexpr int KI = 128, BLK = 16, BITS = 8; };
+
+// Everything thread (g, t) streams for one iteration (8 blocks) of rows g, g+8.
+template <int L>
+struct Frag {
+    uint4 ca[2], cb[2];    // codes of blocks 2t, 2t+1: row g (ca), row g+8 (cb)
+    uint4 ma, mb;          // sb6: 16-byte scale records;  sym: .x,.y = 8 scale codes, .z = d bits
+    uint4 pa, pb;          // regrouped bit-planes of the two blocks
+};
+
+template <int L>
+__device__ __forceinline__ void load_frag(Frag<L>& f, const QView& q, int r0, int r1, int it, int t) {
+    using G = Geo<L>;
+    const size_t R0 = static_cast<size_t>(r0), R1 = static_cast<size_t>(r1);
+    if (L <= ML_SB6_6) {
+        const int nsb = q.cols >> 8;
+        const size_t rowb = static_cast<size_t>(q.cols >> 1);
+        const uint8_t* p0 = q.codes + R0 * rowb + it * 128 + t * 32;
+        const uint8_t* p1 = q.codes + R1 * rowb + it * 128 + t * 32;
+        f.ca[0] = ld_stream_u128(p0); f.ca[1] = ld_stream_u128(p0 + 16);
+        f.cb[0] = ld_stream_u128(p1); f.cb[1] = ld_stream_u128(p1 + 16);
+        f.ma = ld_stream_u128(q.dev_meta + (R0 * nsb + it) * 16);
+        f.mb = ld_stream_u128(q.dev_meta + (R1 * nsb + it) * 16);
+        if (G::BITS == 5) {
+            const size_t nb = static_cast<size_t>(q.cols >> 5);
+            const uint2 a = ld_stream_u64(q.dev_planes + R0 * nb + it * 8 + 2 * t);
+            const uint2 b = ld_stream_u64(q.dev_planes + R1 * nb + it * 8 + 2 * t);
+            f.pa = make_uint4(a.x, a.y, 0, 0); f.pb = make_uint4(b.x, b.y, 0, 0);
+        } else if (G::BITS == 6) {
+            const size_t nb = static_cast<size_t>(q.cols >> 5);
+            f.pa = ld_stream_u128(q.dev_planes + (R0 * nb + it * 8 + 2 * t) * 2);
+            f.pb = ld_stream_u128(q.dev_planes + (R1 * nb + it * 8 + 2 * t) * 2);
+        }
+    } else {
+        const size_t nb16 = static_cast<size_t>(q.cols >> 4);
+        const int nsb = q.cols >> 8;
+        if (L == ML_SYM6) {
+            const size_t rowb = static_cast<size_t>(q.cols >> 1);
+            f.ca[0] = ld_stream_u128(q.codes + R0 * rowb + it * 64 + t * 16);
+            f.cb[0] = ld_stream_u128(q.codes + R1 * rowb + it * 64 + t * 16);
+            const uint2 a = ld_stream_u64(q.dev_planes + R0 * nb16 + it * 8 + 2 * t);
+            const uint2 b = ld_stream_u64(q.dev_planes + R1 * nb16 + it * 8 + 2 * t);
+            f.pa = make_uint4(a.x, a.y, 0, 0); f.pb = make_uint4(b.x, b.y, 0, 0);
+        } else {
+            const size_t rowb = static_cast<size_t>(q.cols);
+            const uint8_t* p0 = q.codes + R0 * rowb + it * 128 + t * 32;
+            const uint8_t* p1 = q.codes + R1 * rowb + it * 128 + t * 32;
+            f.ca[0] = ld_stream_u128(p0); f.ca[1] = ld_stream_u128(p0 + 16);
+            f.cb[0] = ld_stream_u128(p1); f.cb[1] = ld_stream_u128(p1 + 16);
+        }
+        const uint2 sa = ld_stream_u64(reinterpret_cast<const uint8_t*>(q.qs) + R0 * nb16 + it * 8);
+        const uint2 sb = ld_stream_u64(reinterpret_cast<const uint8_t*>(q.qs) + R1 * nb16 + it * 8);
+        f.ma = make_uint4(sa.x, sa.y, ld_stream_u16(q.d + R0 * nsb + (it >> 1)), 0);
+        f.mb = make_uint4(sb.x, sb.y, ld_stream_u16(q.d + R1 * nsb + (it >> 1)), 0);
+    }
+}
+
+__device__ __forceinline__ uint32_t word_of(const uint4& v, int j) {
+    return j == 0 ? v.x : j == 1 ? v.y : j == 2 ? v.z : v.w;
+}
+
+// A-operand words of block h (0/1 of the thread's pair): for MMA step j the
+// low-half word (weights in K slots 4t..4t+3) and the high-half word (slots
+// 16+4t..).  `pl` holds the regrouped planes of this block.
+template <int L>
+__device__ __forceinline__ void a_words(const uint4 (&c)[2], const uint4& planes, int h, int j,
+                                        uint32_t& lo, uint32_t& hi) {
+    using G = Geo<L>;
+    if (L <= ML_SB6_6) {
+        const uint32_t w = word_of(c[h], j);
+        lo = w & 0x0F0F0F0Fu;
+        hi = (w >> 4) & 0x0F0F0F0Fu;
+        if (G::BITS == 5) {
+            // plane word: bit (8b + G) = code bit 4 of weight (G < 4 ? 4G + b : 16 + 4(G-4) + b)
+            const uint32_t p = h ? planes.y : planes.x;
+            lo |= (p << (4 - j)) & 0x10101010u;
+            hi |= (p >> j) & 0x10101010u;
+        } else if (G::BITS == 6) {
+            // two words per block: bits (8b + 2j, 8b + 2j + 1) = code bits (4, 5) of weight
+            // 4j + b (first word) / 16 + 4j + b (second word)
+            const uint32_t p0 = h ? planes.z : planes.x, p1 = h ? planes.w : planes.y;
+            lo |= (j < 2 ? (p0 << (4 - 2 * j)) : (p0 >> (2 * j - 4))) & 0x30303030u;
+            hi |= (j < 2 ? (p1 << (4 - 2 * j)) : (p1 >> (2 * j - 4))) & 0x30303030u;
+        }
+    } else if (L == ML_SYM6) {
+        // block of 16: two code words; step 0 takes the low nibbles (weights 0-3, 4-7),
+        // step 1 the high nibbles (weights 8-11, 12-15).  Plane word: bits
+        // (8b + 2G, 8b + 2G + 1) = code bits (4, 5) of weight (G < 2 ? 4G + b : 8 + 4(G-2) + b)
+        const uint32_t w0 = h ? c[0].z : c[0].x, w1 = h ? c[0].w : c[0].y;
+        const uint32_t p = h ? planes.y : planes.x;
+        if (j == 0) {
+            lo = (w0 & 0x0F0F0F0Fu) | ((p << 4) & 0x30303030u);
+            hi = (w1 & 0x0F0F0F0Fu) | ((p << 2) & 0x30303030u);
+        } else {
+            lo = ((w0 >> 4) & 0x0F0F0F0Fu) | (p & 0x30303030u);
+            hi = ((w1 >> 4) & 0x0F0F0F0Fu) | ((p >> 2) & 0x30303030u);
+        }
+    } else {
+        lo = word_of(c[h], 2 * j);
+        hi = word_of(c[h], 2 * j + 1);
+    }
+}
+
+// Activation -> fixed point digits in shared memory.
+//   dig[d][i]  signed 7-bit digit d (0: most significant) of X_i = round(x_i * 2^e)
+//   xs16[k]    sum of X over elements 16k..16k+15 (exact, as float)
+// Returns 2^-e (the factor that undoes the scaling) and whether x was finite.
+__device__ __forceinline__ float4 load_x4(const void* x, int dtype, int i) {
+    if (dtype == RWKVQ_F32) return __ldg(reinterpret_cast<const float4*>(x) + i);
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(x) + i);
+    if (dtype == RWKVQ_F16) {
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xFFFF0000u),
+                       __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xFFFF0000u));
+}
+
+__device__ __forceinline__ void split_digits(int X, int& d1, int& d2, int& d3) {
+    d3 = ((X + 64) & 127) - 64;
+    const int x1 = (X - d3) >> 7;
+    d2 = ((x1 + 64) & 127) - 64;
+    d1 = (x1 - d2) >> 7;
+}
+
+__device__ __forceinline__ float prepare_x(const void* x, int dtype, int n_in, int8_t* dig,
+                                           float* xs16, float* red, bool& finite) {
+    const int tid = threadIdx.x, n4 = n_in >> 2;
+    float amax = 0.f;
+    for (int i = tid; i < n4; i += blockDim.x) {
+        const float4 v = load_x4(x, dtype, i);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        if (!(fabsf(v.x) + fabsf(v.y) + fabsf(v.z) + fabsf(v.w) < INFINITY)) amax = INFINITY;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    if ((tid & 31) == 0) red[tid >> 5] = amax;
+    __syncthreads();
+    amax = 0.f;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) amax = fmaxf(amax, red[w]);
+    finite = amax < INFINITY;
+    int e = 0;
+    if (finite && amax > 0.f) frexpf(amax, &e);          // amax <= 2^e
+    const float scale = finite ? ldexpf(1.f, 20 - e) : 0.f;
+    for (int i = tid; i < n4; i += blockDim.x) {
+        const float4 v = load_x4(x, dtype, i);
+        const int X0 = __float2int_rn(v.x * scale), X1 = __float2int_rn(v.y * scale);
+        const int X2 = __float2int_rn(v.z * scale), X3 = __float2int_rn(v.w * scale);
+        int a[4], b[4], c[4];
+        split_digits(X0, a[0], b[0], c[0]); split_digits(X1, a[1], b[1], c[1]);
+        split_digits(X2, a[2], b[2], c[2]); split_digits(X3, a[3], b[3], c[3]);
+        auto pack = [](const int (&d)[4]) {
+            return (d[0] & 0xFF) | ((d[1] & 0xFF) << 8) | ((d[2] & 0xFF) << 16) | (static_cast<uint32_t>(d[3] & 0xFF) << 24);
+        };
+        reinterpret_cast<uint32_t*>(dig)[i] = pack(a);
+        reinterpret_cast<uint32_t*>(dig + n_in)[i] = pack(b);
+        reinterpret_cast<uint32_t*>(dig + 2 * n_in)[i] = pack(c);
+        int s = X0 + X1 + X2 + X3;        // the 4 lanes of an aligned quad cover one 16-chunk
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+        if ((tid & 3) == 0) xs16[i >> 2] = static_cast<float>(s);
+    }
+    __syncthreads();
+    return finite ? ldexpf(1.f, e - 20) : 0.f;
+}
+
+template <int L, int WT>
+__global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaArgs a) {
+    using G = Geo<L>;
+    constexpr int WK = kMmaWarps / WT;
+    constexpr bool SB6 = L <= ML_SB6_6;
+    constexpr bool A_UNSIGNED = L != ML_SYM8;
+    extern __shared__ __align__(16) unsigned char smem[];
+    const QView& q = a.t[blockIdx.y];
+    const int n_in = q.cols;
+    int8_t* dig = reinterpret_cast<int8_t*>(smem);
+    float* xs16 = reinterpret_cast<float*>(smem + 3 * n_in);
+    float* red = xs16 + (n_in >> 4);                      // [kMmaWarps * 16]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int tile = blockIdx.x * WT + warp / WK, ks = warp % WK;
+    const int r0 = min(tile * 16 + g, q.rows - 1), r1 = min(tile * 16 + g + 8, q.rows - 1);
+    const int n_iters = n_in / G::KI;
+
+    // first weight loads go out before the activations are touched
+    Frag<L> cur;
+    const bool have_work = ks < n_iters;
+    if (have_work) load_frag<L>(cur, q, r0, r1, ks, t);
+
+    const size_t esz = (a.x_dtype == RWKVQ_F32) ? 4 : 2;
+    const char* xv = static_cast<const char*>(a.x) + (a.fused ? blockIdx.y * a.ldx * esz : 0);
+    bool finite;
+    const float unscale = prepare_x(xv, a.x_dtype, n_in, dig, xs16, red, finite);
+
+    // which B columns this lane feeds: column 2t+dg of MMA set 1, column 2t of set 2
+    const bool b_set1 = (g >> 1) == t;
+    const bool b_set2 = g == 2 * t;
+    const int8_t* dig1 = dig + (g & 1) * n_in;
+    const int8_t* dig3 = dig + 2 * n_in;
+
+    float acc0 = 0.f, acc1 = 0.f;     // rows g, g+8
+    for (int it = ks; it < n_iters; it += WK) {
+        Frag<L> nxt;
+        if (it + WK < n_iters) load_frag<L>(nxt, q, r0, r1, it + WK, t);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int blk = it * 8 + 2 * t + h;            // block index along the row
+            int c[4] = {0, 0, 0, 0}, e[4] = {0, 0, 0, 0};
+            if (SB6) {
+                uint4 b1lo = make_uint4(0, 0, 0, 0), b1hi = b1lo, b3lo = b1lo, b3hi = b1lo;
+                if (b_set1) {
+                    b1lo = *reinterpret_cast<const uint4*>(dig1 + blk * 32);
+                    b1hi = *reinterpret_cast<const uint4*>(dig1 + blk * 32 + 16);
+                }
+                if (b_set2) {
+                    b3lo = *reinterpret_cast<const uint4*>(dig3 + blk * 32);
+                    b3hi = *reinterpret_cast<const uint4*>(dig3 + blk * 32 + 16);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t a0, a1, a2, a3;
+                    a_words<L>(cur.ca, cur.pa, h, j, a0, a2);
+                    a_words<L>(cur.cb, cur.pb, h, j, a1, a3);
+                    mma_i8<A_UNSIGNED>(c, a0, a1, a2, a3, word_of(b1lo, j), word_of(b1hi, j));
+                    mma_i8<A_UNSIGNED>(e, a0, a1, a2, a3, word_of(b3lo, j), word_of(b3hi, j));
+                }
+            } else {
+                uint4 b1 = make_uint4(0, 0, 0, 0), b3 = b1;
+                if (b_set1) b1 = *reinterpret_cast<const uint4*>(dig1 + blk * 16);
+                if (b_set2) b3 = *reinterpret_cast<const uint4*>(dig3 + blk * 16);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    uint32_t a0, a1, a2, a3;
+                    a_words<L>(cur.ca, cur.pa, h, j, a0, a2);
+                    a_words<L>(cur.cb, cur.pb, h, j, a1, a3);
+                    mma_i8<A_UNSIGNED>(c, a0, a1, a2, a3, word_of(b1, 2 * j), word_of(b1, 2 * j + 1));
+                    mma_i8<A_UNSIGNED>(e, a0, a1, a2, a3, word_of(b3, 2 * j), word_of(b3, 2 * j + 1));
+                }
+            }
+            // c[0], c[1]: row g digits 1, 2;  c[2], c[3]: row g+8;  e[0], e[2]: digit 3
+            const float f0 = fmaf(static_cast<float>(c[0]), 16384.f, fmaf(static_cast<float>(c[1]), 128.f, static_cast<float>(e[0])));
+            const float f1 = fmaf(static_cast<float>(c[2]), 16384.f, fmaf(static_cast<float>(c[3]), 128.f, static_cast<float>(e[2])));
+            if (SB6) {
+                const float xsum = xs16[2 * blk] + xs16[2 * blk + 1];
+                float s0, m0, s1, m1;
+                sb6_scale_min(cur.ma.x, cur.ma.y, cur.ma.z, 2 * t + h, half_bits_to_float(cur.ma.w & 0xFFFFu),
+                              half_bits_to_float(cur.ma.w >> 16), s0, m0);
+                sb6_scale_min(cur.mb.x, cur.mb.y, cur.mb.z, 2 * t + h, half_bits_to_float(cur.mb.w & 0xFFFFu),
+                              half_bits_to_float(cur.mb.w >> 16), s1, m1);
+                acc0 = fmaf(s0, f0, fmaf(m0, xsum, acc0));
+                acc1 = fmaf(s1, f1, fmaf(m1, xsum, acc1));
+            } else {
+                const int jb = 2 * t + h;
+                const uint32_t wa = jb < 4 ? cur.ma.x : cur.ma.y, wb = jb < 4 ? cur.mb.x : cur.mb.y;
+                const int qa = static_cast<int8_t>((wa >> (8 * (jb & 3))) & 0xFFu);
+                const int qb = static_cast<int8_t>((wb >> (8 * (jb & 3))) & 0xFFu);
+                const float s0 = half_roundtrip(__fmul_rn(static_cast<float>(qa), half_bits_to_float(cur.ma.z)));
+                const float s1 = half_roundtrip(__fmul_rn(static_cast<float>(qb), half_bits_to_float(cur.mb.z)));
+                const float off = (L == ML_SYM6) ? -32.f * xs16[blk] : 0.f;   // codes are stored +32
+                acc0 = fmaf(s0, f0 + off, acc0);
+                acc1 = fmaf(s1, f1 + off, acc1);
+            }
+        }
+        cur = nxt;
+    }
+
+    // the 4 lanes of a quad hold the 8 blocks of each iteration
+    acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 1); acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 2);
+    acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, 1); acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, 2);
+    __syncthreads();                       // `red` was used by prepare_x
+    if (t == 0) { red[warp * 16 + g] = acc0; red[warp * 16 + g + 8] = acc1; }
+    __syncthreads();
+    if (threadIdx.x < WT * 16) {
+        const int tl = threadIdx.x >> 4, r = threadIdx.x & 15;
+        const int row = (blockIdx.x * WT + tl) * 16 + r;
+        if (row < q.rows) {
+            float v = 0.f;
+#pragma unroll
+            for (int k = 0; k < WK; ++k) v += red[(tl * WK + k) * 16 + r];
+            v = finite ? v * unscale : NAN;
+            const long long idx = (a.fused ? static_cast<long long>(blockIdx.y) * a.ldy : 0) + row;
+            if (a.epilogue == RWKVQ_EPI_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
+            else if (a.epilogue == RWKVQ_EPI_ADD) v = __fadd_rn(v, a.resid[idx]);
+            a.y[idx] = v;
+        }
+    }
+}
+
+// ------------------------------------------------------------ relayout kernels
+__global__ void relayout_meta_kernel(QView t, uint8_t* out) {
+    const int nsb = t.cols >> 8;
+    const size_t total = static_cast<size_t>(t.rows) * nsb;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        uint8_t* o = out + i * 16;
+        for (int k = 0; k < 12; ++k) o[k] = t.qsqm[i * 12 + k];
+        const uint16_t d = reinterpret_cast<const uint16_t*>(t.d)[i];
+        const uint16_t dm = reinterpret_cast<const uint16_t*>(t.dm)[i];
+        o[12] = d & 0xFF; o[13] = d >> 8; o[14] = dm & 0xFF; o[15] = dm >> 8;
+    }
+}
+
+// One output word per thread.  `mode` 5: sb6@5, 6: sb6@6 (two words per block), 16: sym@6.
+__global__ void relayout_planes_kernel(QView t, uint32_t* out, int mode) {
+    const size_t words_per_row = mode == 5 ? (t.cols >> 5) : mode == 6 ? (t.cols >> 4) : (t.cols >> 4);
+    const size_t total = static_cast<size_t>(t.rows) * words_per_row;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t r = i / words_per_row, wi = i % words_per_row;
+        const uint8_t* qh = t.qh + r * (t.cols >> 3);
+        const uint8_t* qh2 = t.qh2 ? t.qh2 + r * (t.cols >> 3) : nullptr;
+        uint32_t w = 0;
+        if (mode == 5) {
+            const int c0 = static_cast<int>(wi) * 32;
+            for (int G = 0; G < 8; ++G)
+                for (int b = 0; b < 4; ++b) {
+                    const int wt = G < 4 ? 4 * G + b : 16 + 4 * (G - 4) + b;
+                    w |= plane_bit(qh, c0 + wt) << (8 * b + G);
+                }
+        } else if (mode == 6) {
+            const int c0 = static_cast<int>(wi >> 1) * 32, second = static_cast<int>(wi & 1);
+            for (int j = 0; j < 4; ++j)
+                for (int b = 0; b < 4; ++b) {
+                    const int wt = second * 16 + 4 * j + b;
+                    w |= plane_bit(qh, c0 + wt) << (8 * b + 2 * j);
+                    w |= plane_bit(qh2, c0 + wt) << (8 * b + 2 * j + 1);
+                }
+        } else {
+            const int c0 = static_cast<int>(wi) * 16;
+            for (int G = 0; G < 4; ++G)
+                for (int b = 0; b < 4; ++b) {
+                    const int wt = G < 2 ? 4 * G + b : 8 + 4 * (G - 2) + b;
+                    w |= plane_bit(qh, c0 + wt) << (8 * b + 2 * G);
+                    w |= plane_bit(qh2, c0 + wt) << (8 * b + 2 * G + 1);
+                }
+        }
+        out[i] = w;
+    }
+}
+
+int mma_layout_of(const rwkvq_qtensor& t) {
+    if (t.kind == RWKVQ_KIND_SB6 && t.dev_meta && (t.bits == 4 || t.dev_planes)) return ML_SB6_4 + (t.bits - 4);
+    if (t.kind == RWKVQ_KIND_SYM && t.bits == 8) return ML_SYM8;
+    if (t.kind == RWKVQ_KIND_SYM && t.bits == 6 && t.dev_planes) return ML_SYM6;
+    return -1;
+}
+
+static int pick_wt(int rows) {
+    const int tiles = (rows + 15) / 16;
+    for (int wt = 8; wt > 1; wt >>= 1)
+        if ((tiles + wt - 1) / wt >= 148) return wt;
+    return 1;
+}
+
+template <int L, int WT>
+static int launch_one(const MmaArgs& a, int rows, int cols, int n_mats, cudaStream_t s) {
+    const size_t smem = 3 * static_cast<size_t>(cols) + 4 * (cols / 16) + kMmaWarps * 16 * 4;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<L, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem));
+        if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "gemv_mma: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    }
+    const int tiles = (rows + 15) / 16;
+    gemv_mma_kernel<L, WT><<<dim3((tiles + WT - 1) / WT, n_mats), kMmaWarps * 32, smem, s>>>(a);
+    return RWKVQ_OK;
+}
+
+template <int L>
+static int launch_wt(const MmaArgs& a, int rows, int cols, int n_mats, cudaStream_t s) {
+    switch (pick_wt(rows)) {
+        case 8: return launch_one<L, 8>(a, rows, cols, n_mats, s);
+        case 4: return launch_one<L, 4>(a, rows, cols, n_mats, s);
+        case 2: return launch_one<L, 2>(a, rows, cols, n_mats, s);
+        default: return launch_one<L, 1>(a, rows, cols, n_mats, s);
+    }
+}
+
+// Launch the single-vector tensor-core GEMV for `n_mats` same-shape matrices.
+int launch_gemv_mma(int layout, const rwkvq_qtensor* ts, int n_mats, const void* x, int x_dtype,
+                    long long ldx, float* y, long long ldy, int epilogue, const float* resid,
+                    int fused, cudaStream_t s) {
+    MmaArgs a{};
+    for (int k = 0; k < n_mats; ++k) a.t[k] = make_view(ts[k]);
+    a.x = x; a.x_dtype = x_dtype; a.ldx = ldx; a.y = y; a.ldy = ldy;
+    a.resid = resid; a.epilogue = epilogue; a.fused = fused;
+    const int rows = ts[0].rows, cols = ts[0].cols;
+    int rc;
+    switch (layout) {
+        case ML_SB6_4: rc = launch_wt<ML_SB6_4>(a, rows, cols, n_mats, s); break;
+        case ML_SB6_5: rc = launch_wt<ML_SB6_5>(a, rows, cols, n_mats, s); break;
+        case ML_SB6_6: rc = launch_wt<ML_SB6_6>(a, rows, cols, n_mats, s); break;
+        case ML_SYM6: rc = launch_wt<ML_SYM6>(a, rows, cols, n_mats, s); break;
+        default: rc = launch_wt<ML_SYM8>(a, rows, cols, n_mats, s); break;
+    }
+    return rc;
+}
+
+}  // namespace rwkvq
+
+using namespace rwkvq;
+
+extern "C" {
+
+int rwkvq_relayout_meta(const rwkvq_qtensor* t, void* meta_out, void* stream) {
+    int rc = validate_qtensor(t, "rwkvq_relayout_meta");
+    if (rc) return rc;
+    RWKVQ_REQUIRE(t->kind == RWKVQ_KIND_SB6, RWKVQ_E_DTYPE, "rwkvq_relayout_meta: only sb6 tensors have scale records");
+    RWKVQ_REQUIRE(meta_out != nullptr && aligned(meta_out, 16), RWKVQ_E_ALIGN, "rwkvq_relayout_meta: out must be 16-byte aligned");
+    relayout_meta_kernel<<<148 * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(make_view(*t),
+                                                                                 static_cast<uint8_t*>(meta_out));
+    return check_launch("rwkvq_relayout_meta");
+}
+
+int rwkvq_relayout_planes(const rwkvq_qtensor* t, void* planes_out, void* stream) {
+    int rc = validate_qtensor(t, "rwkvq_relayout_planes");
+    if (rc) return rc;
+    int mode = 0;
+    if (t->kind == RWKVQ_KIND_SB6 && t->bits == 5) mode = 5;
+    else if (t->kind == RWKVQ_KIND_SB6 && t->bits == 6) mode = 6;
+    else if (t->kind == RWKVQ_KIND_SYM && t->bits == 6) mode = 16;
+    RWKVQ_REQUIRE(mode != 0, RWKVQ_E_DTYPE, "rwkvq_relayout_planes: tensor has no bit-planes");
+    RWKVQ_REQUIRE(planes_out != nullptr && aligned(planes_out, 16), RWKVQ_E_ALIGN,
+                  "rwkvq_relayout_planes: out must be 16-byte aligned");
+    relayout_planes_kernel<<<148 * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        make_view(*t), static_cast<uint32_t*>(planes_out), mode);
+    return check_launch("rwkvq_relayout_planes");
+}
+
+}  // extern "C"

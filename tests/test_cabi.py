@@ -34,8 +34,8 @@ def test_error_strings_and_struct_layout():
     assert lib.rwkvq_abi_version() >= 1
     assert lib.rwkvq_strerror(0) == b"ok"
     assert b"shape" in lib.rwkvq_strerror(-1)
-    # rwkvq_qtensor: six int32 then nine pointers
-    assert ctypes.sizeof(_lib.QTensorStruct) == 6 * 4 + 9 * 8
+    # rwkvq_qtensor: six int32 then eleven pointers
+    assert ctypes.sizeof(_lib.QTensorStruct) == 6 * 4 + 11 * 8
     assert _lib.QTensorStruct.codes.offset == 24
 
 
