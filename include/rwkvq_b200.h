@@ -23,6 +23,7 @@
 #ifndef RWKVQ_B200_H
 #define RWKVQ_B200_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -89,7 +90,8 @@ typedef struct rwkvq_qtensor {
     /* Optional device-side relayout of the small side streams (same byte count as
      * the file buffers, made once at load by rwkvq_relayout_*; codes stay as in the
      * file).  When both are NULL the kernels read the file buffers only.
-     *   dev_meta    sb6: [rows, cols/256] records of 16 B = qsqm (12 B) | d | dm
+     *   dev_meta    sb6: [rows, cols/256] records of 16 B: word t = the scale/min codes of
+     *               blocks 2t, 2t+1 and one byte of (d | dm << 16)
      *   dev_planes  bit-planes regrouped per block so that one shift + mask yields
      *               the high code bits of 4 weights (see rwkvq_relayout_planes) */
     const void* dev_meta;
@@ -151,6 +153,64 @@ int rwkvq_gemv_fused(const rwkvq_qtensor* ts_host, int K, const void* x, int x_d
  */
 int rwkvq_gemv_t(const rwkvq_qtensor* t, const float* x, int N, int64_t ldx,
                  float* y, int64_t ldy, int act, int round_w, void* stream);
+
+
+/*
+ * WKV-7 recurrence with state in and out, any T >= 1, head size 64:
+ *   sa = S a;  S = S diag(w) + sa b^T + v k^T;  y = S r      (S indexed [value, key])
+ * Stands behind wkv7_infer(r, w, k, v, a, b, state) -> (out, new_state) of the
+ * external rwkv_metal package as called at backends/metal/quant_model.py:118-125
+ * (math: models/rwkv7_ref.py:244-254).  r..b [B, T, H, 64] fp32 (w is the decay),
+ * h_in [B, H, 64, 64] or NULL for a zero state, h_out may alias h_in.
+ */
+int rwkvq_wkv7(const float* r, const float* w, const float* k, const float* v, const float* a,
+               const float* b, const float* h_in, float* out, float* h_out, int B, int T, int H,
+               int head_size, void* stream);
+
+/*
+ * (group_norm(wkv) * ln_w + ln_b + (sum_head r*k*r_k) * v) * g for N rows of H heads.
+ * Stands behind fused_tail.wkv_tail (backends/metal/fused_tail.py:92-110).
+ */
+int rwkvq_wkv_tail(const float* wkv, const float* r, const float* k, const float* v, const float* r_k,
+                   const float* ln_w, const float* ln_b, const float* g, float* out, int N, int H,
+                   int head_size, float eps, void* stream);
+
+/* One layer / one model as device pointers; dense vectors are fp32 [D] already in the
+ * reference's load-time precision (quant_model.py:128-154). LoRA tensors are stored [in, out]. */
+typedef struct rwkvq_layer {
+    const float *ln1_w, *ln1_b, *ln2_w, *ln2_b;
+    const float* x_mix;                 /* [6, D]: r, w, k, v, a, g lerp coefficients */
+    const float *w0, *a0, *v0;          /* [D]; v0 NULL on layer 0 */
+    const float *k_k, *k_a, *r_k, *lnx_w, *lnx_b;
+    const float* ffn_x_k;
+    rwkvq_qtensor w1, w2, a1, a2, v1, v2, g1, g2;
+    rwkvq_qtensor Wr, Wk, Wv, Wo, Wfk, Wfv;
+} rwkvq_layer;
+
+typedef struct rwkvq_model {
+    int32_t n_layer, n_embd, head_size, vocab_size, ffn_dim, max_rank;
+    rwkvq_qtensor emb, head;
+    const float *ln0_w, *ln0_b, *lnout_w, *lnout_b;
+    const rwkvq_layer* layers;          /* HOST array [n_layer] */
+} rwkvq_model;
+
+/* Bytes of device scratch rwkvq_decode_step needs for batch B (logits included). */
+size_t rwkvq_decode_workspace_bytes(const rwkvq_model* m_host, int B);
+
+/*
+ * One token for B independent streams: embedding gather, all layers, head.
+ * Stands behind QuantRWKV7.forward_stateful with T = 1
+ * (backends/metal/quant_model.py:964-990; block :827-836, time-mix :638-728,
+ * channel-mix :803-809).  State is updated in place:
+ *   wkv_host[l]    [B, H, 64, 64]   tshift_host[l], cshift_host[l]  [B, D]
+ * (host arrays of device pointers; a fresh stream starts from zeros).
+ * logits [B, vocab] fp32 (NULL: kept in the workspace), next_tokens [B] int64 greedy
+ * argmax (NULL: skipped), tokens [B] int64 on the device.
+ */
+int rwkvq_decode_step(const rwkvq_model* m_host, int B, const int64_t* tokens,
+                      float* const* wkv_host, float* const* tshift_host, float* const* cshift_host,
+                      void* workspace, size_t workspace_bytes, float* logits, int64_t* next_tokens,
+                      void* stream);
 
 /*
  * Load-time relayout of the side streams of an sb6 / sym tensor for the decode

@@ -29,6 +29,26 @@ class QTensorStruct(C.Structure):
                 ("dev_meta", C.c_void_p), ("dev_planes", C.c_void_p)]
 
 
+_FP = C.c_void_p
+
+
+class LayerStruct(C.Structure):
+    """``rwkvq_layer`` of the header."""
+    _fields_ = ([(n, _FP) for n in ("ln1_w", "ln1_b", "ln2_w", "ln2_b", "x_mix", "w0", "a0", "v0",
+                                    "k_k", "k_a", "r_k", "lnx_w", "lnx_b", "ffn_x_k")]
+                + [(n, QTensorStruct) for n in ("w1", "w2", "a1", "a2", "v1", "v2", "g1", "g2",
+                                                "Wr", "Wk", "Wv", "Wo", "Wfk", "Wfv")])
+
+
+class ModelStruct(C.Structure):
+    """``rwkvq_model`` of the header."""
+    _fields_ = ([(n, C.c_int32) for n in ("n_layer", "n_embd", "head_size", "vocab_size", "ffn_dim",
+                                          "max_rank")]
+                + [("emb", QTensorStruct), ("head", QTensorStruct)]
+                + [(n, _FP) for n in ("ln0_w", "ln0_b", "lnout_w", "lnout_b")]
+                + [("layers", C.POINTER(LayerStruct))])
+
+
 class RwkvqError(RuntimeError):
     def __init__(self, code: int, name: str, detail: str):
         super().__init__(f"{name} failed: {code} ({detail})")
@@ -48,6 +68,12 @@ _PROTOS = {
                              C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
     "rwkvq_gemv_fused": (C.c_int, [C.POINTER(QTensorStruct), C.c_int, C.c_void_p, C.c_int,
                                    C.c_void_p, C.c_void_p]),
+    "rwkvq_wkv7": (C.c_int, [C.c_void_p] * 9 + [C.c_int] * 4 + [C.c_void_p]),
+    "rwkvq_wkv_tail": (C.c_int, [C.c_void_p] * 9 + [C.c_int] * 3 + [C.c_float, C.c_void_p]),
+    "rwkvq_decode_workspace_bytes": (C.c_size_t, [C.POINTER(ModelStruct), C.c_int]),
+    "rwkvq_decode_step": (C.c_int, [C.POINTER(ModelStruct), C.c_int, C.c_void_p,
+                                    C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                    C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rwkvq_relayout_meta": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_void_p]),
     "rwkvq_relayout_planes": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_void_p]),
     "rwkvq_gemv_t": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_int64,

@@ -3,6 +3,9 @@ from .ops import DeviceQT  # noqa: F401
 from .quant_linear_gw import GwQuantLinear, GwQuantLinearFused  # noqa: F401
 from .quant_linear_sym import SymQuantLinear, SymQuantLinearFused  # noqa: F401
 from .quant_linear_v2 import DenseLinear, QuantLinearV2  # noqa: F401
+from .fused_tail import can_fuse_tail, wkv_tail  # noqa: F401
+from .wkv7 import wkv7_infer, wkv7_train  # noqa: F401
+from .quant_model import Decoder, QuantRWKV7  # noqa: F401
 
 
 def linear_for(qt, device="cuda"):

@@ -113,6 +113,10 @@ class DeviceQT:
     def nbytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.bufs)
 
+    def nbytes_file(self) -> int:
+        """Bytes of the tensor in the file format (the relayout copies excluded)."""
+        return sum(t.numel() * t.element_size() for t in self.bufs[:9])
+
     def slice_rows(self, a: int, b: int) -> "DeviceQT":
         """Rows [a, b) as a view: every layout stores rows first and blocks along
         the columns, so any row range is a valid tensor (formats/reader.py:130-152)."""

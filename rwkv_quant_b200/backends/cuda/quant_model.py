@@ -1,0 +1,344 @@
+"""RWKV-7 (x070) inference model over a ``.rwkvq`` checkpoint on the CUDA kernels.
+
+Same surface as the reference's ``QuantRWKV7`` (backends/metal/quant_model.py:839-990):
+``QuantRWKV7(load_raw(path))``, ``init_state(B)``, ``step`` / ``forward_stateful(idx,
+states, last_only, tail_only)``, ``forward_hidden``, ``__call__(idx)``; plus
+``generate`` (the greedy loop of tests/bench_decode_vs_gguf.py:84-96) and
+``decoder(B)`` which replays one whole token as a CUDA graph.
+
+Two execution paths share the same weights (kept packed on the device):
+  T == 1   one call of ``rwkvq_decode_step`` (all kernels of a token launched from C)
+  T  > 1   per-layer ops over all B*T positions: quantized linears, LoRA products,
+           ``wkv7_infer`` and ``wkv_tail`` are library kernels; layer norms, lerps and
+           gates are elementwise torch ops on the device.
+Weight precision follows the reference's loader (quant_model.py:128-154, 245-262):
+quantized linears are used exactly as coded; every other tensor is rounded to bf16,
+then to fp16 when it is 2-D with min(shape) >= 32 (LoRA, embedding, r_k).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.nn.functional as F
+
+from . import ops
+from .fused_tail import wkv_tail
+from .quant_linear_gw import GEMM_MIN_BATCH_NB
+from .wkv7 import wkv7_infer
+from ... import _lib
+from ..._lib import LayerStruct, ModelStruct
+
+_DECAY = -0.606531     # -exp(-0.5), quant_model.py:701
+
+
+def _dense_param(qt, device):
+    """A non-linear tensor as fp32 on the device in the reference's load-time precision."""
+    if qt.bits >= 16:
+        t = qt.dense.float()
+    else:
+        dq = ops.DeviceQT(qt, device, relayout=False)
+        t = ops.dequant(dq.bufs, dq.meta, torch.float32, True).cpu()
+    if t.ndim == 2 and min(t.shape) >= 32:
+        t = t.half().float()
+    return t.to(device).contiguous()
+
+
+class _Layer:
+    pass
+
+
+class QuantRWKV7:
+    def __init__(self, ckpt, device="cuda", gemm_min_batch=GEMM_MIN_BATCH_NB):
+        if ckpt.naming != "world":
+            raise NotImplementedError("only world-naming checkpoints are supported")
+        _lib.load(check_device=True)
+        self.device = torch.device(device)
+        self.naming = ckpt.naming
+        self.n_layer, self.n_embd = ckpt.n_layer, ckpt.n_embd
+        self.head_size = ckpt.head_size
+        self.n_head = ckpt.n_embd // ckpt.head_size
+        self.vocab_size = ckpt.vocab_size
+        self.gemm_min_batch = int(gemm_min_batch)
+        T = ckpt.tensors
+        dev = self.device
+        dq = lambda key: ops.DeviceQT(T[key], dev)
+        vec = lambda key: _dense_param(T[key], dev).reshape(-1)
+
+        self.emb, self.head = dq("emb.weight"), dq("head.weight")
+        self.ln0 = (vec("blocks.0.ln0.weight"), vec("blocks.0.ln0.bias"))
+        self.ln_out = (vec("ln_out.weight"), vec("ln_out.bias"))
+        self.blocks = []
+        for i in range(self.n_layer):
+            p, a, f = f"blocks.{i}.", f"blocks.{i}.att.", f"blocks.{i}.ffn."
+            L = _Layer()
+            L.ln1 = (vec(p + "ln1.weight"), vec(p + "ln1.bias"))
+            L.ln2 = (vec(p + "ln2.weight"), vec(p + "ln2.bias"))
+            L.x_mix = torch.stack([vec(a + n) for n in ("x_r", "x_w", "x_k", "x_v", "x_a", "x_g")]).contiguous()
+            L.w0, L.a0 = vec(a + "w0"), vec(a + "a0")
+            L.v0 = vec(a + "v0") if i > 0 else None
+            L.k_k, L.k_a, L.r_k = vec(a + "k_k"), vec(a + "k_a"), vec(a + "r_k")
+            L.lnx = (vec(a + "ln_x.weight"), vec(a + "ln_x.bias"))
+            L.ffn_x_k = vec(f + "x_k")
+            for nm in ("w1", "w2", "a1", "a2", "g1", "g2") + (("v1", "v2") if i > 0 else ()):
+                setattr(L, nm, dq(a + nm))
+            if i == 0:
+                L.v1 = L.v2 = None
+            L.Wr, L.Wk = dq(a + "receptance.weight"), dq(a + "key.weight")
+            L.Wv, L.Wo = dq(a + "value.weight"), dq(a + "output.weight")
+            L.Wfk, L.Wfv = dq(f + "key.weight"), dq(f + "value.weight")
+            self.blocks.append(L)
+        self.ffn_dim = self.blocks[0].Wfk.rows
+        self.max_rank = max(max(L.w1.cols, L.a1.cols, L.g1.cols, L.v1.cols if L.v1 else 0)
+                            for L in self.blocks)
+        self._build_struct()
+        self._ws = {}
+        torch.cuda.synchronize(dev)
+
+    # ------------------------------------------------------------------ C descriptors
+    def _build_struct(self):
+        n = self.n_layer
+        self._layers_c = (LayerStruct * n)()
+        p = lambda t: t.data_ptr() if t is not None else None
+        for i, L in enumerate(self.blocks):
+            s = self._layers_c[i]
+            s.ln1_w, s.ln1_b, s.ln2_w, s.ln2_b = p(L.ln1[0]), p(L.ln1[1]), p(L.ln2[0]), p(L.ln2[1])
+            s.x_mix, s.w0, s.a0, s.v0 = p(L.x_mix), p(L.w0), p(L.a0), p(L.v0)
+            s.k_k, s.k_a, s.r_k = p(L.k_k), p(L.k_a), p(L.r_k)
+            s.lnx_w, s.lnx_b, s.ffn_x_k = p(L.lnx[0]), p(L.lnx[1]), p(L.ffn_x_k)
+            for nm in ("w1", "w2", "a1", "a2", "v1", "v2", "g1", "g2", "Wr", "Wk", "Wv", "Wo", "Wfk", "Wfv"):
+                d = getattr(L, nm)
+                if d is not None:
+                    setattr(s, nm, d.struct)
+        m = ModelStruct()
+        m.n_layer, m.n_embd, m.head_size = self.n_layer, self.n_embd, self.head_size
+        m.vocab_size, m.ffn_dim, m.max_rank = self.vocab_size, self.ffn_dim, self.max_rank
+        m.emb, m.head = self.emb.struct, self.head.struct
+        m.ln0_w, m.ln0_b = p(self.ln0[0]), p(self.ln0[1])
+        m.lnout_w, m.lnout_b = p(self.ln_out[0]), p(self.ln_out[1])
+        m.layers = C.cast(self._layers_c, C.POINTER(LayerStruct))
+        self._model_c = m
+
+    def weight_nbytes(self, with_emb=False) -> int:
+        """File-format bytes a decode step streams (embedding excluded by default)."""
+        n = self.head.nbytes_file()
+        for L in self.blocks:
+            for nm in ("w1", "w2", "a1", "a2", "v1", "v2", "g1", "g2", "Wr", "Wk", "Wv", "Wo", "Wfk", "Wfv"):
+                d = getattr(L, nm)
+                if d is not None:
+                    n += d.nbytes_file()
+        return n + (self.emb.nbytes_file() if with_emb else 0)
+
+    # ------------------------------------------------------------------ state
+    def init_state(self, batch_size: int = 1):
+        """[(wkv [B,H,S,S], tmix_shift, cmix_shift)] * n_layer; shifts start as None
+        (= zeros), as in the reference (quant_model.py:902-908)."""
+        H, S = self.n_head, self.head_size
+        return [(torch.zeros((batch_size, H, S, S), device=self.device), None, None)
+                for _ in range(self.n_layer)]
+
+    @staticmethod
+    def clone_state(states):
+        """Deep copy; T == 1 steps update a state in place, so keep a clone to roll back."""
+        return [tuple(None if t is None else t.clone() for t in st) for st in states]
+
+    def _materialize(self, states, B):
+        out = []
+        for wkv, ts, cs in states:
+            z = lambda t: (torch.zeros((B, 1, self.n_embd), device=self.device) if t is None
+                           else t.reshape(B, 1, self.n_embd).contiguous().float())
+            out.append((wkv.contiguous().float(), z(ts), z(cs)))
+        return out
+
+    # ------------------------------------------------------------------ T == 1
+    def _workspace(self, B):
+        if B not in self._ws:
+            n = _lib.load().rwkvq_decode_workspace_bytes(C.byref(self._model_c), B)
+            self._ws[B] = torch.empty(n, dtype=torch.uint8, device=self.device)
+        return self._ws[B]
+
+    def _decode(self, tokens, states, logits=None, next_tokens=None):
+        """tokens [B] int64 on the device; states materialised; updates them in place."""
+        B = tokens.shape[0]
+        ws = self._workspace(B)
+        arr = lambda k: (C.c_void_p * self.n_layer)(*[st[k].data_ptr() for st in states])
+        if logits is None:
+            logits = torch.empty((B, self.vocab_size), dtype=torch.float32, device=self.device)
+        lib = _lib.load()
+        _lib.check(lib.rwkvq_decode_step(C.byref(self._model_c), B, tokens.data_ptr(), arr(0), arr(1), arr(2),
+                                         ws.data_ptr(), ws.numel(), logits.data_ptr(),
+                                         None if next_tokens is None else next_tokens.data_ptr(),
+                                         _lib.stream_ptr()), "rwkvq_decode_step")
+        return logits
+
+    # ------------------------------------------------------------------ T > 1
+    def _linear(self, dq, x, epilogue=_lib.EPI_NONE, resid=None):
+        """x [N, IN] fp32 -> [N, OUT]: weight-streaming GEMV below the crossover, else
+        dequantise once and use a dense fp32 GEMM."""
+        if x.shape[0] < self.gemm_min_batch:
+            return ops.gemv(dq.bufs, dq.meta, x, epilogue, resid)
+        y = x @ ops.dequant(dq.bufs, dq.meta, torch.float32, False).t()
+        if epilogue == _lib.EPI_RELU2:
+            y = torch.relu(y) ** 2
+        elif epilogue == _lib.EPI_ADD:
+            y = y + resid
+        return y
+
+    @staticmethod
+    def _shift(x, prev):
+        return torch.cat([prev, x[:, :-1]], dim=1), x[:, -1:].contiguous()
+
+    def _block_seq(self, i, L, x, v_first, state):
+        B, T, D = x.shape
+        H, S = self.n_head, self.head_size
+        wkv, ts, cs = state
+        lin = lambda dq, t, **kw: self._linear(dq, t.reshape(B * T, -1).contiguous(), **kw)
+        lora = lambda dq, t, act=0: ops.gemv_t(dq.bufs, dq.meta, t.reshape(B * T, -1).contiguous(), act, True)
+        xn = F.layer_norm(x, (D,), *L.ln1)
+        shifted, ts = self._shift(xn, ts)
+        xx = shifted - xn
+        xr, xw, xk, xv, xa, xg = (xn + xx * L.x_mix[j] for j in range(6))
+        r, k, v = lin(L.Wr, xr), lin(L.Wk, xk), lin(L.Wv, xv)
+        y_w = lora(L.w2, lora(L.w1, xw, 1))
+        y_a = lora(L.a2, lora(L.a1, xa))
+        g = lora(L.g2, lora(L.g1, xg, 2))
+        w = torch.exp(_DECAY * torch.sigmoid(y_w + L.w0))
+        a = torch.sigmoid(y_a + L.a0)
+        kk = (k * L.k_k).reshape(B, T, H, S)
+        kk = kk / torch.sqrt((kk * kk).sum(-1, keepdim=True) + 1e-12)
+        k = k * (1.0 + (a - 1.0) * L.k_a)
+        if i == 0:
+            v_first = v
+        else:
+            v = v + (v_first - v) * torch.sigmoid(lora(L.v2, lora(L.v1, xv)) + L.v0)
+        r4 = lambda t: t.reshape(B, T, H, S)
+        out, wkv = wkv7_infer(r4(r), r4(w), r4(k), r4(v), -kk, kk * r4(a), wkv)
+        og = wkv_tail(out, r, k, v, L.r_k, L.lnx[0], L.lnx[1], g, H, S)
+        x = lin(L.Wo, og, epilogue=_lib.EPI_ADD, resid=x.reshape(B * T, D).contiguous()).reshape(B, T, D)
+        xn = F.layer_norm(x, (D,), *L.ln2)
+        shifted, cs = self._shift(xn, cs)
+        h = lin(L.Wfk, xn + (shifted - xn) * L.ffn_x_k, epilogue=_lib.EPI_RELU2)
+        x = self._linear(L.Wfv, h, epilogue=_lib.EPI_ADD, resid=x.reshape(B * T, D).contiguous()).reshape(B, T, D)
+        return x, v_first, (wkv, ts, cs)
+
+    def _embed(self, idx):
+        """Rows of the packed table in the loader's precision fp16(bf16(.))."""
+        flat = idx.reshape(-1).clamp(0, self.vocab_size - 1)
+        uniq, inv = torch.unique(flat, return_inverse=True)
+        if self.emb.kind == "dense":
+            rows = self.emb.bufs[0][uniq].float()
+        else:
+            bufs = [b[uniq].contiguous() if b.numel() and b.shape[0] == self.emb.rows else b
+                    for b in self.emb.bufs[:9]] + list(self.emb.bufs[9:])
+            meta = list(self.emb.meta)
+            meta[2] = uniq.numel()
+            bufs[9] = bufs[10] = torch.empty(0, dtype=torch.uint8, device=self.device)
+            rows = ops.dequant(bufs, meta, torch.float32, True)
+        return rows.half().float()[inv].reshape(*idx.shape, self.n_embd)
+
+    def forward_hidden(self, idx, states):
+        idx = torch.as_tensor(idx, device=self.device).long()
+        B, T = idx.shape
+        states = self._materialize(states, B)
+        x = F.layer_norm(self._embed(idx), (self.n_embd,), *self.ln0)
+        v_first, new_states = None, []
+        for i, (L, st) in enumerate(zip(self.blocks, states)):
+            x, v_first, st = self._block_seq(i, L, x, v_first, st)
+            new_states.append(st)
+        return F.layer_norm(x, (self.n_embd,), *self.ln_out), new_states
+
+    def forward_stateful(self, idx, states, last_only: bool = False, tail_only: int = 0):
+        """idx [B, T] -> (logits [B, T | 1 | tail_only, V] fp32, new_states).
+        T == 1 updates the given state tensors in place and returns them."""
+        idx = torch.as_tensor(idx, device=self.device).long()
+        B, T = idx.shape
+        if T == 1:
+            st = self._materialize(states, B)
+            logits = self._decode(idx.reshape(B).contiguous(), st)
+            return logits.reshape(B, 1, self.vocab_size), st
+        x, new_states = self.forward_hidden(idx, states)
+        if last_only:
+            x = x[:, -1:]
+        elif tail_only and T > tail_only:
+            x = x[:, -tail_only:]
+        n = x.shape[1]
+        logits = self._linear(self.head, x.reshape(B * n, self.n_embd).contiguous())
+        return logits.reshape(B, n, self.vocab_size), new_states
+
+    @property
+    def step(self):
+        return self.forward_stateful
+
+    def __call__(self, idx):
+        idx = torch.as_tensor(idx, device=self.device).long()
+        return self.forward_stateful(idx, self.init_state(idx.shape[0]))[0]
+
+    # ------------------------------------------------------------------ generation
+    def generate(self, idx, n_tokens: int):
+        """Greedy decode: prefill ``idx`` [B, T], then ``n_tokens`` argmax steps.
+        Returns (tokens [B, n_tokens], states)."""
+        idx = torch.as_tensor(idx, device=self.device).long()
+        B = idx.shape[0]
+        logits, st = self.forward_stateful(idx, self.init_state(B), last_only=True)
+        dec = self.decoder(B, states=st, use_graph=False)
+        tok = logits[:, -1].argmax(-1)
+        out = []
+        for _ in range(n_tokens):
+            out.append(tok.clone())
+            tok = dec.step(tok)
+        return torch.stack(out, dim=1), dec.states
+
+    def decoder(self, batch_size: int = 1, states=None, use_graph: bool = True):
+        return Decoder(self, batch_size, states, use_graph)
+
+
+class Decoder:
+    """Token-by-token greedy decoding of B streams with device-resident state.
+    ``step(tokens)`` feeds tokens [B] and returns the argmax next tokens [B] (device);
+    with ``use_graph`` the whole token (all kernels) is one CUDA-graph replay."""
+
+    def __init__(self, model: QuantRWKV7, batch_size, states=None, use_graph=True):
+        self.m, self.B = model, batch_size
+        st = model.init_state(batch_size) if states is None else states
+        self.states = model._materialize(st, batch_size)
+        dev = model.device
+        self.tokens = torch.zeros(batch_size, dtype=torch.long, device=dev)
+        self.next_tokens = torch.zeros(batch_size, dtype=torch.long, device=dev)
+        self.logits = torch.empty((batch_size, model.vocab_size), dtype=torch.float32, device=dev)
+        self.graph = None
+        self.launches_per_step = None
+        if use_graph:
+            self._capture()
+
+    def _run(self):
+        self.m._decode(self.tokens, self.states, self.logits, self.next_tokens)
+
+    def _capture(self):
+        snap = QuantRWKV7.clone_state(self.states)
+        s = torch.cuda.Stream(device=self.m.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._run()                       # warm-up outside capture (lazy attribute set-up)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                self._run()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        for dst, src in zip(self.states, snap):       # undo the two trial steps
+            for d, t in zip(dst, src):
+                d.copy_(t)
+        self.graph = g
+
+    def step(self, tokens=None):
+        if tokens is not None:
+            self.tokens.copy_(tokens.reshape(self.B), non_blocking=True)
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self._run()
+        return self.next_tokens
+
+    def feed_back(self):
+        """Use the last argmax as the next input without leaving the device."""
+        self.tokens.copy_(self.next_tokens)

@@ -71,26 +71,61 @@ struct Frag {
     uint4 pa, pb;          // regrouped bit-planes of the two blocks
 };
 
+// sb6 scale record (16 bytes per row and super-block, written by rwkvq_relayout_meta):
+// word t (t = 0..3) serves the thread that owns blocks 2t and 2t+1:
+//   bits  0-5  qs[2t]      bits  6-11 qs[2t+1]        (6-bit scale codes)
+//   bits 12-17 qm[2t]+31   bits 18-23 qm[2t+1]+31     (6-bit min codes as stored)
+//   bits 24-31 byte t of the 32-bit value (d | dm << 16) (the two fp16 super-scales)
+// Returns (s0, s1) and (m0, m1) of the two blocks: s = max(fp16(qs*d), 1e-8),
+// m = fp16(qm*dm).  A half-precision multiply of the exact small integer by the
+// fp16 super-scale rounds the exact product once, which is the codec's definition.
+__device__ __forceinline__ void sb6_pair_scales(const uint4& rec, int t, float2& s, float2& m) {
+    const uint32_t w = (t & 2) ? ((t & 1) ? rec.w : rec.z) : ((t & 1) ? rec.y : rec.x);
+    const uint32_t dd = __byte_perm(rec.x, rec.y, 0x7373);     // half2(d, d)
+    const uint32_t dmm = __byte_perm(rec.z, rec.w, 0x7373);    // half2(dm, dm)
+    // 1024 + code as fp16 bits, two codes per register
+    const uint32_t qs = (w & 0x3Fu) | ((w << 10) & 0x003F0000u) | 0x64006400u;
+    const uint32_t qm = ((w >> 12) & 0x3Fu) | ((w >> 2) & 0x003F0000u) | 0x64006400u;
+    const __half2 hs = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&qs), __float2half2_rn(1024.f)),
+                               *reinterpret_cast<const __half2*>(&dd));
+    const __half2 hm = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&qm), __float2half2_rn(1055.f)),
+                               *reinterpret_cast<const __half2*>(&dmm));
+    s = __half22float2(hs);
+    m = __half22float2(hm);
+    s.x = fmaxf(s.x, 1e-8f);
+    s.y = fmaxf(s.y, 1e-8f);
+}
+
+// sym: the two int8 scale codes of blocks 2t, 2t+1 times the fp16 super-scale
+__device__ __forceinline__ float2 sym_pair_scales(uint32_t q_lo, uint32_t q_hi, uint32_t d_bits, int t) {
+    const uint32_t w = (t & 2) ? q_hi : q_lo;
+    const uint32_t two = (t & 1) ? (w >> 16) : (w & 0xFFFFu);          // bytes 2t, 2t+1
+    // (code + 128) + 1024 as fp16 bits
+    const uint32_t u = ((two ^ 0x8080u) & 0xFFu) | (((two ^ 0x8080u) << 8) & 0x00FF0000u) | 0x64006400u;
+    const uint32_t dd = d_bits | (d_bits << 16);
+    const __half2 hs = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&u), __float2half2_rn(1152.f)),
+                               *reinterpret_cast<const __half2*>(&dd));
+    return __half22float2(hs);
+}
+
+// Direct (register) loads of iteration `it` of rows r0, r1 for thread t.
 template <int L>
 __device__ __forceinline__ void load_frag(Frag<L>& f, const QView& q, int r0, int r1, int it, int t) {
-    using G = Geo<L>;
     const size_t R0 = static_cast<size_t>(r0), R1 = static_cast<size_t>(r1);
     if (L <= ML_SB6_6) {
         const int nsb = q.cols >> 8;
-        const size_t rowb = static_cast<size_t>(q.cols >> 1);
+        const size_t rowb = static_cast<size_t>(q.cols >> 1), nb = static_cast<size_t>(q.cols >> 5);
         const uint8_t* p0 = q.codes + R0 * rowb + it * 128 + t * 32;
         const uint8_t* p1 = q.codes + R1 * rowb + it * 128 + t * 32;
         f.ca[0] = ld_stream_u128(p0); f.ca[1] = ld_stream_u128(p0 + 16);
         f.cb[0] = ld_stream_u128(p1); f.cb[1] = ld_stream_u128(p1 + 16);
         f.ma = ld_stream_u128(q.dev_meta + (R0 * nsb + it) * 16);
         f.mb = ld_stream_u128(q.dev_meta + (R1 * nsb + it) * 16);
-        if (G::BITS == 5) {
-            const size_t nb = static_cast<size_t>(q.cols >> 5);
+        if (L == ML_SB6_5) {
             const uint2 a = ld_stream_u64(q.dev_planes + R0 * nb + it * 8 + 2 * t);
             const uint2 b = ld_stream_u64(q.dev_planes + R1 * nb + it * 8 + 2 * t);
             f.pa = make_uint4(a.x, a.y, 0, 0); f.pb = make_uint4(b.x, b.y, 0, 0);
-        } else if (G::BITS == 6) {
-            const size_t nb = static_cast<size_t>(q.cols >> 5);
+        } else if (L == ML_SB6_6) {
             f.pa = ld_stream_u128(q.dev_planes + (R0 * nb + it * 8 + 2 * t) * 2);
             f.pb = ld_stream_u128(q.dev_planes + (R1 * nb + it * 8 + 2 * t) * 2);
         }
@@ -187,7 +222,8 @@ __device__ __forceinline__ void split_digits(int X, int& d1, int& d2, int& d3) {
     d1 = (x1 - d2) >> 7;
 }
 
-__device__ __forceinline__ float prepare_x(const void* x, int dtype, int n_in, int8_t* dig,
+// `bits` = 20 (|X| <= 2^20) or 19: chosen so that |sum over one block of q*X| < 2^31.
+__device__ __forceinline__ float prepare_x(const void* x, int dtype, int n_in, int bits, int8_t* dig,
                                            float* xs16, float* red, bool& finite) {
     const int tid = threadIdx.x, n4 = n_in >> 2;
     float amax = 0.f;
@@ -205,7 +241,7 @@ __device__ __forceinline__ float prepare_x(const void* x, int dtype, int n_in, i
     finite = amax < INFINITY;
     int e = 0;
     if (finite && amax > 0.f) frexpf(amax, &e);          // amax <= 2^e
-    const float scale = finite ? ldexpf(1.f, 20 - e) : 0.f;
+    const float scale = finite ? ldexpf(1.f, bits - e) : 0.f;
     for (int i = tid; i < n4; i += blockDim.x) {
         const float4 v = load_x4(x, dtype, i);
         const int X0 = __float2int_rn(v.x * scale), X1 = __float2int_rn(v.y * scale);
@@ -225,37 +261,56 @@ __device__ __forceinline__ float prepare_x(const void* x, int dtype, int n_in, i
         if ((tid & 3) == 0) xs16[i >> 2] = static_cast<float>(s);
     }
     __syncthreads();
-    return finite ? ldexpf(1.f, e - 20) : 0.f;
+    return finite ? ldexpf(1.f, e - bits) : 0.f;
 }
 
-template <int L, int WT>
+// Persistent kernel: gridDim.x CTAs walk the 16-row tiles of matrix blockIdx.y with
+// stride gridDim.x * WT.  Inside a CTA step the 8 warps form WT tiles x WK slices
+// of the K loop; the activations are prepared once per CTA.  Each warp sees a flat
+// sequence of work items (tile, iteration); the loads of item n+1 are issued
+// before item n is consumed.
+template <int L, int WK>
 __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaArgs a) {
     using G = Geo<L>;
-    constexpr int WK = kMmaWarps / WT;
+    constexpr int WT = kMmaWarps / WK;
     constexpr bool SB6 = L <= ML_SB6_6;
     constexpr bool A_UNSIGNED = L != ML_SYM8;
     extern __shared__ __align__(16) unsigned char smem[];
     const QView& q = a.t[blockIdx.y];
     const int n_in = q.cols;
     int8_t* dig = reinterpret_cast<int8_t*>(smem);
-    float* xs16 = reinterpret_cast<float*>(smem + 3 * n_in);
-    float* red = xs16 + (n_in >> 4);                      // [kMmaWarps * 16]
+    float* xs16 = reinterpret_cast<float*>(dig + 3 * n_in);
+    float* red = xs16 + (n_in >> 4);                                     // [2][kMmaWarps * 16]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int tile = blockIdx.x * WT + warp / WK, ks = warp % WK;
-    const int r0 = min(tile * 16 + g, q.rows - 1), r1 = min(tile * 16 + g + 8, q.rows - 1);
+    const int tl = warp / WK, ks = warp % WK;
     const int n_iters = n_in / G::KI;
-
-    // first weight loads go out before the activations are touched
-    Frag<L> cur;
-    const bool have_work = ks < n_iters;
-    if (have_work) load_frag<L>(cur, q, r0, r1, ks, t);
+    const int n_tiles = (q.rows + 15) >> 4;
+    const int step = gridDim.x * WT;
+    const int ipt = (n_iters - ks + WK - 1) / WK;          // this warp's iterations per tile
+    const int n_steps = ((n_tiles + WT - 1) / WT - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                        static_cast<int>(gridDim.x);
+    const int n_items = n_steps * ipt;
+    // prefetch side: item counter -> (tile, iteration)
+    int i_n = 0, i_tile = blockIdx.x * WT + tl, i_j = 0;
+    Frag<L> nxt;
+    auto fetch_next = [&]() {
+        if (i_n < n_items && i_tile < n_tiles) {
+            const int r0 = min(i_tile * 16 + g, q.rows - 1), r1 = min(i_tile * 16 + g + 8, q.rows - 1);
+            load_frag<L>(nxt, q, r0, r1, ks + i_j * WK, t);
+        }
+        ++i_n;
+        if (++i_j == ipt) { i_j = 0; i_tile += step; }
+    };
+    // the first weight loads go out before the activations are touched
+    fetch_next();
 
     const size_t esz = (a.x_dtype == RWKVQ_F32) ? 4 : 2;
     const char* xv = static_cast<const char*>(a.x) + (a.fused ? blockIdx.y * a.ldx * esz : 0);
     bool finite;
-    const float unscale = prepare_x(xv, a.x_dtype, n_in, dig, xs16, red, finite);
+    const float unscale = prepare_x(xv, a.x_dtype, n_in, L == ML_SYM8 ? 19 : 20, dig, xs16, red, finite);
+    __syncthreads();
 
     // which B columns this lane feeds: column 2t+dg of MMA set 1, column 2t of set 2
     const bool b_set1 = (g >> 1) == t;
@@ -263,111 +318,118 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaAr
     const int8_t* dig1 = dig + (g & 1) * n_in;
     const int8_t* dig3 = dig + 2 * n_in;
 
-    float acc0 = 0.f, acc1 = 0.f;     // rows g, g+8
-    for (int it = ks; it < n_iters; it += WK) {
-        Frag<L> nxt;
-        if (it + WK < n_iters) load_frag<L>(nxt, q, r0, r1, it + WK, t);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int blk = it * 8 + 2 * t + h;            // block index along the row
-            int c[4] = {0, 0, 0, 0}, e[4] = {0, 0, 0, 0};
+    int c_n = 0, buf = 0;
+    for (int base = blockIdx.x * WT; base < n_tiles; base += step, buf ^= 1) {
+        const int tile = base + tl;
+        float acc0 = 0.f, acc1 = 0.f;     // rows g, g+8 of this tile
+        for (int j = 0; j < ipt; ++j, ++c_n) {
+            const Frag<L> cur = nxt;
+            fetch_next();
+            if (tile >= n_tiles) continue;
+            const int it = ks + j * WK;
+
+            float2 sa, sb, ma = make_float2(0.f, 0.f), mb = ma;
             if (SB6) {
-                uint4 b1lo = make_uint4(0, 0, 0, 0), b1hi = b1lo, b3lo = b1lo, b3hi = b1lo;
-                if (b_set1) {
-                    b1lo = *reinterpret_cast<const uint4*>(dig1 + blk * 32);
-                    b1hi = *reinterpret_cast<const uint4*>(dig1 + blk * 32 + 16);
-                }
-                if (b_set2) {
-                    b3lo = *reinterpret_cast<const uint4*>(dig3 + blk * 32);
-                    b3hi = *reinterpret_cast<const uint4*>(dig3 + blk * 32 + 16);
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    uint32_t a0, a1, a2, a3;
-                    a_words<L>(cur.ca, cur.pa, h, j, a0, a2);
-                    a_words<L>(cur.cb, cur.pb, h, j, a1, a3);
-                    mma_i8<A_UNSIGNED>(c, a0, a1, a2, a3, word_of(b1lo, j), word_of(b1hi, j));
-                    mma_i8<A_UNSIGNED>(e, a0, a1, a2, a3, word_of(b3lo, j), word_of(b3hi, j));
-                }
+                sb6_pair_scales(cur.ma, t, sa, ma);
+                sb6_pair_scales(cur.mb, t, sb, mb);
             } else {
-                uint4 b1 = make_uint4(0, 0, 0, 0), b3 = b1;
-                if (b_set1) b1 = *reinterpret_cast<const uint4*>(dig1 + blk * 16);
-                if (b_set2) b3 = *reinterpret_cast<const uint4*>(dig3 + blk * 16);
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    uint32_t a0, a1, a2, a3;
-                    a_words<L>(cur.ca, cur.pa, h, j, a0, a2);
-                    a_words<L>(cur.cb, cur.pb, h, j, a1, a3);
-                    mma_i8<A_UNSIGNED>(c, a0, a1, a2, a3, word_of(b1, 2 * j), word_of(b1, 2 * j + 1));
-                    mma_i8<A_UNSIGNED>(e, a0, a1, a2, a3, word_of(b3, 2 * j), word_of(b3, 2 * j + 1));
-                }
+                sa = sym_pair_scales(cur.ma.x, cur.ma.y, cur.ma.z, t);
+                sb = sym_pair_scales(cur.mb.x, cur.mb.y, cur.mb.z, t);
             }
-            // c[0], c[1]: row g digits 1, 2;  c[2], c[3]: row g+8;  e[0], e[2]: digit 3
-            const float f0 = fmaf(static_cast<float>(c[0]), 16384.f, fmaf(static_cast<float>(c[1]), 128.f, static_cast<float>(e[0])));
-            const float f1 = fmaf(static_cast<float>(c[2]), 16384.f, fmaf(static_cast<float>(c[3]), 128.f, static_cast<float>(e[2])));
-            if (SB6) {
-                const float xsum = xs16[2 * blk] + xs16[2 * blk + 1];
-                float s0, m0, s1, m1;
-                sb6_scale_min(cur.ma.x, cur.ma.y, cur.ma.z, 2 * t + h, half_bits_to_float(cur.ma.w & 0xFFFFu),
-                              half_bits_to_float(cur.ma.w >> 16), s0, m0);
-                sb6_scale_min(cur.mb.x, cur.mb.y, cur.mb.z, 2 * t + h, half_bits_to_float(cur.mb.w & 0xFFFFu),
-                              half_bits_to_float(cur.mb.w >> 16), s1, m1);
-                acc0 = fmaf(s0, f0, fmaf(m0, xsum, acc0));
-                acc1 = fmaf(s1, f1, fmaf(m1, xsum, acc1));
-            } else {
-                const int jb = 2 * t + h;
-                const uint32_t wa = jb < 4 ? cur.ma.x : cur.ma.y, wb = jb < 4 ? cur.mb.x : cur.mb.y;
-                const int qa = static_cast<int8_t>((wa >> (8 * (jb & 3))) & 0xFFu);
-                const int qb = static_cast<int8_t>((wb >> (8 * (jb & 3))) & 0xFFu);
-                const float s0 = half_roundtrip(__fmul_rn(static_cast<float>(qa), half_bits_to_float(cur.ma.z)));
-                const float s1 = half_roundtrip(__fmul_rn(static_cast<float>(qb), half_bits_to_float(cur.mb.z)));
-                const float off = (L == ML_SYM6) ? -32.f * xs16[blk] : 0.f;   // codes are stored +32
-                acc0 = fmaf(s0, f0 + off, acc0);
-                acc1 = fmaf(s1, f1 + off, acc1);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int blk = it * 8 + 2 * t + h;            // block index along the row
+                int c[4] = {0, 0, 0, 0}, e[4] = {0, 0, 0, 0};
+                if (SB6) {
+                    uint4 b1lo = make_uint4(0, 0, 0, 0), b1hi = b1lo, b3lo = b1lo, b3hi = b1lo;
+                    if (b_set1) {
+                        b1lo = *reinterpret_cast<const uint4*>(dig1 + blk * 32);
+                        b1hi = *reinterpret_cast<const uint4*>(dig1 + blk * 32 + 16);
+                    }
+                    if (b_set2) {
+                        b3lo = *reinterpret_cast<const uint4*>(dig3 + blk * 32);
+                        b3hi = *reinterpret_cast<const uint4*>(dig3 + blk * 32 + 16);
+                    }
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) {
+                        uint32_t a0, a1, a2, a3;
+                        a_words<L>(cur.ca, cur.pa, h, jj, a0, a2);
+                        a_words<L>(cur.cb, cur.pb, h, jj, a1, a3);
+                        mma_i8<A_UNSIGNED>(c, a0, a1, a2, a3, word_of(b1lo, jj), word_of(b1hi, jj));
+                        mma_i8<A_UNSIGNED>(e, a0, a1, a2, a3, word_of(b3lo, jj), word_of(b3hi, jj));
+                    }
+                } else {
+                    uint4 b1 = make_uint4(0, 0, 0, 0), b3 = b1;
+                    if (b_set1) b1 = *reinterpret_cast<const uint4*>(dig1 + blk * 16);
+                    if (b_set2) b3 = *reinterpret_cast<const uint4*>(dig3 + blk * 16);
+#pragma unroll
+                    for (int jj = 0; jj < 2; ++jj) {
+                        uint32_t a0, a1, a2, a3;
+                        a_words<L>(cur.ca, cur.pa, h, jj, a0, a2);
+                        a_words<L>(cur.cb, cur.pb, h, jj, a1, a3);
+                        mma_i8<A_UNSIGNED>(c, a0, a1, a2, a3, word_of(b1, 2 * jj), word_of(b1, 2 * jj + 1));
+                        mma_i8<A_UNSIGNED>(e, a0, a1, a2, a3, word_of(b3, 2 * jj), word_of(b3, 2 * jj + 1));
+                    }
+                }
+                // c[0], c[1]: row g digits 1, 2;  c[2], c[3]: row g+8;  e[0], e[2]: digit 3.
+                // The recombined value is the exact integer sum q*X of the block (< 2^31).
+                const float f0 = static_cast<float>((c[0] << 14) + (c[1] << 7) + e[0]);
+                const float f1 = static_cast<float>((c[2] << 14) + (c[3] << 7) + e[2]);
+                const float s0 = h ? sa.y : sa.x, s1 = h ? sb.y : sb.x;
+                if (SB6) {
+                    const float xsum = xs16[2 * blk] + xs16[2 * blk + 1];
+                    acc0 = fmaf(s0, f0, fmaf(h ? ma.y : ma.x, xsum, acc0));
+                    acc1 = fmaf(s1, f1, fmaf(h ? mb.y : mb.x, xsum, acc1));
+                } else {
+                    const float off = (L == ML_SYM6) ? -32.f * xs16[blk] : 0.f;   // codes are stored +32
+                    acc0 = fmaf(s0, f0 + off, acc0);
+                    acc1 = fmaf(s1, f1 + off, acc1);
+                }
             }
         }
-        cur = nxt;
-    }
-
-    // the 4 lanes of a quad hold the 8 blocks of each iteration
-    acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 1); acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 2);
-    acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, 1); acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, 2);
-    __syncthreads();                       // `red` was used by prepare_x
-    if (t == 0) { red[warp * 16 + g] = acc0; red[warp * 16 + g + 8] = acc1; }
-    __syncthreads();
-    if (threadIdx.x < WT * 16) {
-        const int tl = threadIdx.x >> 4, r = threadIdx.x & 15;
-        const int row = (blockIdx.x * WT + tl) * 16 + r;
-        if (row < q.rows) {
-            float v = 0.f;
+        // the 4 lanes of a quad hold the 8 blocks of each iteration
+        acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 1); acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 2);
+        acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, 1); acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, 2);
+        float* rb = red + buf * (kMmaWarps * 16);
+        if (t == 0) { rb[warp * 16 + g] = acc0; rb[warp * 16 + g + 8] = acc1; }
+        __syncthreads();
+        if (threadIdx.x < WT * 16) {
+            const int wtl = threadIdx.x >> 4, r = threadIdx.x & 15;
+            const int row = (base + wtl) * 16 + r;
+            if (row < q.rows) {
+                float v = 0.f;
 #pragma unroll
-            for (int k = 0; k < WK; ++k) v += red[(tl * WK + k) * 16 + r];
-            v = finite ? v * unscale : NAN;
-            const long long idx = (a.fused ? static_cast<long long>(blockIdx.y) * a.ldy : 0) + row;
-            if (a.epilogue == RWKVQ_EPI_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
-            else if (a.epilogue == RWKVQ_EPI_ADD) v = __fadd_rn(v, a.resid[idx]);
-            a.y[idx] = v;
+                for (int k = 0; k < WK; ++k) v += rb[(wtl * WK + k) * 16 + r];
+                v = finite ? v * unscale : NAN;
+                const long long idx = (a.fused ? static_cast<long long>(blockIdx.y) * a.ldy : 0) + row;
+                if (a.epilogue == RWKVQ_EPI_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
+                else if (a.epilogue == RWKVQ_EPI_ADD) v = __fadd_rn(v, a.resid[idx]);
+                a.y[idx] = v;
+            }
         }
     }
 }
 
 // ------------------------------------------------------------ relayout kernels
-__global__ void relayout_meta_kernel(QView t, uint8_t* out) {
+__global__ void relayout_meta_kernel(QView t, uint32_t* out) {
     const int nsb = t.cols >> 8;
     const size_t total = static_cast<size_t>(t.rows) * nsb;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        uint8_t* o = out + i * 16;
-        for (int k = 0; k < 12; ++k) o[k] = t.qsqm[i * 12 + k];
-        const uint16_t d = reinterpret_cast<const uint16_t*>(t.d)[i];
-        const uint16_t dm = reinterpret_cast<const uint16_t*>(t.dm)[i];
-        o[12] = d & 0xFF; o[13] = d >> 8; o[14] = dm & 0xFF; o[15] = dm >> 8;
+        const uint8_t* mp = t.qsqm + i * 12;
+        uint64_t qs = 0, qm = 0;
+        for (int k = 0; k < 6; ++k) { qs |= static_cast<uint64_t>(mp[k]) << (8 * k); qm |= static_cast<uint64_t>(mp[6 + k]) << (8 * k); }
+        const uint32_t dd = reinterpret_cast<const uint16_t*>(t.d)[i] |
+                            (static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(t.dm)[i]) << 16);
+        for (int w = 0; w < 4; ++w)
+            out[i * 4 + w] = sixbit(qs, 2 * w) | (sixbit(qs, 2 * w + 1) << 6) | (sixbit(qm, 2 * w) << 12) |
+                             (sixbit(qm, 2 * w + 1) << 18) | (((dd >> (8 * w)) & 0xFFu) << 24);
     }
 }
 
 // One output word per thread.  `mode` 5: sb6@5, 6: sb6@6 (two words per block), 16: sym@6.
 __global__ void relayout_planes_kernel(QView t, uint32_t* out, int mode) {
-    const size_t words_per_row = mode == 5 ? (t.cols >> 5) : mode == 6 ? (t.cols >> 4) : (t.cols >> 4);
+    const size_t words_per_row = mode == 5 ? (t.cols >> 5) : (t.cols >> 4);
     const size_t total = static_cast<size_t>(t.rows) * words_per_row;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -410,34 +472,30 @@ int mma_layout_of(const rwkvq_qtensor& t) {
     return -1;
 }
 
-static int pick_wt(int rows) {
-    const int tiles = (rows + 15) / 16;
-    for (int wt = 8; wt > 1; wt >>= 1)
-        if ((tiles + wt - 1) / wt >= 148) return wt;
-    return 1;
-}
+constexpr int kResidentCtas = 2 * 148;     // 2 CTAs of 256 threads per SM at <= 128 registers
 
-template <int L, int WT>
+template <int L, int WK>
 static int launch_one(const MmaArgs& a, int rows, int cols, int n_mats, cudaStream_t s) {
-    const size_t smem = 3 * static_cast<size_t>(cols) + 4 * (cols / 16) + kMmaWarps * 16 * 4;
+    constexpr int WT = kMmaWarps / WK;
+    const size_t smem = 3 * static_cast<size_t>(cols) + 4 * (cols / 16) + 2 * kMmaWarps * 16 * 4;
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<L, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<L, WK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(smem));
         if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "gemv_mma: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
-    const int tiles = (rows + 15) / 16;
-    gemv_mma_kernel<L, WT><<<dim3((tiles + WT - 1) / WT, n_mats), kMmaWarps * 32, smem, s>>>(a);
+    const int units = ((rows + 15) / 16 + WT - 1) / WT;
+    const int cap = kResidentCtas / n_mats > 0 ? kResidentCtas / n_mats : 1;
+    gemv_mma_kernel<L, WK><<<dim3(units < cap ? units : cap, n_mats), kMmaWarps * 32, smem, s>>>(a);
     return RWKVQ_OK;
 }
 
 template <int L>
-static int launch_wt(const MmaArgs& a, int rows, int cols, int n_mats, cudaStream_t s) {
-    switch (pick_wt(rows)) {
-        case 8: return launch_one<L, 8>(a, rows, cols, n_mats, s);
-        case 4: return launch_one<L, 4>(a, rows, cols, n_mats, s);
-        case 2: return launch_one<L, 2>(a, rows, cols, n_mats, s);
-        default: return launch_one<L, 1>(a, rows, cols, n_mats, s);
-    }
+static int launch_wk(const MmaArgs& a, int rows, int cols, int n_mats, cudaStream_t s) {
+    const int n_iters = cols / Geo<L>::KI;
+    if (n_iters >= 8) return launch_one<L, 8>(a, rows, cols, n_mats, s);
+    if (n_iters >= 4) return launch_one<L, 4>(a, rows, cols, n_mats, s);
+    if (n_iters >= 2) return launch_one<L, 2>(a, rows, cols, n_mats, s);
+    return launch_one<L, 1>(a, rows, cols, n_mats, s);
 }
 
 // Launch the single-vector tensor-core GEMV for `n_mats` same-shape matrices.
@@ -449,15 +507,13 @@ int launch_gemv_mma(int layout, const rwkvq_qtensor* ts, int n_mats, const void*
     a.x = x; a.x_dtype = x_dtype; a.ldx = ldx; a.y = y; a.ldy = ldy;
     a.resid = resid; a.epilogue = epilogue; a.fused = fused;
     const int rows = ts[0].rows, cols = ts[0].cols;
-    int rc;
     switch (layout) {
-        case ML_SB6_4: rc = launch_wt<ML_SB6_4>(a, rows, cols, n_mats, s); break;
-        case ML_SB6_5: rc = launch_wt<ML_SB6_5>(a, rows, cols, n_mats, s); break;
-        case ML_SB6_6: rc = launch_wt<ML_SB6_6>(a, rows, cols, n_mats, s); break;
-        case ML_SYM6: rc = launch_wt<ML_SYM6>(a, rows, cols, n_mats, s); break;
-        default: rc = launch_wt<ML_SYM8>(a, rows, cols, n_mats, s); break;
+        case ML_SB6_4: return launch_wk<ML_SB6_4>(a, rows, cols, n_mats, s);
+        case ML_SB6_5: return launch_wk<ML_SB6_5>(a, rows, cols, n_mats, s);
+        case ML_SB6_6: return launch_wk<ML_SB6_6>(a, rows, cols, n_mats, s);
+        case ML_SYM6: return launch_wk<ML_SYM6>(a, rows, cols, n_mats, s);
+        default: return launch_wk<ML_SYM8>(a, rows, cols, n_mats, s);
     }
-    return rc;
 }
 
 }  // namespace rwkvq
@@ -472,7 +528,7 @@ int rwkvq_relayout_meta(const rwkvq_qtensor* t, void* meta_out, void* stream) {
     RWKVQ_REQUIRE(t->kind == RWKVQ_KIND_SB6, RWKVQ_E_DTYPE, "rwkvq_relayout_meta: only sb6 tensors have scale records");
     RWKVQ_REQUIRE(meta_out != nullptr && aligned(meta_out, 16), RWKVQ_E_ALIGN, "rwkvq_relayout_meta: out must be 16-byte aligned");
     relayout_meta_kernel<<<148 * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(make_view(*t),
-                                                                                 static_cast<uint8_t*>(meta_out));
+                                                                                 static_cast<uint32_t*>(meta_out));
     return check_launch("rwkvq_relayout_meta");
 }
 

@@ -1,0 +1,163 @@
+"""WKV-7, time-mix tail and the whole model on the GPU against the CPU oracle.
+
+Tolerances: logits relmax <= 1e-3 against the fp32 oracle with the same weight
+precision policy; WKV state max|delta| is asserted and printed; greedy tokens must
+agree wherever the oracle's top-2 margin exceeds the logit tolerance.
+"""
+import os
+import zlib
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+from helpers import relmax
+from oracle import codec_np as oc
+from oracle.build_c import wkv7_seq
+from oracle.model_np import OracleRWKV7, wkv7_np
+
+pytestmark = pytest.mark.gpu
+
+# (B, T, H) of the reference's WKV gate (tests/test_wkv_infer_parity.py:34-36)
+WKV_CASES = [(1, 1, 32), (1, 3, 32), (1, 16, 32), (1, 512, 32), (1, 1, 40), (1, 512, 40), (1, 512, 16),
+             (2, 128, 32), (1, 7, 32)]
+
+
+def wkv_inputs(B, T, H, S=64):
+    """Input recipe of tests/test_wkv_infer_parity.py:38-53."""
+    rs = np.random.RandomState(zlib.crc32(f"wkv7-infer-{B}-{T}-{H}".encode()) & 0x7FFFFFFF)
+    g = lambda sc=1.0: (rs.randn(B, T, H, S) * sc).astype(np.float32)
+    r, k, v, a, b = g(), g(), g(), g(0.1), g(0.1)
+    w = (0.85 + 0.14 * rs.rand(B, T, H, S)).astype(np.float32)
+    h = (rs.randn(B, H, S, S) * 0.05).astype(np.float32)
+    return r, w, k, v, a, b, h
+
+
+@pytest.mark.parametrize("case", WKV_CASES)
+def test_wkv7_infer(cuda_lib, case):
+    from rwkv_quant_b200.backends.cuda import wkv7_infer
+    ins = wkv_inputs(*case)
+    ref_out, ref_h = wkv7_seq(*ins)          # sequential order of the reference's kernel
+    dev = [torch.from_numpy(x).cuda() for x in ins]
+    h_before = dev[6].clone()
+    out, h = wkv7_infer(*dev)
+    assert torch.equal(dev[6], h_before), "the input state must not be modified"
+    out, h = out.cpu().numpy(), h.cpu().numpy()
+    d_state = float(np.abs(h - ref_h).max())
+    print(f"wkv7 {case}: out relmax {relmax(out, ref_out):.2e}, state max|delta| {d_state:.2e}")
+    assert relmax(out, ref_out) <= 1e-4 and d_state <= 1e-3 * max(1.0, np.abs(ref_h).max())
+    # state carry: two calls == one call
+    if case[1] >= 2:
+        c = case[1] // 2
+        o1, h1 = wkv7_infer(*[t[:, :c].contiguous() for t in dev[:6]], dev[6])
+        o2, h2 = wkv7_infer(*[t[:, c:].contiguous() for t in dev[:6]], h1)
+        assert torch.equal(torch.cat([o1, o2], 1).cpu(), torch.from_numpy(out))
+        assert torch.equal(h2.cpu(), torch.from_numpy(h))
+
+
+def test_wkv_tail(cuda_lib):
+    from rwkv_quant_b200.backends.cuda import can_fuse_tail, wkv_tail
+    assert can_fuse_tail(32, 64)
+    rs = np.random.RandomState(3)
+    N, H, S = 5, 32, 64
+    D = H * S
+    wkv, r, k, v, g = (rs.randn(N, D).astype(np.float32) for _ in range(5))
+    r_k, lw, lb = (rs.randn(D).astype(np.float32) for _ in range(3))
+    x = wkv.reshape(N, H, S).astype(np.float64)
+    mu = x.mean(-1, keepdims=True)
+    var = ((x - mu) ** 2).mean(-1, keepdims=True)
+    nrm = ((x - mu) / np.sqrt(var + 64e-5)).reshape(N, D) * lw + lb
+    dp = (r * k * r_k).reshape(N, H, S).astype(np.float64).sum(-1, keepdims=True)
+    ref = (nrm + (dp * v.reshape(N, H, S)).reshape(N, D)) * g
+    t = lambda a: torch.from_numpy(a).cuda()
+    out = wkv_tail(t(wkv), t(r), t(k), t(v), t(r_k), t(lw), t(lb), t(g), H, S).cpu().numpy()
+    assert relmax(out, ref) <= 1e-5
+
+
+def _load(preset):
+    from rwkv_quant_b200.backends.cuda import QuantRWKV7
+    from rwkv_quant_b200.formats import load_raw
+    path = os.path.join(GOLDEN, f"toy_{preset}.rwkvq")
+    man, arr = oc.open_rwkvq(path)
+    return QuantRWKV7(load_raw(path)), OracleRWKV7(man, arr), np.load(os.path.join(GOLDEN, f"toy_{preset}_ref.npz"))
+
+
+@pytest.mark.parametrize("preset", ["reduction", "compression"])
+def test_model_matches_oracle(cuda_lib, preset):
+    """Reference-written toy checkpoint: sequence path, token-by-token path and the
+    mixed use of both against the oracle (logits and every state tensor)."""
+    model, oracle, z = _load(preset)
+    idx = z["idx"]
+    B, T = idx.shape
+    ref, ref_st = oracle.forward_stateful(idx, oracle.init_state(B))
+    # distance to the reference's own all-bf16 forward, for the record
+    print(f"{preset}: oracle vs RWKV7Ref relmax {relmax(ref, z['logits']):.2e}")
+    # whole sequence
+    lo, st = model.forward_stateful(idx, model.init_state(B))
+    assert lo.shape == (B, T, model.vocab_size) and lo.dtype == torch.float32
+    assert relmax(lo.cpu().numpy(), ref) <= 1e-3, relmax(lo.cpu().numpy(), ref)
+    assert relmax(model(idx).cpu().numpy(), ref) <= 1e-3
+    # token by token (the decode kernels), states updated in place
+    st1 = model.init_state(B)
+    outs = []
+    for t in range(T):
+        lo1, st1 = model.forward_stateful(idx[:, t:t + 1], st1)
+        outs.append(lo1.cpu().numpy())
+    tb = np.concatenate(outs, 1)
+    print(f"{preset}: decode path vs oracle relmax {relmax(tb, ref):.2e}")
+    assert relmax(tb, ref) <= 1e-3
+    for (w, ts, cs), (w2, ts2, cs2), (rw, rts, rcs) in zip(st, st1, ref_st):
+        for got in (w, w2):
+            d = float(np.abs(got.cpu().numpy() - rw).max())
+            assert d <= 1e-3 * max(1.0, np.abs(rw).max()), d
+        for got in (ts, ts2):
+            assert relmax(got.reshape(B, -1).cpu().numpy(), rts) <= 1e-3
+        for got in (cs, cs2):
+            assert relmax(got.reshape(B, -1).cpu().numpy(), rcs) <= 1e-3
+    # prefill then decode; last_only / tail_only
+    lo_p, st_p = model.forward_stateful(idx[:, :10], model.init_state(B), last_only=True)
+    assert lo_p.shape == (B, 1, model.vocab_size)
+    assert relmax(lo_p.cpu().numpy(), ref[:, 9:10]) <= 1e-3
+    lo_n, st_p = model.forward_stateful(idx[:, 10:11], st_p)
+    assert relmax(lo_n.cpu().numpy(), ref[:, 10:11]) <= 1e-3
+    lo_t, _ = model.forward_stateful(idx, model.init_state(B), tail_only=3)
+    assert relmax(lo_t.cpu().numpy(), ref[:, -3:]) <= 1e-3
+    hid, _ = model.forward_hidden(idx, model.init_state(B))
+    rh, _ = oracle.forward_hidden(idx, oracle.init_state(B))
+    assert relmax(hid.cpu().numpy(), rh) <= 1e-3
+
+
+@pytest.mark.parametrize("recipe", ["compression", "reduction", "sb6_int6", "compression_eh8"])
+def test_greedy_decode_graph_and_eager(cuda_lib, recipe):
+    """Synthetic toy build: greedy tokens of the CUDA-graph decoder == eager decoder,
+    and == the oracle wherever its top-2 margin is clear of the tolerance."""
+    from rwkv_quant_b200 import synth
+    from rwkv_quant_b200.backends.cuda import QuantRWKV7
+    from rwkv_quant_b200.formats import save_rwkvq
+    import tempfile
+    ck = synth.build_checkpoint("toy", recipe, seed=11)
+    with tempfile.TemporaryDirectory() as d:
+        p = os.path.join(d, "m.rwkvq")
+        save_rwkvq(ck, p)
+        man, arr = oc.open_rwkvq(p)
+        oracle = OracleRWKV7(man, arr)
+        prompt = np.random.default_rng(5).integers(1, 500, (3, 9))
+        model = QuantRWKV7(ck)
+        toks, _ = model.generate(prompt, 12)
+        # graph replay from the same prefilled state
+        lo, st = model.forward_stateful(prompt, model.init_state(3), last_only=True)
+        dec = model.decoder(3, states=st, use_graph=True)
+        tok, got = lo[:, -1].argmax(-1), []
+        for _ in range(12):
+            got.append(tok.clone())
+            tok = dec.step(tok).clone()
+        assert torch.equal(torch.stack(got, 1), toks), "graph replay and eager decode disagree"
+        # oracle, teacher-forced on our tokens
+        ours = toks.cpu().numpy()
+        logits, ost = oracle.forward_stateful(prompt, oracle.init_state(3), last_only=True)
+        for t in range(12):
+            top2 = np.sort(logits[:, -1], axis=-1)[:, -2:]
+            clear = (top2[:, 1] - top2[:, 0]) > 2e-3 * np.abs(logits).max()
+            assert (logits[:, -1].argmax(-1)[clear] == ours[clear, t]).all(), f"step {t}"
+            logits, ost = oracle.forward_stateful(ours[:, t:t + 1], ost)
