@@ -288,8 +288,14 @@ class QuantRWKV7:
             tok = dec.step(tok)
         return torch.stack(out, dim=1), dec.states
 
-    def decoder(self, batch_size: int = 1, states=None, use_graph: bool = True):
-        return Decoder(self, batch_size, states, use_graph)
+    def decoder(self, batch_size: int = 1, states=None, use_graph: bool = True, self_feed: bool = False):
+        return Decoder(self, batch_size, states, use_graph, self_feed)
+
+    @property
+    def launches_per_token(self) -> int:
+        """Kernels one decoded token launches at batch 1: per layer 2 norm/shift/lerp,
+        6 GEMV, 2 LoRA, 1 time-mix core; plus embedding, final norm, head, argmax (2)."""
+        return self.n_layer * 11 + 5
 
 
 class Decoder:
@@ -297,8 +303,9 @@ class Decoder:
     ``step(tokens)`` feeds tokens [B] and returns the argmax next tokens [B] (device);
     with ``use_graph`` the whole token (all kernels) is one CUDA-graph replay."""
 
-    def __init__(self, model: QuantRWKV7, batch_size, states=None, use_graph=True):
+    def __init__(self, model: QuantRWKV7, batch_size, states=None, use_graph=True, self_feed=False):
         self.m, self.B = model, batch_size
+        self.self_feed = self_feed        # the replayed graph ends by feeding the argmax back
         st = model.init_state(batch_size) if states is None else states
         self.states = model._materialize(st, batch_size)
         dev = model.device
@@ -312,6 +319,8 @@ class Decoder:
 
     def _run(self):
         self.m._decode(self.tokens, self.states, self.logits, self.next_tokens)
+        if self.self_feed:
+            self.tokens.copy_(self.next_tokens)
 
     def _capture(self):
         snap = QuantRWKV7.clone_state(self.states)
@@ -328,6 +337,7 @@ class Decoder:
         for dst, src in zip(self.states, snap):       # undo the two trial steps
             for d, t in zip(dst, src):
                 d.copy_(t)
+        self.tokens.zero_()
         self.graph = g
 
     def step(self, tokens=None):

@@ -4,8 +4,8 @@
 // Per layer (backends/metal/quant_model.py:638-728, 803-836):
 //   ln_shift_mix   LN1 + token shift + the six lerps           -> xs[6][B][D]
 //   gemv x3        r, k, v projections (one fused launch)
-//   lora_multi     the LoRA down projections w1, a1, v1, g1 (tanh / - / - / sigmoid)
-//   lora_multi     the LoRA up projections w2, a2, v2, g2
+//   lora_down      the LoRA down projections w1, a1, v1, g1 as row-chunk partial sums
+//   lora_up        activation (tanh / - / - / sigmoid) and the up projections w2, a2, v2, g2
 //   tmix_core      decay, gates, kk, k and v updates, WKV-7 step on the 64x64 state,
 //                  group norm, bonus, gate                      -> og[B][D]
 //   gemv + add     output projection and residual
@@ -104,15 +104,33 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
     }
 }
 
-// ---- batched LoRA products: up to 4 branches, each y = act(x @ Wt) with Wt stored [in, out]
-constexpr int kLmWarps = 8, kLmCols = 128, kLmMaxN = 8;
-struct LoraMultiArgs {
+// ---- batched LoRA products, tensors stored [in, out] (a warp reads 128 contiguous codes)
+//
+// down:  part[br][chunk][n][j] = sum_{i in chunk} x_br[n][i] * W1_br[i][j]     (j < rank)
+//        grid (row chunks of 64, branches); the partial sums go to scratch in a fixed
+//        layout and are added in chunk order by the consumer, so the result does not
+//        depend on scheduling.
+// up:    h[j] = act_br(sum_chunk part[br][chunk][n][j]);  y_br[n][c] = sum_j h[j] * W2_br[j][c]
+//        grid (column tiles of 128, branches).
+constexpr int kLmMaxN = 8;            // right-hand sides per launch
+constexpr int kLdRows = 64;           // rows of W1 per CTA
+constexpr int kLuCols = 128;          // columns of W2 per CTA
+constexpr int kLmMaxRank = 512;
+
+struct LoraDownArgs {
     QView t[4];
-    const float* x[4];
-    float* y[4];
+    const float* x[4];      // [n_cols, ldx]
+    float* part;            // [4][n_chunks][kLmMaxN][max_rank]
+    long long ldx;
+    int n_cols, n_chunks, max_rank;
+};
+struct LoraUpArgs {
+    QView t[4];
+    const float* part;
+    float* y[4];            // [n_cols, ldy]
     int act[4];
-    long long ldx, ldy;
-    int n_cols;     // right-hand sides (<= kLmMaxN)
+    long long ldy;
+    int n_cols, n_chunks, max_rank;
 };
 
 __device__ __forceinline__ void lora_w4(const QView& t, int i, int c, float (&w)[4]) {
@@ -136,28 +154,87 @@ __device__ __forceinline__ void lora_w4(const QView& t, int i, int c, float (&w)
     for (int k = 0; k < 4; ++k) w[k] = dense_param_rounding(w[k]);
 }
 
-__global__ void __launch_bounds__(kLmWarps * 32) lora_multi_kernel(const LoraMultiArgs a) {
-    __shared__ float red[kLmWarps][kLmMaxN][kLmCols];
+// 256 threads = 4 row groups x 64 column threads (4 columns each, rank <= 256 per pass)
+__global__ void __launch_bounds__(256) lora_down_kernel(const LoraDownArgs a) {
+    __shared__ float red[4][kLmMaxN][256];
+    const int br = blockIdx.y, chunk = blockIdx.x;
+    const QView& t = a.t[br];
+    const int rg = threadIdx.x >> 6, ct = threadIdx.x & 63;
+    const int row0 = chunk * kLdRows;
+    for (int c0 = 0; c0 < t.cols; c0 += 256) {
+        const int c = c0 + ct * 4;
+        float acc[kLmMaxN][4];
+#pragma unroll
+        for (int n = 0; n < kLmMaxN; ++n)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) acc[n][k] = 0.f;
+        if (c < t.cols) {
+#pragma unroll 4
+            for (int i = row0 + rg; i < min(row0 + kLdRows, t.rows); i += 4) {
+                float w[4];
+                lora_w4(t, i, c, w);
+#pragma unroll
+                for (int n = 0; n < kLmMaxN; ++n) {
+                    if (n >= a.n_cols) break;
+                    const float xv = __ldg(a.x[br] + n * a.ldx + i);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) acc[n][k] = fmaf(xv, w[k], acc[n][k]);
+                }
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int n = 0; n < kLmMaxN; ++n) {
+            if (n >= a.n_cols) break;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) red[rg][n][ct * 4 + k] = acc[n][k];
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < a.n_cols * 256; idx += 256) {
+            const int n = idx >> 8, cc = idx & 255;
+            if (c0 + cc >= t.cols) continue;
+            const float v = (red[0][n][cc] + red[1][n][cc]) + (red[2][n][cc] + red[3][n][cc]);
+            a.part[((static_cast<size_t>(br) * a.n_chunks + chunk) * kLmMaxN + n) * a.max_rank + c0 + cc] = v;
+        }
+    }
+}
+
+// 256 threads = 8 row groups x 32 column threads (4 columns each)
+__global__ void __launch_bounds__(256) lora_up_kernel(const LoraUpArgs a) {
+    __shared__ float h[kLmMaxN][kLmMaxRank];
+    __shared__ float red[8][kLmMaxN][kLuCols];
     const int br = blockIdx.y;
     const QView& t = a.t[br];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int c = blockIdx.x * kLmCols + lane * 4;
-    if (blockIdx.x * kLmCols >= t.cols) return;
+    if (blockIdx.x * kLuCols >= t.cols) return;
+    const int rank = t.rows;
+    for (int idx = threadIdx.x; idx < a.n_cols * rank; idx += 256) {
+        const int n = idx / rank, j = idx % rank;
+        float v = 0.f;
+        for (int ch = 0; ch < a.n_chunks; ++ch)
+            v += a.part[((static_cast<size_t>(br) * a.n_chunks + ch) * kLmMaxN + n) * a.max_rank + j];
+        if (a.act[br] == 1) v = tanhf(v);
+        else if (a.act[br] == 2) v = sigmoidf_(v);
+        h[n][j] = v;
+    }
+    __syncthreads();
+    const int rg = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.x * kLuCols + lane * 4;
     float acc[kLmMaxN][4];
 #pragma unroll
     for (int n = 0; n < kLmMaxN; ++n)
 #pragma unroll
         for (int k = 0; k < 4; ++k) acc[n][k] = 0.f;
     if (c < t.cols) {
-        for (int i = warp; i < t.rows; i += kLmWarps) {
+#pragma unroll 4
+        for (int j = rg; j < rank; j += 8) {
             float w[4];
-            lora_w4(t, i, c, w);
+            lora_w4(t, j, c, w);
 #pragma unroll
             for (int n = 0; n < kLmMaxN; ++n) {
                 if (n >= a.n_cols) break;
-                const float xv = __ldg(a.x[br] + n * a.ldx + i);
+                const float hv = h[n][j];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) acc[n][k] = fmaf(xv, w[k], acc[n][k]);
+                for (int k = 0; k < 4; ++k) acc[n][k] = fmaf(hv, w[k], acc[n][k]);
             }
         }
     }
@@ -165,18 +242,16 @@ __global__ void __launch_bounds__(kLmWarps * 32) lora_multi_kernel(const LoraMul
     for (int n = 0; n < kLmMaxN; ++n) {
         if (n >= a.n_cols) break;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) red[warp][n][lane * 4 + k] = acc[n][k];
+        for (int k = 0; k < 4; ++k) red[rg][n][lane * 4 + k] = acc[n][k];
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < a.n_cols * kLmCols; idx += blockDim.x) {
-        const int n = idx / kLmCols, cc = idx % kLmCols;
-        const int col = blockIdx.x * kLmCols + cc;
+    for (int idx = threadIdx.x; idx < a.n_cols * kLuCols; idx += 256) {
+        const int n = idx / kLuCols, cc = idx % kLuCols;
+        const int col = blockIdx.x * kLuCols + cc;
         if (col >= t.cols) continue;
         float v = 0.f;
 #pragma unroll
-        for (int w = 0; w < kLmWarps; ++w) v += red[w][n][cc];
-        if (a.act[br] == 1) v = tanhf(v);
-        else if (a.act[br] == 2) v = sigmoidf_(v);
+        for (int w = 0; w < 8; ++w) v += red[w][n][cc];
         a.y[br][n * a.ldy + col] = v;
     }
 }
@@ -260,28 +335,44 @@ __global__ void __launch_bounds__(256) tmix_core_kernel(const TmixCoreArgs p) {
     }
 }
 
-__global__ void __launch_bounds__(256) argmax_kernel(const float* logits, long long* out, int V) {
+// greedy argmax in two stages (lowest index wins ties): 64 slices per row, then one CTA
+constexpr int kArgSlices = 64;
+__device__ __forceinline__ void argmax_combine(float& best, int& idx, float ov, int oi) {
+    if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+}
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const float* logits, float* pv, int* pi, int V) {
     __shared__ float bv[8];
     __shared__ int bi[8];
-    const float* row = logits + static_cast<size_t>(blockIdx.x) * V;
+    const float* row = logits + static_cast<size_t>(blockIdx.y) * V;
+    const int per = (V + kArgSlices - 1) / kArgSlices;
+    const int lo = blockIdx.x * per, hi = min(lo + per, V);
     float best = -INFINITY;
-    int idx = 0;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best) { best = v; idx = i; }
-    }
+    int idx = V;
+    for (int i = lo + threadIdx.x; i < hi; i += 256) argmax_combine(best, idx, row[i], i);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
-        const int oi = __shfl_xor_sync(0xFFFFFFFFu, idx, o);
-        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
-    }
+    for (int o = 16; o > 0; o >>= 1)
+        argmax_combine(best, idx, __shfl_xor_sync(0xFFFFFFFFu, best, o), __shfl_xor_sync(0xFFFFFFFFu, idx, o));
     if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (int w = 1; w < 8; ++w)
-            if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
-        out[blockIdx.x] = idx;
+        for (int w = 1; w < 8; ++w) argmax_combine(best, idx, bv[w], bi[w]);
+        pv[blockIdx.y * kArgSlices + blockIdx.x] = best;
+        pi[blockIdx.y * kArgSlices + blockIdx.x] = idx;
+    }
+}
+__global__ void __launch_bounds__(kArgSlices) argmax_final_kernel(const float* pv, const int* pi, long long* out, int V) {
+    float best = pv[blockIdx.x * kArgSlices + threadIdx.x];
+    int idx = pi[blockIdx.x * kArgSlices + threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        argmax_combine(best, idx, __shfl_xor_sync(0xFFFFFFFFu, best, o), __shfl_xor_sync(0xFFFFFFFFu, idx, o));
+    __shared__ float bv[2];
+    __shared__ int bi[2];
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        argmax_combine(best, idx, bv[1], bi[1]);
+        out[blockIdx.x] = idx < V ? idx : 0;
     }
 }
 
@@ -292,7 +383,8 @@ using namespace rwkvq;
 namespace {
 
 struct Workspace {
-    float *x, *xs, *rkv, *hid, *yl, *og, *xk, *hffn, *xo, *v_first, *logits;
+    float *x, *xs, *rkv, *part, *yl, *og, *xk, *hffn, *xo, *v_first, *logits, *argv;
+    int n_chunks;
     size_t bytes;
 };
 
@@ -305,30 +397,45 @@ Workspace carve(const rwkvq_model& m, int B, void* base) {
         off += ((n * sizeof(float) + 255) / 256) * 256;
         return p;
     };
-    w.x = take(b * D); w.xs = take(6 * b * D); w.rkv = take(3 * b * D); w.hid = take(4 * b * R);
+    w.x = take(b * D); w.xs = take(6 * b * D); w.rkv = take(3 * b * D);
+    w.n_chunks = static_cast<int>((D + kLdRows - 1) / kLdRows);
+    w.part = take(4 * static_cast<size_t>(w.n_chunks) * kLmMaxN * R);
     w.yl = take(4 * b * D); w.og = take(b * D); w.xk = take(b * D); w.hffn = take(b * F);
     w.xo = take(b * D); w.v_first = take(b * D); w.logits = take(b * V);
+    w.argv = take(2 * b * kArgSlices);
     w.bytes = off;
     return w;
 }
 
-int lora_multi(const rwkvq_qtensor* const* ts, const float* const* xs, float* const* ys, const int* acts,
-               int n_br, int B, long long ldx, long long ldy, cudaStream_t s) {
+// y_br = (act_br(x_br @ W1_br)) @ W2_br for up to 4 branches, B right-hand sides
+int lora_pair(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, const float* const* xs,
+              float* const* ys, const int* acts, int n_br, int B, int D, int max_rank, float* part,
+              int n_chunks, cudaStream_t s) {
+    LoraDownArgs d{};
+    LoraUpArgs u{};
     int max_cols = 0;
-    LoraMultiArgs a{};
     for (int i = 0; i < n_br; ++i) {
-        int rc = validate_qtensor(ts[i], "rwkvq_decode_step(lora)");
+        int rc = validate_qtensor(t1[i], "rwkvq_decode_step(lora down)");
         if (rc) return rc;
-        a.t[i] = make_view(*ts[i]);
-        a.x[i] = xs[i]; a.y[i] = ys[i]; a.act[i] = acts[i];
-        if (ts[i]->cols > max_cols) max_cols = ts[i]->cols;
+        rc = validate_qtensor(t2[i], "rwkvq_decode_step(lora up)");
+        if (rc) return rc;
+        RWKVQ_REQUIRE(t1[i]->rows == D && t1[i]->cols == t2[i]->rows && t1[i]->cols <= max_rank &&
+                          t1[i]->cols <= kLmMaxRank,
+                      RWKVQ_E_SHAPE, "rwkvq_decode_step: LoRA branch %d has shapes [%d,%d] x [%d,%d]", i,
+                      t1[i]->rows, t1[i]->cols, t2[i]->rows, t2[i]->cols);
+        d.t[i] = make_view(*t1[i]);
+        u.t[i] = make_view(*t2[i]);
+        u.act[i] = acts[i];
+        if (t2[i]->cols > max_cols) max_cols = t2[i]->cols;
     }
-    a.ldx = ldx; a.ldy = ldy;
+    d.part = part; d.ldx = D; d.n_chunks = n_chunks; d.max_rank = max_rank;
+    u.part = part; u.ldy = D; u.n_chunks = n_chunks; u.max_rank = max_rank;
     for (int n0 = 0; n0 < B; n0 += kLmMaxN) {
-        LoraMultiArgs c = a;
-        c.n_cols = B - n0 < kLmMaxN ? B - n0 : kLmMaxN;
-        for (int i = 0; i < n_br; ++i) { c.x[i] = a.x[i] + n0 * ldx; c.y[i] = a.y[i] + n0 * ldy; }
-        lora_multi_kernel<<<dim3((max_cols + kLmCols - 1) / kLmCols, n_br), kLmWarps * 32, 0, s>>>(c);
+        const int nc = B - n0 < kLmMaxN ? B - n0 : kLmMaxN;
+        d.n_cols = u.n_cols = nc;
+        for (int i = 0; i < n_br; ++i) { d.x[i] = xs[i] + static_cast<size_t>(n0) * D; u.y[i] = ys[i] + static_cast<size_t>(n0) * D; }
+        lora_down_kernel<<<dim3(n_chunks, n_br), 256, 0, s>>>(d);
+        lora_up_kernel<<<dim3((max_cols + kLuCols - 1) / kLuCols, n_br), 256, 0, s>>>(u);
     }
     return RWKVQ_OK;
 }
@@ -378,21 +485,14 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         if (rc) return rc;
         rc = rwkvq_gemv(&L.Wv, xv, RWKVQ_F32, B, D, v, D, RWKVQ_EPI_NONE, nullptr, stream);
         if (rc) return rc;
-        const size_t BR = static_cast<size_t>(B) * m->max_rank;
-        float *hw = w.hid, *ha = w.hid + BR, *hv = w.hid + 2 * BR, *hg = w.hid + 3 * BR;
         float *yw = w.yl, *ya = w.yl + BD, *yv = w.yl + 2 * BD, *yg = w.yl + 3 * BD;
         {
             const rwkvq_qtensor* t1[4] = {&L.w1, &L.a1, &L.g1, &L.v1};
-            const float* x1[4] = {xw, xa, xg, xv};
-            float* y1[4] = {hw, ha, hg, hv};
-            const int act1[4] = {1, 0, 2, 0};
-            rc = lora_multi(t1, x1, y1, act1, layer0 ? 3 : 4, B, D, m->max_rank, s);
-            if (rc) return rc;
             const rwkvq_qtensor* t2[4] = {&L.w2, &L.a2, &L.g2, &L.v2};
-            const float* x2[4] = {hw, ha, hg, hv};
+            const float* x1[4] = {xw, xa, xg, xv};
             float* y2[4] = {yw, ya, yg, yv};
-            const int act2[4] = {0, 0, 0, 0};
-            rc = lora_multi(t2, x2, y2, act2, layer0 ? 3 : 4, B, m->max_rank, D, s);
+            const int act[4] = {1, 0, 2, 0};       // tanh (decay), none, sigmoid (gate), none
+            rc = lora_pair(t1, t2, x1, y2, act, layer0 ? 3 : 4, B, D, m->max_rank, w.part, w.n_chunks, s);
             if (rc) return rc;
         }
         TmixCoreArgs tc{r, k, v, yw, ya, layer0 ? nullptr : yv, yg, L.w0, L.a0, L.v0, L.k_k, L.k_a, L.r_k,
@@ -410,7 +510,12 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
     ln_shift_mix_kernel<<<B, kRowThreads, 0, s>>>(w.x, m->lnout_w, m->lnout_b, nullptr, nullptr, 0, w.xo, B, D);
     rc = rwkvq_gemv(&m->head, w.xo, RWKVQ_F32, B, D, lg, V, RWKVQ_EPI_NONE, nullptr, stream);
     if (rc) return rc;
-    if (next_tokens) argmax_kernel<<<B, 256, 0, s>>>(lg, reinterpret_cast<long long*>(next_tokens), V);
+    if (next_tokens) {
+        float* pv = w.argv;
+        int* pi = reinterpret_cast<int*>(w.argv + static_cast<size_t>(B) * kArgSlices);
+        argmax_partial_kernel<<<dim3(kArgSlices, B), 256, 0, s>>>(lg, pv, pi, V);
+        argmax_final_kernel<<<B, kArgSlices, 0, s>>>(pv, pi, reinterpret_cast<long long*>(next_tokens), V);
+    }
     return check_launch("rwkvq_decode_step");
 }
 
