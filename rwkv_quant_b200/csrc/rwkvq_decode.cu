@@ -79,28 +79,49 @@ __global__ void __launch_bounds__(kRowThreads) embed_ln0_kernel(QView emb, const
 
 // xn = LN(x[b]); prev = shift[b] (zeros for a fresh stream); shift[b] = xn;
 // out[m][b] = xn + (prev - xn) * mix[m]   for m < n_mix   (n_mix = 0: out[0][b] = xn)
-__global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* x, const float* ln_w,
-                                                                  const float* ln_b, float* shift,
-                                                                  const float* mix, int n_mix, float* out,
-                                                                  int B, int D) {
+// All loads are issued before the reductions so that their latencies overlap.
+template <int NMIX>
+__global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* __restrict__ x,
+                                                                  const float* __restrict__ ln_w,
+                                                                  const float* __restrict__ ln_b,
+                                                                  float* __restrict__ shift,
+                                                                  const float* __restrict__ mix,
+                                                                  float* __restrict__ out, int B, int D) {
     __shared__ float red[kRowThreads / 32];
     const int b = blockIdx.x;
-    float v[kRowPer];
+    float v[kRowPer], prev[kRowPer], lw[kRowPer], lb[kRowPer];
 #pragma unroll
     for (int i = 0; i < kRowPer; ++i) {
         const int d = threadIdx.x + i * kRowThreads;
-        v[i] = (d < D) ? x[static_cast<size_t>(b) * D + d] : 0.f;
+        const bool ok = d < D;
+        const size_t bd = static_cast<size_t>(b) * D + d;
+        v[i] = ok ? x[bd] : 0.f;
+        lw[i] = ok ? ln_w[d] : 0.f;
+        lb[i] = ok ? ln_b[d] : 0.f;
+        prev[i] = (ok && NMIX > 0) ? shift[bd] : 0.f;
     }
-    layer_norm_row<kRowPer>(v, D, ln_w, ln_b, red);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < kRowPer; ++i) s += v[i];
+    const float mean = block_sum(s, red) / D;
+    float s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < kRowPer; ++i) {
+        const float c = (threadIdx.x + i * kRowThreads < D) ? v[i] - mean : 0.f;
+        s2 += c * c;
+    }
+    const float inv = 1.0f / sqrtf(block_sum(s2, red) / D + 1e-5f);
 #pragma unroll
     for (int i = 0; i < kRowPer; ++i) {
         const int d = threadIdx.x + i * kRowThreads;
         if (d >= D) continue;
         const size_t bd = static_cast<size_t>(b) * D + d;
-        if (n_mix == 0) { out[bd] = v[i]; continue; }
-        const float xx = shift[bd] - v[i];
-        shift[bd] = v[i];
-        for (int m = 0; m < n_mix; ++m) out[(static_cast<size_t>(m) * B) * D + bd] = v[i] + xx * mix[m * D + d];
+        const float xn = (v[i] - mean) * inv * lw[i] + lb[i];
+        if (NMIX == 0) { out[bd] = xn; continue; }
+        const float xx = prev[i] - xn;
+        shift[bd] = xn;
+#pragma unroll
+        for (int m = 0; m < NMIX; ++m) out[(static_cast<size_t>(m) * B) * D + bd] = xn + xx * __ldg(mix + m * D + d);
     }
 }
 
@@ -133,52 +154,64 @@ struct LoraUpArgs {
     int n_cols, n_chunks, max_rank;
 };
 
-__device__ __forceinline__ void lora_w4(const QView& t, int i, int c, float (&w)[4]) {
+// 4 consecutive weights of stored row i at column c, in the loader's precision.
+// MODE 0: asym, cols % 4 == 0;  1: per-row int8, cols % 4 == 0;  2: anything (slow).
+template <int MODE>
+__device__ __forceinline__ void lora_w4(const QView& t, int i, int c, int nb, int blk, float (&w)[4]) {
     const size_t I = static_cast<size_t>(i);
-    if (t.kind == RWKVQ_KIND_ASYM && (t.cols & 3) == 0) {
+    if (MODE == 0) {
         const uint32_t q = ld_stream_u32(t.codes + I * t.cols + c);
-        const int nb = (t.cols + t.gs - 1) / t.gs;
-        const float s = static_cast<const float*>(t.scale)[I * nb + c / t.gs], m = t.mn[I * nb + c / t.gs];
+        const float s = __ldg(static_cast<const float*>(t.scale) + I * nb + blk), m = __ldg(t.mn + I * nb + blk);
 #pragma unroll
         for (int k = 0; k < 4; ++k) w[k] = __fadd_rn(__fmul_rn(static_cast<float>((q >> (8 * k)) & 0xFFu), s), m);
-    } else if (t.kind == RWKVQ_KIND_RTN && t.bits > 4 && (t.cols & 3) == 0) {
+    } else if (MODE == 1) {
         const uint32_t q = ld_stream_u32(t.codes + I * t.cols + c);
-        const float s = __half2float(static_cast<const __half*>(t.scale)[I]);
+        const float s = __half2float(__ldg(static_cast<const __half*>(t.scale) + I));
 #pragma unroll
         for (int k = 0; k < 4; ++k) w[k] = __fmul_rn(static_cast<float>(static_cast<int8_t>((q >> (8 * k)) & 0xFFu)), s);
     } else {
-#pragma unroll
         for (int k = 0; k < 4; ++k) w[k] = (c + k < t.cols) ? decode_element(t, i, c + k) : 0.f;
     }
 #pragma unroll
     for (int k = 0; k < 4; ++k) w[k] = dense_param_rounding(w[k]);
 }
 
-// 256 threads = 4 row groups x 64 column threads (4 columns each, rank <= 256 per pass)
-__global__ void __launch_bounds__(256) lora_down_kernel(const LoraDownArgs a) {
-    __shared__ float red[4][kLmMaxN][256];
-    const int br = blockIdx.y, chunk = blockIdx.x;
-    const QView& t = a.t[br];
+__device__ __forceinline__ int lora_mode(const QView& t) {
+    if (t.kind == RWKVQ_KIND_ASYM && (t.cols & 3) == 0) return 0;
+    if (t.kind == RWKVQ_KIND_RTN && t.bits > 4 && (t.cols & 3) == 0) return 1;
+    return 2;
+}
+
+// 256 threads = 4 row groups x 64 column threads (4 columns each, 256 columns per pass)
+template <int MODE>
+__device__ __forceinline__ void lora_down_body(const LoraDownArgs& a, const QView& t, const float* __restrict__ x,
+                                               float (&red)[4][kLmMaxN][256]) {
+    const int chunk = blockIdx.x, br = blockIdx.y;
     const int rg = threadIdx.x >> 6, ct = threadIdx.x & 63;
     const int row0 = chunk * kLdRows;
+    const int nb = MODE == 0 ? (t.cols + t.gs - 1) / t.gs : 0;
     for (int c0 = 0; c0 < t.cols; c0 += 256) {
         const int c = c0 + ct * 4;
+        const int blk = MODE == 0 ? c / t.gs : 0;
         float acc[kLmMaxN][4];
 #pragma unroll
         for (int n = 0; n < kLmMaxN; ++n)
 #pragma unroll
             for (int k = 0; k < 4; ++k) acc[n][k] = 0.f;
         if (c < t.cols) {
-#pragma unroll 4
-            for (int i = row0 + rg; i < min(row0 + kLdRows, t.rows); i += 4) {
-                float w[4];
-                lora_w4(t, i, c, w);
+            constexpr int RPT = kLdRows / 4;          // rows per thread, all loads issued together
+            float w[RPT][4];
 #pragma unroll
-                for (int n = 0; n < kLmMaxN; ++n) {
-                    if (n >= a.n_cols) break;
-                    const float xv = __ldg(a.x[br] + n * a.ldx + i);
+            for (int r = 0; r < RPT; ++r) lora_w4<MODE>(t, min(row0 + rg + 4 * r, t.rows - 1), c, nb, blk, w[r]);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) acc[n][k] = fmaf(xv, w[k], acc[n][k]);
+            for (int n = 0; n < kLmMaxN; ++n) {
+                if (n >= a.n_cols) break;
+#pragma unroll
+                for (int r = 0; r < RPT; ++r) {
+                    const int i = row0 + rg + 4 * r;
+                    const float xv = i < t.rows ? __ldg(x + n * a.ldx + i) : 0.f;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) acc[n][k] = fmaf(xv, w[r][k], acc[n][k]);
                 }
             }
         }
@@ -199,7 +232,46 @@ __global__ void __launch_bounds__(256) lora_down_kernel(const LoraDownArgs a) {
     }
 }
 
+__global__ void __launch_bounds__(256) lora_down_kernel(const LoraDownArgs a) {
+    __shared__ float red[4][kLmMaxN][256];
+    const QView& t = a.t[blockIdx.y];
+    const float* x = a.x[blockIdx.y];
+    switch (lora_mode(t)) {
+        case 0: lora_down_body<0>(a, t, x, red); break;
+        case 1: lora_down_body<1>(a, t, x, red); break;
+        default: lora_down_body<2>(a, t, x, red); break;
+    }
+}
+
 // 256 threads = 8 row groups x 32 column threads (4 columns each)
+template <int MODE>
+__device__ __forceinline__ void lora_up_body(const LoraUpArgs& a, const QView& t, const float (&h)[kLmMaxN][kLmMaxRank],
+                                             float (&acc)[kLmMaxN][4]) {
+    const int rg = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.x * kLuCols + lane * 4;
+    const int rank = t.rows;
+    const int nb = MODE == 0 ? (t.cols + t.gs - 1) / t.gs : 0;
+    const int blk = MODE == 0 ? c / t.gs : 0;
+    if (c >= t.cols) return;
+    for (int j0 = rg; j0 < rank; j0 += 64) {          // 8 rows of this thread per batch of loads
+        float w[8][4];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) lora_w4<MODE>(t, min(j0 + 8 * r, rank - 1), c, nb, blk, w[r]);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const int j = j0 + 8 * r;
+            if (j >= rank) break;
+#pragma unroll
+            for (int n = 0; n < kLmMaxN; ++n) {
+                if (n >= a.n_cols) break;
+                const float hv = h[n][j];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc[n][k] = fmaf(hv, w[r][k], acc[n][k]);
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256) lora_up_kernel(const LoraUpArgs a) {
     __shared__ float h[kLmMaxN][kLmMaxRank];
     __shared__ float red[8][kLmMaxN][kLuCols];
@@ -209,34 +281,33 @@ __global__ void __launch_bounds__(256) lora_up_kernel(const LoraUpArgs a) {
     const int rank = t.rows;
     for (int idx = threadIdx.x; idx < a.n_cols * rank; idx += 256) {
         const int n = idx / rank, j = idx % rank;
+        const float* pp = a.part + ((static_cast<size_t>(br) * a.n_chunks) * kLmMaxN + n) * a.max_rank + j;
+        const size_t stride = static_cast<size_t>(kLmMaxN) * a.max_rank;
         float v = 0.f;
-        for (int ch = 0; ch < a.n_chunks; ++ch)
-            v += a.part[((static_cast<size_t>(br) * a.n_chunks + ch) * kLmMaxN + n) * a.max_rank + j];
+        int ch = 0;
+        for (; ch + 8 <= a.n_chunks; ch += 8) {       // 8 loads in flight, summed in chunk order
+            float pv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) pv[u] = __ldcg(pp + (ch + u) * stride);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v += pv[u];
+        }
+        for (; ch < a.n_chunks; ++ch) v += __ldcg(pp + ch * stride);
         if (a.act[br] == 1) v = tanhf(v);
         else if (a.act[br] == 2) v = sigmoidf_(v);
         h[n][j] = v;
     }
     __syncthreads();
     const int rg = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int c = blockIdx.x * kLuCols + lane * 4;
     float acc[kLmMaxN][4];
 #pragma unroll
     for (int n = 0; n < kLmMaxN; ++n)
 #pragma unroll
         for (int k = 0; k < 4; ++k) acc[n][k] = 0.f;
-    if (c < t.cols) {
-#pragma unroll 4
-        for (int j = rg; j < rank; j += 8) {
-            float w[4];
-            lora_w4(t, j, c, w);
-#pragma unroll
-            for (int n = 0; n < kLmMaxN; ++n) {
-                if (n >= a.n_cols) break;
-                const float hv = h[n][j];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) acc[n][k] = fmaf(hv, w[k], acc[n][k]);
-            }
-        }
+    switch (lora_mode(t)) {
+        case 0: lora_up_body<0>(a, t, h, acc); break;
+        case 1: lora_up_body<1>(a, t, h, acc); break;
+        default: lora_up_body<2>(a, t, h, acc); break;
     }
 #pragma unroll
     for (int n = 0; n < kLmMaxN; ++n) {
@@ -273,6 +344,15 @@ __global__ void __launch_bounds__(256) tmix_core_kernel(const TmixCoreArgs p) {
     __shared__ float red[8];
     const int hi = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
     const size_t row = static_cast<size_t>(b) * p.D + hi * 64;
+    // the state slice of this thread is requested first: it is the largest load
+    const int dv = tid >> 2, part = tid & 3;
+    float* hp = p.state + ((static_cast<size_t>(b) * p.H + hi) * 64 + dv) * 64 + part * 16;
+    float h[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 v4 = __ldcs(reinterpret_cast<const float4*>(hp + 4 * i));
+        h[4 * i] = v4.x; h[4 * i + 1] = v4.y; h[4 * i + 2] = v4.z; h[4 * i + 3] = v4.w;
+    }
     float kk = 0.f, av = 0.f;
     if (tid < 64) {
         const int c = hi * 64 + tid;
@@ -294,14 +374,6 @@ __global__ void __launch_bounds__(256) tmix_core_kernel(const TmixCoreArgs p) {
     }
     __syncthreads();
     // one WKV-7 step on the thread's 16 state columns
-    const int dv = tid >> 2, part = tid & 3;
-    float* hp = p.state + ((static_cast<size_t>(b) * p.H + hi) * 64 + dv) * 64 + part * 16;
-    float h[16];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float4 v4 = *reinterpret_cast<const float4*>(hp + 4 * i);
-        h[4 * i] = v4.x; h[4 * i + 1] = v4.y; h[4 * i + 2] = v4.z; h[4 * i + 3] = v4.w;
-    }
     float sa = 0.f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) sa = fmaf(h[i], sA[part * 16 + i], sa);
@@ -475,7 +547,7 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         const rwkvq_layer& L = m->layers[l];
         const bool layer0 = l == 0;
         // ---- time mix
-        ln_shift_mix_kernel<<<B, kRowThreads, 0, s>>>(w.x, L.ln1_w, L.ln1_b, tshift[l], L.x_mix, 6, w.xs, B, D);
+        ln_shift_mix_kernel<6><<<B, kRowThreads, 0, s>>>(w.x, L.ln1_w, L.ln1_b, tshift[l], L.x_mix, w.xs, B, D);
         float *xr = w.xs, *xw = w.xs + BD, *xk = w.xs + 2 * BD, *xv = w.xs + 3 * BD, *xa = w.xs + 4 * BD,
               *xg = w.xs + 5 * BD;
         float *r = w.rkv, *k = w.rkv + BD, *v = w.rkv + 2 * BD;
@@ -501,13 +573,13 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         rc = rwkvq_gemv(&L.Wo, w.og, RWKVQ_F32, B, D, w.x, D, RWKVQ_EPI_ADD, w.x, stream);
         if (rc) return rc;
         // ---- channel mix
-        ln_shift_mix_kernel<<<B, kRowThreads, 0, s>>>(w.x, L.ln2_w, L.ln2_b, cshift[l], L.ffn_x_k, 1, w.xk, B, D);
+        ln_shift_mix_kernel<1><<<B, kRowThreads, 0, s>>>(w.x, L.ln2_w, L.ln2_b, cshift[l], L.ffn_x_k, w.xk, B, D);
         rc = rwkvq_gemv(&L.Wfk, w.xk, RWKVQ_F32, B, D, w.hffn, F, RWKVQ_EPI_RELU2, nullptr, stream);
         if (rc) return rc;
         rc = rwkvq_gemv(&L.Wfv, w.hffn, RWKVQ_F32, B, F, w.x, D, RWKVQ_EPI_ADD, w.x, stream);
         if (rc) return rc;
     }
-    ln_shift_mix_kernel<<<B, kRowThreads, 0, s>>>(w.x, m->lnout_w, m->lnout_b, nullptr, nullptr, 0, w.xo, B, D);
+    ln_shift_mix_kernel<0><<<B, kRowThreads, 0, s>>>(w.x, m->lnout_w, m->lnout_b, nullptr, nullptr, w.xo, B, D);
     rc = rwkvq_gemv(&m->head, w.xo, RWKVQ_F32, B, D, lg, V, RWKVQ_EPI_NONE, nullptr, stream);
     if (rc) return rc;
     if (next_tokens) {
