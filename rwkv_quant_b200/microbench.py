@@ -1,0 +1,127 @@
+"""Small single-purpose runs for profiling and A/B timing.
+
+    python -m rwkv_quant_b200.microbench gemv LAYOUT BITS ROWS COLS [--n N] [--launches K]
+    python -m rwkv_quant_b200.microbench decode [--layers L] [--recipe R] [--steps S] [--batch B]
+    python -m rwkv_quant_b200.microbench sweep          # GEMV shapes of the 1.5B model, GB/s each
+
+`gemv` and `decode` do a handful of launches and exit (suitable under a profiler);
+`sweep` replays a ring of distinct weight buffers (working set >> L2) as a CUDA graph and
+prints microseconds per launch and GB/s of file-format bytes.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+
+import torch
+
+from . import _lib, synth
+from .backends.cuda import QuantRWKV7, ops
+
+_Q = {"sb6": synth.quant_sb6, "sym": synth.quant_sym, "rtn": synth.quant_rtn}
+
+
+def _tensor(layout, bits, rows, cols, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    w = torch.randn(rows, cols, device="cuda", generator=g) * 0.02
+    return ops.DeviceQT(_Q[layout]("w", "g", w, bits))
+
+
+def gemv(layout, bits, rows, cols, n=1, launches=4):
+    lib = _lib.load(check_device=True)
+    dqs = [_tensor(layout, bits, rows, cols, s) for s in range(launches)]
+    x = torch.randn(n, cols, device="cuda")
+    y = torch.empty(n, rows, device="cuda")
+    for d in dqs:
+        _lib.check(lib.rwkvq_gemv(C.byref(d.struct), x.data_ptr(), 0, n, cols, y.data_ptr(), rows, 0, None,
+                                  _lib.stream_ptr()), "rwkvq_gemv")
+    torch.cuda.synchronize()
+    print("ok", float(y.abs().sum()))
+
+
+def decode(layers=4, recipe="compression", steps=3, batch=1, model="1.5b"):
+    ck = synth.build_checkpoint(model, recipe, seed=0, device="cuda", n_layer=layers)
+    m = QuantRWKV7(ck)
+    del ck
+    dec = m.decoder(batch, use_graph=False)
+    for _ in range(steps):
+        dec.step()
+        dec.feed_back()
+    torch.cuda.synchronize()
+    print("ok", dec.next_tokens.tolist())
+
+
+def time_ring(layout, bits, rows, cols, n=1, ring_bytes=1.5e9, iters=5):
+    lib = _lib.load(check_device=True)
+    base = _tensor(layout, bits, rows, cols)
+    nb = base.nbytes_file()
+    k = max(2, min(64, int(ring_bytes // nb)))
+    ring = [base]
+    for _ in range(k - 1):
+        d = object.__new__(ops.DeviceQT)
+        d.__dict__.update(base.__dict__)
+        d.bufs = [b.clone() if b.numel() else b for b in base.bufs]
+        d.struct = ops._descr(d.bufs, d.meta)
+        ring.append(d)
+    x = torch.randn(n, cols, device="cuda")
+    y = torch.empty(n, rows, device="cuda")
+
+    def run():
+        s = _lib.stream_ptr()
+        for d in ring:
+            lib.rwkvq_gemv(C.byref(d.struct), x.data_ptr(), 0, n, cols, y.data_ptr(), rows, 0, None, s)
+    st = torch.cuda.Stream()
+    st.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(st):
+        run()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            run()
+    torch.cuda.current_stream().wait_stream(st)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = 1e9
+    for _ in range(iters):
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    us = best * 1e3 / k
+    print(f"{layout}{bits} [{rows},{cols}] N={n}: {us:8.2f} us/launch {nb / us / 1e3:8.1f} GB/s "
+          f"({nb / 1e6:.2f} MB, ring {k})", flush=True)
+    return us
+
+
+def sweep():
+    for args in [("sb6", 4, 8192, 2048), ("sb6", 4, 2048, 8192), ("sb6", 5, 2048, 2048), ("sb6", 5, 65536, 2048),
+                 ("sb6", 6, 8192, 2048), ("sym", 8, 2048, 2048), ("sym", 6, 8192, 2048), ("sym", 6, 2048, 8192),
+                 ("sym", 8, 65536, 2048), ("rtn", 8, 8192, 2048)]:
+        time_ring(*args)
+    time_ring("sb6", 4, 8192, 2048, n=8)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemv")
+    g.add_argument("layout"); g.add_argument("bits", type=int); g.add_argument("rows", type=int)
+    g.add_argument("cols", type=int); g.add_argument("--n", type=int, default=1)
+    g.add_argument("--launches", type=int, default=4)
+    d = sub.add_parser("decode")
+    d.add_argument("--layers", type=int, default=4); d.add_argument("--recipe", default="compression")
+    d.add_argument("--steps", type=int, default=3); d.add_argument("--batch", type=int, default=1)
+    sub.add_parser("sweep")
+    a = ap.parse_args()
+    if a.cmd == "gemv":
+        gemv(a.layout, a.bits, a.rows, a.cols, a.n, a.launches)
+    elif a.cmd == "decode":
+        decode(a.layers, a.recipe, a.steps, a.batch)
+    else:
+        sweep()
+
+
+if __name__ == "__main__":
+    main()
