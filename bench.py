@@ -209,13 +209,12 @@ def gemv_phase(model, steps, warmup):
 def run_ours(a, rank, world, local_rank):
     import torch
     import torch.distributed as dist
-    from rwkv_quant_b200 import synth
+    from rwkv_quant_b200 import dp, synth
     from rwkv_quant_b200.backends.cuda import QuantRWKV7
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    dp.init("nccl", dev)
     ck = synth.build_checkpoint(a.model, a.recipe, seed=0, device=dev)
     model = QuantRWKV7(ck, device=dev)
     del ck
@@ -225,16 +224,11 @@ def run_ours(a, rank, world, local_rank):
     state_bytes = 2 * model.n_layer * model.n_head * 64 * 64 * 4 * B
 
     def sync_all():
-        if world > 1:
-            dist.barrier()
+        torch.cuda.synchronize()
+        dp.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(sec):
-        if world == 1:
-            return sec
-        t = torch.tensor([sec], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    max_over_ranks = lambda sec: dp.max_over_ranks(sec, dev)
 
     prompt = torch.from_numpy(__import__("numpy").random.default_rng(rank).integers(1, 60000, (B,))).to(dev)
     # ---- device-resident loop: one graph replay per token, argmax fed back on the device
@@ -280,8 +274,7 @@ def run_ours(a, rank, world, local_rank):
     g_bytes, g_launches, g_sec = gemv_phase(model, a.steps, a.warmup)
     peak, peak_kind = measured_peak()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        dp.finalize()
         return
     total_tokens = world * B * a.steps
     value = total_tokens / t_dev
@@ -316,8 +309,7 @@ def run_ours(a, rank, world, local_rank):
                                 "sample": f"{info['tokens_timed']} tokens on a 2-layer build at full width / "
                                           f"vocabulary, scaled to {model.n_layer} layers + head"}
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    dp.finalize()
 
 
 def main():

@@ -294,8 +294,8 @@ class QuantRWKV7:
     @property
     def launches_per_token(self) -> int:
         """Kernels one decoded token launches at batch 1: per layer 2 norm/shift/lerp,
-        6 GEMV, 2 LoRA, 1 time-mix core; plus embedding, final norm, head, argmax (2)."""
-        return self.n_layer * 11 + 5
+        4 GEMV (r/k/v fused), 2 LoRA, 1 time-mix core; plus embedding, final norm, head, argmax (2)."""
+        return self.n_layer * 9 + 5
 
 
 class Decoder:

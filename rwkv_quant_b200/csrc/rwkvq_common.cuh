@@ -21,11 +21,33 @@ int check_launch(const char* what);
         if (!(cond)) return ::rwkvq::fail((code), __VA_ARGS__); \
     } while (0)
 
+// Launch with programmatic stream serialization: the kernel may start while its
+// predecessor in the stream is still draining; it must execute pdl_wait() before it
+// reads anything the predecessor wrote and before its first global write.
+// RWKVQ_PDL=0 in the environment turns the attribute off.
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 static inline bool aligned(const void* p, size_t a) {
     return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0;
 }
 
 // -------------------------------------------------------------- device side
+
+// Programmatic dependent launch: no-ops when the launch did not opt in.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 
 // Weights are read exactly once per launch: bypass L1 allocation so that the
 // activation vector stays cached.
@@ -227,6 +249,6 @@ int validate_qtensor(const rwkvq_qtensor* t, const char* who);
 int mma_layout_of(const rwkvq_qtensor& t);
 int launch_gemv_mma(int layout, const rwkvq_qtensor* ts, int n_mats, const void* x, int x_dtype,
                     long long ldx, float* y, long long ldy, int epilogue, const float* resid,
-                    int fused, cudaStream_t s);
+                    int fused, cudaStream_t s, const void* const* x_each = nullptr);
 
 }  // namespace rwkvq

@@ -1,6 +1,7 @@
 // Error plumbing, argument validation and the dequantisation kernels.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "rwkvq_common.cuh"
 
@@ -21,6 +22,14 @@ int fail(int code, const char* fmt, ...) {
     vsnprintf(g_detail, sizeof(g_detail), fmt, ap);
     va_end(ap);
     return code;
+}
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("RWKVQ_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
 }
 
 int check_launch(const char* what) {

@@ -61,6 +61,8 @@ __global__ void __launch_bounds__(kRowThreads) embed_ln0_kernel(QView emb, const
                                                                float* x, int D) {
     __shared__ float red[kRowThreads / 32];
     const int b = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     long long tok = tokens[b];
     tok = tok < 0 ? 0 : (tok >= emb.rows ? emb.rows - 1 : tok);
     float v[kRowPer];
@@ -90,14 +92,20 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
     __shared__ float red[kRowThreads / 32];
     const int b = blockIdx.x;
     float v[kRowPer], prev[kRowPer], lw[kRowPer], lb[kRowPer];
+    pdl_launch_dependents();
+#pragma unroll
+    for (int i = 0; i < kRowPer; ++i) {          // parameters do not depend on the previous kernel
+        const int d = threadIdx.x + i * kRowThreads;
+        lw[i] = d < D ? ln_w[d] : 0.f;
+        lb[i] = d < D ? ln_b[d] : 0.f;
+    }
+    pdl_wait();
 #pragma unroll
     for (int i = 0; i < kRowPer; ++i) {
         const int d = threadIdx.x + i * kRowThreads;
         const bool ok = d < D;
         const size_t bd = static_cast<size_t>(b) * D + d;
         v[i] = ok ? x[bd] : 0.f;
-        lw[i] = ok ? ln_w[d] : 0.f;
-        lb[i] = ok ? ln_b[d] : 0.f;
         prev[i] = (ok && NMIX > 0) ? shift[bd] : 0.f;
     }
     float s = 0.f;
@@ -203,6 +211,7 @@ __device__ __forceinline__ void lora_down_body(const LoraDownArgs& a, const QVie
             float w[RPT][4];
 #pragma unroll
             for (int r = 0; r < RPT; ++r) lora_w4<MODE>(t, min(row0 + rg + 4 * r, t.rows - 1), c, nb, blk, w[r]);
+            pdl_wait();              // the weights above are constants; x comes from the previous kernel
 #pragma unroll
             for (int n = 0; n < kLmMaxN; ++n) {
                 if (n >= a.n_cols) break;
@@ -215,6 +224,7 @@ __device__ __forceinline__ void lora_down_body(const LoraDownArgs& a, const QVie
                 }
             }
         }
+        pdl_wait();
         __syncthreads();
 #pragma unroll
         for (int n = 0; n < kLmMaxN; ++n) {
@@ -236,6 +246,7 @@ __global__ void __launch_bounds__(256) lora_down_kernel(const LoraDownArgs a) {
     __shared__ float red[4][kLmMaxN][256];
     const QView& t = a.t[blockIdx.y];
     const float* x = a.x[blockIdx.y];
+    pdl_launch_dependents();
     switch (lora_mode(t)) {
         case 0: lora_down_body<0>(a, t, x, red); break;
         case 1: lora_down_body<1>(a, t, x, red); break;
@@ -277,6 +288,8 @@ __global__ void __launch_bounds__(256) lora_up_kernel(const LoraUpArgs a) {
     __shared__ float red[8][kLmMaxN][kLuCols];
     const int br = blockIdx.y;
     const QView& t = a.t[br];
+    pdl_launch_dependents();
+    pdl_wait();
     if (blockIdx.x * kLuCols >= t.cols) return;
     const int rank = t.rows;
     for (int idx = threadIdx.x; idx < a.n_cols * rank; idx += 256) {
@@ -353,6 +366,8 @@ __global__ void __launch_bounds__(256) tmix_core_kernel(const TmixCoreArgs p) {
         const float4 v4 = __ldcs(reinterpret_cast<const float4*>(hp + 4 * i));
         h[4 * i] = v4.x; h[4 * i + 1] = v4.y; h[4 * i + 2] = v4.z; h[4 * i + 3] = v4.w;
     }
+    pdl_launch_dependents();
+    pdl_wait();            // the state above was written a whole token ago
     float kk = 0.f, av = 0.f;
     if (tid < 64) {
         const int c = hi * 64 + tid;
@@ -415,6 +430,8 @@ __device__ __forceinline__ void argmax_combine(float& best, int& idx, float ov, 
 __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* logits, float* pv, int* pi, int V) {
     __shared__ float bv[8];
     __shared__ int bi[8];
+    pdl_launch_dependents();
+    pdl_wait();
     const float* row = logits + static_cast<size_t>(blockIdx.y) * V;
     const int per = (V + kArgSlices - 1) / kArgSlices;
     const int lo = blockIdx.x * per, hi = min(lo + per, V);
@@ -433,6 +450,7 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* logits
     }
 }
 __global__ void __launch_bounds__(kArgSlices) argmax_final_kernel(const float* pv, const int* pi, long long* out, int V) {
+    pdl_wait();
     float best = pv[blockIdx.x * kArgSlices + threadIdx.x];
     int idx = pi[blockIdx.x * kArgSlices + threadIdx.x];
 #pragma unroll
@@ -506,8 +524,8 @@ int lora_pair(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, co
         const int nc = B - n0 < kLmMaxN ? B - n0 : kLmMaxN;
         d.n_cols = u.n_cols = nc;
         for (int i = 0; i < n_br; ++i) { d.x[i] = xs[i] + static_cast<size_t>(n0) * D; u.y[i] = ys[i] + static_cast<size_t>(n0) * D; }
-        lora_down_kernel<<<dim3(n_chunks, n_br), 256, 0, s>>>(d);
-        lora_up_kernel<<<dim3((max_cols + kLuCols - 1) / kLuCols, n_br), 256, 0, s>>>(u);
+        launch_pdl(lora_down_kernel, dim3(n_chunks, n_br), dim3(256), 0, s, d);
+        launch_pdl(lora_up_kernel, dim3((max_cols + kLuCols - 1) / kLuCols, n_br), dim3(256), 0, s, u);
     }
     return RWKVQ_OK;
 }
@@ -541,22 +559,36 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
     if (rc) return rc;
     float* lg = logits ? logits : w.logits;
 
-    embed_ln0_kernel<<<B, kRowThreads, 0, s>>>(make_view(m->emb), reinterpret_cast<const long long*>(tokens),
-                                              m->ln0_w, m->ln0_b, w.x, D);
+    launch_pdl(embed_ln0_kernel, dim3(B), dim3(kRowThreads), 0, s, make_view(m->emb),
+               reinterpret_cast<const long long*>(tokens), m->ln0_w, m->ln0_b, w.x, D);
     for (int l = 0; l < m->n_layer; ++l) {
         const rwkvq_layer& L = m->layers[l];
         const bool layer0 = l == 0;
         // ---- time mix
-        ln_shift_mix_kernel<6><<<B, kRowThreads, 0, s>>>(w.x, L.ln1_w, L.ln1_b, tshift[l], L.x_mix, w.xs, B, D);
+        launch_pdl(ln_shift_mix_kernel<6>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln1_w, L.ln1_b, tshift[l], L.x_mix, w.xs, B, D);
         float *xr = w.xs, *xw = w.xs + BD, *xk = w.xs + 2 * BD, *xv = w.xs + 3 * BD, *xa = w.xs + 4 * BD,
               *xg = w.xs + 5 * BD;
         float *r = w.rkv, *k = w.rkv + BD, *v = w.rkv + 2 * BD;
-        rc = rwkvq_gemv(&L.Wr, xr, RWKVQ_F32, B, D, r, D, RWKVQ_EPI_NONE, nullptr, stream);
-        if (rc) return rc;
-        rc = rwkvq_gemv(&L.Wk, xk, RWKVQ_F32, B, D, k, D, RWKVQ_EPI_NONE, nullptr, stream);
-        if (rc) return rc;
-        rc = rwkvq_gemv(&L.Wv, xv, RWKVQ_F32, B, D, v, D, RWKVQ_EPI_NONE, nullptr, stream);
-        if (rc) return rc;
+        const int ml = mma_layout_of(L.Wr);
+        if (B == 1 && ml >= 0 && mma_layout_of(L.Wk) == ml && mma_layout_of(L.Wv) == ml && L.Wk.rows == D &&
+            L.Wv.rows == D && L.Wr.rows == D && L.Wk.cols == D && L.Wv.cols == D && L.Wr.cols == D) {
+            // r, k, v in one launch: three matrices, three inputs (rows 0, 2, 3 of xs)
+            for (const rwkvq_qtensor* t : {&L.Wr, &L.Wk, &L.Wv}) {
+                rc = validate_qtensor(t, "rwkvq_decode_step(r/k/v)");
+                if (rc) return rc;
+            }
+            const rwkvq_qtensor three[3] = {L.Wr, L.Wk, L.Wv};
+            const void* x_each[3] = {xr, xk, xv};
+            rc = launch_gemv_mma(ml, three, 3, xr, RWKVQ_F32, D, r, D, RWKVQ_EPI_NONE, nullptr, 1, s, x_each);
+            if (rc) return rc;
+        } else {
+            rc = rwkvq_gemv(&L.Wr, xr, RWKVQ_F32, B, D, r, D, RWKVQ_EPI_NONE, nullptr, stream);
+            if (rc) return rc;
+            rc = rwkvq_gemv(&L.Wk, xk, RWKVQ_F32, B, D, k, D, RWKVQ_EPI_NONE, nullptr, stream);
+            if (rc) return rc;
+            rc = rwkvq_gemv(&L.Wv, xv, RWKVQ_F32, B, D, v, D, RWKVQ_EPI_NONE, nullptr, stream);
+            if (rc) return rc;
+        }
         float *yw = w.yl, *ya = w.yl + BD, *yv = w.yl + 2 * BD, *yg = w.yl + 3 * BD;
         {
             const rwkvq_qtensor* t1[4] = {&L.w1, &L.a1, &L.g1, &L.v1};
@@ -569,24 +601,24 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         }
         TmixCoreArgs tc{r, k, v, yw, ya, layer0 ? nullptr : yv, yg, L.w0, L.a0, L.v0, L.k_k, L.k_a, L.r_k,
                         L.lnx_w, L.lnx_b, w.v_first, wkv[l], w.og, D, H, layer0 ? 1 : 0};
-        tmix_core_kernel<<<dim3(H, B), 256, 0, s>>>(tc);
+        launch_pdl(tmix_core_kernel, dim3(H, B), dim3(256), 0, s, tc);
         rc = rwkvq_gemv(&L.Wo, w.og, RWKVQ_F32, B, D, w.x, D, RWKVQ_EPI_ADD, w.x, stream);
         if (rc) return rc;
         // ---- channel mix
-        ln_shift_mix_kernel<1><<<B, kRowThreads, 0, s>>>(w.x, L.ln2_w, L.ln2_b, cshift[l], L.ffn_x_k, w.xk, B, D);
+        launch_pdl(ln_shift_mix_kernel<1>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln2_w, L.ln2_b, cshift[l], L.ffn_x_k, w.xk, B, D);
         rc = rwkvq_gemv(&L.Wfk, w.xk, RWKVQ_F32, B, D, w.hffn, F, RWKVQ_EPI_RELU2, nullptr, stream);
         if (rc) return rc;
         rc = rwkvq_gemv(&L.Wfv, w.hffn, RWKVQ_F32, B, F, w.x, D, RWKVQ_EPI_ADD, w.x, stream);
         if (rc) return rc;
     }
-    ln_shift_mix_kernel<0><<<B, kRowThreads, 0, s>>>(w.x, m->lnout_w, m->lnout_b, nullptr, nullptr, w.xo, B, D);
+    launch_pdl(ln_shift_mix_kernel<0>, dim3(B), dim3(kRowThreads), 0, s, w.x, m->lnout_w, m->lnout_b, static_cast<float*>(nullptr), static_cast<const float*>(nullptr), w.xo, B, D);
     rc = rwkvq_gemv(&m->head, w.xo, RWKVQ_F32, B, D, lg, V, RWKVQ_EPI_NONE, nullptr, stream);
     if (rc) return rc;
     if (next_tokens) {
         float* pv = w.argv;
         int* pi = reinterpret_cast<int*>(w.argv + static_cast<size_t>(B) * kArgSlices);
-        argmax_partial_kernel<<<dim3(kArgSlices, B), 256, 0, s>>>(lg, pv, pi, V);
-        argmax_final_kernel<<<B, kArgSlices, 0, s>>>(pv, pi, reinterpret_cast<long long*>(next_tokens), V);
+        launch_pdl(argmax_partial_kernel, dim3(kArgSlices, B), dim3(256), 0, s, static_cast<const float*>(lg), pv, pi, V);
+        launch_pdl(argmax_final_kernel, dim3(B), dim3(kArgSlices), 0, s, static_cast<const float*>(pv), static_cast<const int*>(pi), reinterpret_cast<long long*>(next_tokens), V);
     }
     return check_launch("rwkvq_decode_step");
 }

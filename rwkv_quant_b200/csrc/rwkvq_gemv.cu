@@ -252,6 +252,7 @@ struct Chunk<CK_RTN8> {
 template <int KIND, int R, int NC>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 gemv_chunk_kernel(const GemvArgs a) {
+    pdl_wait();
     const QView& t = a.t[blockIdx.y];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = (blockIdx.x * kWarpsPerCta + warp) * R;
@@ -310,6 +311,7 @@ gemv_chunk_kernel(const GemvArgs a) {
 // decode element by element.  Slow; serves dense bf16, rtn nibbles, asym in
 // [out, in] orientation and shapes the chunk kernels reject.
 __global__ void __launch_bounds__(kWarpsPerCta * 32) gemv_generic_kernel(const GemvArgs a) {
+    pdl_wait();
     const QView& t = a.t[0];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * kWarpsPerCta + warp;

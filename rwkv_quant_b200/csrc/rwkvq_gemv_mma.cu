@@ -31,6 +31,7 @@ constexpr int kMmaMaxFused = 4;
 struct MmaArgs {
     QView t[kMmaMaxFused];
     const void* x;      // [n_mats, ldx] (fused) or [ldx]
+    const void* xk[kMmaMaxFused];   // optional per-matrix inputs (fused launches with scattered rows)
     int x_dtype;
     long long ldx;
     float* y;
@@ -303,11 +304,15 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaAr
         ++i_n;
         if (++i_j == ipt) { i_j = 0; i_tile += step; }
     };
-    // the first weight loads go out before the activations are touched
+    // the first weight loads go out before the activations are touched (and before the
+    // producer of the activations has finished, when launched programmatically)
+    pdl_launch_dependents();
     fetch_next();
+    pdl_wait();
 
     const size_t esz = (a.x_dtype == RWKVQ_F32) ? 4 : 2;
-    const char* xv = static_cast<const char*>(a.x) + (a.fused ? blockIdx.y * a.ldx * esz : 0);
+    const char* xv = a.xk[blockIdx.y] ? static_cast<const char*>(a.xk[blockIdx.y])
+                                      : static_cast<const char*>(a.x) + (a.fused ? blockIdx.y * a.ldx * esz : 0);
     bool finite;
     const float unscale = prepare_x(xv, a.x_dtype, n_in, L == ML_SYM8 ? 19 : 20, dig, xs16, red, finite);
     __syncthreads();
@@ -485,7 +490,9 @@ static int launch_one(const MmaArgs& a, int rows, int cols, int n_mats, cudaStre
     }
     const int units = ((rows + 15) / 16 + WT - 1) / WT;
     const int cap = kResidentCtas / n_mats > 0 ? kResidentCtas / n_mats : 1;
-    gemv_mma_kernel<L, WK><<<dim3(units < cap ? units : cap, n_mats), kMmaWarps * 32, smem, s>>>(a);
+    cudaError_t le = launch_pdl(gemv_mma_kernel<L, WK>, dim3(units < cap ? units : cap, n_mats), dim3(kMmaWarps * 32),
+                                smem, s, a);
+    if (le != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "gemv_mma: %s", cudaGetErrorString(le));
     return RWKVQ_OK;
 }
 
@@ -501,9 +508,9 @@ static int launch_wk(const MmaArgs& a, int rows, int cols, int n_mats, cudaStrea
 // Launch the single-vector tensor-core GEMV for `n_mats` same-shape matrices.
 int launch_gemv_mma(int layout, const rwkvq_qtensor* ts, int n_mats, const void* x, int x_dtype,
                     long long ldx, float* y, long long ldy, int epilogue, const float* resid,
-                    int fused, cudaStream_t s) {
+                    int fused, cudaStream_t s, const void* const* x_each) {
     MmaArgs a{};
-    for (int k = 0; k < n_mats; ++k) a.t[k] = make_view(ts[k]);
+    for (int k = 0; k < n_mats; ++k) { a.t[k] = make_view(ts[k]); a.xk[k] = x_each ? x_each[k] : nullptr; }
     a.x = x; a.x_dtype = x_dtype; a.ldx = ldx; a.y = y; a.ldy = ldy;
     a.resid = resid; a.epilogue = epilogue; a.fused = fused;
     const int rows = ts[0].rows, cols = ts[0].cols;
