@@ -1,3 +1,7 @@
+// Every kernel here may be launched programmatically (resident while its producer is
+// still running), so values produced by earlier kernels are read with L2-coherent
+// loads (__ldcg) after pdl_wait(); only weights and parameters use cached paths.
+//
 // Single-token decode step of a quantized RWKV-7 model: the glue kernels between
 // the GEMVs and the host-side launch sequence (rwkvq_decode_step).
 //
@@ -63,7 +67,7 @@ __global__ void __launch_bounds__(kRowThreads) embed_ln0_kernel(QView emb, const
     const int b = blockIdx.x;
     pdl_launch_dependents();
     pdl_wait();
-    long long tok = tokens[b];
+    long long tok = __ldcg(tokens + b);
     tok = tok < 0 ? 0 : (tok >= emb.rows ? emb.rows - 1 : tok);
     float v[kRowPer];
 #pragma unroll
@@ -105,8 +109,8 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
         const int d = threadIdx.x + i * kRowThreads;
         const bool ok = d < D;
         const size_t bd = static_cast<size_t>(b) * D + d;
-        v[i] = ok ? x[bd] : 0.f;
-        prev[i] = (ok && NMIX > 0) ? shift[bd] : 0.f;
+        v[i] = ok ? __ldcg(x + bd) : 0.f;
+        prev[i] = (ok && NMIX > 0) ? __ldcg(shift + bd) : 0.f;
     }
     float s = 0.f;
 #pragma unroll
@@ -218,7 +222,7 @@ __device__ __forceinline__ void lora_down_body(const LoraDownArgs& a, const QVie
 #pragma unroll
                 for (int r = 0; r < RPT; ++r) {
                     const int i = row0 + rg + 4 * r;
-                    const float xv = i < t.rows ? __ldg(x + n * a.ldx + i) : 0.f;
+                    const float xv = i < t.rows ? __ldcg(x + n * a.ldx + i) : 0.f;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) acc[n][k] = fmaf(xv, w[r][k], acc[n][k]);
                 }
@@ -371,15 +375,15 @@ __global__ void __launch_bounds__(256) tmix_core_kernel(const TmixCoreArgs p) {
     float kk = 0.f, av = 0.f;
     if (tid < 64) {
         const int c = hi * 64 + tid;
-        const float r = p.r[row + tid], k = p.k[row + tid];
-        float v = p.v[row + tid];
-        const float w = expf(-0.606531f * sigmoidf_(p.yw[row + tid] + p.w0[c]));
-        av = sigmoidf_(p.ya[row + tid] + p.a0[c]);
+        const float r = __ldcg(p.r + row + tid), k = __ldcg(p.k + row + tid);
+        float v = __ldcg(p.v + row + tid);
+        const float w = expf(-0.606531f * sigmoidf_(__ldcg(p.yw + row + tid) + p.w0[c]));
+        av = sigmoidf_(__ldcg(p.ya + row + tid) + p.a0[c]);
         kk = k * p.k_k[c];
         const float k2 = k * (1.0f + (av - 1.0f) * p.k_a[c]);
         if (p.layer0) p.v_first[row + tid] = v;
-        else v = v + (p.v_first[row + tid] - v) * sigmoidf_(p.yv[row + tid] + p.v0[c]);
-        sW[tid] = w; sK[tid] = k2; sR[tid] = r; sV[tid] = v; sG[tid] = p.g[row + tid];
+        else v = v + (__ldcg(p.v_first + row + tid) - v) * sigmoidf_(__ldcg(p.yv + row + tid) + p.v0[c]);
+        sW[tid] = w; sK[tid] = k2; sR[tid] = r; sV[tid] = v; sG[tid] = __ldcg(p.g + row + tid);
     }
     const float n2 = block_sum(tid < 64 ? kk * kk : 0.f, red);
     if (tid < 64) {
@@ -437,7 +441,7 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* logits
     const int lo = blockIdx.x * per, hi = min(lo + per, V);
     float best = -INFINITY;
     int idx = V;
-    for (int i = lo + threadIdx.x; i < hi; i += 256) argmax_combine(best, idx, row[i], i);
+    for (int i = lo + threadIdx.x; i < hi; i += 256) argmax_combine(best, idx, __ldcg(row + i), i);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1)
         argmax_combine(best, idx, __shfl_xor_sync(0xFFFFFFFFu, best, o), __shfl_xor_sync(0xFFFFFFFFu, idx, o));
@@ -451,8 +455,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* logits
 }
 __global__ void __launch_bounds__(kArgSlices) argmax_final_kernel(const float* pv, const int* pi, long long* out, int V) {
     pdl_wait();
-    float best = pv[blockIdx.x * kArgSlices + threadIdx.x];
-    int idx = pi[blockIdx.x * kArgSlices + threadIdx.x];
+    float best = __ldcg(pv + blockIdx.x * kArgSlices + threadIdx.x);
+    int idx = __ldcg(pi + blockIdx.x * kArgSlices + threadIdx.x);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1)
         argmax_combine(best, idx, __shfl_xor_sync(0xFFFFFFFFu, best, o), __shfl_xor_sync(0xFFFFFFFFu, idx, o));

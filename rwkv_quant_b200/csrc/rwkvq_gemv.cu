@@ -36,7 +36,7 @@ __device__ __forceinline__ float apply_epilogue(float v, int epi, const float* r
         v = fmaxf(v, 0.0f);
         return v * v;
     }
-    if (epi == RWKVQ_EPI_ADD) return __fadd_rn(v, resid[idx]);
+    if (epi == RWKVQ_EPI_ADD) return __fadd_rn(v, __ldcg(resid + idx));
     return v;
 }
 
@@ -47,14 +47,14 @@ __device__ __forceinline__ void load_x_chunk(const void* x, int dtype, int p, fl
         const float4* xp = reinterpret_cast<const float4*>(static_cast<const float*>(x) + p * 32);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const float4 v = __ldg(xp + i);
+            const float4 v = __ldcg(xp + i);
             xs[4 * i + 0] = v.x; xs[4 * i + 1] = v.y; xs[4 * i + 2] = v.z; xs[4 * i + 3] = v.w;
         }
     } else {
         const uint4* xp = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + p * 32);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const uint4 v = __ldg(xp + i);
+            const uint4 v = __ldcg(xp + i);
             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int k = 0; k < 4; ++k) {

@@ -205,8 +205,10 @@ __device__ __forceinline__ void a_words(const uint4 (&c)[2], const uint4& planes
 //   xs16[k]    sum of X over elements 16k..16k+15 (exact, as float)
 // Returns 2^-e (the factor that undoes the scaling) and whether x was finite.
 __device__ __forceinline__ float4 load_x4(const void* x, int dtype, int i) {
-    if (dtype == RWKVQ_F32) return __ldg(reinterpret_cast<const float4*>(x) + i);
-    const uint2 v = __ldg(reinterpret_cast<const uint2*>(x) + i);
+    // L2-coherent loads: under programmatic dependent launch this kernel is resident
+    // while its producer still writes x, so the L1 / read-only path must not be used
+    if (dtype == RWKVQ_F32) return __ldcg(reinterpret_cast<const float4*>(x) + i);
+    const uint2 v = __ldcg(reinterpret_cast<const uint2*>(x) + i);
     if (dtype == RWKVQ_F16) {
         const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
         const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
@@ -408,7 +410,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaAr
                 v = finite ? v * unscale : NAN;
                 const long long idx = (a.fused ? static_cast<long long>(blockIdx.y) * a.ldy : 0) + row;
                 if (a.epilogue == RWKVQ_EPI_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
-                else if (a.epilogue == RWKVQ_EPI_ADD) v = __fadd_rn(v, a.resid[idx]);
+                else if (a.epilogue == RWKVQ_EPI_ADD) v = __fadd_rn(v, __ldcg(a.resid + idx));
                 a.y[idx] = v;
             }
         }

@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(kLoraWarps * 32) gemv_t_kernel(const LoraArgs 
 #pragma unroll
             for (int n = 0; n < kLoraMaxN; ++n) {
                 if (n >= a.n_cols) break;
-                const float xv = __ldg(a.x + n * a.ldx + i);
+                const float xv = __ldcg(a.x + n * a.ldx + i);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) acc[n][k] = fmaf(xv, w[k], acc[n][k]);
             }
