@@ -132,6 +132,23 @@ int rwkvq_gemv(const rwkvq_qtensor* t, const void* x, int x_dtype, int N, int64_
                float* y, int64_t ldy, int epilogue, const float* resid, void* stream);
 
 /*
+ * Quantized linear for MANY right-hand sides on the tcgen05 tensor cores (prefill,
+ * batched decode):  y[n, o] = epi( sum_c W[o, c] x[n, c] ),  n < M.
+ * Stands behind the N >= 128 branch of GwQuantLinear.__call__ / SymQuantLinear.__call__
+ * (backends/metal/quant_linear_gw.py:846-849, quant_linear_sym.py:481-484: dequantise to
+ * fp16, then a dense matmul) with the dequantisation fused into the operand producer, so
+ * no dense copy of W is ever written.  Operands are fp16 (weights: fp16(q*s+m); tokens:
+ * scaled per row by a power of two), accumulation fp32 in tensor memory.
+ *   x [M, ldx] fp32, y [M, ldy] fp32, sb6 / sym tensors only.
+ *   workspace: rwkvq_gemm_workspace_bytes(M) bytes; its first int32 is a status word the
+ *   kernel sets to RWKVQ_E_TIMEOUT if a bounded wait on the tensor-core pipeline ran out
+ *   (read it after synchronising the stream; 0 = ok).
+ */
+size_t rwkvq_gemm_workspace_bytes(int M);
+int rwkvq_gemm(const rwkvq_qtensor* t, const float* x, int M, int64_t ldx, float* y, int64_t ldy,
+               int epilogue, const float* resid, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * K same-shape matrices, K different inputs, one launch: y[k] = W_k x[k].
  * Stands behind GwQuantLinearFused / SymQuantLinearFused
  * (quant_linear_gw.py:943-1020, quant_linear_sym.py:519-574); results are
@@ -194,7 +211,9 @@ typedef struct rwkvq_model {
     const rwkvq_layer* layers;          /* HOST array [n_layer] */
 } rwkvq_model;
 
-/* Bytes of device scratch rwkvq_decode_step needs for batch B (logits included). */
+/* Bytes of device scratch rwkvq_decode_step needs for batch B (logits included).
+ * The workspace must be zero-filled once before its first use (arrival counters of
+ * the K-split GEMV live in it and reset themselves after every launch). */
 size_t rwkvq_decode_workspace_bytes(const rwkvq_model* m_host, int B);
 
 /*

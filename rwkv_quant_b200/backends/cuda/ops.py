@@ -190,6 +190,26 @@ def _(bufs, meta, x, act, round_w):
     return torch.empty((x.shape[0], meta[3]), dtype=torch.float32, device=x.device)
 
 
+def gemm(dq: "DeviceQT", x: torch.Tensor, epilogue: int = 0, resid: Optional[torch.Tensor] = None,
+         check: bool = False) -> torch.Tensor:
+    """x [M, IN] fp32 -> y [M, OUT] fp32 on the tcgen05 tensor cores with the dequantisation
+    fused into the operand producer (sb6 / sym tensors).  ``check`` synchronises and raises
+    if the kernel reported that a bounded pipeline wait ran out."""
+    _require_cuda(x, resid)
+    lib = _lib.load()
+    x = x.float().contiguous()
+    m = x.shape[0]
+    nws = lib.rwkvq_gemm_workspace_bytes(m)
+    ws = torch.empty(nws, dtype=torch.uint8, device=x.device)
+    y = torch.empty((m, dq.rows), dtype=torch.float32, device=x.device)
+    _lib.check(lib.rwkvq_gemm(C.byref(dq.struct), x.data_ptr(), m, x.stride(0), y.data_ptr(), y.stride(0),
+                              epilogue, _lib.ptr(resid), ws.data_ptr(), nws, _lib.stream_ptr()), "rwkvq_gemm")
+    if check:
+        st = int(ws[:4].view(torch.int32).item())
+        _lib.check(st, "rwkvq_gemm(kernel status)")
+    return y
+
+
 def gemv_fused(dqts: Sequence[DeviceQT], xstack: torch.Tensor) -> torch.Tensor:
     """K same-shape matrices, K inputs [K, IN] -> [K, OUT], one launch."""
     _require_cuda(xstack)

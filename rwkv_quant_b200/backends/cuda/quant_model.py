@@ -154,7 +154,7 @@ class QuantRWKV7:
     def _workspace(self, B):
         if B not in self._ws:
             n = _lib.load().rwkvq_decode_workspace_bytes(C.byref(self._model_c), B)
-            self._ws[B] = torch.empty(n, dtype=torch.uint8, device=self.device)
+            self._ws[B] = torch.zeros(n, dtype=torch.uint8, device=self.device)    # counters start at zero
         return self._ws[B]
 
     def _decode(self, tokens, states, logits=None, next_tokens=None):

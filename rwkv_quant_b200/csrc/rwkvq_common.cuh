@@ -249,6 +249,7 @@ int validate_qtensor(const rwkvq_qtensor* t, const char* who);
 int mma_layout_of(const rwkvq_qtensor& t);
 int launch_gemv_mma(int layout, const rwkvq_qtensor* ts, int n_mats, const void* x, int x_dtype,
                     long long ldx, float* y, long long ldy, int epilogue, const float* resid,
-                    int fused, cudaStream_t s, const void* const* x_each = nullptr);
+                    int fused, cudaStream_t s, const void* const* x_each = nullptr, float* scratch = nullptr);
+size_t gemv_mma_scratch_bytes();
 
 }  // namespace rwkvq

@@ -477,7 +477,7 @@ using namespace rwkvq;
 namespace {
 
 struct Workspace {
-    float *x, *xs, *rkv, *part, *yl, *og, *xk, *hffn, *xo, *v_first, *logits, *argv;
+    float *x, *xs, *rkv, *part, *yl, *og, *xk, *hffn, *xo, *v_first, *logits, *argv, *gscratch;
     int n_chunks;
     size_t bytes;
 };
@@ -497,11 +497,26 @@ Workspace carve(const rwkvq_model& m, int B, void* base) {
     w.yl = take(4 * b * D); w.og = take(b * D); w.xk = take(b * D); w.hffn = take(b * F);
     w.xo = take(b * D); w.v_first = take(b * D); w.logits = take(b * V);
     w.argv = take(2 * b * kArgSlices);
+    w.gscratch = take(gemv_mma_scratch_bytes() / sizeof(float));
     w.bytes = off;
     return w;
 }
 
 // y_br = (act_br(x_br @ W1_br)) @ W2_br for up to 4 branches, B right-hand sides
+// One quantized linear for B right-hand sides; the single-vector tensor-core kernel gets
+// the K-split scratch, everything else goes through the public entry point.
+int linear(const rwkvq_qtensor* t, const float* x, int B, int in, float* y, int out, int epi, const float* resid,
+           float* scratch, void* stream) {
+    const int ml = mma_layout_of(*t);
+    if (B == 1 && ml >= 0) {
+        int rc = validate_qtensor(t, "rwkvq_decode_step(linear)");
+        if (rc) return rc;
+        return launch_gemv_mma(ml, t, 1, x, RWKVQ_F32, in, y, out, epi, resid, 0, static_cast<cudaStream_t>(stream),
+                               nullptr, scratch);
+    }
+    return rwkvq_gemv(t, x, RWKVQ_F32, B, in, y, out, epi, resid, stream);
+}
+
 int lora_pair(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, const float* const* xs,
               float* const* ys, const int* acts, int n_br, int B, int D, int max_rank, float* part,
               int n_chunks, cudaStream_t s) {
@@ -583,7 +598,7 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
             }
             const rwkvq_qtensor three[3] = {L.Wr, L.Wk, L.Wv};
             const void* x_each[3] = {xr, xk, xv};
-            rc = launch_gemv_mma(ml, three, 3, xr, RWKVQ_F32, D, r, D, RWKVQ_EPI_NONE, nullptr, 1, s, x_each);
+            rc = launch_gemv_mma(ml, three, 3, xr, RWKVQ_F32, D, r, D, RWKVQ_EPI_NONE, nullptr, 1, s, x_each, w.gscratch);
             if (rc) return rc;
         } else {
             rc = rwkvq_gemv(&L.Wr, xr, RWKVQ_F32, B, D, r, D, RWKVQ_EPI_NONE, nullptr, stream);
@@ -606,17 +621,17 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         TmixCoreArgs tc{r, k, v, yw, ya, layer0 ? nullptr : yv, yg, L.w0, L.a0, L.v0, L.k_k, L.k_a, L.r_k,
                         L.lnx_w, L.lnx_b, w.v_first, wkv[l], w.og, D, H, layer0 ? 1 : 0};
         launch_pdl(tmix_core_kernel, dim3(H, B), dim3(256), 0, s, tc);
-        rc = rwkvq_gemv(&L.Wo, w.og, RWKVQ_F32, B, D, w.x, D, RWKVQ_EPI_ADD, w.x, stream);
+        rc = linear(&L.Wo, w.og, B, D, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, stream);
         if (rc) return rc;
         // ---- channel mix
         launch_pdl(ln_shift_mix_kernel<1>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln2_w, L.ln2_b, cshift[l], L.ffn_x_k, w.xk, B, D);
-        rc = rwkvq_gemv(&L.Wfk, w.xk, RWKVQ_F32, B, D, w.hffn, F, RWKVQ_EPI_RELU2, nullptr, stream);
+        rc = linear(&L.Wfk, w.xk, B, D, w.hffn, F, RWKVQ_EPI_RELU2, nullptr, w.gscratch, stream);
         if (rc) return rc;
-        rc = rwkvq_gemv(&L.Wfv, w.hffn, RWKVQ_F32, B, F, w.x, D, RWKVQ_EPI_ADD, w.x, stream);
+        rc = linear(&L.Wfv, w.hffn, B, F, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, stream);
         if (rc) return rc;
     }
     launch_pdl(ln_shift_mix_kernel<0>, dim3(B), dim3(kRowThreads), 0, s, w.x, m->lnout_w, m->lnout_b, static_cast<float*>(nullptr), static_cast<const float*>(nullptr), w.xo, B, D);
-    rc = rwkvq_gemv(&m->head, w.xo, RWKVQ_F32, B, D, lg, V, RWKVQ_EPI_NONE, nullptr, stream);
+    rc = linear(&m->head, w.xo, B, D, lg, V, RWKVQ_EPI_NONE, nullptr, w.gscratch, stream);
     if (rc) return rc;
     if (next_tokens) {
         float* pv = w.argv;

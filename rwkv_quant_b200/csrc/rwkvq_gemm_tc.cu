@@ -1,0 +1,369 @@
+// Dequant-fused tensor-core GEMM for many right-hand sides (prefill, batched decode):
+//     y[n, o] = epi( sum_c W[o, c] * x[n, c] ),   n < M tokens.
+//
+// tcgen05 formulation: the WEIGHTS are the M = 128 operand, the tokens are the UMMA N
+// dimension (16..256), so the packed weight stream is read exactly once per token tile
+// and the accumulator D[128 out-rows, N tokens] lives in tensor memory.
+//   producers (all 256 threads of the CTA): unpack a [128 rows, 64 K] slab of the file
+//     layout (nibbles / planes / int8 + block scales) to fp16 = fp16(q*s + m) with one
+//     HFMA2 per two weights (s and m ARE fp16 values by the codec's definition, so the
+//     fused multiply-add rounds the exact value once) and store it K-major with the
+//     128-byte swizzle the UMMA shared-memory descriptor expects; the same threads
+//     convert the activation slab [N, 64 K] fp32 -> fp16 (scaled per token by a power
+//     of two so that no value leaves the fp16 range);
+//   one elected thread issues four tcgen05.mma (K = 16 each) per slab and commits them
+//     to the mbarrier that frees the slab's ring stage;
+//   epilogue: tcgen05.ld of the accumulator (lane = output row, column = token),
+//     un-scale, relu^2 / residual, coalesced stores.
+// Every wait on an mbarrier is bounded; on expiry the kernel records an error code,
+// skips the remaining work, frees its tensor memory and returns.
+#include "rwkvq_common.cuh"
+
+namespace rwkvq {
+
+constexpr int kGmThreads = 256;
+constexpr int kGmRows = 128;          // output rows per CTA (UMMA M)
+constexpr int kGmK = 64;              // K per ring stage: one 128-byte swizzle row of fp16
+constexpr int kGmStages = 3;
+constexpr unsigned kGmSpinLimit = 1u << 24;
+
+struct GemmArgs {
+    QView t;
+    const float* x;        // [M, ldx] fp32
+    long long ldx;
+    float* y;              // [M, ldy] fp32
+    long long ldy;
+    const float* resid;
+    const float* row_scale;   // [M] power of two: x * row_scale fits fp16
+    int* status;              // device word: first error code, 0 = ok
+    int M, epilogue;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    const uint32_t a = smem_addr(bar);
+    for (unsigned i = 0; i < kGmSpinLimit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+            : "=r"(done)
+            : "r"(a), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(dst_smem)),
+                 "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// K-major operand tile, 128-byte swizzle: row r (128 bytes = 64 fp16) sits in the
+// 1024-byte atom r/8; its 16-byte chunk c is stored at chunk position c ^ (r % 8).
+__device__ __forceinline__ uint32_t sw128_offset(int r, int chunk) {
+    return static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4));
+}
+// Shared-memory matrix descriptor: start address, leading offset (unused for a
+// swizzled K-major tile), stride between 8-row atoms = 1024 bytes, version 1, SWIZZLE_128B.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(1) << 16) |
+           (static_cast<uint64_t>(1024 >> 4) << 32) | (static_cast<uint64_t>(1) << 46) |
+           (static_cast<uint64_t>(2) << 61);
+}
+// Instruction descriptor of kind::f16: D = f32, A = B = fp16, both K-major, M = 128, N.
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+    return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kGmRows >> 4) << 24);
+}
+
+// ---- weight slab producer ---------------------------------------------------------
+// 4 code bytes of a word -> 4 fp16 = fp16(code * s + m), two HFMA2.  `bias` is the value
+// to subtract from (1024 + byte): 1024 for unsigned codes, 1056 / 1152 for codes stored
+// +32 / bytes biased by 128.
+__device__ __forceinline__ uint2 bytes_to_half4(uint32_t w, __half2 bias, __half2 s2, __half2 m2) {
+    const uint32_t lo = __byte_perm(w, 0x64646464u, 0x4140), hi = __byte_perm(w, 0x64646464u, 0x4342);
+    const __half2 a = __hfma2(__hsub2(*reinterpret_cast<const __half2*>(&lo), bias), s2, m2);
+    const __half2 b = __hfma2(__hsub2(*reinterpret_cast<const __half2*>(&hi), bias), s2, m2);
+    return make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+
+// Thread (row, half) converts 32 consecutive weights of `row` starting at column k0 + 32*half
+// and stores them as 4 swizzled 16-byte chunks of the A tile.
+__device__ __forceinline__ void produce_weights(const QView& t, int row_g, int r, int half, int k0,
+                                                unsigned char* a_tile) {
+    const size_t R = static_cast<size_t>(row_g);
+    const int c0 = k0 + 32 * half;                 // first column
+    uint32_t bytes[8];                             // 32 codes as bytes, column order
+    __half2 s2[2], m2[2], bias;                    // per 16 columns
+    if (t.kind == RWKVQ_KIND_SB6) {
+        const int blk = c0 >> 5, nsb = t.cols >> 8;
+        const uint4 c = ld_stream_u128(t.codes + R * (t.cols >> 1) + blk * 16);
+        const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+        uint32_t h = 0, h2 = 0;
+        if (t.qh) h = ld_stream_u32(t.qh + R * (t.cols >> 3) + blk * 4);
+        if (t.qh2) h2 = ld_stream_u32(t.qh2 + R * (t.cols >> 3) + blk * 4);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {              // byte k of the block: column k (low), k + 16 (high)
+            bytes[i] = (w[i] & 0x0F0F0F0Fu) | spread_nibble<4>((h >> (4 * i)) & 0xFu) |
+                       spread_nibble<5>((h2 >> (4 * i)) & 0xFu);
+            bytes[4 + i] = ((w[i] >> 4) & 0x0F0F0F0Fu) | spread_nibble<4>((h >> (16 + 4 * i)) & 0xFu) |
+                           spread_nibble<5>((h2 >> (16 + 4 * i)) & 0xFu);
+        }
+        const uint8_t* mp = t.qsqm + (R * nsb + (blk >> 3)) * 12;
+        float s, m;
+        sb6_scale_min(ld_stream_u32(mp), ld_stream_u32(mp + 4), ld_stream_u32(mp + 8), blk & 7,
+                      __half2float(t.d[R * nsb + (blk >> 3)]), __half2float(t.dm[R * nsb + (blk >> 3)]), s, m);
+        s2[0] = s2[1] = __float2half2_rn(s);
+        m2[0] = m2[1] = __float2half2_rn(m);
+        bias = __float2half2_rn(1024.f);
+    } else {                                       // sym: two blocks of 16
+        const int b16 = c0 >> 4, nsb = t.cols >> 8;
+        const float d = __half2float(t.d[R * nsb + (c0 >> 8)]);
+        const uint32_t qs2 = ld_stream_u16(t.qs + R * (t.cols >> 4) + b16);
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            const int q = static_cast<int8_t>((qs2 >> (8 * b)) & 0xFFu);
+            s2[b] = __float2half2_rn(half_roundtrip(__fmul_rn(static_cast<float>(q), d)));
+            m2[b] = __float2half2_rn(0.f);
+        }
+        if (t.bits == 8) {
+            const uint8_t* cp = t.codes + R * t.cols + c0;
+            const uint4 ca = ld_stream_u128(cp), cb = ld_stream_u128(cp + 16);
+            const uint32_t w[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) bytes[i] = w[i] ^ 0x80808080u;      // code + 128
+            bias = __float2half2_rn(1152.f);
+        } else {
+            const uint4 c = ld_stream_u128(t.codes + R * (t.cols >> 1) + (c0 >> 1));
+            const uint32_t h = ld_stream_u32(t.qh + R * (t.cols >> 3) + (c0 >> 3));
+            const uint32_t h2 = ld_stream_u32(t.qh2 + R * (t.cols >> 3) + (c0 >> 3));
+            const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+            for (int b = 0; b < 2; ++b)            // block b: words 2b, 2b+1; byte k: column k (low), k + 8 (high)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int cl = 16 * b + 4 * i, ch = cl + 8;
+                    bytes[4 * b + i] = (w[2 * b + i] & 0x0F0F0F0Fu) | spread_nibble<4>((h >> cl) & 0xFu) |
+                                       spread_nibble<5>((h2 >> cl) & 0xFu);
+                    bytes[4 * b + 2 + i] = ((w[2 * b + i] >> 4) & 0x0F0F0F0Fu) | spread_nibble<4>((h >> ch) & 0xFu) |
+                                           spread_nibble<5>((h2 >> ch) & 0xFu);
+                }
+            bias = __float2half2_rn(1056.f);       // stored code = value + 32
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {                  // chunk j: columns 8j .. 8j+7 of the 32
+        const uint2 a = bytes_to_half4(bytes[2 * j], bias, s2[j >> 1], m2[j >> 1]);
+        const uint2 b = bytes_to_half4(bytes[2 * j + 1], bias, s2[j >> 1], m2[j >> 1]);
+        *reinterpret_cast<uint4*>(a_tile + sw128_offset(r, 4 * half + j)) = make_uint4(a.x, a.y, b.x, b.y);
+    }
+}
+
+template <int NT>   // tokens per CTA tile (UMMA N): 16, 32, 64, 128 or 256
+__global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int A_BYTES = kGmRows * 128, B_BYTES = NT * 128, STAGE = A_BYTES + B_BYTES;
+    constexpr uint32_t TM_COLS = NT < 32 ? 32 : NT;
+    __shared__ uint64_t bar_free[kGmStages];
+    __shared__ uint64_t bar_done;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_fail;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const QView& t = a.t;
+    const int row0 = blockIdx.x * kGmRows, tok0 = blockIdx.y * NT;
+    const int n_k = t.cols / kGmK;
+
+    if (tid == 0) {
+        for (int s = 0; s < kGmStages; ++s) mbar_init(&bar_free[s], 1);
+        mbar_init(&bar_done, 1);
+        s_fail = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) tmem_alloc(&s_tmem, TM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+    const uint32_t idesc = umma_idesc(NT);
+
+    const int pr = tid >> 1, ph = tid & 1;                     // producer: (row in tile, 32-column half)
+    const int row_g = min(row0 + pr, t.rows - 1);
+    for (int i = 0; i < n_k; ++i) {
+        const int s = i % kGmStages;
+        unsigned char* a_tile = smem + s * STAGE;
+        unsigned char* b_tile = a_tile + A_BYTES;
+        if (i >= kGmStages) {                                  // wait until the MMAs that read this stage are done
+            if (!mbar_wait_bounded(&bar_free[s], ((i / kGmStages) - 1) & 1)) s_fail = 1;
+        }
+        if (!s_fail) {
+            produce_weights(t, row_g, pr, ph, i * kGmK, a_tile);
+            // activations: NT tokens x 8 chunks of 8 columns
+            for (int c = tid; c < NT * 8; c += kGmThreads) {
+                const int n = c >> 3, ch = c & 7, tok = tok0 + n;
+                uint4 o = make_uint4(0, 0, 0, 0);
+                if (tok < a.M) {
+                    const float sc = __ldcg(a.row_scale + tok);
+                    const float4* xp = reinterpret_cast<const float4*>(a.x + tok * a.ldx + i * kGmK + ch * 8);
+                    const float4 u = __ldcg(xp), v = __ldcg(xp + 1);
+                    const __half2 h0 = __floats2half2_rn(u.x * sc, u.y * sc), h1 = __floats2half2_rn(u.z * sc, u.w * sc);
+                    const __half2 h2 = __floats2half2_rn(v.x * sc, v.y * sc), h3 = __floats2half2_rn(v.z * sc, v.w * sc);
+                    o = make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1),
+                                   *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
+                }
+                *reinterpret_cast<uint4*>(b_tile + sw128_offset(n, ch)) = o;
+            }
+        }
+        fence_async_smem();                                    // generic-proxy stores -> visible to the tensor core
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0 && !s_fail) {
+            tc_fence_after();
+            const uint64_t ad = umma_desc(smem_addr(a_tile)), bd = umma_desc(smem_addr(b_tile));
+#pragma unroll
+            for (int k = 0; k < kGmK / 16; ++k)                // 32 bytes further along K per step
+                umma_f16(tmem, ad + 2 * k, bd + 2 * k, idesc, (i | k) ? 1u : 0u);
+            umma_commit(&bar_free[s]);
+            if (i == n_k - 1) umma_commit(&bar_done);
+        }
+    }
+    if (!s_fail && !mbar_wait_bounded(&bar_done, 0)) s_fail = 1;
+    tc_fence_after();
+    __syncthreads();
+    if (s_fail) {
+        if (tid == 0) atomicCAS(a.status, 0, RWKVQ_E_TIMEOUT);
+    } else {
+        // warp w reads lanes 32*(w%4) .. +31 (= output rows); warps w and w+4 split the tokens
+        const int row = row0 + (warp & 3) * 32 + lane;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+        for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += 16) {
+            float v[8];
+            tmem_ld8(lane_base + c0, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int tok = tok0 + c0 + j;
+                if (tok < a.M && row < t.rows) {
+                    float r = v[j] / __ldcg(a.row_scale + tok);
+                    const long long idx = tok * a.ldy + row;
+                    if (a.epilogue == RWKVQ_EPI_RELU2) { r = fmaxf(r, 0.f); r = r * r; }
+                    else if (a.epilogue == RWKVQ_EPI_ADD) r = __fadd_rn(r, __ldcg(a.resid + idx));
+                    a.y[idx] = r;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, TM_COLS);
+}
+
+// power-of-two scale per token row so that |x * scale| <= 2^14 (fp16-safe with headroom)
+__global__ void __launch_bounds__(256) row_scale_kernel(const float* x, long long ldx, int cols, float* scale) {
+    __shared__ float red[8];
+    const float* row = x + blockIdx.x * ldx;
+    float amax = 0.f;
+    for (int i = threadIdx.x; i < cols; i += 256) amax = fmaxf(amax, fabsf(__ldcg(row + i)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
+        int e = 0;
+        if (amax > 0.f && amax < INFINITY) frexpf(amax, &e);
+        scale[blockIdx.x] = ldexpf(1.f, 14 - e);
+    }
+}
+
+}  // namespace rwkvq
+
+using namespace rwkvq;
+
+namespace {
+template <int NT>
+int launch_gemm(const GemmArgs& a, int rows, int M, cudaStream_t s) {
+    const size_t smem = static_cast<size_t>(kGmStages) * (kGmRows * 128 + NT * 128) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem));
+        if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "rwkvq_gemm: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    gemm_tc_kernel<NT><<<dim3((rows + kGmRows - 1) / kGmRows, (M + NT - 1) / NT), kGmThreads, smem, s>>>(a);
+    return RWKVQ_OK;
+}
+}  // namespace
+
+extern "C" {
+
+size_t rwkvq_gemm_workspace_bytes(int M) { return 256 + sizeof(float) * static_cast<size_t>(M < 1 ? 1 : M); }
+
+int rwkvq_gemm(const rwkvq_qtensor* t, const float* x, int M, int64_t ldx, float* y, int64_t ldy, int epilogue,
+               const float* resid, void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = validate_qtensor(t, "rwkvq_gemm");
+    if (rc) return rc;
+    RWKVQ_REQUIRE(t->kind == RWKVQ_KIND_SB6 || t->kind == RWKVQ_KIND_SYM, RWKVQ_E_DTYPE,
+                  "rwkvq_gemm: only sb6 and sym tensors have a tensor-core path (kind %d)", t->kind);
+    RWKVQ_REQUIRE(x && y && workspace, RWKVQ_E_NULL, "rwkvq_gemm: null pointer");
+    RWKVQ_REQUIRE(M >= 1 && ldx >= t->cols && ldy >= t->rows, RWKVQ_E_SHAPE, "rwkvq_gemm: M=%d ldx=%lld ldy=%lld", M,
+                  (long long)ldx, (long long)ldy);
+    RWKVQ_REQUIRE(aligned(x, 16) && ldx % 4 == 0 && aligned(workspace, 16), RWKVQ_E_ALIGN,
+                  "rwkvq_gemm: x, its row stride and the workspace must be 16-byte aligned");
+    RWKVQ_REQUIRE(workspace_bytes >= rwkvq_gemm_workspace_bytes(M), RWKVQ_E_LIMIT, "rwkvq_gemm: workspace %zu < %zu bytes",
+                  workspace_bytes, rwkvq_gemm_workspace_bytes(M));
+    RWKVQ_REQUIRE(epilogue >= RWKVQ_EPI_NONE && epilogue <= RWKVQ_EPI_ADD, RWKVQ_E_DTYPE, "rwkvq_gemm: epilogue %d", epilogue);
+    RWKVQ_REQUIRE(epilogue != RWKVQ_EPI_ADD || resid, RWKVQ_E_NULL, "rwkvq_gemm: resid is null");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    GemmArgs a{};
+    a.t = make_view(*t);
+    a.x = x; a.ldx = ldx; a.y = y; a.ldy = ldy; a.resid = resid; a.M = M; a.epilogue = epilogue;
+    a.status = static_cast<int*>(workspace);
+    float* scale = reinterpret_cast<float*>(static_cast<char*>(workspace) + 256);
+    a.row_scale = scale;
+    cudaMemsetAsync(a.status, 0, sizeof(int), s);
+    row_scale_kernel<<<M, 256, 0, s>>>(x, ldx, t->cols, scale);
+    if (M <= 16) rc = launch_gemm<16>(a, t->rows, M, s);
+    else if (M <= 32) rc = launch_gemm<32>(a, t->rows, M, s);
+    else if (M <= 64) rc = launch_gemm<64>(a, t->rows, M, s);
+    else rc = launch_gemm<128>(a, t->rows, M, s);
+    if (rc) return rc;
+    return check_launch("rwkvq_gemm");
+}
+
+}  // extern "C"

@@ -39,6 +39,12 @@ struct MmaArgs {
     const float* resid;
     int epilogue;
     int fused;
+    // split of the K loop over gridDim.z CTAs: partial row sums go to `partial`
+    // [gridDim.z][n_mats][rows_padded] and the last CTA of a tile group to arrive
+    // (counted in `counters`, which it resets) adds them in slice order
+    float* partial;
+    unsigned int* counters;
+    int rows_padded;
 };
 
 template <bool A_UNSIGNED>
@@ -226,27 +232,37 @@ __device__ __forceinline__ void split_digits(int X, int& d1, int& d2, int& d3) {
 }
 
 // `bits` = 20 (|X| <= 2^20) or 19: chosen so that |sum over one block of q*X| < 2^31.
+// x is read once: up to kXRegs float4 per thread stay in registers between the max
+// pass and the conversion pass (IN <= 8192 at 256 threads); longer vectors are re-read.
+constexpr int kXRegs = 8;
 __device__ __forceinline__ float prepare_x(const void* x, int dtype, int n_in, int bits, int8_t* dig,
                                            float* xs16, float* red, bool& finite) {
-    const int tid = threadIdx.x, n4 = n_in >> 2;
+    const int tid = threadIdx.x, n4 = n_in >> 2, nt = blockDim.x;
+    float4 xr[kXRegs];
     float amax = 0.f;
-    for (int i = tid; i < n4; i += blockDim.x) {
-        const float4 v = load_x4(x, dtype, i);
+    auto upd = [&](const float4& v) {
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
         if (!(fabsf(v.x) + fabsf(v.y) + fabsf(v.z) + fabsf(v.w) < INFINITY)) amax = INFINITY;
+    };
+#pragma unroll
+    for (int k = 0; k < kXRegs; ++k) {
+        const int i = tid + k * nt;
+        xr[k] = i < n4 ? load_x4(x, dtype, i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+#pragma unroll
+    for (int k = 0; k < kXRegs; ++k) upd(xr[k]);
+    for (int i = tid + kXRegs * nt; i < n4; i += nt) upd(load_x4(x, dtype, i));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
     if ((tid & 31) == 0) red[tid >> 5] = amax;
     __syncthreads();
     amax = 0.f;
-    for (int w = 0; w < (blockDim.x >> 5); ++w) amax = fmaxf(amax, red[w]);
+    for (int w = 0; w < (nt >> 5); ++w) amax = fmaxf(amax, red[w]);
     finite = amax < INFINITY;
     int e = 0;
     if (finite && amax > 0.f) frexpf(amax, &e);          // amax <= 2^e
     const float scale = finite ? ldexpf(1.f, bits - e) : 0.f;
-    for (int i = tid; i < n4; i += blockDim.x) {
-        const float4 v = load_x4(x, dtype, i);
+    auto emit = [&](int i, const float4& v) {
         const int X0 = __float2int_rn(v.x * scale), X1 = __float2int_rn(v.y * scale);
         const int X2 = __float2int_rn(v.z * scale), X3 = __float2int_rn(v.w * scale);
         int a[4], b[4], c[4];
@@ -262,7 +278,13 @@ __device__ __forceinline__ float prepare_x(const void* x, int dtype, int n_in, i
         s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
         s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
         if ((tid & 3) == 0) xs16[i >> 2] = static_cast<float>(s);
+    };
+#pragma unroll
+    for (int k = 0; k < kXRegs; ++k) {
+        const int i = tid + k * nt;
+        if (i < n4) emit(i, xr[k]);          // n4 is a multiple of 64: whole warps take this branch together
     }
+    for (int i = tid + kXRegs * nt; i < n4; i += nt) emit(i, load_x4(x, dtype, i));
     __syncthreads();
     return finite ? ldexpf(1.f, e - bits) : 0.f;
 }
@@ -288,7 +310,9 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaAr
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int tl = warp / WK, ks = warp % WK;
-    const int n_iters = n_in / G::KI;
+    const int KS = gridDim.z;                               // K slices across CTAs
+    const int n_iters = n_in / G::KI / KS;                  // iterations of this CTA's slice
+    const int it0 = blockIdx.z * n_iters;
     const int n_tiles = (q.rows + 15) >> 4;
     const int step = gridDim.x * WT;
     const int ipt = (n_iters - ks + WK - 1) / WK;          // this warp's iterations per tile
@@ -301,7 +325,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaAr
     auto fetch_next = [&]() {
         if (i_n < n_items && i_tile < n_tiles) {
             const int r0 = min(i_tile * 16 + g, q.rows - 1), r1 = min(i_tile * 16 + g + 8, q.rows - 1);
-            load_frag<L>(nxt, q, r0, r1, ks + i_j * WK, t);
+            load_frag<L>(nxt, q, r0, r1, it0 + ks + i_j * WK, t);
         }
         ++i_n;
         if (++i_j == ipt) { i_j = 0; i_tile += step; }
@@ -333,7 +357,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaAr
             const Frag<L> cur = nxt;
             fetch_next();
             if (tile >= n_tiles) continue;
-            const int it = ks + j * WK;
+            const int it = it0 + ks + j * WK;
 
             float2 sa, sb, ma = make_float2(0.f, 0.f), mb = ma;
             if (SB6) {
@@ -400,18 +424,55 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaAr
         float* rb = red + buf * (kMmaWarps * 16);
         if (t == 0) { rb[warp * 16 + g] = acc0; rb[warp * 16 + g + 8] = acc1; }
         __syncthreads();
-        if (threadIdx.x < WT * 16) {
-            const int wtl = threadIdx.x >> 4, r = threadIdx.x & 15;
-            const int row = (base + wtl) * 16 + r;
-            if (row < q.rows) {
+        if (KS == 1) {
+            if (threadIdx.x < WT * 16) {
+                const int wtl = threadIdx.x >> 4, r = threadIdx.x & 15;
+                const int row = (base + wtl) * 16 + r;
+                if (row < q.rows) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int k = 0; k < WK; ++k) v += rb[(wtl * WK + k) * 16 + r];
+                    v = finite ? v * unscale : NAN;
+                    const long long idx = (a.fused ? static_cast<long long>(blockIdx.y) * a.ldy : 0) + row;
+                    if (a.epilogue == RWKVQ_EPI_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
+                    else if (a.epilogue == RWKVQ_EPI_ADD) v = __fadd_rn(v, __ldcg(a.resid + idx));
+                    a.y[idx] = v;
+                }
+            }
+        } else {
+            __shared__ unsigned int s_last;
+            float* part = a.partial + (static_cast<size_t>(blockIdx.z) * gridDim.y + blockIdx.y) * a.rows_padded;
+            if (threadIdx.x < WT * 16) {
+                const int wtl = threadIdx.x >> 4, r = threadIdx.x & 15;
+                const int row = (base + wtl) * 16 + r;
                 float v = 0.f;
 #pragma unroll
                 for (int k = 0; k < WK; ++k) v += rb[(wtl * WK + k) * 16 + r];
-                v = finite ? v * unscale : NAN;
-                const long long idx = (a.fused ? static_cast<long long>(blockIdx.y) * a.ldy : 0) + row;
-                if (a.epilogue == RWKVQ_EPI_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
-                else if (a.epilogue == RWKVQ_EPI_ADD) v = __fadd_rn(v, __ldcg(a.resid + idx));
-                a.y[idx] = v;
+                if (row < a.rows_padded) __stcg(part + row, finite ? v * unscale : NAN);
+            }
+            __threadfence();
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                unsigned int* ctr = a.counters + blockIdx.y * ((n_tiles + WT - 1) / WT) + base / WT;
+                const unsigned int old = atomicAdd(ctr, 1u);
+                s_last = (old == static_cast<unsigned int>(KS - 1));
+                if (s_last) *ctr = 0u;                      // ready for the next launch
+            }
+            __syncthreads();
+            if (s_last) {
+                __threadfence();
+                if (threadIdx.x < WT * 16) {
+                    const int row = base * 16 + threadIdx.x;
+                    if (row < q.rows) {
+                        float v = 0.f;
+                        for (int z = 0; z < KS; ++z)
+                            v += __ldcg(a.partial + (static_cast<size_t>(z) * gridDim.y + blockIdx.y) * a.rows_padded + row);
+                        const long long idx = (a.fused ? static_cast<long long>(blockIdx.y) * a.ldy : 0) + row;
+                        if (a.epilogue == RWKVQ_EPI_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
+                        else if (a.epilogue == RWKVQ_EPI_ADD) v = __fadd_rn(v, __ldcg(a.resid + idx));
+                        a.y[idx] = v;
+                    }
+                }
             }
         }
     }
@@ -480,9 +541,16 @@ int mma_layout_of(const rwkvq_qtensor& t) {
 }
 
 constexpr int kResidentCtas = 2 * 148;     // 2 CTAs of 256 threads per SM at <= 128 registers
+constexpr int kSplitMaxRows = 4096;        // rows a K-split launch may have (scratch sizing)
+constexpr int kSplitMaxSlices = 4;
+
+// Scratch of a K-split launch: partial sums, then the (self-resetting) arrival counters.
+size_t gemv_mma_scratch_bytes() {
+    return sizeof(float) * kSplitMaxSlices * kMmaMaxFused * kSplitMaxRows + sizeof(unsigned int) * 1024;
+}
 
 template <int L, int WK>
-static int launch_one(const MmaArgs& a, int rows, int cols, int n_mats, cudaStream_t s) {
+static int launch_one(MmaArgs& a, int rows, int cols, int n_mats, int KS, cudaStream_t s) {
     constexpr int WT = kMmaWarps / WK;
     const size_t smem = 3 * static_cast<size_t>(cols) + 4 * (cols / 16) + 2 * kMmaWarps * 16 * 4;
     if (smem > 48 * 1024) {
@@ -491,37 +559,67 @@ static int launch_one(const MmaArgs& a, int rows, int cols, int n_mats, cudaStre
         if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "gemv_mma: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
     const int units = ((rows + 15) / 16 + WT - 1) / WT;
-    const int cap = kResidentCtas / n_mats > 0 ? kResidentCtas / n_mats : 1;
-    cudaError_t le = launch_pdl(gemv_mma_kernel<L, WK>, dim3(units < cap ? units : cap, n_mats), dim3(kMmaWarps * 32),
-                                smem, s, a);
+    const int cap = kResidentCtas / (n_mats * KS) > 0 ? kResidentCtas / (n_mats * KS) : 1;
+    a.rows_padded = ((rows + 15) / 16) * 16;
+    cudaError_t le = launch_pdl(gemv_mma_kernel<L, WK>, dim3(units < cap ? units : cap, n_mats, KS),
+                                dim3(kMmaWarps * 32), smem, s, a);
     if (le != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "gemv_mma: %s", cudaGetErrorString(le));
     return RWKVQ_OK;
 }
 
+// Work split: a single wave of co-resident CTAs whenever the matrix allows it.
+//   * few row tiles, long rows  -> K is also split across CTAs (needs scratch)
+//   * tiles * n_mats <= resident CTAs -> one tile per CTA, its 8 warps split K
+//   * more tiles -> WT tiles per CTA so that the grid still fits one wave
+//   * very many tiles (head) -> persistent CTAs, 8 warps split K of each tile
 template <int L>
-static int launch_wk(const MmaArgs& a, int rows, int cols, int n_mats, cudaStream_t s) {
+static int launch_wk(MmaArgs& a, int rows, int cols, int n_mats, float* scratch, cudaStream_t s) {
     const int n_iters = cols / Geo<L>::KI;
-    if (n_iters >= 8) return launch_one<L, 8>(a, rows, cols, n_mats, s);
-    if (n_iters >= 4) return launch_one<L, 4>(a, rows, cols, n_mats, s);
-    if (n_iters >= 2) return launch_one<L, 2>(a, rows, cols, n_mats, s);
-    return launch_one<L, 1>(a, rows, cols, n_mats, s);
+    const int tiles = (rows + 15) / 16;
+    int KS = 1;
+    if (scratch && n_iters >= 16 && rows <= kSplitMaxRows) {
+        if (tiles * n_mats * 4 <= kResidentCtas && n_iters >= 32) KS = 4;
+        else if (tiles * n_mats * 2 <= kResidentCtas) KS = 2;
+    }
+    if (KS > 1) {
+        a.partial = scratch;
+        a.counters = reinterpret_cast<unsigned int*>(scratch + kSplitMaxSlices * kMmaMaxFused * kSplitMaxRows);
+        return launch_one<L, 8>(a, rows, cols, n_mats, KS, s);
+    }
+    int wt = 1;
+    if (tiles * n_mats > kResidentCtas) {
+        wt = 0;
+        for (int c = 2; c <= 8; c <<= 1)
+            if (((tiles + c - 1) / c) * n_mats <= kResidentCtas && 8 / c <= n_iters) { wt = c; break; }
+        if (wt == 0) wt = 1;                 // persistent loop
+    }
+    int wk = 8 / wt;
+    while (wk > n_iters) wk >>= 1;           // short rows: fewer K slices, more tiles per CTA
+    switch (wk) {
+        case 8: return launch_one<L, 8>(a, rows, cols, n_mats, 1, s);
+        case 4: return launch_one<L, 4>(a, rows, cols, n_mats, 1, s);
+        case 2: return launch_one<L, 2>(a, rows, cols, n_mats, 1, s);
+        default: return launch_one<L, 1>(a, rows, cols, n_mats, 1, s);
+    }
 }
 
 // Launch the single-vector tensor-core GEMV for `n_mats` same-shape matrices.
+// `scratch` (gemv_mma_scratch_bytes(), zero-initialised once, reusable) enables the
+// K split across CTAs; nullptr disables it.
 int launch_gemv_mma(int layout, const rwkvq_qtensor* ts, int n_mats, const void* x, int x_dtype,
                     long long ldx, float* y, long long ldy, int epilogue, const float* resid,
-                    int fused, cudaStream_t s, const void* const* x_each) {
+                    int fused, cudaStream_t s, const void* const* x_each, float* scratch) {
     MmaArgs a{};
     for (int k = 0; k < n_mats; ++k) { a.t[k] = make_view(ts[k]); a.xk[k] = x_each ? x_each[k] : nullptr; }
     a.x = x; a.x_dtype = x_dtype; a.ldx = ldx; a.y = y; a.ldy = ldy;
     a.resid = resid; a.epilogue = epilogue; a.fused = fused;
     const int rows = ts[0].rows, cols = ts[0].cols;
     switch (layout) {
-        case ML_SB6_4: return launch_wk<ML_SB6_4>(a, rows, cols, n_mats, s);
-        case ML_SB6_5: return launch_wk<ML_SB6_5>(a, rows, cols, n_mats, s);
-        case ML_SB6_6: return launch_wk<ML_SB6_6>(a, rows, cols, n_mats, s);
-        case ML_SYM6: return launch_wk<ML_SYM6>(a, rows, cols, n_mats, s);
-        default: return launch_wk<ML_SYM8>(a, rows, cols, n_mats, s);
+        case ML_SB6_4: return launch_wk<ML_SB6_4>(a, rows, cols, n_mats, scratch, s);
+        case ML_SB6_5: return launch_wk<ML_SB6_5>(a, rows, cols, n_mats, scratch, s);
+        case ML_SB6_6: return launch_wk<ML_SB6_6>(a, rows, cols, n_mats, scratch, s);
+        case ML_SYM6: return launch_wk<ML_SYM6>(a, rows, cols, n_mats, scratch, s);
+        default: return launch_wk<ML_SYM8>(a, rows, cols, n_mats, scratch, s);
     }
 }
 
