@@ -140,11 +140,14 @@ int rwkvq_gemv(const rwkvq_qtensor* t, const void* x, int x_dtype, int N, int64_
  * no dense copy of W is ever written.  Operands are fp16 (weights: fp16(q*s+m); tokens:
  * scaled per row by a power of two), accumulation fp32 in tensor memory.
  *   x [M, ldx] fp32, y [M, ldy] fp32, sb6 / sym tensors only.
- *   workspace: rwkvq_gemm_workspace_bytes(M) bytes; its first int32 is a status word the
+ *   workspace: rwkvq_gemm_workspace_bytes_for(M, IN) bytes, 256-byte aligned (or
+ *   rwkvq_gemm_workspace_bytes(M), which covers IN <= 16384); it holds the fp16 copy of x the
+ *   TMA loads read, the split-K accumulator tiles and a header.  Its first int32 is a status word the
  *   kernel sets to RWKVQ_E_TIMEOUT if a bounded wait on the tensor-core pipeline ran out
  *   (read it after synchronising the stream; 0 = ok).
  */
 size_t rwkvq_gemm_workspace_bytes(int M);
+size_t rwkvq_gemm_workspace_bytes_for(int M, int max_cols);
 int rwkvq_gemm(const rwkvq_qtensor* t, const float* x, int M, int64_t ldx, float* y, int64_t ldy,
                int epilogue, const float* resid, void* workspace, size_t workspace_bytes, void* stream);
 

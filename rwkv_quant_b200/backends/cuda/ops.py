@@ -199,7 +199,7 @@ def gemm(dq: "DeviceQT", x: torch.Tensor, epilogue: int = 0, resid: Optional[tor
     lib = _lib.load()
     x = x.float().contiguous()
     m = x.shape[0]
-    nws = lib.rwkvq_gemm_workspace_bytes(m)
+    nws = lib.rwkvq_gemm_workspace_bytes_for(m, dq.cols)
     ws = torch.empty(nws, dtype=torch.uint8, device=x.device)
     y = torch.empty((m, dq.rows), dtype=torch.float32, device=x.device)
     _lib.check(lib.rwkvq_gemm(C.byref(dq.struct), x.data_ptr(), m, x.stride(0), y.data_ptr(), y.stride(0),

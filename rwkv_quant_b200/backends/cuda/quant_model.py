@@ -49,7 +49,7 @@ class _Layer:
 
 
 class QuantRWKV7:
-    def __init__(self, ckpt, device="cuda", gemm_min_batch=GEMM_MIN_BATCH_NB):
+    def __init__(self, ckpt, device="cuda", gemm_min_batch=GEMM_MIN_BATCH_NB, gemv_max_batch=2):
         if ckpt.naming != "world":
             raise NotImplementedError("only world-naming checkpoints are supported")
         _lib.load(check_device=True)
@@ -60,6 +60,7 @@ class QuantRWKV7:
         self.n_head = ckpt.n_embd // ckpt.head_size
         self.vocab_size = ckpt.vocab_size
         self.gemm_min_batch = int(gemm_min_batch)
+        self.gemv_max_batch = int(gemv_max_batch)
         T = ckpt.tensors
         dev = self.device
         dq = lambda key: ops.DeviceQT(T[key], dev)
@@ -93,6 +94,7 @@ class QuantRWKV7:
                             for L in self.blocks)
         self._build_struct()
         self._ws = {}
+        self._lora_dense = {}
         torch.cuda.synchronize(dev)
 
     # ------------------------------------------------------------------ C descriptors
@@ -173,8 +175,13 @@ class QuantRWKV7:
 
     # ------------------------------------------------------------------ T > 1
     def _linear(self, dq, x, epilogue=_lib.EPI_NONE, resid=None):
-        """x [N, IN] fp32 -> [N, OUT]: weight-streaming GEMV below the crossover, else
-        dequantise once and use a dense fp32 GEMM."""
+        """x [N, IN] fp32 -> [N, OUT].  Up to ``gemv_max_batch`` rows: the exact
+        weight-streaming GEMV per row; more rows: the dequant-fused tensor-core GEMM
+        (sb6 / sym); other layouts at large N: dequantise once + dense fp32 GEMM."""
+        if x.shape[0] <= self.gemv_max_batch:
+            return ops.gemv(dq.bufs, dq.meta, x, epilogue, resid)
+        if dq.kind in ("sb6", "sym"):
+            return ops.gemm(dq, x, epilogue, resid)
         if x.shape[0] < self.gemm_min_batch:
             return ops.gemv(dq.bufs, dq.meta, x, epilogue, resid)
         y = x @ ops.dequant(dq.bufs, dq.meta, torch.float32, False).t()
@@ -183,6 +190,19 @@ class QuantRWKV7:
         elif epilogue == _lib.EPI_ADD:
             y = y + resid
         return y
+
+    def _lora_seq(self, dq, x, act):
+        """x [N, in] @ W [in, out] for a LoRA tensor stored [in, out].  Few rows: the packed
+        kernel; many rows: a dense fp32 GEMM on the weights dequantised once (kept in the
+        loader's precision fp16(bf16(.)), 4 bytes per LoRA weight)."""
+        if x.shape[0] <= 8:
+            return ops.gemv_t(dq.bufs, dq.meta, x.contiguous(), act, True)
+        w = self._lora_dense.get(id(dq))
+        if w is None:
+            w = ops.dequant(dq.bufs, dq.meta, torch.float32, True).half().float()
+            self._lora_dense[id(dq)] = w
+        y = x @ w
+        return torch.tanh(y) if act == 1 else torch.sigmoid(y) if act == 2 else y
 
     @staticmethod
     def _shift(x, prev):
@@ -193,7 +213,7 @@ class QuantRWKV7:
         H, S = self.n_head, self.head_size
         wkv, ts, cs = state
         lin = lambda dq, t, **kw: self._linear(dq, t.reshape(B * T, -1).contiguous(), **kw)
-        lora = lambda dq, t, act=0: ops.gemv_t(dq.bufs, dq.meta, t.reshape(B * T, -1).contiguous(), act, True)
+        lora = lambda dq, t, act=0: self._lora_seq(dq, t.reshape(B * T, -1), act)
         xn = F.layer_norm(x, (D,), *L.ln1)
         shifted, ts = self._shift(xn, ts)
         xx = shifted - xn

@@ -477,7 +477,7 @@ using namespace rwkvq;
 namespace {
 
 struct Workspace {
-    float *x, *xs, *rkv, *part, *yl, *og, *xk, *hffn, *xo, *v_first, *logits, *argv, *gscratch;
+    float *x, *xs, *rkv, *part, *yl, *og, *xk, *hffn, *xo, *v_first, *logits, *argv, *gscratch, *gemm_ws;
     int n_chunks;
     size_t bytes;
 };
@@ -498,6 +498,7 @@ Workspace carve(const rwkvq_model& m, int B, void* base) {
     w.xo = take(b * D); w.v_first = take(b * D); w.logits = take(b * V);
     w.argv = take(2 * b * kArgSlices);
     w.gscratch = take(gemv_mma_scratch_bytes() / sizeof(float));
+    w.gemm_ws = take(rwkvq_gemm_workspace_bytes_for(B, static_cast<int>(F > D ? F : D)) / sizeof(float) + 1);
     w.bytes = off;
     return w;
 }
@@ -506,7 +507,7 @@ Workspace carve(const rwkvq_model& m, int B, void* base) {
 // One quantized linear for B right-hand sides; the single-vector tensor-core kernel gets
 // the K-split scratch, everything else goes through the public entry point.
 int linear(const rwkvq_qtensor* t, const float* x, int B, int in, float* y, int out, int epi, const float* resid,
-           float* scratch, void* stream) {
+           float* scratch, void* gemm_ws, void* stream) {
     const int ml = mma_layout_of(*t);
     if (B == 1 && ml >= 0) {
         int rc = validate_qtensor(t, "rwkvq_decode_step(linear)");
@@ -514,6 +515,8 @@ int linear(const rwkvq_qtensor* t, const float* x, int B, int in, float* y, int 
         return launch_gemv_mma(ml, t, 1, x, RWKVQ_F32, in, y, out, epi, resid, 0, static_cast<cudaStream_t>(stream),
                                nullptr, scratch);
     }
+    if (B > 2 && (t->kind == RWKVQ_KIND_SB6 || t->kind == RWKVQ_KIND_SYM))     // tensor-core path, weights read once
+        return rwkvq_gemm(t, x, B, in, y, out, epi, resid, gemm_ws, rwkvq_gemm_workspace_bytes_for(B, in), stream);
     return rwkvq_gemv(t, x, RWKVQ_F32, B, in, y, out, epi, resid, stream);
 }
 
@@ -601,11 +604,11 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
             rc = launch_gemv_mma(ml, three, 3, xr, RWKVQ_F32, D, r, D, RWKVQ_EPI_NONE, nullptr, 1, s, x_each, w.gscratch);
             if (rc) return rc;
         } else {
-            rc = rwkvq_gemv(&L.Wr, xr, RWKVQ_F32, B, D, r, D, RWKVQ_EPI_NONE, nullptr, stream);
+            rc = linear(&L.Wr, xr, B, D, r, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream);
             if (rc) return rc;
-            rc = rwkvq_gemv(&L.Wk, xk, RWKVQ_F32, B, D, k, D, RWKVQ_EPI_NONE, nullptr, stream);
+            rc = linear(&L.Wk, xk, B, D, k, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream);
             if (rc) return rc;
-            rc = rwkvq_gemv(&L.Wv, xv, RWKVQ_F32, B, D, v, D, RWKVQ_EPI_NONE, nullptr, stream);
+            rc = linear(&L.Wv, xv, B, D, v, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream);
             if (rc) return rc;
         }
         float *yw = w.yl, *ya = w.yl + BD, *yv = w.yl + 2 * BD, *yg = w.yl + 3 * BD;
@@ -621,17 +624,17 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         TmixCoreArgs tc{r, k, v, yw, ya, layer0 ? nullptr : yv, yg, L.w0, L.a0, L.v0, L.k_k, L.k_a, L.r_k,
                         L.lnx_w, L.lnx_b, w.v_first, wkv[l], w.og, D, H, layer0 ? 1 : 0};
         launch_pdl(tmix_core_kernel, dim3(H, B), dim3(256), 0, s, tc);
-        rc = linear(&L.Wo, w.og, B, D, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, stream);
+        rc = linear(&L.Wo, w.og, B, D, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, w.gemm_ws, stream);
         if (rc) return rc;
         // ---- channel mix
         launch_pdl(ln_shift_mix_kernel<1>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln2_w, L.ln2_b, cshift[l], L.ffn_x_k, w.xk, B, D);
-        rc = linear(&L.Wfk, w.xk, B, D, w.hffn, F, RWKVQ_EPI_RELU2, nullptr, w.gscratch, stream);
+        rc = linear(&L.Wfk, w.xk, B, D, w.hffn, F, RWKVQ_EPI_RELU2, nullptr, w.gscratch, w.gemm_ws, stream);
         if (rc) return rc;
-        rc = linear(&L.Wfv, w.hffn, B, F, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, stream);
+        rc = linear(&L.Wfv, w.hffn, B, F, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, w.gemm_ws, stream);
         if (rc) return rc;
     }
     launch_pdl(ln_shift_mix_kernel<0>, dim3(B), dim3(kRowThreads), 0, s, w.x, m->lnout_w, m->lnout_b, static_cast<float*>(nullptr), static_cast<const float*>(nullptr), w.xo, B, D);
-    rc = linear(&m->head, w.xo, B, D, lg, V, RWKVQ_EPI_NONE, nullptr, w.gscratch, stream);
+    rc = linear(&m->head, w.xo, B, D, lg, V, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream);
     if (rc) return rc;
     if (next_tokens) {
         float* pv = w.argv;

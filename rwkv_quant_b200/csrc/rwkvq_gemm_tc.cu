@@ -4,19 +4,25 @@
 // tcgen05 formulation: the WEIGHTS are the M = 128 operand, the tokens are the UMMA N
 // dimension (16..256), so the packed weight stream is read exactly once per token tile
 // and the accumulator D[128 out-rows, N tokens] lives in tensor memory.
+//   a pre-pass writes the activations once as fp16, scaled per token by a power of two so
+//     that no value leaves the fp16 range;
 //   producers (all 256 threads of the CTA): unpack a [128 rows, 64 K] slab of the file
 //     layout (nibbles / planes / int8 + block scales) to fp16 = fp16(q*s + m) with one
 //     HFMA2 per two weights (s and m ARE fp16 values by the codec's definition, so the
 //     fused multiply-add rounds the exact value once) and store it K-major with the
-//     128-byte swizzle the UMMA shared-memory descriptor expects; the same threads
-//     convert the activation slab [N, 64 K] fp32 -> fp16 (scaled per token by a power
-//     of two so that no value leaves the fp16 range);
+//     128-byte swizzle the UMMA shared-memory descriptor expects; the packed bytes of the
+//     next slab are already in flight (register prefetch);
+//   the activation slab [N, 64 K] of each stage arrives by TMA (cp.async.bulk.tensor.2d,
+//     SWIZZLE_128B, mbarrier complete_tx), issued by one thread one stage ahead; rows
+//     beyond M are zero-filled by the tensor map;
 //   one elected thread issues four tcgen05.mma (K = 16 each) per slab and commits them
 //     to the mbarrier that frees the slab's ring stage;
 //   epilogue: tcgen05.ld of the accumulator (lane = output row, column = token),
 //     un-scale, relu^2 / residual, coalesced stores.
 // Every wait on an mbarrier is bounded; on expiry the kernel records an error code,
 // skips the remaining work, frees its tensor memory and returns.
+#include <cuda.h>
+
 #include "rwkvq_common.cuh"
 
 namespace rwkvq {
@@ -24,18 +30,22 @@ namespace rwkvq {
 constexpr int kGmThreads = 256;
 constexpr int kGmRows = 128;          // output rows per CTA (UMMA M)
 constexpr int kGmK = 64;              // K per ring stage: one 128-byte swizzle row of fp16
-constexpr int kGmStages = 3;
+constexpr int kGmAStages = 2;         // unpacked weight slabs
+constexpr int kGmBStages = 4;         // activation slabs (TMA), issued kGmAhead iterations ahead
+constexpr int kGmAhead = 2;
 constexpr unsigned kGmSpinLimit = 1u << 24;
 
 struct GemmArgs {
     QView t;
-    const float* x;        // [M, ldx] fp32
+    const float* x;        // [M, ldx] fp32 (read by the pre-pass only)
     long long ldx;
     float* y;              // [M, ldy] fp32
     long long ldy;
     const float* resid;
     const float* row_scale;   // [M] power of two: x * row_scale fits fp16
     int* status;              // device word: first error code, 0 = ok
+    unsigned int* counters;   // [row tiles * token tiles] arrivals of the K slices (zeroed per call)
+    float* partial;           // [CTA][NT][128] accumulator tiles of a K-split launch
     int M, epilogue;
 };
 
@@ -58,6 +68,17 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
         if (done) return true;
     }
     return false;
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+// 2-D tile load, this CTA's shared memory only (no multicast)
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_addr(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_addr(bar))
+        : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(dst_smem)),
@@ -121,21 +142,48 @@ __device__ __forceinline__ uint2 bytes_to_half4(uint32_t w, __half2 bias, __half
     return make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
 }
 
-// Thread (row, half) converts 32 consecutive weights of `row` starting at column k0 + 32*half
-// and stores them as 4 swizzled 16-byte chunks of the A tile.
-__device__ __forceinline__ void produce_weights(const QView& t, int row_g, int r, int half, int k0,
-                                                unsigned char* a_tile) {
+// Packed bytes of 32 consecutive weights of one row (thread = (row, 32-column half)).
+struct Packed {
+    uint4 c0, c1;          // codes (c1: second 16 bytes of int8 layouts)
+    uint32_t h, h2;        // bit-plane words of the 32 columns
+    uint32_t m0, m1, m2;   // sb6: 12 bytes of scale codes;  sym: m0 = two int8 scale codes
+    uint32_t dd;           // sb6: d | dm << 16;  sym: d
+};
+
+__device__ __forceinline__ void load_packed(Packed& p, const QView& t, int row_g, int c0) {
     const size_t R = static_cast<size_t>(row_g);
-    const int c0 = k0 + 32 * half;                 // first column
+    const int nsb = t.cols >> 8;
+    p.h = p.h2 = 0;
+    if (t.kind == RWKVQ_KIND_SB6) {
+        const int blk = c0 >> 5;
+        p.c0 = ld_stream_u128(t.codes + R * (t.cols >> 1) + blk * 16);
+        if (t.qh) p.h = ld_stream_u32(t.qh + R * (t.cols >> 3) + blk * 4);
+        if (t.qh2) p.h2 = ld_stream_u32(t.qh2 + R * (t.cols >> 3) + blk * 4);
+        const uint8_t* mp = t.qsqm + (R * nsb + (blk >> 3)) * 12;
+        p.m0 = ld_stream_u32(mp); p.m1 = ld_stream_u32(mp + 4); p.m2 = ld_stream_u32(mp + 8);
+        p.dd = ld_stream_u16(t.d + R * nsb + (blk >> 3)) | (ld_stream_u16(t.dm + R * nsb + (blk >> 3)) << 16);
+    } else {
+        p.dd = ld_stream_u16(t.d + R * nsb + (c0 >> 8));
+        p.m0 = ld_stream_u16(t.qs + R * (t.cols >> 4) + (c0 >> 4));
+        if (t.bits == 8) {
+            const uint8_t* cp = t.codes + R * t.cols + c0;
+            p.c0 = ld_stream_u128(cp); p.c1 = ld_stream_u128(cp + 16);
+        } else {
+            p.c0 = ld_stream_u128(t.codes + R * (t.cols >> 1) + (c0 >> 1));
+            p.h = ld_stream_u32(t.qh + R * (t.cols >> 3) + (c0 >> 3));
+            p.h2 = ld_stream_u32(t.qh2 + R * (t.cols >> 3) + (c0 >> 3));
+        }
+    }
+}
+
+// 32 weights -> fp16, stored as 4 swizzled 16-byte chunks of row r of the A tile.
+__device__ __forceinline__ void convert_store(const Packed& p, const QView& t, int r, int half, int c0,
+                                              unsigned char* a_tile) {
     uint32_t bytes[8];                             // 32 codes as bytes, column order
     __half2 s2[2], m2[2], bias;                    // per 16 columns
+    const uint32_t h = p.h, h2 = p.h2;
     if (t.kind == RWKVQ_KIND_SB6) {
-        const int blk = c0 >> 5, nsb = t.cols >> 8;
-        const uint4 c = ld_stream_u128(t.codes + R * (t.cols >> 1) + blk * 16);
-        const uint32_t w[4] = {c.x, c.y, c.z, c.w};
-        uint32_t h = 0, h2 = 0;
-        if (t.qh) h = ld_stream_u32(t.qh + R * (t.cols >> 3) + blk * 4);
-        if (t.qh2) h2 = ld_stream_u32(t.qh2 + R * (t.cols >> 3) + blk * 4);
+        const uint32_t w[4] = {p.c0.x, p.c0.y, p.c0.z, p.c0.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {              // byte k of the block: column k (low), k + 16 (high)
             bytes[i] = (w[i] & 0x0F0F0F0Fu) | spread_nibble<4>((h >> (4 * i)) & 0xFu) |
@@ -143,35 +191,27 @@ __device__ __forceinline__ void produce_weights(const QView& t, int row_g, int r
             bytes[4 + i] = ((w[i] >> 4) & 0x0F0F0F0Fu) | spread_nibble<4>((h >> (16 + 4 * i)) & 0xFu) |
                            spread_nibble<5>((h2 >> (16 + 4 * i)) & 0xFu);
         }
-        const uint8_t* mp = t.qsqm + (R * nsb + (blk >> 3)) * 12;
         float s, m;
-        sb6_scale_min(ld_stream_u32(mp), ld_stream_u32(mp + 4), ld_stream_u32(mp + 8), blk & 7,
-                      __half2float(t.d[R * nsb + (blk >> 3)]), __half2float(t.dm[R * nsb + (blk >> 3)]), s, m);
+        sb6_scale_min(p.m0, p.m1, p.m2, (c0 >> 5) & 7, half_bits_to_float(p.dd & 0xFFFFu),
+                      half_bits_to_float(p.dd >> 16), s, m);
         s2[0] = s2[1] = __float2half2_rn(s);
         m2[0] = m2[1] = __float2half2_rn(m);
         bias = __float2half2_rn(1024.f);
     } else {                                       // sym: two blocks of 16
-        const int b16 = c0 >> 4, nsb = t.cols >> 8;
-        const float d = __half2float(t.d[R * nsb + (c0 >> 8)]);
-        const uint32_t qs2 = ld_stream_u16(t.qs + R * (t.cols >> 4) + b16);
+        const float d = half_bits_to_float(p.dd);
 #pragma unroll
         for (int b = 0; b < 2; ++b) {
-            const int q = static_cast<int8_t>((qs2 >> (8 * b)) & 0xFFu);
+            const int q = static_cast<int8_t>((p.m0 >> (8 * b)) & 0xFFu);
             s2[b] = __float2half2_rn(half_roundtrip(__fmul_rn(static_cast<float>(q), d)));
             m2[b] = __float2half2_rn(0.f);
         }
         if (t.bits == 8) {
-            const uint8_t* cp = t.codes + R * t.cols + c0;
-            const uint4 ca = ld_stream_u128(cp), cb = ld_stream_u128(cp + 16);
-            const uint32_t w[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+            const uint32_t w[8] = {p.c0.x, p.c0.y, p.c0.z, p.c0.w, p.c1.x, p.c1.y, p.c1.z, p.c1.w};
 #pragma unroll
             for (int i = 0; i < 8; ++i) bytes[i] = w[i] ^ 0x80808080u;      // code + 128
             bias = __float2half2_rn(1152.f);
         } else {
-            const uint4 c = ld_stream_u128(t.codes + R * (t.cols >> 1) + (c0 >> 1));
-            const uint32_t h = ld_stream_u32(t.qh + R * (t.cols >> 3) + (c0 >> 3));
-            const uint32_t h2 = ld_stream_u32(t.qh2 + R * (t.cols >> 3) + (c0 >> 3));
-            const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+            const uint32_t w[4] = {p.c0.x, p.c0.y, p.c0.z, p.c0.w};
 #pragma unroll
             for (int b = 0; b < 2; ++b)            // block b: words 2b, 2b+1; byte k: column k (low), k + 8 (high)
 #pragma unroll
@@ -194,12 +234,15 @@ __device__ __forceinline__ void produce_weights(const QView& t, int row_g, int r
 }
 
 template <int NT>   // tokens per CTA tile (UMMA N): 16, 32, 64, 128 or 256
-__global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a) {
+__global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    constexpr int A_BYTES = kGmRows * 128, B_BYTES = NT * 128, STAGE = A_BYTES + B_BYTES;
+    constexpr int A_BYTES = kGmRows * 128, B_BYTES = NT * 128;
     constexpr uint32_t TM_COLS = NT < 32 ? 32 : NT;
-    __shared__ uint64_t bar_free[kGmStages];
+    unsigned char* a_ring = smem;                               // [kGmAStages][A_BYTES]
+    unsigned char* b_ring = smem + kGmAStages * A_BYTES;        // [kGmBStages][B_BYTES]
+    __shared__ uint64_t bar_mma[kGmBStages];     // MMAs of iteration i (slot i % kGmBStages) have completed
+    __shared__ uint64_t bar_full[kGmBStages];    // the activation tile of iteration i has landed
     __shared__ uint64_t bar_done;
     __shared__ uint32_t s_tmem;
     __shared__ int s_fail;
@@ -207,10 +250,12 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const QView& t = a.t;
     const int row0 = blockIdx.x * kGmRows, tok0 = blockIdx.y * NT;
-    const int n_k = t.cols / kGmK;
+    const int KS = gridDim.z;
+    const int n_k = t.cols / kGmK / KS;                        // K iterations of this CTA's slice
+    const int k_first = blockIdx.z * n_k;
 
     if (tid == 0) {
-        for (int s = 0; s < kGmStages; ++s) mbar_init(&bar_free[s], 1);
+        for (int s = 0; s < kGmBStages; ++s) { mbar_init(&bar_mma[s], 1); mbar_init(&bar_full[s], 1); }
         mbar_init(&bar_done, 1);
         s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -224,41 +269,44 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
 
     const int pr = tid >> 1, ph = tid & 1;                     // producer: (row in tile, 32-column half)
     const int row_g = min(row0 + pr, t.rows - 1);
+    Packed nxt, nxt2;                                          // packed bytes of iterations i+1, i+2 in flight
+    load_packed(nxt, t, row_g, k_first * kGmK + 32 * ph);
+    if (n_k > 1) load_packed(nxt2, t, row_g, (k_first + 1) * kGmK + 32 * ph);
+    auto issue_b = [&](int j) {                                // activation tile of iteration j (thread 0 only)
+        const int sb = j % kGmBStages;
+        mbar_expect_tx(&bar_full[sb], B_BYTES);
+        tma_load_2d(b_ring + sb * B_BYTES, &xmap, (k_first + j) * kGmK, tok0, &bar_full[sb]);
+    };
+    if (tid == 0)
+        for (int j = 0; j < kGmAhead && j < n_k; ++j) issue_b(j);
     for (int i = 0; i < n_k; ++i) {
-        const int s = i % kGmStages;
-        unsigned char* a_tile = smem + s * STAGE;
-        unsigned char* b_tile = a_tile + A_BYTES;
-        if (i >= kGmStages) {                                  // wait until the MMAs that read this stage are done
-            if (!mbar_wait_bounded(&bar_free[s], ((i / kGmStages) - 1) & 1)) s_fail = 1;
+        const Packed cur = nxt;
+        nxt = nxt2;
+        if (i + 2 < n_k) load_packed(nxt2, t, row_g, (k_first + i + 2) * kGmK + 32 * ph);
+        if (tid == 0 && i + kGmAhead < n_k && !s_fail) {
+            // slot of iteration i + kGmAhead was last read by the MMAs of iteration i + kGmAhead - kGmBStages
+            const int j = i + kGmAhead, jp = j - kGmBStages;
+            if (jp >= 0 && !mbar_wait_bounded(&bar_mma[jp % kGmBStages], (jp / kGmBStages) & 1)) s_fail = 1;
+            else issue_b(j);
         }
-        if (!s_fail) {
-            produce_weights(t, row_g, pr, ph, i * kGmK, a_tile);
-            // activations: NT tokens x 8 chunks of 8 columns
-            for (int c = tid; c < NT * 8; c += kGmThreads) {
-                const int n = c >> 3, ch = c & 7, tok = tok0 + n;
-                uint4 o = make_uint4(0, 0, 0, 0);
-                if (tok < a.M) {
-                    const float sc = __ldcg(a.row_scale + tok);
-                    const float4* xp = reinterpret_cast<const float4*>(a.x + tok * a.ldx + i * kGmK + ch * 8);
-                    const float4 u = __ldcg(xp), v = __ldcg(xp + 1);
-                    const __half2 h0 = __floats2half2_rn(u.x * sc, u.y * sc), h1 = __floats2half2_rn(u.z * sc, u.w * sc);
-                    const __half2 h2 = __floats2half2_rn(v.x * sc, v.y * sc), h3 = __floats2half2_rn(v.z * sc, v.w * sc);
-                    o = make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1),
-                                   *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
-                }
-                *reinterpret_cast<uint4*>(b_tile + sw128_offset(n, ch)) = o;
-            }
+        unsigned char* a_tile = a_ring + (i % kGmAStages) * A_BYTES;
+        unsigned char* b_tile = b_ring + (i % kGmBStages) * B_BYTES;
+        if (i >= kGmAStages) {                                 // the MMAs of iteration i - kGmAStages read this A slab
+            const int ip = i - kGmAStages;
+            if (!mbar_wait_bounded(&bar_mma[ip % kGmBStages], (ip / kGmBStages) & 1)) s_fail = 1;
         }
+        if (!s_fail) convert_store(cur, t, pr, ph, (k_first + i) * kGmK + 32 * ph, a_tile);
         fence_async_smem();                                    // generic-proxy stores -> visible to the tensor core
         tc_fence_before();
         __syncthreads();
+        if (tid == 0 && !s_fail && !mbar_wait_bounded(&bar_full[i % kGmBStages], (i / kGmBStages) & 1)) s_fail = 1;
         if (tid == 0 && !s_fail) {
             tc_fence_after();
             const uint64_t ad = umma_desc(smem_addr(a_tile)), bd = umma_desc(smem_addr(b_tile));
 #pragma unroll
             for (int k = 0; k < kGmK / 16; ++k)                // 32 bytes further along K per step
                 umma_f16(tmem, ad + 2 * k, bd + 2 * k, idesc, (i | k) ? 1u : 0u);
-            umma_commit(&bar_free[s]);
+            umma_commit(&bar_mma[i % kGmBStages]);
             if (i == n_k - 1) umma_commit(&bar_done);
         }
     }
@@ -269,20 +317,64 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
         if (tid == 0) atomicCAS(a.status, 0, RWKVQ_E_TIMEOUT);
     } else {
         // warp w reads lanes 32*(w%4) .. +31 (= output rows); warps w and w+4 split the tokens
-        const int row = row0 + (warp & 3) * 32 + lane;
+        const int rl = (warp & 3) * 32 + lane, row = row0 + rl;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-        for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += 16) {
-            float v[8];
-            tmem_ld8(lane_base + c0, v);
+        auto finish = [&](float r, int tok) {
+            if (tok < a.M && row < t.rows) {
+                r = r / __ldcg(a.row_scale + tok);
+                const long long idx = tok * a.ldy + row;
+                if (a.epilogue == RWKVQ_EPI_RELU2) { r = fmaxf(r, 0.f); r = r * r; }
+                else if (a.epilogue == RWKVQ_EPI_ADD) r = __fadd_rn(r, __ldcg(a.resid + idx));
+                a.y[idx] = r;
+            }
+        };
+        if (KS == 1) {
+            for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += 16) {
+                float v[8];
+                tmem_ld8(lane_base + c0, v);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int tok = tok0 + c0 + j;
-                if (tok < a.M && row < t.rows) {
-                    float r = v[j] / __ldcg(a.row_scale + tok);
-                    const long long idx = tok * a.ldy + row;
-                    if (a.epilogue == RWKVQ_EPI_RELU2) { r = fmaxf(r, 0.f); r = r * r; }
-                    else if (a.epilogue == RWKVQ_EPI_ADD) r = __fadd_rn(r, __ldcg(a.resid + idx));
-                    a.y[idx] = r;
+                for (int j = 0; j < 8; ++j) finish(v[j], tok0 + c0 + j);
+            }
+        } else {
+            // this CTA's accumulator tile goes to its scratch slot [token][row]
+            const size_t tile_id = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
+            float* mine = a.partial + (tile_id * KS + blockIdx.z) * (NT * kGmRows);
+            for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += 16) {
+                float v[8];
+                tmem_ld8(lane_base + c0, v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) __stcg(mine + (c0 + j) * kGmRows + rl, v[j]);
+            }
+            __threadfence();
+            __syncthreads();
+            __shared__ unsigned int s_last;
+            if (tid == 0) s_last = (atomicAdd(a.counters + tile_id, 1u) == static_cast<unsigned int>(KS - 1));
+            __syncthreads();
+            if (s_last) {                           // last K slice to arrive adds the tiles in slice order
+                __threadfence();
+                const float* base = a.partial + tile_id * KS * (NT * kGmRows);
+                // warps w and w+4 take alternate groups of 8 tokens; 8 x KS loads are in flight per
+                // thread and every token's slices are added in slice order
+                for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += 16) {
+                    float r[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) r[j] = 0.f;
+                    for (int z0 = 0; z0 < KS; z0 += 4) {
+                        float pv[4][8];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                pv[u][j] = z0 + u < KS
+                                               ? __ldcg(base + (static_cast<size_t>(z0 + u) * NT + c0 + j) * kGmRows + rl)
+                                               : 0.f;
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) r[j] += pv[u][j];
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) finish(r[j], tok0 + c0 + j);
                 }
             }
         }
@@ -292,8 +384,10 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
     if (warp == 0) tmem_dealloc(tmem, TM_COLS);
 }
 
-// power-of-two scale per token row so that |x * scale| <= 2^14 (fp16-safe with headroom)
-__global__ void __launch_bounds__(256) row_scale_kernel(const float* x, long long ldx, int cols, float* scale) {
+// Pre-pass, one CTA per token: power-of-two scale so that |x * scale| <= 2^14, and the
+// scaled row as fp16 (the tensor the TMA loads read).
+__global__ void __launch_bounds__(256) row_scale_kernel(const float* x, long long ldx, int cols, float* scale,
+                                                        __half* x16) {
     __shared__ float red[8];
     const float* row = x + blockIdx.x * ldx;
     float amax = 0.f;
@@ -302,11 +396,16 @@ __global__ void __launch_bounds__(256) row_scale_kernel(const float* x, long lon
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
-        int e = 0;
-        if (amax > 0.f && amax < INFINITY) frexpf(amax, &e);
-        scale[blockIdx.x] = ldexpf(1.f, 14 - e);
+    amax = red[0];
+    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
+    int e = 0;
+    if (amax > 0.f && amax < INFINITY) frexpf(amax, &e);
+    const float sc = ldexpf(1.f, 14 - e);
+    if (threadIdx.x == 0) scale[blockIdx.x] = sc;
+    __half2* out = reinterpret_cast<__half2*>(x16 + static_cast<size_t>(blockIdx.x) * cols);
+    for (int i = threadIdx.x; i < (cols >> 1); i += 256) {
+        const float2 v = __ldcg(reinterpret_cast<const float2*>(row) + i);
+        out[i] = __floats2half2_rn(v.x * sc, v.y * sc);
     }
 }
 
@@ -315,9 +414,46 @@ __global__ void __launch_bounds__(256) row_scale_kernel(const float* x, long lon
 using namespace rwkvq;
 
 namespace {
+constexpr int kGemmResident = 2 * 148;
+constexpr size_t kGemmHeader = 8192;        // status word + arrival counters (zeroed every call)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// fp16 activations [M, cols] row-major; box = [NT tokens, 64 columns], 128-byte swizzle, zero fill
+int make_xmap(CUtensorMap* map, const __half* x16, int M, int cols, int nt) {
+    EncodeTiledFn enc = encode_tiled();
+    RWKVQ_REQUIRE(enc != nullptr, RWKVQ_E_ARCH, "rwkvq_gemm: cuTensorMapEncodeTiled is not available");
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * sizeof(__half)};
+    const cuuint32_t box[2] = {kGmK, static_cast<cuuint32_t>(nt)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(x16), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    RWKVQ_REQUIRE(r == CUDA_SUCCESS, RWKVQ_E_LAUNCH, "rwkvq_gemm: cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+    return RWKVQ_OK;
+}
+
 template <int NT>
-int launch_gemm(const GemmArgs& a, int rows, int M, cudaStream_t s) {
-    const size_t smem = static_cast<size_t>(kGmStages) * (kGmRows * 128 + NT * 128) + 1024;
+int launch_gemm(GemmArgs& a, int rows, int cols, int M, float* partial, const __half* x16, cudaStream_t s) {
+    CUtensorMap xmap;
+    int mrc = make_xmap(&xmap, x16, M, cols, NT);
+    if (mrc) return mrc;
+    const size_t smem = static_cast<size_t>(kGmAStages) * kGmRows * 128 + static_cast<size_t>(kGmBStages) * NT * 128 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -325,14 +461,31 @@ int launch_gemm(const GemmArgs& a, int rows, int M, cudaStream_t s) {
         if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "rwkvq_gemm: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    gemm_tc_kernel<NT><<<dim3((rows + kGmRows - 1) / kGmRows, (M + NT - 1) / NT), kGmThreads, smem, s>>>(a);
+    const int rt = (rows + kGmRows - 1) / kGmRows, tt = (M + NT - 1) / NT, n_k = cols / kGmK;
+    // K slices across CTAs until about one wave of CTAs is reached (power of two, >= 2 iterations each)
+    int KS = 1;
+    while (rt * tt * KS * 2 <= kGemmResident && n_k % (KS * 2) == 0 && n_k / (KS * 2) >= 2 &&
+           rt * tt <= static_cast<int>((kGemmHeader - 256) / sizeof(unsigned int)))
+        KS *= 2;
+    a.partial = partial;
+    gemm_tc_kernel<NT><<<dim3(rt, tt, KS), kGmThreads, smem, s>>>(a, xmap);
     return RWKVQ_OK;
 }
 }  // namespace
 
 extern "C" {
 
-size_t rwkvq_gemm_workspace_bytes(int M) { return 256 + sizeof(float) * static_cast<size_t>(M < 1 ? 1 : M); }
+// header | row scales [M] | K-split accumulator tiles (one wave of CTAs x 128 x NT floats) | fp16 activations
+static size_t gemm_ws_partial_off(size_t m) { return kGemmHeader + ((sizeof(float) * m + 255) / 256) * 256; }
+static size_t gemm_ws_x16_off(size_t m) {
+    const size_t nt = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
+    return gemm_ws_partial_off(m) + sizeof(float) * kGemmResident * kGmRows * nt;
+}
+size_t rwkvq_gemm_workspace_bytes_for(int M, int max_cols) {
+    const size_t m = static_cast<size_t>(M < 1 ? 1 : M);
+    return gemm_ws_x16_off(m) + sizeof(__half) * m * static_cast<size_t>(max_cols) + 256;
+}
+size_t rwkvq_gemm_workspace_bytes(int M) { return rwkvq_gemm_workspace_bytes_for(M, 16384); }
 
 int rwkvq_gemm(const rwkvq_qtensor* t, const float* x, int M, int64_t ldx, float* y, int64_t ldy, int epilogue,
                const float* resid, void* workspace, size_t workspace_bytes, void* stream) {
@@ -343,25 +496,29 @@ int rwkvq_gemm(const rwkvq_qtensor* t, const float* x, int M, int64_t ldx, float
     RWKVQ_REQUIRE(x && y && workspace, RWKVQ_E_NULL, "rwkvq_gemm: null pointer");
     RWKVQ_REQUIRE(M >= 1 && ldx >= t->cols && ldy >= t->rows, RWKVQ_E_SHAPE, "rwkvq_gemm: M=%d ldx=%lld ldy=%lld", M,
                   (long long)ldx, (long long)ldy);
-    RWKVQ_REQUIRE(aligned(x, 16) && ldx % 4 == 0 && aligned(workspace, 16), RWKVQ_E_ALIGN,
-                  "rwkvq_gemm: x, its row stride and the workspace must be 16-byte aligned");
-    RWKVQ_REQUIRE(workspace_bytes >= rwkvq_gemm_workspace_bytes(M), RWKVQ_E_LIMIT, "rwkvq_gemm: workspace %zu < %zu bytes",
-                  workspace_bytes, rwkvq_gemm_workspace_bytes(M));
+    RWKVQ_REQUIRE(aligned(x, 16) && ldx % 4 == 0 && aligned(workspace, 256), RWKVQ_E_ALIGN,
+                  "rwkvq_gemm: x and its row stride must be 16-byte aligned, the workspace 256-byte aligned");
+    RWKVQ_REQUIRE(workspace_bytes >= rwkvq_gemm_workspace_bytes_for(M, t->cols), RWKVQ_E_LIMIT,
+                  "rwkvq_gemm: workspace %zu < %zu bytes", workspace_bytes, rwkvq_gemm_workspace_bytes_for(M, t->cols));
     RWKVQ_REQUIRE(epilogue >= RWKVQ_EPI_NONE && epilogue <= RWKVQ_EPI_ADD, RWKVQ_E_DTYPE, "rwkvq_gemm: epilogue %d", epilogue);
     RWKVQ_REQUIRE(epilogue != RWKVQ_EPI_ADD || resid, RWKVQ_E_NULL, "rwkvq_gemm: resid is null");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    char* ws = static_cast<char*>(workspace);
     GemmArgs a{};
     a.t = make_view(*t);
     a.x = x; a.ldx = ldx; a.y = y; a.ldy = ldy; a.resid = resid; a.M = M; a.epilogue = epilogue;
-    a.status = static_cast<int*>(workspace);
-    float* scale = reinterpret_cast<float*>(static_cast<char*>(workspace) + 256);
+    a.status = reinterpret_cast<int*>(ws);
+    a.counters = reinterpret_cast<unsigned int*>(ws + 256);
+    float* scale = reinterpret_cast<float*>(ws + kGemmHeader);
+    float* partial = reinterpret_cast<float*>(ws + gemm_ws_partial_off(M));
+    __half* x16 = reinterpret_cast<__half*>(ws + gemm_ws_x16_off(M));
     a.row_scale = scale;
-    cudaMemsetAsync(a.status, 0, sizeof(int), s);
-    row_scale_kernel<<<M, 256, 0, s>>>(x, ldx, t->cols, scale);
-    if (M <= 16) rc = launch_gemm<16>(a, t->rows, M, s);
-    else if (M <= 32) rc = launch_gemm<32>(a, t->rows, M, s);
-    else if (M <= 64) rc = launch_gemm<64>(a, t->rows, M, s);
-    else rc = launch_gemm<128>(a, t->rows, M, s);
+    cudaMemsetAsync(ws, 0, kGemmHeader, s);
+    row_scale_kernel<<<M, 256, 0, s>>>(x, ldx, t->cols, scale, x16);
+    if (M <= 16) rc = launch_gemm<16>(a, t->rows, t->cols, M, partial, x16, s);
+    else if (M <= 32) rc = launch_gemm<32>(a, t->rows, t->cols, M, partial, x16, s);
+    else if (M <= 64) rc = launch_gemm<64>(a, t->rows, t->cols, M, partial, x16, s);
+    else rc = launch_gemm<128>(a, t->rows, t->cols, M, partial, x16, s);
     if (rc) return rc;
     return check_launch("rwkvq_gemm");
 }

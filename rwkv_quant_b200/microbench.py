@@ -3,6 +3,7 @@
     python -m rwkv_quant_b200.microbench gemv LAYOUT BITS ROWS COLS [--n N] [--launches K]
     python -m rwkv_quant_b200.microbench decode [--layers L] [--recipe R] [--steps S] [--batch B]
     python -m rwkv_quant_b200.microbench sweep          # GEMV shapes of the 1.5B model, GB/s each
+    python -m rwkv_quant_b200.microbench prefill [--T 512] [--batch B] [--recipe R]
 
 `gemv` and `decode` do a handful of launches and exit (suitable under a profiler);
 `sweep` replays a ring of distinct weight buffers (working set >> L2) as a CUDA graph and
@@ -49,6 +50,27 @@ def decode(layers=4, recipe="compression", steps=3, batch=1, model="1.5b"):
         dec.feed_back()
     torch.cuda.synchronize()
     print("ok", dec.next_tokens.tolist())
+
+
+def prefill(layers=24, recipe="reduction", T=512, batch=1, model="1.5b", reps=3):
+    """pp{T}: one stateful call over a prompt of T tokens, logits for the last position."""
+    ck = synth.build_checkpoint(model, recipe, seed=0, device="cuda", n_layer=layers)
+    m = QuantRWKV7(ck)
+    del ck
+    g = torch.Generator().manual_seed(0)
+    idx = torch.randint(1, 60000, (batch, T), generator=g).cuda()
+    m.forward_stateful(idx, m.init_state(batch), last_only=True)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = 1e9
+    for _ in range(reps):
+        st = m.init_state(batch)
+        e0.record()
+        m.forward_stateful(idx, st, last_only=True)
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    print(f"pp{T} batch {batch} {recipe} {layers} layers: {best:.2f} ms  {batch * T / best * 1e3:.0f} tok/s", flush=True)
 
 
 def time_ring(layout, bits, rows, cols, n=1, ring_bytes=1.5e9, iters=5):
@@ -114,11 +136,16 @@ def main():
     d.add_argument("--layers", type=int, default=4); d.add_argument("--recipe", default="compression")
     d.add_argument("--steps", type=int, default=3); d.add_argument("--batch", type=int, default=1)
     sub.add_parser("sweep")
+    pf = sub.add_parser("prefill")
+    pf.add_argument("--layers", type=int, default=24); pf.add_argument("--recipe", default="reduction")
+    pf.add_argument("--T", type=int, default=512); pf.add_argument("--batch", type=int, default=1)
     a = ap.parse_args()
     if a.cmd == "gemv":
         gemv(a.layout, a.bits, a.rows, a.cols, a.n, a.launches)
     elif a.cmd == "decode":
         decode(a.layers, a.recipe, a.steps, a.batch)
+    elif a.cmd == "prefill":
+        prefill(a.layers, a.recipe, a.T, a.batch)
     else:
         sweep()
 
