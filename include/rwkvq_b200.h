@@ -174,6 +174,31 @@ int rwkvq_gemv_fused(const rwkvq_qtensor* ts_host, int K, const void* x, int x_d
 int rwkvq_gemv_t(const rwkvq_qtensor* t, const float* x, int N, int64_t ldx,
                  float* y, int64_t ldy, int act, int round_w, void* stream);
 
+/*
+ * Single-vector rwkvq_gemv that allocates nothing.  NO COUNTERPART IN THE
+ * REFERENCE: added for callers that may not allocate on the call path (an
+ * inference server's steady-state loop that has frozen its memory pool, a host
+ * thread under a real-time budget, code running where cudaMalloc would
+ * synchronise the device).
+ *   y[o] = epi( sum_c W[o, c] x[c] ),  x [cols] of x_dtype, y / resid [rows] fp32.
+ * The K loop is split across CTAs; the slices' partial sums and arrival counters
+ * live in a 260 KiB __device__ array inside the library, whose address is looked
+ * up once per device.  The call issues one cudaMemsetAsync (counters) and one
+ * kernel on `stream`; it calls no cudaMalloc / cudaFree nor any allocating
+ * library routine.
+ *   limits  rows <= 4096, cols <= 16384 (RWKVQ_E_LIMIT beyond); sb6 tensors need
+ *           dev_meta (and dev_planes at 5 / 6 bits), sym@6 needs dev_planes
+ *           (RWKVQ_E_DTYPE otherwise); x 16-byte aligned.
+ *   set-up  the first call on a device resolves the array's address (and may load
+ *           the module): make it before any stream capture begins.
+ *   races   every call on a device uses the same array: two calls that can
+ *           overlap (different streams or threads) race on it; serialise them.
+ * Results equal rwkvq_gemv's up to fp32 summation order and are bit-identical
+ * from call to call.
+ */
+int rwkvq_gemv_static(const rwkvq_qtensor* t, const void* x, int x_dtype, float* y,
+                      int epilogue, const float* resid, void* stream);
+
 
 /*
  * WKV-7 recurrence with state in and out, any T >= 1, head size 64:

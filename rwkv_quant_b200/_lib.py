@@ -82,6 +82,8 @@ _PROTOS = {
     "rwkvq_relayout_planes": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_void_p]),
     "rwkvq_gemv_t": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_int64,
                                C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
+    "rwkvq_gemv_static": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_void_p,
+                                    C.c_int, C.c_void_p, C.c_void_p]),
 }
 
 

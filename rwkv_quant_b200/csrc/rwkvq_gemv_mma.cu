@@ -655,3 +655,69 @@ int rwkvq_relayout_planes(const rwkvq_qtensor* t, void* planes_out, void* stream
 }
 
 }  // extern "C"
+
+// ------------------------------------------------- K-split GEMV, built-in scratch
+// The K-split launch needs room for the slices' partial row sums and for its
+// arrival counters.  This variant keeps that room in the module image, so the call
+// path never asks the CUDA allocator for anything.
+namespace rwkvq {
+
+constexpr int kStaticMaxRows = kSplitMaxRows;     // largest OUT served
+constexpr int kStaticMaxCols = 16384;             // largest IN served (shared-memory staging of x)
+constexpr size_t kStaticPartialFloats = static_cast<size_t>(kSplitMaxSlices) * kMmaMaxFused * kSplitMaxRows;
+constexpr size_t kStaticCounterWords = 1024;
+constexpr int kStaticMaxDevices = 64;
+
+// 256 KiB of partial sums followed by 4 KiB of counters; zero at module load.
+static __device__ __align__(256) float g_static_scratch[kStaticPartialFloats + kStaticCounterWords];
+
+// Device address of the scratch on the current device, looked up once per device.
+static int static_scratch(float** out) {
+    static float* ptrs[kStaticMaxDevices] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "rwkvq_gemv_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kStaticMaxDevices)
+        return fail(RWKVQ_E_LIMIT, "rwkvq_gemv_static: device ordinal %d, at most %d devices", dev, kStaticMaxDevices);
+    float* p = __atomic_load_n(&ptrs[dev], __ATOMIC_ACQUIRE);
+    if (p == nullptr) {
+        void* sym = nullptr;
+        e = cudaGetSymbolAddress(&sym, g_static_scratch);
+        if (e != cudaSuccess || sym == nullptr)
+            return fail(RWKVQ_E_LAUNCH, "rwkvq_gemv_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        p = static_cast<float*>(sym);
+        __atomic_store_n(&ptrs[dev], p, __ATOMIC_RELEASE);   // racing threads store the same address
+    }
+    *out = p;
+    return RWKVQ_OK;
+}
+
+}  // namespace rwkvq
+
+extern "C" int rwkvq_gemv_static(const rwkvq_qtensor* t, const void* x, int x_dtype, float* y, int epilogue,
+                                 const float* resid, void* stream) {
+    int rc = validate_qtensor(t, "rwkvq_gemv_static");
+    if (rc) return rc;
+    RWKVQ_REQUIRE(x != nullptr && y != nullptr, RWKVQ_E_NULL, "rwkvq_gemv_static: x or y is null");
+    RWKVQ_REQUIRE(x_dtype == RWKVQ_F32 || x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_DTYPE,
+                  "rwkvq_gemv_static: x_dtype %d", x_dtype);
+    RWKVQ_REQUIRE(aligned(x, 16), RWKVQ_E_ALIGN, "rwkvq_gemv_static: x must be 16-byte aligned");
+    RWKVQ_REQUIRE(epilogue >= RWKVQ_EPI_NONE && epilogue <= RWKVQ_EPI_ADD, RWKVQ_E_DTYPE,
+                  "rwkvq_gemv_static: epilogue %d", epilogue);
+    RWKVQ_REQUIRE(epilogue != RWKVQ_EPI_ADD || resid != nullptr, RWKVQ_E_NULL, "rwkvq_gemv_static: resid is null");
+    const int ml = mma_layout_of(*t);
+    RWKVQ_REQUIRE(ml >= 0, RWKVQ_E_DTYPE,
+                  "rwkvq_gemv_static: needs an sb6 tensor with relayouted records/planes or a sym tensor");
+    RWKVQ_REQUIRE(t->rows <= kStaticMaxRows && t->cols <= kStaticMaxCols, RWKVQ_E_LIMIT,
+                  "rwkvq_gemv_static: [%d, %d] exceeds the built-in scratch, at most [%d, %d]", t->rows, t->cols,
+                  kStaticMaxRows, kStaticMaxCols);
+    float* scratch = nullptr;
+    rc = static_scratch(&scratch);
+    if (rc) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // the arrival counters must read zero when the kernel starts
+    cudaError_t e = cudaMemsetAsync(scratch + kStaticPartialFloats, 0, kStaticCounterWords * sizeof(unsigned int), s);
+    if (e != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "rwkvq_gemv_static: cudaMemsetAsync: %s", cudaGetErrorString(e));
+    rc = launch_gemv_mma(ml, t, 1, x, x_dtype, t->cols, y, t->rows, epilogue, resid, 0, s, nullptr, scratch);
+    return rc ? rc : check_launch("rwkvq_gemv_static");
+}
