@@ -46,6 +46,8 @@ def parse():
     ap.add_argument("--recipe", default="compression")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--decoder", default="chain", choices=["persistent", "chain"],
+                    help="batch-1 decoder: one persistent kernel per token, or the launch chain")
     return ap.parse_args()
 
 
@@ -232,7 +234,9 @@ def run_ours(a, rank, world, local_rank):
 
     prompt = torch.from_numpy(__import__("numpy").random.default_rng(rank).integers(1, 60000, (B,))).to(dev)
     # ---- device-resident loop: one graph replay per token, argmax fed back on the device
-    dec = model.decoder(B, use_graph=True, self_feed=True)
+    persistent = a.decoder == "persistent"
+    dec = model.decoder(B, use_graph=True, self_feed=True, persistent=persistent)
+    dec_kind = type(dec).__name__
     dec.tokens.copy_(prompt)
     for _ in range(a.warmup):
         dec.step()
@@ -249,7 +253,7 @@ def run_ours(a, rank, world, local_rank):
     clocks = clk.summary()
 
     # ---- end to end: token ids from pinned host memory, argmax read back every step
-    dec2 = model.decoder(B, use_graph=True, self_feed=False)
+    dec2 = model.decoder(B, use_graph=True, self_feed=False, persistent=persistent)
     host_tok = torch.empty(B, dtype=torch.long).pin_memory()
     host_tok.copy_(prompt.cpu())
     host_out = torch.empty(B, dtype=torch.long).pin_memory()
@@ -289,12 +293,14 @@ def run_ours(a, rank, world, local_rank):
         "config": {"workload": f"rwkv7-{a.model} {a.recipe} random-init, greedy decode tg{a.steps}, "
                                f"{B} stream(s) per GPU, full replica per GPU",
                    "streams_per_gpu": B, "weight_bytes_per_token": w_bytes,
+                   "decoder": ("one persistent cooperative kernel per token" if dec_kind == "PersistentDecoder"
+                               else "CUDA-graph replay of the launch chain"),
                    "state_bytes_per_step": state_bytes,
                    "l2": "weights per token (>= 800 MB) exceed the 126 MB L2; no flush needed",
                    "vs_baseline_ref": "75.3 tok/s tg128 on Apple M4 (reference README), other hardware"},
         "e2e": {"value": total_tokens / t_e2e, "unit": "tok/s", "h2d_bytes_per_step": 8 * B,
                 "d2h_bytes_per_step": 8 * B},
-        "gpu_launches": (model.launches_per_token + 1) * a.steps,
+        "gpu_launches": (dec.launches_per_step or (model.launches_per_token + 1)) * a.steps,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": g_bytes / g_sec / 1e9, "peak": peak, "unit": "GB/s",
                      "frac": g_bytes / g_sec / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,

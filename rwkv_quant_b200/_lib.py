@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_HERE, "librwkvq_b200.so")
 F32, F16, BF16 = 0, 1, 2
 KIND = {"dense": 0, "sb6": 1, "sym": 2, "asym": 3, "rtn": 4}
 EPI_NONE, EPI_RELU2, EPI_ADD = 0, 1, 2
+E_SHAPE, E_ALIGN, E_DTYPE, E_ARCH, E_LAUNCH, E_TIMEOUT, E_NULL, E_LIMIT = -1, -2, -3, -4, -5, -6, -7, -8
 DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
 
@@ -84,6 +85,18 @@ _PROTOS = {
                                C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
     "rwkvq_gemv_static": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_void_p,
                                     C.c_int, C.c_void_p, C.c_void_p]),
+    "rwkvq_decoder_workspace_bytes": (C.c_size_t, [C.POINTER(ModelStruct)]),
+    "rwkvq_decoder_create": (C.c_int, [C.POINTER(ModelStruct), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                       C.POINTER(C.c_void_p), C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p,
+                                       C.POINTER(C.c_void_p)]),
+    "rwkvq_decoder_destroy": (None, [C.c_void_p]),
+    "rwkvq_decoder_token": (C.c_void_p, [C.c_void_p]),
+    "rwkvq_decoder_logits": (C.c_void_p, [C.c_void_p]),
+    "rwkvq_decoder_grid": (C.c_int, [C.c_void_p]),
+    "rwkvq_decoder_stages": (C.c_int, [C.c_void_p]),
+    "rwkvq_decoder_set_trace": (None, [C.c_void_p, C.c_void_p]),
+    "rwkvq_decoder_step": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "rwkvq_decoder_status": (C.c_int, [C.c_void_p, C.c_void_p]),
 }
 
 

@@ -308,7 +308,16 @@ class QuantRWKV7:
             tok = dec.step(tok)
         return torch.stack(out, dim=1), dec.states
 
-    def decoder(self, batch_size: int = 1, states=None, use_graph: bool = True, self_feed: bool = False):
+    def decoder(self, batch_size: int = 1, states=None, use_graph: bool = True, self_feed: bool = False,
+                persistent=None):
+        """``persistent=True`` selects the one-kernel decoder (one stream, every linear in a
+        tensor-core GEMV layout); the default is the CUDA-graph launch chain, which is the
+        faster of the two on B200 (the persistent kernel's stages are instruction-latency
+        bound at 8 warps per SM; see ``microbench timeline``)."""
+        if persistent:
+            if batch_size != 1:
+                raise ValueError("the persistent decoder serves one stream")
+            return PersistentDecoder(self, states)
         return Decoder(self, batch_size, states, use_graph, self_feed)
 
     @property
@@ -372,3 +381,59 @@ class Decoder:
     def feed_back(self):
         """Use the last argmax as the next input without leaving the device."""
         self.tokens.copy_(self.next_tokens)
+
+
+class PersistentDecoder:
+    """One stream decoded by the persistent cooperative kernel: one launch per token, the
+    argmax is fed back on the device.  ``tokens`` is both the input slot and, after a
+    step, the greedy next token; ``step(tokens)`` overrides the fed-back token."""
+
+    B = 1
+    launches_per_step = 1
+    graph = None
+    self_feed = True
+
+    def __init__(self, model: QuantRWKV7, states=None):
+        self.m = model
+        st = model.init_state(1) if states is None else states
+        self.states = model._materialize(st, 1)
+        dev = model.device
+        lib = _lib.load()
+        nbytes = lib.rwkvq_decoder_workspace_bytes(C.byref(model._model_c))
+        if nbytes == 0:
+            raise _lib.RwkvqError(_lib.E_DTYPE, "rwkvq_decoder_workspace_bytes",
+                                  lib.rwkvq_last_error_detail().decode() or "model not servable by the persistent decoder")
+        self._ws = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+        self.logits = torch.empty((1, model.vocab_size), dtype=torch.float32, device=dev)
+        arr = lambda k: (C.c_void_p * model.n_layer)(*[s[k].data_ptr() for s in self.states])
+        self._h = C.c_void_p()
+        with torch.cuda.device(dev):
+            _lib.check(lib.rwkvq_decoder_create(C.byref(model._model_c), arr(0), arr(1), arr(2), self._ws.data_ptr(),
+                                                nbytes, self.logits.data_ptr(), _lib.stream_ptr(), C.byref(self._h)),
+                       "rwkvq_decoder_create")
+        off = lib.rwkvq_decoder_token(self._h) - self._ws.data_ptr()
+        self.tokens = self._ws[off:off + 8].view(torch.long)
+        self.next_tokens = self.tokens
+        self.grid = lib.rwkvq_decoder_grid(self._h)
+        self.stages = lib.rwkvq_decoder_stages(self._h)
+
+    def step(self, tokens=None):
+        if tokens is not None:
+            self.tokens.copy_(tokens.reshape(1), non_blocking=True)
+        _lib.check(_lib.load().rwkvq_decoder_step(self._h, _lib.stream_ptr()), "rwkvq_decoder_step")
+        return self.tokens
+
+    def feed_back(self):
+        pass                                   # the kernel already wrote the argmax into the input slot
+
+    def check(self):
+        """Synchronise and raise if a grid barrier of the kernel ran out of polls."""
+        _lib.check(_lib.load().rwkvq_decoder_status(self._h, _lib.stream_ptr()), "rwkvq_decoder_status")
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                _lib.load().rwkvq_decoder_destroy(h)
+            except Exception:
+                pass

@@ -52,6 +52,73 @@ def decode(layers=4, recipe="compression", steps=3, batch=1, model="1.5b"):
     print("ok", dec.next_tokens.tolist())
 
 
+def timeline(layers=24, recipe="compression", model="1.5b", warm=6):
+    """Stage timeline of the persistent decode kernel for one token: per stage kind the
+    span on the critical path (barrier exit to barrier exit), the slowest CTA's work time
+    and the time between the last arrival and the barrier exit."""
+    import ctypes as C
+
+    import numpy as np
+
+    from . import _lib
+    ck = synth.build_checkpoint(model, recipe, seed=0, device="cuda", n_layer=layers)
+    m = QuantRWKV7(ck)
+    del ck
+    dec = m.decoder(1, persistent=True)
+    for _ in range(warm):
+        dec.step()
+    torch.cuda.synchronize()
+    n, g = dec.stages, dec.grid
+    buf = torch.zeros(n * g * 8, dtype=torch.int64, device="cuda")
+    lib = _lib.load()
+    lib.rwkvq_decoder_set_trace(dec._h, buf.data_ptr())
+    dec.step()
+    dec.check()
+    lib.rwkvq_decoder_set_trace(dec._h, None)
+    t = buf.cpu().numpy().reshape(n, g, 8).astype(np.float64)
+    t0 = t[0, :, 0].min()
+    raw = t
+    t = (t - t0) * 1e-3                                  # microseconds
+    # inside the GEMV stages, for CTA 0 (always a GEMV CTA): start -> row normalised -> digits -> items -> outputs
+    inner = {}
+    for i in range(n - 1):
+        if raw[i, 0, 4] == 0 or (i < layers * 5 and i % 5 == 1):
+            continue
+        name = (["S1 rkv+lora", "S2 tmix", "S3 out", "S4 ffn.key", "S5 ffn.value"][i % 5] if i < layers * 5 else "head")
+        c = 5
+        ln = (t[i, c, 3] - t[i, c, 0]) if raw[i, c, 3] else 0.0
+        inner.setdefault(name, []).append((ln, t[i, c, 4] - t[i, c, 0], t[i, c, 5] - t[i, c, 4], t[i, c, 6] - t[i, c, 5],
+                                           (t[i, c, 7] - t[i, c, 0]) if raw[i, c, 7] else 0.0))
+    print(f"SM clock during the launch: {raw[n - 1, 0, 3] / raw[n - 1, 0, 4] * 1e3:.0f} MHz")
+    kinds = ["S1 rkv+lora", "S2 tmix", "S3 out", "S4 ffn.key", "S5 ffn.value"]
+    rows = {}
+    prev_exit = 0.0
+    for i in range(n - 1):
+        name = kinds[i % 5] if i < layers * 5 else ["head", "argmax", "argmax final"][i - layers * 5]
+        exit_ = t[i, :, 2].max()
+        work = (t[i, :, 1] - t[i, :, 0]).max()
+        last_arrival = t[i, :, 1].max()
+        rows.setdefault(name, []).append((exit_ - prev_exit, work, exit_ - last_arrival, t[i, :, 0].max() - t[i, :, 0].min()))
+        prev_exit = exit_
+    print(f"persistent decode timeline, {model} {recipe} {layers} layers, grid {g}, {n} stages; total {t[n - 1, 0, 1]:.1f} us")
+    print(f"{'stage':<14}{'count':>6}{'span us':>10}{'max work':>10}{'barrier':>10}{'start skew':>12}")
+    for name, v in rows.items():
+        a = np.array(v)
+        print(f"{name:<14}{len(v):>6}{a[:, 0].mean():>10.2f}{a[:, 1].mean():>10.2f}{a[:, 2].mean():>10.2f}{a[:, 3].mean():>12.2f}")
+    print("CTA 5 inside the GEMV stages (us): LN done, input ready (cumulative), items, epilogue, first input load landed")
+    for name, v in inner.items():
+        a = np.array(v)
+        print(f"{name:<14}{a[:, 0].mean():>10.2f}{a[:, 1].mean():>10.2f}{a[:, 2].mean():>10.2f}{a[:, 3].mean():>10.2f}{a[:, 4].mean():>10.2f}")
+    tm = np.array([[t[i, 5, k] - t[i, 5, 0] for k in (3, 4, 5, 6, 1)] for i in range(1, layers * 5, 5)])
+    print("CTA 5 inside S2 (us, cumulative): staged data landed, hidden vectors, LoRA up, WKV step, done")
+    print("              " + "".join(f"{v:>10.2f}" for v in tm.mean(0)))
+    # which CTAs finish last in S1 / S2
+    for k, nm in ((0, "S1"), (1, "S2")):
+        w = (raw[k + 5] [:, 1] - raw[k + 5][:, 0]) * 1e-3
+        order = np.argsort(-w)[:4]
+        print(nm, "layer 1 slowest CTAs:", [(int(c), round(float(w[c]), 2)) for c in order], "median", round(float(np.median(w)), 2))
+
+
 def prefill(layers=24, recipe="reduction", T=512, batch=1, model="1.5b", reps=3):
     """pp{T}: one stateful call over a prompt of T tokens, logits for the last position."""
     ck = synth.build_checkpoint(model, recipe, seed=0, device="cuda", n_layer=layers)
@@ -139,7 +206,13 @@ def main():
     pf = sub.add_parser("prefill")
     pf.add_argument("--layers", type=int, default=24); pf.add_argument("--recipe", default="reduction")
     pf.add_argument("--T", type=int, default=512); pf.add_argument("--batch", type=int, default=1)
+    tl = sub.add_parser("timeline")
+    tl.add_argument("--layers", type=int, default=24); tl.add_argument("--recipe", default="compression")
+    tl.add_argument("--model", default="1.5b")
     a = ap.parse_args()
+    if a.cmd == "timeline":
+        timeline(a.layers, a.recipe, a.model)
+        return
     if a.cmd == "gemv":
         gemv(a.layout, a.bits, a.rows, a.cols, a.n, a.launches)
     elif a.cmd == "decode":

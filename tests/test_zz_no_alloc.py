@@ -46,6 +46,7 @@ def _static(lib, dq, x, epilogue=0, resid=None):
     ("sb6", 6, 272, 4096),      # rows not a multiple of the 16-row tile
     ("sym", 6, 1024, 2048),
     ("sym", 8, 4096, 1024),     # largest row count served; too short for a K split
+    ("rtn", 8, 640, 4096),      # per-row int8
 ])
 def test_static_matches_allocating_entry_point_twice(cuda_lib, layout, bits, rows, cols):
     from rwkv_quant_b200.backends.cuda import ops
@@ -89,7 +90,7 @@ def test_static_refuses_what_does_not_fit(cuda_lib):
     no_records = _linear("sb6", 5, 256, 512, seed=3, relayout=False)
     rc, _ = _static(cuda_lib, no_records, x[:512])
     assert rc == E_DTYPE
-    rtn = _linear("rtn", 8, 256, 512, seed=4)
-    rc, _ = _static(cuda_lib, rtn, x[:512])
+    rtn4 = _linear("rtn", 4, 256, 512, seed=4)          # packed nibbles: no tensor-core layout
+    rc, _ = _static(cuda_lib, rtn4, x[:512])
     assert rc == E_DTYPE
     torch.cuda.synchronize()
