@@ -314,6 +314,34 @@ int rwkvq_decoder_status(rwkvq_decoder* d, void* stream);
 int rwkvq_relayout_meta(const rwkvq_qtensor* t, void* meta_out, void* stream);
 int rwkvq_relayout_planes(const rwkvq_qtensor* t, void* planes_out, void* stream);
 
+/*
+ * Tensor-parallel row split (2.9B variant): every rank computes the output rows it owns
+ * with rwkvq_gemv on a row slice of the tensor (any row range is a valid tensor in every
+ * layout: the file buffers slice on axis 0, cf. formats/reader.py:144-152) and the slices
+ * are exchanged by peer stores over NVLink.  No counterpart in the reference (single
+ * device); the exchange stands where an NCCL all-gather would.
+ *
+ *   rwkvq_tp_alloc / rwkvq_tp_free   zero-filled device buffer from cudaMalloc (set-up time
+ *       only), shareable with rwkvq_ipc_export
+ *   rwkvq_ipc_export / _open / _close  64-byte CUDA IPC handle of a buffer; mapping of a
+ *       peer's buffer into this process (peer access enabled lazily)
+ *   rwkvq_tp_allgather_store   src [count] fp32 = this rank's slice.  Stores it into
+ *       segment `rank` of dst_ptrs[p] for every rank p (host array of `world` device
+ *       pointers, entry `rank` being this rank's own buffer), raises flag_ptrs[p][rank] =
+ *       epoch, and waits until flag_ptrs[rank][0..world) all reached `epoch`.  `epoch` must
+ *       grow by one per exchange on every rank; use two destination buffers alternately
+ *       per exchange site.  After `max_spins` polls the kernel gives up, stores
+ *       RWKVQ_E_TIMEOUT in *status (device int, 0 = ok) and returns; count % 4 == 0.
+ */
+int rwkvq_tp_alloc(size_t bytes, void** out);
+int rwkvq_tp_free(void* p);
+int rwkvq_ipc_export(const void* dev_ptr, void* handle64);
+int rwkvq_ipc_open(const void* handle64, void** out);
+int rwkvq_ipc_close(void* p);
+int rwkvq_tp_allgather_store(const float* src, int count, float* const* dst_ptrs,
+                             unsigned int* const* flag_ptrs, int rank, int world, unsigned int epoch,
+                             int* status, long long max_spins, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

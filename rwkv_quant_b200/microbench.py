@@ -119,6 +119,70 @@ def timeline(layers=24, recipe="compression", model="1.5b", warm=6):
         print(nm, "layer 1 slowest CTAs:", [(int(c), round(float(w[c]), 2)) for c in order], "median", round(float(np.median(w)), 2))
 
 
+def tp_chain(model="2.9b", recipe="compression", exchange="p2p", iters=200):
+    """Row-split tensor-parallel GEMV chain of one layer (output projection, ffn key, ffn
+    value: three exchanges) plus the head, for the ranks of a torchrun launch (one process
+    per GPU).  Prints microseconds per layer chain and per head, max over ranks, as a CUDA
+    graph when the exchange allows it (peer stores) and as plain launches otherwise."""
+    import os
+
+    import torch.distributed as dist
+
+    from . import tp
+    rank, local = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+    world = dist.get_world_size()
+    dims = synth.MODEL_DIMS[model]
+    D, F, V = dims["n_embd"], dims["ffn"], dims["vocab"]
+    bits = {"compression": ("sb6", 5, "sb6", 4), "reduction": ("sym", 8, "sym", 6)}[recipe]
+
+    def lin(layout, b, rows, cols, seed):
+        g = torch.Generator().manual_seed(seed)
+        w = torch.randn(rows, cols, generator=g) * 0.02
+        fn = {"sb6": synth.quant_sb6, "sym": synth.quant_sym}[layout]
+        return ops.DeviceQT(fn("w", "g", w, b), device=dev)
+
+    out, key = lin(bits[0], bits[1], D, D, 1), lin(bits[2], bits[3], F, D, 2)
+    val, head = lin(bits[2], bits[3], D, F, 3), lin(bits[0], bits[1], V, D, 4)
+    g = tp.TPGroup(device=dev, exchange=exchange)
+    lo, lk = tp.TPRowLinear(g, out, "out", 64), tp.TPRowLinear(g, key, "key", 64)
+    lv, lh = tp.TPRowLinear(g, val, "value", 64), tp.TPRowLinear(g, head, "head", 64)
+    x = torch.randn(D, device=dev)
+
+    def layer(x):
+        a = lo(x, 2, x)
+        return lv(lk(a, 1), 2, a)
+
+    def timed(fn, n):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / n], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    t_layer = timed(lambda: layer(x), iters)
+    t_head = timed(lambda: lh(x), iters)
+    g.check()
+    wbytes = (out.nbytes_file() + key.nbytes_file() + val.nbytes_file())
+    if rank == 0:
+        print(f"tp chain {model} {recipe} world {world} exchange {exchange}: layer (o, key, value) {t_layer:.1f} us "
+              f"({wbytes / world / t_layer / 1e3:.0f} GB/s per GPU), head {t_head:.1f} us "
+              f"({head.nbytes_file() / world / t_head / 1e3:.0f} GB/s per GPU)", flush=True)
+    g.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def prefill(layers=24, recipe="reduction", T=512, batch=1, model="1.5b", reps=3):
     """pp{T}: one stateful call over a prompt of T tokens, logits for the last position."""
     ck = synth.build_checkpoint(model, recipe, seed=0, device="cuda", n_layer=layers)
@@ -209,7 +273,13 @@ def main():
     tl = sub.add_parser("timeline")
     tl.add_argument("--layers", type=int, default=24); tl.add_argument("--recipe", default="compression")
     tl.add_argument("--model", default="1.5b")
+    tpp = sub.add_parser("tp")
+    tpp.add_argument("--model", default="2.9b"); tpp.add_argument("--recipe", default="compression")
+    tpp.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"])
     a = ap.parse_args()
+    if a.cmd == "tp":
+        tp_chain(a.model, a.recipe, a.exchange)
+        return
     if a.cmd == "timeline":
         timeline(a.layers, a.recipe, a.model)
         return
