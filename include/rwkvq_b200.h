@@ -328,9 +328,10 @@ int rwkvq_relayout_planes(const rwkvq_qtensor* t, void* planes_out, void* stream
  *   rwkvq_tp_allgather_store   src [count] fp32 = this rank's slice.  Stores it into
  *       segment `rank` of dst_ptrs[p] for every rank p (host array of `world` device
  *       pointers, entry `rank` being this rank's own buffer), raises flag_ptrs[p][rank] =
- *       epoch, and waits until flag_ptrs[rank][0..world) all reached `epoch`.  `epoch` must
- *       grow by one per exchange on every rank; use two destination buffers alternately
- *       per exchange site.  After `max_spins` polls the kernel gives up, stores
+ *       epoch, and waits until flag_ptrs[rank][0..world) all reached the epoch = the number
+ *       of this exchange, kept in `epoch_ctr` (device, [world] words, zero at start, private
+ *       to the rank), so a captured CUDA graph can be replayed; every rank must issue the
+ *       same sequence of exchanges; use two destination buffers alternately per site.  After `max_spins` polls the kernel gives up, stores
  *       RWKVQ_E_TIMEOUT in *status (device int, 0 = ok) and returns; count % 4 == 0.
  */
 int rwkvq_tp_alloc(size_t bytes, void** out);
@@ -339,7 +340,7 @@ int rwkvq_ipc_export(const void* dev_ptr, void* handle64);
 int rwkvq_ipc_open(const void* handle64, void** out);
 int rwkvq_ipc_close(void* p);
 int rwkvq_tp_allgather_store(const float* src, int count, float* const* dst_ptrs,
-                             unsigned int* const* flag_ptrs, int rank, int world, unsigned int epoch,
+                             unsigned int* const* flag_ptrs, int rank, int world, unsigned int* epoch_ctr,
                              int* status, long long max_spins, void* stream);
 
 #ifdef __cplusplus

@@ -91,7 +91,7 @@ _PROTOS = {
     "rwkvq_ipc_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "rwkvq_ipc_close": (C.c_int, [C.c_void_p]),
     "rwkvq_tp_allgather_store": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
-                                           C.c_int, C.c_int, C.c_uint, C.c_void_p, C.c_longlong, C.c_void_p]),
+                                           C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p]),
     "rwkvq_decoder_workspace_bytes": (C.c_size_t, [C.POINTER(ModelStruct)]),
     "rwkvq_decoder_create": (C.c_int, [C.POINTER(ModelStruct), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                        C.POINTER(C.c_void_p), C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p,

@@ -6,8 +6,9 @@
 //   writes that slice into segment r of the destination buffer of EVERY rank (its own
 //   included), makes the stores visible system-wide, raises flag[r] = epoch in every
 //   rank's flag array, and then waits until all `world` flags of its own array have
-//   reached the epoch.  When the kernel completes, the local destination buffer holds the
-//   whole vector and later kernels of the stream may read it.
+//   reached the epoch (the number of this exchange, counted on the device).  When the
+//   kernel completes, the local destination buffer holds the whole vector and later
+//   kernels of the stream may read it.
 //
 // Every wait is bounded: after max_spins polls the kernel stores RWKVQ_E_TIMEOUT in the
 // status word and returns, so a rank that never arrives (crashed, or not launched) cannot
@@ -25,7 +26,7 @@ struct TpArgs {
     float* dst[kTpMaxWorld];            // peer-mapped destination buffers, index = rank
     unsigned int* flags[kTpMaxWorld];   // peer-mapped flag arrays [world]
     int count, rank, world;
-    unsigned int epoch;
+    unsigned int* epoch_ctr;            // [world] exchange counters of this rank, one per CTA
     long long max_spins;
     int* status;
 };
@@ -48,17 +49,18 @@ __global__ void __launch_bounds__(256) tp_allgather_store_kernel(const TpArgs a)
     for (int i = threadIdx.x; i < n4; i += blockDim.x)
         reinterpret_cast<float4*>(out)[i] = __ldcg(reinterpret_cast<const float4*>(a.src) + i);
     for (int i = (n4 << 2) + threadIdx.x; i < a.count; i += blockDim.x) out[i] = __ldcg(a.src + i);
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();                // the release below is cumulative over the CTA's stores
     if (threadIdx.x == 0) {
-        st_release_sys(a.flags[p] + a.rank, a.epoch);
+        // the exchange number lives on the device so that a captured graph can be replayed
+        const unsigned int epoch = a.epoch_ctr[p] + 1;
+        a.epoch_ctr[p] = epoch;
+        st_release_sys(a.flags[p] + a.rank, epoch);
         // now wait for rank p's slice in the local buffer
         const unsigned int* mine = a.flags[a.rank] + p;
         long long spins = 0;
         bool ok = true;
-        while (static_cast<int>(ld_acquire_sys(mine) - a.epoch) < 0) {
+        while (static_cast<int>(ld_acquire_sys(mine) - epoch) < 0) {
             if (++spins > a.max_spins) { ok = false; break; }
-            __nanosleep(64);
         }
         if (!ok) atomicExch(a.status, RWKVQ_E_TIMEOUT);
         __threadfence_system();
@@ -111,14 +113,14 @@ int rwkvq_ipc_close(void* p) {
 }
 
 int rwkvq_tp_allgather_store(const float* src, int count, float* const* dst_ptrs, unsigned int* const* flag_ptrs,
-                             int rank, int world, unsigned int epoch, int* status, long long max_spins, void* stream) {
-    RWKVQ_REQUIRE(src && dst_ptrs && flag_ptrs && status, RWKVQ_E_NULL, "rwkvq_tp_allgather_store: null pointer");
+                             int rank, int world, unsigned int* epoch_ctr, int* status, long long max_spins, void* stream) {
+    RWKVQ_REQUIRE(src && dst_ptrs && flag_ptrs && status && epoch_ctr, RWKVQ_E_NULL, "rwkvq_tp_allgather_store: null pointer");
     RWKVQ_REQUIRE(world >= 1 && world <= kTpMaxWorld && rank >= 0 && rank < world, RWKVQ_E_LIMIT,
                   "rwkvq_tp_allgather_store: rank %d of %d (at most %d ranks)", rank, world, kTpMaxWorld);
     RWKVQ_REQUIRE(count > 0 && aligned(src, 16), RWKVQ_E_ALIGN, "rwkvq_tp_allgather_store: src must be 16-byte aligned");
     RWKVQ_REQUIRE(max_spins > 0, RWKVQ_E_LIMIT, "rwkvq_tp_allgather_store: max_spins must be positive");
     TpArgs a{};
-    a.src = src; a.count = count; a.rank = rank; a.world = world; a.epoch = epoch; a.max_spins = max_spins;
+    a.src = src; a.count = count; a.rank = rank; a.world = world; a.epoch_ctr = epoch_ctr; a.max_spins = max_spins;
     a.status = status;
     for (int r = 0; r < world; ++r) {
         RWKVQ_REQUIRE(dst_ptrs[r] && flag_ptrs[r], RWKVQ_E_NULL, "rwkvq_tp_allgather_store: rank %d buffers missing", r);

@@ -147,38 +147,67 @@ def tp_chain(model="2.9b", recipe="compression", exchange="p2p", iters=200):
 
     out, key = lin(bits[0], bits[1], D, D, 1), lin(bits[2], bits[3], F, D, 2)
     val, head = lin(bits[2], bits[3], D, F, 3), lin(bits[0], bits[1], V, D, 4)
-    g = tp.TPGroup(device=dev, exchange=exchange)
-    lo, lk = tp.TPRowLinear(g, out, "out", 64), tp.TPRowLinear(g, key, "key", 64)
-    lv, lh = tp.TPRowLinear(g, val, "value", 64), tp.TPRowLinear(g, head, "head", 64)
     x = torch.randn(D, device=dev)
+    if exchange == "none":                     # every rank computes the whole matrices (no split)
+        class _Whole:
+            def __init__(self, dq): self.dq = dq
+            def __call__(self, v, epi=0, resid=None):
+                return ops.gemv(self.dq.bufs, self.dq.meta, v.reshape(1, -1), epi,
+                                None if resid is None else resid.reshape(1, -1))[0]
+        g = None
+        lo, lk, lv, lh = _Whole(out), _Whole(key), _Whole(val), _Whole(head)
+        split = 1
+    else:
+        g = tp.TPGroup(device=dev, exchange=exchange)
+        lo, lk = tp.TPRowLinear(g, out, "out", 64), tp.TPRowLinear(g, key, "key", 64)
+        lv, lh = tp.TPRowLinear(g, val, "value", 64), tp.TPRowLinear(g, head, "head", 64)
+        split = world
 
     def layer(x):
         a = lo(x, 2, x)
         return lv(lk(a, 1), 2, a)
 
     def timed(fn, n):
-        for _ in range(5):
+        """fn replayed n times as one CUDA graph (plain launches if capture is refused)."""
+        for _ in range(4):                     # an even count keeps the sites' buffer parity
             fn()
         torch.cuda.synchronize(); dist.barrier()
+        graph = None
+        try:
+            st = torch.cuda.Stream(device=dev)
+            st.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(st):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=st):
+                    fn(); fn()
+            torch.cuda.current_stream().wait_stream(st)
+        except Exception as e:                 # noqa: BLE001 - report and fall back
+            if rank == 0:
+                print("graph capture refused:", str(e)[:120])
+            graph = None
+        run = (lambda: graph.replay()) if graph is not None else (lambda: (fn(), fn()))
+        run(); torch.cuda.synchronize(); dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(n):
-            fn()
+        for _ in range(n // 2):
+            run()
         e1.record()
         torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / n], device=dev, dtype=torch.float64)
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / (2 * (n // 2))], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t)
 
     t_layer = timed(lambda: layer(x), iters)
     t_head = timed(lambda: lh(x), iters)
-    g.check()
+    if g is not None:
+        g.check()
     wbytes = (out.nbytes_file() + key.nbytes_file() + val.nbytes_file())
     if rank == 0:
         print(f"tp chain {model} {recipe} world {world} exchange {exchange}: layer (o, key, value) {t_layer:.1f} us "
-              f"({wbytes / world / t_layer / 1e3:.0f} GB/s per GPU), head {t_head:.1f} us "
-              f"({head.nbytes_file() / world / t_head / 1e3:.0f} GB/s per GPU)", flush=True)
-    g.close()
+              f"({wbytes / split / t_layer / 1e3:.0f} GB/s per GPU), head {t_head:.1f} us "
+              f"({head.nbytes_file() / split / t_head / 1e3:.0f} GB/s per GPU)", flush=True)
+    if g is not None:
+        g.close()
     dist.barrier()
     dist.destroy_process_group()
 
@@ -275,7 +304,7 @@ def main():
     tl.add_argument("--model", default="1.5b")
     tpp = sub.add_parser("tp")
     tpp.add_argument("--model", default="2.9b"); tpp.add_argument("--recipe", default="compression")
-    tpp.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"])
+    tpp.add_argument("--exchange", default="p2p", choices=["p2p", "nccl", "none"])
     a = ap.parse_args()
     if a.cmd == "tp":
         tp_chain(a.model, a.recipe, a.exchange)

@@ -67,6 +67,7 @@ class TPGroup:
             self._lib = _lib.load(check_device=True)
             self._check = _lib.check
             self.status = torch.zeros(1, dtype=torch.int32, device=device)
+            self._ctr = torch.zeros(8, dtype=torch.int32, device=device)      # exchange counters (device side)
             self._flags_ptrs = self._shared(4 * 8)          # [world] u32 arrival words, zero at start
 
     # ---- shared buffers ---------------------------------------------------------------
@@ -124,7 +125,7 @@ class TPGroup:
             from . import _lib
             flags = (C.c_void_p * self.world)(*self._flags_ptrs)
             self._check(self._lib.rwkvq_tp_allgather_store(local.data_ptr(), local.numel(), tabs[k], flags, self.rank,
-                                                           self.world, self._epoch, self.status.data_ptr(),
+                                                           self.world, self._ctr.data_ptr(), self.status.data_ptr(),
                                                            self.MAX_SPINS, _lib.stream_ptr()),
                         "rwkvq_tp_allgather_store")
         elif self.exchange == "nccl":
