@@ -148,6 +148,10 @@ int rwkvq_gemv(const rwkvq_qtensor* t, const void* x, int x_dtype, int N, int64_
  */
 size_t rwkvq_gemm_workspace_bytes(int M);
 size_t rwkvq_gemm_workspace_bytes_for(int M, int max_cols);
+/* Profiling aid: with a device buffer of 512 uint64 set, CTA (0,0,0) of every later rwkvq_gemm
+ * launch records global-timer nanoseconds of its pipeline events (slot map in the kernel source);
+ * NULL (the default) switches it off. */
+void rwkvq_gemm_set_trace(void* buf512);
 int rwkvq_gemm(const rwkvq_qtensor* t, const float* x, int M, int64_t ldx, float* y, int64_t ldy,
                int epilogue, const float* resid, void* workspace, size_t workspace_bytes, void* stream);
 

@@ -85,6 +85,7 @@ _PROTOS = {
                                C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
     "rwkvq_gemv_static": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_void_p,
                                     C.c_int, C.c_void_p, C.c_void_p]),
+    "rwkvq_gemm_set_trace": (None, [C.c_void_p]),
     "rwkvq_tp_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "rwkvq_tp_free": (C.c_int, [C.c_void_p]),
     "rwkvq_ipc_export": (C.c_int, [C.c_void_p, C.c_void_p]),

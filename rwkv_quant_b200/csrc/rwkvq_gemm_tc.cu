@@ -27,12 +27,14 @@
 
 namespace rwkvq {
 
-constexpr int kGmThreads = 256;
+constexpr int kGmProducers = 512;     // warps 0-15 unpack weights (and run the epilogue)
+constexpr int kGmThreads = 544;       // + warp 16: one lane issues the TMA loads and the MMAs
+constexpr int kGmPasses = 128 * 8 / kGmProducers;   // items (32 weights) per producer thread and macro-iteration
 constexpr int kGmRows = 128;          // output rows per CTA (UMMA M)
-constexpr int kGmK = 64;              // K per ring stage: one 128-byte swizzle row of fp16
-constexpr int kGmAStages = 2;         // unpacked weight slabs
-constexpr int kGmBStages = 4;         // activation slabs (TMA), issued kGmAhead iterations ahead
-constexpr int kGmAhead = 2;
+constexpr int kGmK = 64;              // K per slab: one 128-byte swizzle row of fp16
+constexpr int kGmSlabs = 4;           // slabs per macro-iteration (K = 256 = one super-block), 2 A stages
+constexpr int kGmMaxBSlots = 8;       // activation slabs in flight (TMA)
+__host__ __device__ constexpr int gemm_b_slots(int nt) { return nt >= 128 ? 6 : 8; }
 constexpr unsigned kGmSpinLimit = 1u << 24;
 
 struct GemmArgs {
@@ -47,6 +49,10 @@ struct GemmArgs {
     unsigned int* counters;   // [row tiles * token tiles] arrivals of the K slices (zeroed per call)
     float* partial;           // [CTA][NT][128] accumulator tiles of a K-split launch
     int M, epilogue;
+    // optional timeline of CTA (0,0,0), nanoseconds of the global timer: [0] start, [1] accumulator
+    // complete, [2] end; [8 + 4 i + {0 weights of macro-iteration i converted, 1 its stage was free,
+    // 2 issuer saw it full, 3 issuer issued its MMAs}]
+    unsigned long long* trace;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------
@@ -131,7 +137,13 @@ __device__ __forceinline__ uint32_t umma_idesc(int n) {
     return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kGmRows >> 4) << 24);
 }
 
-// ---- weight slab producer ---------------------------------------------------------
+// ---- weight producer ----------------------------------------------------------------
+// One macro-iteration covers K = 256 (one super-block): four 64-K slabs of the A operand.
+// The 128 rows x 8 items (32 columns each) of a macro-iteration are spread over the 256
+// producer threads so that the 8 lanes of a row read the row's packed super-block as one
+// contiguous run (128 B of nibble codes / 256 B of int8 codes, 32 B of each bit-plane, one
+// 16-byte scale record): item q of thread tid is (row 32 q + tid / 8, item tid % 8).
+
 // 4 code bytes of a word -> 4 fp16 = fp16(code * s + m), two HFMA2.  `bias` is the value
 // to subtract from (1024 + byte): 1024 for unsigned codes, 1056 / 1152 for codes stored
 // +32 / bytes biased by 128.
@@ -142,29 +154,34 @@ __device__ __forceinline__ uint2 bytes_to_half4(uint32_t w, __half2 bias, __half
     return make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
 }
 
-// Packed bytes of 32 consecutive weights of one row (thread = (row, 32-column half)).
+// Packed bytes of one item: 32 consecutive weights of one row.
 struct Packed {
     uint4 c0, c1;          // codes (c1: second 16 bytes of int8 layouts)
     uint32_t h, h2;        // bit-plane words of the 32 columns
-    uint32_t m0, m1, m2;   // sb6: 12 bytes of scale codes;  sym: m0 = two int8 scale codes
-    uint32_t dd;           // sb6: d | dm << 16;  sym: d
+    uint4 rec;             // sb6: 16-byte scale record (relayouted) or {m0, m1, m2, d | dm << 16} from the file
+                           // sym: .x = two int8 scale codes, .y = d
 };
 
-__device__ __forceinline__ void load_packed(Packed& p, const QView& t, int row_g, int c0) {
+// item `it` (0..7) of super-block `sbk` of row `row_g`
+__device__ __forceinline__ void load_packed(Packed& p, const QView& t, int row_g, int sbk, int it) {
     const size_t R = static_cast<size_t>(row_g);
     const int nsb = t.cols >> 8;
+    const int c0 = sbk * 256 + it * 32;
     p.h = p.h2 = 0;
     if (t.kind == RWKVQ_KIND_SB6) {
-        const int blk = c0 >> 5;
-        p.c0 = ld_stream_u128(t.codes + R * (t.cols >> 1) + blk * 16);
-        if (t.qh) p.h = ld_stream_u32(t.qh + R * (t.cols >> 3) + blk * 4);
-        if (t.qh2) p.h2 = ld_stream_u32(t.qh2 + R * (t.cols >> 3) + blk * 4);
-        const uint8_t* mp = t.qsqm + (R * nsb + (blk >> 3)) * 12;
-        p.m0 = ld_stream_u32(mp); p.m1 = ld_stream_u32(mp + 4); p.m2 = ld_stream_u32(mp + 8);
-        p.dd = ld_stream_u16(t.d + R * nsb + (blk >> 3)) | (ld_stream_u16(t.dm + R * nsb + (blk >> 3)) << 16);
+        p.c0 = ld_stream_u128(t.codes + R * (t.cols >> 1) + (c0 >> 1));
+        if (t.qh) p.h = ld_stream_u32(t.qh + R * (t.cols >> 3) + (c0 >> 3));
+        if (t.qh2) p.h2 = ld_stream_u32(t.qh2 + R * (t.cols >> 3) + (c0 >> 3));
+        if (t.dev_meta) {
+            p.rec = ld_stream_u128(t.dev_meta + (R * nsb + sbk) * 16);
+        } else {
+            const uint8_t* mp = t.qsqm + (R * nsb + sbk) * 12;
+            p.rec.x = ld_stream_u32(mp); p.rec.y = ld_stream_u32(mp + 4); p.rec.z = ld_stream_u32(mp + 8);
+            p.rec.w = ld_stream_u16(t.d + R * nsb + sbk) | (ld_stream_u16(t.dm + R * nsb + sbk) << 16);
+        }
     } else {
-        p.dd = ld_stream_u16(t.d + R * nsb + (c0 >> 8));
-        p.m0 = ld_stream_u16(t.qs + R * (t.cols >> 4) + (c0 >> 4));
+        p.rec.y = ld_stream_u16(t.d + R * nsb + sbk);
+        p.rec.x = ld_stream_u16(t.qs + R * (t.cols >> 4) + (c0 >> 4));
         if (t.bits == 8) {
             const uint8_t* cp = t.codes + R * t.cols + c0;
             p.c0 = ld_stream_u128(cp); p.c1 = ld_stream_u128(cp + 16);
@@ -176,12 +193,13 @@ __device__ __forceinline__ void load_packed(Packed& p, const QView& t, int row_g
     }
 }
 
-// 32 weights -> fp16, stored as 4 swizzled 16-byte chunks of row r of the A tile.
-__device__ __forceinline__ void convert_store(const Packed& p, const QView& t, int r, int half, int c0,
-                                              unsigned char* a_tile) {
+// 32 weights -> fp16, stored as 4 swizzled 16-byte chunks of row r: chunks 4*half .. +3 of
+// the slab (item / 2), half = item % 2.
+__device__ __forceinline__ void convert_store(const Packed& p, const QView& t, int r, int it, unsigned char* a_slab) {
     uint32_t bytes[8];                             // 32 codes as bytes, column order
     __half2 s2[2], m2[2], bias;                    // per 16 columns
     const uint32_t h = p.h, h2 = p.h2;
+    const int half = it & 1;
     if (t.kind == RWKVQ_KIND_SB6) {
         const uint32_t w[4] = {p.c0.x, p.c0.y, p.c0.z, p.c0.w};
 #pragma unroll
@@ -192,16 +210,28 @@ __device__ __forceinline__ void convert_store(const Packed& p, const QView& t, i
                            spread_nibble<5>((h2 >> (16 + 4 * i)) & 0xFu);
         }
         float s, m;
-        sb6_scale_min(p.m0, p.m1, p.m2, (c0 >> 5) & 7, half_bits_to_float(p.dd & 0xFFFFu),
-                      half_bits_to_float(p.dd >> 16), s, m);
+        if (t.dev_meta) {
+            // record word it/2: 6-bit scale codes of blocks 2(it/2), 2(it/2)+1, min codes (+31), one byte of d | dm << 16
+            const int tt = it >> 1;
+            const uint32_t w4 = (tt & 2) ? ((tt & 1) ? p.rec.w : p.rec.z) : ((tt & 1) ? p.rec.y : p.rec.x);
+            const uint32_t dd = __byte_perm(p.rec.x, p.rec.y, 0x0073) & 0xFFFFu;     // d
+            const uint32_t dm = __byte_perm(p.rec.z, p.rec.w, 0x0073) & 0xFFFFu;     // dm
+            const float qs = static_cast<float>((w4 >> (6 * half)) & 0x3Fu);
+            const float qm = static_cast<float>(static_cast<int>((w4 >> (12 + 6 * half)) & 0x3Fu) - 31);
+            s = fmaxf(half_roundtrip(__fmul_rn(qs, half_bits_to_float(dd))), 1e-8f);
+            m = half_roundtrip(__fmul_rn(qm, half_bits_to_float(dm)));
+        } else {
+            sb6_scale_min(p.rec.x, p.rec.y, p.rec.z, it, half_bits_to_float(p.rec.w & 0xFFFFu),
+                          half_bits_to_float(p.rec.w >> 16), s, m);
+        }
         s2[0] = s2[1] = __float2half2_rn(s);
         m2[0] = m2[1] = __float2half2_rn(m);
         bias = __float2half2_rn(1024.f);
     } else {                                       // sym: two blocks of 16
-        const float d = half_bits_to_float(p.dd);
+        const float d = half_bits_to_float(p.rec.y);
 #pragma unroll
         for (int b = 0; b < 2; ++b) {
-            const int q = static_cast<int8_t>((p.m0 >> (8 * b)) & 0xFFu);
+            const int q = static_cast<int8_t>((p.rec.x >> (8 * b)) & 0xFFu);
             s2[b] = __float2half2_rn(half_roundtrip(__fmul_rn(static_cast<float>(q), d)));
             m2[b] = __float2half2_rn(0.f);
         }
@@ -229,99 +259,156 @@ __device__ __forceinline__ void convert_store(const Packed& p, const QView& t, i
     for (int j = 0; j < 4; ++j) {                  // chunk j: columns 8j .. 8j+7 of the 32
         const uint2 a = bytes_to_half4(bytes[2 * j], bias, s2[j >> 1], m2[j >> 1]);
         const uint2 b = bytes_to_half4(bytes[2 * j + 1], bias, s2[j >> 1], m2[j >> 1]);
-        *reinterpret_cast<uint4*>(a_tile + sw128_offset(r, 4 * half + j)) = make_uint4(a.x, a.y, b.x, b.y);
+        *reinterpret_cast<uint4*>(a_slab + sw128_offset(r, 4 * half + j)) = make_uint4(a.x, a.y, b.x, b.y);
     }
 }
 
-template <int NT>   // tokens per CTA tile (UMMA N): 16, 32, 64, 128 or 256
+__device__ __forceinline__ void trace_mark(const GemmArgs& a, int slot) {
+    if (a.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && slot < 512) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        a.trace[slot] = t;
+    }
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+// Warps 0-15: producers (and the epilogue).  Warp 16, one lane: issues the activation TMA
+// loads and the MMAs.  Producers and issuer meet only through mbarriers:
+//   bar_afull[s]  one arrival per producer thread: the four A slabs of stage s are written
+//   bar_afree[s]  tcgen05.commit: the MMAs that read stage s have completed
+//   bar_bfull[k]  TMA bytes of activation slot k have landed;  bar_bfree[k]  its MMAs completed
+template <int NT>   // tokens per CTA tile (UMMA N): 16, 32, 64 or 128
 __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    constexpr int A_BYTES = kGmRows * 128, B_BYTES = NT * 128;
+    constexpr int SLAB_BYTES = kGmRows * 128, B_BYTES = NT * 128;
+    constexpr int BS = gemm_b_slots(NT);
     constexpr uint32_t TM_COLS = NT < 32 ? 32 : NT;
-    unsigned char* a_ring = smem;                               // [kGmAStages][A_BYTES]
-    unsigned char* b_ring = smem + kGmAStages * A_BYTES;        // [kGmBStages][B_BYTES]
-    __shared__ uint64_t bar_mma[kGmBStages];     // MMAs of iteration i (slot i % kGmBStages) have completed
-    __shared__ uint64_t bar_full[kGmBStages];    // the activation tile of iteration i has landed
-    __shared__ uint64_t bar_done;
+    unsigned char* a_ring = smem;                                        // [2 stages][4 slabs][SLAB_BYTES]
+    unsigned char* b_ring = smem + 2 * kGmSlabs * SLAB_BYTES;            // [BS][B_BYTES]
+    __shared__ uint64_t bar_afull[2], bar_afree[2], bar_bfull[kGmMaxBSlots], bar_bfree[kGmMaxBSlots], bar_done;
     __shared__ uint32_t s_tmem;
-    __shared__ int s_fail;
+    __shared__ volatile int s_fail;
+    __shared__ float s_unscale[NT];              // 1 / token scale (exact: the scales are powers of two)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const QView& t = a.t;
     const int row0 = blockIdx.x * kGmRows, tok0 = blockIdx.y * NT;
     const int KS = gridDim.z;
-    const int n_k = t.cols / kGmK / KS;                        // K iterations of this CTA's slice
-    const int k_first = blockIdx.z * n_k;
+    const int n_m = (t.cols >> 8) / KS;                         // macro-iterations (super-blocks) of this CTA's K slice
+    const int sb_first = blockIdx.z * n_m;
 
     if (tid == 0) {
-        for (int s = 0; s < kGmBStages; ++s) { mbar_init(&bar_mma[s], 1); mbar_init(&bar_full[s], 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&bar_afull[s], kGmProducers); mbar_init(&bar_afree[s], 1); }
+        for (int s = 0; s < BS; ++s) { mbar_init(&bar_bfull[s], 1); mbar_init(&bar_bfree[s], 1); }
         mbar_init(&bar_done, 1);
         s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) tmem_alloc(&s_tmem, TM_COLS);
+    if (tid < NT) s_unscale[tid] = (tok0 + tid < a.M) ? 1.0f / __ldcg(a.row_scale + tok0 + tid) : 0.f;
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
-    const uint32_t idesc = umma_idesc(NT);
+    if (tid == 0) trace_mark(a, 0);
 
-    const int pr = tid >> 1, ph = tid & 1;                     // producer: (row in tile, 32-column half)
-    const int row_g = min(row0 + pr, t.rows - 1);
-    Packed nxt, nxt2;                                          // packed bytes of iterations i+1, i+2 in flight
-    load_packed(nxt, t, row_g, k_first * kGmK + 32 * ph);
-    if (n_k > 1) load_packed(nxt2, t, row_g, (k_first + 1) * kGmK + 32 * ph);
-    auto issue_b = [&](int j) {                                // activation tile of iteration j (thread 0 only)
-        const int sb = j % kGmBStages;
-        mbar_expect_tx(&bar_full[sb], B_BYTES);
-        tma_load_2d(b_ring + sb * B_BYTES, &xmap, (k_first + j) * kGmK, tok0, &bar_full[sb]);
-    };
-    if (tid == 0)
-        for (int j = 0; j < kGmAhead && j < n_k; ++j) issue_b(j);
-    for (int i = 0; i < n_k; ++i) {
-        const Packed cur = nxt;
-        nxt = nxt2;
-        if (i + 2 < n_k) load_packed(nxt2, t, row_g, (k_first + i + 2) * kGmK + 32 * ph);
-        if (tid == 0 && i + kGmAhead < n_k && !s_fail) {
-            // slot of iteration i + kGmAhead was last read by the MMAs of iteration i + kGmAhead - kGmBStages
-            const int j = i + kGmAhead, jp = j - kGmBStages;
-            if (jp >= 0 && !mbar_wait_bounded(&bar_mma[jp % kGmBStages], (jp / kGmBStages) & 1)) s_fail = 1;
-            else issue_b(j);
-        }
-        unsigned char* a_tile = a_ring + (i % kGmAStages) * A_BYTES;
-        unsigned char* b_tile = b_ring + (i % kGmBStages) * B_BYTES;
-        if (i >= kGmAStages) {                                 // the MMAs of iteration i - kGmAStages read this A slab
-            const int ip = i - kGmAStages;
-            if (!mbar_wait_bounded(&bar_mma[ip % kGmBStages], (ip / kGmBStages) & 1)) s_fail = 1;
-        }
-        if (!s_fail) convert_store(cur, t, pr, ph, (k_first + i) * kGmK + 32 * ph, a_tile);
-        fence_async_smem();                                    // generic-proxy stores -> visible to the tensor core
-        tc_fence_before();
-        __syncthreads();
-        if (tid == 0 && !s_fail && !mbar_wait_bounded(&bar_full[i % kGmBStages], (i / kGmBStages) & 1)) s_fail = 1;
-        if (tid == 0 && !s_fail) {
-            tc_fence_after();
-            const uint64_t ad = umma_desc(smem_addr(a_tile)), bd = umma_desc(smem_addr(b_tile));
+    if (warp == kGmProducers / 32) {
+        // ------------------------------------------------------------------ issuer
+        if (lane == 0) {
+            // Activation slabs travel in pairs (one mbarrier, one commit per pair): a
+            // tcgen05.commit drains the tensor pipe (~700 cycles), so they are kept rare.
+            const uint32_t idesc = umma_idesc(NT);
+            constexpr int NP = BS / 2;                          // pair slots of the activation ring
+            const int n_pairs = n_m * kGmSlabs / 2;
+            auto issue_pair = [&](int q) -> bool {              // slabs 2q, 2q+1 of this CTA -> pair slot q % NP
+                const int ps = q % NP;
+                if (q >= NP && !mbar_wait_bounded(&bar_bfree[ps], ((q / NP) - 1) & 1)) return false;
+                mbar_expect_tx(&bar_bfull[ps], 2 * B_BYTES);
+                tma_load_2d(b_ring + (2 * ps) * B_BYTES, &xmap, (sb_first * kGmSlabs + 2 * q) * kGmK, tok0, &bar_bfull[ps]);
+                tma_load_2d(b_ring + (2 * ps + 1) * B_BYTES, &xmap, (sb_first * kGmSlabs + 2 * q + 1) * kGmK, tok0,
+                            &bar_bfull[ps]);
+                return true;
+            };
+            bool ok = true;
+            int issued = 0;
+            for (; issued < NP - 1 && issued < n_pairs && ok; ++issued) ok = issue_pair(issued);
+            for (int q = 0; q < n_pairs && ok; ++q) {
+                const int i = q >> 1, st = i & 1, ps = q % NP;
+                if ((q & 1) == 0 && !mbar_wait_bounded(&bar_afull[st], (i >> 1) & 1)) { ok = false; break; }
+                if ((q & 1) == 0) trace_mark(a, 8 + 4 * i + 2);
+                if (!mbar_wait_bounded(&bar_bfull[ps], (q / NP) & 1)) { ok = false; break; }
+                tc_fence_after();
 #pragma unroll
-            for (int k = 0; k < kGmK / 16; ++k)                // 32 bytes further along K per step
-                umma_f16(tmem, ad + 2 * k, bd + 2 * k, idesc, (i | k) ? 1u : 0u);
-            umma_commit(&bar_mma[i % kGmBStages]);
-            if (i == n_k - 1) umma_commit(&bar_done);
+                for (int s2 = 0; s2 < 2; ++s2) {
+                    const int sl = (q & 1) * 2 + s2;
+                    const uint64_t ad = umma_desc(smem_addr(a_ring + (st * kGmSlabs + sl) * SLAB_BYTES));
+                    const uint64_t bd = umma_desc(smem_addr(b_ring + (2 * ps + s2) * B_BYTES));
+#pragma unroll
+                    for (int k = 0; k < kGmK / 16; ++k)        // 32 bytes further along K per step
+                        umma_f16(tmem, ad + 2 * k, bd + 2 * k, idesc, (q | s2 | k) ? 1u : 0u);
+                }
+                umma_commit(&bar_bfree[ps]);
+                if (q & 1) { umma_commit(&bar_afree[st]); trace_mark(a, 8 + 4 * i + 3); }
+                // refill the pair slot consumed before this one while the tensor pipe is busy
+                if (issued < n_pairs) { ok = issue_pair(issued); ++issued; }
+            }
+            if (ok) umma_commit(&bar_done);
+            else s_fail = 1;
+        }
+    } else {
+        // ------------------------------------------------------------------ producers
+        constexpr int PR = kGmProducers / 8;                    // rows per pass
+        const int pit = tid & 7, prow = tid >> 3;               // item of the super-block, row within a pass
+        Packed P0[kGmPasses], P1[kGmPasses];                    // packed bytes of macro-iterations i, i + 1 (static roles)
+        auto load_all = [&](Packed (&P)[kGmPasses], int i) {
+#pragma unroll
+            for (int q = 0; q < kGmPasses; ++q)
+                load_packed(P[q], t, min(row0 + PR * q + prow, t.rows - 1), sb_first + i, pit);
+        };
+        auto produce = [&](Packed (&P)[kGmPasses], int i) {
+            const int st = i & 1;
+            // one lane per warp polls: 256 threads spinning on a shared-memory barrier starve the
+            // issuer's own barrier, TMA and MMA instructions
+            if (i >= 2) {
+                if (lane == 0 && !s_fail && !mbar_wait_bounded(&bar_afree[st], ((i >> 1) - 1) & 1)) s_fail = 1;
+                __syncwarp();
+            }
+            if (tid == 0) trace_mark(a, 8 + 4 * i + 1);
+            if (!s_fail) {
+                unsigned char* slab = a_ring + (st * kGmSlabs + (pit >> 1)) * SLAB_BYTES;
+#pragma unroll
+                for (int q = 0; q < kGmPasses; ++q) convert_store(P[q], t, PR * q + prow, pit, slab);
+            }
+            fence_async_smem();                                 // generic-proxy stores -> visible to the tensor core
+            mbar_arrive(&bar_afull[st]);
+            if (tid == 0) trace_mark(a, 8 + 4 * i);
+            if (i + 2 < n_m) load_all(P, i + 2);                // the registers are free again: two iterations ahead
+        };
+        load_all(P0, 0);
+        if (n_m > 1) load_all(P1, 1);
+        for (int i = 0; i < n_m; i += 2) {
+            produce(P0, i);
+            if (i + 1 < n_m) produce(P1, i + 1);
         }
     }
-    if (!s_fail && !mbar_wait_bounded(&bar_done, 0)) s_fail = 1;
+    // ---------------------------------------------------------------------- epilogue
+    if (lane == 0 && !s_fail && !mbar_wait_bounded(&bar_done, 0)) s_fail = 1;
+    __syncwarp();
     tc_fence_after();
     __syncthreads();
+    if (tid == 0) trace_mark(a, 1);
     if (s_fail) {
         if (tid == 0) atomicCAS(a.status, 0, RWKVQ_E_TIMEOUT);
-    } else {
-        // warp w reads lanes 32*(w%4) .. +31 (= output rows); warps w and w+4 split the tokens
+    } else if (warp < kGmProducers / 32) {
+        // warp w reads lanes 32*(w%4) .. +31 (= output rows); the warps that share a lane group split the tokens
         const int rl = (warp & 3) * 32 + lane, row = row0 + rl;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
         auto finish = [&](float r, int tok) {
             if (tok < a.M && row < t.rows) {
-                r = r / __ldcg(a.row_scale + tok);
+                r = r * s_unscale[tok - tok0];
                 const long long idx = tok * a.ldy + row;
                 if (a.epilogue == RWKVQ_EPI_RELU2) { r = fmaxf(r, 0.f); r = r * r; }
                 else if (a.epilogue == RWKVQ_EPI_ADD) r = __fadd_rn(r, __ldcg(a.resid + idx));
@@ -329,7 +416,7 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
             }
         };
         if (KS == 1) {
-            for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += 16) {
+            for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += kGmProducers / 16) {
                 float v[8];
                 tmem_ld8(lane_base + c0, v);
 #pragma unroll
@@ -339,55 +426,69 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
             // this CTA's accumulator tile goes to its scratch slot [token][row]
             const size_t tile_id = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
             float* mine = a.partial + (tile_id * KS + blockIdx.z) * (NT * kGmRows);
-            for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += 16) {
+            for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += kGmProducers / 16) {
                 float v[8];
                 tmem_ld8(lane_base + c0, v);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) __stcg(mine + (c0 + j) * kGmRows + rl, v[j]);
             }
             __threadfence();
-            __syncthreads();
-            __shared__ unsigned int s_last;
-            if (tid == 0) s_last = (atomicAdd(a.counters + tile_id, 1u) == static_cast<unsigned int>(KS - 1));
-            __syncthreads();
-            if (s_last) {                           // last K slice to arrive adds the tiles in slice order
-                __threadfence();
-                const float* base = a.partial + tile_id * KS * (NT * kGmRows);
-                // warps w and w+4 take alternate groups of 8 tokens; 8 x KS loads are in flight per
-                // thread and every token's slices are added in slice order
-                for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += 16) {
-                    float r[8];
+        }
+    }
+    if (KS > 1 && !s_fail) {                        // block-uniform: every thread takes the same path
+        __shared__ unsigned int s_last;
+        const size_t tile_id = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
+        __syncthreads();
+        if (tid == 0) s_last = (atomicAdd(a.counters + tile_id, 1u) == static_cast<unsigned int>(KS - 1));
+        __syncthreads();
+        if (s_last && warp < kGmProducers / 32) {   // last K slice to arrive adds the tiles in slice order
+            __threadfence();
+            const int rl = (warp & 3) * 32 + lane, row = row0 + rl;
+            const float* base = a.partial + tile_id * KS * (NT * kGmRows);
+            // warps of one lane group take alternate groups of 8 tokens; 8 x 4 loads are in flight per
+            // thread and every token's slices are added in slice order
+            for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += kGmProducers / 16) {
+                float r[8];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) r[j] = 0.f;
-                    for (int z0 = 0; z0 < KS; z0 += 4) {
-                        float pv[4][8];
+                for (int j = 0; j < 8; ++j) r[j] = 0.f;
+                for (int z0 = 0; z0 < KS; z0 += 4) {
+                    float pv[4][8];
 #pragma unroll
-                        for (int u = 0; u < 4; ++u)
+                    for (int u = 0; u < 4; ++u)
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                pv[u][j] = z0 + u < KS
-                                               ? __ldcg(base + (static_cast<size_t>(z0 + u) * NT + c0 + j) * kGmRows + rl)
-                                               : 0.f;
+                        for (int j = 0; j < 8; ++j)
+                            pv[u][j] = z0 + u < KS
+                                           ? __ldcg(base + (static_cast<size_t>(z0 + u) * NT + c0 + j) * kGmRows + rl)
+                                           : 0.f;
 #pragma unroll
-                        for (int u = 0; u < 4; ++u)
+                    for (int u = 0; u < 4; ++u)
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) r[j] += pv[u][j];
+                        for (int j = 0; j < 8; ++j) r[j] += pv[u][j];
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int tok = tok0 + c0 + j;
+                    if (tok < a.M && row < t.rows) {
+                        float v = r[j] * s_unscale[tok - tok0];
+                        const long long idx = tok * a.ldy + row;
+                        if (a.epilogue == RWKVQ_EPI_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
+                        else if (a.epilogue == RWKVQ_EPI_ADD) v = __fadd_rn(v, __ldcg(a.resid + idx));
+                        a.y[idx] = v;
                     }
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) finish(r[j], tok0 + c0 + j);
                 }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) trace_mark(a, 2);
     if (warp == 0) tmem_dealloc(tmem, TM_COLS);
 }
 
 // Pre-pass, one CTA per token: power-of-two scale so that |x * scale| <= 2^14, and the
 // scaled row as fp16 (the tensor the TMA loads read).
 __global__ void __launch_bounds__(256) row_scale_kernel(const float* x, long long ldx, int cols, float* scale,
-                                                        __half* x16) {
+                                                        __half* x16, long long pitch) {
     __shared__ float red[8];
     const float* row = x + blockIdx.x * ldx;
     float amax = 0.f;
@@ -402,7 +503,7 @@ __global__ void __launch_bounds__(256) row_scale_kernel(const float* x, long lon
     if (amax > 0.f && amax < INFINITY) frexpf(amax, &e);
     const float sc = ldexpf(1.f, 14 - e);
     if (threadIdx.x == 0) scale[blockIdx.x] = sc;
-    __half2* out = reinterpret_cast<__half2*>(x16 + static_cast<size_t>(blockIdx.x) * cols);
+    __half2* out = reinterpret_cast<__half2*>(x16 + static_cast<size_t>(blockIdx.x) * pitch);
     for (int i = threadIdx.x; i < (cols >> 1); i += 256) {
         const float2 v = __ldcg(reinterpret_cast<const float2*>(row) + i);
         out[i] = __floats2half2_rn(v.x * sc, v.y * sc);
@@ -414,7 +515,12 @@ __global__ void __launch_bounds__(256) row_scale_kernel(const float* x, long lon
 using namespace rwkvq;
 
 namespace {
-constexpr int kGemmResident = 2 * 148;
+unsigned long long* g_gemm_trace = nullptr;      // set by rwkvq_gemm_set_trace (profiling aid)
+constexpr int kGemmResident = 2 * 148;     // accumulator tiles the K-split scratch holds
+constexpr int kGemmSms = 148;
+// Row pitch of the fp16 activation copy: 128 bytes more than the row, so that the 128 rows
+// of a TMA box do not all map to the same L2 slice (a power-of-two pitch does).
+inline size_t x16_pitch(int cols) { return static_cast<size_t>(cols) + 64; }
 constexpr size_t kGemmHeader = 8192;        // status word + arrival counters (zeroed every call)
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -438,7 +544,7 @@ int make_xmap(CUtensorMap* map, const __half* x16, int M, int cols, int nt) {
     EncodeTiledFn enc = encode_tiled();
     RWKVQ_REQUIRE(enc != nullptr, RWKVQ_E_ARCH, "rwkvq_gemm: cuTensorMapEncodeTiled is not available");
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(M)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * sizeof(__half)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(x16_pitch(cols)) * sizeof(__half)};
     const cuuint32_t box[2] = {kGmK, static_cast<cuuint32_t>(nt)};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(x16), dims, strides, box, estr,
@@ -453,7 +559,7 @@ int launch_gemm(GemmArgs& a, int rows, int cols, int M, float* partial, const __
     CUtensorMap xmap;
     int mrc = make_xmap(&xmap, x16, M, cols, NT);
     if (mrc) return mrc;
-    const size_t smem = static_cast<size_t>(kGmAStages) * kGmRows * 128 + static_cast<size_t>(kGmBStages) * NT * 128 + 1024;
+    const size_t smem = static_cast<size_t>(2 * kGmSlabs) * kGmRows * 128 + static_cast<size_t>(gemm_b_slots(NT)) * NT * 128 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -461,10 +567,10 @@ int launch_gemm(GemmArgs& a, int rows, int cols, int M, float* partial, const __
         if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "rwkvq_gemm: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    const int rt = (rows + kGmRows - 1) / kGmRows, tt = (M + NT - 1) / NT, n_k = cols / kGmK;
-    // K slices across CTAs until about one wave of CTAs is reached (power of two, >= 2 iterations each)
+    const int rt = (rows + kGmRows - 1) / kGmRows, tt = (M + NT - 1) / NT, n_m = cols / 256;
+    // K slices across CTAs while the grid is below one CTA per SM (power of two, >= 2 super-blocks each)
     int KS = 1;
-    while (rt * tt * KS * 2 <= kGemmResident && n_k % (KS * 2) == 0 && n_k / (KS * 2) >= 2 &&
+    while (rt * tt * KS < kGemmSms && n_m % (KS * 2) == 0 && n_m / (KS * 2) >= 2 && rt * tt * KS * 2 <= kGemmResident &&
            rt * tt <= static_cast<int>((kGemmHeader - 256) / sizeof(unsigned int)))
         KS *= 2;
     a.partial = partial;
@@ -483,8 +589,10 @@ static size_t gemm_ws_x16_off(size_t m) {
 }
 size_t rwkvq_gemm_workspace_bytes_for(int M, int max_cols) {
     const size_t m = static_cast<size_t>(M < 1 ? 1 : M);
-    return gemm_ws_x16_off(m) + sizeof(__half) * m * static_cast<size_t>(max_cols) + 256;
+    return gemm_ws_x16_off(m) + sizeof(__half) * m * (static_cast<size_t>(max_cols) + 64) + 256;
 }
+void rwkvq_gemm_set_trace(void* buf512) { g_gemm_trace = static_cast<unsigned long long*>(buf512); }
+
 size_t rwkvq_gemm_workspace_bytes(int M) { return rwkvq_gemm_workspace_bytes_for(M, 16384); }
 
 int rwkvq_gemm(const rwkvq_qtensor* t, const float* x, int M, int64_t ldx, float* y, int64_t ldy, int epilogue,
@@ -513,8 +621,9 @@ int rwkvq_gemm(const rwkvq_qtensor* t, const float* x, int M, int64_t ldx, float
     float* partial = reinterpret_cast<float*>(ws + gemm_ws_partial_off(M));
     __half* x16 = reinterpret_cast<__half*>(ws + gemm_ws_x16_off(M));
     a.row_scale = scale;
+    a.trace = g_gemm_trace;
     cudaMemsetAsync(ws, 0, kGemmHeader, s);
-    row_scale_kernel<<<M, 256, 0, s>>>(x, ldx, t->cols, scale, x16);
+    row_scale_kernel<<<M, 256, 0, s>>>(x, ldx, t->cols, scale, x16, static_cast<long long>(x16_pitch(t->cols)));
     if (M <= 16) rc = launch_gemm<16>(a, t->rows, t->cols, M, partial, x16, s);
     else if (M <= 32) rc = launch_gemm<32>(a, t->rows, t->cols, M, partial, x16, s);
     else if (M <= 64) rc = launch_gemm<64>(a, t->rows, t->cols, M, partial, x16, s);

@@ -212,6 +212,60 @@ def tp_chain(model="2.9b", recipe="compression", exchange="p2p", iters=200):
     dist.destroy_process_group()
 
 
+def gemm_sweep(recipe="compression", Ms=(64, 512, 8192), reps=20):
+    """rwkvq_gemm (pre-pass + tensor-core kernel) on the four linear shapes of a 1.5B layer
+    and the head: microseconds per call (CUDA-graph replay, so that host time does not
+    count) and TFLOP/s = 2 * M * OUT * IN / time."""
+    lay = {"compression": [("sb6", 5, 2048, 2048), ("sb6", 4, 8192, 2048), ("sb6", 4, 2048, 8192), ("sb6", 5, 65536, 2048)],
+           "reduction": [("sym", 8, 2048, 2048), ("sym", 6, 8192, 2048), ("sym", 6, 2048, 8192), ("sym", 8, 65536, 2048)]}[recipe]
+    for layout, bits, rows, cols in lay:
+        dq = _tensor(layout, bits, rows, cols)
+        for M in Ms:
+            if rows == 65536 and M > 512:
+                continue                                   # the head sees the last token of each sequence only
+            x = torch.randn(M, cols, device="cuda")
+            ops.gemm(dq, x, check=True)
+            st = torch.cuda.Stream()
+            st.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(st):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=st):
+                    y = ops.gemm(dq, x)
+            torch.cuda.current_stream().wait_stream(st)
+            g.replay(); torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                g.replay()
+            e1.record(); torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / reps
+            print(f"gemm {layout}@{bits} [{rows},{cols}] M={M}: {us:8.1f} us  {2.0 * M * rows * cols / us / 1e6:7.1f} TFLOP/s", flush=True)
+
+
+def gemm_timeline(layout="sb6", bits=5, rows=2048, cols=2048, M=8192):
+    """Pipeline timeline of CTA (0,0,0) of one rwkvq_gemm launch: per macro-iteration (K = 256)
+    when its weight stage was free, converted, seen full by the issuer and issued."""
+    import numpy as np
+    dq = _tensor(layout, bits, rows, cols)
+    x = torch.randn(M, cols, device="cuda")
+    ops.gemm(dq, x, check=True)
+    buf = torch.zeros(512, dtype=torch.int64, device="cuda")
+    lib = _lib.load()
+    lib.rwkvq_gemm_set_trace(buf.data_ptr())
+    ops.gemm(dq, x)
+    torch.cuda.synchronize()
+    lib.rwkvq_gemm_set_trace(None)
+    t = buf.cpu().numpy().astype(np.float64)
+    t0 = t[0]
+    n = sum(1 for i in range(120) if t[8 + 4 * i] > 0)
+    us = lambda v: (v - t0) / 1e3
+    print(f"gemm timeline {layout}@{bits} [{rows},{cols}] M={M}: accumulator complete {us(t[1]):.2f} us, CTA end {us(t[2]):.2f} us, {n} macro-iterations")
+    print("  i  stage free  converted  issuer full  issued")
+    for i in range(n):
+        r = t[8 + 4 * i: 12 + 4 * i]
+        print(f"{i:3d} {us(r[1]) if r[1] else 0:10.2f} {us(r[0]):10.2f} {us(r[2]):12.2f} {us(r[3]):7.2f}")
+
+
 def prefill(layers=24, recipe="reduction", T=512, batch=1, model="1.5b", reps=3):
     """pp{T}: one stateful call over a prompt of T tokens, logits for the last position."""
     ck = synth.build_checkpoint(model, recipe, seed=0, device="cuda", n_layer=layers)
@@ -305,7 +359,18 @@ def main():
     tpp = sub.add_parser("tp")
     tpp.add_argument("--model", default="2.9b"); tpp.add_argument("--recipe", default="compression")
     tpp.add_argument("--exchange", default="p2p", choices=["p2p", "nccl", "none"])
+    gt = sub.add_parser("gemm-timeline")
+    gt.add_argument("--M", type=int, default=8192); gt.add_argument("--rows", type=int, default=2048)
+    gt.add_argument("--cols", type=int, default=2048)
+    gs = sub.add_parser("gemm-sweep")
+    gs.add_argument("--recipe", default="compression")
     a = ap.parse_args()
+    if a.cmd == "gemm-timeline":
+        gemm_timeline("sb6", 5, a.rows, a.cols, a.M)
+        return
+    if a.cmd == "gemm-sweep":
+        gemm_sweep(a.recipe)
+        return
     if a.cmd == "tp":
         tp_chain(a.model, a.recipe, a.exchange)
         return
