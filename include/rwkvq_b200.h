@@ -224,6 +224,27 @@ int rwkvq_wkv_tail(const float* wkv, const float* r, const float* k, const float
                    const float* ln_w, const float* ln_b, const float* g, float* out, int N, int H,
                    int head_size, float eps, void* stream);
 
+/*
+ * Glue of the sequence (prefill) path for all B*T tokens of a call; the single-token forms
+ * live inside rwkvq_decode_step.
+ *   rwkvq_seq_ln_shift_mix  xn = LayerNorm(x[b,t]); prev = xn[b,t-1] (t = 0: shift_in[b] or
+ *       zeros when NULL); out[m][b,t] = xn + (prev - xn) * mix[m] for m < n_mix (1 or 6);
+ *       shift_out[b] = xn[b,T-1].  Stands behind _layer_norm + _token_shift_stateful + the lerp
+ *       stack (quant_model.py:281-301, 648-651, 803-806).  x [B,T,D], out [n_mix,B,T,D] fp32.
+ *   rwkvq_seq_tmix_pre  decay, gates, kk, k and v updates feeding the WKV-7 scan
+ *       (quant_model.py:700-712): w = exp(-0.606531 sigmoid(yw + w0)), a = sigmoid(ya + a0),
+ *       kk = l2norm per head of k * k_k, k2 = k (1 + (a - 1) k_a),
+ *       v2 = v + (v_first - v) sigmoid(yv + v0) (yv, v_first, v0 NULL on layer 0: v2 = v),
+ *       neg_kk = -kk, kk_a = kk * a.  All [n_tokens, H * 64] fp32.
+ */
+int rwkvq_seq_ln_shift_mix(const float* x, const float* ln_w, const float* ln_b, const float* shift_in,
+                           const float* mix, int n_mix, float* out, float* shift_out, int B, int T, int D,
+                           void* stream);
+int rwkvq_seq_tmix_pre(const float* k, const float* v, const float* yw, const float* ya, const float* yv,
+                       const float* v_first, const float* w0, const float* a0, const float* v0,
+                       const float* k_k, const float* k_a, float* w, float* k2, float* v2, float* neg_kk,
+                       float* kk_a, int64_t n_tokens, int H, void* stream);
+
 /* One layer / one model as device pointers; dense vectors are fp32 [D] already in the
  * reference's load-time precision (quant_model.py:128-154). LoRA tensors are stored [in, out]. */
 typedef struct rwkvq_layer {

@@ -222,6 +222,36 @@ def gemv_fused(dqts: Sequence[DeviceQT], xstack: torch.Tensor) -> torch.Tensor:
     return y
 
 
+def seq_ln_shift_mix(x: torch.Tensor, ln_w, ln_b, shift_in: Optional[torch.Tensor], mix: torch.Tensor):
+    """x [B, T, D] fp32 -> (out [n_mix, B, T, D], new shift state [B, 1, D]); mix [n_mix, D] or [D]."""
+    _require_cuda(x, shift_in, mix)
+    B, T, D = x.shape
+    x = x.float().contiguous()
+    mix2 = mix.reshape(-1, D).contiguous()
+    out = torch.empty((mix2.shape[0], B, T, D), dtype=torch.float32, device=x.device)
+    new_shift = torch.empty((B, 1, D), dtype=torch.float32, device=x.device)
+    sin = None if shift_in is None else shift_in.float().contiguous()
+    _lib.check(_lib.load().rwkvq_seq_ln_shift_mix(x.data_ptr(), ln_w.data_ptr(), ln_b.data_ptr(), _lib.ptr(sin),
+                                                  mix2.data_ptr(), mix2.shape[0], out.data_ptr(), new_shift.data_ptr(),
+                                                  B, T, D, _lib.stream_ptr()), "rwkvq_seq_ln_shift_mix")
+    return out, new_shift
+
+
+def seq_tmix_pre(k, v, yw, ya, yv, v_first, w0, a0, v0, k_k, k_a, n_head: int):
+    """[N, D] fp32 inputs -> (w, k2, v2, -kk, kk*a), each [N, D]; yv / v_first None on layer 0."""
+    _require_cuda(k, v, yw, ya)
+    k, v, yw, ya = (t.contiguous() for t in (k, v, yw, ya))
+    if yv is not None:
+        yv, v_first = yv.contiguous(), v_first.contiguous()
+    outs = [torch.empty_like(k) for _ in range(5)]
+    _lib.check(_lib.load().rwkvq_seq_tmix_pre(k.data_ptr(), v.data_ptr(), yw.data_ptr(), ya.data_ptr(), _lib.ptr(yv),
+                                              _lib.ptr(v_first), w0.data_ptr(), a0.data_ptr(),
+                                              _lib.ptr(v0) if yv is not None else None, k_k.data_ptr(), k_a.data_ptr(),
+                                              *[o.data_ptr() for o in outs], k.shape[0], n_head, _lib.stream_ptr()),
+               "rwkvq_seq_tmix_pre")
+    return outs
+
+
 def as_rows(x: torch.Tensor, n_in: int):
     """[..., IN] -> contiguous [N, IN] of a supported dtype plus the leading shape."""
     if x.shape[-1] != n_in:

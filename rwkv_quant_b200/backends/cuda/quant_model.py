@@ -198,47 +198,41 @@ class QuantRWKV7:
         if x.shape[0] <= 8:
             return ops.gemv_t(dq.bufs, dq.meta, x.contiguous(), act, True)
         w = self._lora_dense.get(id(dq))
-        if w is None:
-            w = ops.dequant(dq.bufs, dq.meta, torch.float32, True).half().float()
+        if w is None:                                   # values are exactly fp16 by the loader's policy
+            w = ops.dequant(dq.bufs, dq.meta, torch.float32, True).half()
             self._lora_dense[id(dq)] = w
-        y = x @ w
+        # x = hi + lo with both halves fp16: two tensor-core GEMMs with fp32 accumulation give
+        # x @ W to ~2^-22 relative (a plain fp32 GEMM runs on the SIMT pipes, 10x slower)
+        hi = x.half()
+        lo = (x - hi.float()).half()
+        y = torch.mm(hi, w, out_dtype=torch.float32) + torch.mm(lo, w, out_dtype=torch.float32)
         return torch.tanh(y) if act == 1 else torch.sigmoid(y) if act == 2 else y
-
-    @staticmethod
-    def _shift(x, prev):
-        return torch.cat([prev, x[:, :-1]], dim=1), x[:, -1:].contiguous()
 
     def _block_seq(self, i, L, x, v_first, state):
         B, T, D = x.shape
         H, S = self.n_head, self.head_size
         wkv, ts, cs = state
-        lin = lambda dq, t, **kw: self._linear(dq, t.reshape(B * T, -1).contiguous(), **kw)
         lora = lambda dq, t, act=0: self._lora_seq(dq, t.reshape(B * T, -1), act)
-        xn = F.layer_norm(x, (D,), *L.ln1)
-        shifted, ts = self._shift(xn, ts)
-        xx = shifted - xn
-        xr, xw, xk, xv, xa, xg = (xn + xx * L.x_mix[j] for j in range(6))
-        r, k, v = lin(L.Wr, xr), lin(L.Wk, xk), lin(L.Wv, xv)
+        N = B * T
+        xs, ts = ops.seq_ln_shift_mix(x, L.ln1[0], L.ln1[1], ts, L.x_mix)          # LN1 + shift + 6 lerps
+        xr, xw, xk, xv, xa, xg = (xs[j].reshape(N, D) for j in range(6))
+        r, k, v = self._linear(L.Wr, xr), self._linear(L.Wk, xk), self._linear(L.Wv, xv)
         y_w = lora(L.w2, lora(L.w1, xw, 1))
         y_a = lora(L.a2, lora(L.a1, xa))
         g = lora(L.g2, lora(L.g1, xg, 2))
-        w = torch.exp(_DECAY * torch.sigmoid(y_w + L.w0))
-        a = torch.sigmoid(y_a + L.a0)
-        kk = (k * L.k_k).reshape(B, T, H, S)
-        kk = kk / torch.sqrt((kk * kk).sum(-1, keepdim=True) + 1e-12)
-        k = k * (1.0 + (a - 1.0) * L.k_a)
         if i == 0:
-            v_first = v
+            v_first, y_v = v, None
         else:
-            v = v + (v_first - v) * torch.sigmoid(lora(L.v2, lora(L.v1, xv)) + L.v0)
+            y_v = lora(L.v2, lora(L.v1, xv))
+        w, k, v2, na, nb = ops.seq_tmix_pre(k, v, y_w, y_a, y_v, None if i == 0 else v_first, L.w0, L.a0, L.v0,
+                                            L.k_k, L.k_a, H)
         r4 = lambda t: t.reshape(B, T, H, S)
-        out, wkv = wkv7_infer(r4(r), r4(w), r4(k), r4(v), -kk, kk * r4(a), wkv)
-        og = wkv_tail(out, r, k, v, L.r_k, L.lnx[0], L.lnx[1], g, H, S)
-        x = lin(L.Wo, og, epilogue=_lib.EPI_ADD, resid=x.reshape(B * T, D).contiguous()).reshape(B, T, D)
-        xn = F.layer_norm(x, (D,), *L.ln2)
-        shifted, cs = self._shift(xn, cs)
-        h = lin(L.Wfk, xn + (shifted - xn) * L.ffn_x_k, epilogue=_lib.EPI_RELU2)
-        x = self._linear(L.Wfv, h, epilogue=_lib.EPI_ADD, resid=x.reshape(B * T, D).contiguous()).reshape(B, T, D)
+        out, wkv = wkv7_infer(r4(r), r4(w), r4(k), r4(v2), r4(na), r4(nb), wkv)
+        og = wkv_tail(out, r, k, v2, L.r_k, L.lnx[0], L.lnx[1], g, H, S)
+        x = self._linear(L.Wo, og.reshape(N, D), epilogue=_lib.EPI_ADD, resid=x.reshape(N, D).contiguous())
+        xk2, cs = ops.seq_ln_shift_mix(x.reshape(B, T, D), L.ln2[0], L.ln2[1], cs, L.ffn_x_k)     # LN2 + shift + lerp
+        h = self._linear(L.Wfk, xk2.reshape(N, D), epilogue=_lib.EPI_RELU2)
+        x = self._linear(L.Wfv, h, epilogue=_lib.EPI_ADD, resid=x).reshape(B, T, D)
         return x, v_first, (wkv, ts, cs)
 
     def _embed(self, idx):

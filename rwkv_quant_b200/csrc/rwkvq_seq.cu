@@ -1,0 +1,153 @@
+// Glue kernels of the sequence (prefill) path, T > 1: what the decode step does inside
+// ln_shift_mix_kernel / tmix_core_kernel for one token, for all B*T tokens of a call.
+//
+//   seq_ln_shift_mix   xn = LN(x[b,t]);  prev = xn[b,t-1] (t = 0: the carried shift state, zeros
+//                      for a fresh stream);  out[m][b,t] = xn + (prev - xn) * mix[m];
+//                      new shift state = xn[b,T-1]            (quant_model.py:281-301, 648-651)
+//   seq_tmix_pre       decay w = exp(-0.606531 sigmoid(yw + w0)), gate a = sigmoid(ya + a0),
+//                      kk = l2norm_head(k * k_k), k' = k (1 + (a - 1) k_a),
+//                      v' = v + (v_first - v) sigmoid(yv + v0) (layers > 0); emits w, k', v',
+//                      -kk and kk*a, the operands of the WKV-7 scan       (quant_model.py:700-712)
+#include "rwkvq_decode_parts.cuh"
+
+namespace rwkvq {
+
+constexpr int kSeqThreads = 256;
+constexpr int kSeqPer = 16;          // D <= 4096
+
+// One CTA per token.  The previous token's normalised row is recomputed here (same code,
+// same bits as the CTA that owns it), so tokens do not depend on one another.
+template <int NMIX>
+__global__ void __launch_bounds__(kSeqThreads) seq_ln_shift_mix_kernel(const float* __restrict__ x,
+                                                                       const float* __restrict__ ln_w,
+                                                                       const float* __restrict__ ln_b,
+                                                                       const float* __restrict__ shift_in,
+                                                                       const float* __restrict__ mix,
+                                                                       float* __restrict__ out,
+                                                                       float* __restrict__ shift_out, int T, int D,
+                                                                       long long n_tokens) {
+    __shared__ float red[kSeqThreads / 32];
+    const long long tok = blockIdx.x;
+    const int b = static_cast<int>(tok / T), t = static_cast<int>(tok % T);
+    const float* row = x + tok * D;
+    float v[kSeqPer], pv[kSeqPer], lw[kSeqPer], lb[kSeqPer];
+#pragma unroll
+    for (int i = 0; i < kSeqPer; ++i) {
+        const int d = threadIdx.x + i * kSeqThreads;
+        const bool ok = d < D;
+        v[i] = ok ? row[d] : 0.f;
+        pv[i] = !ok ? 0.f : (t > 0 ? row[d - D] : (shift_in ? shift_in[static_cast<size_t>(b) * D + d] : 0.f));
+        lw[i] = ok ? ln_w[d] : 0.f;
+        lb[i] = ok ? ln_b[d] : 0.f;
+    }
+    auto normalise = [&](float (&y)[kSeqPer]) {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < kSeqPer; ++i) s += y[i];
+        const float mean = block_sum(s, red) / D;
+        float s2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < kSeqPer; ++i) {
+            const float c = (threadIdx.x + i * kSeqThreads < D) ? y[i] - mean : 0.f;
+            s2 += c * c;
+        }
+        const float inv = 1.0f / sqrtf(block_sum(s2, red) / D + 1e-5f);
+#pragma unroll
+        for (int i = 0; i < kSeqPer; ++i) y[i] = (y[i] - mean) * inv * lw[i] + lb[i];
+    };
+    normalise(v);
+    if (t > 0) normalise(pv);               // t == 0: pv already is a normalised row (or zeros)
+#pragma unroll
+    for (int i = 0; i < kSeqPer; ++i) {
+        const int d = threadIdx.x + i * kSeqThreads;
+        if (d >= D) continue;
+        const float xx = pv[i] - v[i];
+        if (t == T - 1) shift_out[static_cast<size_t>(b) * D + d] = v[i];
+#pragma unroll
+        for (int m = 0; m < NMIX; ++m)
+            out[(static_cast<size_t>(m) * n_tokens + tok) * D + d] = v[i] + xx * __ldg(mix + m * D + d);
+    }
+}
+
+struct TmixPreArgs {
+    const float *k, *v, *yw, *ya, *yv, *v_first;     // [N, D]; yv / v_first null on layer 0
+    const float *w0, *a0, *v0, *k_k, *k_a;           // [D]
+    float *w, *k2, *v2, *na, *nb;                     // [N, D]: decay, k', v', -kk, kk * a
+    long long n_pairs;                                // N * H
+    int H;
+};
+
+// One warp per (token, head): lane owns channels lane and lane + 32 of the head.
+__global__ void __launch_bounds__(256) seq_tmix_pre_kernel(const TmixPreArgs p) {
+    const long long pair = blockIdx.x * 8ll + (threadIdx.x >> 5);
+    if (pair >= p.n_pairs) return;
+    const int lane = threadIdx.x & 31, hd = static_cast<int>(pair % p.H);
+    const size_t base = static_cast<size_t>(pair) * 64;
+    float kk[2], av[2];
+    float n2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int c = hd * 64 + lane + 32 * j;
+        const size_t i = base + lane + 32 * j;
+        const float k = p.k[i];
+        float v = p.v[i];
+        p.w[i] = expf(-0.606531f * sigmoidf_(p.yw[i] + p.w0[c]));
+        av[j] = sigmoidf_(p.ya[i] + p.a0[c]);
+        kk[j] = k * p.k_k[c];
+        n2 += kk[j] * kk[j];
+        p.k2[i] = k * (1.0f + (av[j] - 1.0f) * p.k_a[c]);
+        if (p.yv) v = v + (p.v_first[i] - v) * sigmoidf_(p.yv[i] + p.v0[c]);
+        p.v2[i] = v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) n2 += __shfl_xor_sync(0xFFFFFFFFu, n2, o);
+    const float inv = 1.0f / sqrtf(n2 + 1e-12f);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const size_t i = base + lane + 32 * j;
+        const float kn = kk[j] * inv;
+        p.na[i] = -kn;
+        p.nb[i] = kn * av[j];
+    }
+}
+
+}  // namespace rwkvq
+
+using namespace rwkvq;
+
+extern "C" {
+
+int rwkvq_seq_ln_shift_mix(const float* x, const float* ln_w, const float* ln_b, const float* shift_in,
+                           const float* mix, int n_mix, float* out, float* shift_out, int B, int T, int D,
+                           void* stream) {
+    RWKVQ_REQUIRE(x && ln_w && ln_b && out && shift_out, RWKVQ_E_NULL, "rwkvq_seq_ln_shift_mix: null pointer");
+    RWKVQ_REQUIRE(B >= 1 && T >= 1 && D >= 1 && D <= kSeqThreads * kSeqPer, RWKVQ_E_LIMIT,
+                  "rwkvq_seq_ln_shift_mix: B=%d T=%d D=%d (D at most %d)", B, T, D, kSeqThreads * kSeqPer);
+    RWKVQ_REQUIRE((n_mix == 1 || n_mix == 6) && mix, RWKVQ_E_SHAPE, "rwkvq_seq_ln_shift_mix: n_mix %d (1 or 6)", n_mix);
+    const long long n = static_cast<long long>(B) * T;
+    RWKVQ_REQUIRE(n < (1ll << 31), RWKVQ_E_LIMIT, "rwkvq_seq_ln_shift_mix: %lld tokens", n);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (n_mix == 6)
+        seq_ln_shift_mix_kernel<6><<<static_cast<unsigned>(n), kSeqThreads, 0, s>>>(x, ln_w, ln_b, shift_in, mix, out, shift_out, T, D, n);
+    else
+        seq_ln_shift_mix_kernel<1><<<static_cast<unsigned>(n), kSeqThreads, 0, s>>>(x, ln_w, ln_b, shift_in, mix, out, shift_out, T, D, n);
+    return check_launch("rwkvq_seq_ln_shift_mix");
+}
+
+int rwkvq_seq_tmix_pre(const float* k, const float* v, const float* yw, const float* ya, const float* yv,
+                       const float* v_first, const float* w0, const float* a0, const float* v0, const float* k_k,
+                       const float* k_a, float* w, float* k2, float* v2, float* neg_kk, float* kk_a, int64_t n_tokens,
+                       int H, void* stream) {
+    RWKVQ_REQUIRE(k && v && yw && ya && w0 && a0 && k_k && k_a && w && k2 && v2 && neg_kk && kk_a, RWKVQ_E_NULL,
+                  "rwkvq_seq_tmix_pre: null pointer");
+    RWKVQ_REQUIRE((yv == nullptr) == (v_first == nullptr) && (yv == nullptr || v0 != nullptr), RWKVQ_E_NULL,
+                  "rwkvq_seq_tmix_pre: yv, v_first and v0 go together");
+    RWKVQ_REQUIRE(n_tokens >= 1 && H >= 1, RWKVQ_E_SHAPE, "rwkvq_seq_tmix_pre: n_tokens=%lld H=%d", (long long)n_tokens, H);
+    TmixPreArgs p{k, v, yw, ya, yv, v_first, w0, a0, v0, k_k, k_a, w, k2, v2, neg_kk, kk_a, n_tokens * H, H};
+    const long long blocks = (p.n_pairs + 7) / 8;
+    RWKVQ_REQUIRE(blocks < (1ll << 31), RWKVQ_E_LIMIT, "rwkvq_seq_tmix_pre: too many tokens");
+    seq_tmix_pre_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    return check_launch("rwkvq_seq_tmix_pre");
+}
+
+}  // extern "C"

@@ -7,8 +7,8 @@
 // independent, so a CTA of 256 threads owns one (batch, head): thread (dv, part)
 // keeps 16 columns of row dv in registers for the whole scan, and the two dot
 // products per step are finished with two quad shuffles.  The r/w/k/v/a/b rows of
-// step t+1 are fetched while step t is computed (double-buffered shared memory,
-// one barrier per step).
+// step t+1 are fetched while step t is computed (double-buffered shared memory, one barrier
+// per step; fetching two steps ahead was measured slower).
 #include "rwkvq_common.cuh"
 
 namespace rwkvq {
@@ -23,8 +23,15 @@ struct WkvArgs {
     int B, T, H;
 };
 
-__global__ void __launch_bounds__(256) wkv7_kernel(const WkvArgs p) {
-    __shared__ float sh[2][6][kS];
+// Shared-memory rows of a, w, k, b, r: the 16 values of column quarter `part` start at float
+// part * 20 (4 floats of padding per quarter), so that the four quarters a warp reads with one
+// 128-bit load fall into different bank groups: one wavefront per load instead of 2 x 4.
+constexpr int kRowPad = 80;
+__device__ __forceinline__ int padded(int c) { return (c >> 4) * 20 + (c & 15); }
+
+__global__ void __launch_bounds__(256, 4) wkv7_kernel(const WkvArgs p) {
+    __shared__ __align__(16) float sh[2][5][kRowPad];
+    __shared__ float shv[2][kS];
     const int bh = blockIdx.x, bi = bh / p.H, hi = bh % p.H;
     const int tid = threadIdx.x, dv = tid >> 2, part = tid & 3;
     float h[16];
@@ -48,8 +55,39 @@ __global__ void __launch_bounds__(256) wkv7_kernel(const WkvArgs p) {
         if (tid < 128) x1 = src[4 + (tid >> 6)][base + (tid & 63)];
     };
     auto stash = [&](int buf, float x0, float x1) {
-        sh[buf][tid >> 6][tid & 63] = x0;
-        if (tid < 128) sh[buf][4 + (tid >> 6)][tid & 63] = x1;
+        sh[buf][tid >> 6][padded(tid & 63)] = x0;
+        if (tid < 64) sh[buf][4][padded(tid)] = x1;
+        else if (tid < 128) shv[buf][tid & 63] = x1;
+    };
+    // one step of the recurrence on the rows staged in buffer `cur`
+    auto step = [&](int t, int cur) {
+        const float4* A = reinterpret_cast<const float4*>(sh[cur][0] + part * 20);
+        const float4* W = reinterpret_cast<const float4*>(sh[cur][1] + part * 20);
+        const float4* K = reinterpret_cast<const float4*>(sh[cur][2] + part * 20);
+        const float4* Bv = reinterpret_cast<const float4*>(sh[cur][3] + part * 20);
+        const float4* R = reinterpret_cast<const float4*>(sh[cur][4] + part * 20);
+        const float vv = shv[cur][dv];
+        float sa = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 a4 = A[i];
+            sa = fmaf(h[4 * i], a4.x, sa); sa = fmaf(h[4 * i + 1], a4.y, sa);
+            sa = fmaf(h[4 * i + 2], a4.z, sa); sa = fmaf(h[4 * i + 3], a4.w, sa);
+        }
+        sa += __shfl_xor_sync(0xFFFFFFFFu, sa, 1);
+        sa += __shfl_xor_sync(0xFFFFFFFFu, sa, 2);
+        float y = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 w4 = W[i], k4 = K[i], b4 = Bv[i], r4 = R[i];
+            h[4 * i] = fmaf(w4.x, h[4 * i], fmaf(vv, k4.x, sa * b4.x));             y = fmaf(h[4 * i], r4.x, y);
+            h[4 * i + 1] = fmaf(w4.y, h[4 * i + 1], fmaf(vv, k4.y, sa * b4.y));     y = fmaf(h[4 * i + 1], r4.y, y);
+            h[4 * i + 2] = fmaf(w4.z, h[4 * i + 2], fmaf(vv, k4.z, sa * b4.z));     y = fmaf(h[4 * i + 2], r4.z, y);
+            h[4 * i + 3] = fmaf(w4.w, h[4 * i + 3], fmaf(vv, k4.w, sa * b4.w));     y = fmaf(h[4 * i + 3], r4.w, y);
+        }
+        y += __shfl_xor_sync(0xFFFFFFFFu, y, 1);
+        y += __shfl_xor_sync(0xFFFFFFFFu, y, 2);
+        if (part == 0) p.out[((static_cast<size_t>(bi) * p.T + t) * p.H + hi) * kS + dv] = y;
     };
     float x0, x1;
     fetch(0, x0, x1);
@@ -58,26 +96,7 @@ __global__ void __launch_bounds__(256) wkv7_kernel(const WkvArgs p) {
     for (int t = 0; t < p.T; ++t) {
         const int cur = t & 1;
         if (t + 1 < p.T) fetch(t + 1, x0, x1);
-        const float* A = sh[cur][0] + part * 16;
-        const float* W = sh[cur][1] + part * 16;
-        const float* K = sh[cur][2] + part * 16;
-        const float* Bv = sh[cur][3] + part * 16;
-        const float* R = sh[cur][4] + part * 16;
-        const float vv = sh[cur][5][dv];
-        float sa = 0.f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) sa = fmaf(h[i], A[i], sa);
-        sa += __shfl_xor_sync(0xFFFFFFFFu, sa, 1);
-        sa += __shfl_xor_sync(0xFFFFFFFFu, sa, 2);
-        float y = 0.f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            h[i] = fmaf(W[i], h[i], fmaf(vv, K[i], sa * Bv[i]));
-            y = fmaf(h[i], R[i], y);
-        }
-        y += __shfl_xor_sync(0xFFFFFFFFu, y, 1);
-        y += __shfl_xor_sync(0xFFFFFFFFu, y, 2);
-        if (part == 0) p.out[((static_cast<size_t>(bi) * p.T + t) * p.H + hi) * kS + dv] = y;
+        step(t, cur);
         if (t + 1 < p.T) stash(cur ^ 1, x0, x1);
         __syncthreads();
     }

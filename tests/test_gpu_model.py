@@ -208,3 +208,39 @@ def test_persistent_decoder_matches_launch_chain(cuda_lib, recipe):
     free.check()
     assert got == want
     assert torch.equal(free.logits, forced.logits)
+
+
+def test_sequence_glue_kernels_against_fp32_torch(cuda_lib):
+    """rwkvq_seq_ln_shift_mix / rwkvq_seq_tmix_pre against the same formulas in plain torch fp32
+    (tolerance 2e-6 of the output scale: different reduction orders only), including the carried
+    shift state, a fresh stream (no state) and the layer-0 form without the v branch."""
+    import torch.nn.functional as F
+    from rwkv_quant_b200.backends.cuda import ops
+    g = torch.Generator().manual_seed(21)
+    B, T, D, H = 3, 5, 512, 8
+    rnd = lambda *s: torch.randn(*s, generator=g).cuda()
+    x, lw, lb, mix6, prev = rnd(B, T, D), rnd(D), rnd(D), torch.rand(6, D, generator=g).cuda(), rnd(B, 1, D)
+    for shift_in in (prev, None):
+        for mix in (mix6, mix6[2]):
+            out, new_shift = ops.seq_ln_shift_mix(x, lw, lb, shift_in, mix)
+            xn = F.layer_norm(x, (D,), lw, lb)
+            p0 = shift_in if shift_in is not None else torch.zeros(B, 1, D, device="cuda")
+            shifted = torch.cat([p0, xn[:, :-1]], dim=1)
+            ref = torch.stack([xn + (shifted - xn) * m for m in mix.reshape(-1, D)])
+            assert out.shape == ref.shape
+            assert (out - ref).abs().max().item() <= 2e-6 * ref.abs().max().item() + 1e-6
+            assert (new_shift - xn[:, -1:]).abs().max().item() <= 2e-6 * xn.abs().max().item() + 1e-6
+    N = B * T
+    k, v, yw, ya, yv, vf = (rnd(N, D) for _ in range(6))
+    w0, a0, v0, k_k, k_a = (rnd(D) for _ in range(5))
+    for layer0 in (False, True):
+        w, k2, v2, na, nb = ops.seq_tmix_pre(k, v, yw, ya, None if layer0 else yv, None if layer0 else vf,
+                                             w0, a0, v0, k_k, k_a, H)
+        rw = torch.exp(-0.606531 * torch.sigmoid(yw + w0))
+        ra = torch.sigmoid(ya + a0)
+        kk = (k * k_k).reshape(N, H, 64)
+        kk = (kk / torch.sqrt((kk * kk).sum(-1, keepdim=True) + 1e-12)).reshape(N, D)
+        rk = k * (1.0 + (ra - 1.0) * k_a)
+        rv = v if layer0 else v + (vf - v) * torch.sigmoid(yv + v0)
+        for got, ref, nm in ((w, rw, "w"), (k2, rk, "k"), (v2, rv, "v"), (na, -kk, "-kk"), (nb, kk * ra, "kk*a")):
+            assert (got - ref).abs().max().item() <= 3e-6 * ref.abs().max().item() + 1e-6, (layer0, nm)
