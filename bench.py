@@ -46,6 +46,7 @@ def parse():
     ap.add_argument("--recipe", default="compression")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the b=64 decode and pp512 measurements")
     ap.add_argument("--decoder", default="chain", choices=["persistent", "chain"],
                     help="batch-1 decoder: one persistent kernel per token, or the launch chain")
     return ap.parse_args()
@@ -208,6 +209,50 @@ def gemv_phase(model, steps, warmup):
     return nbytes, len(mats), e0.elapsed_time(e1) * 1e-3 / steps
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the quantized-linear GEMV launches of one decoded
+# token (1.5B compression, b = 1), from the ncu capture summarised under profiles/
+NCU_GEMV_PHASE_DRAM_BYTES = 828225280 + 342272
+
+
+def other_configs(model, a, dev, w_bytes, peak):
+    """The other configurations the metric names, measured in the same process on the same
+    build: 64 concurrent decode streams and prefill pp512 (one stateful call over 512 random
+    token ids, logits of the last position) at batch 1 and 16."""
+    import torch
+    out = {"build": f"{a.model} {a.recipe}"}
+    dec = model.decoder(64, use_graph=True, self_feed=True)
+    dec.tokens.copy_(torch.randint(1, 60000, (64,), device=dev))
+    for _ in range(3):
+        dec.step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    n = 16
+    e0.record()
+    for _ in range(n):
+        dec.step()
+    e1.record()
+    torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) * 1e-3 / n
+    state = 2 * model.n_layer * model.n_head * 64 * 64 * 4 * 64
+    out["decode_b64"] = {"tok_s": 64 / sec, "ms_per_step": sec * 1e3, "hbm_gbs": (w_bytes + state) / sec / 1e9,
+                         "frac_of_peak": (w_bytes + state) / sec / 1e9 / peak}
+    del dec
+    for b in (1, 16):
+        idx = torch.randint(1, 60000, (b, 512), device=dev)
+        model.forward_stateful(idx, model.init_state(b), last_only=True)          # warm-up
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(3):
+            st = model.init_state(b)
+            e0.record()
+            model.forward_stateful(idx, st, last_only=True)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) * 1e-3)
+        out[f"pp512_b{b}"] = {"tok_s": b * 512 / best, "ms": best * 1e3}
+    return out
+
+
 def run_ours(a, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -277,6 +322,9 @@ def run_ours(a, rank, world, local_rank):
     # ---- roofline of the GEMV launches of one token
     g_bytes, g_launches, g_sec = gemv_phase(model, a.steps, a.warmup)
     peak, peak_kind = measured_peak()
+    extras = None
+    if world == 1 and B == 1 and not a.no_extras:
+        extras = other_configs(model, a, dev, w_bytes, peak)
     if rank != 0:
         dp.finalize()
         return
@@ -303,12 +351,17 @@ def run_ours(a, rank, world, local_rank):
         "gpu_launches": (dec.launches_per_step or (model.launches_per_token + 1)) * a.steps,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": g_bytes / g_sec / 1e9, "peak": peak, "unit": "GB/s",
-                     "frac": g_bytes / g_sec / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
+                     "frac": g_bytes / g_sec / 1e9 / peak,
+                     "traffic": NCU_GEMV_PHASE_DRAM_BYTES if (a.model, a.recipe, B) == ("1.5b", "compression", 1) else None,
+                     "traffic_source": "profiles/decode_gemv_phase_dram_traffic_1p5b_compression.md (ncu, one token)",
+                     "peak_kind": peak_kind,
                      "kernel": f"gemv_mma_kernel, the {g_launches} quantized-linear launches of one token",
                      "bytes_per_replay": g_bytes, "us_per_replay": g_sec * 1e6},
         "whole_step": {"hbm_gbs": (w_bytes + state_bytes) / (t_dev / a.steps) / 1e9,
                        "frac_of_peak": (w_bytes + state_bytes) / (t_dev / a.steps) / 1e9 / peak},
     }
+    if extras is not None:
+        line["extras"] = extras
     if not a.no_cpu_baseline:
         v, info = cpu_decode_tok_s(a.model, a.recipe, seconds=16.0)
         line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port",

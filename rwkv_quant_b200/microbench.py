@@ -242,6 +242,16 @@ def gemm_sweep(recipe="compression", Ms=(64, 512, 8192), reps=20):
             print(f"gemm {layout}@{bits} [{rows},{cols}] M={M}: {us:8.1f} us  {2.0 * M * rows * cols / us / 1e6:7.1f} TFLOP/s", flush=True)
 
 
+def gemm_once(layout="sb6", bits=5, rows=2048, cols=2048, M=8192, launches=3):
+    """A few plain rwkvq_gemm launches of one shape (the target of ncu captures)."""
+    dq = _tensor(layout, bits, rows, cols)
+    x = torch.randn(M, cols, device="cuda")
+    for _ in range(launches):
+        y = ops.gemm(dq, x, check=True)
+    torch.cuda.synchronize()
+    print("ok", float(y.abs().sum()))
+
+
 def gemm_timeline(layout="sb6", bits=5, rows=2048, cols=2048, M=8192):
     """Pipeline timeline of CTA (0,0,0) of one rwkvq_gemm launch: per macro-iteration (K = 256)
     when its weight stage was free, converted, seen full by the issuer and issued."""
@@ -359,12 +369,19 @@ def main():
     tpp = sub.add_parser("tp")
     tpp.add_argument("--model", default="2.9b"); tpp.add_argument("--recipe", default="compression")
     tpp.add_argument("--exchange", default="p2p", choices=["p2p", "nccl", "none"])
+    go = sub.add_parser("gemm")
+    go.add_argument("layout"); go.add_argument("bits", type=int); go.add_argument("rows", type=int)
+    go.add_argument("cols", type=int); go.add_argument("--M", type=int, default=8192)
+    go.add_argument("--launches", type=int, default=3)
     gt = sub.add_parser("gemm-timeline")
     gt.add_argument("--M", type=int, default=8192); gt.add_argument("--rows", type=int, default=2048)
     gt.add_argument("--cols", type=int, default=2048)
     gs = sub.add_parser("gemm-sweep")
     gs.add_argument("--recipe", default="compression")
     a = ap.parse_args()
+    if a.cmd == "gemm":
+        gemm_once(a.layout, a.bits, a.rows, a.cols, a.M, a.launches)
+        return
     if a.cmd == "gemm-timeline":
         gemm_timeline("sb6", 5, a.rows, a.cols, a.M)
         return
