@@ -15,6 +15,8 @@
 //   gemv + add     output projection and residual
 //   ln_shift_mix   LN2 + token shift + lerp                     -> xk[B][D]
 //   gemv + relu^2  ffn key;  gemv + add  ffn value and residual
+#include <stdlib.h>
+
 #include "rwkvq_decode_parts.cuh"
 
 namespace rwkvq {
@@ -476,6 +478,30 @@ int linear(const rwkvq_qtensor* t, const float* x, int B, int in, float* y, int 
     return rwkvq_gemv(t, x, RWKVQ_F32, B, in, y, out, epi, resid, stream);
 }
 
+// The LoRA branches depend on the normalised row only, not on r/k/v: they run on a side
+// stream between a fork after LN1 and a join before the time-mix core, so that in a captured
+// graph they form a parallel branch beside the r/k/v GEMV instead of two more links of the
+// dependent chain.  One side stream and two events per device, created on first use (make the
+// first call outside stream capture).  RWKVQ_FORK=0 keeps everything on the caller's stream.
+struct SideLane { cudaStream_t stream = nullptr; cudaEvent_t fork = nullptr, join = nullptr; };
+SideLane* side_lane() {
+    static SideLane lanes[64];
+    static const bool enabled = [] { const char* e = getenv("RWKVQ_FORK"); return !(e && e[0] == '0'); }();
+    if (!enabled) return nullptr;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    SideLane& l = lanes[dev];
+    if (!l.stream) {
+        if (cudaStreamCreateWithFlags(&l.stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&l.join, cudaEventDisableTiming) != cudaSuccess) {
+            l.stream = nullptr;
+            return nullptr;
+        }
+    }
+    return &l;
+}
+
 int lora_pair(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, const float* const* xs,
               float* const* ys, const int* acts, int n_br, int B, int D, int max_rank, float* part,
               int n_chunks, cudaStream_t s) {
@@ -547,6 +573,13 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         float *xr = w.xs, *xw = w.xs + BD, *xk = w.xs + 2 * BD, *xv = w.xs + 3 * BD, *xa = w.xs + 4 * BD,
               *xg = w.xs + 5 * BD;
         float *r = w.rkv, *k = w.rkv + BD, *v = w.rkv + 2 * BD;
+        SideLane* lane = side_lane();
+        cudaStream_t s_lora = s;
+        if (lane) {                                  // fork: the LoRA branches leave the chain here
+            if (cudaEventRecord(lane->fork, s) != cudaSuccess || cudaStreamWaitEvent(lane->stream, lane->fork, 0) != cudaSuccess)
+                return fail(RWKVQ_E_LAUNCH, "rwkvq_decode_step: fork onto the side stream failed");
+            s_lora = lane->stream;
+        }
         const int ml = mma_layout_of(L.Wr);
         if (B == 1 && ml >= 0 && mma_layout_of(L.Wk) == ml && mma_layout_of(L.Wv) == ml && L.Wk.rows == D &&
             L.Wv.rows == D && L.Wr.rows == D && L.Wk.cols == D && L.Wv.cols == D && L.Wr.cols == D) {
@@ -574,8 +607,12 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
             const float* x1[4] = {xw, xa, xg, xv};
             float* y2[4] = {yw, ya, yg, yv};
             const int act[4] = {1, 0, 2, 0};       // tanh (decay), none, sigmoid (gate), none
-            rc = lora_pair(t1, t2, x1, y2, act, layer0 ? 3 : 4, B, D, m->max_rank, w.part, w.n_chunks, s);
+            rc = lora_pair(t1, t2, x1, y2, act, layer0 ? 3 : 4, B, D, m->max_rank, w.part, w.n_chunks, s_lora);
             if (rc) return rc;
+        }
+        if (lane) {                                  // join before the time-mix core
+            if (cudaEventRecord(lane->join, lane->stream) != cudaSuccess || cudaStreamWaitEvent(s, lane->join, 0) != cudaSuccess)
+                return fail(RWKVQ_E_LAUNCH, "rwkvq_decode_step: join of the side stream failed");
         }
         TmixCoreArgs tc{r, k, v, yw, ya, layer0 ? nullptr : yv, yg, L.w0, L.a0, L.v0, L.k_k, L.k_a, L.r_k,
                         L.lnx_w, L.lnx_b, w.v_first, wkv[l], w.og, D, H, layer0 ? 1 : 0};
