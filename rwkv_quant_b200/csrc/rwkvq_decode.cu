@@ -142,9 +142,11 @@ constexpr int kLmMaxRank = 512;
 struct LoraDownArgs {
     QView t[4];
     const float* x[4];      // [n_cols, ldx]
-    float* part;            // [4][n_chunks][kLmMaxN][max_rank]
+    float* part;            // [4][n_chunks][n_stride][max_rank]
     long long ldx;
     int n_cols, n_chunks, max_rank;
+    int n_stride;           // right-hand sides the scratch is laid out for (multiple of kLmMaxN)
+    int rep;                // 64-row sub-chunks one CTA accumulates (more for large batches: fewer partial sums)
 };
 struct LoraUpArgs {
     QView t[4];
@@ -152,16 +154,19 @@ struct LoraUpArgs {
     float* y[4];            // [n_cols, ldy]
     int act[4];
     long long ldy;
-    int n_cols, n_chunks, max_rank;
+    int n_cols, n_chunks, max_rank, n_stride;
 };
 
 // 256 threads = 4 row groups x 64 column threads (4 columns each, 256 columns per pass)
-template <int MODE>
-__device__ __forceinline__ void lora_down_body(const LoraDownArgs& a, const QView& t, const float* __restrict__ x,
+// MULTI = false: one 64-row chunk per CTA (the batch-1 form, loops resolved at compile time)
+template <int MODE, bool MULTI>
+__device__ __forceinline__ void lora_down_body(const LoraDownArgs& a, const QView& t, const float* __restrict__ xall,
                                                float (&red)[4][kLmMaxN][256]) {
     const int chunk = blockIdx.x, br = blockIdx.y;
+    const int n0 = blockIdx.z * kLmMaxN;                  // this CTA's group of right-hand sides
+    const int nc = min(kLmMaxN, a.n_cols - n0);
+    const float* x = xall + static_cast<size_t>(n0) * a.ldx;
     const int rg = threadIdx.x >> 6, ct = threadIdx.x & 63;
-    const int row0 = chunk * kLdRows;
     const int nb = MODE == 0 ? (t.cols + t.gs - 1) / t.gs : 0;
     for (int c0 = 0; c0 < t.cols; c0 += 256) {
         const int c = c0 + ct * 4;
@@ -171,21 +176,26 @@ __device__ __forceinline__ void lora_down_body(const LoraDownArgs& a, const QVie
         for (int n = 0; n < kLmMaxN; ++n)
 #pragma unroll
             for (int k = 0; k < 4; ++k) acc[n][k] = 0.f;
-        if (c < t.cols) {
-            constexpr int RPT = kLdRows / 4;          // rows per thread, all loads issued together
-            float w[RPT][4];
+        const int rep = MULTI ? a.rep : 1;
+#pragma unroll 1
+        for (int sub = 0; sub < rep; ++sub) {
+            const int row0 = (chunk * rep + sub) * kLdRows;
+            if (c < t.cols && row0 < t.rows) {
+                constexpr int RPT = kLdRows / 4;          // rows per thread, all loads issued together
+                float w[RPT][4];
 #pragma unroll
-            for (int r = 0; r < RPT; ++r) lora_w4<MODE>(t, min(row0 + rg + 4 * r, t.rows - 1), c, nb, blk, w[r]);
-            pdl_wait();              // the weights above are constants; x comes from the previous kernel
+                for (int r = 0; r < RPT; ++r) lora_w4<MODE>(t, min(row0 + rg + 4 * r, t.rows - 1), c, nb, blk, w[r]);
+                pdl_wait();              // the weights above are constants; x comes from the previous kernel
 #pragma unroll
-            for (int n = 0; n < kLmMaxN; ++n) {
-                if (n >= a.n_cols) break;
+                for (int n = 0; n < kLmMaxN; ++n) {
+                    if (n >= nc) break;
 #pragma unroll
-                for (int r = 0; r < RPT; ++r) {
-                    const int i = row0 + rg + 4 * r;
-                    const float xv = i < t.rows ? __ldcg(x + n * a.ldx + i) : 0.f;
+                    for (int r = 0; r < RPT; ++r) {
+                        const int i = row0 + rg + 4 * r;
+                        const float xv = i < t.rows ? __ldcg(x + n * a.ldx + i) : 0.f;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) acc[n][k] = fmaf(xv, w[r][k], acc[n][k]);
+                        for (int k = 0; k < 4; ++k) acc[n][k] = fmaf(xv, w[r][k], acc[n][k]);
+                    }
                 }
             }
         }
@@ -193,36 +203,37 @@ __device__ __forceinline__ void lora_down_body(const LoraDownArgs& a, const QVie
         __syncthreads();
 #pragma unroll
         for (int n = 0; n < kLmMaxN; ++n) {
-            if (n >= a.n_cols) break;
+            if (n >= nc) break;
 #pragma unroll
             for (int k = 0; k < 4; ++k) red[rg][n][ct * 4 + k] = acc[n][k];
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < a.n_cols * 256; idx += 256) {
+        for (int idx = threadIdx.x; idx < nc * 256; idx += 256) {
             const int n = idx >> 8, cc = idx & 255;
             if (c0 + cc >= t.cols) continue;
             const float v = (red[0][n][cc] + red[1][n][cc]) + (red[2][n][cc] + red[3][n][cc]);
-            a.part[((static_cast<size_t>(br) * a.n_chunks + chunk) * kLmMaxN + n) * a.max_rank + c0 + cc] = v;
+            a.part[((static_cast<size_t>(br) * a.n_chunks + chunk) * a.n_stride + n0 + n) * a.max_rank + c0 + cc] = v;
         }
     }
 }
 
+template <bool MULTI>
 __global__ void __launch_bounds__(256) lora_down_kernel(const LoraDownArgs a) {
     __shared__ float red[4][kLmMaxN][256];
     const QView& t = a.t[blockIdx.y];
     const float* x = a.x[blockIdx.y];
     pdl_launch_dependents();
     switch (lora_mode(t)) {
-        case 0: lora_down_body<0>(a, t, x, red); break;
-        case 1: lora_down_body<1>(a, t, x, red); break;
-        default: lora_down_body<2>(a, t, x, red); break;
+        case 0: lora_down_body<0, MULTI>(a, t, x, red); break;
+        case 1: lora_down_body<1, MULTI>(a, t, x, red); break;
+        default: lora_down_body<2, MULTI>(a, t, x, red); break;
     }
 }
 
 // 256 threads = 8 row groups x 32 column threads (4 columns each)
 template <int MODE>
-__device__ __forceinline__ void lora_up_body(const LoraUpArgs& a, const QView& t, const float (&h)[kLmMaxN][kLmMaxRank],
-                                             float (&acc)[kLmMaxN][4]) {
+__device__ __forceinline__ void lora_up_body(const LoraUpArgs& a, int n_cols, const QView& t,
+                                             const float (&h)[kLmMaxN][kLmMaxRank], float (&acc)[kLmMaxN][4]) {
     const int rg = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int c = blockIdx.x * kLuCols + lane * 4;
     const int rank = t.rows;
@@ -239,7 +250,7 @@ __device__ __forceinline__ void lora_up_body(const LoraUpArgs& a, const QView& t
             if (j >= rank) break;
 #pragma unroll
             for (int n = 0; n < kLmMaxN; ++n) {
-                if (n >= a.n_cols) break;
+                if (n >= n_cols) break;
                 const float hv = h[n][j];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) acc[n][k] = fmaf(hv, w[r][k], acc[n][k]);
@@ -257,10 +268,12 @@ __global__ void __launch_bounds__(256) lora_up_kernel(const LoraUpArgs a) {
     pdl_wait();
     if (blockIdx.x * kLuCols >= t.cols) return;
     const int rank = t.rows;
-    for (int idx = threadIdx.x; idx < a.n_cols * rank; idx += 256) {
+    const int n0 = blockIdx.z * kLmMaxN;                      // this CTA's group of right-hand sides
+    const int nc = min(kLmMaxN, a.n_cols - n0);
+    for (int idx = threadIdx.x; idx < nc * rank; idx += 256) {
         const int n = idx / rank, j = idx % rank;
-        const float* pp = a.part + ((static_cast<size_t>(br) * a.n_chunks) * kLmMaxN + n) * a.max_rank + j;
-        const size_t stride = static_cast<size_t>(kLmMaxN) * a.max_rank;
+        const float* pp = a.part + ((static_cast<size_t>(br) * a.n_chunks) * a.n_stride + n0 + n) * a.max_rank + j;
+        const size_t stride = static_cast<size_t>(a.n_stride) * a.max_rank;
         float v = 0.f;
         int ch = 0;
         for (; ch + 8 <= a.n_chunks; ch += 8) {       // 8 loads in flight, summed in chunk order
@@ -283,25 +296,25 @@ __global__ void __launch_bounds__(256) lora_up_kernel(const LoraUpArgs a) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) acc[n][k] = 0.f;
     switch (lora_mode(t)) {
-        case 0: lora_up_body<0>(a, t, h, acc); break;
-        case 1: lora_up_body<1>(a, t, h, acc); break;
-        default: lora_up_body<2>(a, t, h, acc); break;
+        case 0: lora_up_body<0>(a, nc, t, h, acc); break;
+        case 1: lora_up_body<1>(a, nc, t, h, acc); break;
+        default: lora_up_body<2>(a, nc, t, h, acc); break;
     }
 #pragma unroll
     for (int n = 0; n < kLmMaxN; ++n) {
-        if (n >= a.n_cols) break;
+        if (n >= nc) break;
 #pragma unroll
         for (int k = 0; k < 4; ++k) red[rg][n][lane * 4 + k] = acc[n][k];
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < a.n_cols * kLuCols; idx += 256) {
+    for (int idx = threadIdx.x; idx < nc * kLuCols; idx += 256) {
         const int n = idx / kLuCols, cc = idx % kLuCols;
         const int col = blockIdx.x * kLuCols + cc;
         if (col >= t.cols) continue;
         float v = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; ++w) v += red[w][n][cc];
-        a.y[br][n * a.ldy + col] = v;
+        a.y[br][static_cast<size_t>(n0 + n) * a.ldy + col] = v;
     }
 }
 
@@ -451,7 +464,7 @@ Workspace carve(const rwkvq_model& m, int B, void* base) {
     };
     w.x = take(b * D); w.xs = take(6 * b * D); w.rkv = take(3 * b * D);
     w.n_chunks = static_cast<int>((D + kLdRows - 1) / kLdRows);
-    w.part = take(4 * static_cast<size_t>(w.n_chunks) * kLmMaxN * R);
+    w.part = take(4 * static_cast<size_t>(w.n_chunks) * ((b + kLmMaxN - 1) / kLmMaxN * kLmMaxN) * R);   // upper bound (rep = 1)
     w.yl = take(4 * b * D); w.og = take(b * D); w.xk = take(b * D); w.hffn = take(b * F);
     w.xo = take(b * D); w.v_first = take(b * D); w.logits = take(b * V);
     w.argv = take(2 * b * kArgSlices);
@@ -502,6 +515,8 @@ SideLane* side_lane() {
     return &l;
 }
 
+int lora_rep(int B) { return B > kLmMaxN ? 8 : 1; }
+
 int lora_pair(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, const float* const* xs,
               float* const* ys, const int* acts, int n_br, int B, int D, int max_rank, float* part,
               int n_chunks, cudaStream_t s) {
@@ -522,15 +537,18 @@ int lora_pair(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, co
         u.act[i] = acts[i];
         if (t2[i]->cols > max_cols) max_cols = t2[i]->cols;
     }
-    d.part = part; d.ldx = D; d.n_chunks = n_chunks; d.max_rank = max_rank;
-    u.part = part; u.ldy = D; u.n_chunks = n_chunks; u.max_rank = max_rank;
-    for (int n0 = 0; n0 < B; n0 += kLmMaxN) {
-        const int nc = B - n0 < kLmMaxN ? B - n0 : kLmMaxN;
-        d.n_cols = u.n_cols = nc;
-        for (int i = 0; i < n_br; ++i) { d.x[i] = xs[i] + static_cast<size_t>(n0) * D; u.y[i] = ys[i] + static_cast<size_t>(n0) * D; }
-        launch_pdl(lora_down_kernel, dim3(n_chunks, n_br), dim3(256), 0, s, d);
-        launch_pdl(lora_up_kernel, dim3((max_cols + kLuCols - 1) / kLuCols, n_br), dim3(256), 0, s, u);
-    }
+    // large batches: a CTA accumulates 8 sub-chunks of 64 rows, so that the up projection adds
+    // 8x fewer partial sums per right-hand side; the groups of 8 right-hand sides are grid.z
+    const int rep = lora_rep(B);
+    const int chunks = (n_chunks + rep - 1) / rep, groups = (B + kLmMaxN - 1) / kLmMaxN;
+    d.part = part; d.ldx = D; d.n_chunks = chunks; d.max_rank = max_rank; d.rep = rep;
+    u.part = part; u.ldy = D; u.n_chunks = chunks; u.max_rank = max_rank;
+    d.n_stride = u.n_stride = groups * kLmMaxN;
+    d.n_cols = u.n_cols = B;
+    for (int i = 0; i < n_br; ++i) { d.x[i] = xs[i]; u.y[i] = ys[i]; }
+    if (rep > 1) launch_pdl(lora_down_kernel<true>, dim3(chunks, n_br, groups), dim3(256), 0, s, d);
+    else launch_pdl(lora_down_kernel<false>, dim3(chunks, n_br, groups), dim3(256), 0, s, d);
+    launch_pdl(lora_up_kernel, dim3((max_cols + kLuCols - 1) / kLuCols, n_br, groups), dim3(256), 0, s, u);
     return RWKVQ_OK;
 }
 
