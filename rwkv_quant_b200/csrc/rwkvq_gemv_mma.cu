@@ -10,7 +10,7 @@ namespace rwkvq {
 // of the K loop; the activations are prepared once per CTA.  Each warp sees a flat
 // sequence of work items (tile, iteration); the loads of item n+1 are issued
 // before item n is consumed.
-template <int L, int WK>
+template <int L, int WK, bool SPLIT>      // SPLIT: the K loop is also split across gridDim.z CTAs
 __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaArgs a) {
     using G = Geo<L>;
     constexpr int WT = kMmaWarps / WK;
@@ -24,9 +24,9 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaAr
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int tl = warp / WK, ks = warp % WK;
-    const int KS = gridDim.z;                               // K slices across CTAs
+    const int KS = SPLIT ? static_cast<int>(gridDim.z) : 1;  // K slices across CTAs
     const int n_iters = n_in / G::KI / KS;                  // iterations of this CTA's slice
-    const int it0 = blockIdx.z * n_iters;
+    const int it0 = SPLIT ? blockIdx.z * n_iters : 0;
     const int n_tiles = (q.rows + 15) >> 4;
     const int step = gridDim.x * WT;
     const int ipt = (n_iters - ks + WK - 1) / WK;          // this warp's iterations per tile
@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaAr
         float* rb = red + buf * (kMmaWarps * 16);
         if (t == 0) { rb[warp * 16 + g] = acc0; rb[warp * 16 + g + 8] = acc1; }
         __syncthreads();
-        if (KS == 1) {
+        if (!SPLIT) {
             if (threadIdx.x < WT * 16) {
                 const int wtl = threadIdx.x >> 4, r = threadIdx.x & 15;
                 const int row = (base + wtl) * 16 + r;
@@ -201,19 +201,19 @@ size_t gemv_mma_scratch_bytes() {
     return sizeof(float) * kSplitMaxSlices * kMmaMaxFused * kSplitMaxRows + sizeof(unsigned int) * 1024;
 }
 
-template <int L, int WK>
+template <int L, int WK, bool SPLIT = false>
 static int launch_one(MmaArgs& a, int rows, int cols, int n_mats, int KS, cudaStream_t s) {
     constexpr int WT = kMmaWarps / WK;
     const size_t smem = 3 * static_cast<size_t>(cols) + 4 * (cols / 16) + 2 * kMmaWarps * 16 * 4;
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<L, WK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<L, WK, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(smem));
         if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "gemv_mma: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
     const int units = ((rows + 15) / 16 + WT - 1) / WT;
     const int cap = kResidentCtas / (n_mats * KS) > 0 ? kResidentCtas / (n_mats * KS) : 1;
     a.rows_padded = ((rows + 15) / 16) * 16;
-    cudaError_t le = launch_pdl(gemv_mma_kernel<L, WK>, dim3(units < cap ? units : cap, n_mats, KS),
+    cudaError_t le = launch_pdl(gemv_mma_kernel<L, WK, SPLIT>, dim3(units < cap ? units : cap, n_mats, KS),
                                 dim3(kMmaWarps * 32), smem, s, a);
     if (le != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "gemv_mma: %s", cudaGetErrorString(le));
     return RWKVQ_OK;
@@ -236,7 +236,7 @@ static int launch_wk(MmaArgs& a, int rows, int cols, int n_mats, float* scratch,
     if (KS > 1) {
         a.partial = scratch;
         a.counters = reinterpret_cast<unsigned int*>(scratch + kSplitMaxSlices * kMmaMaxFused * kSplitMaxRows);
-        return launch_one<L, 8>(a, rows, cols, n_mats, KS, s);
+        return launch_one<L, 8, true>(a, rows, cols, n_mats, KS, s);
     }
     int wt = 1;
     if (tiles * n_mats > kResidentCtas) {
