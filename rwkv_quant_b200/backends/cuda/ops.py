@@ -43,10 +43,7 @@ class DeviceQT:
         shape = tuple(qt.shape)
         if len(shape) != 2:
             raise ValueError(f"{getattr(qt, 'key', '?')}: only 2-D tensors, got {shape}")
-        oi = getattr(qt, "outlier_indices", None)
-        if oi is not None and oi.numel() > 0:
-            raise NotImplementedError(
-                f"{getattr(qt, 'key', '?')}: sparse outlier overrides are not supported")
+        self.outliers = None          # (rows, cols, values fp32, first index of each row run, run lengths)
         self.key = getattr(qt, "key", "")
         self.rows, self.cols = int(shape[0]), int(shape[1])
         self.bits = int(qt.bits)
@@ -88,6 +85,60 @@ class DeviceQT:
         self.struct = _descr(self.bufs, self.meta)
         if relayout and dev.type == "cuda":
             self._relayout()
+        oi = getattr(qt, "outlier_indices", None)
+        if oi is not None and oi.numel() > 0:
+            self._attach_outliers(oi, qt.outlier_values, dev)
+
+    def _attach_outliers(self, oi, ov, dev):
+        """Sparse overrides of per-row tensors (formats/codec.py:279-292): W[r, c] = value.  Kept
+        sorted by (row, column); ``delta`` = value - quantized value is what a product over the
+        packed codes is short of."""
+        if self.kind != "rtn":
+            raise NotImplementedError(f"{self.key}: outlier overrides on a {self.kind!r} tensor")
+        oi = oi.to(dev).long().reshape(-1, 2)
+        vals = ov.to(dev).to(torch.bfloat16).float().reshape(-1)
+        order = torch.argsort(oi[:, 0] * self.cols + oi[:, 1], stable=True)
+        # a position listed twice keeps its last value, as the codec's fancy assignment does
+        key = (oi[:, 0] * self.cols + oi[:, 1])[order]
+        last = torch.ones_like(key, dtype=torch.bool)
+        last[:-1] = key[1:] != key[:-1]
+        order = order[last]
+        rows, cols, vals = oi[order, 0], oi[order, 1], vals[order]
+        wq = dequant(self.bufs, self.meta, torch.float32, False)[rows, cols]
+        uniq, counts = torch.unique_consecutive(rows, return_counts=True)
+        self.outliers = (rows, cols, vals, vals - wq, uniq, counts)
+
+    def dequant(self, out_dtype: torch.dtype = torch.float32, round_bf16: bool = False) -> torch.Tensor:
+        """Dense [rows, cols] with the outlier overrides applied (fp32: the codec's bits)."""
+        w = dequant(self.bufs, self.meta, out_dtype, round_bf16)
+        if self.outliers is not None:
+            rows, cols, vals = self.outliers[:3]
+            w[rows, cols] = vals.to(out_dtype)
+        return w
+
+    def gemv(self, x: torch.Tensor, epilogue: int = 0, resid: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x [N, cols] -> [N, rows]; tensors with outliers add the sparse correction (summed per
+        row in column order: deterministic) before the epilogue."""
+        if self.outliers is None:
+            return gemv(self.bufs, self.meta, x, epilogue, resid)
+        rows, cols, _, delta, uniq, counts = self.outliers
+        y = gemv(self.bufs, self.meta, x, 0, None)
+        contrib = (x.float()[:, cols] * delta).t().contiguous()               # [n_outliers, N]
+        y[:, uniq] += torch.segment_reduce(contrib, "sum", lengths=counts, axis=0).t()
+        if epilogue == _lib.EPI_RELU2:
+            y = torch.relu(y) ** 2
+        elif epilogue == _lib.EPI_ADD:
+            y = y + resid
+        return y
+
+    def densified(self) -> "DeviceQT":
+        """The tensor as a dense bf16 one with the overrides applied (what the kernels that read
+        packed codes directly are given instead of a tensor with outliers)."""
+        from ...formats.container import QuantizedTensor
+        w = self.dequant(torch.float32, True).to(torch.bfloat16)
+        qt = QuantizedTensor(key=self.key, group="", bits=16, shape=(self.rows, self.cols))
+        qt.dense = w
+        return DeviceQT(qt, device=w.device)
 
     def _relayout(self):
         """Regroup the scale records / bit-planes for the decode kernels (same bytes,

@@ -32,12 +32,12 @@ class _QuantLinearBase:
         x2, lead = ops.as_rows(x, self.in_features)
         if resid is not None:
             resid = resid.reshape(-1, self.out_features).contiguous()
-        y = ops.gemv(self.dq.bufs, self.dq.meta, x2, epilogue, resid)
+        y = self.dq.gemv(x2, epilogue, resid)
         return y.reshape(*lead, self.out_features)
 
     def _dequant_w(self, dtype=torch.float32) -> torch.Tensor:
         """Dense [OUT, IN]; the fp32 result equals the numpy codec bit for bit."""
-        return ops.dequant(self.dq.bufs, self.dq.meta, dtype, False)
+        return self.dq.dequant(dtype, False)
 
     def weight_nbytes(self) -> int:
         return self.dq.nbytes()

@@ -37,8 +37,7 @@ def _dense_param(qt, device):
     if qt.bits >= 16:
         t = qt.dense.float()
     else:
-        dq = ops.DeviceQT(qt, device, relayout=False)
-        t = ops.dequant(dq.bufs, dq.meta, torch.float32, True).cpu()
+        t = ops.DeviceQT(qt, device, relayout=False).dequant(torch.float32, True).cpu()
     if t.ndim == 2 and min(t.shape) >= 32:
         t = t.half().float()
     return t.to(device).contiguous()
@@ -63,7 +62,11 @@ class QuantRWKV7:
         self.gemv_max_batch = int(gemv_max_batch)
         T = ckpt.tensors
         dev = self.device
-        dq = lambda key: ops.DeviceQT(T[key], dev)
+        def dq(key):
+            d = ops.DeviceQT(T[key], dev)
+            # the kernels of the model read packed codes directly: a tensor with sparse outlier
+            # overrides is handed to them as a dense bf16 one (its load-time precision anyway)
+            return d.densified() if d.outliers is not None else d
         vec = lambda key: _dense_param(T[key], dev).reshape(-1)
 
         self.emb, self.head = dq("emb.weight"), dq("head.weight")

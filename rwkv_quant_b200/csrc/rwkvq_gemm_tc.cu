@@ -29,12 +29,11 @@ namespace rwkvq {
 
 constexpr int kGmProducers = 512;     // warps 0-15 unpack weights (and run the epilogue)
 constexpr int kGmThreads = 544;       // + warp 16: one lane issues the TMA loads and the MMAs
-constexpr int kGmPasses = 128 * 8 / kGmProducers;   // items (32 weights) per producer thread and macro-iteration
 constexpr int kGmRows = 128;          // output rows per CTA (UMMA M)
 constexpr int kGmK = 64;              // K per slab: one 128-byte swizzle row of fp16
-constexpr int kGmSlabs = 4;           // slabs per macro-iteration (K = 256 = one super-block), 2 A stages
 constexpr int kGmMaxBSlots = 8;       // activation slabs in flight (TMA)
-__host__ __device__ constexpr int gemm_b_slots(int nt) { return nt >= 128 ? 6 : 8; }
+// activation slab slots: as many pairs as fit beside the two weight stages
+__host__ __device__ constexpr int gemm_b_slots(int nt, int km) { return nt >= 256 ? 4 : (nt >= 128 && km == 256) ? 6 : 8; }
 constexpr unsigned kGmSpinLimit = 1u << 24;
 
 struct GemmArgs {
@@ -193,21 +192,33 @@ __device__ __forceinline__ void load_packed(Packed& p, const QView& t, int row_g
     }
 }
 
-// 32 weights -> fp16, stored as 4 swizzled 16-byte chunks of row r: chunks 4*half .. +3 of
-// the slab (item / 2), half = item % 2.
-__device__ __forceinline__ void convert_store(const Packed& p, const QView& t, int r, int it, unsigned char* a_slab) {
+// 32 weights -> fp16, stored as 4 swizzled 16-byte chunks of row r: chunks 4*half .. +3 of the
+// slab.  `it` = item index inside the super-block (selects the block scales).
+__device__ __forceinline__ void convert_store(const Packed& p, const QView& t, int r, int it, int half,
+                                              unsigned char* a_slab) {
     uint32_t bytes[8];                             // 32 codes as bytes, column order
     __half2 s2[2], m2[2], bias;                    // per 16 columns
     const uint32_t h = p.h, h2 = p.h2;
-    const int half = it & 1;
     if (t.kind == RWKVQ_KIND_SB6) {
         const uint32_t w[4] = {p.c0.x, p.c0.y, p.c0.z, p.c0.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {              // byte k of the block: column k (low), k + 16 (high)
-            bytes[i] = (w[i] & 0x0F0F0F0Fu) | spread_nibble<4>((h >> (4 * i)) & 0xFu) |
-                       spread_nibble<5>((h2 >> (4 * i)) & 0xFu);
-            bytes[4 + i] = ((w[i] >> 4) & 0x0F0F0F0Fu) | spread_nibble<4>((h >> (16 + 4 * i)) & 0xFu) |
-                           spread_nibble<5>((h2 >> (16 + 4 * i)) & 0xFu);
+            bytes[i] = w[i] & 0x0F0F0F0Fu;
+            bytes[4 + i] = (w[i] >> 4) & 0x0F0F0F0Fu;
+        }
+        if (t.qh) {                                // uniform over the launch: 4-bit tensors skip the plane work
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                bytes[i] |= spread_nibble<4>((h >> (4 * i)) & 0xFu);
+                bytes[4 + i] |= spread_nibble<4>((h >> (16 + 4 * i)) & 0xFu);
+            }
+        }
+        if (t.qh2) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                bytes[i] |= spread_nibble<5>((h2 >> (4 * i)) & 0xFu);
+                bytes[4 + i] |= spread_nibble<5>((h2 >> (16 + 4 * i)) & 0xFu);
+            }
         }
         float s, m;
         if (t.dev_meta) {
@@ -279,12 +290,17 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 //   bar_afull[s]  one arrival per producer thread: the four A slabs of stage s are written
 //   bar_afree[s]  tcgen05.commit: the MMAs that read stage s have completed
 //   bar_bfull[k]  TMA bytes of activation slot k have landed;  bar_bfree[k]  its MMAs completed
-template <int NT>   // tokens per CTA tile (UMMA N): 16, 32, 64 or 128
+// NT = tokens per CTA tile (UMMA N): 16 .. 256;  KM = K of a macro-iteration: 256 (one super-block,
+// four slabs) or 128 (two slabs; leaves room for the activation tiles of NT = 256)
+template <int NT, int KM>
 __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int SLAB_BYTES = kGmRows * 128, B_BYTES = NT * 128;
-    constexpr int BS = gemm_b_slots(NT);
+    constexpr int kGmSlabs = KM / kGmK;                         // slabs per macro-iteration
+    constexpr int kItems = KM / 32;                             // items (32 weights) per row and macro-iteration
+    constexpr int kGmPasses = kGmRows * kItems / kGmProducers;  // items per producer thread and macro-iteration
+    constexpr int BS = gemm_b_slots(NT, KM);
     constexpr uint32_t TM_COLS = NT < 32 ? 32 : NT;
     unsigned char* a_ring = smem;                                        // [2 stages][4 slabs][SLAB_BYTES]
     unsigned char* b_ring = smem + 2 * kGmSlabs * SLAB_BYTES;            // [BS][B_BYTES]
@@ -297,8 +313,8 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
     const QView& t = a.t;
     const int row0 = blockIdx.x * kGmRows, tok0 = blockIdx.y * NT;
     const int KS = gridDim.z;
-    const int n_m = (t.cols >> 8) / KS;                         // macro-iterations (super-blocks) of this CTA's K slice
-    const int sb_first = blockIdx.z * n_m;
+    const int n_m = (t.cols / KM) / KS;                         // macro-iterations of this CTA's K slice
+    const int m_first = blockIdx.z * n_m;                       // first macro-iteration, in units of KM
 
     if (tid == 0) {
         for (int s = 0; s < 2; ++s) { mbar_init(&bar_afull[s], kGmProducers); mbar_init(&bar_afree[s], 1); }
@@ -327,8 +343,8 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
                 const int ps = q % NP;
                 if (q >= NP && !mbar_wait_bounded(&bar_bfree[ps], ((q / NP) - 1) & 1)) return false;
                 mbar_expect_tx(&bar_bfull[ps], 2 * B_BYTES);
-                tma_load_2d(b_ring + (2 * ps) * B_BYTES, &xmap, (sb_first * kGmSlabs + 2 * q) * kGmK, tok0, &bar_bfull[ps]);
-                tma_load_2d(b_ring + (2 * ps + 1) * B_BYTES, &xmap, (sb_first * kGmSlabs + 2 * q + 1) * kGmK, tok0,
+                tma_load_2d(b_ring + (2 * ps) * B_BYTES, &xmap, (m_first * kGmSlabs + 2 * q) * kGmK, tok0, &bar_bfull[ps]);
+                tma_load_2d(b_ring + (2 * ps + 1) * B_BYTES, &xmap, (m_first * kGmSlabs + 2 * q + 1) * kGmK, tok0,
                             &bar_bfull[ps]);
                 return true;
             };
@@ -336,14 +352,15 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
             int issued = 0;
             for (; issued < NP - 1 && issued < n_pairs && ok; ++issued) ok = issue_pair(issued);
             for (int q = 0; q < n_pairs && ok; ++q) {
-                const int i = q >> 1, st = i & 1, ps = q % NP;
-                if ((q & 1) == 0 && !mbar_wait_bounded(&bar_afull[st], (i >> 1) & 1)) { ok = false; break; }
-                if ((q & 1) == 0) trace_mark(a, 8 + 4 * i + 2);
+                constexpr int PPM = kGmSlabs / 2;                    // pairs per macro-iteration
+                const int i = q / PPM, pq = q % PPM, st = i & 1, ps = q % NP;
+                if (pq == 0 && !mbar_wait_bounded(&bar_afull[st], (i >> 1) & 1)) { ok = false; break; }
+                if (pq == 0) trace_mark(a, 8 + 4 * i + 2);
                 if (!mbar_wait_bounded(&bar_bfull[ps], (q / NP) & 1)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int s2 = 0; s2 < 2; ++s2) {
-                    const int sl = (q & 1) * 2 + s2;
+                    const int sl = pq * 2 + s2;
                     const uint64_t ad = umma_desc(smem_addr(a_ring + (st * kGmSlabs + sl) * SLAB_BYTES));
                     const uint64_t bd = umma_desc(smem_addr(b_ring + (2 * ps + s2) * B_BYTES));
 #pragma unroll
@@ -351,7 +368,7 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
                         umma_f16(tmem, ad + 2 * k, bd + 2 * k, idesc, (q | s2 | k) ? 1u : 0u);
                 }
                 umma_commit(&bar_bfree[ps]);
-                if (q & 1) { umma_commit(&bar_afree[st]); trace_mark(a, 8 + 4 * i + 3); }
+                if (pq == PPM - 1) { umma_commit(&bar_afree[st]); trace_mark(a, 8 + 4 * i + 3); }
                 // refill the pair slot consumed before this one while the tensor pipe is busy
                 if (issued < n_pairs) { ok = issue_pair(issued); ++issued; }
             }
@@ -360,13 +377,14 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
         }
     } else {
         // ------------------------------------------------------------------ producers
-        constexpr int PR = kGmProducers / 8;                    // rows per pass
-        const int pit = tid & 7, prow = tid >> 3;               // item of the super-block, row within a pass
+        constexpr int PR = kGmProducers / kItems;               // rows per pass
+        const int pit = tid % kItems, prow = tid / kItems;      // item of the macro-iteration, row within a pass
         Packed P0[kGmPasses], P1[kGmPasses];                    // packed bytes of macro-iterations i, i + 1 (static roles)
         auto load_all = [&](Packed (&P)[kGmPasses], int i) {
 #pragma unroll
             for (int q = 0; q < kGmPasses; ++q)
-                load_packed(P[q], t, min(row0 + PR * q + prow, t.rows - 1), sb_first + i, pit);
+                load_packed(P[q], t, min(row0 + PR * q + prow, t.rows - 1), ((m_first + i) * KM) >> 8,
+                            (((m_first + i) * KM) >> 5 & 7) + pit);
         };
         auto produce = [&](Packed (&P)[kGmPasses], int i) {
             const int st = i & 1;
@@ -380,7 +398,8 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
             if (!s_fail) {
                 unsigned char* slab = a_ring + (st * kGmSlabs + (pit >> 1)) * SLAB_BYTES;
 #pragma unroll
-                for (int q = 0; q < kGmPasses; ++q) convert_store(P[q], t, PR * q + prow, pit, slab);
+                for (int q = 0; q < kGmPasses; ++q)
+                    convert_store(P[q], t, PR * q + prow, (((m_first + i) * KM) >> 5 & 7) + pit, pit & 1, slab);
             }
             fence_async_smem();                                 // generic-proxy stores -> visible to the tensor core
             mbar_arrive(&bar_afull[st]);
@@ -554,27 +573,27 @@ int make_xmap(CUtensorMap* map, const __half* x16, int M, int cols, int nt) {
     return RWKVQ_OK;
 }
 
-template <int NT>
+template <int NT, int KM>
 int launch_gemm(GemmArgs& a, int rows, int cols, int M, float* partial, const __half* x16, cudaStream_t s) {
     CUtensorMap xmap;
     int mrc = make_xmap(&xmap, x16, M, cols, NT);
     if (mrc) return mrc;
-    const size_t smem = static_cast<size_t>(2 * kGmSlabs) * kGmRows * 128 + static_cast<size_t>(gemm_b_slots(NT)) * NT * 128 + 1024;
+    const size_t smem = static_cast<size_t>(2 * (KM / kGmK)) * kGmRows * 128 + static_cast<size_t>(gemm_b_slots(NT, KM)) * NT * 128 + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT, KM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(smem));
         if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "rwkvq_gemm: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    const int rt = (rows + kGmRows - 1) / kGmRows, tt = (M + NT - 1) / NT, n_m = cols / 256;
+    const int rt = (rows + kGmRows - 1) / kGmRows, tt = (M + NT - 1) / NT, n_m = cols / KM;
     // K slices across CTAs while the grid is below one CTA per SM (power of two, >= 2 super-blocks each)
     int KS = 1;
     while (rt * tt * KS < kGemmSms && n_m % (KS * 2) == 0 && n_m / (KS * 2) >= 2 && rt * tt * KS * 2 <= kGemmResident &&
            rt * tt <= static_cast<int>((kGemmHeader - 256) / sizeof(unsigned int)))
         KS *= 2;
     a.partial = partial;
-    gemm_tc_kernel<NT><<<dim3(rt, tt, KS), kGmThreads, smem, s>>>(a, xmap);
+    gemm_tc_kernel<NT, KM><<<dim3(rt, tt, KS), kGmThreads, smem, s>>>(a, xmap);
     return RWKVQ_OK;
 }
 }  // namespace
@@ -584,7 +603,7 @@ extern "C" {
 // header | row scales [M] | K-split accumulator tiles (one wave of CTAs x 128 x NT floats) | fp16 activations
 static size_t gemm_ws_partial_off(size_t m) { return kGemmHeader + ((sizeof(float) * m + 255) / 256) * 256; }
 static size_t gemm_ws_x16_off(size_t m) {
-    const size_t nt = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
+    const size_t nt = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256;
     return gemm_ws_partial_off(m) + sizeof(float) * kGemmResident * kGmRows * nt;
 }
 size_t rwkvq_gemm_workspace_bytes_for(int M, int max_cols) {
@@ -624,10 +643,18 @@ int rwkvq_gemm(const rwkvq_qtensor* t, const float* x, int M, int64_t ldx, float
     a.trace = g_gemm_trace;
     cudaMemsetAsync(ws, 0, kGemmHeader, s);
     row_scale_kernel<<<M, 256, 0, s>>>(x, ldx, t->cols, scale, x16, static_cast<long long>(x16_pitch(t->cols)));
-    if (M <= 16) rc = launch_gemm<16>(a, t->rows, t->cols, M, partial, x16, s);
-    else if (M <= 32) rc = launch_gemm<32>(a, t->rows, t->cols, M, partial, x16, s);
-    else if (M <= 64) rc = launch_gemm<64>(a, t->rows, t->cols, M, partial, x16, s);
-    else rc = launch_gemm<128>(a, t->rows, t->cols, M, partial, x16, s);
+    if (M <= 16) rc = launch_gemm<16, 256>(a, t->rows, t->cols, M, partial, x16, s);
+    else if (M <= 32) rc = launch_gemm<32, 256>(a, t->rows, t->cols, M, partial, x16, s);
+    else if (M <= 64) rc = launch_gemm<64, 256>(a, t->rows, t->cols, M, partial, x16, s);
+    else {
+        // 256-token tiles (every converted weight serves 256 tokens) once they still give the
+        // SMs enough CTAs or a long K loop; otherwise 128-token tiles
+        const int tiles256 = ((t->rows + kGmRows - 1) / kGmRows) * ((M + 255) / 256);
+        if (M > 128 && (tiles256 >= 64 || t->cols >= 4096))
+            rc = launch_gemm<256, 128>(a, t->rows, t->cols, M, partial, x16, s);
+        else
+            rc = launch_gemm<128, 256>(a, t->rows, t->cols, M, partial, x16, s);
+    }
     if (rc) return rc;
     return check_launch("rwkvq_gemm");
 }

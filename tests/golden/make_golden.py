@@ -153,6 +153,9 @@ def make_codec_cases():
     add_case(store, meta, "rtn/8wide", quantize_tensor("blocks.1.att.g2", W("g2", 64, 512), QuantConfig(g_lora=8), real_gw=True))
     add_case(store, meta, "rtn/4odd", quantize_tensor("blocks.1.att.g1", W("g1o", 40, 65), QuantConfig(g_lora=4), real_gw=True))
     add_case(store, meta, "rtn/8lin", quantize_tensor("blocks.0.att.key.weight", W("rl", 48, 256), QuantConfig(proj=8), real_gw=True))
+    # per-row int8 with sparse outlier overrides (2 % of the columns of every row)
+    add_case(store, meta, "rtn/8outliers", quantize_tensor("blocks.1.att.g1", W("g1x", 96, 256),
+                                                            QuantConfig(g_lora=8, outlier_fracs={"g_lora": 0.02}), real_gw=True))
     store["__meta__"] = np.frombuffer(json.dumps(meta).encode(), dtype=np.uint8)
     np.savez_compressed(os.path.join(HERE, "codec_cases.npz"), **store)
     print("codec cases:", len(meta))

@@ -28,30 +28,29 @@ def _x(n, k, seed, dtype=torch.float32):
 
 def test_dequant_bit_exact_all_golden_cases(cuda_lib, codec_cases):
     from rwkv_quant_b200.backends.cuda import ops
+    n_outlier_cases = 0
     for name, (meta, bufs, _) in codec_cases.items():
-        if "outlier_indices" in bufs:
-            continue
+        n_outlier_cases += "outlier_indices" in bufs        # sparse overrides: applied by DeviceQT.dequant
         dq = ops.DeviceQT(case_to_qt(name, meta, bufs))
-        w = ops.dequant(dq.bufs, dq.meta, torch.float32, False).cpu().numpy()
+        w = dq.dequant(torch.float32, False).cpu().numpy()
         assert digest_f32(w) == meta["digest"], f"{name}: device dequant differs from the codec"
         ref = oracle_dequant_case(meta, bufs)
-        h = ops.dequant(dq.bufs, dq.meta, torch.float16, False).cpu().numpy()
+        h = dq.dequant(torch.float16, False).cpu().numpy()
         np.testing.assert_array_equal(h, ref.astype(np.float16), err_msg=name)
-        b = ops.dequant(dq.bufs, dq.meta, torch.bfloat16, True).float().cpu().numpy()
+        b = dq.dequant(torch.bfloat16, True).float().cpu().numpy()
         np.testing.assert_array_equal(b, oc.f32_to_bf16_rne(ref), err_msg=name)
+    assert n_outlier_cases >= 1, "the golden set lost its outlier case"
 
 
 @pytest.mark.parametrize("xdtype", [torch.float32, torch.float16, torch.bfloat16])
 def test_gemv_golden_cases(cuda_lib, codec_cases, xdtype):
     from rwkv_quant_b200.backends.cuda import ops
     for name, (meta, bufs, _) in codec_cases.items():
-        if "outlier_indices" in bufs:
-            continue
         dq = ops.DeviceQT(case_to_qt(name, meta, bufs))
         w = oracle_dequant_case(meta, bufs).astype(np.float64)
         for n in (1, 2, 3, 8):
             x = _x(n, dq.cols, zlib.crc32(f"{name}-{n}".encode()), xdtype)
-            y = ops.gemv(dq.bufs, dq.meta, x, 0, None).cpu().numpy()
+            y = dq.gemv(x, 0, None).cpu().numpy()
             ref = x.float().cpu().numpy().astype(np.float64) @ w.T
             assert relmax(y, ref) <= TOL, (name, n, relmax(y, ref))
 
@@ -202,3 +201,39 @@ def test_errors_surface_as_exceptions(cuda_lib):
         ops.gemv(dq.bufs, bad, _x(1, 256, 0), 0, None)
     with pytest.raises(RuntimeError):
         ops.gemv(dq.bufs, dq.meta, torch.zeros(1, 256), 0, None)      # CPU tensor: no fallback
+
+
+def test_rtn_outlier_overrides(cuda_lib):
+    """Sparse outlier overrides of per-row tensors (formats/codec.py:279-292): the dense result is
+    the codec's bit for bit, a position listed twice keeps its last value, the GEMV adds the
+    sparse correction before the epilogue (rel <= 1e-3) and is reproducible, and the dense bf16
+    stand-in the model uses equals bf16(dequant)."""
+    from rwkv_quant_b200 import synth
+    from rwkv_quant_b200.backends.cuda import QuantLinearV2, ops
+    g = torch.Generator().manual_seed(5)
+    rows, cols = 96, 256
+    qt = synth.quant_rtn("w", "g", torch.randn(rows, cols, generator=g) * 0.02, 8)
+    idx = torch.tensor([[3, 7], [3, 200], [0, 0], [95, 255], [40, 13], [3, 7], [40, 12]], dtype=torch.int32)
+    val = torch.tensor([0.5, -0.25, 1.0, -2.0, 0.125, 0.75, 3.0]).to(torch.bfloat16)
+    qt.outlier_indices, qt.outlier_values = idx, val
+    n = lambda t: None if t is None else t.numpy()
+    ref = oc.dequant_rtn(n(qt.scale), shape=qt.shape, codes=n(qt.codes), codes_packed=n(qt.codes_packed),
+                         outlier_indices=idx.numpy(), outlier_values=val.float().numpy())
+    assert ref[3, 7] == 0.75
+    lin = QuantLinearV2(qt)
+    np.testing.assert_array_equal(lin._dequant_w(torch.float32).cpu().numpy(), ref)
+    x = _x(3, cols, 17)
+    resid = _x(3, rows, 18)
+    for epi, r in ((0, None), (1, None), (2, resid)):
+        y1 = lin(x, epilogue=epi, resid=r)
+        y2 = lin(x, epilogue=epi, resid=r)
+        assert torch.equal(y1, y2)
+        want = x.cpu().numpy().astype(np.float64) @ ref.astype(np.float64).T
+        if epi == 1:
+            want = np.maximum(want, 0) ** 2
+        elif epi == 2:
+            want = want + resid.cpu().numpy()
+        assert relmax(y1.cpu().numpy(), want) <= TOL, epi
+    dense = lin.dq.densified()
+    assert dense.kind == "dense" and dense.outliers is None
+    np.testing.assert_array_equal(dense.dequant(torch.float32, False).cpu().numpy(), oc.f32_to_bf16_rne(ref))
