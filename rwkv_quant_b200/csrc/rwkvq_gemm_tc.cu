@@ -28,13 +28,16 @@
 namespace rwkvq {
 
 constexpr int kGmProducers = 512;     // warps 0-15 unpack weights (and run the epilogue)
-constexpr int kGmThreads = 544;       // + warp 16: one lane issues the TMA loads and the MMAs
+constexpr int kGmThreads = 576;       // + warp 16: one lane issues the MMAs; warp 17: one lane issues the TMA loads
 constexpr int kGmRows = 128;          // output rows per CTA (UMMA M)
 constexpr int kGmK = 64;              // K per slab: one 128-byte swizzle row of fp16
 constexpr int kGmMaxBSlots = 8;       // activation slabs in flight (TMA)
 // activation slab slots: as many pairs as fit beside the two weight stages
 __host__ __device__ constexpr int gemm_b_slots(int nt, int km) { return nt >= 256 ? 4 : (nt >= 128 && km == 256) ? 6 : 8; }
 constexpr unsigned kGmSpinLimit = 1u << 24;
+// upper bound of one suspended try_wait: without it a waiter that went to sleep before the phase
+// completed was seen to wake only after ~10 us
+constexpr unsigned kGmSuspendNs = 256;
 
 struct GemmArgs {
     QView t;
@@ -66,9 +69,9 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     for (unsigned i = 0; i < kGmSpinLimit; ++i) {
         uint32_t done;
         asm volatile(
-            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
             : "=r"(done)
-            : "r"(a), "r"(parity)
+            : "r"(a), "r"(parity), "r"(kGmSuspendNs)
             : "memory");
         if (done) return true;
     }
@@ -285,8 +288,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 
-// Warps 0-15: producers (and the epilogue).  Warp 16, one lane: issues the activation TMA
-// loads and the MMAs.  Producers and issuer meet only through mbarriers:
+// Warps 0-15: producers (and the epilogue).  Warp 16, one lane: issues the MMAs.  Warp 17, one
+// lane: issues the activation TMA loads.  Producers and issuer meet only through mbarriers:
 //   bar_afull[s]  one arrival per producer thread: the four A slabs of stage s are written
 //   bar_afree[s]  tcgen05.commit: the MMAs that read stage s have completed
 //   bar_bfull[k]  TMA bytes of activation slot k have landed;  bar_bfree[k]  its MMAs completed
@@ -331,46 +334,54 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
     const uint32_t tmem = s_tmem;
     if (tid == 0) trace_mark(a, 0);
 
-    if (warp == kGmProducers / 32) {
-        // ------------------------------------------------------------------ issuer
+    constexpr int NP = BS / 2;                                  // pair slots of the activation ring
+    const int n_pairs = n_m * kGmSlabs / 2;
+    if (warp == kGmProducers / 32 + 1) {
+        // ------------------------------------------------------------------ activation loader
+        // Activation slabs travel in pairs (one mbarrier per pair): slabs 2q, 2q+1 of this CTA go
+        // to pair slot q % NP as soon as the MMAs that read its previous content have completed.
         if (lane == 0) {
-            // Activation slabs travel in pairs (one mbarrier, one commit per pair): a
-            // tcgen05.commit drains the tensor pipe (~700 cycles), so they are kept rare.
-            const uint32_t idesc = umma_idesc(NT);
-            constexpr int NP = BS / 2;                          // pair slots of the activation ring
-            const int n_pairs = n_m * kGmSlabs / 2;
-            auto issue_pair = [&](int q) -> bool {              // slabs 2q, 2q+1 of this CTA -> pair slot q % NP
+            for (int q = 0; q < n_pairs; ++q) {
                 const int ps = q % NP;
-                if (q >= NP && !mbar_wait_bounded(&bar_bfree[ps], ((q / NP) - 1) & 1)) return false;
+                if (q >= NP && !mbar_wait_bounded(&bar_bfree[ps], ((q / NP) - 1) & 1)) { s_fail = 1; break; }
+                if (s_fail) break;
                 mbar_expect_tx(&bar_bfull[ps], 2 * B_BYTES);
                 tma_load_2d(b_ring + (2 * ps) * B_BYTES, &xmap, (m_first * kGmSlabs + 2 * q) * kGmK, tok0, &bar_bfull[ps]);
                 tma_load_2d(b_ring + (2 * ps + 1) * B_BYTES, &xmap, (m_first * kGmSlabs + 2 * q + 1) * kGmK, tok0,
                             &bar_bfull[ps]);
-                return true;
-            };
+            }
+        }
+    } else if (warp == kGmProducers / 32) {
+        // ------------------------------------------------------------------ MMA issuer
+        // A single thread executes dependent scalar code at a few cycles per instruction, so this
+        // loop carries nothing but the waits, the MMAs and the commits: descriptors are formed by
+        // adding slab offsets to two base descriptors.
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(NT);
+            const uint64_t a_desc0 = umma_desc(smem_addr(a_ring)), b_desc0 = umma_desc(smem_addr(b_ring));
+            constexpr int PPM = kGmSlabs / 2;                    // pairs per macro-iteration
             bool ok = true;
-            int issued = 0;
-            for (; issued < NP - 1 && issued < n_pairs && ok; ++issued) ok = issue_pair(issued);
+            int i = 0, pq = 0, ps = 0, bphase = 0;               // macro-iteration, pair in it, pair slot, slot phase
             for (int q = 0; q < n_pairs && ok; ++q) {
-                constexpr int PPM = kGmSlabs / 2;                    // pairs per macro-iteration
-                const int i = q / PPM, pq = q % PPM, st = i & 1, ps = q % NP;
-                if (pq == 0 && !mbar_wait_bounded(&bar_afull[st], (i >> 1) & 1)) { ok = false; break; }
-                if (pq == 0) trace_mark(a, 8 + 4 * i + 2);
-                if (!mbar_wait_bounded(&bar_bfull[ps], (q / NP) & 1)) { ok = false; break; }
+                const int st = i & 1;
+                if (pq == 0) {
+                    if (!mbar_wait_bounded(&bar_afull[st], (i >> 1) & 1)) { ok = false; break; }
+                    trace_mark(a, 8 + 4 * i + 2);
+                }
+                if (!mbar_wait_bounded(&bar_bfull[ps], bphase)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int s2 = 0; s2 < 2; ++s2) {
-                    const int sl = pq * 2 + s2;
-                    const uint64_t ad = umma_desc(smem_addr(a_ring + (st * kGmSlabs + sl) * SLAB_BYTES));
-                    const uint64_t bd = umma_desc(smem_addr(b_ring + (2 * ps + s2) * B_BYTES));
+                    const uint64_t ad = a_desc0 + (static_cast<uint64_t>((st * kGmSlabs + pq * 2 + s2) * SLAB_BYTES) >> 4);
+                    const uint64_t bd = b_desc0 + (static_cast<uint64_t>((2 * ps + s2) * B_BYTES) >> 4);
 #pragma unroll
                     for (int k = 0; k < kGmK / 16; ++k)        // 32 bytes further along K per step
                         umma_f16(tmem, ad + 2 * k, bd + 2 * k, idesc, (q | s2 | k) ? 1u : 0u);
                 }
                 umma_commit(&bar_bfree[ps]);
                 if (pq == PPM - 1) { umma_commit(&bar_afree[st]); trace_mark(a, 8 + 4 * i + 3); }
-                // refill the pair slot consumed before this one while the tensor pipe is busy
-                if (issued < n_pairs) { ok = issue_pair(issued); ++issued; }
+                if (++pq == PPM) { pq = 0; ++i; }
+                if (++ps == NP) { ps = 0; bphase ^= 1; }
             }
             if (ok) umma_commit(&bar_done);
             else s_fail = 1;
