@@ -7,8 +7,8 @@
 // independent, so a CTA of 256 threads owns one (batch, head): thread (dv, part)
 // keeps 16 columns of row dv in registers for the whole scan, and the two dot
 // products per step are finished with two quad shuffles.  The r/w/k/v/a/b rows of
-// step t+1 are fetched while step t is computed (double-buffered shared memory, one barrier
-// per step; fetching two steps ahead was measured slower).
+// following steps are fetched while step t is computed (double-buffered shared memory, one
+// barrier per step).
 #include "rwkvq_common.cuh"
 
 namespace rwkvq {
@@ -29,7 +29,11 @@ struct WkvArgs {
 constexpr int kRowPad = 80;
 __device__ __forceinline__ int padded(int c) { return (c >> 4) * 20 + (c & 15); }
 
-__global__ void __launch_bounds__(256, 4) wkv7_kernel(const WkvArgs p) {
+// DEEP: the rows of step t+2 are requested while step t is computed (two register sets with fixed
+// roles); used when the grid leaves the SMs mostly empty and a step is shorter than a load from L2.
+// Otherwise one step ahead and 4 CTAs per SM.
+template <bool DEEP>
+__global__ void __launch_bounds__(256, DEEP ? 2 : 4) wkv7_kernel(const WkvArgs p) {
     __shared__ __align__(16) float sh[2][5][kRowPad];
     __shared__ float shv[2][kS];
     const int bh = blockIdx.x, bi = bh / p.H, hi = bh % p.H;
@@ -89,16 +93,35 @@ __global__ void __launch_bounds__(256, 4) wkv7_kernel(const WkvArgs p) {
         y += __shfl_xor_sync(0xFFFFFFFFu, y, 2);
         if (part == 0) p.out[((static_cast<size_t>(bi) * p.T + t) * p.H + hi) * kS + dv] = y;
     };
-    float x0, x1;
-    fetch(0, x0, x1);
-    stash(0, x0, x1);
-    __syncthreads();
-    for (int t = 0; t < p.T; ++t) {
-        const int cur = t & 1;
-        if (t + 1 < p.T) fetch(t + 1, x0, x1);
-        step(t, cur);
-        if (t + 1 < p.T) stash(cur ^ 1, x0, x1);
+    if (DEEP) {
+        float e0, e1, o0 = 0.f, o1 = 0.f;
+        fetch(0, e0, e1);
+        stash(0, e0, e1);
+        if (p.T > 1) fetch(1, o0, o1);
         __syncthreads();
+        for (int t = 0; t < p.T; t += 2) {
+            if (t + 2 < p.T) fetch(t + 2, e0, e1);
+            step(t, 0);
+            if (t + 1 < p.T) stash(1, o0, o1);
+            __syncthreads();
+            if (t + 1 >= p.T) break;
+            if (t + 3 < p.T) fetch(t + 3, o0, o1);
+            step(t + 1, 1);
+            if (t + 2 < p.T) stash(0, e0, e1);
+            __syncthreads();
+        }
+    } else {
+        float x0, x1;
+        fetch(0, x0, x1);
+        stash(0, x0, x1);
+        __syncthreads();
+        for (int t = 0; t < p.T; ++t) {
+            const int cur = t & 1;
+            if (t + 1 < p.T) fetch(t + 1, x0, x1);
+            step(t, cur);
+            if (t + 1 < p.T) stash(cur ^ 1, x0, x1);
+            __syncthreads();
+        }
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -149,7 +172,8 @@ int rwkvq_wkv7(const float* r, const float* w, const float* k, const float* v, c
     RWKVQ_REQUIRE(B >= 1 && T >= 1 && H >= 1, RWKVQ_E_SHAPE, "rwkvq_wkv7: B=%d T=%d H=%d", B, T, H);
     RWKVQ_REQUIRE(aligned(h_out, 16) && aligned(h_in, 16), RWKVQ_E_ALIGN, "rwkvq_wkv7: state must be 16-byte aligned");
     WkvArgs p{r, w, k, v, a, b, h_in, out, h_out, B, T, H};
-    wkv7_kernel<<<B * H, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    if (B * H <= 2 * 148 && T > 2) wkv7_kernel<true><<<B * H, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    else wkv7_kernel<false><<<B * H, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
     return check_launch("rwkvq_wkv7");
 }
 
