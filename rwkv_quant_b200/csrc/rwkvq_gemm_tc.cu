@@ -326,8 +326,10 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
         s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // Launched programmatically behind the pre-pass: everything up to the first use of the
+    // activations (barrier set-up, TMEM, the first packed weights) overlaps with it.
+    pdl_launch_dependents();
     if (warp == 0) tmem_alloc(&s_tmem, TM_COLS);
-    if (tid < NT) s_unscale[tid] = (tok0 + tid < a.M) ? 1.0f / __ldcg(a.row_scale + tok0 + tid) : 0.f;
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -341,6 +343,7 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
         // Activation slabs travel in pairs (one mbarrier per pair): slabs 2q, 2q+1 of this CTA go
         // to pair slot q % NP as soon as the MMAs that read its previous content have completed.
         if (lane == 0) {
+            pdl_wait();                                         // the fp16 activations come from the pre-pass
             for (int q = 0; q < n_pairs; ++q) {
                 const int ps = q % NP;
                 if (q >= NP && !mbar_wait_bounded(&bar_bfree[ps], ((q / NP) - 1) & 1)) { s_fail = 1; break; }
@@ -427,6 +430,8 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
     // ---------------------------------------------------------------------- epilogue
     if (lane == 0 && !s_fail && !mbar_wait_bounded(&bar_done, 0)) s_fail = 1;
     __syncwarp();
+    pdl_wait();                                                 // token scales, residual, K-split scratch
+    if (tid < NT) s_unscale[tid] = (tok0 + tid < a.M) ? 1.0f / __ldcg(a.row_scale + tok0 + tid) : 0.f;
     tc_fence_after();
     __syncthreads();
     if (tid == 0) trace_mark(a, 1);
@@ -518,8 +523,12 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
 // Pre-pass, one CTA per token: power-of-two scale so that |x * scale| <= 2^14, and the
 // scaled row as fp16 (the tensor the TMA loads read).
 __global__ void __launch_bounds__(256) row_scale_kernel(const float* x, long long ldx, int cols, float* scale,
-                                                        __half* x16, long long pitch) {
+                                                        __half* x16, long long pitch, uint4* header, int header_words16) {
     __shared__ float red[8];
+    pdl_launch_dependents();
+    pdl_wait();                 // x comes from the previous kernel, which may also still read this workspace
+    if (blockIdx.x == 0)        // status word and K-split arrival counters of the GEMM that follows
+        for (int i = threadIdx.x; i < header_words16; i += 256) header[i] = make_uint4(0, 0, 0, 0);
     const float* row = x + blockIdx.x * ldx;
     float amax = 0.f;
     for (int i = threadIdx.x; i < cols; i += 256) amax = fmaxf(amax, fabsf(__ldcg(row + i)));
@@ -604,7 +613,8 @@ int launch_gemm(GemmArgs& a, int rows, int cols, int M, float* partial, const __
            rt * tt <= static_cast<int>((kGemmHeader - 256) / sizeof(unsigned int)))
         KS *= 2;
     a.partial = partial;
-    gemm_tc_kernel<NT, KM><<<dim3(rt, tt, KS), kGmThreads, smem, s>>>(a, xmap);
+    cudaError_t le = launch_pdl(gemm_tc_kernel<NT, KM>, dim3(rt, tt, KS), dim3(kGmThreads), smem, s, a, xmap);
+    if (le != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "rwkvq_gemm: %s", cudaGetErrorString(le));
     return RWKVQ_OK;
 }
 }  // namespace
@@ -652,8 +662,10 @@ int rwkvq_gemm(const rwkvq_qtensor* t, const float* x, int M, int64_t ldx, float
     __half* x16 = reinterpret_cast<__half*>(ws + gemm_ws_x16_off(M));
     a.row_scale = scale;
     a.trace = g_gemm_trace;
-    cudaMemsetAsync(ws, 0, kGemmHeader, s);
-    row_scale_kernel<<<M, 256, 0, s>>>(x, ldx, t->cols, scale, x16, static_cast<long long>(x16_pitch(t->cols)));
+    cudaError_t le = launch_pdl(row_scale_kernel, dim3(M), dim3(256), 0, s, x, static_cast<long long>(ldx), t->cols, scale, x16,
+                                static_cast<long long>(x16_pitch(t->cols)), reinterpret_cast<uint4*>(ws),
+                                static_cast<int>(kGemmHeader / 16));
+    if (le != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "rwkvq_gemm(pre-pass): %s", cudaGetErrorString(le));
     if (M <= 16) rc = launch_gemm<16, 256>(a, t->rows, t->cols, M, partial, x16, s);
     else if (M <= 32) rc = launch_gemm<32, 256>(a, t->rows, t->cols, M, partial, x16, s);
     else if (M <= 64) rc = launch_gemm<64, 256>(a, t->rows, t->cols, M, partial, x16, s);
