@@ -32,7 +32,12 @@ class _QuantLinearBase:
         x2, lead = ops.as_rows(x, self.in_features)
         if resid is not None:
             resid = resid.reshape(-1, self.out_features).contiguous()
-        y = self.dq.gemv(x2, epilogue, resid)
+        if x2.shape[0] >= GEMM_MIN_BATCH_NB and self.dq.kind in ("sb6", "sym"):
+            # the reference's crossover (quant_linear_gw.py:846-849, quant_linear_sym.py:481-484):
+            # its dequant + fp16 matmul; here the dequantisation is fused into the tensor-core GEMM
+            y = ops.gemm(self.dq, x2.float(), epilogue, resid)
+        else:
+            y = self.dq.gemv(x2, epilogue, resid)
         return y.reshape(*lead, self.out_features)
 
     def _dequant_w(self, dtype=torch.float32) -> torch.Tensor:

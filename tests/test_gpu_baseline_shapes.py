@@ -49,6 +49,10 @@ def test_layer_linear_shapes_batches(cuda_lib, layout, bits, rows, cols):
     assert torch.equal(outs[8][:1], outs[1]) and torch.equal(outs[64][:8], outs[8])
     # the tensor-core GEMM (what the model uses beyond 2 rows): fp16 activations scaled per token
     from rwkv_quant_b200.backends.cuda import ops
+    x512 = torch.randn(512, cols, generator=g).cuda()           # at and beyond 128 rows the operator itself
+    y = lin(x512)                                               # switches to the GEMM, as the reference does
+    ref = x512.double() @ w64.t()
+    assert (y.double() - ref).abs().max().item() <= TOL * ref.abs().max().item(), (layout, bits, 512)
     for n in (8, 64):
         y = ops.gemm(lin.dq, x64[:n], check=True)
         ref = x64[:n].double() @ w64.t()
