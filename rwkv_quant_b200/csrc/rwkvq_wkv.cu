@@ -71,24 +71,30 @@ __global__ void __launch_bounds__(256, DEEP ? 2 : 4) wkv7_kernel(const WkvArgs p
         const float4* Bv = reinterpret_cast<const float4*>(sh[cur][3] + part * 20);
         const float4* R = reinterpret_cast<const float4*>(sh[cur][4] + part * 20);
         const float vv = shv[cur][dv];
-        float sa = 0.f;
+        // four independent partial sums per dot product (a chain of 16 dependent FMAs is the
+        // longest link of a step otherwise), combined pairwise
+        float ps[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float4 a4 = A[i];
-            sa = fmaf(h[4 * i], a4.x, sa); sa = fmaf(h[4 * i + 1], a4.y, sa);
-            sa = fmaf(h[4 * i + 2], a4.z, sa); sa = fmaf(h[4 * i + 3], a4.w, sa);
+            ps[i] = h[4 * i] * a4.x;
+            ps[i] = fmaf(h[4 * i + 1], a4.y, ps[i]);
+            ps[i] = fmaf(h[4 * i + 2], a4.z, ps[i]);
+            ps[i] = fmaf(h[4 * i + 3], a4.w, ps[i]);
         }
+        float sa = (ps[0] + ps[1]) + (ps[2] + ps[3]);
         sa += __shfl_xor_sync(0xFFFFFFFFu, sa, 1);
         sa += __shfl_xor_sync(0xFFFFFFFFu, sa, 2);
-        float y = 0.f;
+        float py[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float4 w4 = W[i], k4 = K[i], b4 = Bv[i], r4 = R[i];
-            h[4 * i] = fmaf(w4.x, h[4 * i], fmaf(vv, k4.x, sa * b4.x));             y = fmaf(h[4 * i], r4.x, y);
-            h[4 * i + 1] = fmaf(w4.y, h[4 * i + 1], fmaf(vv, k4.y, sa * b4.y));     y = fmaf(h[4 * i + 1], r4.y, y);
-            h[4 * i + 2] = fmaf(w4.z, h[4 * i + 2], fmaf(vv, k4.z, sa * b4.z));     y = fmaf(h[4 * i + 2], r4.z, y);
-            h[4 * i + 3] = fmaf(w4.w, h[4 * i + 3], fmaf(vv, k4.w, sa * b4.w));     y = fmaf(h[4 * i + 3], r4.w, y);
+            h[4 * i] = fmaf(w4.x, h[4 * i], fmaf(vv, k4.x, sa * b4.x));             py[i] = h[4 * i] * r4.x;
+            h[4 * i + 1] = fmaf(w4.y, h[4 * i + 1], fmaf(vv, k4.y, sa * b4.y));     py[i] = fmaf(h[4 * i + 1], r4.y, py[i]);
+            h[4 * i + 2] = fmaf(w4.z, h[4 * i + 2], fmaf(vv, k4.z, sa * b4.z));     py[i] = fmaf(h[4 * i + 2], r4.z, py[i]);
+            h[4 * i + 3] = fmaf(w4.w, h[4 * i + 3], fmaf(vv, k4.w, sa * b4.w));     py[i] = fmaf(h[4 * i + 3], r4.w, py[i]);
         }
+        float y = (py[0] + py[1]) + (py[2] + py[3]);
         y += __shfl_xor_sync(0xFFFFFFFFu, y, 1);
         y += __shfl_xor_sync(0xFFFFFFFFu, y, 2);
         if (part == 0) p.out[((static_cast<size_t>(bi) * p.T + t) * p.H + hi) * kS + dv] = y;
