@@ -240,6 +240,10 @@ int rwkvq_wkv_tail(const float* wkv, const float* r, const float* k, const float
 int rwkvq_seq_ln_shift_mix(const float* x, const float* ln_w, const float* ln_b, const float* shift_in,
                            const float* mix, int n_mix, float* out, float* shift_out, int B, int T, int D,
                            void* stream);
+/* x fp32 [rows, cols] -> out fp16 [rows, 2 * cols] = [fp16(x) | fp16(x - fp16(x))]: the operand of the
+ * dense LoRA products of long sequences (x @ W = [hi | lo] @ [W; W] on fp16 tensor cores, fp32
+ * accumulation; the reference casts x to fp16 there: quant_model.py:204-208). */
+int rwkvq_split_fp16(const float* x, void* out_fp16, int64_t rows, int cols, void* stream);
 int rwkvq_seq_tmix_pre(const float* k, const float* v, const float* yw, const float* ya, const float* yv,
                        const float* v_first, const float* w0, const float* a0, const float* v0,
                        const float* k_k, const float* k_a, float* w, float* k2, float* v2, float* neg_kk,

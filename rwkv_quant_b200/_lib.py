@@ -88,6 +88,7 @@ _PROTOS = {
     "rwkvq_gemm_set_trace": (None, [C.c_void_p]),
     "rwkvq_seq_ln_shift_mix": (C.c_int, [C.c_void_p] * 5 + [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                          C.c_void_p]),
+    "rwkvq_split_fp16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
     "rwkvq_seq_tmix_pre": (C.c_int, [C.c_void_p] * 16 + [C.c_int64, C.c_int, C.c_void_p]),
     "rwkvq_tp_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "rwkvq_tp_free": (C.c_int, [C.c_void_p]),

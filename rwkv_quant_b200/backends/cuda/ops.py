@@ -288,6 +288,16 @@ def seq_ln_shift_mix(x: torch.Tensor, ln_w, ln_b, shift_in: Optional[torch.Tenso
     return out, new_shift
 
 
+def split_fp16(x: torch.Tensor) -> torch.Tensor:
+    """x fp32 [N, K] -> fp16 [N, 2K] = [hi | lo], hi + lo = x to ~2^-22 relative."""
+    _require_cuda(x)
+    x = x.float().contiguous()
+    out = torch.empty((x.shape[0], 2 * x.shape[1]), dtype=torch.float16, device=x.device)
+    _lib.check(_lib.load().rwkvq_split_fp16(x.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1], _lib.stream_ptr()),
+               "rwkvq_split_fp16")
+    return out
+
+
 def seq_tmix_pre(k, v, yw, ya, yv, v_first, w0, a0, v0, k_k, k_a, n_head: int):
     """[N, D] fp32 inputs -> (w, k2, v2, -kk, kk*a), each [N, D]; yv / v_first None on layer 0."""
     _require_cuda(k, v, yw, ya)

@@ -203,12 +203,14 @@ class QuantRWKV7:
         w = self._lora_dense.get(id(dq))
         if w is None:                                   # values are exactly fp16 by the loader's policy
             w = ops.dequant(dq.bufs, dq.meta, torch.float32, True).half()
+            w = torch.cat([w, w], dim=0).contiguous()   # stacked twice: see split_fp16
             self._lora_dense[id(dq)] = w
-        # x = hi + lo with both halves fp16: two tensor-core GEMMs with fp32 accumulation give
-        # x @ W to ~2^-22 relative (a plain fp32 GEMM runs on the SIMT pipes, 10x slower)
-        hi = x.half()
-        lo = (x - hi.float()).half()
-        y = torch.mm(hi, w, out_dtype=torch.float32) + torch.mm(lo, w, out_dtype=torch.float32)
+        # x = hi + lo with both halves fp16: [hi | lo] @ [W; W] on the tensor cores with fp32
+        # accumulation gives x @ W to ~2^-22 relative (a plain fp32 GEMM runs on the SIMT pipes)
+        if x.shape[1] % 2:
+            y = x @ w[: x.shape[1]].float()
+        else:
+            y = torch.mm(ops.split_fp16(x), w, out_dtype=torch.float32)
         return torch.tanh(y) if act == 1 else torch.sigmoid(y) if act == 2 else y
 
     def _block_seq(self, i, L, x, v_first, state):

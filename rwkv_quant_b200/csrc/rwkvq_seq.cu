@@ -111,6 +111,25 @@ __global__ void __launch_bounds__(256) seq_tmix_pre_kernel(const TmixPreArgs p) 
     }
 }
 
+// x fp32 [rows, cols] -> out fp16 [rows, 2 * cols] = [hi | lo] with hi = fp16(x), lo = fp16(x - hi):
+// a product of [hi | lo] with a matrix stacked twice equals x @ W to ~2^-22 relative while running
+// on the fp16 tensor cores.  One pass over x.
+__global__ void __launch_bounds__(256) split_fp16_kernel(const float* __restrict__ x, __half* __restrict__ out,
+                                                         long long n_pairs, int cols) {
+    const int half_cols = cols >> 1;
+    for (long long i = blockIdx.x * 256ll + threadIdx.x; i < n_pairs; i += gridDim.x * 256ll) {
+        const long long r = i / half_cols;
+        const int c = static_cast<int>(i % half_cols) * 2;
+        const float2 v = *reinterpret_cast<const float2*>(x + r * cols + c);
+        const __half2 hi = __floats2half2_rn(v.x, v.y);
+        const float2 hf = __half22float2(hi);
+        const __half2 lo = __floats2half2_rn(v.x - hf.x, v.y - hf.y);
+        __half* o = out + r * 2 * cols + c;
+        *reinterpret_cast<__half2*>(o) = hi;
+        *reinterpret_cast<__half2*>(o + cols) = lo;
+    }
+}
+
 }  // namespace rwkvq
 
 using namespace rwkvq;
@@ -148,6 +167,19 @@ int rwkvq_seq_tmix_pre(const float* k, const float* v, const float* yw, const fl
     RWKVQ_REQUIRE(blocks < (1ll << 31), RWKVQ_E_LIMIT, "rwkvq_seq_tmix_pre: too many tokens");
     seq_tmix_pre_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
     return check_launch("rwkvq_seq_tmix_pre");
+}
+
+int rwkvq_split_fp16(const float* x, void* out_fp16, int64_t rows, int cols, void* stream) {
+    RWKVQ_REQUIRE(x && out_fp16, RWKVQ_E_NULL, "rwkvq_split_fp16: null pointer");
+    RWKVQ_REQUIRE(rows >= 1 && cols >= 2 && cols % 2 == 0, RWKVQ_E_SHAPE, "rwkvq_split_fp16: rows=%lld cols=%d (even)",
+                  (long long)rows, cols);
+    RWKVQ_REQUIRE(aligned(x, 8) && aligned(out_fp16, 4), RWKVQ_E_ALIGN, "rwkvq_split_fp16: x needs 8-byte, out 4-byte alignment");
+    const long long n_pairs = rows * (cols / 2);
+    long long blocks = (n_pairs + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    split_fp16_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, static_cast<__half*>(out_fp16), n_pairs, cols);
+    return check_launch("rwkvq_split_fp16");
 }
 
 }  // extern "C"

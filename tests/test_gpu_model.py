@@ -244,3 +244,24 @@ def test_sequence_glue_kernels_against_fp32_torch(cuda_lib):
         rv = v if layer0 else v + (vf - v) * torch.sigmoid(yv + v0)
         for got, ref, nm in ((w, rw, "w"), (k2, rk, "k"), (v2, rv, "v"), (na, -kk, "-kk"), (nb, kk * ra, "kk*a")):
             assert (got - ref).abs().max().item() <= 3e-6 * ref.abs().max().item() + 1e-6, (layer0, nm)
+
+
+def test_split_fp16_and_stacked_lora_product(cuda_lib):
+    """rwkvq_split_fp16: [hi | lo] with hi = fp16(x) and hi + lo = x to 2^-21 of |x|; the product with
+    a twice-stacked fp16 matrix equals the fp64 product to 1e-5 of its scale (fp32 accumulation on the
+    tensor cores over K = 512 terms; a plain fp16 product of x.half() would be off by ~5e-4)."""
+    from rwkv_quant_b200.backends.cuda import ops
+    g = torch.Generator().manual_seed(31)
+    x = (torch.randn(37, 256, generator=g) * 3).cuda()
+    s = ops.split_fp16(x)
+    assert s.shape == (37, 512) and s.dtype == torch.float16
+    hi, lo = s[:, :256], s[:, 256:]
+    assert torch.equal(hi, x.half())
+    assert ((hi.double() + lo.double()) - x.double()).abs().max().item() <= 2.0 ** -21 * x.abs().max().item()
+    w = (torch.randn(256, 96, generator=g) * 0.05).cuda().half()
+    y = torch.mm(s, torch.cat([w, w], 0), out_dtype=torch.float32)
+    ref = x.double() @ w.double()
+    err = (y.double() - ref).abs().max().item() / ref.abs().max().item()
+    assert err <= 1e-5, err
+    plain = (torch.mm(x.half(), w, out_dtype=torch.float32).double() - ref).abs().max().item() / ref.abs().max().item()
+    assert err < 0.1 * plain, (err, plain)
