@@ -4,11 +4,9 @@
 //     sa = S a;   S = S diag(w) + sa b^T + v k^T;   y = S r
 // (call site backends/metal/quant_model.py:118-125, math models/rwkv7_ref.py:244-254,
 // prototype kernel tests/bench_wkv_shared.py:64-97).  The 64 state rows are
-// independent, so a CTA of 256 threads owns one (batch, head): thread (dv, part)
-// keeps 16 columns of row dv in registers for the whole scan, and the two dot
-// products per step are finished with two quad shuffles.  The r/w/k/v/a/b rows of
-// following steps are fetched while step t is computed (double-buffered shared memory, one
-// barrier per step).
+// independent, so a CTA owns one (batch, head) and its threads keep tiles of the state in
+// registers for the whole scan; the two dot products per step end in shuffles.  The
+// r/w/k/v/a/b rows of following steps are staged in shared memory ahead of time (see below).
 #include "rwkvq_common.cuh"
 
 namespace rwkvq {
@@ -23,115 +21,189 @@ struct WkvArgs {
     int B, T, H;
 };
 
-// Shared-memory rows of a, w, k, b, r: the 16 values of column quarter `part` start at float
-// part * 20 (4 floats of padding per quarter), so that the four quarters a warp reads with one
-// 128-bit load fall into different bank groups: one wavefront per load instead of 2 x 4.
-constexpr int kRowPad = 80;
-__device__ __forceinline__ int padded(int c) { return (c >> 4) * 20 + (c & 15); }
+// Thread tile.  What bounds a step is the shared-memory return path (128 bytes per clock and SM:
+// every float a thread loads costs its warp one cycle, broadcast or not), so a thread owns a
+// tile of R state rows x 8 columns: per step it loads 8 columns of a, w, k, b, r and R values of v
+// (40 + R floats for 8 R state elements; one row x 16 columns would load 81 for 16).  Eight lanes
+// span the 64 columns of a row group, so a dot product ends in three shuffle stages; a warp holds
+// four row groups.  R = 4: 128 threads, the short dependency chain for grids that leave SMs
+// nearly empty; R = 8: 64 threads, least shared-memory traffic per step for full grids.
+//
+// Staging: the r/w/k/v/a/b rows of kWkvChunk steps form one chunk; a ring of kWkvStages chunks in
+// shared memory is filled with 16-byte cp.async copies issued two chunks (16 steps) ahead, so a load
+// from HBM has thousands of cycles to land.  Within a chunk the warps run free of one another,
+// and the CTA meets at one barrier per chunk, which also releases the ring slot that is refilled next.
+constexpr int kWkvChunk = 8;
+constexpr int kWkvStages = 3;
+constexpr int kWkvStepFloats = 6 * kS;                            // a, w, k, b, r, v
+constexpr int kWkvChunkFloats = kWkvChunk * kWkvStepFloats;
+constexpr size_t kWkvSmemBytes = sizeof(float) * kWkvStages * kWkvChunkFloats;
 
-// DEEP: the rows of step t+2 are requested while step t is computed (two register sets with fixed
-// roles); used when the grid leaves the SMs mostly empty and a step is shorter than a load from L2.
-// Otherwise one step ahead and 4 CTAs per SM.
-template <bool DEEP>
-__global__ void __launch_bounds__(256, DEEP ? 2 : 4) wkv7_kernel(const WkvArgs p) {
-    __shared__ __align__(16) float sh[2][5][kRowPad];
-    __shared__ float shv[2][kS];
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gmem_src) {
+    const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Sums y[0..R) over the 8 lanes of a row group, halving the number of live values at each stage
+// (a lane keeps the half its lane bit selects and sends the other); returns the total of row
+// `row` (also returned) - lanes 0..R-1 of the group end with distinct rows.
+template <int R>
+__device__ __forceinline__ float reduce_rows(float (&y)[R], int c, int& row) {
+    row = 0;
+    int n = R;
+#pragma unroll
+    for (int m = 1; m < 8; m <<= 1) {
+        if (n > 1) {
+            const int half = n >> 1;
+            const bool up = (c & m) != 0;
+#pragma unroll
+            for (int i = 0; i < R / 2; ++i) {
+                if (i < half) {
+                    const float send = up ? y[i] : y[i + half];
+                    const float keep = up ? y[i + half] : y[i];
+                    y[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, m);
+                }
+            }
+            row += up ? half : 0;
+            n = half;
+        } else {
+            y[0] += __shfl_xor_sync(0xFFFFFFFFu, y[0], m);
+        }
+    }
+    return y[0];
+}
+
+template <int R>
+__global__ void __launch_bounds__(512 / R, 4) wkv7_kernel(const WkvArgs p) {
+    constexpr int kThreads = 512 / R;
+    extern __shared__ __align__(16) float ring[];
     const int bh = blockIdx.x, bi = bh / p.H, hi = bh % p.H;
-    const int tid = threadIdx.x, dv = tid >> 2, part = tid & 3;
-    float h[16];
-    const size_t hbase = (static_cast<size_t>(bh) * kS + dv) * kS + part * 16;
-    if (p.h_in) {
+    const int tid = threadIdx.x, c = tid & 7, dv0 = (tid >> 3) * R;
+    float2 h[R][4];                               // rows dv0 + j, columns 8c + 2q, 8c + 2q + 1
+    const size_t hbase = (static_cast<size_t>(bh) * kS + dv0) * kS + c * 8;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float4 v4 = *reinterpret_cast<const float4*>(p.h_in + hbase + 4 * i);
-            h[4 * i] = v4.x; h[4 * i + 1] = v4.y; h[4 * i + 2] = v4.z; h[4 * i + 3] = v4.w;
-        }
-    } else {
+    for (int j = 0; j < R; ++j) {
+        if (p.h_in) {
+            const float4 lo4 = *reinterpret_cast<const float4*>(p.h_in + hbase + j * kS);
+            const float4 hi4 = *reinterpret_cast<const float4*>(p.h_in + hbase + j * kS + 4);
+            h[j][0] = make_float2(lo4.x, lo4.y); h[j][1] = make_float2(lo4.z, lo4.w);
+            h[j][2] = make_float2(hi4.x, hi4.y); h[j][3] = make_float2(hi4.z, hi4.w);
+        } else {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) h[i] = 0.f;
-    }
-    const float* src[6] = {p.a, p.w, p.k, p.b, p.r, p.v};
-    // thread `tid` stages value tid (and tid+256 for tid < 128) of the 6 x 64 row set
-    auto fetch = [&](int t, float& x0, float& x1) {
-        const size_t base = ((static_cast<size_t>(bi) * p.T + t) * p.H + hi) * kS;
-        x0 = src[tid >> 6][base + (tid & 63)];
-        x1 = 0.f;
-        if (tid < 128) x1 = src[4 + (tid >> 6)][base + (tid & 63)];
-    };
-    auto stash = [&](int buf, float x0, float x1) {
-        sh[buf][tid >> 6][padded(tid & 63)] = x0;
-        if (tid < 64) sh[buf][4][padded(tid)] = x1;
-        else if (tid < 128) shv[buf][tid & 63] = x1;
-    };
-    // one step of the recurrence on the rows staged in buffer `cur`
-    auto step = [&](int t, int cur) {
-        const float4* A = reinterpret_cast<const float4*>(sh[cur][0] + part * 20);
-        const float4* W = reinterpret_cast<const float4*>(sh[cur][1] + part * 20);
-        const float4* K = reinterpret_cast<const float4*>(sh[cur][2] + part * 20);
-        const float4* Bv = reinterpret_cast<const float4*>(sh[cur][3] + part * 20);
-        const float4* R = reinterpret_cast<const float4*>(sh[cur][4] + part * 20);
-        const float vv = shv[cur][dv];
-        // four independent partial sums per dot product (a chain of 16 dependent FMAs is the
-        // longest link of a step otherwise), combined pairwise
-        float ps[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float4 a4 = A[i];
-            ps[i] = h[4 * i] * a4.x;
-            ps[i] = fmaf(h[4 * i + 1], a4.y, ps[i]);
-            ps[i] = fmaf(h[4 * i + 2], a4.z, ps[i]);
-            ps[i] = fmaf(h[4 * i + 3], a4.w, ps[i]);
-        }
-        float sa = (ps[0] + ps[1]) + (ps[2] + ps[3]);
-        sa += __shfl_xor_sync(0xFFFFFFFFu, sa, 1);
-        sa += __shfl_xor_sync(0xFFFFFFFFu, sa, 2);
-        float py[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float4 w4 = W[i], k4 = K[i], b4 = Bv[i], r4 = R[i];
-            h[4 * i] = fmaf(w4.x, h[4 * i], fmaf(vv, k4.x, sa * b4.x));             py[i] = h[4 * i] * r4.x;
-            h[4 * i + 1] = fmaf(w4.y, h[4 * i + 1], fmaf(vv, k4.y, sa * b4.y));     py[i] = fmaf(h[4 * i + 1], r4.y, py[i]);
-            h[4 * i + 2] = fmaf(w4.z, h[4 * i + 2], fmaf(vv, k4.z, sa * b4.z));     py[i] = fmaf(h[4 * i + 2], r4.z, py[i]);
-            h[4 * i + 3] = fmaf(w4.w, h[4 * i + 3], fmaf(vv, k4.w, sa * b4.w));     py[i] = fmaf(h[4 * i + 3], r4.w, py[i]);
-        }
-        float y = (py[0] + py[1]) + (py[2] + py[3]);
-        y += __shfl_xor_sync(0xFFFFFFFFu, y, 1);
-        y += __shfl_xor_sync(0xFFFFFFFFu, y, 2);
-        if (part == 0) p.out[((static_cast<size_t>(bi) * p.T + t) * p.H + hi) * kS + dv] = y;
-    };
-    if (DEEP) {
-        float e0, e1, o0 = 0.f, o1 = 0.f;
-        fetch(0, e0, e1);
-        stash(0, e0, e1);
-        if (p.T > 1) fetch(1, o0, o1);
-        __syncthreads();
-        for (int t = 0; t < p.T; t += 2) {
-            if (t + 2 < p.T) fetch(t + 2, e0, e1);
-            step(t, 0);
-            if (t + 1 < p.T) stash(1, o0, o1);
-            __syncthreads();
-            if (t + 1 >= p.T) break;
-            if (t + 3 < p.T) fetch(t + 3, o0, o1);
-            step(t + 1, 1);
-            if (t + 2 < p.T) stash(0, e0, e1);
-            __syncthreads();
-        }
-    } else {
-        float x0, x1;
-        fetch(0, x0, x1);
-        stash(0, x0, x1);
-        __syncthreads();
-        for (int t = 0; t < p.T; ++t) {
-            const int cur = t & 1;
-            if (t + 1 < p.T) fetch(t + 1, x0, x1);
-            step(t, cur);
-            if (t + 1 < p.T) stash(cur ^ 1, x0, x1);
-            __syncthreads();
+            for (int q = 0; q < 4; ++q) h[j][q] = make_float2(0.f, 0.f);
         }
     }
+    const size_t row0 = (static_cast<size_t>(bi) * p.T * p.H + hi) * kS;     // step 0 of this (batch, head)
+    const size_t step_stride = static_cast<size_t>(p.H) * kS;
+    // Copy roles: a step is 96 pieces of 16 bytes (row q >> 4 of a, w, k, b, r, v; floats 4 (q & 15) ..).
+    // R = 4: thread q < 96 copies piece q of every step; R = 8: thread q < 48 copies pieces q and q + 48.
+    constexpr int kOwn = kThreads >= 96 ? 1 : 2, kCopiers = 96 / kOwn;
+    const float* cp_src[kOwn];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-        *reinterpret_cast<float4*>(p.h_out + hbase + 4 * i) = make_float4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
+    for (int o = 0; o < kOwn; ++o) {
+        const int q = (tid + o * kCopiers) % 96, row = q >> 4;
+        const float* base = row == 0 ? p.a : row == 1 ? p.w : row == 2 ? p.k : row == 3 ? p.b : row == 4 ? p.r : p.v;
+        cp_src[o] = base + row0 + (q & 15) * 4;
+    }
+    auto issue = [&](int chunk) {
+        if (tid >= kCopiers) return;
+        float* stage = ring + (chunk % kWkvStages) * kWkvChunkFloats + tid * 4;
+        const int t0 = chunk * kWkvChunk;
+#pragma unroll
+        for (int s = 0; s < kWkvChunk; ++s) {
+            if (t0 + s < p.T) {
+#pragma unroll
+                for (int o = 0; o < kOwn; ++o)
+                    cp_async16(stage + s * kWkvStepFloats + o * kCopiers * 4, cp_src[o] + (t0 + s) * step_stride);
+            }
+        }
+    };
+    // One step of the recurrence on the rows staged at `st`.  Packed fp32 arithmetic: two lanes per
+    // instruction, each lane an IEEE fma.
+    auto step = [&](int t, const float* st) {
+        float2 x[4], kv[4];
+        auto load8 = [&](int row, float2 (&d)[4]) {
+            const float4 lo4 = *reinterpret_cast<const float4*>(st + row * kS + c * 8);
+            const float4 hi4 = *reinterpret_cast<const float4*>(st + row * kS + c * 8 + 4);
+            d[0] = make_float2(lo4.x, lo4.y); d[1] = make_float2(lo4.z, lo4.w);
+            d[2] = make_float2(hi4.x, hi4.y); d[3] = make_float2(hi4.z, hi4.w);
+        };
+        float vv[R];
+#pragma unroll
+        for (int j = 0; j < R; j += 4) {
+            const float4 v4 = *reinterpret_cast<const float4*>(st + 5 * kS + dv0 + j);
+            vv[j] = v4.x; vv[j + 1] = v4.y; vv[j + 2] = v4.z; vv[j + 3] = v4.w;
+        }
+        load8(0, x);                                  // a
+        float sa[R];
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            float2 p0 = __fmul2_rn(h[j][0], x[0]), p1 = __fmul2_rn(h[j][1], x[1]);
+            p0 = __ffma2_rn(h[j][2], x[2], p0);
+            p1 = __ffma2_rn(h[j][3], x[3], p1);
+            p0 = __fadd2_rn(p0, p1);
+            sa[j] = p0.x + p0.y;
+        }
+#pragma unroll
+        for (int m = 1; m < 8; m <<= 1) {
+#pragma unroll
+            for (int j = 0; j < R; ++j) sa[j] += __shfl_xor_sync(0xFFFFFFFFu, sa[j], m);
+        }
+        load8(3, x);                                  // b
+        load8(2, kv);                                 // k
+        float2 u[R][4];                               // v k^T + sa b^T
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            const float2 sa2 = make_float2(sa[j], sa[j]), vv2 = make_float2(vv[j], vv[j]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) u[j][q] = __ffma2_rn(vv2, kv[q], __fmul2_rn(sa2, x[q]));
+        }
+        load8(1, x);                                  // w
+        load8(4, kv);                                 // r
+        float y[R];
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) h[j][q] = __ffma2_rn(x[q], h[j][q], u[j][q]);
+            float2 p0 = __fmul2_rn(h[j][0], kv[0]), p1 = __fmul2_rn(h[j][1], kv[1]);
+            p0 = __ffma2_rn(h[j][2], kv[2], p0);
+            p1 = __ffma2_rn(h[j][3], kv[3], p1);
+            p0 = __fadd2_rn(p0, p1);
+            y[j] = p0.x + p0.y;
+        }
+        int row;
+        const float total = reduce_rows<R>(y, c, row);
+        if (c < R) p.out[row0 + t * step_stride + dv0 + row] = total;
+    };
+    const int n_chunks = (p.T + kWkvChunk - 1) / kWkvChunk;
+#pragma unroll
+    for (int ch = 0; ch < kWkvStages - 1; ++ch) {
+        if (ch < n_chunks) issue(ch);
+        cp_async_commit();                       // empty groups keep the count uniform
+    }
+    for (int ch = 0; ch < n_chunks; ++ch) {
+        cp_async_wait<kWkvStages - 2>();         // this thread's pieces of chunk ch have landed
+        __syncthreads();                         // everybody's have, and chunk ch-1 is consumed
+        if (ch + kWkvStages - 1 < n_chunks) issue(ch + kWkvStages - 1);     // into the slot of chunk ch-1
+        cp_async_commit();
+        const float* stage = ring + (ch % kWkvStages) * kWkvChunkFloats;
+        const int t0 = ch * kWkvChunk, n = min(kWkvChunk, p.T - t0);
+        if (n == kWkvChunk) {
+#pragma unroll
+            for (int s = 0; s < kWkvChunk; ++s) step(t0 + s, stage + s * kWkvStepFloats);
+        } else {
+            for (int s = 0; s < n; ++s) step(t0 + s, stage + s * kWkvStepFloats);
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+        *reinterpret_cast<float4*>(p.h_out + hbase + j * kS) = make_float4(h[j][0].x, h[j][0].y, h[j][1].x, h[j][1].y);
+        *reinterpret_cast<float4*>(p.h_out + hbase + j * kS + 4) = make_float4(h[j][2].x, h[j][2].y, h[j][3].x, h[j][3].y);
+    }
 }
 
 // (group_norm(wkv) * ln_w + ln_b + (sum r*k*r_k) * v) * g per (row, head); a warp per
@@ -177,9 +249,12 @@ int rwkvq_wkv7(const float* r, const float* w, const float* k, const float* v, c
     RWKVQ_REQUIRE(head_size == kS, RWKVQ_E_SHAPE, "rwkvq_wkv7: head size %d, only 64 is built", head_size);
     RWKVQ_REQUIRE(B >= 1 && T >= 1 && H >= 1, RWKVQ_E_SHAPE, "rwkvq_wkv7: B=%d T=%d H=%d", B, T, H);
     RWKVQ_REQUIRE(aligned(h_out, 16) && aligned(h_in, 16), RWKVQ_E_ALIGN, "rwkvq_wkv7: state must be 16-byte aligned");
+    RWKVQ_REQUIRE(aligned(r, 16) && aligned(w, 16) && aligned(k, 16) && aligned(v, 16) && aligned(a, 16) && aligned(b, 16),
+                  RWKVQ_E_ALIGN, "rwkvq_wkv7: r/w/k/v/a/b must be 16-byte aligned");
     WkvArgs p{r, w, k, v, a, b, h_in, out, h_out, B, T, H};
-    if (B * H <= 2 * 148 && T > 2) wkv7_kernel<true><<<B * H, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    else wkv7_kernel<false><<<B * H, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (B * H > 2 * 148) wkv7_kernel<8><<<B * H, 64, kWkvSmemBytes, st>>>(p);
+    else wkv7_kernel<4><<<B * H, 128, kWkvSmemBytes, st>>>(p);
     return check_launch("rwkvq_wkv7");
 }
 

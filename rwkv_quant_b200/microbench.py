@@ -4,6 +4,7 @@
     python -m rwkv_quant_b200.microbench decode [--layers L] [--recipe R] [--steps S] [--batch B]
     python -m rwkv_quant_b200.microbench sweep          # GEMV shapes of the 1.5B model, GB/s each
     python -m rwkv_quant_b200.microbench prefill [--T 512] [--batch B] [--recipe R]
+    python -m rwkv_quant_b200.microbench wkv [--batch B] [--T 512] [--H 32]   # the WKV-7 scan alone
 
 `gemv` and `decode` do a handful of launches and exit (suitable under a profiler);
 `sweep` replays a ring of distinct weight buffers (working set >> L2) as a CUDA graph and
@@ -349,6 +350,37 @@ def sweep():
     time_ring("sb6", 4, 8192, 2048, n=8)
 
 
+def wkv(B, T, H, launches=6):
+    """rwkvq_wkv7 alone on random rows: microseconds per launch (inputs rotate over sets that
+    together exceed L2 when one set does not)."""
+    from .backends.cuda.wkv7 import wkv7_infer
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(5)
+    set_bytes = 7 * B * T * H * 64 * 4
+    n_sets = max(2, min(8, int(300e6 // set_bytes) + 1))
+    rnd = lambda: torch.randn(B, T, H, 64, device=dev, generator=g) * 0.5
+    sets = []
+    for _ in range(n_sets):
+        r, k, v = rnd(), rnd(), rnd()
+        w = torch.exp(-0.606531 * torch.sigmoid(rnd()))
+        kk = torch.nn.functional.normalize(rnd(), dim=-1)
+        sets.append((r, w, k, v, -kk, kk * torch.sigmoid(rnd())))
+    st = torch.zeros(B, H, 64, 64, device=dev)
+    for i in range(3):
+        wkv7_infer(*sets[i % n_sets], st)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(launches + 1)]
+    torch.cuda.synchronize()
+    ev[0].record()
+    for i in range(launches):
+        wkv7_infer(*sets[i % n_sets], st)
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    us = sorted(ev[i].elapsed_time(ev[i + 1]) * 1e3 for i in range(launches))
+    nb = set_bytes
+    print(f"wkv7 B={B} T={T} H={H}: median {us[len(us) // 2]:.1f} us  min {us[0]:.1f} us  "
+          f"({nb / 1e6:.1f} MB of rows, {nb / us[len(us) // 2] / 1e3:.0f} GB/s)", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -378,7 +410,13 @@ def main():
     gt.add_argument("--cols", type=int, default=2048)
     gs = sub.add_parser("gemm-sweep")
     gs.add_argument("--recipe", default="compression")
+    wk = sub.add_parser("wkv")
+    wk.add_argument("--batch", type=int, default=1); wk.add_argument("--T", type=int, default=512)
+    wk.add_argument("--H", type=int, default=32)
     a = ap.parse_args()
+    if a.cmd == "wkv":
+        wkv(a.batch, a.T, a.H)
+        return
     if a.cmd == "gemm":
         gemm_once(a.layout, a.bits, a.rows, a.cols, a.M, a.launches)
         return

@@ -21,7 +21,7 @@ pytestmark = pytest.mark.gpu
 
 # (B, T, H) of the reference's WKV gate (tests/test_wkv_infer_parity.py:34-36)
 WKV_CASES = [(1, 1, 32), (1, 3, 32), (1, 16, 32), (1, 512, 32), (1, 1, 40), (1, 512, 40), (1, 512, 16),
-             (2, 128, 32), (1, 7, 32)]
+             (2, 128, 32), (1, 7, 32), (1, 8, 32), (1, 9, 32), (2, 24, 16), (1, 25, 32), (3, 41, 4)]    # chunk edges (8 steps)
 
 
 def wkv_inputs(B, T, H, S=64):
