@@ -69,13 +69,14 @@ class OracleRWKV7:
         self.H = self.D // self.S
         self.V = manifest["vocab_size"]
         self.naming = manifest["naming"]
-        assert self.naming == "world", "the oracle covers world-naming checkpoints"
+        assert self.naming in ("world", "custom"), self.naming
         self._lin_mode = linear_weights
         self._mm = matmul or (lambda x, w: x @ w.T)
 
         self.emb = self._dense("emb.weight")
         self.head = self._linear("head.weight")
-        self.ln0 = (self._dense("blocks.0.ln0.weight"), self._dense("blocks.0.ln0.bias"))
+        ln0 = "ln0." if self.naming == "custom" else "blocks.0.ln0."     # quant_model.py:856-859
+        self.ln0 = (self._dense(ln0 + "weight"), self._dense(ln0 + "bias"))
         self.ln_out = (self._dense("ln_out.weight"), self._dense("ln_out.bias"))
         self.layers = [self._layer(i) for i in range(self.L)]
 
@@ -92,7 +93,33 @@ class OracleRWKV7:
             w = C.f32_to_bf16_rne(w)
         return np.ascontiguousarray(w, dtype=F32)
 
+    def _layer_custom(self, i):
+        """Custom naming (quant_model.py:317-340, 791): tmix./cmix. prefixes, LoRA pairs stored as
+        nn.Linear weights [out, in] (no transposition), the w0/a0/v0 vectors as *_lora_B.bias."""
+        p, a, f = f"blocks.{i}.", f"blocks.{i}.tmix.", f"blocks.{i}.cmix."
+        d = self._dense
+        lw = dict(
+            ln1=(d(p + "ln1.weight"), d(p + "ln1.bias")),
+            ln2=(d(p + "ln2.weight"), d(p + "ln2.bias")),
+            x=np.stack([d(a + n).reshape(-1) for n in ("x_r", "x_w", "x_k", "x_v", "x_a", "x_g")]),
+            w1=d(a + "w_lora_A.weight"), w2=d(a + "w_lora_B.weight"), w0=d(a + "w_lora_B.bias").reshape(-1),
+            a1=d(a + "a_lora_A.weight"), a2=d(a + "a_lora_B.weight"), a0=d(a + "a_lora_B.bias").reshape(-1),
+            g1=d(a + "g_lora_A.weight"), g2=d(a + "g_lora_B.weight"),
+            k_k=d(a + "k_k").reshape(self.H, self.S), k_a=d(a + "k_a").reshape(self.H, self.S),
+            r_k=d(a + "r_k").reshape(self.H, self.S),
+            ln_x=(d(a + "ln_x.weight"), d(a + "ln_x.bias")),
+            Wr=self._linear(a + "r_proj.weight"), Wk=self._linear(a + "k_proj.weight"),
+            Wv=self._linear(a + "v_proj.weight"), Wo=self._linear(a + "o_proj.weight"),
+            fx=d(f + "x_k").reshape(-1),
+            Wfk=self._linear(f + "key.weight"), Wfv=self._linear(f + "value.weight"))
+        if i > 0:
+            lw.update(v1=d(a + "v_lora_A.weight"), v2=d(a + "v_lora_B.weight"),
+                      v0=d(a + "v_lora_B.bias").reshape(-1))
+        return lw
+
     def _layer(self, i):
+        if self.naming == "custom":
+            return self._layer_custom(i)
         p, a, f = f"blocks.{i}.", f"blocks.{i}.att.", f"blocks.{i}.ffn."
         d = self._dense
         lw = dict(

@@ -140,6 +140,16 @@ class DeviceQT:
         qt.dense = w
         return DeviceQT(qt, device=w.device)
 
+    def transposed_dense(self) -> "DeviceQT":
+        """W^T as a dense bf16 tensor [cols, rows] (overrides applied): how a LoRA matrix stored
+        as an nn.Linear weight [out, in] is handed to the kernels, which read LoRA matrices
+        [in, out]."""
+        from ...formats.container import QuantizedTensor
+        w = self.dequant(torch.float32, True).t().contiguous().to(torch.bfloat16)
+        qt = QuantizedTensor(key=self.key, group="", bits=16, shape=(self.cols, self.rows))
+        qt.dense = w
+        return DeviceQT(qt, device=w.device)
+
     def _relayout(self):
         """Regroup the scale records / bit-planes for the decode kernels (same bytes,
         done once at load on the device)."""

@@ -49,8 +49,8 @@ class _Layer:
 
 class QuantRWKV7:
     def __init__(self, ckpt, device="cuda", gemm_min_batch=GEMM_MIN_BATCH_NB, gemv_max_batch=2):
-        if ckpt.naming != "world":
-            raise NotImplementedError("only world-naming checkpoints are supported")
+        if ckpt.naming not in ("world", "custom"):
+            raise NotImplementedError(f"checkpoint naming {ckpt.naming!r} (world or custom)")
         _lib.load(check_device=True)
         self.device = torch.device(device)
         self.naming = ckpt.naming
@@ -70,26 +70,39 @@ class QuantRWKV7:
         vec = lambda key: _dense_param(T[key], dev).reshape(-1)
 
         self.emb, self.head = dq("emb.weight"), dq("head.weight")
-        self.ln0 = (vec("blocks.0.ln0.weight"), vec("blocks.0.ln0.bias"))
+        custom = self.naming == "custom"                     # key schemes: quant_model.py:317-364, 791, 856-859
+        ln0 = "ln0." if custom else "blocks.0.ln0."
+        self.ln0 = (vec(ln0 + "weight"), vec(ln0 + "bias"))
         self.ln_out = (vec("ln_out.weight"), vec("ln_out.bias"))
+        proj = {"Wr": "r_proj", "Wk": "k_proj", "Wv": "v_proj", "Wo": "o_proj"} if custom else \
+               {"Wr": "receptance", "Wk": "key", "Wv": "value", "Wo": "output"}
         self.blocks = []
         for i in range(self.n_layer):
-            p, a, f = f"blocks.{i}.", f"blocks.{i}.att.", f"blocks.{i}.ffn."
+            p = f"blocks.{i}."
+            a, f = (p + "tmix.", p + "cmix.") if custom else (p + "att.", p + "ffn.")
             L = _Layer()
             L.ln1 = (vec(p + "ln1.weight"), vec(p + "ln1.bias"))
             L.ln2 = (vec(p + "ln2.weight"), vec(p + "ln2.bias"))
             L.x_mix = torch.stack([vec(a + n) for n in ("x_r", "x_w", "x_k", "x_v", "x_a", "x_g")]).contiguous()
-            L.w0, L.a0 = vec(a + "w0"), vec(a + "a0")
-            L.v0 = vec(a + "v0") if i > 0 else None
+            branches = ("w", "a", "g") + (("v",) if i > 0 else ())
+            L.v0 = L.v1 = L.v2 = None
+            for br in branches:
+                if custom:
+                    # nn.Linear weights [out, in] -> the [in, out] orientation the kernels read
+                    setattr(L, br + "1", dq(a + br + "_lora_A.weight").transposed_dense())
+                    setattr(L, br + "2", dq(a + br + "_lora_B.weight").transposed_dense())
+                    if br != "g":
+                        setattr(L, br + "0", vec(a + br + "_lora_B.bias"))
+                else:
+                    setattr(L, br + "1", dq(a + br + "1"))
+                    setattr(L, br + "2", dq(a + br + "2"))
+                    if br != "g":
+                        setattr(L, br + "0", vec(a + br + "0"))
             L.k_k, L.k_a, L.r_k = vec(a + "k_k"), vec(a + "k_a"), vec(a + "r_k")
             L.lnx = (vec(a + "ln_x.weight"), vec(a + "ln_x.bias"))
             L.ffn_x_k = vec(f + "x_k")
-            for nm in ("w1", "w2", "a1", "a2", "g1", "g2") + (("v1", "v2") if i > 0 else ()):
-                setattr(L, nm, dq(a + nm))
-            if i == 0:
-                L.v1 = L.v2 = None
-            L.Wr, L.Wk = dq(a + "receptance.weight"), dq(a + "key.weight")
-            L.Wv, L.Wo = dq(a + "value.weight"), dq(a + "output.weight")
+            for nm, key in proj.items():
+                setattr(L, nm, dq(a + key + ".weight"))
             L.Wfk, L.Wfv = dq(f + "key.weight"), dq(f + "value.weight")
             self.blocks.append(L)
         self.ffn_dim = self.blocks[0].Wfk.rows
@@ -196,8 +209,8 @@ class QuantRWKV7:
 
     def _lora_seq(self, dq, x, act):
         """x [N, in] @ W [in, out] for a LoRA tensor stored [in, out].  Few rows: the packed
-        kernel; many rows: a dense fp32 GEMM on the weights dequantised once (kept in the
-        loader's precision fp16(bf16(.)), 4 bytes per LoRA weight)."""
+        kernel; many rows: a tensor-core GEMM on the weights dequantised once (kept in the
+        loader's precision fp16(bf16(.)), stacked twice: 4 bytes per LoRA weight)."""
         if x.shape[0] <= 8:
             return ops.gemv_t(dq.bufs, dq.meta, x.contiguous(), act, True)
         w = self._lora_dense.get(id(dq))

@@ -1,6 +1,6 @@
 """Generate the golden fixtures of this directory from the UNMODIFIED reference.
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py [/path/to/reference] [all|codec|toy|custom]
 
 Needs the reference project importable (default /root/reference); the fixtures
 it writes are committed so that the tests run where the reference is absent.
@@ -17,6 +17,8 @@ it writes are committed so that the tests run where the reference is absent.
                        rwkv_quant.quantize() with both presets
   toy_<preset>_ref.npz token ids, RWKV7Ref (cpu, fp32) logits on the dequantised
                        state dict, residual-stream trace
+  toy_custom_<cfg>.rwkvq / _ref.npz  the same model under custom naming, written by the
+                       reference's writer.save(); RWKV7Ref logits
 """
 import hashlib
 import json
@@ -230,6 +232,75 @@ def make_toy_models():
               "absmax", float(logits.abs().max()))
 
 
+WORLD_TO_CUSTOM = {"receptance": "r_proj", "key": "k_proj", "value": "v_proj", "output": "o_proj"}
+
+
+def toy_custom_state_dict(**kw):
+    """The same random model under "custom" naming (tests/test_quant_model_smoke.py:31-73):
+    blocks.N.tmix.* / cmix.*, top-level ln0, LoRA pairs as nn.Linear weights [out, in] with the
+    world w0/a0/v0 vectors as the B biases."""
+    sd, out = toy_world_state_dict(**kw), {}
+    for k, v in sd.items():
+        parts = k.split(".")
+        if k.startswith("blocks.0.ln0."):
+            out["ln0." + parts[-1]] = v
+        elif len(parts) >= 4 and parts[2] == "att":
+            tp, nm = ".".join(parts[:2]) + ".tmix.", parts[3]
+            if nm in WORLD_TO_CUSTOM:
+                out[tp + WORLD_TO_CUSTOM[nm] + ".weight"] = v
+            elif len(nm) == 2 and nm[0] in "wavg" and nm[1] in "012":
+                if nm[1] == "0":
+                    out[tp + nm[0] + "_lora_B.bias"] = v.reshape(-1)
+                else:
+                    out[tp + nm[0] + "_lora_" + ("A" if nm[1] == "1" else "B") + ".weight"] = v.t().contiguous()
+            else:
+                out[tp + ".".join(parts[3:])] = v
+        elif len(parts) >= 4 and parts[2] == "ffn":
+            out[".".join(parts[:2]) + ".cmix." + ".".join(parts[3:])] = v
+        else:
+            out[k] = v
+    # layer 0 has no value-residual branch under custom naming
+    for k in [k for k in out if k.startswith("blocks.0.tmix.v_lora_")]:
+        del out[k]
+    return out
+
+
+def make_toy_custom():
+    """toy_custom_<cfg>.rwkvq: custom-naming checkpoints written by the reference's save() (the
+    int8 + SpQR configuration of tests/test_quant_parity.py:97 and the compression preset), with
+    RWKV7Ref logits on the dequantised weights."""
+    from safetensors.torch import save_file
+    from rwkv_quant.formats.writer import save
+    cfg_c = PRESETS["compression"]
+    cfg_c.act_stats_path = None
+    int8 = QuantConfig(proj=8, cmix=8, outlier_fracs={"proj": 0.02, "cmix": 0.01})
+    # d128: the dimensions of the reference's own model-level tests (D=128, H=2, V=256)
+    for name, cfg, (L, D, S, V) in (("int8", int8, (2, 256, 64, 512)), ("compression", cfg_c, (2, 256, 64, 512)),
+                                    ("d128_int8", int8, (2, 128, 64, 256))):
+        sd = toy_custom_state_dict(L=L, D=D, V=V, S=S)
+        idx = torch.from_numpy(np.random.default_rng(1).integers(1, V - 12, (2, 24)))
+        out = os.path.join(HERE, f"toy_custom_{name}.rwkvq")
+        save(sd, cfg, out, naming="custom", n_layer=L, n_embd=D, head_size=S, vocab_size=V)
+        deq = reader.load_dequantized(out)
+        d = f"/tmp/rwkvq_toy_custom_{name}"
+        os.makedirs(d, exist_ok=True)
+        save_file({k: v.contiguous() for k, v in deq.items()}, f"{d}/model.safetensors")
+        with open(f"{d}/config.json", "w") as f:
+            json.dump({"n_layer": L, "n_embd": D, "head_size": S, "vocab_size": V}, f)
+        model = RWKV7Ref(d, device="cpu", dtype=torch.float32)
+        with torch.no_grad():
+            logits = model.forward(idx)
+        np.savez_compressed(os.path.join(HERE, f"toy_custom_{name}_ref.npz"), idx=idx.numpy(),
+                            logits=logits.numpy().astype(np.float32))
+        print("custom", name, os.path.getsize(out), "bytes; logits", tuple(logits.shape),
+              "absmax", float(logits.abs().max()))
+
+
 if __name__ == "__main__":
-    make_codec_cases()
-    make_toy_models()
+    which = sys.argv[2] if len(sys.argv) > 2 else "all"
+    if which in ("all", "codec"):
+        make_codec_cases()
+    if which in ("all", "toy"):
+        make_toy_models()
+    if which in ("all", "custom"):
+        make_toy_custom()

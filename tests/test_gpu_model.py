@@ -128,6 +128,41 @@ def test_model_matches_oracle(cuda_lib, preset):
     assert relmax(hid.cpu().numpy(), rh) <= 1e-3
 
 
+@pytest.mark.parametrize("cfg", ["int8", "compression", "d128_int8"])
+def test_custom_naming_model(cuda_lib, cfg):
+    """Custom-naming checkpoints written by the reference (tmix./cmix. keys, LoRA pairs stored
+    [out, in] with biases; int8 + sparse overrides as in tests/test_quant_parity.py:97, and the
+    compression preset): sequence path, decode path and the graph decoder against the oracle and
+    against the reference's own RWKV7Ref logits (its model-level gate is 1e-2)."""
+    from rwkv_quant_b200.backends.cuda import QuantRWKV7
+    from rwkv_quant_b200.formats import load_raw
+    path = os.path.join(GOLDEN, f"toy_custom_{cfg}.rwkvq")
+    man, arr = oc.open_rwkvq(path)
+    z = np.load(os.path.join(GOLDEN, f"toy_custom_{cfg}_ref.npz"))
+    ck = load_raw(path)
+    assert ck.naming == "custom"
+    model = QuantRWKV7(ck)
+    # tensors with overrides reach the kernels as dense bf16: compare those with the oracle's bf16 linears
+    has_overrides = any(getattr(q, "outlier_indices", None) is not None and q.outlier_indices.numel() > 0
+                        for q in ck.tensors.values())
+    oracle = OracleRWKV7(man, arr, linear_weights="bf16" if has_overrides else "exact")
+    idx = z["idx"]
+    B, T = idx.shape
+    ref, _ = oracle.forward_stateful(idx, oracle.init_state(B))
+    lo, _ = model.forward_stateful(idx, model.init_state(B))
+    d_seq = relmax(lo.cpu().numpy(), ref)
+    st, outs = model.init_state(B), []
+    for t in range(T):
+        lo1, st = model.forward_stateful(idx[:, t:t + 1], st)
+        outs.append(lo1.cpu().numpy())
+    d_dec = relmax(np.concatenate(outs, 1), ref)
+    print(f"custom {cfg}: sequence {d_seq:.2e}, decode {d_dec:.2e}, vs RWKV7Ref {relmax(lo.cpu().numpy(), z['logits']):.2e}")
+    assert d_seq <= 1e-3 and d_dec <= 1e-3
+    assert relmax(lo.cpu().numpy(), z["logits"]) <= 1e-2
+    toks, _ = model.generate(idx[:, :6], 8)           # the graph decoder runs on it too
+    assert toks.shape == (B, 8)
+
+
 @pytest.mark.parametrize("recipe", ["compression", "reduction", "sb6_int6", "compression_eh8"])
 def test_greedy_decode_graph_and_eager(cuda_lib, recipe):
     """Synthetic toy build: greedy tokens of the CUDA-graph decoder == eager decoder,

@@ -34,6 +34,19 @@ def test_matches_reference_forward(preset):
     print(f"{preset}: exact-linears vs all-bf16 reference forward relmax {d:.3e}")
 
 
+@pytest.mark.parametrize("cfg", ["int8", "compression", "d128_int8"])
+def test_custom_naming_matches_reference_forward(cfg):
+    """Custom-naming checkpoints written by the reference's writer.save() (tmix./cmix. keys, LoRA
+    pairs as [out, in] linears with biases; tests/test_quant_parity.py:97-118)."""
+    man, arr = oc.open_rwkvq(os.path.join(GOLDEN, f"toy_custom_{cfg}.rwkvq"))
+    assert man["naming"] == "custom"
+    z = np.load(os.path.join(GOLDEN, f"toy_custom_{cfg}_ref.npz"))
+    m = OracleRWKV7(man, arr, linear_weights="bf16")
+    hidden, _ = m.forward_hidden(z["idx"], m.init_state(z["idx"].shape[0]))
+    assert relmax(hidden @ m.head.T, z["logits"]) < 5e-6
+    assert relmax(OracleRWKV7(man, arr)(z["idx"]), z["logits"]) < 1e-2
+
+
 @pytest.mark.parametrize("preset", ["reduction", "compression"])
 def test_streaming_equals_whole(preset):
     """Whole prompt == chunks == token by token (tests/test_streaming_inference.py)."""
