@@ -154,6 +154,13 @@ size_t rwkvq_gemm_workspace_bytes_for(int M, int max_cols);
 void rwkvq_gemm_set_trace(void* buf512);
 int rwkvq_gemm(const rwkvq_qtensor* t, const float* x, int M, int64_t ldx, float* y, int64_t ldy,
                int epilogue, const float* resid, void* workspace, size_t workspace_bytes, void* stream);
+/* The same product on activations the caller has already brought into the form the kernel reads
+ * (rwkvq_seq_ln_shift_mix_prep writes it): x16 fp16 [M, rwkvq_gemm_x16_pitch(IN)] = x * row_scale[m],
+ * row_scale [M] fp32 powers of two.  The workspace (same size rule) then only carries the header
+ * and the split-K tiles. */
+size_t rwkvq_gemm_x16_pitch(int cols);
+int rwkvq_gemm_x16(const rwkvq_qtensor* t, const void* x16, const float* row_scale, int M, float* y, int64_t ldy,
+                   int epilogue, const float* resid, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * K same-shape matrices, K different inputs, one launch: y[k] = W_k x[k].
@@ -240,6 +247,15 @@ int rwkvq_wkv_tail(const float* wkv, const float* r, const float* k, const float
 int rwkvq_seq_ln_shift_mix(const float* x, const float* ln_w, const float* ln_b, const float* shift_in,
                            const float* mix, int n_mix, float* out, float* shift_out, int B, int T, int D,
                            void* stream);
+/* rwkvq_seq_ln_shift_mix with each mix row written in the form(s) its consumers read, selected
+ * per mix by modes[m] (host array; bit 0: scaled fp16 copy + scale for rwkvq_gemm_x16 into
+ * out_x16[m] [N, D + 64] / out_scale[m] [N]; bit 1: fp16 hi/lo split as rwkvq_split_fp16 into
+ * out_split[m] [N, 2 D]; bit 2: fp32 row into out_f32[m] [N, D]).  Pointer tables are host arrays
+ * of n_mix device pointers (entries of unselected forms are ignored).  D even. */
+int rwkvq_seq_ln_shift_mix_prep(const float* x, const float* ln_w, const float* ln_b, const float* shift_in,
+                                const float* mix, int n_mix, const int* modes, void* const* out_x16,
+                                float* const* out_scale, void* const* out_split, float* const* out_f32,
+                                float* shift_out, int B, int T, int D, void* stream);
 /* x fp32 [rows, cols] -> out fp16 [rows, 2 * cols] = [fp16(x) | fp16(x - fp16(x))]: the operand of the
  * dense LoRA products of long sequences (x @ W = [hi | lo] @ [W; W] on fp16 tensor cores, fp32
  * accumulation; the reference casts x to fp16 there: quant_model.py:204-208). */

@@ -89,6 +89,13 @@ _PROTOS = {
     "rwkvq_seq_ln_shift_mix": (C.c_int, [C.c_void_p] * 5 + [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                          C.c_void_p]),
     "rwkvq_split_fp16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
+    "rwkvq_gemm_x16_pitch": (C.c_size_t, [C.c_int]),
+    "rwkvq_gemm_x16": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int64,
+                                 C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "rwkvq_seq_ln_shift_mix_prep": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                              C.POINTER(C.c_int), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                              C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p,
+                                              C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "rwkvq_seq_tmix_pre": (C.c_int, [C.c_void_p] * 16 + [C.c_int64, C.c_int, C.c_void_p]),
     "rwkvq_tp_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "rwkvq_tp_free": (C.c_int, [C.c_void_p]),

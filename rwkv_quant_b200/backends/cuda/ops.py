@@ -271,6 +271,71 @@ def gemm(dq: "DeviceQT", x: torch.Tensor, epilogue: int = 0, resid: Optional[tor
     return y
 
 
+class PreparedRows:
+    """Activation rows in the forms their consumers read (made by ``seq_ln_shift_mix_prep``):
+    ``x16``/``scale`` for ``gemm_x16``, ``split`` ([hi | lo] fp16) for the LoRA products, ``f32``."""
+    __slots__ = ("x16", "scale", "split", "f32", "n", "cols")
+
+    def __init__(self, n, cols):
+        self.x16 = self.scale = self.split = self.f32 = None
+        self.n, self.cols = n, cols
+
+
+PREP_SCALED, PREP_SPLIT, PREP_F32 = 1, 2, 4
+
+
+def gemm_x16(dq: "DeviceQT", rows: PreparedRows, epilogue: int = 0, resid: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``gemm`` on rows already scaled and rounded to fp16 (no pre-pass over the activations)."""
+    _require_cuda(rows.x16, resid)
+    lib = _lib.load()
+    m = rows.n
+    nws = lib.rwkvq_gemm_workspace_bytes_for(m, 0)
+    ws = torch.empty(nws, dtype=torch.uint8, device=rows.x16.device)
+    y = torch.empty((m, dq.rows), dtype=torch.float32, device=rows.x16.device)
+    _lib.check(lib.rwkvq_gemm_x16(C.byref(dq.struct), rows.x16.data_ptr(), rows.scale.data_ptr(), m, y.data_ptr(),
+                                  y.stride(0), epilogue, _lib.ptr(resid), ws.data_ptr(), nws, _lib.stream_ptr()),
+               "rwkvq_gemm_x16")
+    return y
+
+
+def seq_ln_shift_mix_prep(x: torch.Tensor, ln_w, ln_b, shift_in: Optional[torch.Tensor], mix: torch.Tensor,
+                          modes: Sequence[int]):
+    """``seq_ln_shift_mix`` writing every mix row in the forms ``modes[m]`` selects (PREP_SCALED |
+    PREP_SPLIT | PREP_F32) -> ([PreparedRows] * n_mix, new shift state [B, 1, D])."""
+    _require_cuda(x, shift_in, mix)
+    lib = _lib.load()
+    B, T, D = x.shape
+    N = B * T
+    x = x.float().contiguous()
+    mix2 = mix.reshape(-1, D).contiguous()
+    n_mix = mix2.shape[0]
+    assert len(modes) == n_mix
+    pitch = lib.rwkvq_gemm_x16_pitch(D)
+    dev = x.device
+    rows, tabs = [], [[None] * n_mix for _ in range(4)]
+    for m, mode in enumerate(modes):
+        r = PreparedRows(N, D)
+        if mode & PREP_SCALED:
+            r.x16 = torch.empty((N, pitch), dtype=torch.float16, device=dev)
+            r.scale = torch.empty(N, dtype=torch.float32, device=dev)
+            tabs[0][m], tabs[1][m] = r.x16.data_ptr(), r.scale.data_ptr()
+        if mode & PREP_SPLIT:
+            r.split = torch.empty((N, 2 * D), dtype=torch.float16, device=dev)
+            tabs[2][m] = r.split.data_ptr()
+        if mode & PREP_F32:
+            r.f32 = torch.empty((N, D), dtype=torch.float32, device=dev)
+            tabs[3][m] = r.f32.data_ptr()
+        rows.append(r)
+    new_shift = torch.empty((B, 1, D), dtype=torch.float32, device=dev)
+    sin = None if shift_in is None else shift_in.float().contiguous()
+    ctab = [(C.c_void_p * n_mix)(*t) for t in tabs]
+    _lib.check(lib.rwkvq_seq_ln_shift_mix_prep(x.data_ptr(), ln_w.data_ptr(), ln_b.data_ptr(), _lib.ptr(sin),
+                                               mix2.data_ptr(), n_mix, (C.c_int * n_mix)(*modes), ctab[0], ctab[1],
+                                               ctab[2], ctab[3], new_shift.data_ptr(), B, T, D, _lib.stream_ptr()),
+               "rwkvq_seq_ln_shift_mix_prep")
+    return rows, new_shift
+
+
 def gemv_fused(dqts: Sequence[DeviceQT], xstack: torch.Tensor) -> torch.Tensor:
     """K same-shape matrices, K inputs [K, IN] -> [K, OUT], one launch."""
     _require_cuda(xstack)

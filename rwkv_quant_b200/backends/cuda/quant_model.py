@@ -111,6 +111,7 @@ class QuantRWKV7:
         self._build_struct()
         self._ws = {}
         self._lora_dense = {}
+        self.fused_prep = True       # sequence path: LN/shift/lerp rows written in their consumers' forms
         torch.cuda.synchronize(dev)
 
     # ------------------------------------------------------------------ C descriptors
@@ -213,11 +214,7 @@ class QuantRWKV7:
         loader's precision fp16(bf16(.)), stacked twice: 4 bytes per LoRA weight)."""
         if x.shape[0] <= 8:
             return ops.gemv_t(dq.bufs, dq.meta, x.contiguous(), act, True)
-        w = self._lora_dense.get(id(dq))
-        if w is None:                                   # values are exactly fp16 by the loader's policy
-            w = ops.dequant(dq.bufs, dq.meta, torch.float32, True).half()
-            w = torch.cat([w, w], dim=0).contiguous()   # stacked twice: see split_fp16
-            self._lora_dense[id(dq)] = w
+        w = self._lora_stacked(dq)
         # x = hi + lo with both halves fp16: [hi | lo] @ [W; W] on the tensor cores with fp32
         # accumulation gives x @ W to ~2^-22 relative (a plain fp32 GEMM runs on the SIMT pipes)
         if x.shape[1] % 2:
@@ -226,30 +223,71 @@ class QuantRWKV7:
             y = torch.mm(ops.split_fp16(x), w, out_dtype=torch.float32)
         return torch.tanh(y) if act == 1 else torch.sigmoid(y) if act == 2 else y
 
+    def _linear_rows(self, dq, rows, epilogue=_lib.EPI_NONE, resid=None):
+        """``_linear`` on rows prepared by ``seq_ln_shift_mix_prep`` (sb6 / sym tensors read the
+        scaled fp16 copy directly; other layouts take the fp32 rows)."""
+        if rows.x16 is not None and dq.kind in ("sb6", "sym"):
+            return ops.gemm_x16(dq, rows, epilogue, resid)
+        return self._linear(dq, rows.f32, epilogue, resid)
+
+    def _lora_rows(self, dq, rows, act):
+        """``_lora_seq`` on prepared rows: the [hi | lo] fp16 split times the twice-stacked matrix."""
+        if rows.split is None:
+            return self._lora_seq(dq, rows.f32, act)
+        y = torch.mm(rows.split, self._lora_stacked(dq), out_dtype=torch.float32)
+        return torch.tanh(y) if act == 1 else torch.sigmoid(y) if act == 2 else y
+
+    def _lora_stacked(self, dq):
+        w = self._lora_dense.get(id(dq))
+        if w is None:                                   # values are exactly fp16 by the loader's policy
+            w = ops.dequant(dq.bufs, dq.meta, torch.float32, True).half()
+            w = torch.cat([w, w], dim=0).contiguous()   # stacked twice: see split_fp16
+            self._lora_dense[id(dq)] = w
+        return w
+
+    def _prep_modes(self, N, lins):
+        """Which form each mix row is written in: the scaled fp16 copy when its linear runs on
+        the dequant-fused GEMM, else fp32."""
+        gemm = lambda dq: dq.kind in ("sb6", "sym") and N > self.gemv_max_batch
+        return [ops.PREP_SCALED if gemm(dq) else ops.PREP_F32 for dq in lins]
+
     def _block_seq(self, i, L, x, v_first, state):
         B, T, D = x.shape
         H, S = self.n_head, self.head_size
         wkv, ts, cs = state
-        lora = lambda dq, t, act=0: self._lora_seq(dq, t.reshape(B * T, -1), act)
         N = B * T
-        xs, ts = ops.seq_ln_shift_mix(x, L.ln1[0], L.ln1[1], ts, L.x_mix)          # LN1 + shift + 6 lerps
-        xr, xw, xk, xv, xa, xg = (xs[j].reshape(N, D) for j in range(6))
-        r, k, v = self._linear(L.Wr, xr), self._linear(L.Wk, xk), self._linear(L.Wv, xv)
-        y_w = lora(L.w2, lora(L.w1, xw, 1))
-        y_a = lora(L.a2, lora(L.a1, xa))
-        g = lora(L.g2, lora(L.g1, xg, 2))
+        if self.fused_prep and N > 8 and D % 2 == 0:
+            # LN1 + shift + 6 lerps, each row written once in the form its consumers read
+            mr, mk, mv = self._prep_modes(N, (L.Wr, L.Wk, L.Wv))
+            modes = [mr, ops.PREP_SPLIT, mk, mv | (ops.PREP_SPLIT if i > 0 else 0), ops.PREP_SPLIT, ops.PREP_SPLIT]
+            (xr, xw, xk, xv, xa, xg), ts = ops.seq_ln_shift_mix_prep(x, L.ln1[0], L.ln1[1], ts, L.x_mix, modes)
+            lin, lora = self._linear_rows, self._lora_rows
+        else:
+            xs, ts = ops.seq_ln_shift_mix(x, L.ln1[0], L.ln1[1], ts, L.x_mix)          # LN1 + shift + 6 lerps
+            xr, xw, xk, xv, xa, xg = (xs[j].reshape(N, D) for j in range(6))
+            lin, lora = self._linear, self._lora_seq
+        lora2 = lambda dq, t, act=0: self._lora_seq(dq, t, act)
+        r, k, v = lin(L.Wr, xr), lin(L.Wk, xk), lin(L.Wv, xv)
+        y_w = lora2(L.w2, lora(L.w1, xw, 1))
+        y_a = lora2(L.a2, lora(L.a1, xa, 0))
+        g = lora2(L.g2, lora(L.g1, xg, 2))
         if i == 0:
             v_first, y_v = v, None
         else:
-            y_v = lora(L.v2, lora(L.v1, xv))
+            y_v = lora2(L.v2, lora(L.v1, xv, 0))
         w, k, v2, na, nb = ops.seq_tmix_pre(k, v, y_w, y_a, y_v, None if i == 0 else v_first, L.w0, L.a0, L.v0,
                                             L.k_k, L.k_a, H)
         r4 = lambda t: t.reshape(B, T, H, S)
         out, wkv = wkv7_infer(r4(r), r4(w), r4(k), r4(v2), r4(na), r4(nb), wkv)
         og = wkv_tail(out, r, k, v2, L.r_k, L.lnx[0], L.lnx[1], g, H, S)
         x = self._linear(L.Wo, og.reshape(N, D), epilogue=_lib.EPI_ADD, resid=x.reshape(N, D).contiguous())
-        xk2, cs = ops.seq_ln_shift_mix(x.reshape(B, T, D), L.ln2[0], L.ln2[1], cs, L.ffn_x_k)     # LN2 + shift + lerp
-        h = self._linear(L.Wfk, xk2.reshape(N, D), epilogue=_lib.EPI_RELU2)
+        if self.fused_prep and N > 8 and D % 2 == 0:
+            (xk2,), cs = ops.seq_ln_shift_mix_prep(x.reshape(B, T, D), L.ln2[0], L.ln2[1], cs, L.ffn_x_k,
+                                                   self._prep_modes(N, (L.Wfk,)))
+            h = self._linear_rows(L.Wfk, xk2, epilogue=_lib.EPI_RELU2)
+        else:
+            xk2, cs = ops.seq_ln_shift_mix(x.reshape(B, T, D), L.ln2[0], L.ln2[1], cs, L.ffn_x_k)     # LN2 + shift + lerp
+            h = self._linear(L.Wfk, xk2.reshape(N, D), epilogue=_lib.EPI_RELU2)
         x = self._linear(L.Wfv, h, epilogue=_lib.EPI_ADD, resid=x).reshape(B, T, D)
         return x, v_first, (wkv, ts, cs)
 

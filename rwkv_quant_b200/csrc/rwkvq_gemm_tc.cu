@@ -549,6 +549,13 @@ __global__ void __launch_bounds__(256) row_scale_kernel(const float* x, long lon
     }
 }
 
+// For activations that arrive already scaled (rwkvq_gemm_x16): only the header is zeroed.
+__global__ void __launch_bounds__(256) gemm_header_zero_kernel(uint4* header, int header_words16) {
+    pdl_launch_dependents();
+    pdl_wait();                 // the previous kernel may still read this workspace
+    for (int i = threadIdx.x; i < header_words16; i += 256) header[i] = make_uint4(0, 0, 0, 0);
+}
+
 }  // namespace rwkvq
 
 using namespace rwkvq;
@@ -617,6 +624,17 @@ int launch_gemm(GemmArgs& a, int rows, int cols, int M, float* partial, const __
     if (le != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "rwkvq_gemm: %s", cudaGetErrorString(le));
     return RWKVQ_OK;
 }
+int dispatch_gemm(GemmArgs& a, const rwkvq_qtensor* t, int M, float* partial, const __half* x16, cudaStream_t s) {
+    if (M <= 16) return launch_gemm<16, 256>(a, t->rows, t->cols, M, partial, x16, s);
+    if (M <= 32) return launch_gemm<32, 256>(a, t->rows, t->cols, M, partial, x16, s);
+    if (M <= 64) return launch_gemm<64, 256>(a, t->rows, t->cols, M, partial, x16, s);
+    // 256-token tiles (every converted weight serves 256 tokens) once they still give the
+    // SMs enough CTAs or a long K loop; otherwise 128-token tiles
+    const int tiles256 = ((t->rows + kGmRows - 1) / kGmRows) * ((M + 255) / 256);
+    if (M > 128 && (tiles256 >= 64 || t->cols >= 4096))
+        return launch_gemm<256, 128>(a, t->rows, t->cols, M, partial, x16, s);
+    return launch_gemm<128, 256>(a, t->rows, t->cols, M, partial, x16, s);
+}
 }  // namespace
 
 extern "C" {
@@ -666,20 +684,42 @@ int rwkvq_gemm(const rwkvq_qtensor* t, const float* x, int M, int64_t ldx, float
                                 static_cast<long long>(x16_pitch(t->cols)), reinterpret_cast<uint4*>(ws),
                                 static_cast<int>(kGemmHeader / 16));
     if (le != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "rwkvq_gemm(pre-pass): %s", cudaGetErrorString(le));
-    if (M <= 16) rc = launch_gemm<16, 256>(a, t->rows, t->cols, M, partial, x16, s);
-    else if (M <= 32) rc = launch_gemm<32, 256>(a, t->rows, t->cols, M, partial, x16, s);
-    else if (M <= 64) rc = launch_gemm<64, 256>(a, t->rows, t->cols, M, partial, x16, s);
-    else {
-        // 256-token tiles (every converted weight serves 256 tokens) once they still give the
-        // SMs enough CTAs or a long K loop; otherwise 128-token tiles
-        const int tiles256 = ((t->rows + kGmRows - 1) / kGmRows) * ((M + 255) / 256);
-        if (M > 128 && (tiles256 >= 64 || t->cols >= 4096))
-            rc = launch_gemm<256, 128>(a, t->rows, t->cols, M, partial, x16, s);
-        else
-            rc = launch_gemm<128, 256>(a, t->rows, t->cols, M, partial, x16, s);
-    }
+    rc = dispatch_gemm(a, t, M, partial, x16, s);
     if (rc) return rc;
     return check_launch("rwkvq_gemm");
+}
+
+size_t rwkvq_gemm_x16_pitch(int cols) { return x16_pitch(cols); }
+
+int rwkvq_gemm_x16(const rwkvq_qtensor* t, const void* x16, const float* row_scale, int M, float* y, int64_t ldy,
+                   int epilogue, const float* resid, void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = validate_qtensor(t, "rwkvq_gemm_x16");
+    if (rc) return rc;
+    RWKVQ_REQUIRE(t->kind == RWKVQ_KIND_SB6 || t->kind == RWKVQ_KIND_SYM, RWKVQ_E_DTYPE,
+                  "rwkvq_gemm_x16: only sb6 and sym tensors have a tensor-core path (kind %d)", t->kind);
+    RWKVQ_REQUIRE(x16 && row_scale && y && workspace, RWKVQ_E_NULL, "rwkvq_gemm_x16: null pointer");
+    RWKVQ_REQUIRE(M >= 1 && ldy >= t->rows, RWKVQ_E_SHAPE, "rwkvq_gemm_x16: M=%d ldy=%lld", M, (long long)ldy);
+    RWKVQ_REQUIRE(aligned(x16, 16) && aligned(workspace, 256), RWKVQ_E_ALIGN,
+                  "rwkvq_gemm_x16: x16 must be 16-byte aligned, the workspace 256-byte aligned");
+    RWKVQ_REQUIRE(workspace_bytes >= gemm_ws_x16_off(M), RWKVQ_E_LIMIT, "rwkvq_gemm_x16: workspace %zu < %zu bytes",
+                  workspace_bytes, gemm_ws_x16_off(M));
+    RWKVQ_REQUIRE(epilogue >= RWKVQ_EPI_NONE && epilogue <= RWKVQ_EPI_ADD, RWKVQ_E_DTYPE, "rwkvq_gemm_x16: epilogue %d", epilogue);
+    RWKVQ_REQUIRE(epilogue != RWKVQ_EPI_ADD || resid, RWKVQ_E_NULL, "rwkvq_gemm_x16: resid is null");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    char* ws = static_cast<char*>(workspace);
+    GemmArgs a{};
+    a.t = make_view(*t);
+    a.y = y; a.ldy = ldy; a.resid = resid; a.M = M; a.epilogue = epilogue;
+    a.status = reinterpret_cast<int*>(ws);
+    a.counters = reinterpret_cast<unsigned int*>(ws + 256);
+    a.row_scale = row_scale;
+    a.trace = g_gemm_trace;
+    cudaError_t le = launch_pdl(gemm_header_zero_kernel, dim3(1), dim3(256), 0, s, reinterpret_cast<uint4*>(ws),
+                                static_cast<int>(kGemmHeader / 16));
+    if (le != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "rwkvq_gemm_x16(header): %s", cudaGetErrorString(le));
+    rc = dispatch_gemm(a, t, M, reinterpret_cast<float*>(ws + gemm_ws_partial_off(M)), static_cast<const __half*>(x16), s);
+    if (rc) return rc;
+    return check_launch("rwkvq_gemm_x16");
 }
 
 }  // extern "C"

@@ -69,6 +69,145 @@ __global__ void __launch_bounds__(kSeqThreads) seq_ln_shift_mix_kernel(const flo
     }
 }
 
+// ---- the same, emitting what the consumers of each mix read ---------------------------------
+// A mix row feeds either the dequant-fused GEMM (which reads a per-token power-of-two-scaled
+// fp16 copy, pitch D + 64 halves, plus the scale) or the LoRA GEMM (which reads the fp16 hi/lo
+// split [hi | lo]), or both; writing those forms here saves the fp32 round trip through HBM and
+// one launch per consumer.  The conversions are those of the GEMM's own pre-pass (scale =
+// 2^(14 - exponent of the row maximum)) and of split_fp16_kernel.
+constexpr int kPrepScaled = 1, kPrepSplit = 2, kPrepF32 = 4;
+struct SeqPrepArgs {
+    const float *x, *ln_w, *ln_b, *shift_in, *mix;
+    float* shift_out;
+    __half* x16[6];        // [N, D + 64]
+    float* scale[6];       // [N]
+    __half* split[6];      // [N, 2 D]
+    float* f32[6];         // [N, D]
+    int mode[6];
+    int T, D, n_mix;
+};
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float m = red[0];
+    for (int w = 1; w < (blockDim.x >> 5); ++w) m = fmaxf(m, red[w]);
+    return m;
+}
+
+// One CTA per token; thread t owns the column pairs 2 (t + 256 i), i < 8 (D <= 4096, D even).
+__global__ void __launch_bounds__(kSeqThreads, 3) seq_ln_shift_mix_prep_kernel(const SeqPrepArgs a) {
+    __shared__ float red[kSeqThreads / 32];
+    constexpr int kPairs = kSeqPer / 2;
+    const long long tok = blockIdx.x;
+    const int D = a.D, b = static_cast<int>(tok / a.T), t = static_cast<int>(tok % a.T);
+    const float* row = a.x + tok * D;
+    float2 v[kPairs], pv[kPairs];
+    const float2 zero = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) {
+        const int d = 2 * (threadIdx.x + i * kSeqThreads);
+        const bool ok = d < D;
+        v[i] = ok ? *reinterpret_cast<const float2*>(row + d) : zero;
+        pv[i] = !ok ? zero
+                    : (t > 0 ? *reinterpret_cast<const float2*>(row + d - D)
+                             : (a.shift_in ? *reinterpret_cast<const float2*>(a.shift_in + static_cast<size_t>(b) * D + d) : zero));
+    }
+    // LayerNorm of the token's row and of its predecessor's at once: the two means, then the two
+    // variances, each pair in one block reduction (one barrier each)
+    __shared__ float2 red_mean[kSeqThreads / 32], red_var[kSeqThreads / 32];
+    auto block_sum2 = [&](float2 q, float2* buf) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            q.x += __shfl_xor_sync(0xFFFFFFFFu, q.x, o);
+            q.y += __shfl_xor_sync(0xFFFFFFFFu, q.y, o);
+        }
+        if ((threadIdx.x & 31) == 0) buf[threadIdx.x >> 5] = q;
+        __syncthreads();
+        float2 tot = buf[0];
+#pragma unroll
+        for (int w = 1; w < kSeqThreads / 32; ++w) { tot.x += buf[w].x; tot.y += buf[w].y; }
+        return tot;
+    };
+    float2 sum = zero;
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) { sum.x += v[i].x + v[i].y; sum.y += pv[i].x + pv[i].y; }
+    sum = block_sum2(sum, red_mean);
+    const float mean = sum.x / D, pmean = sum.y / D;
+    float2 sq = zero;
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) {
+        if (2 * (threadIdx.x + i * kSeqThreads) < D) {
+            const float c0 = v[i].x - mean, c1 = v[i].y - mean, p0 = pv[i].x - pmean, p1 = pv[i].y - pmean;
+            sq.x += c0 * c0 + c1 * c1;
+            sq.y += p0 * p0 + p1 * p1;
+        }
+    }
+    sq = block_sum2(sq, red_var);
+    const float inv = 1.0f / sqrtf(sq.x / D + 1e-5f), pinv = 1.0f / sqrtf(sq.y / D + 1e-5f);
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) {
+        const int d = 2 * (threadIdx.x + i * kSeqThreads);
+        if (d >= D) continue;
+        const float2 lw = __ldg(reinterpret_cast<const float2*>(a.ln_w + d)), lb = __ldg(reinterpret_cast<const float2*>(a.ln_b + d));
+        v[i].x = (v[i].x - mean) * inv * lw.x + lb.x;
+        v[i].y = (v[i].y - mean) * inv * lw.y + lb.y;
+        if (t > 0) {                    // t == 0: pv already is a normalised row (or zeros)
+            pv[i].x = (pv[i].x - pmean) * pinv * lw.x + lb.x;
+            pv[i].y = (pv[i].y - pmean) * pinv * lw.y + lb.y;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) {
+        const int d = 2 * (threadIdx.x + i * kSeqThreads);
+        if (d < D && t == a.T - 1) *reinterpret_cast<float2*>(a.shift_out + static_cast<size_t>(b) * D + d) = v[i];
+        pv[i].x -= v[i].x;                     // xx = prev - cur
+        pv[i].y -= v[i].y;
+    }
+    for (int m = 0; m < a.n_mix; ++m) {
+        float2 val[kPairs];
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < kPairs; ++i) {
+            const int d = 2 * (threadIdx.x + i * kSeqThreads);
+            val[i] = zero;
+            if (d < D) {
+                const float2 mx = __ldg(reinterpret_cast<const float2*>(a.mix + static_cast<size_t>(m) * D + d));
+                val[i].x = v[i].x + pv[i].x * mx.x;
+                val[i].y = v[i].y + pv[i].y * mx.y;
+                amax = fmaxf(amax, fmaxf(fabsf(val[i].x), fabsf(val[i].y)));
+            }
+        }
+        const int mode = a.mode[m];
+        float sc = 1.f;
+        if (mode & kPrepScaled) {
+            amax = block_max(amax, red);
+            int e = 0;
+            if (amax > 0.f && amax < INFINITY) frexpf(amax, &e);
+            sc = ldexpf(1.f, 14 - e);
+            if (threadIdx.x == 0) a.scale[m][tok] = sc;
+        }
+#pragma unroll
+        for (int i = 0; i < kPairs; ++i) {
+            const int d = 2 * (threadIdx.x + i * kSeqThreads);
+            if (d >= D) continue;
+            if (mode & kPrepScaled)
+                *reinterpret_cast<__half2*>(a.x16[m] + tok * (D + 64) + d) = __floats2half2_rn(val[i].x * sc, val[i].y * sc);
+            if (mode & kPrepSplit) {
+                const __half2 hi = __floats2half2_rn(val[i].x, val[i].y);
+                const float2 hf = __half22float2(hi);
+                __half* o = a.split[m] + tok * 2 * D + d;
+                *reinterpret_cast<__half2*>(o) = hi;
+                *reinterpret_cast<__half2*>(o + D) = __floats2half2_rn(val[i].x - hf.x, val[i].y - hf.y);
+            }
+            if (mode & kPrepF32) *reinterpret_cast<float2*>(a.f32[m] + tok * D + d) = val[i];
+        }
+    }
+}
+
 struct TmixPreArgs {
     const float *k, *v, *yw, *ya, *yv, *v_first;     // [N, D]; yv / v_first null on layer 0
     const float *w0, *a0, *v0, *k_k, *k_a;           // [D]
@@ -151,6 +290,46 @@ int rwkvq_seq_ln_shift_mix(const float* x, const float* ln_w, const float* ln_b,
     else
         seq_ln_shift_mix_kernel<1><<<static_cast<unsigned>(n), kSeqThreads, 0, s>>>(x, ln_w, ln_b, shift_in, mix, out, shift_out, T, D, n);
     return check_launch("rwkvq_seq_ln_shift_mix");
+}
+
+int rwkvq_seq_ln_shift_mix_prep(const float* x, const float* ln_w, const float* ln_b, const float* shift_in,
+                                const float* mix, int n_mix, const int* modes, void* const* out_x16,
+                                float* const* out_scale, void* const* out_split, float* const* out_f32,
+                                float* shift_out, int B, int T, int D, void* stream) {
+    RWKVQ_REQUIRE(x && ln_w && ln_b && mix && modes && shift_out, RWKVQ_E_NULL, "rwkvq_seq_ln_shift_mix_prep: null pointer");
+    RWKVQ_REQUIRE(B >= 1 && T >= 1 && D >= 2 && D % 2 == 0 && D <= kSeqThreads * kSeqPer, RWKVQ_E_LIMIT,
+                  "rwkvq_seq_ln_shift_mix_prep: B=%d T=%d D=%d (even, at most %d)", B, T, D, kSeqThreads * kSeqPer);
+    RWKVQ_REQUIRE(n_mix >= 1 && n_mix <= 6, RWKVQ_E_SHAPE, "rwkvq_seq_ln_shift_mix_prep: n_mix %d (1..6)", n_mix);
+    const long long n = static_cast<long long>(B) * T;
+    RWKVQ_REQUIRE(n < (1ll << 31), RWKVQ_E_LIMIT, "rwkvq_seq_ln_shift_mix_prep: %lld tokens", n);
+    RWKVQ_REQUIRE(aligned(x, 8) && aligned(ln_w, 8) && aligned(ln_b, 8) && aligned(mix, 8) && aligned(shift_in, 8) &&
+                      aligned(shift_out, 8), RWKVQ_E_ALIGN, "rwkvq_seq_ln_shift_mix_prep: 8-byte aligned rows required");
+    SeqPrepArgs a{};
+    a.x = x; a.ln_w = ln_w; a.ln_b = ln_b; a.shift_in = shift_in; a.mix = mix; a.shift_out = shift_out;
+    a.T = T; a.D = D; a.n_mix = n_mix;
+    for (int m = 0; m < n_mix; ++m) {
+        const int mode = modes[m];
+        RWKVQ_REQUIRE(mode >= 1 && mode <= 7, RWKVQ_E_DTYPE, "rwkvq_seq_ln_shift_mix_prep: mode[%d] = %d", m, mode);
+        a.mode[m] = mode;
+        if (mode & kPrepScaled) {
+            RWKVQ_REQUIRE(out_x16 && out_scale && out_x16[m] && out_scale[m] && aligned(out_x16[m], 16), RWKVQ_E_NULL,
+                          "rwkvq_seq_ln_shift_mix_prep: scaled output %d missing or unaligned", m);
+            a.x16[m] = static_cast<__half*>(out_x16[m]);
+            a.scale[m] = out_scale[m];
+        }
+        if (mode & kPrepSplit) {
+            RWKVQ_REQUIRE(out_split && out_split[m] && aligned(out_split[m], 4), RWKVQ_E_NULL,
+                          "rwkvq_seq_ln_shift_mix_prep: split output %d missing or unaligned", m);
+            a.split[m] = static_cast<__half*>(out_split[m]);
+        }
+        if (mode & kPrepF32) {
+            RWKVQ_REQUIRE(out_f32 && out_f32[m] && aligned(out_f32[m], 8), RWKVQ_E_NULL,
+                          "rwkvq_seq_ln_shift_mix_prep: fp32 output %d missing or unaligned", m);
+            a.f32[m] = out_f32[m];
+        }
+    }
+    seq_ln_shift_mix_prep_kernel<<<static_cast<unsigned>(n), kSeqThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    return check_launch("rwkvq_seq_ln_shift_mix_prep");
 }
 
 int rwkvq_seq_tmix_pre(const float* k, const float* v, const float* yw, const float* ya, const float* yv,

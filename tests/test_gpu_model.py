@@ -300,3 +300,59 @@ def test_split_fp16_and_stacked_lora_product(cuda_lib):
     assert err <= 1e-5, err
     plain = (torch.mm(x.half(), w, out_dtype=torch.float32).double() - ref).abs().max().item() / ref.abs().max().item()
     assert err < 0.1 * plain, (err, plain)
+
+
+def test_prepared_rows_match_unfused_glue(cuda_lib):
+    """rwkvq_seq_ln_shift_mix_prep: every form of a mix row equals what the separate passes make
+    of the fp32 row (pre-pass scaling of rwkvq_gemm, rwkvq_split_fp16), and rwkvq_gemm_x16 on
+    the prepared rows equals rwkvq_gemm on the fp32 rows bit for bit."""
+    from rwkv_quant_b200 import synth
+    from rwkv_quant_b200.backends.cuda import ops
+    g = torch.Generator().manual_seed(17)
+    B, T, D = 2, 37, 512
+    x = torch.randn(B, T, D, generator=g).cuda() * 2
+    lw, lb = (1 + 0.1 * torch.randn(D, generator=g)).cuda(), (0.1 * torch.randn(D, generator=g)).cuda()
+    mix = torch.rand(6, D, generator=g).cuda()
+    shift = torch.randn(B, 1, D, generator=g).cuda()
+    for sh in (None, shift):
+        ref, ref_shift = ops.seq_ln_shift_mix(x, lw, lb, sh, mix)
+        rows, new_shift = ops.seq_ln_shift_mix_prep(x, lw, lb, sh, mix, [7, 2, 1, 3, 4, 6])
+        assert (new_shift - ref_shift).abs().max().item() <= 2e-6
+        for m, r in enumerate(rows):
+            want = ref[m].reshape(B * T, D)
+            if r.f32 is not None:
+                assert (r.f32 - want).abs().max().item() <= 3e-6 * want.abs().max().item()
+        full = rows[0]                                    # mode 7: all three forms of one row
+        assert torch.equal(full.split, ops.split_fp16(full.f32))
+        amax = full.f32.abs().amax(dim=1)
+        sc = torch.ldexp(torch.ones_like(amax), 14 - torch.frexp(amax)[1])
+        assert torch.equal(full.scale, sc)
+        assert torch.equal(full.x16[:, :D], (full.f32 * sc[:, None]).half())
+        assert rows[1].x16 is None and rows[2].split is None and rows[4].split is None
+    qt = synth.quantize("blocks.0.att.key.weight", "proj", torch.randn(256, D, generator=g) * 0.02,
+                        {"proj": ("sb6", 5)})
+    dq = ops.DeviceQT(qt, "cuda")
+    resid = torch.randn(B * T, 256, generator=g).cuda()
+    for epi, rs in ((0, None), (1, None), (2, resid)):
+        assert torch.equal(ops.gemm_x16(dq, full, epi, rs), ops.gemm(dq, full.f32, epi, rs))
+
+
+def test_sequence_path_prepared_rows_vs_separate_passes(cuda_lib):
+    """The sequence path with rows prepared in the LN kernel against the one with separate passes.
+    The two LayerNorms add in different orders (1e-7), which moves a few fp16 roundings of the GEMM
+    operands: the same 1e-3 gate as against the oracle."""
+    model, oracle, z = _load("compression")
+    idx = np.tile(z["idx"], (1, 3))
+    B = idx.shape[0]
+    assert model.fused_prep
+    lo1, st1 = model.forward_stateful(idx, model.init_state(B))
+    model.fused_prep = False
+    lo0, st0 = model.forward_stateful(idx, model.init_state(B))
+    d = relmax(lo1.cpu().numpy(), lo0.cpu().numpy())
+    print(f"prepared rows vs separate passes: logits relmax {d:.2e}")
+    assert d <= 1e-3
+    ref, _ = oracle.forward_stateful(idx, oracle.init_state(B))
+    assert relmax(lo1.cpu().numpy(), ref) <= 1e-3 and relmax(lo0.cpu().numpy(), ref) <= 1e-3
+    for a, b in zip(st1, st0):
+        for u, w in zip(a, b):
+            assert (u - w).abs().max().item() <= 1e-3 * max(1.0, w.abs().max().item())
