@@ -216,38 +216,35 @@ struct TmixPreArgs {
     int H;
 };
 
-// One warp per (token, head): lane owns channels lane and lane + 32 of the head.
+// One warp per (token, head): lane owns the channel pair 2 lane, 2 lane + 1 of the head (64-bit
+// loads and stores).
 __global__ void __launch_bounds__(256) seq_tmix_pre_kernel(const TmixPreArgs p) {
     const long long pair = blockIdx.x * 8ll + (threadIdx.x >> 5);
     if (pair >= p.n_pairs) return;
     const int lane = threadIdx.x & 31, hd = static_cast<int>(pair % p.H);
-    const size_t base = static_cast<size_t>(pair) * 64;
-    float kk[2], av[2];
-    float n2 = 0.f;
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const int c = hd * 64 + lane + 32 * j;
-        const size_t i = base + lane + 32 * j;
-        const float k = p.k[i];
-        float v = p.v[i];
-        p.w[i] = expf(-0.606531f * sigmoidf_(p.yw[i] + p.w0[c]));
-        av[j] = sigmoidf_(p.ya[i] + p.a0[c]);
-        kk[j] = k * p.k_k[c];
-        n2 += kk[j] * kk[j];
-        p.k2[i] = k * (1.0f + (av[j] - 1.0f) * p.k_a[c]);
-        if (p.yv) v = v + (p.v_first[i] - v) * sigmoidf_(p.yv[i] + p.v0[c]);
-        p.v2[i] = v;
+    const size_t i = static_cast<size_t>(pair) * 64 + 2 * lane;
+    const int c = hd * 64 + 2 * lane;
+    auto ld2 = [](const float* q, size_t at) { return *reinterpret_cast<const float2*>(q + at); };
+    auto st2 = [](float* q, size_t at, float x, float y) { *reinterpret_cast<float2*>(q + at) = make_float2(x, y); };
+    const float2 k = ld2(p.k, i), yw = ld2(p.yw, i), ya = ld2(p.ya, i);
+    float2 v = ld2(p.v, i);
+    const float2 w0 = ld2(p.w0, c), a0 = ld2(p.a0, c), kk_w = ld2(p.k_k, c), ka_w = ld2(p.k_a, c);
+    if (p.yv) {
+        const float2 yv = ld2(p.yv, i), vf = ld2(p.v_first, i), v0 = ld2(p.v0, c);
+        v.x = v.x + (vf.x - v.x) * sigmoidf_(yv.x + v0.x);
+        v.y = v.y + (vf.y - v.y) * sigmoidf_(yv.y + v0.y);
     }
+    st2(p.w, i, expf(-0.606531f * sigmoidf_(yw.x + w0.x)), expf(-0.606531f * sigmoidf_(yw.y + w0.y)));
+    const float ax = sigmoidf_(ya.x + a0.x), ay = sigmoidf_(ya.y + a0.y);
+    const float kx = k.x * kk_w.x, ky = k.y * kk_w.y;
+    float n2 = kx * kx + ky * ky;
+    st2(p.k2, i, k.x * (1.0f + (ax - 1.0f) * ka_w.x), k.y * (1.0f + (ay - 1.0f) * ka_w.y));
+    st2(p.v2, i, v.x, v.y);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) n2 += __shfl_xor_sync(0xFFFFFFFFu, n2, o);
     const float inv = 1.0f / sqrtf(n2 + 1e-12f);
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const size_t i = base + lane + 32 * j;
-        const float kn = kk[j] * inv;
-        p.na[i] = -kn;
-        p.nb[i] = kn * av[j];
-    }
+    st2(p.na, i, -(kx * inv), -(ky * inv));
+    st2(p.nb, i, kx * inv * ax, ky * inv * ay);
 }
 
 // x fp32 [rows, cols] -> out fp16 [rows, 2 * cols] = [hi | lo] with hi = fp16(x), lo = fp16(x - hi):
@@ -341,6 +338,10 @@ int rwkvq_seq_tmix_pre(const float* k, const float* v, const float* yw, const fl
     RWKVQ_REQUIRE((yv == nullptr) == (v_first == nullptr) && (yv == nullptr || v0 != nullptr), RWKVQ_E_NULL,
                   "rwkvq_seq_tmix_pre: yv, v_first and v0 go together");
     RWKVQ_REQUIRE(n_tokens >= 1 && H >= 1, RWKVQ_E_SHAPE, "rwkvq_seq_tmix_pre: n_tokens=%lld H=%d", (long long)n_tokens, H);
+    for (const void* q : {(const void*)k, (const void*)v, (const void*)yw, (const void*)ya, (const void*)yv, (const void*)v_first,
+                          (const void*)w0, (const void*)a0, (const void*)v0, (const void*)k_k, (const void*)k_a, (const void*)w,
+                          (const void*)k2, (const void*)v2, (const void*)neg_kk, (const void*)kk_a})
+        RWKVQ_REQUIRE(aligned(q, 8), RWKVQ_E_ALIGN, "rwkvq_seq_tmix_pre: 8-byte aligned arrays required");
     TmixPreArgs p{k, v, yw, ya, yv, v_first, w0, a0, v0, k_k, k_a, w, k2, v2, neg_kk, kk_a, n_tokens * H, H};
     const long long blocks = (p.n_pairs + 7) / 8;
     RWKVQ_REQUIRE(blocks < (1ll << 31), RWKVQ_E_LIMIT, "rwkvq_seq_tmix_pre: too many tokens");

@@ -122,7 +122,8 @@ __global__ void __launch_bounds__(512 / R, 4) wkv7_kernel(const WkvArgs p) {
         }
     };
     // One step of the recurrence on the rows staged at `st`.  Packed fp32 arithmetic: two lanes per
-    // instruction, each lane an IEEE fma.
+    // instruction, each lane an IEEE fma (measured 13 % faster at B = 16 than the same step in scalar
+    // instructions, which also need 237 registers instead of 198).
     auto step = [&](int t, const float* st) {
         float2 x[4], kv[4];
         auto load8 = [&](int row, float2 (&d)[4]) {
