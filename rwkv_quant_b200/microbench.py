@@ -5,6 +5,7 @@
     python -m rwkv_quant_b200.microbench sweep          # GEMV shapes of the 1.5B model, GB/s each
     python -m rwkv_quant_b200.microbench prefill [--T 512] [--batch B] [--recipe R]
     python -m rwkv_quant_b200.microbench wkv [--batch B] [--T 512] [--H 32]   # the WKV-7 scan alone
+    python -m rwkv_quant_b200.microbench spec [--k 4] [--flush 8]            # speculative vs plain greedy decode
 
 `gemv` and `decode` do a handful of launches and exit (suitable under a profiler);
 `sweep` replays a ring of distinct weight buffers (working set >> L2) as a CUDA graph and
@@ -15,6 +16,7 @@ from __future__ import annotations
 import argparse
 import ctypes as C
 
+import numpy as np
 import torch
 
 from . import _lib, synth
@@ -381,6 +383,35 @@ def wkv(B, T, H, launches=6):
           f"({nb / 1e6:.1f} MB of rows, {nb / us[len(us) // 2] / 1e3:.0f} GB/s)", flush=True)
 
 
+def spec(recipe="compression", n_tokens=128, k=4, flush=8, period=16):
+    """Speculative greedy decoding (n-gram drafts from the stream's own history, verified on the
+    small-T path) against the plain CUDA-graph decoder, one stream, on a prompt of period
+    ``period`` (random-init weights do not continue text, so the acceptance rate here is that of
+    whatever cycle the model falls into, not of natural language)."""
+    import time
+    from .spec_decode import generate_speculative
+    ck = synth.build_checkpoint("1.5b", recipe, seed=0, device="cuda")
+    m = QuantRWKV7(ck)
+    del ck
+    rng = np.random.default_rng(0)
+    prompt = [int(t) for t in rng.integers(1, 60000, period)] * (256 // period)
+    to_idx = lambda rows: torch.as_tensor(rows, device=m.device)
+    for _ in range(2):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        want, _ = m.generate(np.asarray([prompt]), n_tokens)
+        torch.cuda.synchronize()
+        t_plain = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        st = generate_speculative(m, prompt, n_tokens, k=k, flush=flush, to_idx=to_idx)
+        torch.cuda.synchronize()
+        t_spec = time.perf_counter() - t0
+    same = st.tokens == want[0].tolist()
+    print(f"spec decode {recipe}: plain {n_tokens / t_plain:.0f} tok/s (eager decoder incl. prefill), speculative "
+          f"{n_tokens / t_spec:.0f} tok/s; accepted {st.accepted}/{st.drafted}, {st.tokens_per_call:.2f} tokens per model "
+          f"call, {st.flushes} flushes; tokens equal: {same}", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -413,7 +444,13 @@ def main():
     wk = sub.add_parser("wkv")
     wk.add_argument("--batch", type=int, default=1); wk.add_argument("--T", type=int, default=512)
     wk.add_argument("--H", type=int, default=32)
+    sp = sub.add_parser("spec")
+    sp.add_argument("--recipe", default="compression"); sp.add_argument("--n", type=int, default=128)
+    sp.add_argument("--k", type=int, default=4); sp.add_argument("--flush", type=int, default=8)
     a = ap.parse_args()
+    if a.cmd == "spec":
+        spec(a.recipe, a.n, a.k, a.flush)
+        return
     if a.cmd == "wkv":
         wkv(a.batch, a.T, a.H)
         return

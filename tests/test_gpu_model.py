@@ -356,3 +356,18 @@ def test_sequence_path_prepared_rows_vs_separate_passes(cuda_lib):
     for a, b in zip(st1, st0):
         for u, w in zip(a, b):
             assert (u - w).abs().max().item() <= 1e-3 * max(1.0, w.abs().max().item())
+
+
+def test_speculative_decoding_matches_greedy(cuda_lib):
+    """History n-gram drafts verified through forward_stateful(tail_only=...) on the small-T path
+    (semantics of tests/spec_decode_champ.py:89-137): same tokens as plain greedy decoding."""
+    from rwkv_quant_b200.spec_decode import generate_speculative
+    model, oracle, z = _load("compression")
+    prompt = [int(t) for t in z["idx"][0, :10]] * 3
+    want, _ = model.generate(np.asarray([prompt]), 40)
+    to_idx = lambda rows: torch.as_tensor(rows, device=model.device)
+    st = generate_speculative(model, prompt, 40, k=4, flush=6, to_idx=to_idx)
+    print(f"speculative: {st.rounds} rounds, {st.accepted}/{st.drafted} accepted, {st.flushes} flushes, "
+          f"{st.tokens_per_call:.2f} tokens per model call")
+    assert st.tokens == want[0].tolist()
+    assert st.drafted > 0
