@@ -39,6 +39,7 @@ extern "C" {
 #define RWKVQ_E_TIMEOUT  -6   /* a bounded device-side wait ran out                    */
 #define RWKVQ_E_NULL     -7   /* a required pointer is null                            */
 #define RWKVQ_E_LIMIT    -8   /* a size exceeds a documented maximum                   */
+#define RWKVQ_E_FORMAT   -9   /* a file is not a readable .rwkvq container             */
 
 /* element types of activation / output buffers */
 #define RWKVQ_F32   0
@@ -387,6 +388,37 @@ int rwkvq_ipc_close(void* p);
 int rwkvq_tp_allgather_store(const float* src, int count, float* const* dst_ptrs,
                              unsigned int* const* flag_ptrs, int rank, int world, unsigned int* epoch_ctr,
                              int* status, long long max_spins, void* stream);
+
+/*
+ * Torch-free reader of the .rwkvq container (host side): the C counterpart of
+ * codec.open_rwkvq / reader.load_raw (formats/codec.py:496-511, formats/reader.py:42-93).
+ *   rwkvq_file_open     maps the file read-only, parses the safetensors header and the manifest;
+ *                       RWKVQ_E_FORMAT for a foreign container, a missing manifest, a
+ *                       format_version above 2, or buffers that do not fit the file
+ *   rwkvq_file_tensor   descriptor with HOST pointers into the mapping (valid until close);
+ *                       rows = product of the leading dimensions, cols = the last one;
+ *                       `transposed` = stored [in, out]; sparse overrides (int32 [n, 2] row/column,
+ *                       bf16 [n] values) when the tensor carries them, else NULL / 0
+ *   rwkvq_file_upload   one device allocation holding the tensor's buffers (256-byte aligned each),
+ *                       filled by cudaMemcpyAsync on `stream`; dev_view is what the kernels take
+ *                       (dev_meta / dev_planes NULL: run rwkvq_relayout_* for the decode layouts);
+ *                       release with rwkvq_file_free_slab
+ */
+typedef struct rwkvq_file rwkvq_file;
+typedef struct rwkvq_file_info {
+    int32_t format_version;
+    int32_t naming;                 /* 0 = world, 1 = custom */
+    int32_t n_layer, n_embd, head_size, vocab_size;
+    int32_t n_tensors;
+} rwkvq_file_info;
+int rwkvq_file_open(const char* path, rwkvq_file** out);
+void rwkvq_file_close(rwkvq_file* f);
+int rwkvq_file_get_info(const rwkvq_file* f, rwkvq_file_info* out);
+const char* rwkvq_file_tensor_key(const rwkvq_file* f, int index);
+int rwkvq_file_tensor(const rwkvq_file* f, const char* key, rwkvq_qtensor* host_view, int32_t* transposed,
+                      const void** outlier_indices, const void** outlier_values, int64_t* n_outliers);
+int rwkvq_file_upload(const rwkvq_file* f, const char* key, rwkvq_qtensor* dev_view, void** slab, void* stream);
+int rwkvq_file_free_slab(void* slab);
 
 #ifdef __cplusplus
 }

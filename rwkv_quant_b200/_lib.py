@@ -16,7 +16,7 @@ LIB_PATH = os.path.join(_HERE, "librwkvq_b200.so")
 F32, F16, BF16 = 0, 1, 2
 KIND = {"dense": 0, "sb6": 1, "sym": 2, "asym": 3, "rtn": 4}
 EPI_NONE, EPI_RELU2, EPI_ADD = 0, 1, 2
-E_SHAPE, E_ALIGN, E_DTYPE, E_ARCH, E_LAUNCH, E_TIMEOUT, E_NULL, E_LIMIT = -1, -2, -3, -4, -5, -6, -7, -8
+E_SHAPE, E_ALIGN, E_DTYPE, E_ARCH, E_LAUNCH, E_TIMEOUT, E_NULL, E_LIMIT, E_FORMAT = -1, -2, -3, -4, -5, -6, -7, -8, -9
 DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
 
@@ -89,6 +89,14 @@ _PROTOS = {
     "rwkvq_seq_ln_shift_mix": (C.c_int, [C.c_void_p] * 5 + [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                          C.c_void_p]),
     "rwkvq_split_fp16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
+    "rwkvq_file_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "rwkvq_file_close": (None, [C.c_void_p]),
+    "rwkvq_file_get_info": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "rwkvq_file_tensor_key": (C.c_char_p, [C.c_void_p, C.c_int]),
+    "rwkvq_file_tensor": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(QTensorStruct), C.POINTER(C.c_int32),
+                                    C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int64)]),
+    "rwkvq_file_upload": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(QTensorStruct), C.POINTER(C.c_void_p), C.c_void_p]),
+    "rwkvq_file_free_slab": (C.c_int, [C.c_void_p]),
     "rwkvq_gemm_x16_pitch": (C.c_size_t, [C.c_int]),
     "rwkvq_gemm_x16": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int64,
                                  C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
@@ -147,6 +155,11 @@ def check(code: int, name: str) -> None:
         lib = load()
         detail = lib.rwkvq_last_error_detail().decode() or lib.rwkvq_strerror(code).decode()
         raise RwkvqError(code, name, detail)
+
+
+def last_error() -> str:
+    """Detail text of the calling thread's last failed library call."""
+    return load().rwkvq_last_error_detail().decode()
 
 
 def ptr(t) -> int:

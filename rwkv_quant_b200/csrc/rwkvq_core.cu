@@ -125,6 +125,7 @@ const char* rwkvq_strerror(int code) {
         case RWKVQ_E_TIMEOUT: return "bounded device-side wait ran out";
         case RWKVQ_E_NULL: return "required pointer is null";
         case RWKVQ_E_LIMIT: return "size exceeds a documented maximum";
+        case RWKVQ_E_FORMAT: return "not a readable .rwkvq container";
         default: return "unknown error";
     }
 }

@@ -8,6 +8,7 @@
   (tests/test_gw_nb_parity.py), fused == separate (tests/test_sym_fuse_parity.py),
   poison-filled outputs to catch rows the grid does not cover.
 """
+import os
 import zlib
 
 import numpy as np
@@ -237,3 +238,50 @@ def test_rtn_outlier_overrides(cuda_lib):
     dense = lin.dq.densified()
     assert dense.kind == "dense" and dense.outliers is None
     np.testing.assert_array_equal(dense.dequant(torch.float32, False).cpu().numpy(), oc.f32_to_bf16_rne(ref))
+
+
+@pytest.mark.parametrize("name", ["toy_compression", "toy_reduction", "toy_custom_int8"])
+def test_c_reader_upload_feeds_the_kernels(cuda_lib, name):
+    """rwkvq_file_open -> rwkvq_file_upload: the device descriptor made without Python or torch
+    dequantises to the codec's bits (every tensor of a reference-written file), and a GEMV on it
+    equals the GEMV on the Python loader's descriptor."""
+    import ctypes as C
+    from conftest import GOLDEN
+    from oracle import codec_np as oc
+    from rwkv_quant_b200 import _lib
+    from rwkv_quant_b200.backends.cuda import ops
+    from rwkv_quant_b200.formats import load_raw
+    path = os.path.join(GOLDEN, name + ".rwkvq")
+    man, arr = oc.open_rwkvq(path)
+    ck = load_raw(path)
+    h = C.c_void_p()
+    _lib.check(cuda_lib.rwkvq_file_open(path.encode(), C.byref(h)), "rwkvq_file_open")
+    slabs = []
+    try:
+        for key, t in man["tensors"].items():
+            v, slab = _lib.QTensorStruct(), C.c_void_p()
+            _lib.check(cuda_lib.rwkvq_file_upload(h, key.encode(), C.byref(v), C.byref(slab), _lib.stream_ptr()),
+                       "rwkvq_file_upload")
+            slabs.append(slab)
+            out = torch.empty((v.rows, v.cols), dtype=torch.float32, device="cuda")
+            _lib.check(cuda_lib.rwkvq_dequant(C.byref(v), out.data_ptr(), _lib.DTYPE_CODE[torch.float32], 0,
+                                              _lib.stream_ptr()), "rwkvq_dequant")
+            qt = ck.tensors[key]
+            has_outliers = getattr(qt, "outlier_indices", None) is not None and qt.outlier_indices.numel() > 0
+            want = oc.dequant_key(man, arr, key).reshape(v.rows, v.cols)
+            if has_outliers:                           # the descriptor carries the packed codes only
+                want = ops.DeviceQT(qt, "cuda", relayout=False)
+                want = ops.dequant(want.bufs, want.meta, torch.float32, False).cpu().numpy()
+            assert np.array_equal(out.cpu().numpy(), want), key
+            if t["kind"] in ("sb6", "sym") and v.cols % 256 == 0:
+                x = torch.randn(1, v.cols, device="cuda")
+                y = torch.empty((1, v.rows), dtype=torch.float32, device="cuda")
+                _lib.check(cuda_lib.rwkvq_gemv(C.byref(v), x.data_ptr(), 0, 1, v.cols, y.data_ptr(), v.rows, 0, None,
+                                               _lib.stream_ptr()), "rwkvq_gemv")
+                d = ops.DeviceQT(qt, "cuda", relayout=False)
+                assert torch.equal(y, ops.gemv(d.bufs, d.meta, x, 0, None)), key
+        torch.cuda.synchronize()
+    finally:
+        for s in slabs:
+            cuda_lib.rwkvq_file_free_slab(s)
+        cuda_lib.rwkvq_file_close(h)
