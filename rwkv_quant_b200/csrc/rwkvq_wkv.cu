@@ -26,8 +26,9 @@ struct WkvArgs {
 // tile of R state rows x 8 columns: per step it loads 8 columns of a, w, k, b, r and R values of v
 // (40 + R floats for 8 R state elements; one row x 16 columns would load 81 for 16).  Eight lanes
 // span the 64 columns of a row group, so a dot product ends in three shuffle stages; a warp holds
-// four row groups.  R = 4: 128 threads, the short dependency chain for grids that leave SMs
-// nearly empty; R = 8: 64 threads, least shared-memory traffic per step for full grids.
+// four row groups.  R = 8: 64 threads, least shared-memory traffic per step, for full grids;
+// R = 4, and R = 2 with 4 CTAs per head: shorter steps for grids that leave SMs empty (measured:
+// two CTAs of 128 threads per head were slower than one of R = 4).
 //
 // Staging: the r/w/k/v/a/b rows of kWkvChunk steps form one chunk; a ring of kWkvStages chunks in
 // shared memory is filled with 16-byte cp.async copies issued two chunks (16 steps) ahead, so a load
@@ -47,15 +48,14 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// Sums y[0..R) over the 8 lanes of a row group, halving the number of live values at each stage
-// (a lane keeps the half its lane bit selects and sends the other); returns the total of row
-// `row` (also returned) - lanes 0..R-1 of the group end with distinct rows.
+// Sums y[0..R) over the 8 lanes of a row group, one shuffle stage per call (m = 1, 2, 4), halving
+// the number of live values at each stage (a lane keeps the half its lane bit selects and sends
+// the other); afterwards y[0] is the total of row `row` - lanes 0..R-1 of the group end with
+// distinct rows.
 template <int R>
-__device__ __forceinline__ float reduce_rows(float (&y)[R], int c, int& row) {
-    row = 0;
-    int n = R;
-#pragma unroll
-    for (int m = 1; m < 8; m <<= 1) {
+struct RowReduce {
+    int n = R, row = 0;
+    __device__ __forceinline__ void stage(float (&y)[R], int c, int m) {
         if (n > 1) {
             const int half = n >> 1;
             const bool up = (c & m) != 0;
@@ -73,15 +73,17 @@ __device__ __forceinline__ float reduce_rows(float (&y)[R], int c, int& row) {
             y[0] += __shfl_xor_sync(0xFFFFFFFFu, y[0], m);
         }
     }
-    return y[0];
-}
+};
 
-template <int R>
-__global__ void __launch_bounds__(512 / R, 4) wkv7_kernel(const WkvArgs p) {
-    constexpr int kThreads = 512 / R;
+// SPLIT CTAs share one (batch, head): the state rows are independent, so CTA s of the group owns
+// rows s * 64 / SPLIT .. and reads the same staged r/w/k/v/a/b rows (small grids are bound by the
+// latency of a step, which shrinks with the work a warp has per step).
+template <int R, int SPLIT>
+__global__ void __launch_bounds__(512 / R / SPLIT, 4) wkv7_kernel(const WkvArgs p) {
+    constexpr int kThreads = 512 / R / SPLIT;
     extern __shared__ __align__(16) float ring[];
-    const int bh = blockIdx.x, bi = bh / p.H, hi = bh % p.H;
-    const int tid = threadIdx.x, c = tid & 7, dv0 = (tid >> 3) * R;
+    const int bh = blockIdx.x / SPLIT, bi = bh / p.H, hi = bh % p.H;
+    const int tid = threadIdx.x, c = tid & 7, dv0 = (blockIdx.x % SPLIT) * (kS / SPLIT) + (tid >> 3) * R;
     float2 h[R][4];                               // rows dv0 + j, columns 8c + 2q, 8c + 2q + 1
     const size_t hbase = (static_cast<size_t>(bh) * kS + dv0) * kS + c * 8;
 #pragma unroll
@@ -124,6 +126,12 @@ __global__ void __launch_bounds__(512 / R, 4) wkv7_kernel(const WkvArgs p) {
     // One step of the recurrence on the rows staged at `st`.  Packed fp32 arithmetic: two lanes per
     // instruction, each lane an IEEE fma (measured 13 % faster at B = 16 than the same step in scalar
     // instructions, which also need 237 registers instead of 198).
+    // The output sums of step t are reduced and stored during step t+1, stage by stage beside the
+    // shuffles of that step's S a, so that only one shuffle chain per step is exposed.
+    float yp[R];                                      // per-lane partial sums of the pending output
+    int tp = -1;                                      // its step (-1: none yet)
+#pragma unroll
+    for (int j = 0; j < R; ++j) yp[j] = 0.f;
     auto step = [&](int t, const float* st) {
         float2 x[4], kv[4];
         auto load8 = [&](int row, float2 (&d)[4]) {
@@ -134,9 +142,9 @@ __global__ void __launch_bounds__(512 / R, 4) wkv7_kernel(const WkvArgs p) {
         };
         float vv[R];
 #pragma unroll
-        for (int j = 0; j < R; j += 4) {
-            const float4 v4 = *reinterpret_cast<const float4*>(st + 5 * kS + dv0 + j);
-            vv[j] = v4.x; vv[j + 1] = v4.y; vv[j + 2] = v4.z; vv[j + 3] = v4.w;
+        for (int j = 0; j < R; j += 2) {
+            const float2 v2 = *reinterpret_cast<const float2*>(st + 5 * kS + dv0 + j);
+            vv[j] = v2.x; vv[j + 1] = v2.y;
         }
         load8(0, x);                                  // a
         float sa[R];
@@ -148,11 +156,14 @@ __global__ void __launch_bounds__(512 / R, 4) wkv7_kernel(const WkvArgs p) {
             p0 = __fadd2_rn(p0, p1);
             sa[j] = p0.x + p0.y;
         }
+        RowReduce<R> rr;
 #pragma unroll
         for (int m = 1; m < 8; m <<= 1) {
 #pragma unroll
             for (int j = 0; j < R; ++j) sa[j] += __shfl_xor_sync(0xFFFFFFFFu, sa[j], m);
+            rr.stage(yp, c, m);
         }
+        if (tp >= 0 && c < R) p.out[row0 + tp * step_stride + dv0 + rr.row] = yp[0];
         load8(3, x);                                  // b
         load8(2, kv);                                 // k
         float2 u[R][4];                               // v k^T + sa b^T
@@ -164,7 +175,6 @@ __global__ void __launch_bounds__(512 / R, 4) wkv7_kernel(const WkvArgs p) {
         }
         load8(1, x);                                  // w
         load8(4, kv);                                 // r
-        float y[R];
 #pragma unroll
         for (int j = 0; j < R; ++j) {
 #pragma unroll
@@ -173,11 +183,9 @@ __global__ void __launch_bounds__(512 / R, 4) wkv7_kernel(const WkvArgs p) {
             p0 = __ffma2_rn(h[j][2], kv[2], p0);
             p1 = __ffma2_rn(h[j][3], kv[3], p1);
             p0 = __fadd2_rn(p0, p1);
-            y[j] = p0.x + p0.y;
+            yp[j] = p0.x + p0.y;
         }
-        int row;
-        const float total = reduce_rows<R>(y, c, row);
-        if (c < R) p.out[row0 + t * step_stride + dv0 + row] = total;
+        tp = t;
     };
     const int n_chunks = (p.T + kWkvChunk - 1) / kWkvChunk;
 #pragma unroll
@@ -200,6 +208,12 @@ __global__ void __launch_bounds__(512 / R, 4) wkv7_kernel(const WkvArgs p) {
         }
     }
     cp_async_wait<0>();
+    {                                                 // the output of the last step
+        RowReduce<R> rr;
+#pragma unroll
+        for (int m = 1; m < 8; m <<= 1) rr.stage(yp, c, m);
+        if (tp >= 0 && c < R) p.out[row0 + tp * step_stride + dv0 + rr.row] = yp[0];
+    }
 #pragma unroll
     for (int j = 0; j < R; ++j) {
         *reinterpret_cast<float4*>(p.h_out + hbase + j * kS) = make_float4(h[j][0].x, h[j][0].y, h[j][1].x, h[j][1].y);
@@ -254,8 +268,12 @@ int rwkvq_wkv7(const float* r, const float* w, const float* k, const float* v, c
                   RWKVQ_E_ALIGN, "rwkvq_wkv7: r/w/k/v/a/b must be 16-byte aligned");
     WkvArgs p{r, w, k, v, a, b, h_in, out, h_out, B, T, H};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (B * H > 2 * 148) wkv7_kernel<8><<<B * H, 64, kWkvSmemBytes, st>>>(p);
-    else wkv7_kernel<4><<<B * H, 128, kWkvSmemBytes, st>>>(p);
+    // few (batch, head) pairs: smaller tiles and several CTAs per pair, so that a step is short;
+    // full grids: the largest tile (least shared-memory traffic and issue per state element)
+    const int pairs = B * H;
+    if (pairs > 2 * 148) wkv7_kernel<8, 1><<<pairs, 64, kWkvSmemBytes, st>>>(p);
+    else if (pairs > 74) wkv7_kernel<4, 1><<<pairs, 128, kWkvSmemBytes, st>>>(p);
+    else wkv7_kernel<2, 4><<<pairs * 4, 64, kWkvSmemBytes, st>>>(p);
     return check_launch("rwkvq_wkv7");
 }
 
