@@ -9,7 +9,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 GOLDEN = os.path.join(ROOT, "tests", "golden")
-REFERENCE = os.environ.get("RWKVQ_REFERENCE", "/root/reference")
+REFERENCE = os.environ.get("RWKVQ_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference"))
 
 
 def pytest_configure(config):

@@ -2,7 +2,8 @@
 
     python tests/golden/make_golden.py [/path/to/reference] [all|codec|toy|custom]
 
-Needs the reference project importable (default /root/reference); the fixtures
+Needs the reference project importable (default: a `reference` directory beside this
+repository, or $RWKVQ_REFERENCE); the fixtures
 it writes are committed so that the tests run where the reference is absent.
 
   codec_cases.npz      packed buffers made by the reference's packers
@@ -29,7 +30,9 @@ import zlib
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+HERE_ = os.path.dirname(os.path.abspath(__file__))
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get(
+    "RWKVQ_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE_))), "reference"))
 sys.path.insert(0, REF)
 HERE = os.path.dirname(os.path.abspath(__file__))
 
