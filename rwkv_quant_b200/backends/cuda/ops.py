@@ -43,6 +43,10 @@ class DeviceQT:
         shape = tuple(qt.shape)
         if len(shape) != 2:
             raise ValueError(f"{getattr(qt, 'key', '?')}: only 2-D tensors, got {shape}")
+        # the descriptor carries no buffer sizes: a short buffer or an override outside the
+        # tensor must be refused here, on the host, before a kernel indexes it
+        from ...formats.container import check_tensor_sizes
+        check_tensor_sizes(qt)
         self.outliers = None          # (rows, cols, values fp32, first index of each row run, run lengths)
         self.key = getattr(qt, "key", "")
         self.rows, self.cols = int(shape[0]), int(shape[1])

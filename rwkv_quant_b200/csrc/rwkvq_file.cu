@@ -269,7 +269,64 @@ int fill_view(const TensorEntry& t, rwkvq_qtensor* v) {
         default: return fail(RWKVQ_E_DTYPE, "%s: unknown layout kind %d", t.key.c_str(), t.kind);
     }
     if (!v->codes) return fail(RWKVQ_E_FORMAT, "%s: the code buffer of its layout is missing", t.key.c_str());
-    return RWKVQ_OK;
+    // The descriptor carries no buffer sizes, so every buffer the kernels will index is checked here
+    // against the byte count its layout, bit width and manifest shape imply (formats/writer.py:236-337).
+    const unsigned long long R = static_cast<unsigned long long>(t.rows), Cc = static_cast<unsigned long long>(t.cols);
+    const unsigned long long n = R * Cc;
+    int rc = RWKVQ_OK;
+    auto need = [&](const char* name, unsigned long long bytes, bool required) {
+        if (rc) return;
+        const Buffer* b = t.field(name);
+        if (!b) {
+            if (required) rc = fail(RWKVQ_E_FORMAT, "%s: buffer %s of its layout is missing", t.key.c_str(), name);
+            return;
+        }
+        if (b->bytes != bytes)
+            rc = fail(RWKVQ_E_FORMAT, "%s: buffer %s holds %zu bytes, shape [%lld, %lld] at %d bits needs %llu",
+                      t.key.c_str(), name, b->bytes, t.rows, t.cols, t.bits, bytes);
+    };
+    switch (t.kind) {
+        case RWKVQ_KIND_DENSE: need("dense", n * 2, true); break;
+        case RWKVQ_KIND_SB6: {
+            if (t.gs <= 0 || t.sb <= 0 || Cc % (static_cast<unsigned long long>(t.gs) * t.sb))
+                return fail(RWKVQ_E_FORMAT, "%s: %lld columns do not divide into groups of %d x %d", t.key.c_str(), t.cols, t.gs, t.sb);
+            const unsigned long long nsb = Cc / (static_cast<unsigned long long>(t.gs) * t.sb);
+            need("codes_packed", n / 2, true);
+            need("gw_qh", n / 8, t.bits >= 5);
+            need("gw_qh2", n / 8, t.bits >= 6);
+            need("gw_qsqm", R * nsb * (static_cast<unsigned long long>(t.sb) * 12 / 8), true);
+            need("gw_d", R * nsb * 2, true);
+            need("gw_dm", R * nsb * 2, true);
+            break;
+        }
+        case RWKVQ_KIND_SYM: {
+            if (t.gs <= 0 || t.sb <= 0 || Cc % (static_cast<unsigned long long>(t.gs) * t.sb))
+                return fail(RWKVQ_E_FORMAT, "%s: %lld columns do not divide into groups of %d x %d", t.key.c_str(), t.cols, t.gs, t.sb);
+            if (t.field("codes")) need("codes", n, true);
+            else {
+                need("codes_packed", n / 2, true);
+                need("gw_qh", n / 8, t.bits >= 5);
+                need("gw_qh2", n / 8, t.bits >= 6);
+            }
+            need("gw_qs", R * (Cc / t.gs), true);
+            need("gw_d", R * (Cc / (static_cast<unsigned long long>(t.gs) * t.sb)) * 2, true);
+            break;
+        }
+        case RWKVQ_KIND_ASYM: {
+            if (t.gs <= 0) return fail(RWKVQ_E_FORMAT, "%s: group size %d", t.key.c_str(), t.gs);
+            const unsigned long long nb = (Cc + t.gs - 1) / t.gs;
+            need("codes", n, true);
+            need("gw_scale", R * nb * 4, true);
+            need("gw_min", R * nb * 4, true);
+            break;
+        }
+        default:   // per-row
+            if (t.field("codes")) need("codes", n, true);
+            else need("codes_packed", R * ((Cc + 1) / 2), true);
+            need("scale", R * 2, true);
+            break;
+    }
+    return rc;
 }
 
 }  // namespace
@@ -403,8 +460,15 @@ int rwkvq_file_tensor(const rwkvq_file* f, const char* key, rwkvq_qtensor* host_
     const Buffer* oi = t.field("outlier_indices");
     const Buffer* ov = t.field("outlier_values");
     const bool has = oi && ov && oi->bytes > 0;
-    if (has) RWKVQ_REQUIRE(oi->dtype == "I32" && ov->dtype == "BF16" && oi->bytes == 4 * ov->bytes, RWKVQ_E_FORMAT,
-                           "%s: outlier buffers are not int32 [n, 2] + bf16 [n]", key);
+    if (has) {
+        RWKVQ_REQUIRE(oi->dtype == "I32" && ov->dtype == "BF16" && oi->bytes == 4 * ov->bytes, RWKVQ_E_FORMAT,
+                      "%s: outlier buffers are not int32 [n, 2] + bf16 [n]", key);
+        const int32_t* rc2 = reinterpret_cast<const int32_t*>(oi->ptr);      // an override outside the tensor would
+        for (size_t i = 0; i < ov->bytes / 2; ++i)                           // become a stray device write
+            RWKVQ_REQUIRE(rc2[2 * i] >= 0 && rc2[2 * i] < t.rows && rc2[2 * i + 1] >= 0 && rc2[2 * i + 1] < t.cols,
+                          RWKVQ_E_FORMAT, "%s: outlier %zu at (%d, %d) lies outside the [%lld, %lld] tensor", key, i,
+                          rc2[2 * i], rc2[2 * i + 1], t.rows, t.cols);
+    }
     if (outlier_indices) *outlier_indices = has ? oi->ptr : nullptr;
     if (outlier_values) *outlier_values = has ? ov->ptr : nullptr;
     if (n_outliers) *n_outliers = has ? static_cast<int64_t>(ov->bytes / 2) : 0;

@@ -229,9 +229,10 @@ static int launch_wk(MmaArgs& a, int rows, int cols, int n_mats, float* scratch,
     const int n_iters = cols / Geo<L>::KI;
     const int tiles = (rows + 15) / 16;
     int KS = 1;
+    // the kernel gives every slice n_iters / KS iterations: only an exact division covers the row
     if (scratch && n_iters >= 16 && rows <= kSplitMaxRows) {
-        if (tiles * n_mats * 4 <= kResidentCtas && n_iters >= 32) KS = 4;
-        else if (tiles * n_mats * 2 <= kResidentCtas) KS = 2;
+        if (tiles * n_mats * 4 <= kResidentCtas && n_iters >= 32 && n_iters % 4 == 0) KS = 4;
+        else if (tiles * n_mats * 2 <= kResidentCtas && n_iters % 2 == 0) KS = 2;
     }
     if (KS > 1) {
         a.partial = scratch;

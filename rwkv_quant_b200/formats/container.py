@@ -101,6 +101,88 @@ class QuantizedCheckpoint:
         return sum(qt.nbytes() for k, qt in self.tensors.items() if k not in exclude)
 
 
+def expected_field_elems(kind: str, bits: int, rows: int, cols: int, gs: int, sb: int,
+                         int8_codes: bool) -> dict:
+    """Element count every buffer of a tensor must have for its stored shape [rows, cols]
+    (formats/writer.py:236-337, codec.py:81-105): what the kernels index without further
+    checks.  ``int8_codes``: the tensor carries ``codes`` rather than ``codes_packed``."""
+    n = rows * cols
+    if kind == "dense":
+        return {"dense": n}
+    if kind == "sb6":
+        if gs <= 0 or sb <= 0 or cols % (gs * sb):
+            raise ValueError(f"sb6 tensor with {cols} columns, group {gs} x {sb}")
+        nsb = cols // (gs * sb)
+        out = {"codes_packed": n // 2, "gw_qsqm": rows * nsb * (sb * 12 // 8), "gw_d": rows * nsb,
+               "gw_dm": rows * nsb}
+        if bits >= 5:
+            out["gw_qh"] = n // 8
+        if bits >= 6:
+            out["gw_qh2"] = n // 8
+        return out
+    if kind == "sym":
+        if gs <= 0 or sb <= 0 or cols % (gs * sb):
+            raise ValueError(f"sym tensor with {cols} columns, group {gs} x {sb}")
+        out = {"gw_qs": rows * (cols // gs), "gw_d": rows * (cols // (gs * sb))}
+        if int8_codes:
+            out["codes"] = n
+        else:
+            out["codes_packed"] = n // 2
+            if bits >= 5:
+                out["gw_qh"] = n // 8
+            if bits >= 6:
+                out["gw_qh2"] = n // 8
+        return out
+    if kind == "asym":
+        if gs <= 0:
+            raise ValueError(f"asym tensor with group {gs}")
+        nb = (cols + gs - 1) // gs
+        return {"codes": n, "gw_scale": rows * nb, "gw_min": rows * nb}
+    if kind == "rtn":
+        return {("codes" if int8_codes else "codes_packed"): n if int8_codes else rows * ((cols + 1) // 2),
+                "scale": rows}
+    raise ValueError(f"unknown layout kind {kind!r}")
+
+
+def check_tensor_sizes(qt) -> None:
+    """Refuse (ValueError) a tensor whose buffers do not have the sizes its manifest shape, layout
+    and bit width imply, or whose sparse overrides point outside it, before any kernel indexes
+    them.  The reference fails on the host for such files too (numpy reshape in its codec).
+    Works on this package's QuantizedTensor and on the reference's (same field names)."""
+    shape = tuple(int(v) for v in qt.shape)
+    bits = int(qt.bits)
+    kind = "dense" if bits >= 16 else (getattr(qt, "gw_mode", "") or "rtn")
+    key = getattr(qt, "key", "?")
+    if not shape or min(shape) < 1:
+        raise ValueError(f"{key}: unusable shape {shape}")
+    cols = shape[-1]
+    rows = 1
+    for v in shape[:-1]:
+        rows *= v
+    have = lambda f: getattr(qt, f, None) is not None and getattr(qt, f).numel() > 0
+    want = expected_field_elems(kind, bits, rows, cols, int(getattr(qt, "gw_gs", 0) or 0),
+                                int(getattr(qt, "gw_sb", 0) or 0), have("codes"))
+    if kind in ("sb6", "sym"):                  # a plane the bit width does not call for is still read when present
+        for f in ("gw_qh", "gw_qh2"):
+            if have(f):
+                want.setdefault(f, rows * cols // 8)
+    for f, n in want.items():
+        got = getattr(qt, f).numel() if have(f) else 0
+        if got != n:
+            raise ValueError(f"{key}: buffer {f} has {got} elements, its {kind}@{bits} layout of shape "
+                             f"{list(shape)} needs {n}")
+    if have("outlier_indices"):
+        oi = qt.outlier_indices.reshape(-1, 2)
+        nv = qt.outlier_values.numel() if have("outlier_values") else 0
+        if oi.shape[0] != nv:
+            raise ValueError(f"{key}: {oi.shape[0]} outlier positions for {nv} values")
+        if len(shape) != 2:
+            raise ValueError(f"{key}: outlier overrides on a {len(shape)}-D tensor")
+        r, c = oi[:, 0].long(), oi[:, 1].long()
+        if bool(((r < 0) | (r >= rows) | (c < 0) | (c >= cols)).any()):
+            raise ValueError(f"{key}: an outlier override points outside the [{rows}, {cols}] tensor")
+
+
 def is_raw_lora_world(key: str) -> bool:
     """World checkpoints keep blocks.N.att.{w,a,v,g}{1,2} as [in, out]
     (formats/codec.py:529-535)."""
@@ -178,6 +260,7 @@ def load_raw(path: str) -> QuantizedCheckpoint:
         for f in t["fields"]:
             name = f"{key}::{f}"
             setattr(qt, f, _to_torch(arrays[name], dtypes[name]))
+        check_tensor_sizes(qt)
         if kind == "dense" and qt.dense is not None:
             qt.dense = qt.dense.reshape(qt.shape)
         tensors[key] = qt

@@ -43,6 +43,15 @@ def codec_cases():
 
 
 @pytest.fixture(scope="session")
+def config1_case():
+    """(meta, {field: ndarray}, x fp16 [1, 2048], y fp32 [1, 8192]) of tests/golden/config1_gemv.npz:
+    the single-GEMV benchmark tensor as packed by the reference's search packer."""
+    z = np.load(os.path.join(GOLDEN, "config1_gemv.npz"))
+    meta = json.loads(bytes(z["__meta__"]).decode())["config1"]
+    return meta, {f: z[f"config1::{f}"] for f in meta["fields"]}, z["x"], z["y"]
+
+
+@pytest.fixture(scope="session")
 def cuda_lib():
     """The loaded C-ABI library on a B200; GPU tests fail (not skip) if it is missing."""
     import torch

@@ -1,6 +1,6 @@
 """Generate the golden fixtures of this directory from the UNMODIFIED reference.
 
-    python tests/golden/make_golden.py [/path/to/reference] [all|codec|toy|custom]
+    python tests/golden/make_golden.py [/path/to/reference] [all|codec|toy|custom|config1]
 
 Needs the reference project importable (default: a `reference` directory beside this
 repository, or $RWKVQ_REFERENCE); the fixtures
@@ -14,6 +14,10 @@ it writes are committed so that the tests run where the reference is absent.
                        tests/fixtures/gw_golden.json that a packed layout exists
                        for: digest(fake-dequant) which packer -> dequant must
                        reproduce (the claim of tests/test_groupwise_parity.py:82-115)
+  config1_gemv.npz     W [8192, 2048] = randn(seed 0) * 0.02 packed by quantize_tensor with
+                       cmix = 4, group 32, asym_sb6_search (the single-GEMV benchmark
+                       configuration), the codec digest of its dequantised form, x fp16
+                       [1, 2048] = default_rng(0).standard_normal and y = x.f32 @ Wdq.T
   toy_<preset>.rwkvq   2-layer D=256 world-naming random-init model quantized by
                        rwkv_quant.quantize() with both presets
   toy_<preset>_ref.npz token ids, RWKV7Ref (cpu, fp32) logits on the dequantised
@@ -166,6 +170,26 @@ def make_codec_cases():
     print("codec cases:", len(meta))
 
 
+def make_config1():
+    """The single-GEMV configuration, packed by the reference's search packer."""
+    w = torch.randn(8192, 2048, generator=torch.Generator().manual_seed(0)) * 0.02
+    cfg = QuantConfig(cmix=4, group_scale={"cmix": 32}, group_scale_mode={"cmix": "asym_sb6_search"},
+                      act_stats_path=None)
+    qt = quantize_tensor("blocks.0.ffn.key.weight", w, cfg, real_gw=True)
+    store, meta = {}, {}
+    add_case(store, meta, "config1", qt)
+    deq = ref_dequant(qt)
+    x = np.random.default_rng(0).standard_normal((1, 2048)).astype(np.float16)
+    store["x"] = x
+    store["y"] = (x.astype(np.float32) @ deq.T).astype(np.float32)
+    store["__meta__"] = np.frombuffer(json.dumps(meta).encode(), dtype=np.uint8)
+    path = os.path.join(HERE, "config1_gemv.npz")
+    np.savez_compressed(path, **store)
+    nbytes = sum(store[f"config1::{f}"].nbytes for f in meta["config1"]["fields"])
+    print("config 1:", meta["config1"]["kind"], meta["config1"]["bits"], nbytes, "packed bytes;",
+          os.path.getsize(path), "bytes on disk")
+
+
 # ---------------------------------------------------------------- toy model
 def lora_ranks(d):
     f = lambda c, p: max(32, int(round((c * (d ** p)) / 32) * 32))
@@ -307,3 +331,5 @@ if __name__ == "__main__":
         make_toy_models()
     if which in ("all", "custom"):
         make_toy_custom()
+    if which in ("all", "config1"):
+        make_config1()

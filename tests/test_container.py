@@ -119,6 +119,48 @@ def test_rejects_foreign_and_future(tmp_path):
     assert ck.tensors["blocks.0.att.w1"].transposed and not ck.tensors["head.weight"].transposed
 
 
+def test_rejects_buffers_that_do_not_fit_the_manifest_shape(tmp_path):
+    """A manifest whose shape is larger than its buffers, a short side buffer, or a sparse
+    override outside the tensor is refused on the host (ValueError), by the reader and by the
+    device-side tensor view alike: the kernels' descriptors carry no buffer sizes."""
+    src = os.path.join(GOLDEN, "toy_compression.rwkvq")
+    p = str(tmp_path / "x.rwkvq")
+    def grow_rows(m, h):
+        m["tensors"]["blocks.0.ffn.key.weight"]["shape"][0] += 16
+    _rewrite_manifest(src, p, grow_rows)
+    with pytest.raises(ValueError, match="codes_packed"):
+        container.load_raw(p)
+    def wrong_bits(m, h):                      # 5-bit layout whose plane buffer is not listed
+        t = m["tensors"]["blocks.0.att.key.weight"]
+        t["fields"] = [f for f in t["fields"] if f != "gw_qh"]
+    _rewrite_manifest(src, p, wrong_bits)
+    with pytest.raises(ValueError, match="gw_qh"):
+        container.load_raw(p)
+    def grow_lora(m, h):
+        m["tensors"]["blocks.1.att.w1"]["shape"][1] += 64      # one more block than gw_scale holds
+    _rewrite_manifest(src, p, grow_lora)
+    with pytest.raises(ValueError):
+        container.load_raw(p)
+    # the in-memory objects are checked too (no file involved)
+    qt = synth.quant_sb6("w", "g", torch.randn(32, 512) * 0.02, 5)
+    container.check_tensor_sizes(qt)
+    qt.gw_d = qt.gw_d[:-1]
+    with pytest.raises(ValueError, match="gw_d"):
+        container.check_tensor_sizes(qt)
+    qt = synth.quant_rtn("w", "g", torch.randn(32, 64) * 0.02, 8)
+    qt.outlier_indices = torch.tensor([[3, 5], [32, 0]], dtype=torch.int32)
+    qt.outlier_values = torch.zeros(2, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="outside"):
+        container.check_tensor_sizes(qt)
+    qt.outlier_indices = torch.tensor([[3, 5], [31, 63]], dtype=torch.int32)
+    container.check_tensor_sizes(qt)
+    from rwkv_quant_b200.backends.cuda import ops
+    qt.outlier_indices = torch.tensor([[3, 64]], dtype=torch.int32)
+    qt.outlier_values = torch.zeros(1, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        ops.DeviceQT(qt, device="cpu", relayout=False)
+
+
 def test_weight_bytes_of_full_size_recipes():
     """Per-token streamed bytes of the 1.5B builds from the layout arithmetic:
     about 876 MB (compression) and 1289 MB (reduction) without the embedding."""

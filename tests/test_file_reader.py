@@ -142,6 +142,55 @@ def test_c_reader_refusals(tmp_path):
     lib.rwkvq_file_close(h)
 
 
+def test_c_reader_refuses_buffers_that_do_not_fit_the_shape(tmp_path):
+    """The descriptor has no buffer sizes: a manifest shape larger than its buffers, a missing
+    plane, or a sparse override outside the tensor is refused when the descriptor is made."""
+    import torch
+    from rwkv_quant_b200 import synth
+    lib = _lib.load()
+    src = os.path.join(GOLDEN, "toy_compression.rwkvq")
+    p = str(tmp_path / "x.rwkvq")
+
+    def tensor_rc(key):
+        rc, h = _open(lib, p)
+        assert rc == 0, _lib.last_error()
+        v = _lib.QTensorStruct()
+        rc = lib.rwkvq_file_tensor(h, key.encode(), C.byref(v), None, None, None, None)
+        slab, dv = C.c_void_p(), _lib.QTensorStruct()
+        rc_up = lib.rwkvq_file_upload(h, key.encode(), C.byref(dv), C.byref(slab), None)   # refused before any CUDA call
+        lib.rwkvq_file_close(h)
+        assert rc_up == rc and slab.value is None
+        return rc
+
+    def grow_rows(m, h):
+        m["tensors"]["blocks.0.ffn.key.weight"]["shape"][0] += 16
+    _rewrite_manifest(src, p, grow_rows)
+    assert tensor_rc("blocks.0.ffn.key.weight") == _lib.E_FORMAT and "codes_packed" in _lib.last_error()
+    def drop_plane(m, h):
+        t = m["tensors"]["blocks.0.att.key.weight"]
+        t["fields"] = [f for f in t["fields"] if f != "gw_qh"]
+    _rewrite_manifest(src, p, drop_plane)
+    assert tensor_rc("blocks.0.att.key.weight") == _lib.E_FORMAT and "gw_qh" in _lib.last_error()
+    def grow_lora(m, h):
+        m["tensors"]["blocks.1.att.w1"]["shape"][1] += 64
+    _rewrite_manifest(src, p, grow_lora)
+    assert tensor_rc("blocks.1.att.w1") == _lib.E_FORMAT
+    # an override that points outside its tensor
+    ck = synth.build_checkpoint("toy", "compression", seed=1)
+    qt = ck.tensors["blocks.0.att.g1"]
+    qt.outlier_indices = torch.tensor([[0, 1], [qt.shape[0], 0]], dtype=torch.int32)
+    qt.outlier_values = torch.zeros(2, dtype=torch.bfloat16)
+    container.save_rwkvq(ck, p)
+    rc, h = _open(lib, p)
+    assert rc == 0
+    v = _lib.QTensorStruct()
+    assert lib.rwkvq_file_tensor(h, b"blocks.0.att.g1", C.byref(v), None, None, None, None) == _lib.E_FORMAT
+    assert "outside" in _lib.last_error()
+    lib.rwkvq_file_close(h)
+    with pytest.raises(ValueError, match="outside"):
+        container.load_raw(p)
+
+
 def test_json_strings_with_escapes(tmp_path):
     """config_repr and tokenizer may carry quotes, backslashes and non-ASCII text."""
     lib = _lib.load()

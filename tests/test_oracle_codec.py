@@ -28,6 +28,18 @@ def test_golden_codec_cases_bit_exact(codec_cases):
         assert digest_f32(w) == meta["digest"], name
 
 
+def test_config1_reference_packed(config1_case):
+    """The single-GEMV configuration (W [8192, 2048] int4 g32, packed by the reference's
+    asym_sb6_search packer): 9 437 184 packed bytes, oracle dequant hits the reference codec's
+    digest, and the oracle's matvec reproduces the reference's y."""
+    meta, bufs, x, y = config1_case
+    assert (meta["kind"], meta["bits"], meta["shape"]) == ("sb6", 4, [8192, 2048])
+    assert sum(a.nbytes for a in bufs.values()) == 9437184
+    w = oracle_dequant_case(meta, bufs)
+    assert digest_f32(w) == meta["digest"]
+    np.testing.assert_allclose(x.astype(np.float32) @ w.T, y, rtol=0, atol=1e-5 * np.abs(y).max())
+
+
 def test_reference_known_answers(codec_cases):
     """digest(oracle(packed)) == the hash the reference froze for its quantiser."""
     known = json.load(open(os.path.join(GOLDEN, "gw_known_answers.json")))["hashes"]

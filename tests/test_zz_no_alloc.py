@@ -47,6 +47,10 @@ def _static(lib, dq, x, epilogue=0, resid=None):
     ("sym", 6, 1024, 2048),
     ("sym", 8, 4096, 1024),     # largest row count served; too short for a K split
     ("rtn", 8, 640, 4096),      # per-row int8
+    ("sb6", 6, 1024, 17 * 256),   # 17 iterations: no even split, every column must still be multiplied
+    ("sym", 8, 1024, 34 * 128),   # 34 iterations: 2 slices, not 4
+    ("rtn", 8, 1024, 34 * 128),
+    ("sb6", 4, 512, 33 * 256),    # odd count at the 4-way size
 ])
 def test_static_matches_allocating_entry_point_twice(cuda_lib, layout, bits, rows, cols):
     from rwkv_quant_b200.backends.cuda import ops
