@@ -18,7 +18,9 @@
  *   - return value: 0 on success, a negative RWKVQ_E_* code otherwise
  *     (rwkvq_strerror() gives the text, rwkvq_last_error_detail() the detail of
  *     the calling thread's last failure);
- *   - thread-safe when called on distinct streams.
+ *   - thread-safe when called on distinct streams (calls that share a stream must come
+ *     from one thread at a time, as for any stream-ordered API); rwkvq_gemv_static is the
+ *     exception documented at its declaration.
  */
 #ifndef RWKVQ_B200_H
 #define RWKVQ_B200_H
@@ -149,10 +151,6 @@ int rwkvq_gemv(const rwkvq_qtensor* t, const void* x, int x_dtype, int N, int64_
  */
 size_t rwkvq_gemm_workspace_bytes(int M);
 size_t rwkvq_gemm_workspace_bytes_for(int M, int max_cols);
-/* Profiling aid: with a device buffer of 512 uint64 set, CTA (0,0,0) of every later rwkvq_gemm
- * launch records global-timer nanoseconds of its pipeline events (slot map in the kernel source);
- * NULL (the default) switches it off. */
-void rwkvq_gemm_set_trace(void* buf512);
 int rwkvq_gemm(const rwkvq_qtensor* t, const float* x, int M, int64_t ldx, float* y, int64_t ldy,
                int epilogue, const float* resid, void* workspace, size_t workspace_bytes, void* stream);
 /* The same product on activations the caller has already brought into the form the kernel reads
@@ -304,49 +302,6 @@ int rwkvq_decode_step(const rwkvq_model* m_host, int B, const int64_t* tokens,
                       float* const* wkv_host, float* const* tshift_host, float* const* cshift_host,
                       void* workspace, size_t workspace_bytes, float* logits, int64_t* next_tokens,
                       void* stream);
-
-/*
- * The same token step for ONE stream as a single persistent cooperative kernel
- * (2 CTAs per SM stay resident; the ~5 stages per layer are separated by grid-wide
- * barriers instead of kernel boundaries and the weight stream is prefetched across
- * them).  Stands behind the same reference call as rwkvq_decode_step with B = 1
- * (backends/metal/quant_model.py:964-990) plus the greedy argmax of generate()
- * (quant_model.py:1014-1040).
- *
- *   rwkvq_decoder_workspace_bytes  device bytes the decoder needs (0: model not
- *       servable: see rwkvq_last_error_detail)
- *   rwkvq_decoder_create   builds the stage program in `workspace` (256-byte aligned,
- *       owned by the caller, alive as long as the decoder).  Every quantized linear
- *       must have a tensor-core GEMV layout (sb6 with dev_meta / dev_planes, sym);
- *       otherwise RWKVQ_E_DTYPE and the caller uses rwkvq_decode_step.  State
- *       pointers as in rwkvq_decode_step with B = 1; `logits` [vocab] fp32 or NULL
- *       (kept inside the workspace).  Synchronises `stream` once.
- *   rwkvq_decoder_token    device int64 slot: the token the next step consumes; the
- *       step overwrites it with the greedy argmax, so consecutive steps decode
- *       without host involvement.  Write it (stream-ordered) to force a token.
- *   rwkvq_decoder_step     one token: ONE cooperative launch on `stream`.
- *   rwkvq_decoder_status   synchronises `stream`; RWKVQ_E_TIMEOUT if a grid barrier of
- *       a step ran out of polls (the kernel then returned early; the decoder stays
- *       refused until it is created again).
- * Steps of one decoder must not overlap; no other kernel may need the SMs while a
- * step runs (the launch fails instead of hanging if the grid cannot be co-resident).
- */
-typedef struct rwkvq_decoder rwkvq_decoder;
-size_t rwkvq_decoder_workspace_bytes(const rwkvq_model* m_host);
-int rwkvq_decoder_create(const rwkvq_model* m_host, float* const* wkv_host, float* const* tshift_host,
-                         float* const* cshift_host, void* workspace, size_t workspace_bytes, float* logits,
-                         void* stream, rwkvq_decoder** out);
-void rwkvq_decoder_destroy(rwkvq_decoder* d);
-int64_t* rwkvq_decoder_token(rwkvq_decoder* d);
-float* rwkvq_decoder_logits(rwkvq_decoder* d);
-int rwkvq_decoder_grid(const rwkvq_decoder* d);
-int rwkvq_decoder_stages(const rwkvq_decoder* d);
-/* Profiling aid: with a device buffer of stages * grid * 8 uint64 set, every CTA records the
- * global-timer nanoseconds at which it started each stage, finished its work and left the
- * barrier, plus marks inside the GEMV stages ([stage][cta][8]); NULL (the default) switches it off. */
-void rwkvq_decoder_set_trace(rwkvq_decoder* d, void* buf);
-int rwkvq_decoder_step(rwkvq_decoder* d, void* stream);
-int rwkvq_decoder_status(rwkvq_decoder* d, void* stream);
 
 /*
  * Load-time relayout of the side streams of an sb6 / sym tensor for the decode

@@ -85,7 +85,6 @@ _PROTOS = {
                                C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
     "rwkvq_gemv_static": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_void_p,
                                     C.c_int, C.c_void_p, C.c_void_p]),
-    "rwkvq_gemm_set_trace": (None, [C.c_void_p]),
     "rwkvq_seq_ln_shift_mix": (C.c_int, [C.c_void_p] * 5 + [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                          C.c_void_p]),
     "rwkvq_split_fp16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
@@ -112,18 +111,6 @@ _PROTOS = {
     "rwkvq_ipc_close": (C.c_int, [C.c_void_p]),
     "rwkvq_tp_allgather_store": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                            C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p]),
-    "rwkvq_decoder_workspace_bytes": (C.c_size_t, [C.POINTER(ModelStruct)]),
-    "rwkvq_decoder_create": (C.c_int, [C.POINTER(ModelStruct), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
-                                       C.POINTER(C.c_void_p), C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p,
-                                       C.POINTER(C.c_void_p)]),
-    "rwkvq_decoder_destroy": (None, [C.c_void_p]),
-    "rwkvq_decoder_token": (C.c_void_p, [C.c_void_p]),
-    "rwkvq_decoder_logits": (C.c_void_p, [C.c_void_p]),
-    "rwkvq_decoder_grid": (C.c_int, [C.c_void_p]),
-    "rwkvq_decoder_stages": (C.c_int, [C.c_void_p]),
-    "rwkvq_decoder_set_trace": (None, [C.c_void_p, C.c_void_p]),
-    "rwkvq_decoder_step": (C.c_int, [C.c_void_p, C.c_void_p]),
-    "rwkvq_decoder_status": (C.c_int, [C.c_void_p, C.c_void_p]),
 }
 
 

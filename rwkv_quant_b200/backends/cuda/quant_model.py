@@ -170,16 +170,22 @@ class QuantRWKV7:
         return out
 
     # ------------------------------------------------------------------ T == 1
+    def _new_workspace(self, B):
+        n = _lib.load().rwkvq_decode_workspace_bytes(C.byref(self._model_c), B)
+        return torch.zeros(n, dtype=torch.uint8, device=self.device)               # counters start at zero
+
     def _workspace(self, B):
         if B not in self._ws:
-            n = _lib.load().rwkvq_decode_workspace_bytes(C.byref(self._model_c), B)
-            self._ws[B] = torch.zeros(n, dtype=torch.uint8, device=self.device)    # counters start at zero
+            self._ws[B] = self._new_workspace(B)
         return self._ws[B]
 
-    def _decode(self, tokens, states, logits=None, next_tokens=None):
-        """tokens [B] int64 on the device; states materialised; updates them in place."""
+    def _decode(self, tokens, states, logits=None, next_tokens=None, ws=None):
+        """tokens [B] int64 on the device; states materialised; updates them in place.
+        ``ws``: a workspace of the caller's own (steps that may overlap on the device must not
+        share one); default: the model's workspace for this batch size."""
         B = tokens.shape[0]
-        ws = self._workspace(B)
+        if ws is None:
+            ws = self._workspace(B)
         arr = lambda k: (C.c_void_p * self.n_layer)(*[st[k].data_ptr() for st in states])
         if logits is None:
             logits = torch.empty((B, self.vocab_size), dtype=torch.float32, device=self.device)
@@ -358,16 +364,8 @@ class QuantRWKV7:
             tok = dec.step(tok)
         return torch.stack(out, dim=1), dec.states
 
-    def decoder(self, batch_size: int = 1, states=None, use_graph: bool = True, self_feed: bool = False,
-                persistent=None):
-        """``persistent=True`` selects the one-kernel decoder (one stream, every linear in a
-        tensor-core GEMV layout); the default is the CUDA-graph launch chain, which is the
-        faster of the two on B200 (the persistent kernel's stages are instruction-latency
-        bound at 8 warps per SM; see ``microbench timeline``)."""
-        if persistent:
-            if batch_size != 1:
-                raise ValueError("the persistent decoder serves one stream")
-            return PersistentDecoder(self, states)
+    def decoder(self, batch_size: int = 1, states=None, use_graph: bool = True, self_feed: bool = False):
+        """A ``Decoder``: the whole token of ``batch_size`` streams as one CUDA-graph replay."""
         return Decoder(self, batch_size, states, use_graph, self_feed)
 
     @property
@@ -391,13 +389,14 @@ class Decoder:
         self.tokens = torch.zeros(batch_size, dtype=torch.long, device=dev)
         self.next_tokens = torch.zeros(batch_size, dtype=torch.long, device=dev)
         self.logits = torch.empty((batch_size, model.vocab_size), dtype=torch.float32, device=dev)
+        self._ws = model._new_workspace(batch_size)       # its own: decoders on different streams may overlap
         self.graph = None
         self.launches_per_step = None
         if use_graph:
             self._capture()
 
     def _run(self):
-        self.m._decode(self.tokens, self.states, self.logits, self.next_tokens)
+        self.m._decode(self.tokens, self.states, self.logits, self.next_tokens, self._ws)
         if self.self_feed:
             self.tokens.copy_(self.next_tokens)
 
@@ -431,59 +430,3 @@ class Decoder:
     def feed_back(self):
         """Use the last argmax as the next input without leaving the device."""
         self.tokens.copy_(self.next_tokens)
-
-
-class PersistentDecoder:
-    """One stream decoded by the persistent cooperative kernel: one launch per token, the
-    argmax is fed back on the device.  ``tokens`` is both the input slot and, after a
-    step, the greedy next token; ``step(tokens)`` overrides the fed-back token."""
-
-    B = 1
-    launches_per_step = 1
-    graph = None
-    self_feed = True
-
-    def __init__(self, model: QuantRWKV7, states=None):
-        self.m = model
-        st = model.init_state(1) if states is None else states
-        self.states = model._materialize(st, 1)
-        dev = model.device
-        lib = _lib.load()
-        nbytes = lib.rwkvq_decoder_workspace_bytes(C.byref(model._model_c))
-        if nbytes == 0:
-            raise _lib.RwkvqError(_lib.E_DTYPE, "rwkvq_decoder_workspace_bytes",
-                                  lib.rwkvq_last_error_detail().decode() or "model not servable by the persistent decoder")
-        self._ws = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
-        self.logits = torch.empty((1, model.vocab_size), dtype=torch.float32, device=dev)
-        arr = lambda k: (C.c_void_p * model.n_layer)(*[s[k].data_ptr() for s in self.states])
-        self._h = C.c_void_p()
-        with torch.cuda.device(dev):
-            _lib.check(lib.rwkvq_decoder_create(C.byref(model._model_c), arr(0), arr(1), arr(2), self._ws.data_ptr(),
-                                                nbytes, self.logits.data_ptr(), _lib.stream_ptr(), C.byref(self._h)),
-                       "rwkvq_decoder_create")
-        off = lib.rwkvq_decoder_token(self._h) - self._ws.data_ptr()
-        self.tokens = self._ws[off:off + 8].view(torch.long)
-        self.next_tokens = self.tokens
-        self.grid = lib.rwkvq_decoder_grid(self._h)
-        self.stages = lib.rwkvq_decoder_stages(self._h)
-
-    def step(self, tokens=None):
-        if tokens is not None:
-            self.tokens.copy_(tokens.reshape(1), non_blocking=True)
-        _lib.check(_lib.load().rwkvq_decoder_step(self._h, _lib.stream_ptr()), "rwkvq_decoder_step")
-        return self.tokens
-
-    def feed_back(self):
-        pass                                   # the kernel already wrote the argmax into the input slot
-
-    def check(self):
-        """Synchronise and raise if a grid barrier of the kernel ran out of polls."""
-        _lib.check(_lib.load().rwkvq_decoder_status(self._h, _lib.stream_ptr()), "rwkvq_decoder_status")
-
-    def __del__(self):
-        h, self._h = getattr(self, "_h", None), None
-        if h:
-            try:
-                _lib.load().rwkvq_decoder_destroy(h)
-            except Exception:
-                pass

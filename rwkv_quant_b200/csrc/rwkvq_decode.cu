@@ -17,6 +17,10 @@
 //   gemv + relu^2  ffn key;  gemv + add  ffn value and residual
 #include <stdlib.h>
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "rwkvq_decode_parts.cuh"
 
 namespace rwkvq {
@@ -494,23 +498,31 @@ int linear(const rwkvq_qtensor* t, const float* x, int B, int in, float* y, int 
 // The LoRA branches depend on the normalised row only, not on r/k/v: they run on a side
 // stream between a fork after LN1 and a join before the time-mix core, so that in a captured
 // graph they form a parallel branch beside the r/k/v GEMV instead of two more links of the
-// dependent chain.  One side stream and two events per device, created on first use (make the
-// first call outside stream capture).  RWKVQ_FORK=0 keeps everything on the caller's stream.
+// dependent chain.  One side stream and two events per (device, caller stream), created on the
+// first call that uses that stream (make it outside stream capture): sequences issued on
+// different streams, from one or several host threads, never share an event.  Calls on the SAME
+// stream must come from one thread at a time, as for any stream-ordered API.
+// RWKVQ_FORK=0 keeps everything on the caller's stream.
 struct SideLane { cudaStream_t stream = nullptr; cudaEvent_t fork = nullptr, join = nullptr; };
-SideLane* side_lane() {
-    static SideLane lanes[64];
+SideLane* side_lane(cudaStream_t caller) {
     static const bool enabled = [] { const char* e = getenv("RWKVQ_FORK"); return !(e && e[0] == '0'); }();
     if (!enabled) return nullptr;
+    static std::mutex mu;
+    static std::map<std::pair<int, cudaStream_t>, SideLane> lanes;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    SideLane& l = lanes[dev];
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    SideLane& l = lanes[std::make_pair(dev, caller)];
     if (!l.stream) {
-        if (cudaStreamCreateWithFlags(&l.stream, cudaStreamNonBlocking) != cudaSuccess ||
-            cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) != cudaSuccess ||
-            cudaEventCreateWithFlags(&l.join, cudaEventDisableTiming) != cudaSuccess) {
-            l.stream = nullptr;
+        SideLane n;
+        if (cudaStreamCreateWithFlags(&n.stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&n.fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&n.join, cudaEventDisableTiming) != cudaSuccess) {
+            if (n.fork) cudaEventDestroy(n.fork);
+            if (n.stream) cudaStreamDestroy(n.stream);
             return nullptr;
         }
+        l = n;
     }
     return &l;
 }
@@ -591,7 +603,7 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         float *xr = w.xs, *xw = w.xs + BD, *xk = w.xs + 2 * BD, *xv = w.xs + 3 * BD, *xa = w.xs + 4 * BD,
               *xg = w.xs + 5 * BD;
         float *r = w.rkv, *k = w.rkv + BD, *v = w.rkv + 2 * BD;
-        SideLane* lane = side_lane();
+        SideLane* lane = side_lane(s);
         cudaStream_t s_lora = s;
         if (lane) {                                  // fork: the LoRA branches leave the chain here
             if (cudaEventRecord(lane->fork, s) != cudaSuccess || cudaStreamWaitEvent(lane->stream, lane->fork, 0) != cudaSuccess)

@@ -1,5 +1,4 @@
-// Small device functions shared by the launch-chain decode step and the persistent
-// decode kernel.
+// Small device functions shared by the kernels of the decode step.
 #pragma once
 #include "rwkvq_common.cuh"
 

@@ -6,7 +6,7 @@
 // and the accumulator D[128 out-rows, N tokens] lives in tensor memory.
 //   a pre-pass writes the activations once as fp16, scaled per token by a power of two so
 //     that no value leaves the fp16 range;
-//   producers (all 256 threads of the CTA): unpack a [128 rows, 64 K] slab of the file
+//   producers (16 warps = 512 threads; two more warps hold the TMA and the MMA issuer lanes): unpack a [128 rows, 64 K] slab of the file
 //     layout (nibbles / planes / int8 + block scales) to fp16 = fp16(q*s + m) with one
 //     HFMA2 per two weights (s and m ARE fp16 values by the codec's definition, so the
 //     fused multiply-add rounds the exact value once) and store it K-major with the
@@ -561,7 +561,7 @@ __global__ void __launch_bounds__(256) gemm_header_zero_kernel(uint4* header, in
 using namespace rwkvq;
 
 namespace {
-unsigned long long* g_gemm_trace = nullptr;      // set by rwkvq_gemm_set_trace (profiling aid)
+unsigned long long* g_gemm_trace = nullptr;      // set by rwkvq_profiling_gemm_trace (rwkvq_profiling.h)
 constexpr int kGemmResident = 2 * 148;     // accumulator tiles the K-split scratch holds
 constexpr int kGemmSms = 148;
 // Row pitch of the fp16 activation copy: 128 bytes more than the row, so that the 128 rows
@@ -606,12 +606,15 @@ int launch_gemm(GemmArgs& a, int rows, int cols, int M, float* partial, const __
     int mrc = make_xmap(&xmap, x16, M, cols, NT);
     if (mrc) return mrc;
     const size_t smem = static_cast<size_t>(2 * (KM / kGmK)) * kGmRows * 128 + static_cast<size_t>(gemm_b_slots(NT, KM)) * NT * 128 + 1024;
-    static bool configured = false;
-    if (!configured) {
+    // the attribute belongs to the (function, device) pair: remember it per device of this process
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) dev = 0;
+    if (dev >= 64 || !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT, KM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(smem));
         if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "rwkvq_gemm: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        configured = true;
+        if (dev < 64) configured[dev] = true;
     }
     const int rt = (rows + kGmRows - 1) / kGmRows, tt = (M + NT - 1) / NT, n_m = cols / KM;
     // K slices across CTAs while the grid is below one CTA per SM (power of two, >= 2 super-blocks each)
@@ -649,7 +652,7 @@ size_t rwkvq_gemm_workspace_bytes_for(int M, int max_cols) {
     const size_t m = static_cast<size_t>(M < 1 ? 1 : M);
     return gemm_ws_x16_off(m) + sizeof(__half) * m * (static_cast<size_t>(max_cols) + 64) + 256;
 }
-void rwkvq_gemm_set_trace(void* buf512) { g_gemm_trace = static_cast<unsigned long long*>(buf512); }
+void rwkvq_profiling_gemm_trace(void* buf512) { g_gemm_trace = static_cast<unsigned long long*>(buf512); }
 
 size_t rwkvq_gemm_workspace_bytes(int M) { return rwkvq_gemm_workspace_bytes_for(M, 16384); }
 

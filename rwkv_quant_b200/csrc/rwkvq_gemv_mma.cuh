@@ -1,5 +1,4 @@
-// Device-side building blocks of the integer tensor-core GEMV, shared by the stand-alone
-// GEMV kernel and the persistent whole-token decode kernel.
+// Device-side building blocks of the integer tensor-core GEMV.
 //
 //
 // The codes of the .rwkvq layouts are small integers, so the inner products

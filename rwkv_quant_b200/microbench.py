@@ -55,73 +55,6 @@ def decode(layers=4, recipe="compression", steps=3, batch=1, model="1.5b"):
     print("ok", dec.next_tokens.tolist())
 
 
-def timeline(layers=24, recipe="compression", model="1.5b", warm=6):
-    """Stage timeline of the persistent decode kernel for one token: per stage kind the
-    span on the critical path (barrier exit to barrier exit), the slowest CTA's work time
-    and the time between the last arrival and the barrier exit."""
-    import ctypes as C
-
-    import numpy as np
-
-    from . import _lib
-    ck = synth.build_checkpoint(model, recipe, seed=0, device="cuda", n_layer=layers)
-    m = QuantRWKV7(ck)
-    del ck
-    dec = m.decoder(1, persistent=True)
-    for _ in range(warm):
-        dec.step()
-    torch.cuda.synchronize()
-    n, g = dec.stages, dec.grid
-    buf = torch.zeros(n * g * 8, dtype=torch.int64, device="cuda")
-    lib = _lib.load()
-    lib.rwkvq_decoder_set_trace(dec._h, buf.data_ptr())
-    dec.step()
-    dec.check()
-    lib.rwkvq_decoder_set_trace(dec._h, None)
-    t = buf.cpu().numpy().reshape(n, g, 8).astype(np.float64)
-    t0 = t[0, :, 0].min()
-    raw = t
-    t = (t - t0) * 1e-3                                  # microseconds
-    # inside the GEMV stages, for CTA 0 (always a GEMV CTA): start -> row normalised -> digits -> items -> outputs
-    inner = {}
-    for i in range(n - 1):
-        if raw[i, 0, 4] == 0 or (i < layers * 5 and i % 5 == 1):
-            continue
-        name = (["S1 rkv+lora", "S2 tmix", "S3 out", "S4 ffn.key", "S5 ffn.value"][i % 5] if i < layers * 5 else "head")
-        c = 5
-        ln = (t[i, c, 3] - t[i, c, 0]) if raw[i, c, 3] else 0.0
-        inner.setdefault(name, []).append((ln, t[i, c, 4] - t[i, c, 0], t[i, c, 5] - t[i, c, 4], t[i, c, 6] - t[i, c, 5],
-                                           (t[i, c, 7] - t[i, c, 0]) if raw[i, c, 7] else 0.0))
-    print(f"SM clock during the launch: {raw[n - 1, 0, 3] / raw[n - 1, 0, 4] * 1e3:.0f} MHz")
-    kinds = ["S1 rkv+lora", "S2 tmix", "S3 out", "S4 ffn.key", "S5 ffn.value"]
-    rows = {}
-    prev_exit = 0.0
-    for i in range(n - 1):
-        name = kinds[i % 5] if i < layers * 5 else ["head", "argmax", "argmax final"][i - layers * 5]
-        exit_ = t[i, :, 2].max()
-        work = (t[i, :, 1] - t[i, :, 0]).max()
-        last_arrival = t[i, :, 1].max()
-        rows.setdefault(name, []).append((exit_ - prev_exit, work, exit_ - last_arrival, t[i, :, 0].max() - t[i, :, 0].min()))
-        prev_exit = exit_
-    print(f"persistent decode timeline, {model} {recipe} {layers} layers, grid {g}, {n} stages; total {t[n - 1, 0, 1]:.1f} us")
-    print(f"{'stage':<14}{'count':>6}{'span us':>10}{'max work':>10}{'barrier':>10}{'start skew':>12}")
-    for name, v in rows.items():
-        a = np.array(v)
-        print(f"{name:<14}{len(v):>6}{a[:, 0].mean():>10.2f}{a[:, 1].mean():>10.2f}{a[:, 2].mean():>10.2f}{a[:, 3].mean():>12.2f}")
-    print("CTA 5 inside the GEMV stages (us): LN done, input ready (cumulative), items, epilogue, first input load landed")
-    for name, v in inner.items():
-        a = np.array(v)
-        print(f"{name:<14}{a[:, 0].mean():>10.2f}{a[:, 1].mean():>10.2f}{a[:, 2].mean():>10.2f}{a[:, 3].mean():>10.2f}{a[:, 4].mean():>10.2f}")
-    tm = np.array([[t[i, 5, k] - t[i, 5, 0] for k in (3, 4, 5, 6, 1)] for i in range(1, layers * 5, 5)])
-    print("CTA 5 inside S2 (us, cumulative): staged data landed, hidden vectors, LoRA up, WKV step, done")
-    print("              " + "".join(f"{v:>10.2f}" for v in tm.mean(0)))
-    # which CTAs finish last in S1 / S2
-    for k, nm in ((0, "S1"), (1, "S2")):
-        w = (raw[k + 5] [:, 1] - raw[k + 5][:, 0]) * 1e-3
-        order = np.argsort(-w)[:4]
-        print(nm, "layer 1 slowest CTAs:", [(int(c), round(float(w[c]), 2)) for c in order], "median", round(float(np.median(w)), 2))
-
-
 def tp_chain(model="2.9b", recipe="compression", exchange="p2p", iters=200):
     """Row-split tensor-parallel GEMV chain of one layer (output projection, ffn key, ffn
     value: three exchanges) plus the head, for the ranks of a torchrun launch (one process
@@ -264,10 +197,12 @@ def gemm_timeline(layout="sb6", bits=5, rows=2048, cols=2048, M=8192):
     ops.gemm(dq, x, check=True)
     buf = torch.zeros(512, dtype=torch.int64, device="cuda")
     lib = _lib.load()
-    lib.rwkvq_gemm_set_trace(buf.data_ptr())
+    _trace = lib.rwkvq_profiling_gemm_trace          # rwkvq_profiling.h: not part of the C ABI
+    _trace.restype, _trace.argtypes = None, [C.c_void_p]
+    _trace(buf.data_ptr())
     ops.gemm(dq, x)
     torch.cuda.synchronize()
-    lib.rwkvq_gemm_set_trace(None)
+    _trace(None)
     t = buf.cpu().numpy().astype(np.float64)
     t0 = t[0]
     n = sum(1 for i in range(120) if t[8 + 4 * i] > 0)
@@ -426,9 +361,6 @@ def main():
     pf = sub.add_parser("prefill")
     pf.add_argument("--layers", type=int, default=24); pf.add_argument("--recipe", default="reduction")
     pf.add_argument("--T", type=int, default=512); pf.add_argument("--batch", type=int, default=1)
-    tl = sub.add_parser("timeline")
-    tl.add_argument("--layers", type=int, default=24); tl.add_argument("--recipe", default="compression")
-    tl.add_argument("--model", default="1.5b")
     tpp = sub.add_parser("tp")
     tpp.add_argument("--model", default="2.9b"); tpp.add_argument("--recipe", default="compression")
     tpp.add_argument("--exchange", default="p2p", choices=["p2p", "nccl", "none"])
@@ -465,9 +397,6 @@ def main():
         return
     if a.cmd == "tp":
         tp_chain(a.model, a.recipe, a.exchange)
-        return
-    if a.cmd == "timeline":
-        timeline(a.layers, a.recipe, a.model)
         return
     if a.cmd == "gemv":
         gemv(a.layout, a.bits, a.rows, a.cols, a.n, a.launches)
