@@ -91,11 +91,26 @@ def f32_to_bf16_rne(x: np.ndarray) -> np.ndarray:
     """float32 -> float32 holding the nearest-even bf16 value (what
     ``tensor.to(torch.bfloat16)`` does; reader._dequantize_one rounds every
     dequantised tensor this way, formats/reader.py:114-127)."""
-    u = np.asarray(x, dtype=F32).view(np.uint32).astype(np.uint64)
-    nan = np.isnan(x)
-    r = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
-    out = r.astype(np.uint32).view(F32).copy()
-    out[nan] = np.nan
+    x = np.ascontiguousarray(x, dtype=F32)
+    out = np.empty_like(x)
+    flat_in, flat_out = x.reshape(-1), out.reshape(-1)
+
+    def part(a, b):
+        u = flat_in[a:b].view(np.uint32)
+        nan = np.isnan(flat_in[a:b])
+        r = u + (np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1)))     # wraps only for NaN patterns
+        r &= np.uint32(0xFFFF0000)
+        o = r.view(F32)
+        o[nan] = np.nan
+        flat_out[a:b] = o
+    n, step = flat_in.size, 1 << 22
+    if n <= step:
+        part(0, n)
+    else:
+        import os
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(max_workers=min(32, os.cpu_count() or 1)) as ex:
+            list(ex.map(lambda a: part(a, min(a + step, n)), range(0, n, step)))
     return out
 
 
@@ -214,7 +229,31 @@ def open_rwkvq(path: str):
 
 def dequant_key(manifest, arrays, key) -> np.ndarray:
     """One tensor -> float32 in the stored orientation.
-    Restates codec.dequant_key (formats/codec.py:538-571)."""
+    Restates codec.dequant_key (formats/codec.py:538-571).  Large 2-D block-quantized tensors
+    are decoded in row chunks on a thread pool (rows are independent in every layout and numpy
+    releases the interpreter lock inside its loops); the result is the same array."""
+    m = manifest["tensors"][key]
+    kind, shape = m["kind"], tuple(m["shape"])
+    if kind in ("sb6", "sym") and len(shape) == 2 and shape[0] * shape[1] >= (1 << 22) and shape[0] >= 64:
+        import os
+        from concurrent.futures import ThreadPoolExecutor
+        rows = shape[0]
+        step = max(16, min(1024, rows // 8))
+        out = np.empty(shape, F32)
+        names = [f for f in m["fields"] if arrays[f"{key}::{f}"].shape[:1] == (rows,)]
+
+        def chunk(a):
+            b = min(a + step, rows)
+            sub = {f"{key}::{f}": arrays[f"{key}::{f}"][a:b] for f in names}
+            man = {"tensors": {key: dict(m, shape=[b - a, shape[1]])}}
+            out[a:b] = _dequant_one(man, sub, key)
+        with ThreadPoolExecutor(max_workers=min(32, os.cpu_count() or 1)) as ex:
+            list(ex.map(chunk, range(0, rows, step)))
+        return out
+    return _dequant_one(manifest, arrays, key)
+
+
+def _dequant_one(manifest, arrays, key) -> np.ndarray:
     m = manifest["tensors"][key]
     kind, shape = m["kind"], tuple(m["shape"])
     g = lambda f: arrays.get(f"{key}::{f}")
