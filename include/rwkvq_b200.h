@@ -135,6 +135,25 @@ int rwkvq_gemv(const rwkvq_qtensor* t, const void* x, int x_dtype, int N, int64_
                float* y, int64_t ldy, int epilogue, const float* resid, void* stream);
 
 /*
+ * The same product for a SMALL BATCH of right-hand sides (decode streams, short verify runs)
+ * with every packed weight byte read once for the whole batch.  Stands behind the multi-column
+ * GEMV kernels of the reference, which decode each weight once for up to 4 columns and loop
+ * over chunks of 4 (GwQuantLinear._gemv_nb / _get_kernel_k3nb, backends/metal/quant_linear_gw.py:
+ * 658-744, 850-905; SymQuantLinear._gemv, quant_linear_sym.py:485-516): here one pass serves
+ * up to 64 columns (groups of 64 beyond that).
+ *   x [N, ldx] fp32 (rows 16-byte aligned, ldx % 4 == 0), y / resid [N, ldy] fp32.
+ *   Tensors: sb6 with dev_meta (and dev_planes at 5 / 6 bits), sym (dev_planes at 6 bits),
+ *   per-row int8 with cols % 128 == 0; RWKVQ_E_DTYPE otherwise (use rwkvq_gemv).
+ * Operands are fp16 (weights fp16(q*s+m); each token scaled by a power of two per 512-column
+ * chunk), accumulation fp32 on mma.sync tensor cores; results differ from rwkvq_gemv's within
+ * ~2e-4 of max|y| and do not depend on N's grouping only up to that rounding (not batch-invariant
+ * bit for bit).  Allocates nothing and needs no workspace: the K split is reduced across a
+ * thread-block cluster through distributed shared memory.
+ */
+int rwkvq_gemv_batch(const rwkvq_qtensor* t, const float* x, int N, int64_t ldx, float* y, int64_t ldy,
+                     int epilogue, const float* resid, void* stream);
+
+/*
  * Quantized linear for MANY right-hand sides on the tcgen05 tensor cores (prefill,
  * batched decode):  y[n, o] = epi( sum_c W[o, c] x[n, c] ),  n < M.
  * Stands behind the N >= 128 branch of GwQuantLinear.__call__ / SymQuantLinear.__call__

@@ -255,6 +255,32 @@ def _(bufs, meta, x, act, round_w):
     return torch.empty((x.shape[0], meta[3]), dtype=torch.float32, device=x.device)
 
 
+def has_batch_layout(dq: "DeviceQT") -> bool:
+    """Whether ``gemv_batch`` serves the tensor (the layouts of the tensor-core GEMV family)."""
+    if dq.outliers is not None:
+        return False
+    if dq.kind == "sb6":
+        return dq.bufs[_BUF_ORDER.index("dev_meta")].numel() > 0 and dq.cols % 256 == 0
+    if dq.kind == "sym":
+        return dq.cols % 256 == 0 and (dq.bits == 8 or dq.bufs[_BUF_ORDER.index("dev_planes")].numel() > 0)
+    return dq.kind == "rtn" and dq.bits > 4 and dq.cols % 128 == 0
+
+
+def gemv_batch(dq: "DeviceQT", x: torch.Tensor, epilogue: int = 0, resid: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [N, IN] -> y [N, OUT] fp32 with the packed weights read once for all N rows (mma.sync
+    tensor cores, tokens as the MMA columns, fp16 operands, fp32 accumulation)."""
+    _require_cuda(x, resid)
+    lib = _lib.load()
+    x = x.float()
+    if x.stride(-1) != 1 or x.stride(0) % 4 or x.data_ptr() % 16:
+        x = x.contiguous()
+    n = x.shape[0]
+    y = torch.empty((n, dq.rows), dtype=torch.float32, device=x.device)
+    _lib.check(lib.rwkvq_gemv_batch(C.byref(dq.struct), x.data_ptr(), n, x.stride(0), y.data_ptr(), y.stride(0),
+                                    epilogue, _lib.ptr(resid), _lib.stream_ptr()), "rwkvq_gemv_batch")
+    return y
+
+
 def gemm(dq: "DeviceQT", x: torch.Tensor, epilogue: int = 0, resid: Optional[torch.Tensor] = None,
          check: bool = False) -> torch.Tensor:
     """x [M, IN] fp32 -> y [M, OUT] fp32 on the tcgen05 tensor cores with the dequantisation

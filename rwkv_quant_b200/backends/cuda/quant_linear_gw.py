@@ -15,6 +15,9 @@ from ... import _lib
 # N at or above which the dequant + tensor-core GEMM path takes over from the
 # weight-streaming GEMV (the reference's crossover constant, quant_linear_gw.py:153)
 GEMM_MIN_BATCH_NB = 128
+# N up to which every column gets its own exact single-vector launch (results independent of
+# the batch they were computed in); between the two the weights-once small-batch kernel runs
+GEMV_MAX_BATCH = 2
 
 
 class _QuantLinearBase:
@@ -36,6 +39,10 @@ class _QuantLinearBase:
             # the reference's crossover (quant_linear_gw.py:846-849, quant_linear_sym.py:481-484):
             # its dequant + fp16 matmul; here the dequantisation is fused into the tensor-core GEMM
             y = ops.gemm(self.dq, x2.float(), epilogue, resid)
+        elif x2.shape[0] > GEMV_MAX_BATCH and ops.has_batch_layout(self.dq):
+            # the reference decodes each weight once per chunk of 4 columns (_gemv_nb,
+            # quant_linear_gw.py:850-905); here once per 64 columns
+            y = ops.gemv_batch(self.dq, x2, epilogue, resid)
         else:
             y = self.dq.gemv(x2, epilogue, resid)
         return y.reshape(*lead, self.out_features)

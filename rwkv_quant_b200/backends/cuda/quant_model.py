@@ -60,6 +60,7 @@ class QuantRWKV7:
         self.vocab_size = ckpt.vocab_size
         self.gemm_min_batch = int(gemm_min_batch)
         self.gemv_max_batch = int(gemv_max_batch)
+        self.batch_max = 64              # rows up to which the weights-once small-batch kernel serves a linear
         T = ckpt.tensors
         dev = self.device
         def dq(key):
@@ -203,6 +204,8 @@ class QuantRWKV7:
         (sb6 / sym); other layouts at large N: dequantise once + dense fp32 GEMM."""
         if x.shape[0] <= self.gemv_max_batch:
             return ops.gemv(dq.bufs, dq.meta, x, epilogue, resid)
+        if x.shape[0] <= self.batch_max and ops.has_batch_layout(dq):
+            return ops.gemv_batch(dq, x, epilogue, resid)
         if dq.kind in ("sb6", "sym"):
             return ops.gemm(dq, x, epilogue, resid)
         if x.shape[0] < self.gemm_min_batch:
@@ -254,7 +257,7 @@ class QuantRWKV7:
     def _prep_modes(self, N, lins):
         """Which form each mix row is written in: the scaled fp16 copy when its linear runs on
         the dequant-fused GEMM, else fp32."""
-        gemm = lambda dq: dq.kind in ("sb6", "sym") and N > self.gemv_max_batch
+        gemm = lambda dq: dq.kind in ("sb6", "sym") and N > max(self.gemv_max_batch, self.batch_max)
         return [ops.PREP_SCALED if gemm(dq) else ops.PREP_F32 for dq in lins]
 
     def _block_seq(self, i, L, x, v_first, state):

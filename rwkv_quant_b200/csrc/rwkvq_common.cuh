@@ -251,5 +251,9 @@ int launch_gemv_mma(int layout, const rwkvq_qtensor* ts, int n_mats, const void*
                     long long ldx, float* y, long long ldy, int epilogue, const float* resid,
                     int fused, cudaStream_t s, const void* const* x_each = nullptr, float* scratch = nullptr);
 size_t gemv_mma_scratch_bytes();
+// Small-batch tensor-core kernel (rwkvq_gemv_batch.cu): n_mats same-shape matrices, each with its
+// own [N, ldx] fp32 input and [N, ldy] output, weights read once for all N right-hand sides.
+int launch_gemv_batch(const rwkvq_qtensor* ts, int n_mats, const float* const* xs, int N, long long ldx,
+                      float* const* ys, long long ldy, int epilogue, const float* const* resids, cudaStream_t s);
 
 }  // namespace rwkvq

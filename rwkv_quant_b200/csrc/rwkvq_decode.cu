@@ -451,6 +451,8 @@ using namespace rwkvq;
 
 namespace {
 
+constexpr int kBatchMax = 256;     // streams up to which the small-batch kernel serves the linears of a step
+
 struct Workspace {
     float *x, *xs, *rkv, *part, *yl, *og, *xk, *hffn, *xo, *v_first, *logits, *argv, *gscratch, *gemm_ws;
     int n_chunks;
@@ -490,7 +492,15 @@ int linear(const rwkvq_qtensor* t, const float* x, int B, int in, float* y, int 
         return launch_gemv_mma(ml, t, 1, x, RWKVQ_F32, in, y, out, epi, resid, 0, static_cast<cudaStream_t>(stream),
                                nullptr, scratch);
     }
-    if (B > 2 && (t->kind == RWKVQ_KIND_SB6 || t->kind == RWKVQ_KIND_SYM))     // tensor-core path, weights read once
+    if (B > 2 && B <= kBatchMax && ml >= 0) {            // small batch: weights read once, tokens as MMA columns
+        int rc = validate_qtensor(t, "rwkvq_decode_step(linear)");
+        if (rc) return rc;
+        const float* xs[1] = {x};
+        float* ys[1] = {y};
+        const float* rs[1] = {resid};
+        return launch_gemv_batch(t, 1, xs, B, in, ys, out, epi, rs, static_cast<cudaStream_t>(stream));
+    }
+    if (B > 2 && (t->kind == RWKVQ_KIND_SB6 || t->kind == RWKVQ_KIND_SYM))     // tcgen05 path for large batches
         return rwkvq_gemm(t, x, B, in, y, out, epi, resid, gemm_ws, rwkvq_gemm_workspace_bytes_for(B, in), stream);
     return rwkvq_gemv(t, x, RWKVQ_F32, B, in, y, out, epi, resid, stream);
 }
@@ -621,6 +631,17 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
             const rwkvq_qtensor three[3] = {L.Wr, L.Wk, L.Wv};
             const void* x_each[3] = {xr, xk, xv};
             rc = launch_gemv_mma(ml, three, 3, xr, RWKVQ_F32, D, r, D, RWKVQ_EPI_NONE, nullptr, 1, s, x_each, w.gscratch);
+            if (rc) return rc;
+        } else if (B > 2 && B <= kBatchMax && ml >= 0 && mma_layout_of(L.Wk) == ml && mma_layout_of(L.Wv) == ml &&
+                   L.Wk.rows == L.Wr.rows && L.Wv.rows == L.Wr.rows && L.Wk.cols == L.Wr.cols && L.Wv.cols == L.Wr.cols) {
+            for (const rwkvq_qtensor* t : {&L.Wr, &L.Wk, &L.Wv}) {
+                rc = validate_qtensor(t, "rwkvq_decode_step(r/k/v)");
+                if (rc) return rc;
+            }
+            const rwkvq_qtensor three[3] = {L.Wr, L.Wk, L.Wv};
+            const float* x3[3] = {xr, xk, xv};
+            float* y3[3] = {r, k, v};
+            rc = launch_gemv_batch(three, 3, x3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, s);
             if (rc) return rc;
         } else {
             rc = linear(&L.Wr, xr, B, D, r, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream);

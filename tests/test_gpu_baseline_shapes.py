@@ -45,8 +45,11 @@ def test_layer_linear_shapes_batches(cuda_lib, layout, bits, rows, cols):
             assert y.shape == (n, rows) and err <= TOL, (layout, bits, n, dt, err)
             if dt == torch.float32:
                 outs[n] = y
-    # the weight-streaming GEMV computes every right-hand side on its own: rows do not depend on N
-    assert torch.equal(outs[8][:1], outs[1]) and torch.equal(outs[64][:8], outs[8])
+    # beyond 2 rows the operator reads the weights once for the whole batch (fp16 operands on the
+    # tensor cores): rows agree with the exact single-vector kernel within the operand rounding
+    scale = outs[1].abs().max().item()
+    assert (outs[8][:1] - outs[1]).abs().max().item() <= 5e-4 * scale
+    assert (outs[64][:8] - outs[8]).abs().max().item() <= 5e-4 * scale
     # the tensor-core GEMM (what the model uses beyond 2 rows): fp16 activations scaled per token
     from rwkv_quant_b200.backends.cuda import ops
     x512 = torch.randn(512, cols, generator=g).cuda()           # at and beyond 128 rows the operator itself

@@ -214,6 +214,95 @@ def test_gemv_wide_dynamic_range_activations(cuda_lib, layout, bits, n):
     assert relmax(y_small, ref_small) <= 5e-3
 
 
+BATCH_SHAPES = [(16, 256), (48, 512), (2048, 2048), (100, 2560), (2048, 8192), (1024, 4352), (8192, 2048), (2560, 10240)]
+
+
+@pytest.mark.parametrize("layout,bits", LAYOUTS[:6])
+@pytest.mark.parametrize("rows,cols", BATCH_SHAPES)
+def test_gemv_batch_matches_oracle(cuda_lib, layout, bits, rows, cols):
+    """The weights-once small-batch kernel against the fp64 product with the oracle's weights, for
+    every batch-size class (1, 2, 4, 8 token tiles; a ragged last tile; more than one 64-token
+    group) and every K split the launcher can choose (cluster of 1, 2, 4, 5, 8 CTAs; one or
+    several staged chunks); NaN-filled output so that an unwritten element cannot pass."""
+    import ctypes as C
+    from rwkv_quant_b200 import _lib
+    from rwkv_quant_b200.backends.cuda import ops
+    qt = _synth_linear(layout, bits, rows, cols, seed=rows + cols + bits)
+    dq = ops.DeviceQT(qt)
+    assert ops.has_batch_layout(dq)
+    w = _oracle_w(qt).astype(np.float64)
+    worst = 0.0
+    for n in (3, 8, 13, 32, 64, 70):
+        x = _x(n, cols, rows * 31 + cols + n)
+        y = torch.full((n, rows), float("nan"), device="cuda")
+        _lib.check(cuda_lib.rwkvq_gemv_batch(C.byref(dq.struct), x.data_ptr(), n, cols, y.data_ptr(), rows, 0, None,
+                                             _lib.stream_ptr()), "rwkvq_gemv_batch")
+        y = y.cpu().numpy()
+        assert np.isfinite(y).all(), f"n={n}: an element was not written"
+        ref = x.cpu().numpy().astype(np.float64) @ w.T
+        worst = max(worst, relmax(y, ref))
+        assert relmax(y, ref) <= TOL, (n, relmax(y, ref))
+    print(f"gemv_batch {layout}@{bits} [{rows},{cols}]: worst relmax {worst:.2e}")
+
+
+def test_gemv_batch_epilogues_scaling_and_refusals(cuda_lib):
+    import ctypes as C
+    from rwkv_quant_b200 import _lib
+    from rwkv_quant_b200.backends.cuda import ops
+    qt = _synth_linear("sb6", 5, 768, 2048, seed=4)
+    dq = ops.DeviceQT(qt)
+    w = _oracle_w(qt).astype(np.float64)
+    x = _x(9, 2048, 12)
+    resid = _x(9, 768, 13)
+    y0 = ops.gemv_batch(dq, x)
+    assert torch.equal(ops.gemv_batch(dq, x, 1, None), torch.relu(y0) ** 2)
+    assert torch.equal(ops.gemv_batch(dq, x, 2, resid), resid + y0)
+    assert torch.equal(ops.gemv_batch(dq, x), y0), "two launches on the same input differ"
+    # rows of very different magnitude in one batch, and a channel 1000 x larger than the rest:
+    # every token is scaled on its own, per staged chunk
+    xs = x.clone()
+    xs[0] *= 1e-6
+    xs[1] *= 3e4
+    xs[2, 5] *= 1000.0
+    xs[3] = 0.0
+    ref = xs.cpu().numpy().astype(np.float64) @ w.T
+    y = ops.gemv_batch(dq, xs).cpu().numpy()
+    for n in range(9):
+        assert np.abs(y[n] - ref[n]).max() <= TOL * max(np.abs(ref[n]).max(), 1e-30), n
+    assert (y[3] == 0).all()
+    # non-finite input propagates to its own row only
+    xs[4, 100] = float("inf")
+    y = ops.gemv_batch(dq, xs)
+    assert not torch.isfinite(y[4]).any() and torch.isfinite(y[[0, 1, 2, 3, 5, 6, 7, 8]]).all()
+    # strided rows
+    xp = torch.zeros(9, 2048 + 64, device="cuda")
+    xp[:, :2048] = x
+    assert torch.equal(ops.gemv_batch(dq, xp[:, :2048]), y0)
+    # layouts without the tensor-core form are refused, not served by something else
+    rtn4 = ops.DeviceQT(_synth_linear("rtn", 4, 64, 256))
+    yb = torch.empty(3, 64, device="cuda")
+    assert cuda_lib.rwkvq_gemv_batch(C.byref(rtn4.struct), x.data_ptr(), 3, 256, yb.data_ptr(), 64, 0, None,
+                                     _lib.stream_ptr()) == _lib.E_DTYPE
+    assert cuda_lib.rwkvq_gemv_batch(C.byref(dq.struct), x.data_ptr() + 4, 3, 2048, y0.data_ptr(), 768, 0, None,
+                                     _lib.stream_ptr()) == _lib.E_ALIGN
+
+
+def test_linear_classes_route_small_batches_through_the_batch_kernel(cuda_lib):
+    """3 <= N < 128 through the operator class: one pass over the weights (the reference reads them
+    once per chunk of 4 columns), result within the fp16-operand rounding of the exact kernel."""
+    from rwkv_quant_b200.backends import cuda as be
+    from rwkv_quant_b200.backends.cuda import ops
+    for layout, bits in (("sb6", 4), ("sym", 6), ("rtn", 8)):
+        qt = _synth_linear(layout, bits, 512, 1024, seed=bits)
+        lin = be.linear_for(qt)
+        x = _x(40, 1024, 3)
+        y = lin(x)
+        assert torch.equal(y, ops.gemv_batch(lin.dq, x))
+        exact = ops.gemv(lin.dq.bufs, lin.dq.meta, x, 0, None)
+        assert (y - exact).abs().max().item() <= 5e-4 * exact.abs().max().item()
+        assert torch.equal(lin(x[:2]), exact[:2])          # 1 and 2 rows: the exact kernel
+
+
 def test_errors_surface_as_exceptions(cuda_lib):
     from rwkv_quant_b200 import _lib
     from rwkv_quant_b200.backends.cuda import ops
