@@ -144,14 +144,17 @@ int rwkvq_gemv(const rwkvq_qtensor* t, const void* x, int x_dtype, int N, int64_
  *   x [N, ldx] fp32 (rows 16-byte aligned, ldx % 4 == 0), y / resid [N, ldy] fp32.
  *   Tensors: sb6 with dev_meta (and dev_planes at 5 / 6 bits), sym (dev_planes at 6 bits),
  *   per-row int8 with cols % 128 == 0; RWKVQ_E_DTYPE otherwise (use rwkvq_gemv).
- * Operands are fp16 (weights fp16(q*s+m); each token scaled by a power of two per 512-column
- * chunk), accumulation fp32 on mma.sync tensor cores; results differ from rwkvq_gemv's within
- * ~2e-4 of max|y| and do not depend on N's grouping only up to that rounding (not batch-invariant
- * bit for bit).  Allocates nothing and needs no workspace: the K split is reduced across a
- * thread-block cluster through distributed shared memory.
+ * Operands are fp16 (weights fp16(q*s+m); each token scaled by a power of two chosen from its
+ * max|x|), accumulation fp32 on mma.sync tensor cores; results differ from rwkvq_gemv's within
+ * ~2e-4 of max|y| (a column's bits may depend on the batch it is computed in; two calls on the same
+ * input give the same bits).  The K split is reduced across a thread-block cluster through
+ * distributed shared memory: no scratch for partial sums.
+ *   workspace: rwkvq_gemv_batch_workspace_bytes(N) bytes (one float per row: the max|x| a
+ *   one-block-per-row pre-pass writes before the product kernel starts).
  */
+size_t rwkvq_gemv_batch_workspace_bytes(int N);
 int rwkvq_gemv_batch(const rwkvq_qtensor* t, const float* x, int N, int64_t ldx, float* y, int64_t ldy,
-                     int epilogue, const float* resid, void* stream);
+                     int epilogue, const float* resid, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Quantized linear for MANY right-hand sides on the tcgen05 tensor cores (prefill,

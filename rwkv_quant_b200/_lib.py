@@ -67,8 +67,9 @@ _PROTOS = {
     "rwkvq_dequant": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "rwkvq_gemv": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_int, C.c_int64,
                              C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
+    "rwkvq_gemv_batch_workspace_bytes": (C.c_size_t, [C.c_int]),
     "rwkvq_gemv_batch": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_int64,
-                                   C.c_int, C.c_void_p, C.c_void_p]),
+                                   C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "rwkvq_gemm_workspace_bytes": (C.c_size_t, [C.c_int]),
     "rwkvq_gemm_workspace_bytes_for": (C.c_size_t, [C.c_int, C.c_int]),
     "rwkvq_gemm": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_int64,

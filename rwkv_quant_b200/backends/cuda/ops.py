@@ -276,8 +276,10 @@ def gemv_batch(dq: "DeviceQT", x: torch.Tensor, epilogue: int = 0, resid: Option
         x = x.contiguous()
     n = x.shape[0]
     y = torch.empty((n, dq.rows), dtype=torch.float32, device=x.device)
+    nws = lib.rwkvq_gemv_batch_workspace_bytes(n)
+    ws = torch.empty(nws, dtype=torch.uint8, device=x.device)
     _lib.check(lib.rwkvq_gemv_batch(C.byref(dq.struct), x.data_ptr(), n, x.stride(0), y.data_ptr(), y.stride(0),
-                                    epilogue, _lib.ptr(resid), _lib.stream_ptr()), "rwkvq_gemv_batch")
+                                    epilogue, _lib.ptr(resid), ws.data_ptr(), nws, _lib.stream_ptr()), "rwkvq_gemv_batch")
     return y
 
 

@@ -252,8 +252,19 @@ int launch_gemv_mma(int layout, const rwkvq_qtensor* ts, int n_mats, const void*
                     int fused, cudaStream_t s, const void* const* x_each = nullptr, float* scratch = nullptr);
 size_t gemv_mma_scratch_bytes();
 // Small-batch tensor-core kernel (rwkvq_gemv_batch.cu): n_mats same-shape matrices, each with its
-// own [N, ldx] fp32 input and [N, ldy] output, weights read once for all N right-hand sides.
-int launch_gemv_batch(const rwkvq_qtensor* ts, int n_mats, const float* const* xs, int N, long long ldx,
-                      float* const* ys, long long ldy, int epilogue, const float* const* resids, cudaStream_t s);
+// own [N, ldx] input and [N, ldy] output; weights read once for all N right-hand sides.  Inputs are
+// fp32 rows with scales[k] = max|x| of every row (written by the producer of x or by launch_row_amax),
+// or (half_in) fp16 rows already multiplied per row by a power of two with scales[k] = its inverse.
+// amax_outs (optional, per matrix): [N] slots the kernel merges max|y| per token into (atomic max on
+// the bit pattern; zero them before the launch).
+int launch_gemv_batch(const rwkvq_qtensor* ts, int n_mats, const void* const* xs, bool half_in, const float* const* scales,
+                      int N, long long ldx, float* const* ys, long long ldy, int epilogue, const float* const* resids,
+                      float* const* amax_outs, cudaStream_t s);
+// LoRA pair of the time-mix block for a batch of streams on the tensor cores (rwkvq_lora_mma.cu)
+bool lora_mma_ok(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, int n_br, int D);
+int launch_lora_pair_mma(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, const float* const* xs,
+                         float* const* ys, const int* acts, int n_br, int B, int D, int max_rank, float* h, int n_stride,
+                         cudaStream_t s);
+int launch_row_amax(const float* x, long long ldx, int cols, int N, float* amax, cudaStream_t s);
 
 }  // namespace rwkvq

@@ -85,8 +85,18 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
                                                                   const float* __restrict__ ln_b,
                                                                   float* __restrict__ shift,
                                                                   const float* __restrict__ mix,
-                                                                  float* __restrict__ out, int B, int D) {
+                                                                  float* __restrict__ out, int B, int D,
+                                                                  __half* __restrict__ x16_out, float* __restrict__ unscale_out,
+                                                                  int x16_mask,
+                                                                  float* __restrict__ zero_a, float* __restrict__ zero_b) {
+    // x16_out (optional) [max(NMIX, 1)][B][D] with unscale_out [max(NMIX, 1)][B]: the rows selected by
+    // x16_mask also as fp16(out * 2^s), s chosen from the row's max so that no value leaves the fp16
+    // range, and 2^-s: the form the small-batch linear reads (half the bytes, no conversion there);
+    // zero_a / zero_b (optional) [B]: slots later kernels of the layer merge their own row maxima
+    // into, cleared here for stream b
+    constexpr int NM = NMIX > 0 ? NMIX : 1;
     __shared__ float red[kRowThreads / 32];
+    __shared__ float redm[kRowThreads / 32][NM];
     const int b = blockIdx.x;
     float v[kRowPer], prev[kRowPer], lw[kRowPer], lb[kRowPer];
     pdl_launch_dependents();
@@ -97,6 +107,10 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
         lb[i] = d < D ? ln_b[d] : 0.f;
     }
     pdl_wait();
+    if (threadIdx.x == 0) {
+        if (zero_a) zero_a[b] = 0.f;
+        if (zero_b) zero_b[b] = 0.f;
+    }
 #pragma unroll
     for (int i = 0; i < kRowPer; ++i) {
         const int d = threadIdx.x + i * kRowThreads;
@@ -116,17 +130,65 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
         s2 += c * c;
     }
     const float inv = 1.0f / sqrtf(block_sum(s2, red) / D + 1e-5f);
+    float mx[NM];
+#pragma unroll
+    for (int m = 0; m < NM; ++m) mx[m] = 0.f;
 #pragma unroll
     for (int i = 0; i < kRowPer; ++i) {
         const int d = threadIdx.x + i * kRowThreads;
         if (d >= D) continue;
         const size_t bd = static_cast<size_t>(b) * D + d;
         const float xn = (v[i] - mean) * inv * lw[i] + lb[i];
-        if (NMIX == 0) { out[bd] = xn; continue; }
+        if (NMIX == 0) { out[bd] = xn; mx[0] = fmaxf(mx[0], fabsf(xn)); continue; }
         const float xx = prev[i] - xn;
         shift[bd] = xn;
 #pragma unroll
-        for (int m = 0; m < NMIX; ++m) out[(static_cast<size_t>(m) * B) * D + bd] = xn + xx * __ldg(mix + m * D + d);
+        for (int m = 0; m < NMIX; ++m) {
+            const float o = xn + xx * __ldg(mix + m * D + d);
+            out[(static_cast<size_t>(m) * B) * D + bd] = o;
+            mx[m < NM ? m : 0] = fmaxf(mx[m < NM ? m : 0], fabsf(o));
+        }
+    }
+    if (x16_out != nullptr) {
+        __shared__ float sc_m[NM];
+#pragma unroll
+        for (int m = 0; m < NM; ++m) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx[m] = fmaxf(mx[m], __shfl_xor_sync(0xFFFFFFFFu, mx[m], o));
+            if ((threadIdx.x & 31) == 0) redm[threadIdx.x >> 5][m] = mx[m];
+        }
+        __syncthreads();
+        if (threadIdx.x < NM) {
+            float r = 0.f;
+            for (int w = 0; w < kRowThreads / 32; ++w) r = fmaxf(r, redm[w][threadIdx.x]);
+            // |x| * 2^(14 - e) <= 2^14 with max|x| <= 2^e; a non-finite row keeps scale 1 and propagates
+            float s1 = 1.f, u1 = 1.f;
+            if (r > 0.f && r < INFINITY) {
+                int e = 0;
+                frexpf(r, &e);
+                e = max(-100, e);
+                s1 = ldexpf(1.f, 14 - e);
+                u1 = ldexpf(1.f, e - 14);
+            }
+            sc_m[threadIdx.x] = s1;
+            if ((x16_mask >> threadIdx.x) & 1) unscale_out[threadIdx.x * B + b] = u1;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < kRowPer; ++i) {
+            const int d = threadIdx.x + i * kRowThreads;
+            if (d >= D) continue;
+            const size_t bd = static_cast<size_t>(b) * D + d;
+            const float xn = (v[i] - mean) * inv * lw[i] + lb[i];
+            if (NMIX == 0) { x16_out[bd] = __float2half_rn(xn * sc_m[0]); continue; }
+            const float xx = prev[i] - xn;
+#pragma unroll
+            for (int m = 0; m < NMIX; ++m) {
+                if (!((x16_mask >> m) & 1)) continue;
+                const float o = xn + xx * __ldg(mix + m * D + d);
+                x16_out[(static_cast<size_t>(m) * B) * D + bd] = __float2half_rn(o * sc_m[m < NM ? m : 0]);
+            }
+        }
     }
 }
 
@@ -332,6 +394,7 @@ struct TmixCoreArgs {
     float* state;                      // [B, H, 64, 64] in place
     float* og;                         // [B, D]
     int D, H, layer0;
+    float* og_amax;                    // optional [B]: max|og| per stream is merged into it (atomic max on the bits)
 };
 
 __global__ void __launch_bounds__(256) tmix_core_kernel(const TmixCoreArgs p) {
@@ -400,7 +463,14 @@ __global__ void __launch_bounds__(256) tmix_core_kernel(const TmixCoreArgs p) {
     if (tid < 64) {
         const int c = hi * 64 + tid;
         const float nrm = dc * (1.0f / sqrtf(var + 64e-5f));
-        p.og[row + tid] = (nrm * p.lnx_w[c] + p.lnx_b[c] + dp * sV[tid]) * sG[tid];
+        const float o = (nrm * p.lnx_w[c] + p.lnx_b[c] + dp * sV[tid]) * sG[tid];
+        p.og[row + tid] = o;
+        if (p.og_amax != nullptr) {          // warps 0 and 1 hold the 64 outputs
+            float m = fabsf(o);
+#pragma unroll
+            for (int of = 16; of > 0; of >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, of));
+            if ((tid & 31) == 0) atomicMax(reinterpret_cast<int*>(p.og_amax) + b, __float_as_int(m));
+        }
     }
 }
 
@@ -452,10 +522,14 @@ using namespace rwkvq;
 namespace {
 
 constexpr int kBatchMax = 256;     // streams up to which the small-batch kernel serves the linears of a step
+inline bool batch_path(int B) { return B > 2 && B <= kBatchMax; }
 
 struct Workspace {
     float *x, *xs, *rkv, *part, *yl, *og, *xk, *hffn, *xo, *v_first, *logits, *argv, *gscratch, *gemm_ws;
+    float* amax;             // [10][B] per-row scale inverses / maxima for the small-batch linears: 6 mix rows, og, xk, hffn, xo
+    __half *xs16, *xk16, *xo16;     // fp16 forms of the mix rows, the channel-mix row and the final row
     int n_chunks;
+    size_t part_floats;
     size_t bytes;
 };
 
@@ -470,10 +544,15 @@ Workspace carve(const rwkvq_model& m, int B, void* base) {
     };
     w.x = take(b * D); w.xs = take(6 * b * D); w.rkv = take(3 * b * D);
     w.n_chunks = static_cast<int>((D + kLdRows - 1) / kLdRows);
-    w.part = take(4 * static_cast<size_t>(w.n_chunks) * ((b + kLmMaxN - 1) / kLmMaxN * kLmMaxN) * R);   // upper bound (rep = 1)
+    w.part_floats = 4 * static_cast<size_t>(w.n_chunks) * ((b + kLmMaxN - 1) / kLmMaxN * kLmMaxN) * R;   // upper bound (rep = 1)
+    w.part = take(w.part_floats);
     w.yl = take(4 * b * D); w.og = take(b * D); w.xk = take(b * D); w.hffn = take(b * F);
     w.xo = take(b * D); w.v_first = take(b * D); w.logits = take(b * V);
     w.argv = take(2 * b * kArgSlices);
+    w.amax = take(10 * b);
+    w.xs16 = reinterpret_cast<__half*>(take(3 * b * D));
+    w.xk16 = reinterpret_cast<__half*>(take((b * D + 1) / 2));
+    w.xo16 = reinterpret_cast<__half*>(take((b * D + 1) / 2));
     w.gscratch = take(gemv_mma_scratch_bytes() / sizeof(float));
     w.gemm_ws = take(rwkvq_gemm_workspace_bytes_for(B, static_cast<int>(F > D ? F : D)) / sizeof(float) + 1);
     w.bytes = off;
@@ -483,8 +562,12 @@ Workspace carve(const rwkvq_model& m, int B, void* base) {
 // y_br = (act_br(x_br @ W1_br)) @ W2_br for up to 4 branches, B right-hand sides
 // One quantized linear for B right-hand sides; the single-vector tensor-core kernel gets
 // the K-split scratch, everything else goes through the public entry point.
+// x16 / x_scale: the fp16 form of x with its per-row scale inverses (what the LayerNorm kernels write
+// on the small-batch path), or null with x_scale = max|x| per row for fp32 rows; y_amax: optional
+// slots max|y| per row is merged into.
 int linear(const rwkvq_qtensor* t, const float* x, int B, int in, float* y, int out, int epi, const float* resid,
-           float* scratch, void* gemm_ws, void* stream) {
+           float* scratch, void* gemm_ws, void* stream, const __half* x16 = nullptr, const float* x_scale = nullptr,
+           float* y_amax = nullptr) {
     const int ml = mma_layout_of(*t);
     if (B == 1 && ml >= 0) {
         int rc = validate_qtensor(t, "rwkvq_decode_step(linear)");
@@ -492,13 +575,15 @@ int linear(const rwkvq_qtensor* t, const float* x, int B, int in, float* y, int 
         return launch_gemv_mma(ml, t, 1, x, RWKVQ_F32, in, y, out, epi, resid, 0, static_cast<cudaStream_t>(stream),
                                nullptr, scratch);
     }
-    if (B > 2 && B <= kBatchMax && ml >= 0) {            // small batch: weights read once, tokens as MMA columns
+    if (batch_path(B) && ml >= 0 && x_scale) {            // small batch: weights read once, tokens as MMA columns
         int rc = validate_qtensor(t, "rwkvq_decode_step(linear)");
         if (rc) return rc;
-        const float* xs[1] = {x};
+        const void* xs[1] = {x16 ? static_cast<const void*>(x16) : static_cast<const void*>(x)};
+        const float* sc[1] = {x_scale};
         float* ys[1] = {y};
         const float* rs[1] = {resid};
-        return launch_gemv_batch(t, 1, xs, B, in, ys, out, epi, rs, static_cast<cudaStream_t>(stream));
+        float* ao[1] = {y_amax};
+        return launch_gemv_batch(t, 1, xs, x16 != nullptr, sc, B, in, ys, out, epi, rs, ao, static_cast<cudaStream_t>(stream));
     }
     if (B > 2 && (t->kind == RWKVQ_KIND_SB6 || t->kind == RWKVQ_KIND_SYM))     // tcgen05 path for large batches
         return rwkvq_gemm(t, x, B, in, y, out, epi, resid, gemm_ws, rwkvq_gemm_workspace_bytes_for(B, in), stream);
@@ -541,7 +626,7 @@ int lora_rep(int B) { return B > kLmMaxN ? 8 : 1; }
 
 int lora_pair(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, const float* const* xs,
               float* const* ys, const int* acts, int n_br, int B, int D, int max_rank, float* part,
-              int n_chunks, cudaStream_t s) {
+              size_t part_floats, int n_chunks, cudaStream_t s) {
     LoraDownArgs d{};
     LoraUpArgs u{};
     int max_cols = 0;
@@ -558,6 +643,12 @@ int lora_pair(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, co
         u.t[i] = make_view(*t2[i]);
         u.act[i] = acts[i];
         if (t2[i]->cols > max_cols) max_cols = t2[i]->cols;
+    }
+    if (B > kLmMaxN && lora_mma_ok(t1, t2, n_br, D)) {
+        // more than one group of streams: both products on the tensor cores, matrices read once
+        const int n_stride = ((B + 63) / 64) * 64;
+        if (static_cast<size_t>(4) * n_stride * max_rank <= part_floats)
+            return launch_lora_pair_mma(t1, t2, xs, ys, acts, n_br, B, D, max_rank, part, n_stride, s);
     }
     // large batches: a CTA accumulates 8 sub-chunks of 64 rows, so that the up projection adds
     // 8x fewer partial sums per right-hand side; the groups of 8 right-hand sides are grid.z
@@ -609,7 +700,13 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         const rwkvq_layer& L = m->layers[l];
         const bool layer0 = l == 0;
         // ---- time mix
-        launch_pdl(ln_shift_mix_kernel<6>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln1_w, L.ln1_b, tshift[l], L.x_mix, w.xs, B, D);
+        // the row maxima feed the small-batch linears: slots 0-5 the six mix rows, 6 og, 7 xk, 8 hffn, 9 xo
+        const bool bp = batch_path(B);
+        float* am = bp ? w.amax : nullptr;
+        float *am_og = bp ? w.amax + 6 * B : nullptr, *am_xk = bp ? w.amax + 7 * B : nullptr;
+        float *am_h = bp ? w.amax + 8 * B : nullptr;
+        launch_pdl(ln_shift_mix_kernel<6>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln1_w, L.ln1_b, tshift[l], L.x_mix, w.xs, B, D,
+                   bp ? w.xs16 : static_cast<__half*>(nullptr), am, 0b001101, am_og, am_h);      // r, k, v rows also as fp16
         float *xr = w.xs, *xw = w.xs + BD, *xk = w.xs + 2 * BD, *xv = w.xs + 3 * BD, *xa = w.xs + 4 * BD,
               *xg = w.xs + 5 * BD;
         float *r = w.rkv, *k = w.rkv + BD, *v = w.rkv + 2 * BD;
@@ -632,23 +729,26 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
             const void* x_each[3] = {xr, xk, xv};
             rc = launch_gemv_mma(ml, three, 3, xr, RWKVQ_F32, D, r, D, RWKVQ_EPI_NONE, nullptr, 1, s, x_each, w.gscratch);
             if (rc) return rc;
-        } else if (B > 2 && B <= kBatchMax && ml >= 0 && mma_layout_of(L.Wk) == ml && mma_layout_of(L.Wv) == ml &&
+        } else if (bp && ml >= 0 && mma_layout_of(L.Wk) == ml && mma_layout_of(L.Wv) == ml &&
                    L.Wk.rows == L.Wr.rows && L.Wv.rows == L.Wr.rows && L.Wk.cols == L.Wr.cols && L.Wv.cols == L.Wr.cols) {
             for (const rwkvq_qtensor* t : {&L.Wr, &L.Wk, &L.Wv}) {
                 rc = validate_qtensor(t, "rwkvq_decode_step(r/k/v)");
                 if (rc) return rc;
             }
             const rwkvq_qtensor three[3] = {L.Wr, L.Wk, L.Wv};
-            const float* x3[3] = {xr, xk, xv};
+            const void* x3[3] = {w.xs16, w.xs16 + 2 * BD, w.xs16 + 3 * BD};
+            const float* a3[3] = {am, am + 2 * B, am + 3 * B};
             float* y3[3] = {r, k, v};
-            rc = launch_gemv_batch(three, 3, x3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, s);
+            rc = launch_gemv_batch(three, 3, x3, true, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, s);
             if (rc) return rc;
         } else {
-            rc = linear(&L.Wr, xr, B, D, r, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream);
+            rc = linear(&L.Wr, xr, B, D, r, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream, bp ? w.xs16 : nullptr, am);
             if (rc) return rc;
-            rc = linear(&L.Wk, xk, B, D, k, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream);
+            rc = linear(&L.Wk, xk, B, D, k, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream,
+                        bp ? w.xs16 + 2 * BD : nullptr, bp ? am + 2 * B : nullptr);
             if (rc) return rc;
-            rc = linear(&L.Wv, xv, B, D, v, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream);
+            rc = linear(&L.Wv, xv, B, D, v, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream,
+                        bp ? w.xs16 + 3 * BD : nullptr, bp ? am + 3 * B : nullptr);
             if (rc) return rc;
         }
         float *yw = w.yl, *ya = w.yl + BD, *yv = w.yl + 2 * BD, *yg = w.yl + 3 * BD;
@@ -658,7 +758,7 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
             const float* x1[4] = {xw, xa, xg, xv};
             float* y2[4] = {yw, ya, yg, yv};
             const int act[4] = {1, 0, 2, 0};       // tanh (decay), none, sigmoid (gate), none
-            rc = lora_pair(t1, t2, x1, y2, act, layer0 ? 3 : 4, B, D, m->max_rank, w.part, w.n_chunks, s_lora);
+            rc = lora_pair(t1, t2, x1, y2, act, layer0 ? 3 : 4, B, D, m->max_rank, w.part, w.part_floats, w.n_chunks, s_lora);
             if (rc) return rc;
         }
         if (lane) {                                  // join before the time-mix core
@@ -666,19 +766,23 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
                 return fail(RWKVQ_E_LAUNCH, "rwkvq_decode_step: join of the side stream failed");
         }
         TmixCoreArgs tc{r, k, v, yw, ya, layer0 ? nullptr : yv, yg, L.w0, L.a0, L.v0, L.k_k, L.k_a, L.r_k,
-                        L.lnx_w, L.lnx_b, w.v_first, wkv[l], w.og, D, H, layer0 ? 1 : 0};
+                        L.lnx_w, L.lnx_b, w.v_first, wkv[l], w.og, D, H, layer0 ? 1 : 0, am_og};
         launch_pdl(tmix_core_kernel, dim3(H, B), dim3(256), 0, s, tc);
-        rc = linear(&L.Wo, w.og, B, D, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, w.gemm_ws, stream);
+        rc = linear(&L.Wo, w.og, B, D, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, w.gemm_ws, stream, nullptr, am_og);
         if (rc) return rc;
         // ---- channel mix
-        launch_pdl(ln_shift_mix_kernel<1>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln2_w, L.ln2_b, cshift[l], L.ffn_x_k, w.xk, B, D);
-        rc = linear(&L.Wfk, w.xk, B, D, w.hffn, F, RWKVQ_EPI_RELU2, nullptr, w.gscratch, w.gemm_ws, stream);
+        launch_pdl(ln_shift_mix_kernel<1>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln2_w, L.ln2_b, cshift[l], L.ffn_x_k, w.xk, B, D,
+                   bp ? w.xk16 : static_cast<__half*>(nullptr), am_xk, 1, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
+        rc = linear(&L.Wfk, w.xk, B, D, w.hffn, F, RWKVQ_EPI_RELU2, nullptr, w.gscratch, w.gemm_ws, stream, bp ? w.xk16 : nullptr,
+                    am_xk, am_h);
         if (rc) return rc;
-        rc = linear(&L.Wfv, w.hffn, B, F, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, w.gemm_ws, stream);
+        rc = linear(&L.Wfv, w.hffn, B, F, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, w.gemm_ws, stream, nullptr, am_h);
         if (rc) return rc;
     }
-    launch_pdl(ln_shift_mix_kernel<0>, dim3(B), dim3(kRowThreads), 0, s, w.x, m->lnout_w, m->lnout_b, static_cast<float*>(nullptr), static_cast<const float*>(nullptr), w.xo, B, D);
-    rc = linear(&m->head, w.xo, B, D, lg, V, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream);
+    float* am_xo = batch_path(B) ? w.amax + 9 * B : nullptr;
+    launch_pdl(ln_shift_mix_kernel<0>, dim3(B), dim3(kRowThreads), 0, s, w.x, m->lnout_w, m->lnout_b, static_cast<float*>(nullptr), static_cast<const float*>(nullptr), w.xo, B, D,
+               am_xo ? w.xo16 : static_cast<__half*>(nullptr), am_xo, 1, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
+    rc = linear(&m->head, w.xo, B, D, lg, V, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream, am_xo ? w.xo16 : nullptr, am_xo);
     if (rc) return rc;
     if (next_tokens) {
         float* pv = w.argv;

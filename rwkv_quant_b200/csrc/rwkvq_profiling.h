@@ -11,6 +11,11 @@ extern "C" {
  * process records global-timer nanoseconds of its pipeline events (slot map in the kernel source);
  * NULL (the default) switches it off. */
 void rwkvq_profiling_gemm_trace(void* buf512);
+/* With a device buffer of 8 uint64 set, CTA (0,0,0) of every later small-batch launch records
+ * global-timer nanoseconds: 0 start, 1 producer done, 2 activations staged, 3 products done,
+ * 4 cluster barrier passed, 5 reduced and stored, 6 end.  force_ks > 0 overrides the launcher's choice:
+ * low 4 bits the cluster size, +16 groups of 256 rows, +32 groups of 128 rows. */
+void rwkvq_profiling_batch_trace(void* buf8, int force_ks);
 #ifdef __cplusplus
 }
 #endif

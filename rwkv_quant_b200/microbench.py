@@ -178,6 +178,58 @@ def gemm_sweep(recipe="compression", Ms=(64, 512, 8192), reps=20):
             print(f"gemm {layout}@{bits} [{rows},{cols}] M={M}: {us:8.1f} us  {2.0 * M * rows * cols / us / 1e6:7.1f} TFLOP/s", flush=True)
 
 
+def batch_sweep(recipe="compression", Ns=(8, 64), reps=40, ring=24):
+    """rwkvq_gemv_batch on the linear shapes of a 1.5B layer and the head: microseconds per launch in
+    a CUDA graph over a ring of distinct weight copies (working set beyond the L2), GB/s of file
+    bytes, and the in-kernel marks of CTA (0,0,0) for one launch."""
+    lib = _lib.load()
+    tr = lib.rwkvq_profiling_batch_trace            # rwkvq_profiling.h: not part of the C ABI
+    tr.restype, tr.argtypes = None, [C.c_void_p, C.c_int]
+    lay = {"compression": [("sb6", 5, 2048, 2048), ("sb6", 4, 8192, 2048), ("sb6", 4, 2048, 8192), ("sb6", 5, 65536, 2048)],
+           "reduction": [("sym", 8, 2048, 2048), ("sym", 6, 8192, 2048), ("sym", 6, 2048, 8192), ("sym", 8, 65536, 2048)]}[recipe]
+    for layout, bits, rows, cols in lay:
+        n_ring = 2 if rows == 65536 else ring
+        dqs = [_tensor(layout, bits, rows, cols, seed=i) for i in range(n_ring)]
+        for N in Ns:
+            x = torch.randn(N, cols, device="cuda")
+            y = torch.empty(N, rows, device="cuda")
+            ws = torch.empty(max(256, lib.rwkvq_gemv_batch_workspace_bytes(N)), dtype=torch.uint8, device="cuda")
+            for ks in (0, 4 | 32, 8 | 32, 2 | 16, 4 | 16, 8 | 16):      # forced cluster size; +16: 256-row groups, +32: 128-row
+                tr(None, ks)
+
+                def run():
+                    for dq in dqs:
+                        _lib.check(lib.rwkvq_gemv_batch(C.byref(dq.struct), x.data_ptr(), N, cols, y.data_ptr(), rows, 0,
+                                                        None, ws.data_ptr(), ws.numel(), _lib.stream_ptr()), "rwkvq_gemv_batch")
+                run()
+                st = torch.cuda.Stream()
+                st.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(st):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=st):
+                        run()
+                torch.cuda.current_stream().wait_stream(st)
+                g.replay(); torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps):
+                    g.replay()
+                e1.record(); torch.cuda.synchronize()
+                us = e0.elapsed_time(e1) * 1e3 / reps / n_ring
+                buf = torch.zeros(8, dtype=torch.int64, device="cuda")
+                tr(buf.data_ptr(), ks)
+                _lib.check(lib.rwkvq_gemv_batch(C.byref(dqs[0].struct), x.data_ptr(), N, cols, y.data_ptr(), rows, 0, None,
+                                                ws.data_ptr(), ws.numel(), _lib.stream_ptr()), "rwkvq_gemv_batch")
+                torch.cuda.synchronize()
+                tr(None, 0)
+                m = buf.cpu().numpy().astype(np.float64)
+                marks = " ".join(f"{(m[i] - m[0]) * 1e-3:.1f}" for i in range(1, 7))
+                print(f"batch {layout}@{bits} [{rows},{cols}] N={N} ks={(str(ks & 15) + ('/256' if ks & 16 else '/128')) if ks else 'auto'}: {us:7.1f} us/launch "
+                      f"{dqs[0].nbytes_file() / us / 1e3:7.0f} GB/s   marks(us) {marks}", flush=True)
+        del dqs
+        torch.cuda.empty_cache()
+
+
 def gemm_once(layout="sb6", bits=5, rows=2048, cols=2048, M=8192, launches=3):
     """A few plain rwkvq_gemm launches of one shape (the target of ncu captures)."""
     dq = _tensor(layout, bits, rows, cols)
@@ -368,6 +420,8 @@ def main():
     go.add_argument("layout"); go.add_argument("bits", type=int); go.add_argument("rows", type=int)
     go.add_argument("cols", type=int); go.add_argument("--M", type=int, default=8192)
     go.add_argument("--launches", type=int, default=3)
+    bs = sub.add_parser("batch-sweep")
+    bs.add_argument("--recipe", default="compression")
     gt = sub.add_parser("gemm-timeline")
     gt.add_argument("--M", type=int, default=8192); gt.add_argument("--rows", type=int, default=2048)
     gt.add_argument("--cols", type=int, default=2048)
@@ -388,6 +442,9 @@ def main():
         return
     if a.cmd == "gemm":
         gemm_once(a.layout, a.bits, a.rows, a.cols, a.M, a.launches)
+        return
+    if a.cmd == "batch-sweep":
+        batch_sweep(a.recipe)
         return
     if a.cmd == "gemm-timeline":
         gemm_timeline("sb6", 5, a.rows, a.cols, a.M)

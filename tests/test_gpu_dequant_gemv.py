@@ -235,8 +235,9 @@ def test_gemv_batch_matches_oracle(cuda_lib, layout, bits, rows, cols):
     for n in (3, 8, 13, 32, 64, 70):
         x = _x(n, cols, rows * 31 + cols + n)
         y = torch.full((n, rows), float("nan"), device="cuda")
+        ws = torch.empty(cuda_lib.rwkvq_gemv_batch_workspace_bytes(n), dtype=torch.uint8, device="cuda")
         _lib.check(cuda_lib.rwkvq_gemv_batch(C.byref(dq.struct), x.data_ptr(), n, cols, y.data_ptr(), rows, 0, None,
-                                             _lib.stream_ptr()), "rwkvq_gemv_batch")
+                                             ws.data_ptr(), ws.numel(), _lib.stream_ptr()), "rwkvq_gemv_batch")
         y = y.cpu().numpy()
         assert np.isfinite(y).all(), f"n={n}: an element was not written"
         ref = x.cpu().numpy().astype(np.float64) @ w.T
@@ -281,10 +282,13 @@ def test_gemv_batch_epilogues_scaling_and_refusals(cuda_lib):
     # layouts without the tensor-core form are refused, not served by something else
     rtn4 = ops.DeviceQT(_synth_linear("rtn", 4, 64, 256))
     yb = torch.empty(3, 64, device="cuda")
+    ws = torch.empty(256, dtype=torch.uint8, device="cuda")
     assert cuda_lib.rwkvq_gemv_batch(C.byref(rtn4.struct), x.data_ptr(), 3, 256, yb.data_ptr(), 64, 0, None,
-                                     _lib.stream_ptr()) == _lib.E_DTYPE
+                                     ws.data_ptr(), 256, _lib.stream_ptr()) == _lib.E_DTYPE
     assert cuda_lib.rwkvq_gemv_batch(C.byref(dq.struct), x.data_ptr() + 4, 3, 2048, y0.data_ptr(), 768, 0, None,
-                                     _lib.stream_ptr()) == _lib.E_ALIGN
+                                     ws.data_ptr(), 256, _lib.stream_ptr()) == _lib.E_ALIGN
+    assert cuda_lib.rwkvq_gemv_batch(C.byref(dq.struct), x.data_ptr(), 3, 2048, y0.data_ptr(), 768, 0, None,
+                                     ws.data_ptr(), 4, _lib.stream_ptr()) == _lib.E_LIMIT
 
 
 def test_linear_classes_route_small_batches_through_the_batch_kernel(cuda_lib):

@@ -380,3 +380,25 @@ def test_two_decoders_on_two_streams_match_serial_runs(cuda_lib):
     assert not errs, errs
     for i in (0, 1):
         assert torch.equal(res[i], want[i]), f"decoder {i} (two threads)"
+
+
+@pytest.mark.parametrize("preset", ["reduction", "compression"])
+@pytest.mark.parametrize("B", [3, 9, 20, 40, 70])
+def test_decode_batches_match_oracle(cuda_lib, preset, B):
+    """Batched decode on the reference-written toy files: 3..8 streams (small-batch linears, per-
+    stream LoRA kernels), 9..64 (tensor-core LoRA pair: one, two and four 16-stream tiles) and
+    more than 64 (two stream groups), 4 teacher-forced tokens, logits and states against the oracle."""
+    model, oracle, _ = _load(preset)
+    toks = np.random.default_rng(B).integers(1, 500, (B, 4))
+    ref_st = oracle.init_state(B)
+    dec = model.decoder(B, use_graph=False)
+    tk = torch.from_numpy(toks).cuda()
+    for t in range(4):
+        ref, ref_st = oracle.forward_stateful(toks[:, t:t + 1], ref_st)
+        dec.step(tk[:, t])
+        err = relmax(dec.logits.cpu().numpy(), ref[:, 0])
+        assert err <= 1e-3, (t, err)
+    for (w, ts, cs), (rw, rts, rcs) in zip(dec.states, ref_st):
+        assert float(np.abs(w.cpu().numpy() - rw).max()) <= 1e-3 * max(1.0, np.abs(rw).max())
+        assert relmax(ts.reshape(B, -1).cpu().numpy(), rts) <= 1e-3
+        assert relmax(cs.reshape(B, -1).cpu().numpy(), rcs) <= 1e-3
