@@ -367,9 +367,14 @@ class QuantRWKV7:
             tok = dec.step(tok)
         return torch.stack(out, dim=1), dec.states
 
-    def decoder(self, batch_size: int = 1, states=None, use_graph: bool = True, self_feed: bool = False):
+    def decoder(self, batch_size: int = 1, states=None, use_graph: bool = True, self_feed: bool = False, groups=None):
         """A ``Decoder``: the whole token of ``batch_size`` streams as one CUDA-graph replay."""
-        return Decoder(self, batch_size, states, use_graph, self_feed)
+        return Decoder(self, batch_size, states, use_graph, self_feed, groups)
+
+    def decode_groups(self, batch_size: int) -> int:
+        """Stream groups whose launch chains run side by side (see ``Decoder``): two from 48 streams
+        on (measured on B200, 1.5B: 64 streams 4.45 -> 3.84 ms per step; 32 streams and fewer lose)."""
+        return 2 if batch_size >= 48 else 1
 
     @property
     def launches_per_token(self) -> int:
@@ -381,9 +386,14 @@ class QuantRWKV7:
 class Decoder:
     """Token-by-token greedy decoding of B streams with device-resident state.
     ``step(tokens)`` feeds tokens [B] and returns the argmax next tokens [B] (device);
-    with ``use_graph`` the whole token (all kernels) is one CUDA-graph replay."""
+    with ``use_graph`` the whole token (all kernels) is one CUDA-graph replay.
 
-    def __init__(self, model: QuantRWKV7, batch_size, states=None, use_graph=True, self_feed=False):
+    ``groups`` > 1 splits the streams into that many groups whose launch chains run side by
+    side on their own CUDA streams (parallel branches of the captured graph): a chain is a
+    sequence of dependent, latency-bound launches none of which fills the GPU, so two or four
+    of them overlap; the price is that every group streams the weights itself."""
+
+    def __init__(self, model: QuantRWKV7, batch_size, states=None, use_graph=True, self_feed=False, groups=None):
         self.m, self.B = model, batch_size
         self.self_feed = self_feed        # the replayed graph ends by feeding the argmax back
         st = model.init_state(batch_size) if states is None else states
@@ -392,14 +402,32 @@ class Decoder:
         self.tokens = torch.zeros(batch_size, dtype=torch.long, device=dev)
         self.next_tokens = torch.zeros(batch_size, dtype=torch.long, device=dev)
         self.logits = torch.empty((batch_size, model.vocab_size), dtype=torch.float32, device=dev)
-        self._ws = model._new_workspace(batch_size)       # its own: decoders on different streams may overlap
+        if groups is None:
+            groups = model.decode_groups(batch_size)
+        self.groups = max(1, min(int(groups), batch_size))
+        self._bounds = [(g * batch_size // self.groups, (g + 1) * batch_size // self.groups) for g in range(self.groups)]
+        # its own workspaces: decoders (and groups) on different streams may overlap
+        self._ws = [model._new_workspace(b1 - b0) for b0, b1 in self._bounds]
+        self._streams = [torch.cuda.Stream(device=dev) for _ in range(self.groups - 1)]
+        self._views = [([tuple(t[b0:b1] for t in st) for st in self.states], self.tokens[b0:b1], self.logits[b0:b1],
+                        self.next_tokens[b0:b1]) for b0, b1 in self._bounds]
         self.graph = None
         self.launches_per_step = None
         if use_graph:
             self._capture()
 
     def _run(self):
-        self.m._decode(self.tokens, self.states, self.logits, self.next_tokens, self._ws)
+        cur = torch.cuda.current_stream()
+        for g in range(1, self.groups):                 # fork: the other groups leave the caller's stream here
+            st, tok, lg, nxt = self._views[g]
+            s = self._streams[g - 1]
+            s.wait_stream(cur)
+            with torch.cuda.stream(s):
+                self.m._decode(tok, st, lg, nxt, self._ws[g])
+        st, tok, lg, nxt = self._views[0]
+        self.m._decode(tok, st, lg, nxt, self._ws[0])
+        for s in self._streams:
+            cur.wait_stream(s)                          # join
         if self.self_feed:
             self.tokens.copy_(self.next_tokens)
 

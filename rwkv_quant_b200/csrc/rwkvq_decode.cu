@@ -397,72 +397,81 @@ struct TmixCoreArgs {
     float* og_amax;                    // optional [B]: max|og| per stream is merged into it (atomic max on the bits)
 };
 
+// sum over 64 shared-memory values, computed redundantly by every warp (two values per lane):
+// no block-wide barrier beyond the one that published the values
+__device__ __forceinline__ float warp_sum64(const float* v, int lane) {
+    float s = v[lane] + v[lane + 32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+    return s;
+}
+
 __global__ void __launch_bounds__(256) tmix_core_kernel(const TmixCoreArgs p) {
-    __shared__ float sA[64], sW[64], sK[64], sB[64], sR[64], sV[64], sY[64], sG[64];
-    __shared__ float red[8];
-    const int hi = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+    __shared__ float sKK[64], sAV[64], sW[64], sK[64], sR[64], sV[64], sY[64], sG[64], sT[64];
+    const int hi = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
     const size_t row = static_cast<size_t>(b) * p.D + hi * 64;
     // the state slice of this thread is requested first: it is the largest load
+    // thread (dv, part) owns columns 16 i + 4 part + e of state row dv (i, e < 4): every load
+    // instruction of a quad covers 64 contiguous bytes
     const int dv = tid >> 2, part = tid & 3;
-    float* hp = p.state + ((static_cast<size_t>(b) * p.H + hi) * 64 + dv) * 64 + part * 16;
+    float* hp = p.state + ((static_cast<size_t>(b) * p.H + hi) * 64 + dv) * 64 + part * 4;
     float h[16];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float4 v4 = __ldcs(reinterpret_cast<const float4*>(hp + 4 * i));
+        const float4 v4 = __ldcs(reinterpret_cast<const float4*>(hp + 16 * i));
         h[4 * i] = v4.x; h[4 * i + 1] = v4.y; h[4 * i + 2] = v4.z; h[4 * i + 3] = v4.w;
     }
     pdl_launch_dependents();
     pdl_wait();            // the state above was written a whole token ago
-    float kk = 0.f, av = 0.f;
     if (tid < 64) {
         const int c = hi * 64 + tid;
         const float r = __ldcg(p.r + row + tid), k = __ldcg(p.k + row + tid);
         float v = __ldcg(p.v + row + tid);
         const float w = expf(-0.606531f * sigmoidf_(__ldcg(p.yw + row + tid) + p.w0[c]));
-        av = sigmoidf_(__ldcg(p.ya + row + tid) + p.a0[c]);
-        kk = k * p.k_k[c];
+        const float av = sigmoidf_(__ldcg(p.ya + row + tid) + p.a0[c]);
         const float k2 = k * (1.0f + (av - 1.0f) * p.k_a[c]);
         if (p.layer0) p.v_first[row + tid] = v;
         else v = v + (__ldcg(p.v_first + row + tid) - v) * sigmoidf_(__ldcg(p.yv + row + tid) + p.v0[c]);
+        const float kk = k * p.k_k[c];
+        sKK[tid] = kk; sAV[tid] = av; sT[tid] = kk * kk;
         sW[tid] = w; sK[tid] = k2; sR[tid] = r; sV[tid] = v; sG[tid] = __ldcg(p.g + row + tid);
     }
-    const float n2 = block_sum(tid < 64 ? kk * kk : 0.f, red);
-    if (tid < 64) {
-        const float kn = kk / sqrtf(n2 + 1e-12f);
-        sA[tid] = -kn;
-        sB[tid] = kn * av;
-    }
     __syncthreads();
+    // every warp reduces the head-wide sums itself; a = -kk / |kk|, b = -a * a_gate
+    const float inv_n = 1.0f / sqrtf(warp_sum64(sT, lane) + 1e-12f);
     // one WKV-7 step on the thread's 16 state columns
     float sa = 0.f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) sa = fmaf(h[i], sA[part * 16 + i], sa);
+    for (int i = 0; i < 16; ++i) sa = fmaf(h[i], -(sKK[16 * (i >> 2) + 4 * part + (i & 3)] * inv_n), sa);
     sa += __shfl_xor_sync(0xFFFFFFFFu, sa, 1);
     sa += __shfl_xor_sync(0xFFFFFFFFu, sa, 2);
     const float vv = sV[dv];
     float y = 0.f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-        const int dk = part * 16 + i;
-        h[i] = fmaf(sW[dk], h[i], fmaf(vv, sK[dk], sa * sB[dk]));
+        const int dk = 16 * (i >> 2) + 4 * part + (i & 3);
+        const float kn = sKK[dk] * inv_n;
+        h[i] = fmaf(sW[dk], h[i], fmaf(vv, sK[dk], sa * (kn * sAV[dk])));
         y = fmaf(h[i], sR[dk], y);
     }
     y += __shfl_xor_sync(0xFFFFFFFFu, y, 1);
     y += __shfl_xor_sync(0xFFFFFFFFu, y, 2);
 #pragma unroll
     for (int i = 0; i < 4; ++i)
-        *reinterpret_cast<float4*>(hp + 4 * i) = make_float4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
+        *reinterpret_cast<float4*>(hp + 16 * i) = make_float4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
     if (part == 0) sY[dv] = y;
     __syncthreads();
-    // group norm over the head (two-pass), bonus, gate
-    const float yv_ = tid < 64 ? sY[tid] : 0.f;
-    const float mean = block_sum(yv_, red) / 64.f;
-    const float dc = tid < 64 ? yv_ - mean : 0.f;
-    const float var = block_sum(dc * dc, red) / 64.f;
-    const float dp = block_sum(tid < 64 ? sR[tid] * sK[tid] * p.r_k[hi * 64 + tid] : 0.f, red);
-    if (tid < 64) {
+    if (tid < 64) {            // warps 0 and 1: group norm over the head (two-pass), bonus, gate
         const int c = hi * 64 + tid;
-        const float nrm = dc * (1.0f / sqrtf(var + 64e-5f));
+        const float mean = warp_sum64(sY, lane) / 64.f;
+        const float d0 = sY[lane] - mean, d1 = sY[lane + 32] - mean;
+        float var = d0 * d0 + d1 * d1, dp = sR[lane] * sK[lane] * p.r_k[hi * 64 + lane] + sR[lane + 32] * sK[lane + 32] * p.r_k[hi * 64 + lane + 32];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            var += __shfl_xor_sync(0xFFFFFFFFu, var, o);
+            dp += __shfl_xor_sync(0xFFFFFFFFu, dp, o);
+        }
+        const float nrm = (sY[tid] - mean) * (1.0f / sqrtf(var / 64.f + 64e-5f));
         const float o = (nrm * p.lnx_w[c] + p.lnx_b[c] + dp * sV[tid]) * sG[tid];
         p.og[row + tid] = o;
         if (p.og_amax != nullptr) {          // warps 0 and 1 hold the 64 outputs
@@ -644,8 +653,9 @@ int lora_pair(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, co
         u.act[i] = acts[i];
         if (t2[i]->cols > max_cols) max_cols = t2[i]->cols;
     }
-    if (B > kLmMaxN && lora_mma_ok(t1, t2, n_br, D)) {
-        // more than one group of streams: both products on the tensor cores, matrices read once
+    if (B > 2 && lora_mma_ok(t1, t2, n_br, D)) {
+        // a batch of streams: both products on the tensor cores, matrices read once (the per-stream
+        // kernels below keep 1 and 2 streams, whose results do not depend on the batch, and odd shapes)
         const int n_stride = ((B + 63) / 64) * 64;
         if (static_cast<size_t>(4) * n_stride * max_rank <= part_floats)
             return launch_lora_pair_mma(t1, t2, xs, ys, acts, n_br, B, D, max_rank, part, n_stride, s);

@@ -454,6 +454,7 @@ __global__ void __launch_bounds__(256) row_amax_kernel(const float* __restrict__
 
 unsigned long long* g_batch_trace = nullptr;      // set by rwkvq_profiling_batch_trace (rwkvq_profiling.h)
 int g_batch_force_ks = 0;                         // profiling aid: cluster size override (0 = the launcher's choice)
+int g_batch_force_rows = 0, g_batch_force_cols = 0;   // ... for tensors of this shape only (0: every shape)
 
 namespace {
 
@@ -524,7 +525,8 @@ int launch_bt_l(BatchArgs& a, int n_mats, int rows, int cols, int N, cudaStream_
         }
     }
     int ks = best_ks, tpc = best_tpc;
-    if (g_batch_force_ks > 0 && n_iters % (g_batch_force_ks & 15) == 0) {
+    if (g_batch_force_ks > 0 && n_iters % (g_batch_force_ks & 15) == 0 &&
+        (g_batch_force_rows == 0 || (g_batch_force_rows == rows && g_batch_force_cols == cols))) {
         ks = g_batch_force_ks & 15;
         if (g_batch_force_ks & 16) tpc = 16;
         if (g_batch_force_ks & 32) tpc = 8;
@@ -606,6 +608,12 @@ using namespace rwkvq;
 extern "C" void rwkvq_profiling_batch_trace(void* buf8, int force_ks) {
     g_batch_trace = static_cast<unsigned long long*>(buf8);
     g_batch_force_ks = force_ks;
+    g_batch_force_rows = g_batch_force_cols = 0;
+}
+extern "C" void rwkvq_profiling_batch_force(int force_ks, int rows, int cols) {
+    g_batch_force_ks = force_ks;
+    g_batch_force_rows = rows;
+    g_batch_force_cols = cols;
 }
 
 extern "C" size_t rwkvq_gemv_batch_workspace_bytes(int N) { return N > 0 ? ((static_cast<size_t>(N) * sizeof(float) + 255) / 256) * 256 : 0; }

@@ -57,19 +57,61 @@ __device__ __forceinline__ void split4(const float4& v, uint2& hi, uint2& lo) {
     lo = make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
 }
 
-// rows [k0, k0 + kc) x columns [c0, c0 + nc) of a tensor stored [in, out] -> wt[col][row] fp16
-// (k contiguous: the "col" operand of the MMA).  nc is a multiple of 4, at most 128.
+// rows [k0, k0 + kc) x columns [c0, c0 + nc) of a tensor stored [in, out] -> wk[row][col] fp16, the stored
+// orientation (columns contiguous: coalesced loads, 8-byte conflict-free stores); the MMA's "col" operand is
+// read from it with ldmatrix.trans.  nc is a multiple of 4.
+__device__ __forceinline__ uint2 pack4h(const float (&w)[4]) {
+    const __half2 a = __floats2half2_rn(w[0], w[1]), b = __floats2half2_rn(w[2], w[3]);      // exact: fp16 values
+    return make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
 template <int MODE>
-__device__ __forceinline__ void stage_wt(const QView& t, int k0, int kc, int c0, int nc, __half* wt, int pitch) {
+__device__ __forceinline__ void stage_wt(const QView& t, int k0, int kc, int c0, int nc, __half* wk, int pitch) {
     const int groups = nc >> 2;
     const int nb = MODE == 0 ? (t.cols + t.gs - 1) / t.gs : 0;
-    for (int item = threadIdx.x; item < kc * groups; item += kLmmThreads) {
-        const int k = item / groups, cg4 = item - k * groups;
-        const int c = c0 + cg4 * 4;
-        float w[4];
-        lora_w4<MODE>(t, k0 + k, c, nb, MODE == 0 ? c / t.gs : 0, w);
+    const int total = kc * groups;
+    if (MODE == 2) {
+        for (int item = threadIdx.x; item < total; item += kLmmThreads) {
+            const int k = item / groups, cg4 = item - k * groups;
+            float w[4];
+            lora_w4<2>(t, k0 + k, c0 + cg4 * 4, 0, 0, w);
+            *reinterpret_cast<uint2*>(wk + k * pitch + cg4 * 4) = pack4h(w);
+        }
+        return;
+    }
+    // 8 items per thread with all their loads issued together (one item is a latency chain)
+    for (int base = threadIdx.x; base < total; base += 8 * kLmmThreads) {
+        uint32_t q[8];
+        float sc[8], mn[8];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) wt[(cg4 * 4 + e) * pitch + k] = __float2half_rn(w[e]);      // exact: w is an fp16 value
+        for (int u = 0; u < 8; ++u) {
+            const int item = min(base + u * kLmmThreads, total - 1);
+            const int k = item / groups, cg4 = item - k * groups;
+            const size_t I = static_cast<size_t>(k0 + k);
+            const int c = c0 + cg4 * 4;
+            q[u] = ld_stream_u32(t.codes + I * t.cols + c);
+            if (MODE == 0) {
+                sc[u] = __ldg(static_cast<const float*>(t.scale) + I * nb + c / t.gs);
+                mn[u] = __ldg(t.mn + I * nb + c / t.gs);
+            } else {
+                sc[u] = __half2float(__ldg(static_cast<const __half*>(t.scale) + I));
+                mn[u] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int item = base + u * kLmmThreads;
+            if (item >= total) break;
+            const int k = item / groups, cg4 = item - k * groups;
+            float w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t byte = (q[u] >> (8 * e)) & 0xFFu;
+                const float v = MODE == 0 ? __fadd_rn(__fmul_rn(static_cast<float>(byte), sc[u]), mn[u])
+                                          : __fmul_rn(static_cast<float>(static_cast<int8_t>(byte)), sc[u]);
+                w[e] = dense_param_rounding(v);
+            }
+            *reinterpret_cast<uint2*>(wk + k * pitch + cg4 * 4) = pack4h(w);
+        }
     }
 }
 __device__ __forceinline__ void stage_wt_any(const QView& t, int k0, int kc, int c0, int nc, __half* wt, int pitch) {
@@ -83,29 +125,48 @@ __device__ __forceinline__ void stage_wt_any(const QView& t, int k0, int kc, int
 // rows [0, nn) x columns [k0, k0 + kc) of src [*, ld] fp32 -> hi / lo [MT * 16][pitch] fp16 (rows beyond nn: zero)
 __device__ __forceinline__ void stage_split(const float* src, long long ld, int nn, int rows_pad, int k0, int kc,
                                             __half* hi, __half* lo, int pitch) {
-    const int g4 = kc >> 2;
-    for (int item = threadIdx.x; item < rows_pad * g4; item += kLmmThreads) {
-        const int n = item / g4, k4 = item - n * g4;
-        const float4 v = n < nn ? __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(n) * ld + k0) + k4)
-                                : make_float4(0.f, 0.f, 0.f, 0.f);
-        uint2 h, l;
-        split4(v, h, l);
-        *reinterpret_cast<uint2*>(hi + n * pitch + 4 * k4) = h;
-        *reinterpret_cast<uint2*>(lo + n * pitch + 4 * k4) = l;
+    const int g4 = kc >> 2, total = rows_pad * g4;
+    for (int base = threadIdx.x; base < total; base += 8 * kLmmThreads) {      // 8 loads in flight per thread
+        float4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int item = base + u * kLmmThreads;
+            const int n = item / g4, k4 = item - n * g4;
+            v[u] = (item < total && n < nn) ? __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(n) * ld + k0) + k4)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int item = base + u * kLmmThreads;
+            if (item >= total) break;
+            const int n = item / g4, k4 = item - n * g4;
+            uint2 h, l;
+            split4(v[u], h, l);
+            *reinterpret_cast<uint2*>(hi + n * pitch + 4 * k4) = h;
+            *reinterpret_cast<uint2*>(lo + n * pitch + 4 * k4) = l;
+        }
     }
 }
 
-// one k16 step: c[mi][ni] += A(m-tile mi) * B(n-tile ni), hi and lo halves of A
+// B fragments of a k16 step for two adjacent 8-column tiles from wk[k][n] (n contiguous): the four 8x8
+// matrices (k 0-7 | 8-15) x (n 0-7 | 8-15), transposed on the way into the registers
+__device__ __forceinline__ void ldsm_x4_trans(const __half* wk, int pitch, int kk, int n_base, int lane, uint32_t (&b)[2][2]) {
+    const int m = lane >> 3, r = lane & 7;
+    const __half* p = wk + (kk + (m & 1) * 8 + r) * pitch + n_base + (m >> 1) * 8;
+    const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(b[0][0]), "=r"(b[0][1]), "=r"(b[1][0]), "=r"(b[1][1])
+                 : "r"(addr));
+}
+
+// one k16 step: c[mi][ni] += A(m-tile mi) * B(n-tile ni), hi and lo halves of A; NI = 1 or 2 8-column
+// tiles starting at column n_base of wk (both are loaded; one may go unused)
 template <int MI, int NI>
 __device__ __forceinline__ void lmm_step(float (&c)[MI][NI][4], const __half* ahi, const __half* alo, int apitch,
-                                         const __half* wt, int wpitch, int kk, int g, int t) {
-    uint32_t b[NI][2];
-#pragma unroll
-    for (int ni = 0; ni < NI; ++ni) {
-        const __half* bp = wt + (ni * 8 + g) * wpitch + kk + 2 * t;
-        b[ni][0] = *reinterpret_cast<const uint32_t*>(bp);
-        b[ni][1] = *reinterpret_cast<const uint32_t*>(bp + 8);
-    }
+                                         const __half* wk, int wpitch, int n_base, int kk, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    uint32_t b[2][2];
+    ldsm_x4_trans(wk, wpitch, kk, n_base, lane, b);
 #pragma unroll
     for (int mi = 0; mi < MI; ++mi) {
         uint32_t ah[4], al[4];
@@ -134,32 +195,33 @@ __global__ void __launch_bounds__(kLmmThreads) lora_down_mma_kernel(const LoraMm
     const int n0 = tg * MT * 16, nn = min(MT * 16, a.n_tokens - n0);
     const int kc = a.D / kLmmSlices, k0 = rank * kc;
     const int pitch = kc + kLmmPad;
+    constexpr int WP = kLmmRC + kLmmPad;                          // pitch of a weight row (32 rank columns)
     __half* xhi = reinterpret_cast<__half*>(smem);
     __half* xlo = xhi + MT * 16 * pitch;
-    __half* wt = xlo + MT * 16 * pitch;
-    float* part = reinterpret_cast<float*>(wt + kLmmRC * pitch);  // [MT * 16][kLmmRC + 1]
+    __half* wt = xlo + MT * 16 * pitch;                           // [kc][WP]
+    float* part = reinterpret_cast<float*>(wt + kc * WP);         // [MT * 16][kLmmRC + 1]
     constexpr int PP = kLmmRC + 1;
     const bool active = c0 < t.cols;                              // the whole cluster shares branch and column group
     pdl_launch_dependents();
-    if (active) stage_wt_any(t, k0, kc, c0, min(kLmmRC, t.cols - c0), wt, pitch);
-    if (active && t.cols - c0 < kLmmRC)                           // ragged rank: zero columns
-        for (int i = threadIdx.x; i < (kLmmRC - (t.cols - c0)) * pitch; i += kLmmThreads) wt[(t.cols - c0) * pitch + i] = __float2half_rn(0.f);
+    if (active && t.cols - c0 < kLmmRC)                           // ragged rank: the missing columns read as zero
+        for (int i = threadIdx.x; i < kc * WP; i += kLmmThreads) wt[i] = __float2half_rn(0.f);
+    __syncthreads();
+    if (active) stage_wt_any(t, k0, kc, c0, min(kLmmRC, t.cols - c0), wt, WP);
     pdl_wait();
     if (active) stage_split(a.x[br] + static_cast<size_t>(n0) * a.ldx, a.ldx, nn, MT * 16, k0, kc, xhi, xlo, pitch);
     __syncthreads();
     if (active) {
         // 8 warps = MT m-tiles x (8 / MT) groups of the four 8-column tiles
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
-        constexpr int NG = 8 / MT;                                // warp groups along the columns: 2, 4, 8
-        constexpr int NI = NG <= 4 ? 4 / NG : 1;                  // 8-column tiles per warp: 2, 1, 1
+        // 2 * MT (stream tile, 16-column half) pairs over the 8 warps; spare warps split nothing further
+        constexpr int NI = 2;
         const int mi = warp % MT, ngi = warp / MT;
         if (ngi * NI < 4) {
             float c[1][NI][4];
 #pragma unroll
             for (int ni = 0; ni < NI; ++ni) c[0][ni][0] = c[0][ni][1] = c[0][ni][2] = c[0][ni][3] = 0.f;
-            const __half* wtp = wt + ngi * NI * 8 * pitch;
             for (int kk = 0; kk < kc; kk += 16)
-                lmm_step<1, NI>(c, xhi + mi * 16 * pitch, xlo + mi * 16 * pitch, pitch, wtp, pitch, kk, g, tq);
+                lmm_step<1, NI>(c, xhi + mi * 16 * pitch, xlo + mi * 16 * pitch, pitch, wt, WP, ngi * 16, kk, lane);
 #pragma unroll
             for (int ni = 0; ni < NI; ++ni) {
                 const int col = (ngi * NI + ni) * 8 + 2 * tq, row = mi * 16 + g;
@@ -199,11 +261,12 @@ __global__ void __launch_bounds__(kLmmThreads) lora_up_mma_kernel(const LoraMmaA
     const int r = t.rows, c0 = blockIdx.x * kLmmUpCols;
     const int n0 = tg * MT * 16, nn = min(MT * 16, a.n_tokens - n0);
     const int pitch = r + kLmmPad;
+    constexpr int WP = kLmmUpCols + kLmmPad;
     __half* hhi = reinterpret_cast<__half*>(smem);
     __half* hlo = hhi + MT * 16 * pitch;
-    __half* wt = hlo + MT * 16 * pitch;                           // [128][pitch]
+    __half* wt = hlo + MT * 16 * pitch;                           // [r][WP]
     pdl_launch_dependents();
-    stage_wt_any(t, 0, r, c0, kLmmUpCols, wt, pitch);
+    stage_wt_any(t, 0, r, c0, kLmmUpCols, wt, WP);
     pdl_wait();
     stage_split(a.h + (static_cast<size_t>(br) * a.n_stride + n0) * a.max_rank, a.max_rank, nn, MT * 16, 0, r, hhi, hlo, pitch);
     __syncthreads();
@@ -213,8 +276,7 @@ __global__ void __launch_bounds__(kLmmThreads) lora_up_mma_kernel(const LoraMmaA
     for (int mi = 0; mi < MT; ++mi)
 #pragma unroll
         for (int ni = 0; ni < 2; ++ni) c[mi][ni][0] = c[mi][ni][1] = c[mi][ni][2] = c[mi][ni][3] = 0.f;
-    const __half* wtp = wt + warp * 16 * pitch;
-    for (int kk = 0; kk < r; kk += 16) lmm_step<MT, 2>(c, hhi, hlo, pitch, wtp, pitch, kk, g, tq);
+    for (int kk = 0; kk < r; kk += 16) lmm_step<MT, 2>(c, hhi, hlo, pitch, wt, WP, warp * 16, kk, lane);
     float* y = a.y[br] + static_cast<size_t>(n0) * a.ldy + c0 + warp * 16;
 #pragma unroll
     for (int mi = 0; mi < MT; ++mi)
@@ -239,9 +301,10 @@ int lmm_attr(K kernel, size_t smem) {
 template <int MT>
 int launch_lmm(const LoraMmaArgs& a, int groups, int max_cols, cudaStream_t s) {
     const int kc = a.D / kLmmSlices;
-    const size_t smem_d = static_cast<size_t>(2 * MT * 16 + kLmmRC) * (kc + kLmmPad) * sizeof(__half) +
+    const size_t smem_d = (static_cast<size_t>(2 * MT * 16) * (kc + kLmmPad) + static_cast<size_t>(kc) * (kLmmRC + kLmmPad)) * sizeof(__half) +
                           static_cast<size_t>(MT * 16) * (kLmmRC + 1) * sizeof(float);
-    const size_t smem_u = static_cast<size_t>(2 * MT * 16 + kLmmUpCols) * (a.max_rank + kLmmPad) * sizeof(__half);
+    const size_t smem_u = (static_cast<size_t>(2 * MT * 16) * (a.max_rank + kLmmPad) +
+                           static_cast<size_t>(a.max_rank) * (kLmmUpCols + kLmmPad)) * sizeof(__half);
     if (smem_d > static_cast<size_t>(kLmmMaxSmem) || smem_u > static_cast<size_t>(kLmmMaxSmem))
         return fail(RWKVQ_E_LIMIT, "lora_mma: %zu / %zu bytes of shared memory", smem_d, smem_u);
     int rc = lmm_attr(lora_down_mma_kernel<MT>, smem_d);

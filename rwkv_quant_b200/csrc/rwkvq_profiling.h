@@ -16,6 +16,8 @@ void rwkvq_profiling_gemm_trace(void* buf512);
  * 4 cluster barrier passed, 5 reduced and stored, 6 end.  force_ks > 0 overrides the launcher's choice:
  * low 4 bits the cluster size, +16 groups of 256 rows, +32 groups of 128 rows. */
 void rwkvq_profiling_batch_trace(void* buf8, int force_ks);
+/* The same override for tensors of one shape only (rows = 0: every shape); 0 switches it off. */
+void rwkvq_profiling_batch_force(int force_ks, int rows, int cols);
 #ifdef __cplusplus
 }
 #endif

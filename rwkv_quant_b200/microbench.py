@@ -230,6 +230,68 @@ def batch_sweep(recipe="compression", Ns=(8, 64), reps=40, ring=24):
         torch.cuda.empty_cache()
 
 
+def batch_tune(layers=4, batch=64, recipe="compression", model="1.5b", reps=20):
+    """Step time of a `layers`-layer decode graph at `batch` streams with the small-batch linear's
+    launch geometry forced, one tensor shape at a time (cluster size x rows per group): what the
+    launcher's cost model is calibrated against."""
+    lib = _lib.load()
+    force = lib.rwkvq_profiling_batch_force          # rwkvq_profiling.h: not part of the C ABI
+    force.restype, force.argtypes = None, [C.c_int, C.c_int, C.c_int]
+    ck = synth.build_checkpoint(model, recipe, seed=0, device="cuda", n_layer=layers)
+    m = QuantRWKV7(ck)
+    del ck
+    D, F_, V = m.n_embd, m.ffn_dim, m.vocab_size
+
+    def step_us():
+        dec = m.decoder(batch, use_graph=True, self_feed=True)
+        for _ in range(3):
+            dec.step()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            dec.step()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+    force(0, 0, 0)
+    base = step_us()
+    print(f"batch-tune {model} {recipe} {layers} layers, {batch} streams: launcher's choice {base:.1f} us/step", flush=True)
+    for rows, cols, name in ((D, D, "r/k/v, o"), (F_, D, "ffn.key"), (D, F_, "ffn.value"), (V, D, "head")):
+        out = []
+        for tp in (32, 16):
+            for ks in (1, 2, 4, 5, 8):
+                force(ks | tp, rows, cols)
+                try:
+                    out.append((step_us() - base, ks, 128 if tp == 32 else 256))
+                except Exception as e:      # noqa: BLE001
+                    out.append((float("nan"), ks, 128 if tp == 32 else 256))
+        force(0, 0, 0)
+        print(f"  [{rows},{cols}] {name}: " + "  ".join(f"ks{k}/{r}:{d:+.0f}" for d, k, r in out), flush=True)
+
+
+def decode_groups(layers=24, batch=64, recipe="compression", model="1.5b", reps=20):
+    """Step time of batched decode with the streams split into 1, 2, 4, 8 groups whose launch
+    chains run as parallel branches of the graph."""
+    ck = synth.build_checkpoint(model, recipe, seed=0, device="cuda", n_layer=layers)
+    m = QuantRWKV7(ck)
+    del ck
+    for g in (1, 2, 4, 8):
+        if g > batch:
+            break
+        dec = m.decoder(batch, use_graph=True, self_feed=True, groups=g)
+        for _ in range(3):
+            dec.step()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            dec.step()
+        e1.record(); torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        print(f"decode {model} {recipe} {layers} layers, {batch} streams in {g} group(s): {us:.0f} us/step, {batch / us * 1e6:.0f} tok/s", flush=True)
+        del dec
+
+
 def gemm_once(layout="sb6", bits=5, rows=2048, cols=2048, M=8192, launches=3):
     """A few plain rwkvq_gemm launches of one shape (the target of ncu captures)."""
     dq = _tensor(layout, bits, rows, cols)
@@ -420,6 +482,12 @@ def main():
     go.add_argument("layout"); go.add_argument("bits", type=int); go.add_argument("rows", type=int)
     go.add_argument("cols", type=int); go.add_argument("--M", type=int, default=8192)
     go.add_argument("--launches", type=int, default=3)
+    dg = sub.add_parser("decode-groups")
+    dg.add_argument("--layers", type=int, default=24); dg.add_argument("--batch", type=int, default=64)
+    dg.add_argument("--recipe", default="compression"); dg.add_argument("--model", default="1.5b")
+    bt = sub.add_parser("batch-tune")
+    bt.add_argument("--layers", type=int, default=4); bt.add_argument("--batch", type=int, default=64)
+    bt.add_argument("--recipe", default="compression"); bt.add_argument("--model", default="1.5b")
     bs = sub.add_parser("batch-sweep")
     bs.add_argument("--recipe", default="compression")
     gt = sub.add_parser("gemm-timeline")
@@ -442,6 +510,12 @@ def main():
         return
     if a.cmd == "gemm":
         gemm_once(a.layout, a.bits, a.rows, a.cols, a.M, a.launches)
+        return
+    if a.cmd == "decode-groups":
+        decode_groups(a.layers, a.batch, a.recipe, a.model)
+        return
+    if a.cmd == "batch-tune":
+        batch_tune(a.layers, a.batch, a.recipe, a.model)
         return
     if a.cmd == "batch-sweep":
         batch_sweep(a.recipe)
