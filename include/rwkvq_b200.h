@@ -149,8 +149,12 @@ int rwkvq_gemv(const rwkvq_qtensor* t, const void* x, int x_dtype, int N, int64_
  * ~2e-4 of max|y| (a column's bits may depend on the batch it is computed in; two calls on the same
  * input give the same bits).  The K split is reduced across a thread-block cluster through
  * distributed shared memory: no scratch for partial sums.
- *   workspace: rwkvq_gemv_batch_workspace_bytes(N) bytes (one float per row: the max|x| a
- *   one-block-per-row pre-pass writes before the product kernel starts).
+ *   workspace: rwkvq_gemv_batch_workspace_bytes(N) bytes, 16-byte aligned: a status word (first
+ *   int32: RWKVQ_E_TIMEOUT if a bounded wait on the tensor-core pipeline ran out; read it after
+ *   synchronising the stream, 0 = ok) and one float per row, the max|x| a one-block-per-row
+ *   pre-pass writes before the product kernel starts.
+ * sb6 and sym tensors run on the tcgen05 tensor cores (rows of 128 as the UMMA M, the batch as its
+ * N, accumulator in tensor memory); per-row int8 tensors on mma.sync.
  */
 size_t rwkvq_gemv_batch_workspace_bytes(int N);
 int rwkvq_gemv_batch(const rwkvq_qtensor* t, const float* x, int N, int64_t ldx, float* y, int64_t ldy,

@@ -260,13 +260,14 @@ def has_batch_layout(dq: "DeviceQT") -> bool:
     if dq.outliers is not None:
         return False
     if dq.kind == "sb6":
-        return dq.bufs[_BUF_ORDER.index("dev_meta")].numel() > 0 and dq.cols % 256 == 0
+        return dq.cols % 256 == 0
     if dq.kind == "sym":
-        return dq.cols % 256 == 0 and (dq.bits == 8 or dq.bufs[_BUF_ORDER.index("dev_planes")].numel() > 0)
+        return dq.cols % 256 == 0
     return dq.kind == "rtn" and dq.bits > 4 and dq.cols % 128 == 0
 
 
-def gemv_batch(dq: "DeviceQT", x: torch.Tensor, epilogue: int = 0, resid: Optional[torch.Tensor] = None) -> torch.Tensor:
+def gemv_batch(dq: "DeviceQT", x: torch.Tensor, epilogue: int = 0, resid: Optional[torch.Tensor] = None,
+               check: bool = False) -> torch.Tensor:
     """x [N, IN] -> y [N, OUT] fp32 with the packed weights read once for all N rows (mma.sync
     tensor cores, tokens as the MMA columns, fp16 operands, fp32 accumulation)."""
     _require_cuda(x, resid)
@@ -280,6 +281,8 @@ def gemv_batch(dq: "DeviceQT", x: torch.Tensor, epilogue: int = 0, resid: Option
     ws = torch.empty(nws, dtype=torch.uint8, device=x.device)
     _lib.check(lib.rwkvq_gemv_batch(C.byref(dq.struct), x.data_ptr(), n, x.stride(0), y.data_ptr(), y.stride(0),
                                     epilogue, _lib.ptr(resid), ws.data_ptr(), nws, _lib.stream_ptr()), "rwkvq_gemv_batch")
+    if check:          # synchronises: the kernel's own report that a bounded pipeline wait ran out
+        _lib.check(int(ws[:4].view(torch.int32).item()), "rwkvq_gemv_batch(kernel status)")
     return y
 
 

@@ -461,3 +461,10 @@ class Decoder:
     def feed_back(self):
         """Use the last argmax as the next input without leaving the device."""
         self.tokens.copy_(self.next_tokens)
+
+    def check(self):
+        """Synchronise and raise if a bounded device-side wait of a step ran out (the first word of
+        a step's workspace then holds the error code)."""
+        torch.cuda.synchronize(self.m.device)
+        for ws in self._ws:
+            _lib.check(int(ws[:4].view(torch.int32).item()), "rwkvq_decode_step(kernel status)")

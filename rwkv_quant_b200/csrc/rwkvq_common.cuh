@@ -260,11 +260,18 @@ size_t gemv_mma_scratch_bytes();
 int launch_gemv_batch(const rwkvq_qtensor* ts, int n_mats, const void* const* xs, bool half_in, const float* const* scales,
                       int N, long long ldx, float* const* ys, long long ldy, int epilogue, const float* const* resids,
                       float* const* amax_outs, cudaStream_t s);
+// The same product on the tcgen05 tensor cores (rwkvq_gemm_tcb.cu; sb6 / sym tensors, gemm_tcb_ok);
+// status: device word that receives RWKVQ_E_TIMEOUT if a bounded pipeline wait ran out.
+bool gemm_tcb_ok(const rwkvq_qtensor& t);
+bool tcb_enabled();
+int launch_gemm_tcb(const rwkvq_qtensor* ts, int n_mats, const void* const* xs, bool half_in, const float* const* scales,
+                    int N, long long ldx, float* const* ys, long long ldy, int epilogue, const float* const* resids,
+                    float* const* amax_outs, int* status, cudaStream_t s);
 // LoRA pair of the time-mix block for a batch of streams on the tensor cores (rwkvq_lora_mma.cu)
 bool lora_mma_ok(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, int n_br, int D);
 int launch_lora_pair_mma(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, const float* const* xs,
                          float* const* ys, const int* acts, int n_br, int B, int D, int max_rank, float* h, int n_stride,
                          cudaStream_t s);
-int launch_row_amax(const float* x, long long ldx, int cols, int N, float* amax, cudaStream_t s);
+int launch_row_amax(const float* x, long long ldx, int cols, int N, float* amax, int* status, cudaStream_t s);
 
 }  // namespace rwkvq

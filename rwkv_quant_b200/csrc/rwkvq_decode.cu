@@ -533,8 +533,10 @@ namespace {
 constexpr int kBatchMax = 256;     // streams up to which the small-batch kernel serves the linears of a step
 inline bool batch_path(int B) { return B > 2 && B <= kBatchMax; }
 
+
 struct Workspace {
     float *x, *xs, *rkv, *part, *yl, *og, *xk, *hffn, *xo, *v_first, *logits, *argv, *gscratch, *gemm_ws;
+    int* status;             // first word of the workspace: RWKVQ_E_TIMEOUT if a bounded device-side wait of a step ran out
     float* amax;             // [10][B] per-row scale inverses / maxima for the small-batch linears: 6 mix rows, og, xk, hffn, xo
     __half *xs16, *xk16, *xo16;     // fp16 forms of the mix rows, the channel-mix row and the final row
     int n_chunks;
@@ -551,6 +553,7 @@ Workspace carve(const rwkvq_model& m, int B, void* base) {
         off += ((n * sizeof(float) + 255) / 256) * 256;
         return p;
     };
+    w.status = reinterpret_cast<int*>(take(64));
     w.x = take(b * D); w.xs = take(6 * b * D); w.rkv = take(3 * b * D);
     w.n_chunks = static_cast<int>((D + kLdRows - 1) / kLdRows);
     w.part_floats = 4 * static_cast<size_t>(w.n_chunks) * ((b + kLmMaxN - 1) / kLmMaxN * kLmMaxN) * R;   // upper bound (rep = 1)
@@ -576,7 +579,7 @@ Workspace carve(const rwkvq_model& m, int B, void* base) {
 // slots max|y| per row is merged into.
 int linear(const rwkvq_qtensor* t, const float* x, int B, int in, float* y, int out, int epi, const float* resid,
            float* scratch, void* gemm_ws, void* stream, const __half* x16 = nullptr, const float* x_scale = nullptr,
-           float* y_amax = nullptr) {
+           float* y_amax = nullptr, int* status = nullptr) {
     const int ml = mma_layout_of(*t);
     if (B == 1 && ml >= 0) {
         int rc = validate_qtensor(t, "rwkvq_decode_step(linear)");
@@ -592,6 +595,8 @@ int linear(const rwkvq_qtensor* t, const float* x, int B, int in, float* y, int 
         float* ys[1] = {y};
         const float* rs[1] = {resid};
         float* ao[1] = {y_amax};
+        if (tcb_enabled() && gemm_tcb_ok(*t))
+            return launch_gemm_tcb(t, 1, xs, x16 != nullptr, sc, B, in, ys, out, epi, rs, ao, status, static_cast<cudaStream_t>(stream));
         return launch_gemv_batch(t, 1, xs, x16 != nullptr, sc, B, in, ys, out, epi, rs, ao, static_cast<cudaStream_t>(stream));
     }
     if (B > 2 && (t->kind == RWKVQ_KIND_SB6 || t->kind == RWKVQ_KIND_SYM))     // tcgen05 path for large batches
@@ -749,16 +754,19 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
             const void* x3[3] = {w.xs16, w.xs16 + 2 * BD, w.xs16 + 3 * BD};
             const float* a3[3] = {am, am + 2 * B, am + 3 * B};
             float* y3[3] = {r, k, v};
-            rc = launch_gemv_batch(three, 3, x3, true, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, s);
+            if (tcb_enabled() && gemm_tcb_ok(L.Wr))
+                rc = launch_gemm_tcb(three, 3, x3, true, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, w.status, s);
+            else
+                rc = launch_gemv_batch(three, 3, x3, true, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, s);
             if (rc) return rc;
         } else {
-            rc = linear(&L.Wr, xr, B, D, r, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream, bp ? w.xs16 : nullptr, am);
+            rc = linear(&L.Wr, xr, B, D, r, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream, bp ? w.xs16 : nullptr, am, nullptr, w.status);
             if (rc) return rc;
             rc = linear(&L.Wk, xk, B, D, k, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream,
-                        bp ? w.xs16 + 2 * BD : nullptr, bp ? am + 2 * B : nullptr);
+                        bp ? w.xs16 + 2 * BD : nullptr, bp ? am + 2 * B : nullptr, nullptr, w.status);
             if (rc) return rc;
             rc = linear(&L.Wv, xv, B, D, v, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream,
-                        bp ? w.xs16 + 3 * BD : nullptr, bp ? am + 3 * B : nullptr);
+                        bp ? w.xs16 + 3 * BD : nullptr, bp ? am + 3 * B : nullptr, nullptr, w.status);
             if (rc) return rc;
         }
         float *yw = w.yl, *ya = w.yl + BD, *yv = w.yl + 2 * BD, *yg = w.yl + 3 * BD;
@@ -778,21 +786,21 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         TmixCoreArgs tc{r, k, v, yw, ya, layer0 ? nullptr : yv, yg, L.w0, L.a0, L.v0, L.k_k, L.k_a, L.r_k,
                         L.lnx_w, L.lnx_b, w.v_first, wkv[l], w.og, D, H, layer0 ? 1 : 0, am_og};
         launch_pdl(tmix_core_kernel, dim3(H, B), dim3(256), 0, s, tc);
-        rc = linear(&L.Wo, w.og, B, D, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, w.gemm_ws, stream, nullptr, am_og);
+        rc = linear(&L.Wo, w.og, B, D, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, w.gemm_ws, stream, nullptr, am_og, nullptr, w.status);
         if (rc) return rc;
         // ---- channel mix
         launch_pdl(ln_shift_mix_kernel<1>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln2_w, L.ln2_b, cshift[l], L.ffn_x_k, w.xk, B, D,
                    bp ? w.xk16 : static_cast<__half*>(nullptr), am_xk, 1, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
         rc = linear(&L.Wfk, w.xk, B, D, w.hffn, F, RWKVQ_EPI_RELU2, nullptr, w.gscratch, w.gemm_ws, stream, bp ? w.xk16 : nullptr,
-                    am_xk, am_h);
+                    am_xk, am_h, w.status);
         if (rc) return rc;
-        rc = linear(&L.Wfv, w.hffn, B, F, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, w.gemm_ws, stream, nullptr, am_h);
+        rc = linear(&L.Wfv, w.hffn, B, F, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, w.gemm_ws, stream, nullptr, am_h, nullptr, w.status);
         if (rc) return rc;
     }
     float* am_xo = batch_path(B) ? w.amax + 9 * B : nullptr;
     launch_pdl(ln_shift_mix_kernel<0>, dim3(B), dim3(kRowThreads), 0, s, w.x, m->lnout_w, m->lnout_b, static_cast<float*>(nullptr), static_cast<const float*>(nullptr), w.xo, B, D,
                am_xo ? w.xo16 : static_cast<__half*>(nullptr), am_xo, 1, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
-    rc = linear(&m->head, w.xo, B, D, lg, V, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream, am_xo ? w.xo16 : nullptr, am_xo);
+    rc = linear(&m->head, w.xo, B, D, lg, V, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream, am_xo ? w.xo16 : nullptr, am_xo, nullptr, w.status);
     if (rc) return rc;
     if (next_tokens) {
         float* pv = w.argv;

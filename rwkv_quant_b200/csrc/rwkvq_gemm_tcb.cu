@@ -1,0 +1,384 @@
+// Quantized linear for a small batch of right-hand sides (decode streams) on the tcgen05 tensor
+// cores:   y[n, o] = epi( sum_c W[o, c] x[n, c] ),   n < N <= 64 per token group.
+//
+// The mma.sync form of this product (rwkvq_gemv_batch.cu) issues one warp-level MMA per 16 rows x
+// 8 tokens x 16 columns plus a shared-memory load and a share of the code -> fp16 conversion, and
+// on this part those issue slots add up instead of overlapping.  Here a CTA owns 128 output rows
+// (the UMMA M) and all tokens of its group (UMMA N = 16, 32 or 64):
+//   * 8 producer warps read the packed rows of a 256-column pass exactly as the prefill kernel
+//     does (load_packed: one contiguous run per row), one pass ahead in registers, turn them into
+//     fp16(q*s + m) and store them K-major with the 128-byte swizzle (convert_store);
+//   * the same warps stage the activations of the pass: fp16 rows already scaled per token (from
+//     the LayerNorm kernels) are copied, fp32 rows are scaled by the power of two their known
+//     max|x| implies and rounded once; both land in the swizzled K-major layout the tensor core
+//     reads, written with plain stores (no tensor map);
+//   * one lane of a ninth warp issues the 16 tcgen05.mma (M 128, N tokens, K 16) of the pass into
+//     a tensor-memory accumulator and commits them to the mbarrier the producers wait on before
+//     they overwrite the operands;
+//   * the K loop is split over a thread-block cluster (up to 8 CTAs); the accumulator goes
+//     through tcgen05.ld into shared memory (over the dead operand buffers), and after one
+//     cluster barrier every CTA adds a slice of the tile over all ranks through distributed
+//     shared memory in rank order, applies the epilogue and stores.
+// Every mbarrier wait is bounded; on expiry the CTA records RWKVQ_E_TIMEOUT in the status word,
+// skips its work, still passes the cluster barriers, frees its tensor memory and returns.
+#include <cooperative_groups.h>
+
+#include <stdlib.h>
+
+#include <algorithm>
+
+#include "rwkvq_tc.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace rwkvq {
+
+constexpr int kTbProducers = 256;         // warps 0-7: weights, activations, epilogue
+constexpr int kTbThreads = 288;           // + warp 8: one lane issues the MMAs
+constexpr int kTbPassK = 256;             // columns of a pass: one super-block, four 64-K slabs
+constexpr int kTbSlabs = kTbPassK / kGmK;
+constexpr int kTbRP = kGmRows + 4;        // pitch of a partial-sum row
+constexpr int kTbMaxMats = 4;
+
+struct TcbArgs {
+    QView t[kTbMaxMats];
+    const float* x[kTbMaxMats];           // [N, ldx] fp32, or null when x16 is given
+    const float* amax[kTbMaxMats];        // with x:   [N] max|x| per token
+    const __half* x16[kTbMaxMats];        // [N, ldx] fp16 rows = x * 2^s
+    const float* unscale[kTbMaxMats];     // with x16: [N] 2^-s
+    float* y[kTbMaxMats];                 // [N, ldy]
+    const float* resid[kTbMaxMats];
+    float* amax_out[kTbMaxMats];          // optional [N]: max|y| per token is merged into it (atomic max; zeroed by the caller)
+    long long ldx, ldy;
+    int n_tokens, epilogue;
+    int passes;                           // 256-column passes of one CTA's K slice
+    int ks;                               // CTAs along K = cluster size
+    int* status;                          // device word: first error code, 0 = ok
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int SLAB = kGmRows * 128, BSLAB = NT * 128;
+    constexpr uint32_t TM_COLS = NT < 32 ? 32 : NT;
+    constexpr int RP = kTbRP;
+    unsigned char* a_slabs = smem;                               // [4][SLAB]  weights of the pass
+    unsigned char* b_slabs = smem + kTbSlabs * SLAB;             // [4][BSLAB] activations of the pass
+    float* part = reinterpret_cast<float*>(a_slabs);             // [NT][RP], over the operands once the MMAs are done
+    __shared__ uint64_t bar_full, bar_mma;
+    __shared__ uint32_t s_tmem;
+    __shared__ volatile int s_fail;
+    __shared__ float s_sc[NT], s_un[NT], s_omax[NT];
+    cg::cluster_group cluster = cg::this_cluster();
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const QView& t = a.t[blockIdx.y];
+    const int ks = a.ks, rank = static_cast<int>(blockIdx.x) % ks, rt = static_cast<int>(blockIdx.x) / ks;
+    const int row0 = rt * kGmRows;
+    const int n0 = blockIdx.z * NT, nn = min(NT, a.n_tokens - n0);
+    const int np = a.passes, sbk0 = rank * np;
+    const bool is16 = a.x16[blockIdx.y] != nullptr;
+
+    if (tid == 0) {
+        mbar_init(&bar_full, kTbProducers);
+        mbar_init(&bar_mma, 1);
+        s_fail = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    pdl_launch_dependents();
+    if (warp == 0) tmem_alloc(&s_tmem, TM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+
+    if (warp == kTbProducers / 32) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            pdl_wait();
+            const uint32_t idesc = umma_idesc(NT);
+            const uint64_t a_desc0 = umma_desc(smem_addr(a_slabs)), b_desc0 = umma_desc(smem_addr(b_slabs));
+            bool ok = true;
+            for (int p = 0; p < np && ok; ++p) {
+                if (!mbar_wait_bounded(&bar_full, p & 1)) { ok = false; break; }
+                if (s_fail) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int sl = 0; sl < kTbSlabs; ++sl) {
+                    const uint64_t ad = a_desc0 + (static_cast<uint64_t>(sl * SLAB) >> 4);
+                    const uint64_t bd = b_desc0 + (static_cast<uint64_t>(sl * BSLAB) >> 4);
+#pragma unroll
+                    for (int k = 0; k < kGmK / 16; ++k)        // 32 bytes further along K per step
+                        umma_f16(tmem, ad + 2 * k, bd + 2 * k, idesc, (p | sl | k) ? 1u : 0u);
+                }
+                umma_commit(&bar_mma);
+            }
+            if (!ok) s_fail = 1;
+        }
+    } else {
+        // ------------------------------------------------------------------ producers
+        const int pit = tid & 7, prow = tid >> 3;              // item (32 columns) of the pass, row within a group of 32
+        Packed P[4];
+        auto load_all = [&](int p) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) load_packed(P[q], t, min(row0 + 32 * q + prow, t.rows - 1), sbk0 + p, pit);
+        };
+        load_all(0);                                            // weights do not depend on the producer of x
+        pdl_wait();
+        if (tid < NT) {
+            float s1 = 1.f, u1 = 1.f;
+            if (is16) {
+                if (tid < nn) u1 = __ldcg(a.unscale[blockIdx.y] + n0 + tid);
+            } else {
+                // |x| * 2^(14 - e) <= 2^14 with max|x| <= 2^e; a non-finite row keeps scale 1 and propagates
+                const float am = tid < nn ? __ldcg(a.amax[blockIdx.y] + n0 + tid) : 0.f;
+                if (am > 0.f && am < INFINITY) {
+                    int e = 0;
+                    frexpf(am, &e);
+                    e = max(-100, e);
+                    s1 = ldexpf(1.f, 14 - e);
+                    u1 = ldexpf(1.f, e - 14);
+                }
+            }
+            s_sc[tid] = s1; s_un[tid] = u1; s_omax[tid] = 0.f;
+        }
+        // producers only: named barrier 1 (the issuer warp does not take part)
+        asm volatile("bar.sync 1, %0;" ::"n"(kTbProducers) : "memory");
+        constexpr int VPT = NT * 32 / kTbProducers;             // 16-byte activation vectors per thread and pass: 2, 4, 8
+        for (int p = 0; p < np; ++p) {
+            const int kbase = (sbk0 + p) * kTbPassK;
+            uint4 xv[VPT];
+            if (is16) {                                          // requested before the wait and the conversion
+                const __half* xg = a.x16[blockIdx.y] + static_cast<size_t>(n0) * a.ldx + kbase;
+#pragma unroll
+                for (int u = 0; u < VPT; ++u) {
+                    const int idx = tid + u * kTbProducers, n = idx >> 5, k8 = idx & 31;
+                    xv[u] = n < nn ? __ldcg(reinterpret_cast<const uint4*>(xg + static_cast<size_t>(n) * a.ldx) + k8) : make_uint4(0, 0, 0, 0);
+                }
+            }
+            if (p > 0) {                                         // the MMAs of the previous pass have read the operands
+                if (lane == 0 && !s_fail && !mbar_wait_bounded(&bar_mma, (p - 1) & 1)) s_fail = 1;
+                __syncwarp();
+            }
+            if (!s_fail) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) convert_store(P[q], t, 32 * q + prow, pit, pit & 1, a_slabs + (pit >> 1) * SLAB);
+                if (is16) {
+#pragma unroll
+                    for (int u = 0; u < VPT; ++u) {
+                        const int idx = tid + u * kTbProducers, n = idx >> 5, k8 = idx & 31;
+                        *reinterpret_cast<uint4*>(b_slabs + (k8 >> 3) * BSLAB + sw128_offset(n, k8 & 7)) = xv[u];
+                    }
+                } else {
+                    const float* xg = a.x[blockIdx.y] + static_cast<size_t>(n0) * a.ldx + kbase;
+#pragma unroll
+                    for (int h2 = 0; h2 < 2; ++h2) {             // two rounds: half the vectors' loads in flight at a time
+                        float4 f[VPT / 2 > 0 ? VPT / 2 : 1][2];
+#pragma unroll
+                        for (int u = 0; u < VPT / 2; ++u) {
+                            const int idx = tid + (h2 * (VPT / 2) + u) * kTbProducers, n = idx >> 5, k8 = idx & 31;
+                            const float4* src = reinterpret_cast<const float4*>(xg + static_cast<size_t>(n) * a.ldx) + 2 * k8;
+                            f[u][0] = n < nn ? __ldcg(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            f[u][1] = n < nn ? __ldcg(src + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                        for (int u = 0; u < VPT / 2; ++u) {
+                            const int idx = tid + (h2 * (VPT / 2) + u) * kTbProducers, n = idx >> 5, k8 = idx & 31;
+                            const float s1 = s_sc[n];
+                            const __half2 h0 = __floats2half2_rn(f[u][0].x * s1, f[u][0].y * s1), h1 = __floats2half2_rn(f[u][0].z * s1, f[u][0].w * s1);
+                            const __half2 h2v = __floats2half2_rn(f[u][1].x * s1, f[u][1].y * s1), h3 = __floats2half2_rn(f[u][1].z * s1, f[u][1].w * s1);
+                            uint4 pk;
+                            pk.x = *reinterpret_cast<const uint32_t*>(&h0); pk.y = *reinterpret_cast<const uint32_t*>(&h1);
+                            pk.z = *reinterpret_cast<const uint32_t*>(&h2v); pk.w = *reinterpret_cast<const uint32_t*>(&h3);
+                            *reinterpret_cast<uint4*>(b_slabs + (k8 >> 3) * BSLAB + sw128_offset(n, k8 & 7)) = pk;
+                        }
+                    }
+                }
+            }
+            fence_async_smem();                                 // generic-proxy stores -> visible to the tensor core
+            mbar_arrive(&bar_full);
+            if (p + 1 < np) load_all(p + 1);                    // the registers are free again
+        }
+        // the accumulator is complete when the last commit has arrived
+        if (lane == 0 && !s_fail && !mbar_wait_bounded(&bar_mma, (np - 1) & 1)) s_fail = 1;
+        __syncwarp();
+    }
+    tc_fence_after();
+    __syncthreads();
+    const bool failed = s_fail != 0;
+    if (failed) {
+        if (tid == 0 && a.status) atomicCAS(a.status, 0, RWKVQ_E_TIMEOUT);
+    } else if (warp < kTbProducers / 32) {
+        // warp w reads tensor-memory lanes 32 (w % 4) .. +31 (= output rows); the two warps of a lane group split the tokens
+        const int rl = (warp & 3) * 32 + lane;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+        for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += 16) {
+            float v[8];
+            tmem_ld8(lane_base + c0, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) part[(c0 + j) * RP + rl] = v[j] * s_un[c0 + j];
+        }
+    }
+    tc_fence_before();
+    cluster.sync();
+    if (!failed) {
+        // ---- add the ks partial tiles in rank order, epilogue, store: float4 groups of 4 rows
+        float* y = a.y[blockIdx.y] + static_cast<size_t>(n0) * a.ldy;
+        const float* resid = a.resid[blockIdx.y] ? a.resid[blockIdx.y] + static_cast<size_t>(n0) * a.ldy : nullptr;
+        const bool vec_io = (a.ldy % 4 == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0) &&
+                            (resid == nullptr || (reinterpret_cast<uintptr_t>(resid) & 15) == 0);
+        constexpr int g4 = kGmRows / 4;
+        const int total4 = nn * g4;
+        const int per = (total4 + ks - 1) / ks;
+        const int lo = rank * per, hi = min(total4, lo + per);
+        for (int i4 = lo + tid; i4 < hi; i4 += kTbThreads) {
+            const int n = i4 / g4, r = (i4 - n * g4) * 4;
+            const int row = row0 + r;
+            if (row >= t.rows) continue;
+            float4 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (k < ks) v[k] = *reinterpret_cast<const float4*>(cluster.map_shared_rank(part, k) + n * RP + r);
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (k < ks) { s.x += v[k].x; s.y += v[k].y; s.z += v[k].z; s.w += v[k].w; }
+            const size_t o = static_cast<size_t>(n) * a.ldy + row;
+            const bool full = vec_io && row + 3 < t.rows;
+            if (a.epilogue == RWKVQ_EPI_RELU2) {
+                s.x = fmaxf(s.x, 0.f); s.y = fmaxf(s.y, 0.f); s.z = fmaxf(s.z, 0.f); s.w = fmaxf(s.w, 0.f);
+                s.x *= s.x; s.y *= s.y; s.z *= s.z; s.w *= s.w;
+            } else if (a.epilogue == RWKVQ_EPI_ADD) {
+                if (full) {
+                    const float4 rv = __ldcg(reinterpret_cast<const float4*>(resid + o));
+                    s.x = __fadd_rn(s.x, rv.x); s.y = __fadd_rn(s.y, rv.y); s.z = __fadd_rn(s.z, rv.z); s.w = __fadd_rn(s.w, rv.w);
+                } else {
+                    s.x = __fadd_rn(s.x, __ldcg(resid + o));
+                    if (row + 1 < t.rows) s.y = __fadd_rn(s.y, __ldcg(resid + o + 1));
+                    if (row + 2 < t.rows) s.z = __fadd_rn(s.z, __ldcg(resid + o + 2));
+                    if (row + 3 < t.rows) s.w = __fadd_rn(s.w, __ldcg(resid + o + 3));
+                }
+            }
+            if (full) {
+                *reinterpret_cast<float4*>(y + o) = s;
+            } else {
+                y[o] = s.x;
+                if (row + 1 < t.rows) y[o + 1] = s.y;
+                if (row + 2 < t.rows) y[o + 2] = s.z;
+                if (row + 3 < t.rows) y[o + 3] = s.w;
+            }
+            if (a.amax_out[blockIdx.y] != nullptr) {
+                // |v| as int bits orders like the float; a NaN compares above every number and so survives
+                float m = fabsf(s.x);
+                if (row + 1 < t.rows) m = fmaxf(m, fabsf(s.y)) + 0.f * s.y;
+                if (row + 2 < t.rows) m = fmaxf(m, fabsf(s.z)) + 0.f * s.z;
+                if (row + 3 < t.rows) m = fmaxf(m, fabsf(s.w)) + 0.f * s.w;
+                atomicMax(reinterpret_cast<int*>(s_omax) + n, __float_as_int(fabsf(m)));
+            }
+        }
+    }
+    cluster.sync();          // nobody leaves while a peer still reads its partial tile
+    if (!failed && a.amax_out[blockIdx.y] != nullptr && tid < nn) {
+        const int bits = reinterpret_cast<const int*>(s_omax)[tid];
+        if (bits != 0) atomicMax(reinterpret_cast<int*>(a.amax_out[blockIdx.y]) + n0 + tid, bits);
+    }
+    if (warp == 0) tmem_dealloc(tmem, TM_COLS);
+}
+
+namespace {
+
+template <int NT>
+int launch_tcb(TcbArgs& a, int n_mats, int n_groups, int row_tiles, cudaStream_t s) {
+    const size_t smem = 1024 + static_cast<size_t>(kTbSlabs) * (kGmRows * 128 + NT * 128);
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) dev = 0;
+    if (dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcb_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "rwkvq_gemm_tcb: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        if (dev < 64) configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(row_tiles * a.ks, n_mats, n_groups);
+    cfg.blockDim = dim3(kTbThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = a.ks; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tcb_kernel<NT>, a);
+    if (le != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "rwkvq_gemm_tcb: %s", cudaGetErrorString(le));
+    return RWKVQ_OK;
+}
+
+}  // namespace
+
+int g_tcb_force_ks = 0;        // profiling aid (rwkvq_profiling.h): cluster size override
+
+// RWKVQ_TCB=0 in the environment keeps the small-batch linears on the mma.sync kernel (A/B comparisons)
+bool tcb_enabled() {
+    static const bool on = [] { const char* e = getenv("RWKVQ_TCB"); return !(e && e[0] == '0'); }();
+    return on && g_tcb_force_ks >= 0;          // rwkvq_profiling_tcb_force(-1) switches it off at run time
+}
+
+// Whether the tcgen05 small-batch kernel serves the tensor: sb6 / sym in the layouts the prefill
+// kernel's producer reads (block 32 x 8 and 16 x 16), columns a multiple of 256.
+bool gemm_tcb_ok(const rwkvq_qtensor& t) {
+    if (t.cols % 256 != 0 || t.cols < 256) return false;
+    if (t.kind == RWKVQ_KIND_SB6) return t.gs == 32 && t.sb == 8;
+    if (t.kind == RWKVQ_KIND_SYM) return t.gs == 16 && t.sb == 16 && (t.bits == 8 || (t.qh && t.qh2));
+    return false;
+}
+
+// Same contract as launch_gemv_batch (rwkvq_common.cuh), plus the device status word.
+int launch_gemm_tcb(const rwkvq_qtensor* ts, int n_mats, const void* const* xs, bool half_in, const float* const* scales,
+                    int N, long long ldx, float* const* ys, long long ldy, int epilogue, const float* const* resids,
+                    float* const* amax_outs, int* status, cudaStream_t s) {
+    RWKVQ_REQUIRE(n_mats >= 1 && n_mats <= kTbMaxMats, RWKVQ_E_LIMIT, "rwkvq_gemm_tcb: %d matrices", n_mats);
+    TcbArgs a{};
+    for (int k = 0; k < n_mats; ++k) {
+        RWKVQ_REQUIRE(gemm_tcb_ok(ts[k]) && ts[k].kind == ts[0].kind && ts[k].bits == ts[0].bits && ts[k].rows == ts[0].rows &&
+                          ts[k].cols == ts[0].cols, RWKVQ_E_SHAPE, "rwkvq_gemm_tcb: fused matrices must share layout and shape");
+        RWKVQ_REQUIRE(xs[k] && ys[k] && scales[k], RWKVQ_E_NULL, "rwkvq_gemm_tcb: x, its scales or y is null");
+        RWKVQ_REQUIRE(aligned(xs[k], 16) && ldx % 8 == 0, RWKVQ_E_ALIGN, "rwkvq_gemm_tcb: x rows must be 16-byte aligned (ldx %% 8)");
+        a.t[k] = make_view(ts[k]);
+        if (half_in) { a.x16[k] = static_cast<const __half*>(xs[k]); a.unscale[k] = scales[k]; }
+        else { a.x[k] = static_cast<const float*>(xs[k]); a.amax[k] = scales[k]; }
+        a.y[k] = ys[k]; a.resid[k] = resids ? resids[k] : nullptr;
+        a.amax_out[k] = amax_outs ? amax_outs[k] : nullptr;
+        RWKVQ_REQUIRE(epilogue != RWKVQ_EPI_ADD || a.resid[k], RWKVQ_E_NULL, "rwkvq_gemm_tcb: resid is null");
+    }
+    a.ldx = ldx; a.ldy = ldy; a.n_tokens = N; a.epilogue = epilogue; a.status = status;
+    const int rows = ts[0].rows, cols = ts[0].cols;
+    const int nt = N <= 16 ? 16 : N <= 32 ? 32 : 64;
+    const int n_groups = (N + nt - 1) / nt;
+    const int row_tiles = (rows + kGmRows - 1) / kGmRows, n_sb = cols / kTbPassK;
+    // cluster size: a divisor of the pass count, at most 8; cost model in microseconds: waves of
+    // resident CTAs (two per SM) x (set-up and first loads + passes) + reduction
+    const int tiles = row_tiles * n_mats * n_groups;
+    int best_ks = 1;
+    double best = 1e30;
+    for (int c = 1; c <= 8; ++c) {
+        if (n_sb % c) continue;
+        const int waves = (tiles * c + 2 * 148 - 1) / (2 * 148);
+        const double t = waves * (2.5 + 0.9 * (n_sb / c)) + 2.0 + 0.15 * c;
+        if (t < best) { best = t; best_ks = c; }
+    }
+    if (g_tcb_force_ks > 0 && n_sb % g_tcb_force_ks == 0 && g_tcb_force_ks <= 8) best_ks = g_tcb_force_ks;
+    a.ks = best_ks;
+    a.passes = n_sb / best_ks;
+    switch (nt) {
+        case 16: return launch_tcb<16>(a, n_mats, n_groups, row_tiles, s);
+        case 32: return launch_tcb<32>(a, n_mats, n_groups, row_tiles, s);
+        default: return launch_tcb<64>(a, n_mats, n_groups, row_tiles, s);
+    }
+}
+
+}  // namespace rwkvq
+
+extern "C" void rwkvq_profiling_tcb_force(int force_ks) { rwkvq::g_tcb_force_ks = force_ks; }

@@ -431,10 +431,12 @@ __global__ void __launch_bounds__(kBtThreads, 2) gemv_batch_kernel(const BatchAr
 // max|x| of every row (one block per row): the pre-pass of the stand-alone entry point; inside
 // the decode step the producers of the activations write it themselves.  A non-finite row
 // yields inf or nan.
-__global__ void __launch_bounds__(256) row_amax_kernel(const float* __restrict__ x, long long ldx, int cols, float* __restrict__ amax) {
+__global__ void __launch_bounds__(256) row_amax_kernel(const float* __restrict__ x, long long ldx, int cols, float* __restrict__ amax,
+                                                       int* __restrict__ status) {
     __shared__ float red[8];
     pdl_launch_dependents();
     pdl_wait();
+    if (status != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *status = 0;      // status word of the product kernel that follows
     const float* row = x + static_cast<size_t>(blockIdx.x) * ldx;
     float m = 0.f;
     for (int i = threadIdx.x; i < cols / 4; i += 256) {
@@ -595,8 +597,8 @@ int launch_gemv_batch(const rwkvq_qtensor* ts, int n_mats, const void* const* xs
     }
 }
 
-int launch_row_amax(const float* x, long long ldx, int cols, int N, float* amax, cudaStream_t s) {
-    cudaError_t e = launch_pdl(row_amax_kernel, dim3(N), dim3(256), 0, s, x, ldx, cols, amax);
+int launch_row_amax(const float* x, long long ldx, int cols, int N, float* amax, int* status, cudaStream_t s) {
+    cudaError_t e = launch_pdl(row_amax_kernel, dim3(N), dim3(256), 0, s, x, ldx, cols, amax, status);
     if (e != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "row_amax: %s", cudaGetErrorString(e));
     return RWKVQ_OK;
 }
@@ -616,7 +618,8 @@ extern "C" void rwkvq_profiling_batch_force(int force_ks, int rows, int cols) {
     g_batch_force_cols = cols;
 }
 
-extern "C" size_t rwkvq_gemv_batch_workspace_bytes(int N) { return N > 0 ? ((static_cast<size_t>(N) * sizeof(float) + 255) / 256) * 256 : 0; }
+// [status word, padded to 256 bytes][N floats: max|x| per row]
+extern "C" size_t rwkvq_gemv_batch_workspace_bytes(int N) { return N > 0 ? 256 + ((static_cast<size_t>(N) * sizeof(float) + 255) / 256) * 256 : 0; }
 
 extern "C" int rwkvq_gemv_batch(const rwkvq_qtensor* t, const float* x, int N, int64_t ldx, float* y, int64_t ldy,
                                 int epilogue, const float* resid, void* workspace, size_t workspace_bytes, void* stream) {
@@ -626,19 +629,23 @@ extern "C" int rwkvq_gemv_batch(const rwkvq_qtensor* t, const float* x, int N, i
     RWKVQ_REQUIRE(epilogue >= RWKVQ_EPI_NONE && epilogue <= RWKVQ_EPI_ADD, RWKVQ_E_DTYPE, "rwkvq_gemv_batch: epilogue %d", epilogue);
     RWKVQ_REQUIRE(ldx >= t->cols && ldy >= t->rows, RWKVQ_E_SHAPE, "rwkvq_gemv_batch: ldx %lld / ldy %lld", (long long)ldx, (long long)ldy);
     RWKVQ_REQUIRE(x && y, RWKVQ_E_NULL, "rwkvq_gemv_batch: x or y is null");
-    RWKVQ_REQUIRE(mma_layout_of(*t) >= 0, RWKVQ_E_DTYPE,
-                  "rwkvq_gemv_batch: needs an sb6 tensor with relayouted records / planes, a sym tensor or per-row int8");
+    const bool tcb = tcb_enabled() && gemm_tcb_ok(*t) && ldx % 8 == 0;
+    RWKVQ_REQUIRE(tcb || mma_layout_of(*t) >= 0, RWKVQ_E_DTYPE,
+                  "rwkvq_gemv_batch: needs an sb6 tensor, a sym tensor or per-row int8 with columns in multiples of 128");
     RWKVQ_REQUIRE(aligned(x, 16) && ldx % 4 == 0, RWKVQ_E_ALIGN, "rwkvq_gemv_batch: x rows must be 16-byte aligned");
+    RWKVQ_REQUIRE(aligned(workspace, 16), RWKVQ_E_ALIGN, "rwkvq_gemv_batch: workspace must be 16-byte aligned");
     RWKVQ_REQUIRE(workspace && workspace_bytes >= rwkvq_gemv_batch_workspace_bytes(N), RWKVQ_E_LIMIT,
                   "rwkvq_gemv_batch: workspace of %zu bytes, %zu needed", workspace_bytes, rwkvq_gemv_batch_workspace_bytes(N));
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    float* amax = static_cast<float*>(workspace);
-    rc = launch_row_amax(x, ldx, t->cols, N, amax, s);
+    int* status = static_cast<int*>(workspace);
+    float* amax = reinterpret_cast<float*>(static_cast<char*>(workspace) + 256);
+    rc = launch_row_amax(x, ldx, t->cols, N, amax, status, s);
     if (rc) return rc;
     const void* xs[1] = {x};
     const float* am[1] = {amax};
     float* ys[1] = {y};
     const float* rs[1] = {resid};
-    rc = launch_gemv_batch(t, 1, xs, false, am, N, ldx, ys, ldy, epilogue, rs, nullptr, s);
+    rc = tcb ? launch_gemm_tcb(t, 1, xs, false, am, N, ldx, ys, ldy, epilogue, rs, nullptr, status, s)
+             : launch_gemv_batch(t, 1, xs, false, am, N, ldx, ys, ldy, epilogue, rs, nullptr, s);
     return rc ? rc : check_launch("rwkvq_gemv_batch");
 }

@@ -18,6 +18,9 @@ void rwkvq_profiling_gemm_trace(void* buf512);
 void rwkvq_profiling_batch_trace(void* buf8, int force_ks);
 /* The same override for tensors of one shape only (rows = 0: every shape); 0 switches it off. */
 void rwkvq_profiling_batch_force(int force_ks, int rows, int cols);
+/* Small-batch linear on tcgen05: > 0 forces the cluster size, -1 routes every call to the mma.sync
+ * kernel instead, 0 restores the launcher's choice. */
+void rwkvq_profiling_tcb_force(int force_ks);
 #ifdef __cplusplus
 }
 #endif
