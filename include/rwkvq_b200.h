@@ -211,6 +211,24 @@ int rwkvq_gemv_t(const rwkvq_qtensor* t, const float* x, int N, int64_t ldx,
                  float* y, int64_t ldy, int act, int round_w, void* stream);
 
 /*
+ * Up to four LoRA branches for N rows in two launches on the tensor cores:
+ *   y_i[n, :] = act_i( x_i[n, :] @ W1_i ) @ W2_i,   W1_i stored [D, r_i], W2_i stored [r_i, D]
+ * Stands behind QuantTMix._lora for every row count above 2 (backends/metal/quant_model.py:462-526:
+ * the decay, in-context rate, gate and value-residual branches; dense fp16 matmuls there).  The
+ * matrices are read from their file bytes (asym / per-row int8 / dense bf16) and used in the
+ * loader's precision fp16(bf16(w)), which is exact in fp16; x and the rank-space activations enter
+ * as fp16 pairs hi + lo (~2^-22 relative), accumulation fp32.  act: 0 none, 1 tanh, 2 sigmoid.
+ *   t1_host / t2_host  host arrays of n_br descriptors; xs_host / ys_host host arrays of n_br device
+ *   pointers to [N, D] fp32 rows (contiguous, 16-byte aligned); acts_host host array.
+ *   Requirements: D % 128 == 0, ranks multiples of 16 up to 512 (RWKVQ_E_SHAPE otherwise: use
+ *   rwkvq_gemv_t).  workspace: rwkvq_lora_pair_workspace_bytes(N, max rank) bytes, 16-byte aligned.
+ */
+size_t rwkvq_lora_pair_workspace_bytes(int N, int max_rank);
+int rwkvq_lora_pair(const rwkvq_qtensor* t1_host, const rwkvq_qtensor* t2_host, int n_br, const float* const* xs_host,
+                    float* const* ys_host, const int* acts_host, int N, int D, void* workspace, size_t workspace_bytes,
+                    void* stream);
+
+/*
  * Single-vector rwkvq_gemv that allocates nothing.  NO COUNTERPART IN THE
  * REFERENCE: added for callers that may not allocate on the call path (an
  * inference server's steady-state loop that has frozen its memory pool, a host
@@ -285,6 +303,12 @@ int rwkvq_seq_ln_shift_mix_prep(const float* x, const float* ln_w, const float* 
  * dense LoRA products of long sequences (x @ W = [hi | lo] @ [W; W] on fp16 tensor cores, fp32
  * accumulation; the reference casts x to fp16 there: quant_model.py:204-208). */
 int rwkvq_split_fp16(const float* x, void* out_fp16, int64_t rows, int cols, void* stream);
+/* Rows of the embedding table for n_tokens ids in the loader's precision fp16(bf16(.)), LayerNorm 0
+ * applied: x [n_tokens, D] fp32 (quant_model.py:853, 975-976; ids are clamped to the table).  And a
+ * plain LayerNorm of n_rows rows (eps 1e-5), the final norm of the sequence path (:281). */
+int rwkvq_seq_embed_ln0(const rwkvq_qtensor* emb, const int64_t* tokens, const float* ln_w, const float* ln_b, float* x,
+                        int64_t n_tokens, int D, void* stream);
+int rwkvq_seq_layer_norm(const float* x, const float* ln_w, const float* ln_b, float* out, int64_t n_rows, int D, void* stream);
 int rwkvq_seq_tmix_pre(const float* k, const float* v, const float* yw, const float* ya, const float* yv,
                        const float* v_first, const float* w0, const float* a0, const float* v0,
                        const float* k_k, const float* k_a, float* w, float* k2, float* v2, float* neg_kk,

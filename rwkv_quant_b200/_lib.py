@@ -86,10 +86,17 @@ _PROTOS = {
     "rwkvq_relayout_planes": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_void_p]),
     "rwkvq_gemv_t": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_int64,
                                C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
+    "rwkvq_lora_pair_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int]),
+    "rwkvq_lora_pair": (C.c_int, [C.POINTER(QTensorStruct), C.POINTER(QTensorStruct), C.c_int, C.POINTER(C.c_void_p),
+                                  C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_int, C.c_int, C.c_void_p, C.c_size_t,
+                                  C.c_void_p]),
     "rwkvq_gemv_static": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_void_p,
                                     C.c_int, C.c_void_p, C.c_void_p]),
     "rwkvq_seq_ln_shift_mix": (C.c_int, [C.c_void_p] * 5 + [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                          C.c_void_p]),
+    "rwkvq_seq_embed_ln0": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                      C.c_int, C.c_void_p]),
+    "rwkvq_seq_layer_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
     "rwkvq_split_fp16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
     "rwkvq_file_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "rwkvq_file_close": (None, [C.c_void_p]),

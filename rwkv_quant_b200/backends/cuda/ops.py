@@ -286,6 +286,31 @@ def gemv_batch(dq: "DeviceQT", x: torch.Tensor, epilogue: int = 0, resid: Option
     return y
 
 
+def lora_pair_ok(pairs, D: int) -> bool:
+    """Whether ``lora_pair`` serves these (W1 [D, r], W2 [r, D]) tensor pairs."""
+    return D % 128 == 0 and all(a.rows == D and b.cols == D and a.cols == b.rows and a.cols % 16 == 0
+                                and 16 <= a.cols <= 512 and a.outliers is None and b.outliers is None for a, b in pairs)
+
+
+def lora_pair(pairs, xs: Sequence[torch.Tensor], acts: Sequence[int]) -> List[torch.Tensor]:
+    """y_i = act_i(x_i @ W1_i) @ W2_i for up to four (W1, W2) pairs of tensors stored [in, out], x_i
+    [N, D] fp32: two tensor-core launches for all branches (act: 0 none, 1 tanh, 2 sigmoid)."""
+    lib = _lib.load()
+    n_br = len(pairs)
+    xs = [x.float().contiguous() for x in xs]
+    _require_cuda(*xs)
+    N, D = xs[0].shape
+    ys = [torch.empty((N, D), dtype=torch.float32, device=xs[0].device) for _ in range(n_br)]
+    t1 = (QTensorStruct * n_br)(*[a.struct for a, _ in pairs])
+    t2 = (QTensorStruct * n_br)(*[b.struct for _, b in pairs])
+    nws = lib.rwkvq_lora_pair_workspace_bytes(N, max(a.cols for a, _ in pairs))
+    ws = torch.empty(nws, dtype=torch.uint8, device=xs[0].device)
+    _lib.check(lib.rwkvq_lora_pair(t1, t2, n_br, (C.c_void_p * n_br)(*[x.data_ptr() for x in xs]),
+                                   (C.c_void_p * n_br)(*[y.data_ptr() for y in ys]), (C.c_int * n_br)(*acts), N, D,
+                                   ws.data_ptr(), nws, _lib.stream_ptr()), "rwkvq_lora_pair")
+    return ys
+
+
 def gemm(dq: "DeviceQT", x: torch.Tensor, epilogue: int = 0, resid: Optional[torch.Tensor] = None,
          check: bool = False) -> torch.Tensor:
     """x [M, IN] fp32 -> y [M, OUT] fp32 on the tcgen05 tensor cores with the dequantisation
@@ -396,6 +421,27 @@ def seq_ln_shift_mix(x: torch.Tensor, ln_w, ln_b, shift_in: Optional[torch.Tenso
                                                   mix2.data_ptr(), mix2.shape[0], out.data_ptr(), new_shift.data_ptr(),
                                                   B, T, D, _lib.stream_ptr()), "rwkvq_seq_ln_shift_mix")
     return out, new_shift
+
+
+def seq_embed_ln0(emb: "DeviceQT", idx: torch.Tensor, ln_w: torch.Tensor, ln_b: torch.Tensor) -> torch.Tensor:
+    """idx [...] int64 -> LayerNorm0(rows of the packed embedding table) [..., D] fp32, one kernel."""
+    _require_cuda(idx, ln_w)
+    flat = idx.reshape(-1).contiguous().long()
+    out = torch.empty((flat.numel(), emb.cols), dtype=torch.float32, device=idx.device)
+    _lib.check(_lib.load().rwkvq_seq_embed_ln0(C.byref(emb.struct), flat.data_ptr(), ln_w.data_ptr(), ln_b.data_ptr(),
+                                               out.data_ptr(), flat.numel(), emb.cols, _lib.stream_ptr()), "rwkvq_seq_embed_ln0")
+    return out.reshape(*idx.shape, emb.cols)
+
+
+def seq_layer_norm(x: torch.Tensor, ln_w: torch.Tensor, ln_b: torch.Tensor) -> torch.Tensor:
+    """LayerNorm over the last axis (eps 1e-5) of fp32 rows, one kernel."""
+    _require_cuda(x, ln_w)
+    x2 = x.float().contiguous()
+    out = torch.empty_like(x2)
+    D = x2.shape[-1]
+    _lib.check(_lib.load().rwkvq_seq_layer_norm(x2.data_ptr(), ln_w.data_ptr(), ln_b.data_ptr(), out.data_ptr(),
+                                                x2.numel() // D, D, _lib.stream_ptr()), "rwkvq_seq_layer_norm")
+    return out
 
 
 def split_fp16(x: torch.Tensor) -> torch.Tensor:

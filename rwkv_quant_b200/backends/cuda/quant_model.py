@@ -61,6 +61,7 @@ class QuantRWKV7:
         self.gemm_min_batch = int(gemm_min_batch)
         self.gemv_max_batch = int(gemv_max_batch)
         self.batch_max = 64              # rows up to which the weights-once small-batch kernel serves a linear
+        self.lora_pair_max = 1024        # rows up to which the sequence path uses rwkvq_lora_pair (measured: 512 rows equal, 8192 rows slower)
         T = ckpt.tensors
         dev = self.device
         def dq(key):
@@ -265,25 +266,37 @@ class QuantRWKV7:
         H, S = self.n_head, self.head_size
         wkv, ts, cs = state
         N = B * T
+        pairs = [(L.w1, L.w2), (L.a1, L.a2), (L.g1, L.g2)] + ([(L.v1, L.v2)] if i > 0 else [])
+        # both LoRA products of all branches in two launches of the library's own tensor-core kernels, up
+        # to lora_pair_max rows; longer calls (pp512 at batch 16 = 8192 rows) go through a dense fp16 copy
+        # and a library GEMM, which is faster there (the own kernels re-stage x per 32 rank columns)
+        pair_kernel = 2 < N <= self.lora_pair_max and ops.lora_pair_ok(pairs, D)
         if self.fused_prep and N > 8 and D % 2 == 0:
             # LN1 + shift + 6 lerps, each row written once in the form its consumers read
             mr, mk, mv = self._prep_modes(N, (L.Wr, L.Wk, L.Wv))
-            modes = [mr, ops.PREP_SPLIT, mk, mv | (ops.PREP_SPLIT if i > 0 else 0), ops.PREP_SPLIT, ops.PREP_SPLIT]
+            lm = ops.PREP_F32 if pair_kernel else ops.PREP_SPLIT
+            modes = [mr, lm, mk, mv | (lm if i > 0 else 0), lm, lm]
             (xr, xw, xk, xv, xa, xg), ts = ops.seq_ln_shift_mix_prep(x, L.ln1[0], L.ln1[1], ts, L.x_mix, modes)
             lin, lora = self._linear_rows, self._lora_rows
+            f32 = lambda rows: rows.f32
         else:
             xs, ts = ops.seq_ln_shift_mix(x, L.ln1[0], L.ln1[1], ts, L.x_mix)          # LN1 + shift + 6 lerps
             xr, xw, xk, xv, xa, xg = (xs[j].reshape(N, D) for j in range(6))
             lin, lora = self._linear, self._lora_seq
+            f32 = lambda rows: rows
         lora2 = lambda dq, t, act=0: self._lora_seq(dq, t, act)
         r, k, v = lin(L.Wr, xr), lin(L.Wk, xk), lin(L.Wv, xv)
-        y_w = lora2(L.w2, lora(L.w1, xw, 1))
-        y_a = lora2(L.a2, lora(L.a1, xa, 0))
-        g = lora2(L.g2, lora(L.g1, xg, 2))
-        if i == 0:
-            v_first, y_v = v, None
+        if pair_kernel:
+            ys = ops.lora_pair(pairs, [f32(xw), f32(xa), f32(xg)] + ([f32(xv)] if i > 0 else []), [1, 0, 2, 0][:len(pairs)])
+            y_w, y_a, g = ys[:3]
+            y_v = ys[3] if i > 0 else None
         else:
-            y_v = lora2(L.v2, lora(L.v1, xv, 0))
+            y_w = lora2(L.w2, lora(L.w1, xw, 1))
+            y_a = lora2(L.a2, lora(L.a1, xa, 0))
+            g = lora2(L.g2, lora(L.g1, xg, 2))
+            y_v = None if i == 0 else lora2(L.v2, lora(L.v1, xv, 0))
+        if i == 0:
+            v_first = v
         w, k, v2, na, nb = ops.seq_tmix_pre(k, v, y_w, y_a, y_v, None if i == 0 else v_first, L.w0, L.a0, L.v0,
                                             L.k_k, L.k_a, H)
         r4 = lambda t: t.reshape(B, T, H, S)
@@ -319,11 +332,16 @@ class QuantRWKV7:
         idx = torch.as_tensor(idx, device=self.device).long()
         B, T = idx.shape
         states = self._materialize(states, B)
-        x = F.layer_norm(self._embed(idx), (self.n_embd,), *self.ln0)
+        if self.emb.outliers is None and self.n_embd <= 4096:
+            x = ops.seq_embed_ln0(self.emb, idx.clamp(0, self.vocab_size - 1), *self.ln0)     # gather + LN0: one kernel
+        else:
+            x = F.layer_norm(self._embed(idx), (self.n_embd,), *self.ln0)
         v_first, new_states = None, []
         for i, (L, st) in enumerate(zip(self.blocks, states)):
             x, v_first, st = self._block_seq(i, L, x, v_first, st)
             new_states.append(st)
+        if self.n_embd <= 4096:
+            return ops.seq_layer_norm(x, *self.ln_out), new_states
         return F.layer_norm(x, (self.n_embd,), *self.ln_out), new_states
 
     def forward_stateful(self, idx, states, last_only: bool = False, tail_only: int = 0):
@@ -372,9 +390,10 @@ class QuantRWKV7:
         return Decoder(self, batch_size, states, use_graph, self_feed, groups)
 
     def decode_groups(self, batch_size: int) -> int:
-        """Stream groups whose launch chains run side by side (see ``Decoder``): two from 48 streams
-        on (measured on B200, 1.5B: 64 streams 4.45 -> 3.84 ms per step; 32 streams and fewer lose)."""
-        return 2 if batch_size >= 48 else 1
+        """Stream groups whose launch chains run side by side (see ``Decoder``).  Measured on B200
+        (1.5B, 64 streams): two groups of 32 on the mma.sync linears 3.82 ms per step, one group of 64
+        on the tcgen05 linears 3.77 ms; smaller batches lose with groups.  One group is the default."""
+        return 1
 
     @property
     def launches_per_token(self) -> int:

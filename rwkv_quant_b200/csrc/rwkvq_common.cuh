@@ -264,6 +264,7 @@ int launch_gemv_batch(const rwkvq_qtensor* ts, int n_mats, const void* const* xs
 // status: device word that receives RWKVQ_E_TIMEOUT if a bounded pipeline wait ran out.
 bool gemm_tcb_ok(const rwkvq_qtensor& t);
 bool tcb_enabled();
+bool tcb_forced();        // a profiling override asks for the tcgen05 kernel at every batch size
 int launch_gemm_tcb(const rwkvq_qtensor* ts, int n_mats, const void* const* xs, bool half_in, const float* const* scales,
                     int N, long long ldx, float* const* ys, long long ldy, int epilogue, const float* const* resids,
                     float* const* amax_outs, int* status, cudaStream_t s);

@@ -532,6 +532,10 @@ namespace {
 
 constexpr int kBatchMax = 256;     // streams up to which the small-batch kernel serves the linears of a step
 inline bool batch_path(int B) { return B > 2 && B <= kBatchMax; }
+// Which small-batch kernel: measured on B200 (1.5B, whole decode step) the tcgen05 form wins from 33
+// streams on (64 streams: 3.77 against 4.43 ms per step) and loses below (32: 2.87 / 2.68 ms, 8: 2.42 / 2.01 ms):
+// its pass (dependent weight loads -> conversion -> MMA) is longer than a warp-iteration of the mma.sync form
+inline bool tcb_pays(int B) { return tcb_enabled() && B > 32; }
 
 
 struct Workspace {
@@ -595,7 +599,7 @@ int linear(const rwkvq_qtensor* t, const float* x, int B, int in, float* y, int 
         float* ys[1] = {y};
         const float* rs[1] = {resid};
         float* ao[1] = {y_amax};
-        if (tcb_enabled() && gemm_tcb_ok(*t))
+        if (tcb_pays(B) && gemm_tcb_ok(*t))
             return launch_gemm_tcb(t, 1, xs, x16 != nullptr, sc, B, in, ys, out, epi, rs, ao, status, static_cast<cudaStream_t>(stream));
         return launch_gemv_batch(t, 1, xs, x16 != nullptr, sc, B, in, ys, out, epi, rs, ao, static_cast<cudaStream_t>(stream));
     }
@@ -684,6 +688,29 @@ int lora_pair(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, co
 
 extern "C" {
 
+int rwkvq_seq_embed_ln0(const rwkvq_qtensor* emb, const int64_t* tokens, const float* ln_w, const float* ln_b, float* x,
+                        int64_t n_tokens, int D, void* stream) {
+    int rc = validate_qtensor(emb, "rwkvq_seq_embed_ln0");
+    if (rc) return rc;
+    RWKVQ_REQUIRE(tokens && ln_w && ln_b && x, RWKVQ_E_NULL, "rwkvq_seq_embed_ln0: null pointer");
+    RWKVQ_REQUIRE(n_tokens >= 1 && emb->cols == D && D <= kRowThreads * kRowPer, RWKVQ_E_SHAPE,
+                  "rwkvq_seq_embed_ln0: %lld tokens, table [%d, %d], D %d (at most %d)", (long long)n_tokens, emb->rows, emb->cols, D,
+                  kRowThreads * kRowPer);
+    launch_pdl(embed_ln0_kernel, dim3(static_cast<unsigned>(n_tokens)), dim3(kRowThreads), 0, static_cast<cudaStream_t>(stream),
+               make_view(*emb), reinterpret_cast<const long long*>(tokens), ln_w, ln_b, x, D);
+    return check_launch("rwkvq_seq_embed_ln0");
+}
+
+int rwkvq_seq_layer_norm(const float* x, const float* ln_w, const float* ln_b, float* out, int64_t n_rows, int D, void* stream) {
+    RWKVQ_REQUIRE(x && ln_w && ln_b && out, RWKVQ_E_NULL, "rwkvq_seq_layer_norm: null pointer");
+    RWKVQ_REQUIRE(n_rows >= 1 && D >= 1 && D <= kRowThreads * kRowPer, RWKVQ_E_SHAPE, "rwkvq_seq_layer_norm: %lld rows of %d (at most %d)",
+                  (long long)n_rows, D, kRowThreads * kRowPer);
+    launch_pdl(ln_shift_mix_kernel<0>, dim3(static_cast<unsigned>(n_rows)), dim3(kRowThreads), 0, static_cast<cudaStream_t>(stream), x,
+               ln_w, ln_b, static_cast<float*>(nullptr), static_cast<const float*>(nullptr), out, static_cast<int>(n_rows), D,
+               static_cast<__half*>(nullptr), static_cast<float*>(nullptr), 0, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
+    return check_launch("rwkvq_seq_layer_norm");
+}
+
 size_t rwkvq_decode_workspace_bytes(const rwkvq_model* m, int B) {
     if (!m || B < 1) return 0;
     return carve(*m, B, nullptr).bytes;
@@ -754,7 +781,7 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
             const void* x3[3] = {w.xs16, w.xs16 + 2 * BD, w.xs16 + 3 * BD};
             const float* a3[3] = {am, am + 2 * B, am + 3 * B};
             float* y3[3] = {r, k, v};
-            if (tcb_enabled() && gemm_tcb_ok(L.Wr))
+            if (tcb_pays(B) && gemm_tcb_ok(L.Wr))
                 rc = launch_gemm_tcb(three, 3, x3, true, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, w.status, s);
             else
                 rc = launch_gemv_batch(three, 3, x3, true, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, s);

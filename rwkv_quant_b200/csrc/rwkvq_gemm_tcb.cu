@@ -39,6 +39,7 @@ constexpr int kTbPassK = 256;             // columns of a pass: one super-block,
 constexpr int kTbSlabs = kTbPassK / kGmK;
 constexpr int kTbRP = kGmRows + 4;        // pitch of a partial-sum row
 constexpr int kTbMaxMats = 4;
+extern unsigned long long* g_batch_trace;      // rwkvq_gemv_batch.cu: set by rwkvq_profiling_batch_trace
 
 struct TcbArgs {
     QView t[kTbMaxMats];
@@ -54,7 +55,16 @@ struct TcbArgs {
     int passes;                           // 256-column passes of one CTA's K slice
     int ks;                               // CTAs along K = cluster size
     int* status;                          // device word: first error code, 0 = ok
+    unsigned long long* trace;            // profiling aid (rwkvq_profiling.h): global-timer marks of CTA (0,0,0), or null
 };
+
+__device__ __forceinline__ void tb_mark(const TcbArgs& a, int slot) {
+    if (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        a.trace[slot] = t;
+    }
+}
 
 template <int NT>
 __global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a) {
@@ -80,6 +90,7 @@ __global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a
     const int np = a.passes, sbk0 = rank * np;
     const bool is16 = a.x16[blockIdx.y] != nullptr;
 
+    tb_mark(a, 0);
     if (tid == 0) {
         mbar_init(&bar_full, kTbProducers);
         mbar_init(&bar_mma, 1);
@@ -92,6 +103,7 @@ __global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
+    tb_mark(a, 1);
 
     if (warp == kTbProducers / 32) {
         // ------------------------------------------------------------------ MMA issuer
@@ -126,6 +138,7 @@ __global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a
         };
         load_all(0);                                            // weights do not depend on the producer of x
         pdl_wait();
+        tb_mark(a, 2);
         if (tid < NT) {
             float s1 = 1.f, u1 = 1.f;
             if (is16) {
@@ -198,11 +211,13 @@ __global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a
             }
             fence_async_smem();                                 // generic-proxy stores -> visible to the tensor core
             mbar_arrive(&bar_full);
+            if (p == 0) tb_mark(a, 3);
             if (p + 1 < np) load_all(p + 1);                    // the registers are free again
         }
         // the accumulator is complete when the last commit has arrived
         if (lane == 0 && !s_fail && !mbar_wait_bounded(&bar_mma, (np - 1) & 1)) s_fail = 1;
         __syncwarp();
+        tb_mark(a, 4);
     }
     tc_fence_after();
     __syncthreads();
@@ -221,7 +236,9 @@ __global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a
         }
     }
     tc_fence_before();
+    tb_mark(a, 5);
     cluster.sync();
+    tb_mark(a, 6);
     if (!failed) {
         // ---- add the ks partial tiles in rank order, epilogue, store: float4 groups of 4 rows
         float* y = a.y[blockIdx.y] + static_cast<size_t>(n0) * a.ldy;
@@ -278,7 +295,9 @@ __global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a
             }
         }
     }
+    tb_mark(a, 7);
     cluster.sync();          // nobody leaves while a peer still reads its partial tile
+    tb_mark(a, 8);
     if (!failed && a.amax_out[blockIdx.y] != nullptr && tid < nn) {
         const int bits = reinterpret_cast<const int*>(s_omax)[tid];
         if (bits != 0) atomicMax(reinterpret_cast<int*>(a.amax_out[blockIdx.y]) + n0 + tid, bits);
@@ -325,6 +344,8 @@ bool tcb_enabled() {
     static const bool on = [] { const char* e = getenv("RWKVQ_TCB"); return !(e && e[0] == '0'); }();
     return on && g_tcb_force_ks >= 0;          // rwkvq_profiling_tcb_force(-1) switches it off at run time
 }
+bool tcb_forced() { return g_tcb_force_ks > 0;
+}
 
 // Whether the tcgen05 small-batch kernel serves the tensor: sb6 / sym in the layouts the prefill
 // kernel's producer reads (block 32 x 8 and 16 x 16), columns a multiple of 256.
@@ -354,6 +375,7 @@ int launch_gemm_tcb(const rwkvq_qtensor* ts, int n_mats, const void* const* xs, 
         RWKVQ_REQUIRE(epilogue != RWKVQ_EPI_ADD || a.resid[k], RWKVQ_E_NULL, "rwkvq_gemm_tcb: resid is null");
     }
     a.ldx = ldx; a.ldy = ldy; a.n_tokens = N; a.epilogue = epilogue; a.status = status;
+    a.trace = g_batch_trace;
     const int rows = ts[0].rows, cols = ts[0].cols;
     const int nt = N <= 16 ? 16 : N <= 32 ? 32 : 64;
     const int n_groups = (N + nt - 1) / nt;

@@ -629,7 +629,8 @@ extern "C" int rwkvq_gemv_batch(const rwkvq_qtensor* t, const float* x, int N, i
     RWKVQ_REQUIRE(epilogue >= RWKVQ_EPI_NONE && epilogue <= RWKVQ_EPI_ADD, RWKVQ_E_DTYPE, "rwkvq_gemv_batch: epilogue %d", epilogue);
     RWKVQ_REQUIRE(ldx >= t->cols && ldy >= t->rows, RWKVQ_E_SHAPE, "rwkvq_gemv_batch: ldx %lld / ldy %lld", (long long)ldx, (long long)ldy);
     RWKVQ_REQUIRE(x && y, RWKVQ_E_NULL, "rwkvq_gemv_batch: x or y is null");
-    const bool tcb = tcb_enabled() && gemm_tcb_ok(*t) && ldx % 8 == 0;
+    // more than 32 rows: the tcgen05 kernel (measured crossover inside the decode step); fewer: mma.sync
+    const bool tcb = tcb_enabled() && gemm_tcb_ok(*t) && ldx % 8 == 0 && (N > 32 || mma_layout_of(*t) < 0 || tcb_forced());
     RWKVQ_REQUIRE(tcb || mma_layout_of(*t) >= 0, RWKVQ_E_DTYPE,
                   "rwkvq_gemv_batch: needs an sb6 tensor, a sym tensor or per-row int8 with columns in multiples of 128");
     RWKVQ_REQUIRE(aligned(x, 16) && ldx % 4 == 0, RWKVQ_E_ALIGN, "rwkvq_gemv_batch: x rows must be 16-byte aligned");

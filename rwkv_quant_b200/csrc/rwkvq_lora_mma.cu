@@ -18,6 +18,8 @@
 // cluster barrier.
 #include <cooperative_groups.h>
 
+#include <algorithm>
+
 #include "rwkvq_decode_parts.cuh"
 
 namespace cg = cooperative_groups;
@@ -39,6 +41,7 @@ struct LoraMmaArgs {
     int act[4];
     long long ldx, ldy;
     int n_tokens, n_stride, max_rank, n_br, D;
+    int n_groups;            // stream groups of MT * 16; a CTA walks groups blockIdx.y / n_br, + gridDim.y / n_br, ...
 };
 
 __device__ __forceinline__ void lmm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -189,10 +192,10 @@ __global__ void __launch_bounds__(kLmmThreads) lora_down_mma_kernel(const LoraMm
     extern __shared__ __align__(16) unsigned char smem[];
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = blockIdx.x;                                  // K slice = rank in the cluster
-    const int br = static_cast<int>(blockIdx.y) % a.n_br, tg = static_cast<int>(blockIdx.y) / a.n_br;
+    const int br = static_cast<int>(blockIdx.y) % a.n_br, tg0 = static_cast<int>(blockIdx.y) / a.n_br;
+    const int tg_step = static_cast<int>(gridDim.y) / a.n_br;
     const QView& t = a.t1[br];
     const int c0 = blockIdx.z * kLmmRC;
-    const int n0 = tg * MT * 16, nn = min(MT * 16, a.n_tokens - n0);
     const int kc = a.D / kLmmSlices, k0 = rank * kc;
     const int pitch = kc + kLmmPad;
     constexpr int WP = kLmmRC + kLmmPad;                          // pitch of a weight row (32 rank columns)
@@ -208,6 +211,8 @@ __global__ void __launch_bounds__(kLmmThreads) lora_down_mma_kernel(const LoraMm
     __syncthreads();
     if (active) stage_wt_any(t, k0, kc, c0, min(kLmmRC, t.cols - c0), wt, WP);
     pdl_wait();
+    for (int tg = tg0; tg < a.n_groups; tg += tg_step) {          // the staged weights serve every stream group of this CTA
+    const int n0 = tg * MT * 16, nn = min(MT * 16, a.n_tokens - n0);
     if (active) stage_split(a.x[br] + static_cast<size_t>(n0) * a.ldx, a.ldx, nn, MT * 16, k0, kc, xhi, xlo, pitch);
     __syncthreads();
     if (active) {
@@ -250,16 +255,17 @@ __global__ void __launch_bounds__(kLmmThreads) lora_down_mma_kernel(const LoraMm
             a.h[(static_cast<size_t>(br) * a.n_stride + n0 + n) * a.max_rank + c0 + col] = v;
         }
     }
-    cluster.sync();          // nobody leaves while a peer still reads its partial sums
+    cluster.sync();          // nobody overwrites or leaves while a peer still reads its partial sums
+    }
 }
 
 template <int MT>
 __global__ void __launch_bounds__(kLmmThreads) lora_up_mma_kernel(const LoraMmaArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const int br = static_cast<int>(blockIdx.y) % a.n_br, tg = static_cast<int>(blockIdx.y) / a.n_br;
+    const int br = static_cast<int>(blockIdx.y) % a.n_br, tg0 = static_cast<int>(blockIdx.y) / a.n_br;
+    const int tg_step = static_cast<int>(gridDim.y) / a.n_br;
     const QView& t = a.t2[br];
     const int r = t.rows, c0 = blockIdx.x * kLmmUpCols;
-    const int n0 = tg * MT * 16, nn = min(MT * 16, a.n_tokens - n0);
     const int pitch = r + kLmmPad;
     constexpr int WP = kLmmUpCols + kLmmPad;
     __half* hhi = reinterpret_cast<__half*>(smem);
@@ -268,9 +274,12 @@ __global__ void __launch_bounds__(kLmmThreads) lora_up_mma_kernel(const LoraMmaA
     pdl_launch_dependents();
     stage_wt_any(t, 0, r, c0, kLmmUpCols, wt, WP);
     pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+    for (int tg = tg0; tg < a.n_groups; tg += tg_step) {          // the staged weights serve every stream group of this CTA
+    const int n0 = tg * MT * 16, nn = min(MT * 16, a.n_tokens - n0);
+    __syncthreads();                                               // the previous group's operands have been read
     stage_split(a.h + (static_cast<size_t>(br) * a.n_stride + n0) * a.max_rank, a.max_rank, nn, MT * 16, 0, r, hhi, hlo, pitch);
     __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
     float c[MT][2][4];                                            // warp: 8-column tiles 2 warp, 2 warp + 1; all streams
 #pragma unroll
     for (int mi = 0; mi < MT; ++mi)
@@ -286,6 +295,7 @@ __global__ void __launch_bounds__(kLmmThreads) lora_up_mma_kernel(const LoraMmaA
             if (row < nn) *reinterpret_cast<float2*>(y + static_cast<size_t>(row) * a.ldy + col) = make_float2(c[mi][ni][0], c[mi][ni][1]);
             if (row + 8 < nn) *reinterpret_cast<float2*>(y + static_cast<size_t>(row + 8) * a.ldy + col) = make_float2(c[mi][ni][2], c[mi][ni][3]);
         }
+    }
 }
 
 namespace {
@@ -299,7 +309,9 @@ int lmm_attr(K kernel, size_t smem) {
 }
 
 template <int MT>
-int launch_lmm(const LoraMmaArgs& a, int groups, int max_cols, cudaStream_t s) {
+int launch_lmm(LoraMmaArgs& a, int groups, int max_cols, cudaStream_t s) {
+    a.n_groups = groups;
+    const int gy_down = std::min(groups, 4), gy_up = std::min(groups, 8);      // CTAs walk the remaining groups
     const int kc = a.D / kLmmSlices;
     const size_t smem_d = (static_cast<size_t>(2 * MT * 16) * (kc + kLmmPad) + static_cast<size_t>(kc) * (kLmmRC + kLmmPad)) * sizeof(__half) +
                           static_cast<size_t>(MT * 16) * (kLmmRC + 1) * sizeof(float);
@@ -312,7 +324,7 @@ int launch_lmm(const LoraMmaArgs& a, int groups, int max_cols, cudaStream_t s) {
     rc = lmm_attr(lora_up_mma_kernel<MT>, smem_u);
     if (rc) return rc;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(kLmmSlices, a.n_br * groups, (a.max_rank + kLmmRC - 1) / kLmmRC);
+    cfg.gridDim = dim3(kLmmSlices, a.n_br * gy_down, (a.max_rank + kLmmRC - 1) / kLmmRC);
     cfg.blockDim = dim3(kLmmThreads);
     cfg.dynamicSmemBytes = smem_d;
     cfg.stream = s;
@@ -325,7 +337,7 @@ int launch_lmm(const LoraMmaArgs& a, int groups, int max_cols, cudaStream_t s) {
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, lora_down_mma_kernel<MT>, a);
     if (e != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "lora_down_mma: %s", cudaGetErrorString(e));
-    e = launch_pdl(lora_up_mma_kernel<MT>, dim3(max_cols / kLmmUpCols, a.n_br * groups), dim3(kLmmThreads), smem_u, s, a);
+    e = launch_pdl(lora_up_mma_kernel<MT>, dim3(max_cols / kLmmUpCols, a.n_br * gy_up), dim3(kLmmThreads), smem_u, s, a);
     if (e != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "lora_up_mma: %s", cudaGetErrorString(e));
     return RWKVQ_OK;
 }
@@ -364,3 +376,39 @@ int launch_lora_pair_mma(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* co
 }
 
 }  // namespace rwkvq
+
+using namespace rwkvq;
+
+extern "C" size_t rwkvq_lora_pair_workspace_bytes(int N, int max_rank) {
+    if (N < 1 || max_rank < 1) return 0;
+    return static_cast<size_t>(4) * (((N + 63) / 64) * 64) * max_rank * sizeof(float);
+}
+
+extern "C" int rwkvq_lora_pair(const rwkvq_qtensor* t1_host, const rwkvq_qtensor* t2_host, int n_br,
+                               const float* const* xs_host, float* const* ys_host, const int* acts_host, int N, int D,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+    RWKVQ_REQUIRE(t1_host && t2_host && xs_host && ys_host && acts_host && workspace, RWKVQ_E_NULL, "rwkvq_lora_pair: null pointer");
+    RWKVQ_REQUIRE(n_br >= 1 && n_br <= 4 && N >= 1, RWKVQ_E_SHAPE, "rwkvq_lora_pair: %d branches, %d rows", n_br, N);
+    const rwkvq_qtensor* t1[4];
+    const rwkvq_qtensor* t2[4];
+    int max_rank = 0;
+    for (int i = 0; i < n_br; ++i) {
+        int rc = validate_qtensor(&t1_host[i], "rwkvq_lora_pair(down)");
+        if (rc) return rc;
+        rc = validate_qtensor(&t2_host[i], "rwkvq_lora_pair(up)");
+        if (rc) return rc;
+        RWKVQ_REQUIRE(xs_host[i] && ys_host[i], RWKVQ_E_NULL, "rwkvq_lora_pair: x or y of branch %d is null", i);
+        RWKVQ_REQUIRE(aligned(xs_host[i], 16) && aligned(ys_host[i], 16), RWKVQ_E_ALIGN, "rwkvq_lora_pair: rows must be 16-byte aligned");
+        RWKVQ_REQUIRE(acts_host[i] >= 0 && acts_host[i] <= 2, RWKVQ_E_DTYPE, "rwkvq_lora_pair: activation %d", acts_host[i]);
+        t1[i] = &t1_host[i]; t2[i] = &t2_host[i];
+        max_rank = t1_host[i].cols > max_rank ? t1_host[i].cols : max_rank;
+    }
+    RWKVQ_REQUIRE(lora_mma_ok(t1, t2, n_br, D), RWKVQ_E_SHAPE,
+                  "rwkvq_lora_pair: needs D %% 128 == 0, every rank a multiple of 16 up to 512, W1 [D, r], W2 [r, D]");
+    RWKVQ_REQUIRE(aligned(workspace, 16) && workspace_bytes >= rwkvq_lora_pair_workspace_bytes(N, max_rank), RWKVQ_E_LIMIT,
+                  "rwkvq_lora_pair: workspace of %zu bytes, %zu needed (16-byte aligned)", workspace_bytes,
+                  rwkvq_lora_pair_workspace_bytes(N, max_rank));
+    int rc = launch_lora_pair_mma(t1, t2, xs_host, ys_host, acts_host, n_br, N, D, max_rank, static_cast<float*>(workspace),
+                                  ((N + 63) / 64) * 64, static_cast<cudaStream_t>(stream));
+    return rc ? rc : check_launch("rwkvq_lora_pair");
+}

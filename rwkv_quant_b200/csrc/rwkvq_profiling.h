@@ -18,8 +18,9 @@ void rwkvq_profiling_gemm_trace(void* buf512);
 void rwkvq_profiling_batch_trace(void* buf8, int force_ks);
 /* The same override for tensors of one shape only (rows = 0: every shape); 0 switches it off. */
 void rwkvq_profiling_batch_force(int force_ks, int rows, int cols);
-/* Small-batch linear on tcgen05: > 0 forces the cluster size, -1 routes every call to the mma.sync
- * kernel instead, 0 restores the launcher's choice. */
+/* Small-batch linear on tcgen05: > 0 selects it at every batch size and forces the cluster size where
+ * that divides the pass count (1000: every batch size, launcher's cluster size), -1 routes every
+ * call to the mma.sync kernel instead, 0 restores the launcher's choice. */
 void rwkvq_profiling_tcb_force(int force_ks);
 #ifdef __cplusplus
 }

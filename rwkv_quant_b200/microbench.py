@@ -194,8 +194,11 @@ def batch_sweep(recipe="compression", Ns=(8, 64), reps=40, ring=24):
             x = torch.randn(N, cols, device="cuda")
             y = torch.empty(N, rows, device="cuda")
             ws = torch.empty(max(256, lib.rwkvq_gemv_batch_workspace_bytes(N)), dtype=torch.uint8, device="cuda")
-            for ks in (0, 4 | 32, 8 | 32, 2 | 16, 4 | 16, 8 | 16):      # forced cluster size; +16: 256-row groups, +32: 128-row
-                tr(None, ks)
+            tf = lib.rwkvq_profiling_tcb_force
+            tf.restype, tf.argtypes = None, [C.c_int]
+            for ks in (0, 1, 2, 4, 8):                        # forced cluster size of the tcgen05 kernel
+                tr(None, 0)
+                tf(ks)
 
                 def run():
                     for dq in dqs:
@@ -216,15 +219,16 @@ def batch_sweep(recipe="compression", Ns=(8, 64), reps=40, ring=24):
                     g.replay()
                 e1.record(); torch.cuda.synchronize()
                 us = e0.elapsed_time(e1) * 1e3 / reps / n_ring
-                buf = torch.zeros(8, dtype=torch.int64, device="cuda")
-                tr(buf.data_ptr(), ks)
+                buf = torch.zeros(16, dtype=torch.int64, device="cuda")
+                tr(buf.data_ptr(), 0)
                 _lib.check(lib.rwkvq_gemv_batch(C.byref(dqs[0].struct), x.data_ptr(), N, cols, y.data_ptr(), rows, 0, None,
                                                 ws.data_ptr(), ws.numel(), _lib.stream_ptr()), "rwkvq_gemv_batch")
                 torch.cuda.synchronize()
                 tr(None, 0)
+                tf(0)
                 m = buf.cpu().numpy().astype(np.float64)
-                marks = " ".join(f"{(m[i] - m[0]) * 1e-3:.1f}" for i in range(1, 7))
-                print(f"batch {layout}@{bits} [{rows},{cols}] N={N} ks={(str(ks & 15) + ('/256' if ks & 16 else '/128')) if ks else 'auto'}: {us:7.1f} us/launch "
+                marks = " ".join(f"{(m[i] - m[0]) * 1e-3:.1f}" for i in range(1, 9))
+                print(f"batch {layout}@{bits} [{rows},{cols}] N={N} ks={ks or 'auto'}: {us:7.1f} us/launch "
                       f"{dqs[0].nbytes_file() / us / 1e3:7.0f} GB/s   marks(us) {marks}", flush=True)
         del dqs
         torch.cuda.empty_cache()

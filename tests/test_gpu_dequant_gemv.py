@@ -225,7 +225,7 @@ def batch_kernel(request, cuda_lib):
     import ctypes as C
     f = cuda_lib.rwkvq_profiling_tcb_force
     f.restype, f.argtypes = None, [C.c_int]
-    f(-1 if request.param == "mma.sync" else 0)
+    f(-1 if request.param == "mma.sync" else 1000)      # 1000: tcgen05 at every batch size (no valid cluster size: launcher's choice)
     yield request.param
     f(0)
 
