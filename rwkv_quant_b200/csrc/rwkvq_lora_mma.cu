@@ -11,8 +11,8 @@
 //          streams as the 16-row operand and fp32 accumulation, and the 8 slices of a cluster are
 //          added in rank order through distributed shared memory; the activation function is
 //          applied there and h [streams, rank] is written once.
-//   up     grid (128-column tiles of D, branch x stream group): h as an fp16 pair times the
-//          [rank, 128] slice of W2, no split of the short K = rank.
+//   up     grid (32-column tiles of D, branch x stream group): h as an fp16 pair times the
+//          [rank, 32] slice of W2, no split of the short K = rank.
 // Both launches are programmatic-dependent; the weights are staged before the producer's
 // results are awaited.  No wait spins: the only cross-CTA synchronisation is the hardware
 // cluster barrier.
@@ -29,7 +29,7 @@ namespace rwkvq {
 constexpr int kLmmThreads = 256;
 constexpr int kLmmSlices = 8;            // K slices of the down projection = cluster size
 constexpr int kLmmRC = 32;               // rank columns per CTA of the down projection
-constexpr int kLmmUpCols = 128;          // output columns per CTA of the up projection
+constexpr int kLmmUpCols = 32;           // output columns per CTA of the up projection
 constexpr int kLmmPad = 8;               // halves of padding per shared-memory row (bank spread)
 constexpr int kLmmMaxSmem = 200 * 1024;
 
@@ -280,18 +280,23 @@ __global__ void __launch_bounds__(kLmmThreads) lora_up_mma_kernel(const LoraMmaA
     __syncthreads();                                               // the previous group's operands have been read
     stage_split(a.h + (static_cast<size_t>(br) * a.n_stride + n0) * a.max_rank, a.max_rank, nn, MT * 16, 0, r, hhi, hlo, pitch);
     __syncthreads();
-    float c[MT][2][4];                                            // warp: 8-column tiles 2 warp, 2 warp + 1; all streams
+    // warp: 16 of the CTA's columns (warp % NPW) x a share of the stream tiles (warp / NPW)
+    constexpr int NPW = kLmmUpCols / 16, MH = 8 / NPW, MI = MT >= MH ? MT / MH : 1;
+    const int np = warp % NPW, mh = warp / NPW;
+    if (mh * MI >= MT) continue;                                   // few streams: spare warps have no tile (they still meet the barriers above)
+    float c[MI][2][4];
 #pragma unroll
-    for (int mi = 0; mi < MT; ++mi)
+    for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
         for (int ni = 0; ni < 2; ++ni) c[mi][ni][0] = c[mi][ni][1] = c[mi][ni][2] = c[mi][ni][3] = 0.f;
-    for (int kk = 0; kk < r; kk += 16) lmm_step<MT, 2>(c, hhi, hlo, pitch, wt, WP, warp * 16, kk, lane);
-    float* y = a.y[br] + static_cast<size_t>(n0) * a.ldy + c0 + warp * 16;
+    for (int kk = 0; kk < r; kk += 16)
+        lmm_step<MI, 2>(c, hhi + mh * MI * 16 * pitch, hlo + mh * MI * 16 * pitch, pitch, wt, WP, np * 16, kk, lane);
+    float* y = a.y[br] + static_cast<size_t>(n0) * a.ldy + c0 + np * 16;
 #pragma unroll
-    for (int mi = 0; mi < MT; ++mi)
+    for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
         for (int ni = 0; ni < 2; ++ni) {
-            const int row = mi * 16 + g, col = ni * 8 + 2 * tq;
+            const int row = (mh * MI + mi) * 16 + g, col = ni * 8 + 2 * tq;
             if (row < nn) *reinterpret_cast<float2*>(y + static_cast<size_t>(row) * a.ldy + col) = make_float2(c[mi][ni][0], c[mi][ni][1]);
             if (row + 8 < nn) *reinterpret_cast<float2*>(y + static_cast<size_t>(row + 8) * a.ldy + col) = make_float2(c[mi][ni][2], c[mi][ni][3]);
         }
