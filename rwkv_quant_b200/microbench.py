@@ -14,6 +14,7 @@ prints microseconds per launch and GB/s of file-format bytes.
 from __future__ import annotations
 
 import argparse
+import contextlib
 import ctypes as C
 
 import numpy as np
@@ -114,8 +115,9 @@ def tp_chain(model="2.9b", recipe="compression", exchange="p2p", iters=200):
             st.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(st):
                 graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=st):
-                    fn(); fn()
+                with (g.graph_capture() if g is not None else contextlib.nullcontext()):
+                    with torch.cuda.graph(graph, stream=st):
+                        fn(); fn()
             torch.cuda.current_stream().wait_stream(st)
         except Exception as e:                 # noqa: BLE001 - report and fall back
             if rank == 0:
@@ -232,6 +234,18 @@ def batch_sweep(recipe="compression", Ns=(8, 64), reps=40, ring=24):
                       f"{dqs[0].nbytes_file() / us / 1e3:7.0f} GB/s   marks(us) {marks}", flush=True)
         del dqs
         torch.cuda.empty_cache()
+
+
+def batch_once(layout="sb6", bits=4, rows=8192, cols=2048, n=64, launches=3):
+    """A few plain rwkvq_gemv_batch launches, each on its own tensor (cold weights): the target of
+    ncu captures of the small-batch kernels."""
+    lib = _lib.load(check_device=True)
+    dqs = [_tensor(layout, bits, rows, cols, s) for s in range(launches)]
+    x = torch.randn(n, cols, device="cuda")
+    for d in dqs:
+        y = ops.gemv_batch(d, x, check=True)
+    torch.cuda.synchronize()
+    print("ok", float(y.abs().sum()))
 
 
 def batch_tune(layers=4, batch=64, recipe="compression", model="1.5b", reps=20):
@@ -489,6 +503,9 @@ def main():
     dg = sub.add_parser("decode-groups")
     dg.add_argument("--layers", type=int, default=24); dg.add_argument("--batch", type=int, default=64)
     dg.add_argument("--recipe", default="compression"); dg.add_argument("--model", default="1.5b")
+    bo = sub.add_parser("batch-once")
+    bo.add_argument("layout"); bo.add_argument("bits", type=int); bo.add_argument("rows", type=int)
+    bo.add_argument("cols", type=int); bo.add_argument("--n", type=int, default=64); bo.add_argument("--launches", type=int, default=3)
     bt = sub.add_parser("batch-tune")
     bt.add_argument("--layers", type=int, default=4); bt.add_argument("--batch", type=int, default=64)
     bt.add_argument("--recipe", default="compression"); bt.add_argument("--model", default="1.5b")
@@ -517,6 +534,9 @@ def main():
         return
     if a.cmd == "decode-groups":
         decode_groups(a.layers, a.batch, a.recipe, a.model)
+        return
+    if a.cmd == "batch-once":
+        batch_once(a.layout, a.bits, a.rows, a.cols, a.n, a.launches)
         return
     if a.cmd == "batch-tune":
         batch_tune(a.layers, a.batch, a.recipe, a.model)

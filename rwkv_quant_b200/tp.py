@@ -15,6 +15,7 @@ is exercised with the ``gloo`` backend in the CPU tests (``exchange="dist"``).
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
 from typing import List, Optional, Sequence
 
@@ -62,6 +63,7 @@ class TPGroup:
         self._epoch = 0
         self._owned, self._mapped = [], []
         self._sites, self._uses = {}, {}
+        self._cap = None                 # site -> uses inside the capture in progress (graph_capture)
         if exchange == "p2p":
             from . import _lib
             self._lib = _lib.load(check_device=True)
@@ -112,10 +114,33 @@ class TPGroup:
         return self._sites[name]
 
     # ---- the exchange -----------------------------------------------------------------
+    @contextlib.contextmanager
+    def graph_capture(self):
+        """Wrap the capture of a CUDA graph that contains exchanges.  Which of a site's two
+        destination buffers an exchange writes is chosen by a host counter and therefore frozen into
+        the graph: if a graph used a site an odd number of times, every replay would write the same
+        buffer, and a peer one exchange ahead could overwrite it before this rank's consumer has read it
+        (the flags order arrival, not consumption).  On exit this raises unless every site was used an
+        even number of times inside the capture; ``all_gather`` refuses to run under stream capture
+        outside this context."""
+        self._cap = {}
+        try:
+            yield self
+        finally:
+            cap, self._cap = self._cap, None
+        odd = sorted(k for k, v in cap.items() if v % 2)
+        if odd:
+            raise RuntimeError(f"captured graph uses exchange site(s) {odd} an odd number of times: replays would "
+                               f"reuse one destination buffer; issue every site an even number of times per graph")
+
     def all_gather(self, name: str, local: torch.Tensor, n_total: int) -> torch.Tensor:
         """``local`` = this rank's slice (equal sizes on all ranks); returns the gathered
         vector [n_total] (a buffer owned by the group, valid until the site's next-but-one
-        exchange)."""
+        exchange).  Under CUDA-graph capture see ``graph_capture``."""
+        if self._cap is not None:
+            self._cap[name] = self._cap.get(name, 0) + 1
+        elif local.is_cuda and torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("TPGroup.all_gather under stream capture: wrap the capture in TPGroup.graph_capture()")
         tens, tabs = self.site(name, n_total)
         self._epoch += 1
         k = self._uses.get(name, 0) & 1          # the site's two buffers alternate

@@ -66,6 +66,17 @@ for step in range(5):              # the chain of a channel mix, several tokens:
     x = y.clone() / (1.0 + y.abs().max())
 # a returned buffer stays valid for one more exchange at its site, not two
 assert outs[-1].data_ptr() != outs[-2].data_ptr() and outs[-1].data_ptr() == outs[-3].data_ptr()
+# graph-capture bookkeeping: a captured sequence must use every site an even number of times
+with g.graph_capture():
+    for _ in range(2):
+        l2(l1(x, 1), 2, x)
+try:
+    with g.graph_capture():
+        l2(l1(x, 1), 2, x)                 # once: the frozen buffer choice would repeat on every replay
+    raise SystemExit("an odd number of uses of a site inside a capture was accepted")
+except RuntimeError as e:
+    assert "odd number" in str(e), e
+l2(l1(x, 1), 2, x)                         # restores the parity of both sites on every rank
 dist.barrier()
 if rank == 0: print("RANK0_OK")
 dist.destroy_process_group()
