@@ -253,14 +253,16 @@ __global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a
             const int n = i4 / g4, r = (i4 - n * g4) * 4;
             const int row = row0 + r;
             if (row >= t.rows) continue;
-            float4 v[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-                if (k < ks) v[k] = *reinterpret_cast<const float4*>(cluster.map_shared_rank(part, k) + n * RP + r);
             float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int kb = 0; kb < ks; kb += 8) {                // 8 loads in flight, added in rank order
+                float4 v[8];
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
-                if (k < ks) { s.x += v[k].x; s.y += v[k].y; s.z += v[k].z; s.w += v[k].w; }
+                for (int k = 0; k < 8; ++k)
+                    if (kb + k < ks) v[k] = *reinterpret_cast<const float4*>(cluster.map_shared_rank(part, kb + k) + n * RP + r);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    if (kb + k < ks) { s.x += v[k].x; s.y += v[k].y; s.z += v[k].z; s.w += v[k].w; }
+            }
             const size_t o = static_cast<size_t>(n) * a.ldy + row;
             const bool full = vec_io && row + 3 < t.rows;
             if (a.epilogue == RWKVQ_EPI_RELU2) {
@@ -316,6 +318,8 @@ int launch_tcb(TcbArgs& a, int n_mats, int n_groups, int row_tiles, cudaStream_t
     if (dev >= 64 || !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcb_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "rwkvq_gemm_tcb: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        e = cudaFuncSetAttribute(gemm_tcb_kernel<NT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);      // clusters of 16
+        if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "rwkvq_gemm_tcb: cluster size attribute: %s", cudaGetErrorString(e));
         if (dev < 64) configured[dev] = true;
     }
     cudaLaunchConfig_t cfg{};
@@ -391,7 +395,7 @@ int launch_gemm_tcb(const rwkvq_qtensor* ts, int n_mats, const void* const* xs, 
         const double t = waves * (2.5 + 0.9 * (n_sb / c)) + 2.0 + 0.15 * c;
         if (t < best) { best = t; best_ks = c; }
     }
-    if (g_tcb_force_ks > 0 && n_sb % g_tcb_force_ks == 0 && g_tcb_force_ks <= 8) best_ks = g_tcb_force_ks;
+    if (g_tcb_force_ks > 0 && n_sb % g_tcb_force_ks == 0 && g_tcb_force_ks <= 16) best_ks = g_tcb_force_ks;
     a.ks = best_ks;
     a.passes = n_sb / best_ks;
     switch (nt) {

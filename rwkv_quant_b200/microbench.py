@@ -198,7 +198,7 @@ def batch_sweep(recipe="compression", Ns=(8, 64), reps=40, ring=24):
             ws = torch.empty(max(256, lib.rwkvq_gemv_batch_workspace_bytes(N)), dtype=torch.uint8, device="cuda")
             tf = lib.rwkvq_profiling_tcb_force
             tf.restype, tf.argtypes = None, [C.c_int]
-            for ks in (0, 1, 2, 4, 8):                        # forced cluster size of the tcgen05 kernel
+            for ks in (0, 4, 8, 16):                          # forced cluster size of the tcgen05 kernel
                 tr(None, 0)
                 tf(ks)
 
