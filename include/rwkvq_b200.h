@@ -135,6 +135,16 @@ int rwkvq_gemv(const rwkvq_qtensor* t, const void* x, int x_dtype, int N, int64_
                float* y, int64_t ldy, int epilogue, const float* resid, void* stream);
 
 /*
+ * Sparse outlier overrides of a per-row tensor, applied to a product over its packed codes:
+ *   y[n, r] = epi( y[n, r] + sum_{j in row r} delta[j] * x[n, cols[j]] ),  delta = override - quantized value.
+ * Stands behind the CSR tail of the reference's per-row kernels (backends/metal/quant_linear_v2.py:47-55,
+ * CSR build quant_linear.py:17; formats/codec.py:279-292 defines the override).  row_ptr [rows + 1], cols and
+ * delta [n_overrides] sorted by (row, column); call rwkvq_gemv with RWKVQ_EPI_NONE first, the epilogue belongs here.
+ */
+int rwkvq_outlier_tail(const int32_t* row_ptr, const int32_t* cols, const float* delta, int rows, const void* x,
+                       int x_dtype, int N, int64_t ldx, float* y, int64_t ldy, int epilogue, const float* resid, void* stream);
+
+/*
  * The same product for a SMALL BATCH of right-hand sides (decode streams, short verify runs)
  * with every packed weight byte read once for the whole batch.  Stands behind the multi-column
  * GEMV kernels of the reference, which decode each weight once for up to 4 columns and loop

@@ -109,8 +109,10 @@ class DeviceQT:
         order = order[last]
         rows, cols, vals = oi[order, 0], oi[order, 1], vals[order]
         wq = dequant(self.bufs, self.meta, torch.float32, False)[rows, cols]
-        uniq, counts = torch.unique_consecutive(rows, return_counts=True)
-        self.outliers = (rows, cols, vals, vals - wq, uniq, counts)
+        # CSR over the rows for the tail kernel: row_ptr [rows + 1], columns and deltas in (row, column) order
+        row_ptr = torch.zeros(self.rows + 1, dtype=torch.int32, device=dev)
+        row_ptr[1:] = torch.cumsum(torch.bincount(rows, minlength=self.rows), 0).to(torch.int32)
+        self.outliers = (rows, cols, vals, (vals - wq).contiguous(), row_ptr, cols.to(torch.int32).contiguous())
 
     def dequant(self, out_dtype: torch.dtype = torch.float32, round_bf16: bool = False) -> torch.Tensor:
         """Dense [rows, cols] with the outlier overrides applied (fp32: the codec's bits)."""
@@ -121,18 +123,17 @@ class DeviceQT:
         return w
 
     def gemv(self, x: torch.Tensor, epilogue: int = 0, resid: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """x [N, cols] -> [N, rows]; tensors with outliers add the sparse correction (summed per
-        row in column order: deterministic) before the epilogue."""
+        """x [N, cols] -> [N, rows]; tensors with outliers: the product over the packed codes, then the
+        CSR tail kernel adds every row's override terms in column order (deterministic) and applies the
+        epilogue (the reference's per-row kernels carry the same tail, quant_linear_v2.py:47-55)."""
         if self.outliers is None:
             return gemv(self.bufs, self.meta, x, epilogue, resid)
-        rows, cols, _, delta, uniq, counts = self.outliers
+        delta, row_ptr, cols32 = self.outliers[3:6]
         y = gemv(self.bufs, self.meta, x, 0, None)
-        contrib = (x.float()[:, cols] * delta).t().contiguous()               # [n_outliers, N]
-        y[:, uniq] += torch.segment_reduce(contrib, "sum", lengths=counts, axis=0).t()
-        if epilogue == _lib.EPI_RELU2:
-            y = torch.relu(y) ** 2
-        elif epilogue == _lib.EPI_ADD:
-            y = y + resid
+        _lib.check(_lib.load().rwkvq_outlier_tail(row_ptr.data_ptr(), cols32.data_ptr(), delta.data_ptr(), self.rows,
+                                                  x.data_ptr(), _lib.DTYPE_CODE[x.dtype], x.shape[0], x.stride(0),
+                                                  y.data_ptr(), y.stride(0), epilogue, _lib.ptr(resid), _lib.stream_ptr()),
+                   "rwkvq_outlier_tail")
         return y
 
     def densified(self) -> "DeviceQT":

@@ -393,6 +393,33 @@ static int check_x_vector_loads(const void* x, int x_dtype, long long ldx, const
 
 using namespace rwkvq;
 
+namespace rwkvq {
+// Sparse outlier overrides of a per-row tensor (formats/codec.py:279-292: W[r, c] = value after the
+// dequantisation; the Metal kernel's CSR tail, backends/metal/quant_linear_v2.py:47-55): the product over
+// the packed codes is short of sum_j (value_j - quantized_j) x[n, c_j] for the overrides j of row r.
+// One thread per (right-hand side, row) adds its row's terms in column order (deterministic) and
+// applies the epilogue, which the product launch therefore leaves out.
+__global__ void __launch_bounds__(256) outlier_tail_kernel(const int* __restrict__ row_ptr, const int* __restrict__ cols,
+                                                           const float* __restrict__ delta, const void* __restrict__ x,
+                                                           int x_dtype, long long ldx, float* __restrict__ y, long long ldy,
+                                                           const float* __restrict__ resid, int epilogue, int rows, int N) {
+    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (i >= static_cast<long long>(rows) * N) return;
+    const int n = static_cast<int>(i / rows), r = static_cast<int>(i - static_cast<long long>(n) * rows);
+    float v = y[n * ldy + r];
+    for (int j = row_ptr[r]; j < row_ptr[r + 1]; ++j) {
+        const long long xi = n * ldx + cols[j];
+        const float xv = x_dtype == RWKVQ_F32 ? static_cast<const float*>(x)[xi]
+                       : x_dtype == RWKVQ_F16 ? __half2float(static_cast<const __half*>(x)[xi])
+                                              : __bfloat162float(static_cast<const __nv_bfloat16*>(x)[xi]);
+        v = fmaf(xv, delta[j], v);
+    }
+    if (epilogue == RWKVQ_EPI_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
+    else if (epilogue == RWKVQ_EPI_ADD) v = __fadd_rn(v, resid[n * ldy + r]);
+    y[n * ldy + r] = v;
+}
+}  // namespace rwkvq
+
 extern "C" {
 
 int rwkvq_gemv(const rwkvq_qtensor* t, const void* x, int x_dtype, int N, int64_t ldx, float* y,
@@ -483,6 +510,19 @@ int rwkvq_gemv_fused(const rwkvq_qtensor* ts, int K, const void* x, int x_dtype,
     // same rows-per-warp as the single-matrix launch: identical summation order
     dispatch_kind<1>(ck, a, ts[0].rows, K, rows_per_warp(ts[0], 1), static_cast<cudaStream_t>(stream));
     return check_launch("rwkvq_gemv_fused");
+}
+
+int rwkvq_outlier_tail(const int32_t* row_ptr, const int32_t* cols, const float* delta, int rows, const void* x,
+                       int x_dtype, int N, int64_t ldx, float* y, int64_t ldy, int epilogue, const float* resid, void* stream) {
+    RWKVQ_REQUIRE(row_ptr && cols && delta && x && y, RWKVQ_E_NULL, "rwkvq_outlier_tail: null pointer");
+    RWKVQ_REQUIRE(rows >= 1 && N >= 1 && ldy >= rows, RWKVQ_E_SHAPE, "rwkvq_outlier_tail: rows %d, N %d, ldy %lld", rows, N, (long long)ldy);
+    RWKVQ_REQUIRE(x_dtype == RWKVQ_F32 || x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_DTYPE, "rwkvq_outlier_tail: x_dtype %d", x_dtype);
+    RWKVQ_REQUIRE(epilogue >= RWKVQ_EPI_NONE && epilogue <= RWKVQ_EPI_ADD, RWKVQ_E_DTYPE, "rwkvq_outlier_tail: epilogue %d", epilogue);
+    RWKVQ_REQUIRE(epilogue != RWKVQ_EPI_ADD || resid != nullptr, RWKVQ_E_NULL, "rwkvq_outlier_tail: resid is null");
+    const long long total = static_cast<long long>(rows) * N;
+    rwkvq::outlier_tail_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        row_ptr, cols, delta, x, x_dtype, ldx, y, ldy, resid, epilogue, rows, N);
+    return check_launch("rwkvq_outlier_tail");
 }
 
 }  // extern "C"
