@@ -402,3 +402,49 @@ def test_decode_batches_match_oracle(cuda_lib, preset, B):
         assert float(np.abs(w.cpu().numpy() - rw).max()) <= 1e-3 * max(1.0, np.abs(rw).max())
         assert relmax(ts.reshape(B, -1).cpu().numpy(), rts) <= 1e-3
         assert relmax(cs.reshape(B, -1).cpu().numpy(), rcs) <= 1e-3
+
+
+@pytest.mark.parametrize("D,n", [(256, 3), (256, 17), (2048, 64), (2048, 130), (2560, 700)])
+def test_lora_pair_matches_numpy(cuda_lib, D, n):
+    """rwkvq_lora_pair through the C ABI: four branches (asym@6 w / a / v, per-row int8 g; tanh / none /
+    sigmoid / none) in two launches against y = act(x @ W1) @ W2 in float64 with the loader's weight
+    precision fp16(bf16(.)) (quant_model.py:128-154, 462-526), for one, two and four 16-row tiles, several
+    64-row groups and a ragged last group.  rel <= 2e-5: fp16-pair operands, fp32 accumulation."""
+    from rwkv_quant_b200 import synth
+    from rwkv_quant_b200.backends.cuda import ops
+    ranks = synth.lora_ranks(D)
+    g = torch.Generator().manual_seed(D + n)
+    pairs, acts, refs = [], [1, 0, 2, 0], []
+    for br, fn, bits in (("w", synth.quant_asym, 6), ("a", synth.quant_asym, 6), ("g", synth.quant_rtn, 8), ("v", synth.quant_asym, 6)):
+        r = ranks[br]
+        q1 = fn(br + "1", "l", torch.randn(D, r, generator=g) * 0.05, bits)
+        q2 = fn(br + "2", "l", torch.randn(r, D, generator=g) * 0.05, bits)
+        d1, d2 = ops.DeviceQT(q1), ops.DeviceQT(q2)
+        pairs.append((d1, d2))
+        refs.append(tuple(d.dequant(torch.float32, True).half().double().cpu().numpy() for d in (d1, d2)))
+    assert ops.lora_pair_ok(pairs, D)
+    xs = [torch.randn(n, D, generator=g).cuda() for _ in range(4)]
+    ys = ops.lora_pair(pairs, xs, acts)
+    for i, (w1, w2) in enumerate(refs):
+        h = xs[i].double().cpu().numpy() @ w1
+        h = np.tanh(h) if acts[i] == 1 else 1 / (1 + np.exp(-h)) if acts[i] == 2 else h
+        want = h @ w2
+        assert ys[i].shape == (n, D) and relmax(ys[i].cpu().numpy(), want) <= 2e-5, (i, relmax(ys[i].cpu().numpy(), want))
+    assert all(torch.equal(a, b) for a, b in zip(ys, ops.lora_pair(pairs, xs, acts))), "two calls differ"
+    # three branches (layer 0 has no value-residual branch)
+    ys3 = ops.lora_pair(pairs[:3], xs[:3], acts[:3])
+    assert all(torch.equal(a, b) for a, b in zip(ys3, ys[:3]))
+
+
+def test_seq_embed_and_layer_norm_kernels(cuda_lib):
+    """Embedding gather + LayerNorm 0 and the final LayerNorm of the sequence path against torch on
+    the loader-precision table."""
+    import torch.nn.functional as F
+    model, _, _ = _load("compression")
+    idx = torch.from_numpy(np.random.default_rng(2).integers(0, model.vocab_size, (3, 19))).cuda()
+    from rwkv_quant_b200.backends.cuda import ops
+    got = ops.seq_embed_ln0(model.emb, idx, *model.ln0)
+    want = F.layer_norm(model._embed(idx), (model.n_embd,), *model.ln0)
+    assert got.shape == want.shape and (got - want).abs().max().item() <= 2e-6 * want.abs().max().item() + 1e-6
+    x = torch.randn(7, 5, model.n_embd, device="cuda") * 3 + 1
+    assert (ops.seq_layer_norm(x, *model.ln_out) - F.layer_norm(x, (model.n_embd,), *model.ln_out)).abs().max().item() <= 1e-5
