@@ -229,11 +229,11 @@ def linear_phase(model, B, steps, warmup):
 NCU_GEMV_PHASE_DRAM_BYTES_B1 = 828225280 + 342272
 
 
-def time_decode(model, B, prompt, steps, warmup, sync_all, clock_index=None):
+def time_decode(model, B, prompt, steps, warmup, sync_all, clock_index=None, groups=None):
     """Device-resident loop (one graph replay per step, argmax fed back on the device) and the
     end-to-end loop (pinned host token ids in, argmax out, every step): (sec, sec_e2e, clocks, launches)."""
     import torch
-    dec = model.decoder(B, use_graph=True, self_feed=True)
+    dec = model.decoder(B, use_graph=True, self_feed=True, groups=groups)
     dec.tokens.copy_(prompt)
     for _ in range(warmup):
         dec.step()
@@ -248,7 +248,7 @@ def time_decode(model, B, prompt, steps, warmup, sync_all, clock_index=None):
     sync_all()
     t_dev = e0.elapsed_time(e1) * 1e-3
     del dec
-    dec2 = model.decoder(B, use_graph=True, self_feed=False)
+    dec2 = model.decoder(B, use_graph=True, self_feed=False, groups=groups)
     host_tok = torch.empty(B, dtype=torch.long).pin_memory()
     host_tok.copy_(prompt.cpu())
     host_out = torch.empty(B, dtype=torch.long).pin_memory()
@@ -324,8 +324,8 @@ def prefill_block(dev, model_name, peaks, peak_kind):
 def run_ours(a, rank, world, local_rank):
     import numpy as np
     import torch
-    from rwkv_quant_b200 import dp, synth
-    from rwkv_quant_b200.backends.cuda import QuantRWKV7
+    from rwkv_quant_b200 import _lib, dp, synth
+    from rwkv_quant_b200.backends.cuda import QuantRWKV7, ops
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -349,12 +349,29 @@ def run_ours(a, rank, world, local_rank):
 
     max_over_ranks = lambda sec: dp.max_over_ranks(sec, dev)
     prompts = torch.from_numpy(np.random.default_rng(0).integers(1, 60000, (a.streams,))).to(dev)
+    model_groups = model.decode_groups(B)
     t_dev, t_e2e, clocks, launches = time_decode(model, B, prompts[lo:hi], a.steps, a.warmup, sync_all, local_rank)
     t_dev, t_e2e = max_over_ranks(t_dev), max_over_ranks(t_e2e)
     g_bytes, g_launches, g_sec = linear_phase(model, B, min(a.steps, 32), a.warmup)
     step_bytes = w_bytes + state_bytes(model, B)
 
     extras = {}
+    fast_env = ops.batch_fast()
+    if not a.no_extras and world == 1 and B > 2 and not fast_env:
+        # the same step on single fp16 operands (what RWKVQ_BATCH_FAST=1 selects): faster, but its logits
+        # drift to 2-3e-3 of the fp32 oracle over 24 layers, so it is not the default and not `value`
+        lib = _lib.load()
+        sw = lib.rwkvq_profiling_batch_fast            # rwkvq_profiling.h: not part of the C ABI
+        sw.restype, sw.argtypes = None, [C.c_int]
+        sw(1)
+        try:
+            tf, tf_e2e, _, lf = time_decode(model, B, prompts[lo:hi], a.steps, a.warmup, sync_all, local_rank, groups=1)
+        finally:
+            sw(-1)
+        extras["fast_mode"] = {"value": a.streams * a.steps / tf, "unit": "tok/s", "ms_per_step": tf / a.steps * 1e3,
+                               "e2e": {"value": a.streams * a.steps / tf_e2e, "unit": "tok/s"}, "gpu_launches": lf,
+                               "what": "RWKVQ_BATCH_FAST=1: small-batch linears on single fp16 operands (tcgen05 kernel "
+                                       "above 32 streams); logits within 1e-3 of the oracle on 2 layers, 2-3e-3 on 24"}
     if not a.no_extras and world == 1:
         # the single-stream configuration (the one the reference's tg128 number is quoted on)
         tb, tb_e2e, clk1, l1 = time_decode(model, 1, prompts[:1], a.steps, a.warmup, sync_all, local_rank)
@@ -407,14 +424,18 @@ def run_ours(a, rank, world, local_rank):
         "metric": "decode_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": world,
         "steps": a.steps, "warmup": a.warmup, "ms_per_step": sec_step * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "f16 operands (weights fp16(q*s+m), activations scaled per token) -> f32 accumulate"
-                 if B > 2 else "u8 codes x s8 activation digits -> s32, block scales and accumulation f32",
+        "dtype": ("f16 operands (weights fp16(q*s+m), activations scaled per token) -> f32 accumulate" if fast_env else
+                  "f16 operand pairs (weights q*s as product + rounding error, mins on block sums; activations hi + lo, "
+                  "scaled per token) -> f32 accumulate") if B > 2
+                 else "u8 codes x s8 activation digits -> s32, block scales and accumulation f32",
         "data": "synthetic",
         "config": {"workload": f"rwkv7-{a.model} {a.recipe} random-init, greedy decode tg{a.steps}, {a.streams} concurrent "
                                f"streams split over {world} GPU(s) ({B} per GPU), full replica per GPU",
                    "streams": a.streams, "streams_per_gpu": B, "weight_bytes_per_step": w_bytes,
                    "state_bytes_per_step": step_bytes - w_bytes,
-                   "decoder": "CUDA-graph replay of the launch chain",
+                   "decoder": "CUDA-graph replay of the launch chain" +
+                              (f", {model_groups} stream groups side by side" if model_groups > 1 else ""),
+                   "precision": "RWKVQ_BATCH_FAST=1 (single fp16 operands)" if fast_env else "default (two-term operands)",
                    "l2": "weights per step (>= 800 MB) exceed the 126 MB L2; no flush needed",
                    "vs_baseline_ref": "no published number for the 64-stream metric; b1.vs_baseline divides by the "
                                       "reference's 75.3 tok/s at batch 1 on an Apple M4"},
@@ -428,7 +449,8 @@ def run_ours(a, rank, world, local_rank):
                      "bytes_per_step": step_bytes, "us_per_step": sec_step * 1e6},
         "linear_phase": {"bound": "hbm", "achieved": g_bytes / g_sec / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": g_bytes / g_sec / 1e9 / peak, "traffic": None,
-                         "kernel": (f"gemv_batch_kernel, the {g_launches} quantized-linear launches of one step at "
+                         "kernel": (f"row_amax_kernel + {'gemm_tcb_kernel' if (fast_env and B > 32) else 'gemv_batch_kernel'}, "
+                                    f"the {g_launches} launches of the quantized linears of one step at "
                                     f"{B} streams" if B > 2 else f"gemv_mma_kernel, {g_launches} launches"),
                          "bytes_per_replay": g_bytes, "us_per_replay": g_sec * 1e6},
     }

@@ -8,6 +8,7 @@ current CUDA stream.  Nothing here computes on the CPU.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import List, Optional, Sequence
 
 import torch
@@ -254,6 +255,13 @@ def gemv_t(bufs: Sequence[torch.Tensor], meta: Sequence[int], x: torch.Tensor, a
 @gemv_t.register_fake
 def _(bufs, meta, x, act, round_w):
     return torch.empty((x.shape[0], meta[3]), dtype=torch.float32, device=x.device)
+
+
+def batch_fast() -> bool:
+    """RWKVQ_BATCH_FAST=1 in the environment: the small-batch linears use single fp16 operands
+    (and the tcgen05 kernel above 32 rows) instead of the default two-term kernel.  The library
+    reads the variable once, at its first small-batch call."""
+    return os.environ.get("RWKVQ_BATCH_FAST", "")[:1] == "1"
 
 
 def has_batch_layout(dq: "DeviceQT") -> bool:

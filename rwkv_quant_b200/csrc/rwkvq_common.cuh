@@ -263,6 +263,7 @@ int launch_gemv_batch(const rwkvq_qtensor* ts, int n_mats, const void* const* xs
 // The same product on the tcgen05 tensor cores (rwkvq_gemm_tcb.cu; sb6 / sym tensors, gemm_tcb_ok);
 // status: device word that receives RWKVQ_E_TIMEOUT if a bounded pipeline wait ran out.
 bool gemm_tcb_ok(const rwkvq_qtensor& t);
+bool batch_fast();        // RWKVQ_BATCH_FAST=1: single fp16 operands in the small-batch linears (faster, ~5e-4 per linear)
 bool tcb_enabled();
 bool tcb_forced();        // a profiling override asks for the tcgen05 kernel at every batch size
 int launch_gemm_tcb(const rwkvq_qtensor* ts, int n_mats, const void* const* xs, bool half_in, const float* const* scales,

@@ -91,7 +91,9 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
                                                                   float* __restrict__ zero_a, float* __restrict__ zero_b) {
     // x16_out (optional) [max(NMIX, 1)][B][D] with unscale_out [max(NMIX, 1)][B]: the rows selected by
     // x16_mask also as fp16(out * 2^s), s chosen from the row's max so that no value leaves the fp16
-    // range, and 2^-s: the form the small-batch linear reads (half the bytes, no conversion there);
+    // range, and 2^-s: the form the single-term small-batch linear reads (half the bytes, no
+    // conversion there).  With unscale_out alone, max|out| of the selected rows goes there instead
+    // (what the two-term small-batch linear wants beside the fp32 rows);
     // zero_a / zero_b (optional) [B]: slots later kernels of the layer merge their own row maxima
     // into, cleared here for stream b
     constexpr int NM = NMIX > 0 ? NMIX : 1;
@@ -149,7 +151,7 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
             mx[m < NM ? m : 0] = fmaxf(mx[m < NM ? m : 0], fabsf(o));
         }
     }
-    if (x16_out != nullptr) {
+    if (unscale_out != nullptr) {
         __shared__ float sc_m[NM];
 #pragma unroll
         for (int m = 0; m < NM; ++m) {
@@ -161,6 +163,10 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
         if (threadIdx.x < NM) {
             float r = 0.f;
             for (int w = 0; w < kRowThreads / 32; ++w) r = fmaxf(r, redm[w][threadIdx.x]);
+            if (x16_out == nullptr) {
+                if ((x16_mask >> threadIdx.x) & 1) unscale_out[threadIdx.x * B + b] = r;
+                return;
+            }
             // |x| * 2^(14 - e) <= 2^14 with max|x| <= 2^e; a non-finite row keeps scale 1 and propagates
             float s1 = 1.f, u1 = 1.f;
             if (r > 0.f && r < INFINITY) {
@@ -173,6 +179,7 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
             sc_m[threadIdx.x] = s1;
             if ((x16_mask >> threadIdx.x) & 1) unscale_out[threadIdx.x * B + b] = u1;
         }
+        if (x16_out == nullptr) return;
         __syncthreads();
 #pragma unroll
         for (int i = 0; i < kRowPer; ++i) {
@@ -535,7 +542,7 @@ inline bool batch_path(int B) { return B > 2 && B <= kBatchMax; }
 // Which small-batch kernel: measured on B200 (1.5B, whole decode step) the tcgen05 form wins from 33
 // streams on (64 streams: 3.77 against 4.43 ms per step) and loses below (32: 2.87 / 2.68 ms, 8: 2.42 / 2.01 ms):
 // its pass (dependent weight loads -> conversion -> MMA) is longer than a warp-iteration of the mma.sync form
-inline bool tcb_pays(int B) { return tcb_enabled() && B > 32; }
+inline bool tcb_pays(int B) { return batch_fast() && tcb_enabled() && B > 32; }
 
 
 struct Workspace {
@@ -744,11 +751,12 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         // ---- time mix
         // the row maxima feed the small-batch linears: slots 0-5 the six mix rows, 6 og, 7 xk, 8 hffn, 9 xo
         const bool bp = batch_path(B);
+        const bool h16 = bp && batch_fast();          // fp16 rows for the single-term kernels; else fp32 rows and their maxima
         float* am = bp ? w.amax : nullptr;
         float *am_og = bp ? w.amax + 6 * B : nullptr, *am_xk = bp ? w.amax + 7 * B : nullptr;
         float *am_h = bp ? w.amax + 8 * B : nullptr;
         launch_pdl(ln_shift_mix_kernel<6>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln1_w, L.ln1_b, tshift[l], L.x_mix, w.xs, B, D,
-                   bp ? w.xs16 : static_cast<__half*>(nullptr), am, 0b001101, am_og, am_h);      // r, k, v rows also as fp16
+                   h16 ? w.xs16 : static_cast<__half*>(nullptr), am, 0b001101, am_og, am_h);      // scales of the r, k, v rows
         float *xr = w.xs, *xw = w.xs + BD, *xk = w.xs + 2 * BD, *xv = w.xs + 3 * BD, *xa = w.xs + 4 * BD,
               *xg = w.xs + 5 * BD;
         float *r = w.rkv, *k = w.rkv + BD, *v = w.rkv + 2 * BD;
@@ -779,21 +787,22 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
             }
             const rwkvq_qtensor three[3] = {L.Wr, L.Wk, L.Wv};
             const void* x3[3] = {w.xs16, w.xs16 + 2 * BD, w.xs16 + 3 * BD};
+            if (!h16) { x3[0] = xr; x3[1] = xk; x3[2] = xv; }
             const float* a3[3] = {am, am + 2 * B, am + 3 * B};
             float* y3[3] = {r, k, v};
             if (tcb_pays(B) && gemm_tcb_ok(L.Wr))
-                rc = launch_gemm_tcb(three, 3, x3, true, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, w.status, s);
+                rc = launch_gemm_tcb(three, 3, x3, h16, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, w.status, s);
             else
-                rc = launch_gemv_batch(three, 3, x3, true, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, s);
+                rc = launch_gemv_batch(three, 3, x3, h16, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, s);
             if (rc) return rc;
         } else {
-            rc = linear(&L.Wr, xr, B, D, r, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream, bp ? w.xs16 : nullptr, am, nullptr, w.status);
+            rc = linear(&L.Wr, xr, B, D, r, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream, h16 ? w.xs16 : nullptr, am, nullptr, w.status);
             if (rc) return rc;
             rc = linear(&L.Wk, xk, B, D, k, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream,
-                        bp ? w.xs16 + 2 * BD : nullptr, bp ? am + 2 * B : nullptr, nullptr, w.status);
+                        h16 ? w.xs16 + 2 * BD : nullptr, bp ? am + 2 * B : nullptr, nullptr, w.status);
             if (rc) return rc;
             rc = linear(&L.Wv, xv, B, D, v, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream,
-                        bp ? w.xs16 + 3 * BD : nullptr, bp ? am + 3 * B : nullptr, nullptr, w.status);
+                        h16 ? w.xs16 + 3 * BD : nullptr, bp ? am + 3 * B : nullptr, nullptr, w.status);
             if (rc) return rc;
         }
         float *yw = w.yl, *ya = w.yl + BD, *yv = w.yl + 2 * BD, *yg = w.yl + 3 * BD;
@@ -817,8 +826,8 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         if (rc) return rc;
         // ---- channel mix
         launch_pdl(ln_shift_mix_kernel<1>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln2_w, L.ln2_b, cshift[l], L.ffn_x_k, w.xk, B, D,
-                   bp ? w.xk16 : static_cast<__half*>(nullptr), am_xk, 1, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
-        rc = linear(&L.Wfk, w.xk, B, D, w.hffn, F, RWKVQ_EPI_RELU2, nullptr, w.gscratch, w.gemm_ws, stream, bp ? w.xk16 : nullptr,
+                   h16 ? w.xk16 : static_cast<__half*>(nullptr), am_xk, 1, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
+        rc = linear(&L.Wfk, w.xk, B, D, w.hffn, F, RWKVQ_EPI_RELU2, nullptr, w.gscratch, w.gemm_ws, stream, h16 ? w.xk16 : nullptr,
                     am_xk, am_h, w.status);
         if (rc) return rc;
         rc = linear(&L.Wfv, w.hffn, B, F, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, w.gemm_ws, stream, nullptr, am_h, nullptr, w.status);
@@ -826,8 +835,8 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
     }
     float* am_xo = batch_path(B) ? w.amax + 9 * B : nullptr;
     launch_pdl(ln_shift_mix_kernel<0>, dim3(B), dim3(kRowThreads), 0, s, w.x, m->lnout_w, m->lnout_b, static_cast<float*>(nullptr), static_cast<const float*>(nullptr), w.xo, B, D,
-               am_xo ? w.xo16 : static_cast<__half*>(nullptr), am_xo, 1, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
-    rc = linear(&m->head, w.xo, B, D, lg, V, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream, am_xo ? w.xo16 : nullptr, am_xo, nullptr, w.status);
+               (am_xo && batch_fast()) ? w.xo16 : static_cast<__half*>(nullptr), am_xo, 1, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
+    rc = linear(&m->head, w.xo, B, D, lg, V, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream, (am_xo && batch_fast()) ? w.xo16 : nullptr, am_xo, nullptr, w.status);
     if (rc) return rc;
     if (next_tokens) {
         float* pv = w.argv;

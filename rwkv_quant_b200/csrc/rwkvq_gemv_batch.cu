@@ -35,6 +35,7 @@
 #include <cooperative_groups.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "rwkvq_gemv_mma.cuh"
 
@@ -118,6 +119,23 @@ __device__ __forceinline__ void cvt4(uint32_t w, __half2 bias, __half2 s2, __hal
     hi = *reinterpret_cast<const uint32_t*>(&w23);
 }
 
+// Four codes times their block scale as TWO fp16 terms per weight: p = fp16(q*s) and the rounding
+// error of that product, which a fused multiply-add recovers exactly (q*s has at most 19
+// significant bits, p keeps the top 11).  p + e = q*s up to the fp16 subnormal quantum (6e-8
+// absolute).  The block min is not folded in: it multiplies the block's activation sum instead.
+__device__ __forceinline__ void cvt4x(uint32_t w, __half2 bias, __half2 s2, uint32_t& p01, uint32_t& p23, uint32_t& e01,
+                                      uint32_t& e23) {
+    const uint32_t b01 = __byte_perm(w, 0x64646464u, 0x4140), b23 = __byte_perm(w, 0x64646464u, 0x4342);
+    const __half2 q01 = __hsub2(*reinterpret_cast<const __half2*>(&b01), bias);
+    const __half2 q23 = __hsub2(*reinterpret_cast<const __half2*>(&b23), bias);
+    const __half2 w01 = __hmul2(q01, s2), w23 = __hmul2(q23, s2);
+    const __half2 r01 = __hfma2(q01, s2, __hneg2(w01)), r23 = __hfma2(q23, s2, __hneg2(w23));
+    p01 = *reinterpret_cast<const uint32_t*>(&w01);
+    p23 = *reinterpret_cast<const uint32_t*>(&w23);
+    e01 = *reinterpret_cast<const uint32_t*>(&r01);
+    e23 = *reinterpret_cast<const uint32_t*>(&r23);
+}
+
 // Shared-memory order of the staged activations.  An iteration covers KI columns = 8 blocks;
 // thread t of a quad owns blocks 2t + h.  MMA step s = ((h * NJ) + j) * 2 + half takes, from
 // every quad lane, the 4 weights at offset koff(j, half) of its block, so element
@@ -130,13 +148,23 @@ template <int L> struct BtGeo {
 
 
 
-template <int L, int NT>      // NT: 8-token tiles of the MMA N dimension
+// EX: both operands as two fp16 terms (x: hi + lo of the scaled fp32 value; W: q*s as product and
+// rounding error, cvt4x) and three MMAs per step (hi*hi + lo*hi + hi*lo); the block mins, fp16
+// values by the codec's definition, multiply the per-block sums of the activations in one more
+// pair of MMAs per iteration (k = the 8 blocks, which a thread holds in exactly the fragment order
+// it decoded them).  That leaves the fp32 accumulation as the only rounding: the result agrees
+// with an fp32 dequantise-and-multiply to ~1e-6 instead of ~5e-4.  The activations are fp32 rows
+// with their max, scaled to at most 2^9 so that a block sum stays inside the fp16 range; the hi and
+// lo halves of a lane's four activations sit side by side (one 128-bit load per MMA triple).
+template <int L, int NT, bool EX>      // NT: 8-token tiles of the MMA N dimension
 __global__ void __launch_bounds__(kBtThreads, 2) gemv_batch_kernel(const BatchArgs a) {
     using G = Geo<L>;
     using BG = BtGeo<L>;
     constexpr int N8 = NT * 8;
-    constexpr int SP = N8 * 32 + kBtStepPad;          // bytes per MMA step
+    constexpr int SP = N8 * 32 * (EX ? 2 : 1) + kBtStepPad;          // bytes per MMA step
     constexpr bool SB6 = L <= ML_SB6_6;
+    constexpr int SUMB = (EX && SB6) ? N8 * 32 : 0;   // per iteration: the 8 block sums of every token, 8 hi then 8 lo halves
+    constexpr int ITB = BG::STEPS * SP + SUMB;        // bytes per staged iteration
     extern __shared__ __align__(16) unsigned char smem[];
     cg::cluster_group cluster = cg::this_cluster();
 
@@ -195,8 +223,8 @@ __global__ void __launch_bounds__(kBtThreads, 2) gemv_batch_kernel(const BatchAr
                 int e = 0;
                 frexpf(am, &e);
                 e = max(-100, e);                       // 2^(14 - e) must stay finite
-                s1 = ldexpf(1.f, 14 - e);
-                u1 = ldexpf(1.f, e - 14);
+                s1 = ldexpf(1.f, (EX ? 9 : 14) - e);
+                u1 = ldexpf(1.f, e - (EX ? 9 : 14));
             }
         }
         sc[n] = s1;
@@ -211,8 +239,8 @@ __global__ void __launch_bounds__(kBtThreads, 2) gemv_batch_kernel(const BatchAr
         const int blk = rem / G::BLK, off = rem % G::BLK;
         const int tt = blk >> 1, h = blk & 1;
         const int half = SB6 ? (off >> 4) : ((off >> 2) & 1), j = SB6 ? ((off >> 2) & 3) : (off >> 3);
-        const int step = it_l * BG::STEPS + ((h * BG::NJ) + j) * 2 + half;
-        return xs + static_cast<size_t>(step) * SP + n * 32 + tt * 8;
+        const int step = ((h * BG::NJ) + j) * 2 + half;
+        return xs + static_cast<size_t>(it_l) * ITB + step * SP + (n * 32 + tt * 8) * (EX ? 2 : 1);
     };
     // stage columns [kbase, kbase + cits * KI) of every token: one pass, 8 vector loads in flight per thread
     auto stage = [&](int ch) {
@@ -264,7 +292,28 @@ __global__ void __launch_bounds__(kBtThreads, 2) gemv_batch_kernel(const BatchAr
                     uint2 pk;
                     pk.x = *reinterpret_cast<const uint32_t*>(&h01);
                     pk.y = *reinterpret_cast<const uint32_t*>(&h23);
-                    *reinterpret_cast<uint2*>(slot_of(4 * k4, n)) = pk;
+                    unsigned char* slot = slot_of(4 * k4, n);
+                    if (!EX) *reinterpret_cast<uint2*>(slot) = pk;
+                    if (EX) {
+                        const float2 b01 = __half22float2(h01), b23 = __half22float2(h23);
+                        const __half2 l01 = __floats2half2_rn(v[u].x * s1 - b01.x, v[u].y * s1 - b01.y);
+                        const __half2 l23 = __floats2half2_rn(v[u].z * s1 - b23.x, v[u].w * s1 - b23.y);
+                        *reinterpret_cast<uint4*>(slot) = make_uint4(pk.x, pk.y, *reinterpret_cast<const uint32_t*>(&l01),
+                                                                     *reinterpret_cast<const uint32_t*>(&l23));
+                        if (SB6) {      // 8 consecutive lanes hold the 32 columns of one block (every pass of the CTA is full)
+                            float bs = (v[u].x * s1 + v[u].y * s1) + (v[u].z * s1 + v[u].w * s1);
+                            bs += __shfl_xor_sync(0xFFFFFFFFu, bs, 1);
+                            bs += __shfl_xor_sync(0xFFFFFFFFu, bs, 2);
+                            bs += __shfl_xor_sync(0xFFFFFFFFu, bs, 4);
+                            if ((k4 & 7) == 0) {
+                                const int kk = 4 * k4, it_l = kk / G::KI, blk = (kk % G::KI) / G::BLK;
+                                __half* sums = reinterpret_cast<__half*>(xs + static_cast<size_t>(it_l) * ITB + BG::STEPS * SP + n * 32);
+                                const __half sh = __float2half_rn(bs);
+                                sums[blk] = sh;
+                                sums[8 + blk] = __float2half_rn(bs - __half2float(sh));
+                            }
+                        }
+                    }
                 }
             }
         }
@@ -286,6 +335,57 @@ __global__ void __launch_bounds__(kBtThreads, 2) gemv_batch_kernel(const BatchAr
             const Frag<L> cur = nxt;
             fetch_next();
             if (tile >= n_tiles) continue;
+            const unsigned char* xrow = xs + static_cast<size_t>(il) * ITB + (g * 32 + t * 8) * (EX ? 2 : 1);
+            if (EX) {
+                __half2 sa, sb, ma = __float2half2_rn(0.f), mb = ma;
+                if (SB6) {
+                    sb6_pair_scales_h2(cur.ma, t, sa, ma);
+                    sb6_pair_scales_h2(cur.mb, t, sb, mb);
+                } else if (L == ML_RTN8) {
+                    sa = __half2half2(__ushort_as_half(static_cast<unsigned short>(cur.ma.z)));
+                    sb = __half2half2(__ushort_as_half(static_cast<unsigned short>(cur.mb.z)));
+                } else {
+                    sa = sym_pair_scales_h2(cur.ma.x, cur.ma.y, cur.ma.z, t);
+                    sb = sym_pair_scales_h2(cur.mb.x, cur.mb.y, cur.mb.z, t);
+                }
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const __half2 s0 = h ? __high2half2(sa) : __low2half2(sa), s1 = h ? __high2half2(sb) : __low2half2(sb);
+#pragma unroll
+                    for (int j = 0; j < BG::NJ; ++j) {
+                        uint32_t lo0, hi0, lo1, hi1;
+                        a_words<L>(cur.ca, cur.pa, h, j, lo0, hi0);
+                        a_words<L>(cur.cb, cur.pb, h, j, lo1, hi1);
+                        if (L == ML_SYM8 || L == ML_RTN8) { lo0 ^= 0x80808080u; hi0 ^= 0x80808080u; lo1 ^= 0x80808080u; hi1 ^= 0x80808080u; }
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            uint32_t a0, a1, a2, a3, e0, e1, e2, e3;
+                            cvt4x(half ? hi0 : lo0, bias, s0, a0, a2, e0, e2);
+                            cvt4x(half ? hi1 : lo1, bias, s1, a1, a3, e1, e3);
+                            const unsigned char* xp = xrow + (((h * BG::NJ) + j) * 2 + half) * SP;
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                const uint4 b = *reinterpret_cast<const uint4*>(xp + nt * 512);     // hi (x, y), lo (z, w)
+                                mma_f16(c[nt], e0, e1, e2, e3, b.x, b.y);       // small terms first
+                                mma_f16(c[nt], a0, a1, a2, a3, b.z, b.w);
+                                mma_f16(c[nt], a0, a1, a2, a3, b.x, b.y);
+                            }
+                        }
+                    }
+                }
+                if (SB6) {      // + m[row][blk] * sum_blk(x): A = the mins of blocks 2t, 2t+1 (k slots 2t, 2t+1), B = the block sums
+                    const unsigned char* sp = xs + static_cast<size_t>(il) * ITB + BG::STEPS * SP + g * 32 + t * 4;
+                    const uint32_t m0 = *reinterpret_cast<const uint32_t*>(&ma), m1 = *reinterpret_cast<const uint32_t*>(&mb);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const uint32_t bh = *reinterpret_cast<const uint32_t*>(sp + nt * 256);
+                        const uint32_t bl = *reinterpret_cast<const uint32_t*>(sp + nt * 256 + 16);
+                        mma_f16(c[nt], m0, m1, 0u, 0u, bl, 0u);
+                        mma_f16(c[nt], m0, m1, 0u, 0u, bh, 0u);
+                    }
+                }
+                continue;
+            }
             __half2 sa, sb, ma = __float2half2_rn(0.f), mb = ma;
             if (SB6) {
                 sb6_pair_scales_h2(cur.ma, t, sa, ma);
@@ -297,7 +397,6 @@ __global__ void __launch_bounds__(kBtThreads, 2) gemv_batch_kernel(const BatchAr
                 sa = sym_pair_scales_h2(cur.ma.x, cur.ma.y, cur.ma.z, t);
                 sb = sym_pair_scales_h2(cur.mb.x, cur.mb.y, cur.mb.z, t);
             }
-            const unsigned char* xrow = xs + static_cast<size_t>(il) * BG::STEPS * SP + g * 32 + t * 8;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const __half2 s0 = h ? __high2half2(sa) : __low2half2(sa), s1 = h ? __high2half2(sb) : __low2half2(sb);
@@ -454,19 +553,31 @@ __global__ void __launch_bounds__(256) row_amax_kernel(const float* __restrict__
     }
 }
 
+// RWKVQ_BATCH_FAST=1 in the environment (read once) trades accuracy for speed in the small-batch
+// linears: single fp16 operands (relative error ~5e-4 per linear, the arithmetic of the prefill GEMM)
+// and, above 32 rows, the tcgen05 kernel.  The default is the two-term kernel.
+int g_batch_fast = -1;
+bool batch_fast() {
+    if (g_batch_fast < 0) {
+        const char* e = getenv("RWKVQ_BATCH_FAST");
+        g_batch_fast = (e != nullptr && e[0] == '1') ? 1 : 0;
+    }
+    return g_batch_fast == 1;
+}
+
 unsigned long long* g_batch_trace = nullptr;      // set by rwkvq_profiling_batch_trace (rwkvq_profiling.h)
 int g_batch_force_ks = 0;                         // profiling aid: cluster size override (0 = the launcher's choice)
 int g_batch_force_rows = 0, g_batch_force_cols = 0;   // ... for tensors of this shape only (0: every shape)
 
 namespace {
 
-template <int L, int NT>
+template <int L, int NT, bool EX>
 int launch_bt(BatchArgs& a, int n_mats, int n_groups, int n_clusters, size_t smem, cudaStream_t s) {
     static bool configured[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) dev = 0;
     if (dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_batch_kernel<L, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBtMaxSmem);
+        cudaError_t e = cudaFuncSetAttribute(gemv_batch_kernel<L, NT, EX>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBtMaxSmem);
         if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "rwkvq_gemv_batch: shared memory attribute: %s", cudaGetErrorString(e));
         if (dev < 64) configured[dev] = true;
     }
@@ -482,20 +593,22 @@ int launch_bt(BatchArgs& a, int n_mats, int n_groups, int n_clusters, size_t sme
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, gemv_batch_kernel<L, NT>, a);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemv_batch_kernel<L, NT, EX>, a);
     if (le != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "rwkvq_gemv_batch: %s", cudaGetErrorString(le));
     return RWKVQ_OK;
 }
 
 template <int L>
-int launch_bt_l(BatchArgs& a, int n_mats, int rows, int cols, int N, cudaStream_t s) {
+int launch_bt_l(BatchArgs& a, int n_mats, int rows, int cols, int N, bool exact, cudaStream_t s) {
     using G = Geo<L>;
     const int n_iters = cols / G::KI;
-    const int nt = N <= 8 ? 1 : N <= 16 ? 2 : N <= 32 ? 4 : 8;
+    // the two-term kernel works on at most 32 tokens at a time (grid.z walks the groups of a larger batch)
+    const int nt = N <= 8 ? 1 : N <= 16 ? 2 : (N <= 32 || exact) ? 4 : 8;
     const int n8 = nt * 8, n_groups = (N + n8 - 1) / n8;
     const int n_tiles = (rows + 15) / 16;
     const int mats = n_mats * n_groups;
-    const size_t step_bytes = static_cast<size_t>(n8) * 32 + kBtStepPad;
+    const size_t step_bytes = static_cast<size_t>(n8) * 32 * (exact ? 2 : 1) + kBtStepPad;
+    const size_t it_bytes = step_bytes * (G::KI / 16) + ((exact && L <= ML_SB6_6) ? static_cast<size_t>(n8) * 32 : 0);
     auto fixed_bytes = [&](int tpc) { return static_cast<size_t>(3 * n8) * sizeof(float) + static_cast<size_t>(n8) * (tpc * 16 + 4) * sizeof(float); };
     // Cost model (microseconds of the slowest CTA) over the cluster size ks (a divisor of the iteration
     // count) and the rows per group (128 or 256): activations staged once (L2 -> SM traffic of all
@@ -508,7 +621,7 @@ int launch_bt_l(BatchArgs& a, int n_mats, int rows, int cols, int N, cudaStream_
             if (n_iters % c) continue;
             const int ipc = n_iters / c;
             const int max_chunk = static_cast<int>((static_cast<long long>(kBtMaxSmem) - static_cast<long long>(fixed_bytes(tpc))) /
-                                                   static_cast<long long>(step_bytes * (G::KI / 16)));
+                                                   static_cast<long long>(it_bytes));
             if (max_chunk < 1) continue;
             const bool chunked = ipc > max_chunk;
             if (chunked && tpc != 8) continue;
@@ -519,7 +632,7 @@ int launch_bt_l(BatchArgs& a, int n_mats, int rows, int cols, int N, cudaStream_
             const double f = n8 / 64.0;
             const double x_mb = static_cast<double>(clusters) * mats * n8 * cols * (half_in ? 2 : 4) / 1e6 * (chunked ? rounds : 1);
             const double stage_us = 0.8 + x_mb / 3.5;
-            const double it_us = (0.6 + 1.7 * f) * G::KI / 256.0 * (tpc / 8);
+            const double it_us = (exact ? 1.0 + 3.4 * f : 0.6 + 1.7 * f) * G::KI / 256.0 * (tpc / 8);
             const double red_us = 1.6 + 0.15 * c + 0.5 * f * (tpc / 8);
             const double occupancy = (clusters * c * mats > 148) ? 1.35 : 1.0;  // two CTAs share an SM
             const double t = stage_us + rounds * (ipc * it_us * occupancy + red_us) + (c == 8 ? 0.8 : 0.0);
@@ -536,11 +649,11 @@ int launch_bt_l(BatchArgs& a, int n_mats, int rows, int cols, int N, cudaStream_
     a.ks = ks;
     a.its_per_cta = n_iters / ks;
     int max_chunk = static_cast<int>((static_cast<long long>(kBtMaxSmem) - static_cast<long long>(fixed_bytes(tpc))) /
-                                     static_cast<long long>(step_bytes * (G::KI / 16)));
+                                     static_cast<long long>(it_bytes));
     if (a.its_per_cta > max_chunk) {
         tpc = 8;
         max_chunk = static_cast<int>((static_cast<long long>(kBtMaxSmem) - static_cast<long long>(fixed_bytes(tpc))) /
-                                     static_cast<long long>(step_bytes * (G::KI / 16)));
+                                     static_cast<long long>(it_bytes));
     }
     if (max_chunk < 1) return fail(RWKVQ_E_LIMIT, "rwkvq_gemv_batch: no room for one staged iteration");
     a.chunk_its = std::min(a.its_per_cta, max_chunk);
@@ -548,12 +661,19 @@ int launch_bt_l(BatchArgs& a, int n_mats, int rows, int cols, int N, cudaStream_
     const int n_rg = (n_tiles + tpc - 1) / tpc;
     const int slots = std::max(1, (2 * 148) / ks);
     const int n_clusters = std::max(1, std::min(n_rg, std::max(1, slots / std::max(1, mats))));
-    const size_t smem = fixed_bytes(tpc) + static_cast<size_t>(a.chunk_its) * (G::KI / 16) * step_bytes;
+    const size_t smem = fixed_bytes(tpc) + static_cast<size_t>(a.chunk_its) * it_bytes;
+    if (exact) {
+        switch (nt) {
+            case 1: return launch_bt<L, 1, true>(a, n_mats, n_groups, n_clusters, smem, s);
+            case 2: return launch_bt<L, 2, true>(a, n_mats, n_groups, n_clusters, smem, s);
+            default: return launch_bt<L, 4, true>(a, n_mats, n_groups, n_clusters, smem, s);
+        }
+    }
     switch (nt) {
-        case 1: return launch_bt<L, 1>(a, n_mats, n_groups, n_clusters, smem, s);
-        case 2: return launch_bt<L, 2>(a, n_mats, n_groups, n_clusters, smem, s);
-        case 4: return launch_bt<L, 4>(a, n_mats, n_groups, n_clusters, smem, s);
-        default: return launch_bt<L, 8>(a, n_mats, n_groups, n_clusters, smem, s);
+        case 1: return launch_bt<L, 1, false>(a, n_mats, n_groups, n_clusters, smem, s);
+        case 2: return launch_bt<L, 2, false>(a, n_mats, n_groups, n_clusters, smem, s);
+        case 4: return launch_bt<L, 4, false>(a, n_mats, n_groups, n_clusters, smem, s);
+        default: return launch_bt<L, 8, false>(a, n_mats, n_groups, n_clusters, smem, s);
     }
 }
 
@@ -587,13 +707,14 @@ int launch_gemv_batch(const rwkvq_qtensor* ts, int n_mats, const void* const* xs
     a.ldx = ldx; a.ldy = ldy; a.n_tokens = N; a.epilogue = epilogue;
     a.trace = g_batch_trace;
     const int rows = ts[0].rows, cols = ts[0].cols;
+    const bool exact = !half_in && !batch_fast();
     switch (ml) {
-        case ML_SB6_4: return launch_bt_l<ML_SB6_4>(a, n_mats, rows, cols, N, s);
-        case ML_SB6_5: return launch_bt_l<ML_SB6_5>(a, n_mats, rows, cols, N, s);
-        case ML_SB6_6: return launch_bt_l<ML_SB6_6>(a, n_mats, rows, cols, N, s);
-        case ML_SYM6: return launch_bt_l<ML_SYM6>(a, n_mats, rows, cols, N, s);
-        case ML_RTN8: return launch_bt_l<ML_RTN8>(a, n_mats, rows, cols, N, s);
-        default: return launch_bt_l<ML_SYM8>(a, n_mats, rows, cols, N, s);
+        case ML_SB6_4: return launch_bt_l<ML_SB6_4>(a, n_mats, rows, cols, N, exact, s);
+        case ML_SB6_5: return launch_bt_l<ML_SB6_5>(a, n_mats, rows, cols, N, exact, s);
+        case ML_SB6_6: return launch_bt_l<ML_SB6_6>(a, n_mats, rows, cols, N, exact, s);
+        case ML_SYM6: return launch_bt_l<ML_SYM6>(a, n_mats, rows, cols, N, exact, s);
+        case ML_RTN8: return launch_bt_l<ML_RTN8>(a, n_mats, rows, cols, N, exact, s);
+        default: return launch_bt_l<ML_SYM8>(a, n_mats, rows, cols, N, exact, s);
     }
 }
 
@@ -612,6 +733,7 @@ extern "C" void rwkvq_profiling_batch_trace(void* buf8, int force_ks) {
     g_batch_force_ks = force_ks;
     g_batch_force_rows = g_batch_force_cols = 0;
 }
+extern "C" void rwkvq_profiling_batch_fast(int fast) { g_batch_fast = fast < 0 ? -1 : (fast ? 1 : 0); }
 extern "C" void rwkvq_profiling_batch_force(int force_ks, int rows, int cols) {
     g_batch_force_ks = force_ks;
     g_batch_force_rows = rows;
@@ -629,8 +751,10 @@ extern "C" int rwkvq_gemv_batch(const rwkvq_qtensor* t, const float* x, int N, i
     RWKVQ_REQUIRE(epilogue >= RWKVQ_EPI_NONE && epilogue <= RWKVQ_EPI_ADD, RWKVQ_E_DTYPE, "rwkvq_gemv_batch: epilogue %d", epilogue);
     RWKVQ_REQUIRE(ldx >= t->cols && ldy >= t->rows, RWKVQ_E_SHAPE, "rwkvq_gemv_batch: ldx %lld / ldy %lld", (long long)ldx, (long long)ldy);
     RWKVQ_REQUIRE(x && y, RWKVQ_E_NULL, "rwkvq_gemv_batch: x or y is null");
-    // more than 32 rows: the tcgen05 kernel (measured crossover inside the decode step); fewer: mma.sync
-    const bool tcb = tcb_enabled() && gemm_tcb_ok(*t) && ldx % 8 == 0 && (N > 32 || mma_layout_of(*t) < 0 || tcb_forced());
+    // default: the two-term mma.sync kernel.  The tcgen05 kernel (single fp16 operands) serves more than
+    // 32 rows in fast mode, tensors the mma.sync kernel has no layout for, and the profiling override.
+    const bool tcb = tcb_enabled() && gemm_tcb_ok(*t) && ldx % 8 == 0 &&
+                     ((batch_fast() && N > 32) || mma_layout_of(*t) < 0 || tcb_forced());
     RWKVQ_REQUIRE(tcb || mma_layout_of(*t) >= 0, RWKVQ_E_DTYPE,
                   "rwkvq_gemv_batch: needs an sb6 tensor, a sym tensor or per-row int8 with columns in multiples of 128");
     RWKVQ_REQUIRE(aligned(x, 16) && ldx % 4 == 0, RWKVQ_E_ALIGN, "rwkvq_gemv_batch: x rows must be 16-byte aligned");

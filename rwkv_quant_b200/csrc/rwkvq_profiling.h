@@ -22,6 +22,9 @@ void rwkvq_profiling_batch_force(int force_ks, int rows, int cols);
  * that divides the pass count (1000: every batch size, launcher's cluster size), -1 routes every
  * call to the mma.sync kernel instead, 0 restores the launcher's choice. */
 void rwkvq_profiling_tcb_force(int force_ks);
+/* Precision of the small-batch linears: 1 single fp16 operands (what RWKVQ_BATCH_FAST=1 selects),
+ * 0 two-term operands (the default), -1 read the environment again. */
+void rwkvq_profiling_batch_fast(int fast);
 #ifdef __cplusplus
 }
 #endif

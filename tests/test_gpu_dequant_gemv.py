@@ -217,17 +217,25 @@ def test_gemv_wide_dynamic_range_activations(cuda_lib, layout, bits, n):
 BATCH_SHAPES = [(16, 256), (48, 512), (2048, 2048), (100, 2560), (2048, 8192), (1024, 4352), (8192, 2048), (2560, 10240)]
 
 
-@pytest.fixture(params=["tcgen05", "mma.sync"])
+@pytest.fixture(params=["two-term", "mma.sync-fast", "tcgen05-fast"])
 def batch_kernel(request, cuda_lib):
-    """Both kernels behind rwkvq_gemv_batch: sb6 / sym tensors run on the tcgen05 one by default; the
-    library's profiling switch (not part of the C ABI) routes them to the mma.sync one, which always
-    serves per-row int8."""
+    """The three kernels behind rwkvq_gemv_batch: the default two-term mma.sync kernel (both operands
+    as fp16 pairs: fp32-grade results) and, selected by RWKVQ_BATCH_FAST=1 in production and by the
+    library's profiling switches (not part of the C ABI) here, the single-term mma.sync kernel and
+    the tcgen05 kernel (fp16 operands, the arithmetic of the prefill GEMM)."""
     import ctypes as C
     f = cuda_lib.rwkvq_profiling_tcb_force
     f.restype, f.argtypes = None, [C.c_int]
-    f(-1 if request.param == "mma.sync" else 1000)      # 1000: tcgen05 at every batch size (no valid cluster size: launcher's choice)
+    fast = cuda_lib.rwkvq_profiling_batch_fast
+    fast.restype, fast.argtypes = None, [C.c_int]
+    fast(0 if request.param == "two-term" else 1)
+    f(1000 if request.param == "tcgen05-fast" else -1)   # 1000: tcgen05 at every batch size (no valid cluster size: launcher's choice)
     yield request.param
     f(0)
+    fast(-1)
+
+
+BATCH_TOL = {"two-term": 2e-5, "mma.sync-fast": TOL, "tcgen05-fast": TOL}
 
 
 @pytest.mark.parametrize("layout,bits", LAYOUTS[:6])
@@ -243,8 +251,8 @@ def test_gemv_batch_matches_oracle(cuda_lib, batch_kernel, layout, bits, rows, c
     qt = _synth_linear(layout, bits, rows, cols, seed=rows + cols + bits)
     dq = ops.DeviceQT(qt)
     assert ops.has_batch_layout(dq)
-    if layout == "rtn" and batch_kernel == "tcgen05":
-        pytest.skip("per-row int8 has one kernel")
+    if layout == "rtn" and batch_kernel == "tcgen05-fast":
+        pytest.skip("per-row int8 has no tcgen05 form")
     w = _oracle_w(qt).astype(np.float64)
     worst = 0.0
     for n in (3, 8, 13, 32, 64, 70):
@@ -259,7 +267,7 @@ def test_gemv_batch_matches_oracle(cuda_lib, batch_kernel, layout, bits, rows, c
         assert np.isfinite(y).all(), f"n={n}: an element was not written"
         ref = x.cpu().numpy().astype(np.float64) @ w.T
         worst = max(worst, relmax(y, ref))
-        assert relmax(y, ref) <= TOL, (n, relmax(y, ref))
+        assert relmax(y, ref) <= BATCH_TOL[batch_kernel], (n, relmax(y, ref))
     print(f"gemv_batch ({batch_kernel}) {layout}@{bits} [{rows},{cols}]: worst relmax {worst:.2e}")
 
 
@@ -286,7 +294,7 @@ def test_gemv_batch_epilogues_scaling_and_refusals(cuda_lib, batch_kernel):
     ref = xs.cpu().numpy().astype(np.float64) @ w.T
     y = ops.gemv_batch(dq, xs).cpu().numpy()
     for n in range(9):
-        assert np.abs(y[n] - ref[n]).max() <= TOL * max(np.abs(ref[n]).max(), 1e-30), n
+        assert np.abs(y[n] - ref[n]).max() <= BATCH_TOL[batch_kernel] * max(np.abs(ref[n]).max(), 1e-30), n
     assert (y[3] == 0).all()
     # non-finite input propagates to its own row only
     xs[4, 100] = float("inf")
@@ -310,7 +318,7 @@ def test_gemv_batch_epilogues_scaling_and_refusals(cuda_lib, batch_kernel):
 
 def test_linear_classes_route_small_batches_through_the_batch_kernel(cuda_lib):
     """3 <= N < 128 through the operator class: one pass over the weights (the reference reads them
-    once per chunk of 4 columns), result within the fp16-operand rounding of the exact kernel."""
+    once per chunk of 4 columns), result within fp32 rounding of the single-vector kernel."""
     from rwkv_quant_b200.backends import cuda as be
     from rwkv_quant_b200.backends.cuda import ops
     for layout, bits in (("sb6", 4), ("sym", 6), ("rtn", 8)):
@@ -320,7 +328,7 @@ def test_linear_classes_route_small_batches_through_the_batch_kernel(cuda_lib):
         y = lin(x)
         assert torch.equal(y, ops.gemv_batch(lin.dq, x))
         exact = ops.gemv(lin.dq.bufs, lin.dq.meta, x, 0, None)
-        assert (y - exact).abs().max().item() <= 5e-4 * exact.abs().max().item()
+        assert (y - exact).abs().max().item() <= 2e-5 * exact.abs().max().item()
         assert torch.equal(lin(x[:2]), exact[:2])          # 1 and 2 rows: the exact kernel
 
 
