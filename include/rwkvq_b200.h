@@ -150,21 +150,25 @@ int rwkvq_outlier_tail(const int32_t* row_ptr, const int32_t* cols, const float*
  * GEMV kernels of the reference, which decode each weight once for up to 4 columns and loop
  * over chunks of 4 (GwQuantLinear._gemv_nb / _get_kernel_k3nb, backends/metal/quant_linear_gw.py:
  * 658-744, 850-905; SymQuantLinear._gemv, quant_linear_sym.py:485-516): here one pass serves
- * up to 64 columns (groups of 64 beyond that).
+ * up to 32 columns (groups of 32 beyond that, walked by one launch).
  *   x [N, ldx] fp32 (rows 16-byte aligned, ldx % 4 == 0), y / resid [N, ldy] fp32.
  *   Tensors: sb6 with dev_meta (and dev_planes at 5 / 6 bits), sym (dev_planes at 6 bits),
  *   per-row int8 with cols % 128 == 0; RWKVQ_E_DTYPE otherwise (use rwkvq_gemv).
- * Operands are fp16 (weights fp16(q*s+m); each token scaled by a power of two chosen from its
- * max|x|), accumulation fp32 on mma.sync tensor cores; results differ from rwkvq_gemv's within
- * ~2e-4 of max|y| (a column's bits may depend on the batch it is computed in; two calls on the same
- * input give the same bits).  The K split is reduced across a thread-block cluster through
+ * Arithmetic: fp16 tensor-core products with BOTH operands carried as two fp16 terms (weights:
+ * q*s as rounded product + its exact rounding error, block mins on the per-block sums of the
+ * activations; activations: hi + lo of x scaled per token by a power of two chosen from its max|x|),
+ * fp32 accumulation: the result agrees with an fp32 dequantise-and-multiply, and with rwkvq_gemv,
+ * to ~1e-6 of max|y| (a column's last bits may depend on the batch it is computed in; two calls on
+ * the same input give the same bits).  The K split is reduced across a thread-block cluster through
  * distributed shared memory: no scratch for partial sums.
+ * With RWKVQ_BATCH_FAST=1 in the environment (read once per process) single fp16 operands are used
+ * instead (weights fp16(q*s+m)): ~25 % faster at 32 rows and more, results within ~3e-4 of max|y|
+ * per call (the precision of rwkvq_gemm), and sb6 / sym tensors with more than 32 rows run on the
+ * tcgen05 tensor cores (rows of 128 as the UMMA M, the batch as its N, accumulator in tensor memory).
  *   workspace: rwkvq_gemv_batch_workspace_bytes(N) bytes, 16-byte aligned: a status word (first
  *   int32: RWKVQ_E_TIMEOUT if a bounded wait on the tensor-core pipeline ran out; read it after
  *   synchronising the stream, 0 = ok) and one float per row, the max|x| a one-block-per-row
  *   pre-pass writes before the product kernel starts.
- * sb6 and sym tensors run on the tcgen05 tensor cores (rows of 128 as the UMMA M, the batch as its
- * N, accumulator in tensor memory); per-row int8 tensors on mma.sync.
  */
 size_t rwkvq_gemv_batch_workspace_bytes(int N);
 int rwkvq_gemv_batch(const rwkvq_qtensor* t, const float* x, int N, int64_t ldx, float* y, int64_t ldy,

@@ -10,10 +10,11 @@
 //     in turn for 256); thread (g, t) streams the codes of rows g, g+8 for blocks 2t, 2t+1 of each
 //     group of 8 blocks with the same 128-bit loads from the file layout as the single-vector
 //     kernel (load_frag), one group ("iteration") ahead;
-//   * the codes become fp16 weights in registers, fp16(q*s + m): bytes -> halves by a byte
-//     permute onto the exponent pattern of 1024, one subtract and one fused multiply-add per two
-//     weights with the block scale / min, which ARE fp16 values by the codec's definition, so
-//     the product is rounded once (the same operand precision as the prefill GEMM);
+//   * the codes become fp16 weights in registers: bytes -> halves by a byte permute onto the
+//     exponent pattern of 1024 and one subtract; then, in the default two-term form (EX below),
+//     the product with the block scale and its exact rounding error, or, in the single-term form,
+//     fp16(q*s + m) by one fused multiply-add per two weights (rounded once: the operand
+//     precision of the prefill GEMM).  Block scale and min ARE fp16 values by the codec's definition;
 //   * which four k an MMA slot of a thread holds is free as long as both operands agree, so a
 //     thread feeds its OWN block's weights (the block whose scale it decoded) and the
 //     activations are staged in shared memory in exactly that order: per MMA step the 8 tokens
