@@ -29,7 +29,9 @@ constexpr int kGmProducers = 512;     // warps 0-15 unpack weights (and run the 
 constexpr int kGmThreads = 576;       // + warp 16: one lane issues the MMAs; warp 17: one lane issues the TMA loads
 constexpr int kGmMaxBSlots = 8;       // activation slabs in flight (TMA)
 // activation slab slots: as many pairs as fit beside the two weight stages
-__host__ __device__ constexpr int gemm_b_slots(int nt, int km) { return nt >= 256 ? 4 : (nt >= 128 && km == 256) ? 6 : 8; }
+__host__ __device__ constexpr int gemm_b_slots(int nt, int km, int rh = 1) {
+    return rh == 2 ? 3 : nt >= 256 ? 4 : (nt >= 128 && km == 256) ? 6 : 8;
+}
 
 struct GemmArgs {
     QView t;
@@ -59,23 +61,30 @@ __device__ __forceinline__ void trace_mark(const GemmArgs& a, int slot) {
 
 // Warps 0-15: producers (and the epilogue).  Warp 16, one lane: issues the MMAs.  Warp 17, one
 // lane: issues the activation TMA loads.  Producers and issuer meet only through mbarriers:
-//   bar_afull[s]  one arrival per producer thread: the four A slabs of stage s are written
+//   bar_afull[s]  one arrival per producer warp (after every lane's proxy fence): the A slabs of stage s are written
 //   bar_afree[s]  tcgen05.commit: the MMAs that read stage s have completed
 //   bar_bfull[k]  TMA bytes of activation slot k have landed;  bar_bfree[k]  its MMAs completed
 // NT = tokens per CTA tile (UMMA N): 16 .. 256;  KM = K of a macro-iteration: 256 (one super-block,
-// four slabs) or 128 (two slabs; leaves room for the activation tiles of NT = 256)
-template <int NT, int KM>
+// four slabs) or 128 (two slabs; leaves room for the activation tiles of NT = 256);  RH = 128-row
+// halves of the CTA's output tile: with RH = 2 every activation slab feeds two accumulators (all
+// 512 tensor-memory columns at NT = 256), which halves the L2 -> SM traffic per FLOP, the bound
+// of the one-accumulator form at large M.  The activation ring then holds three single slabs
+// instead of two pairs (shared memory: 128 KB of weights + 96 KB of activations).  Measured: a
+// deeper ring (K = 64 stages, five slabs) is no faster; the tensor pipe then runs at ~45 % because
+// the shared memory itself is busy: per K = 64 the MMAs read 96 KB while 64 KB are written.
+template <int NT, int KM, int RH>
 __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int SLAB_BYTES = kGmRows * 128, B_BYTES = NT * 128;
     constexpr int kGmSlabs = KM / kGmK;                         // slabs per macro-iteration
     constexpr int kItems = KM / 32;                             // items (32 weights) per row and macro-iteration
-    constexpr int kGmPasses = kGmRows * kItems / kGmProducers;  // items per producer thread and macro-iteration
-    constexpr int BS = gemm_b_slots(NT, KM);
-    constexpr uint32_t TM_COLS = NT < 32 ? 32 : NT;
-    unsigned char* a_ring = smem;                                        // [2 stages][4 slabs][SLAB_BYTES]
-    unsigned char* b_ring = smem + 2 * kGmSlabs * SLAB_BYTES;            // [BS][B_BYTES]
+    constexpr int kGmPasses = kGmRows * RH * kItems / kGmProducers;  // items per producer thread and macro-iteration
+    constexpr int SPB = RH == 2 ? 1 : 2;                        // activation slabs per ring slot (one mbarrier each)
+    constexpr int BS = gemm_b_slots(NT, KM, RH);
+    constexpr uint32_t TM_COLS = RH * NT < 32 ? 32 : RH * NT;
+    unsigned char* a_ring = smem;                                        // [2 stages][RH][slabs][SLAB_BYTES]
+    unsigned char* b_ring = smem + 2 * RH * kGmSlabs * SLAB_BYTES;       // [BS][B_BYTES]
     __shared__ uint64_t bar_afull[2], bar_afree[2], bar_bfull[kGmMaxBSlots], bar_bfree[kGmMaxBSlots], bar_done;
     __shared__ uint32_t s_tmem;
     __shared__ volatile int s_fail;
@@ -83,13 +92,13 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const QView& t = a.t;
-    const int row0 = blockIdx.x * kGmRows, tok0 = blockIdx.y * NT;
+    const int row0 = blockIdx.x * kGmRows * RH, tok0 = blockIdx.y * NT;
     const int KS = gridDim.z;
     const int n_m = (t.cols / KM) / KS;                         // macro-iterations of this CTA's K slice
     const int m_first = blockIdx.z * n_m;                       // first macro-iteration, in units of KM
 
     if (tid == 0) {
-        for (int s = 0; s < 2; ++s) { mbar_init(&bar_afull[s], kGmProducers); mbar_init(&bar_afree[s], 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&bar_afull[s], kGmProducers / 32); mbar_init(&bar_afree[s], 1); }
         for (int s = 0; s < BS; ++s) { mbar_init(&bar_bfull[s], 1); mbar_init(&bar_bfree[s], 1); }
         mbar_init(&bar_done, 1);
         s_fail = 0;
@@ -105,22 +114,24 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
     const uint32_t tmem = s_tmem;
     if (tid == 0) trace_mark(a, 0);
 
-    constexpr int NP = BS / 2;                                  // pair slots of the activation ring
-    const int n_pairs = n_m * kGmSlabs / 2;
+    constexpr int NP = BS / SPB;                                // slots of the activation ring
+    const int n_pairs = n_m * kGmSlabs / SPB;                   // slot fills of this CTA
     if (warp == kGmProducers / 32 + 1) {
         // ------------------------------------------------------------------ activation loader
-        // Activation slabs travel in pairs (one mbarrier per pair): slabs 2q, 2q+1 of this CTA go
-        // to pair slot q % NP as soon as the MMAs that read its previous content have completed.
+        // Activation slabs travel in groups of SPB (one mbarrier per group): slabs SPB q .. of this CTA
+        // go to slot q % NP as soon as the MMAs that read its previous content have completed.
         if (lane == 0) {
             pdl_wait();                                         // the fp16 activations come from the pre-pass
+            int ps = 0, round = 0;
             for (int q = 0; q < n_pairs; ++q) {
-                const int ps = q % NP;
-                if (q >= NP && !mbar_wait_bounded(&bar_bfree[ps], ((q / NP) - 1) & 1)) { s_fail = 1; break; }
+                if (round > 0 && !mbar_wait_bounded(&bar_bfree[ps], (round - 1) & 1)) { s_fail = 1; break; }
                 if (s_fail) break;
-                mbar_expect_tx(&bar_bfull[ps], 2 * B_BYTES);
-                tma_load_2d(b_ring + (2 * ps) * B_BYTES, &xmap, (m_first * kGmSlabs + 2 * q) * kGmK, tok0, &bar_bfull[ps]);
-                tma_load_2d(b_ring + (2 * ps + 1) * B_BYTES, &xmap, (m_first * kGmSlabs + 2 * q + 1) * kGmK, tok0,
-                            &bar_bfull[ps]);
+                mbar_expect_tx(&bar_bfull[ps], SPB * B_BYTES);
+#pragma unroll
+                for (int s2 = 0; s2 < SPB; ++s2)
+                    tma_load_2d(b_ring + (SPB * ps + s2) * B_BYTES, &xmap, (m_first * kGmSlabs + SPB * q + s2) * kGmK, tok0,
+                                &bar_bfull[ps]);
+                if (++ps == NP) { ps = 0; ++round; }
             }
         }
     } else if (warp == kGmProducers / 32) {
@@ -131,7 +142,7 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(NT);
             const uint64_t a_desc0 = umma_desc(smem_addr(a_ring)), b_desc0 = umma_desc(smem_addr(b_ring));
-            constexpr int PPM = kGmSlabs / 2;                    // pairs per macro-iteration
+            constexpr int PPM = kGmSlabs / SPB;                  // slot fills per macro-iteration
             bool ok = true;
             int i = 0, pq = 0, ps = 0, bphase = 0;               // macro-iteration, pair in it, pair slot, slot phase
             for (int q = 0; q < n_pairs && ok; ++q) {
@@ -143,12 +154,15 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
                 if (!mbar_wait_bounded(&bar_bfull[ps], bphase)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
-                for (int s2 = 0; s2 < 2; ++s2) {
-                    const uint64_t ad = a_desc0 + (static_cast<uint64_t>((st * kGmSlabs + pq * 2 + s2) * SLAB_BYTES) >> 4);
-                    const uint64_t bd = b_desc0 + (static_cast<uint64_t>((2 * ps + s2) * B_BYTES) >> 4);
+                for (int s2 = 0; s2 < SPB; ++s2) {
+                    const uint64_t bd = b_desc0 + (static_cast<uint64_t>((SPB * ps + s2) * B_BYTES) >> 4);
 #pragma unroll
-                    for (int k = 0; k < kGmK / 16; ++k)        // 32 bytes further along K per step
-                        umma_f16(tmem, ad + 2 * k, bd + 2 * k, idesc, (q | s2 | k) ? 1u : 0u);
+                    for (int rh = 0; rh < RH; ++rh) {          // one accumulator per 128-row half
+                        const uint64_t ad = a_desc0 + (static_cast<uint64_t>(((st * RH + rh) * kGmSlabs + pq * SPB + s2) * SLAB_BYTES) >> 4);
+#pragma unroll
+                        for (int k = 0; k < kGmK / 16; ++k)    // 32 bytes further along K per step
+                            umma_f16(tmem + rh * NT, ad + 2 * k, bd + 2 * k, idesc, (q | s2 | k) ? 1u : 0u);
+                    }
                 }
                 umma_commit(&bar_bfree[ps]);
                 if (pq == PPM - 1) { umma_commit(&bar_afree[st]); trace_mark(a, 8 + 4 * i + 3); }
@@ -179,13 +193,16 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
             }
             if (tid == 0) trace_mark(a, 8 + 4 * i + 1);
             if (!s_fail) {
-                unsigned char* slab = a_ring + (st * kGmSlabs + (pit >> 1)) * SLAB_BYTES;
 #pragma unroll
-                for (int q = 0; q < kGmPasses; ++q)
-                    convert_store(P[q], t, PR * q + prow, (((m_first + i) * KM) >> 5 & 7) + pit, pit & 1, slab);
+                for (int q = 0; q < kGmPasses; ++q) {
+                    const int r = PR * q + prow;                // row of the CTA's tile: half r / 128, row r % 128 of its slabs
+                    unsigned char* slab = a_ring + ((st * RH + r / kGmRows) * kGmSlabs + (pit >> 1)) * SLAB_BYTES;
+                    convert_store(P[q], t, r % kGmRows, (((m_first + i) * KM) >> 5 & 7) + pit, pit & 1, slab);
+                }
             }
             fence_async_smem();                                 // generic-proxy stores -> visible to the tensor core
-            mbar_arrive(&bar_afull[st]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_afull[st]);         // one arrival per warp: 512 arrivals on one word serialise
             if (tid == 0) trace_mark(a, 8 + 4 * i);
             if (i + 2 < n_m) load_all(P, i + 2);                // the registers are free again: two iterations ahead
         };
@@ -208,9 +225,9 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
         if (tid == 0) atomicCAS(a.status, 0, RWKVQ_E_TIMEOUT);
     } else if (warp < kGmProducers / 32) {
         // warp w reads lanes 32*(w%4) .. +31 (= output rows); the warps that share a lane group split the tokens
-        const int rl = (warp & 3) * 32 + lane, row = row0 + rl;
+        const int rl = (warp & 3) * 32 + lane;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-        auto finish = [&](float r, int tok) {
+        auto finish = [&](float r, int tok, int row) {
             if (tok < a.M && row < t.rows) {
                 r = r * s_unscale[tok - tok0];
                 const long long idx = tok * a.ldy + row;
@@ -220,22 +237,26 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
             }
         };
         if (KS == 1) {
-            for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += kGmProducers / 16) {
-                float v[8];
-                tmem_ld8(lane_base + c0, v);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) finish(v[j], tok0 + c0 + j);
-            }
+            for (int rh = 0; rh < RH; ++rh)
+                for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += kGmProducers / 16) {
+                    float v[8];
+                    tmem_ld8(lane_base + rh * NT + c0, v);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) finish(v[j], tok0 + c0 + j, row0 + rh * kGmRows + rl);
+                }
         } else {
             // this CTA's accumulator tile goes to its scratch slot [token][row]
             const size_t tile_id = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
-            float* mine = a.partial + (tile_id * KS + blockIdx.z) * (NT * kGmRows);
-            for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += kGmProducers / 16) {
-                float v[8];
-                tmem_ld8(lane_base + c0, v);
+            float* mine = a.partial + (tile_id * KS + blockIdx.z) * (NT * kGmRows * RH);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) __stcg(mine + (c0 + j) * kGmRows + rl, v[j]);
-            }
+            for (int rh = 0; rh < RH; ++rh)
+                for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += kGmProducers / 16) {
+                    float v[8];
+                    tmem_ld8(lane_base + rh * NT + c0, v);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) __stcg(mine + (c0 + j) * (kGmRows * RH) + rh * kGmRows + rl, v[j]);
+                }
             __threadfence();
         }
     }
@@ -247,11 +268,13 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
         __syncthreads();
         if (s_last && warp < kGmProducers / 32) {   // last K slice to arrive adds the tiles in slice order
             __threadfence();
-            const int rl = (warp & 3) * 32 + lane, row = row0 + rl;
-            const float* base = a.partial + tile_id * KS * (NT * kGmRows);
+            const float* base = a.partial + tile_id * KS * (NT * kGmRows * RH);
             // warps of one lane group take alternate groups of 8 tokens; 8 x 4 loads are in flight per
             // thread and every token's slices are added in slice order
+#pragma unroll
+            for (int rh = 0; rh < RH; ++rh)
             for (int c0 = (warp >> 2) * 8; c0 < NT; c0 += kGmProducers / 16) {
+                const int rl = rh * kGmRows + (warp & 3) * 32 + lane, row = row0 + rl;
                 float r[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) r[j] = 0.f;
@@ -262,7 +285,7 @@ __global__ void __launch_bounds__(kGmThreads, 1) gemm_tc_kernel(const GemmArgs a
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
                             pv[u][j] = z0 + u < KS
-                                           ? __ldcg(base + (static_cast<size_t>(z0 + u) * NT + c0 + j) * kGmRows + rl)
+                                           ? __ldcg(base + (static_cast<size_t>(z0 + u) * NT + c0 + j) * (kGmRows * RH) + rl)
                                            : 0.f;
 #pragma unroll
                     for (int u = 0; u < 4; ++u)
@@ -331,6 +354,7 @@ using namespace rwkvq;
 
 namespace {
 unsigned long long* g_gemm_trace = nullptr;      // set by rwkvq_profiling_gemm_trace (rwkvq_profiling.h)
+int g_gemm_acc_mode = 0;                         // rwkvq_profiling_gemm_acc_mode: 0 launcher's choice, 1 never / 2 always 256-row tiles
 constexpr int kGemmResident = 2 * 148;     // accumulator tiles the K-split scratch holds
 constexpr int kGemmSms = 148;
 // Row pitch of the fp16 activation copy: 128 bytes more than the row, so that the 128 rows
@@ -369,30 +393,30 @@ int make_xmap(CUtensorMap* map, const __half* x16, int M, int cols, int nt) {
     return RWKVQ_OK;
 }
 
-template <int NT, int KM>
+template <int NT, int KM, int RH = 1>
 int launch_gemm(GemmArgs& a, int rows, int cols, int M, float* partial, const __half* x16, cudaStream_t s) {
     CUtensorMap xmap;
     int mrc = make_xmap(&xmap, x16, M, cols, NT);
     if (mrc) return mrc;
-    const size_t smem = static_cast<size_t>(2 * (KM / kGmK)) * kGmRows * 128 + static_cast<size_t>(gemm_b_slots(NT, KM)) * NT * 128 + 1024;
+    const size_t smem = static_cast<size_t>(2 * RH * (KM / kGmK)) * kGmRows * 128 + static_cast<size_t>(gemm_b_slots(NT, KM, RH)) * NT * 128 + 1024;
     // the attribute belongs to the (function, device) pair: remember it per device of this process
     static bool configured[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) dev = 0;
     if (dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT, KM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT, KM, RH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(smem));
         if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "rwkvq_gemm: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         if (dev < 64) configured[dev] = true;
     }
-    const int rt = (rows + kGmRows - 1) / kGmRows, tt = (M + NT - 1) / NT, n_m = cols / KM;
+    const int rt = (rows + kGmRows * RH - 1) / (kGmRows * RH), tt = (M + NT - 1) / NT, n_m = cols / KM;
     // K slices across CTAs while the grid is below one CTA per SM (power of two, >= 2 super-blocks each)
     int KS = 1;
-    while (rt * tt * KS < kGemmSms && n_m % (KS * 2) == 0 && n_m / (KS * 2) >= 2 && rt * tt * KS * 2 <= kGemmResident &&
+    while (rt * tt * KS < kGemmSms && n_m % (KS * 2) == 0 && n_m / (KS * 2) >= 2 && rt * tt * KS * 2 * RH <= kGemmResident &&
            rt * tt <= static_cast<int>((kGemmHeader - 256) / sizeof(unsigned int)))
         KS *= 2;
     a.partial = partial;
-    cudaError_t le = launch_pdl(gemm_tc_kernel<NT, KM>, dim3(rt, tt, KS), dim3(kGmThreads), smem, s, a, xmap);
+    cudaError_t le = launch_pdl(gemm_tc_kernel<NT, KM, RH>, dim3(rt, tt, KS), dim3(kGmThreads), smem, s, a, xmap);
     if (le != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "rwkvq_gemm: %s", cudaGetErrorString(le));
     return RWKVQ_OK;
 }
@@ -403,6 +427,14 @@ int dispatch_gemm(GemmArgs& a, const rwkvq_qtensor* t, int M, float* partial, co
     // 256-token tiles (every converted weight serves 256 tokens) once they still give the
     // SMs enough CTAs or a long K loop; otherwise 128-token tiles
     const int tiles256 = ((t->rows + kGmRows - 1) / kGmRows) * ((M + 255) / 256);
+    // 256 rows per CTA (two accumulators per activation slab) once such tiles alone fill the SMs and
+    // their last, partly filled wave does not cost more than the form gains (kTwoAccGain, measured)
+    const int tiles2 = (t->rows / (2 * kGmRows)) * ((M + 255) / 256);
+    auto wave_eff = [](int tiles) { return static_cast<double>(tiles) / (((tiles + kGemmSms - 1) / kGemmSms) * kGemmSms); };
+    constexpr double kTwoAccGain = 1.08;
+    const bool two_pays = tiles2 >= kGemmSms && wave_eff(tiles2) * kTwoAccGain >= wave_eff(tiles256);
+    if (M > 128 && t->rows % (2 * kGmRows) == 0 && g_gemm_acc_mode != 1 && (two_pays || g_gemm_acc_mode == 2))
+        return launch_gemm<256, 128, 2>(a, t->rows, t->cols, M, partial, x16, s);
     if (M > 128 && (tiles256 >= 64 || t->cols >= 4096))
         return launch_gemm<256, 128>(a, t->rows, t->cols, M, partial, x16, s);
     return launch_gemm<128, 256>(a, t->rows, t->cols, M, partial, x16, s);
@@ -422,6 +454,7 @@ size_t rwkvq_gemm_workspace_bytes_for(int M, int max_cols) {
     return gemm_ws_x16_off(m) + sizeof(__half) * m * (static_cast<size_t>(max_cols) + 64) + 256;
 }
 void rwkvq_profiling_gemm_trace(void* buf512) { g_gemm_trace = static_cast<unsigned long long*>(buf512); }
+void rwkvq_profiling_gemm_acc_mode(int mode) { g_gemm_acc_mode = mode; }
 
 size_t rwkvq_gemm_workspace_bytes(int M) { return rwkvq_gemm_workspace_bytes_for(M, 16384); }
 

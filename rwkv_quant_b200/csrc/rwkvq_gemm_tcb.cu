@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a
 
     tb_mark(a, 0);
     if (tid == 0) {
-        mbar_init(&bar_full, kTbProducers);
+        mbar_init(&bar_full, kTbProducers / 32);
         mbar_init(&bar_mma, 1);
         s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -210,7 +210,8 @@ __global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a
                 }
             }
             fence_async_smem();                                 // generic-proxy stores -> visible to the tensor core
-            mbar_arrive(&bar_full);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_full);              // one arrival per warp
             if (p == 0) tb_mark(a, 3);
             if (p + 1 < np) load_all(p + 1);                    // the registers are free again
         }

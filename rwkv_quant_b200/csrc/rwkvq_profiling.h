@@ -11,6 +11,10 @@ extern "C" {
  * process records global-timer nanoseconds of its pipeline events (slot map in the kernel source);
  * NULL (the default) switches it off. */
 void rwkvq_profiling_gemm_trace(void* buf512);
+/* rwkvq_gemm with more than 128 tokens: 1 keeps 128-row tiles (one accumulator per activation slab),
+ * 2 takes 256-row tiles (two accumulators) wherever the row count allows, 0 (the default) leaves the
+ * choice to the launcher (256-row tiles once they alone fill the SMs). */
+void rwkvq_profiling_gemm_acc_mode(int mode);
 /* With a device buffer of 8 uint64 set, CTA (0,0,0) of every later small-batch launch records
  * global-timer nanoseconds: 0 start, 1 producer done, 2 activations staged, 3 products done,
  * 4 cluster barrier passed, 5 reduced and stored, 6 end.  force_ks > 0 overrides the launcher's choice:

@@ -150,10 +150,14 @@ def tp_chain(model="2.9b", recipe="compression", exchange="p2p", iters=200):
     dist.destroy_process_group()
 
 
-def gemm_sweep(recipe="compression", Ms=(64, 512, 8192), reps=20):
+def gemm_sweep(recipe="compression", Ms=(64, 512, 8192), reps=20, acc_mode=0):
     """rwkvq_gemm (pre-pass + tensor-core kernel) on the four linear shapes of a 1.5B layer
     and the head: microseconds per call (CUDA-graph replay, so that host time does not
-    count) and TFLOP/s = 2 * M * OUT * IN / time."""
+    count) and TFLOP/s = 2 * M * OUT * IN / time.  acc_mode: 0 the launcher's tile choice,
+    1 128-row tiles only, 2 256-row tiles wherever legal."""
+    f = _lib.load().rwkvq_profiling_gemm_acc_mode      # rwkvq_profiling.h: not part of the C ABI
+    f.restype, f.argtypes = None, [C.c_int]
+    f(acc_mode)
     lay = {"compression": [("sb6", 5, 2048, 2048), ("sb6", 4, 8192, 2048), ("sb6", 4, 2048, 8192), ("sb6", 5, 65536, 2048)],
            "reduction": [("sym", 8, 2048, 2048), ("sym", 6, 8192, 2048), ("sym", 6, 2048, 8192), ("sym", 8, 65536, 2048)]}[recipe]
     for layout, bits, rows, cols in lay:
@@ -320,10 +324,13 @@ def gemm_once(layout="sb6", bits=5, rows=2048, cols=2048, M=8192, launches=3):
     print("ok", float(y.abs().sum()))
 
 
-def gemm_timeline(layout="sb6", bits=5, rows=2048, cols=2048, M=8192):
-    """Pipeline timeline of CTA (0,0,0) of one rwkvq_gemm launch: per macro-iteration (K = 256)
+def gemm_timeline(layout="sb6", bits=5, rows=2048, cols=2048, M=8192, acc_mode=0):
+    """Pipeline timeline of CTA (0,0,0) of one rwkvq_gemm launch: per macro-iteration
     when its weight stage was free, converted, seen full by the issuer and issued."""
     import numpy as np
+    f = _lib.load().rwkvq_profiling_gemm_acc_mode      # rwkvq_profiling.h: not part of the C ABI
+    f.restype, f.argtypes = None, [C.c_int]
+    f(acc_mode)
     dq = _tensor(layout, bits, rows, cols)
     x = torch.randn(M, cols, device="cuda")
     ops.gemm(dq, x, check=True)
@@ -513,8 +520,8 @@ def main():
     bs.add_argument("--recipe", default="compression")
     gt = sub.add_parser("gemm-timeline")
     gt.add_argument("--M", type=int, default=8192); gt.add_argument("--rows", type=int, default=2048)
-    gt.add_argument("--cols", type=int, default=2048)
-    gs = sub.add_parser("gemm-sweep")
+    gt.add_argument("--cols", type=int, default=2048); gt.add_argument("--acc-mode", type=int, default=0); gt.add_argument("--bits", type=int, default=5)
+    gs = sub.add_parser("gemm-sweep"); gs.add_argument("--acc-mode", type=int, default=0)
     gs.add_argument("--recipe", default="compression")
     wk = sub.add_parser("wkv")
     wk.add_argument("--batch", type=int, default=1); wk.add_argument("--T", type=int, default=512)
@@ -545,10 +552,10 @@ def main():
         batch_sweep(a.recipe)
         return
     if a.cmd == "gemm-timeline":
-        gemm_timeline("sb6", 5, a.rows, a.cols, a.M)
+        gemm_timeline("sb6", a.bits, a.rows, a.cols, a.M, a.acc_mode)
         return
     if a.cmd == "gemm-sweep":
-        gemm_sweep(a.recipe)
+        gemm_sweep(a.recipe, acc_mode=a.acc_mode)
         return
     if a.cmd == "tp":
         tp_chain(a.model, a.recipe, a.exchange)
