@@ -20,6 +20,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaAr
     int8_t* dig = reinterpret_cast<int8_t*>(smem);
     float* xs16 = reinterpret_cast<float*>(dig + 3 * n_in);
     float* red = xs16 + (n_in >> 4);                                     // [2][kMmaWarps * 16]
+    uint8_t* zflag = reinterpret_cast<uint8_t*>(red + 2 * kMmaWarps * 16);   // [n_in / 32] all-zero groups of the activations
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -35,11 +36,12 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaAr
     const int n_items = n_steps * ipt;
     // prefetch side: item counter -> (tile, iteration)
     int i_n = 0, i_tile = blockIdx.x * WT + tl, i_j = 0;
-    Frag<L> nxt;
+    Frag<L> nxt{};
+    const uint8_t* zf = nullptr;           // set once the activations are prepared
     auto fetch_next = [&]() {
         if (i_n < n_items && i_tile < n_tiles) {
             const int r0 = min(i_tile * 16 + g, q.rows - 1), r1 = min(i_tile * 16 + g + 8, q.rows - 1);
-            load_frag<L>(nxt, q, r0, r1, it0 + ks + i_j * WK, t);
+            load_frag<L>(nxt, q, r0, r1, it0 + ks + i_j * WK, t, zf);
         }
         ++i_n;
         if (++i_j == ipt) { i_j = 0; i_tile += step; }
@@ -54,8 +56,11 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaAr
     const char* xv = a.xk[blockIdx.y] ? static_cast<const char*>(a.xk[blockIdx.y])
                                       : static_cast<const char*>(a.x) + (a.fused ? blockIdx.y * a.ldx * esz : 0);
     bool finite;
-    const float unscale = prepare_x(xv, a.x_dtype, n_in, x_bits<L>(), dig, xs16, red, finite);
+    const float unscale = prepare_x(xv, a.x_dtype, n_in, x_bits<L>(), dig, xs16, red, finite, zflag);
     __syncthreads();
+    // exact sparsity skip: groups of 32 columns whose activations are all zero (relu(k)^2 in the channel
+    // mix) are not read from the second fetch on
+    zf = zflag;
 
     int c_n = 0, buf = 0;
     for (int base = blockIdx.x * WT; base < n_tiles; base += step, buf ^= 1) {
@@ -204,7 +209,7 @@ size_t gemv_mma_scratch_bytes() {
 template <int L, int WK, bool SPLIT = false>
 static int launch_one(MmaArgs& a, int rows, int cols, int n_mats, int KS, cudaStream_t s) {
     constexpr int WT = kMmaWarps / WK;
-    const size_t smem = 3 * static_cast<size_t>(cols) + 4 * (cols / 16) + 2 * kMmaWarps * 16 * 4;
+    const size_t smem = 3 * static_cast<size_t>(cols) + 4 * (cols / 16) + 2 * kMmaWarps * 16 * 4 + ((cols / 32 + 15) / 16) * 16;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<L, WK, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(smem));

@@ -123,16 +123,21 @@ __device__ __forceinline__ float2 sym_pair_scales(uint32_t q_lo, uint32_t q_hi, 
 }
 
 // Direct (register) loads of iteration `it` of rows r0, r1 for thread t.
+// zflag (optional, sb6 and 6-bit sym): per aligned group of 32 columns, 1 = the activations of
+// the group are all zero (prepare_x); the 16 bytes of codes of such a group are not read and the
+// fragment keeps whatever it held, which the zero activations multiply.
 template <int L>
-__device__ __forceinline__ void load_frag(Frag<L>& f, const QView& q, int r0, int r1, int it, int t) {
+__device__ __forceinline__ void load_frag(Frag<L>& f, const QView& q, int r0, int r1, int it, int t,
+                                          const uint8_t* zflag = nullptr) {
     const size_t R0 = static_cast<size_t>(r0), R1 = static_cast<size_t>(r1);
     if (L <= ML_SB6_6) {
         const int nsb = q.cols >> 8;
         const size_t rowb = static_cast<size_t>(q.cols >> 1), nb = static_cast<size_t>(q.cols >> 5);
         const uint8_t* p0 = q.codes + R0 * rowb + it * 128 + t * 32;
         const uint8_t* p1 = q.codes + R1 * rowb + it * 128 + t * 32;
-        f.ca[0] = ld_stream_u128(p0); f.ca[1] = ld_stream_u128(p0 + 16);
-        f.cb[0] = ld_stream_u128(p1); f.cb[1] = ld_stream_u128(p1 + 16);
+        const bool z0 = zflag != nullptr && zflag[it * 8 + 2 * t] != 0, z1 = zflag != nullptr && zflag[it * 8 + 2 * t + 1] != 0;
+        if (!z0) { f.ca[0] = ld_stream_u128(p0); f.cb[0] = ld_stream_u128(p1); }
+        if (!z1) { f.ca[1] = ld_stream_u128(p0 + 16); f.cb[1] = ld_stream_u128(p1 + 16); }
         f.ma = ld_stream_u128(q.dev_meta + (R0 * nsb + it) * 16);
         f.mb = ld_stream_u128(q.dev_meta + (R1 * nsb + it) * 16);
         if (L == ML_SB6_5) {
@@ -148,8 +153,10 @@ __device__ __forceinline__ void load_frag(Frag<L>& f, const QView& q, int r0, in
         const int nsb = q.cols >> 8;
         if (L == ML_SYM6) {
             const size_t rowb = static_cast<size_t>(q.cols >> 1);
-            f.ca[0] = ld_stream_u128(q.codes + R0 * rowb + it * 64 + t * 16);
-            f.cb[0] = ld_stream_u128(q.codes + R1 * rowb + it * 64 + t * 16);
+            if (zflag == nullptr || zflag[it * 4 + t] == 0) {
+                f.ca[0] = ld_stream_u128(q.codes + R0 * rowb + it * 64 + t * 16);
+                f.cb[0] = ld_stream_u128(q.codes + R1 * rowb + it * 64 + t * 16);
+            }
             const uint2 a = ld_stream_u64(q.dev_planes + R0 * nb16 + it * 8 + 2 * t);
             const uint2 b = ld_stream_u64(q.dev_planes + R1 * nb16 + it * 8 + 2 * t);
             f.pa = make_uint4(a.x, a.y, 0, 0); f.pb = make_uint4(b.x, b.y, 0, 0);
@@ -247,8 +254,11 @@ __device__ __forceinline__ void split_digits(int X, int& d1, int& d2, int& d3) {
 // x is read once: up to kXRegs float4 per thread stay in registers between the max
 // pass and the conversion pass (IN <= 8192 at 256 threads); longer vectors are re-read.
 constexpr int kXRegs = 8;
+// zflag[c / 32] = 1 where all 32 fixed-point activations of the aligned group are zero: the
+// weights of such a group contribute exactly nothing (integer products, and the block min
+// multiplies the group's sum), so the loader may leave them unread (load_frag).
 __device__ __forceinline__ float prepare_x(const void* x, int dtype, int n_in, int bits, int8_t* dig,
-                                           float* xs16, float* red, bool& finite) {
+                                           float* xs16, float* red, bool& finite, uint8_t* zflag) {
     const int tid = threadIdx.x, n4 = n_in >> 2, nt = blockDim.x;
     float4 xr[kXRegs];
     float amax = 0.f;
@@ -290,6 +300,9 @@ __device__ __forceinline__ float prepare_x(const void* x, int dtype, int n_in, i
         s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
         s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
         if ((tid & 3) == 0) xs16[i >> 2] = static_cast<float>(s);
+        // 8 consecutive lanes cover 32 columns (whole warps get here together)
+        const unsigned nz = __ballot_sync(0xFFFFFFFFu, (X0 | X1 | X2 | X3) != 0);
+        if ((tid & 7) == 0) zflag[i >> 3] = ((nz >> (tid & 24)) & 0xFFu) == 0u;
     };
 #pragma unroll
     for (int k = 0; k < kXRegs; ++k) {
@@ -297,56 +310,6 @@ __device__ __forceinline__ float prepare_x(const void* x, int dtype, int n_in, i
         if (i < n4) emit(i, xr[k]);          // n4 is a multiple of 64: whole warps take this branch together
     }
     for (int i = tid + kXRegs * nt; i < n4; i += nt) emit(i, load_x4(x, dtype, i));
-    __syncthreads();
-    return finite ? ldexpf(1.f, e - bits) : 0.f;
-}
-
-// The same conversion for a vector that already sits in registers: thread `tid` holds
-// elements 4*(tid + k*blockDim.x) .. +3 in xr[k] for k < kXRegs (zeros beyond n_in).
-// `dig` gets three planes of n_in bytes.  Ends with a barrier.
-__device__ __forceinline__ float digits_from_regs(const float4 (&xr)[kXRegs], int n_in, int bits, int8_t* dig,
-                                                  float* xs16, float* red, bool& finite) {
-    const int tid = threadIdx.x, n4 = n_in >> 2, nt = blockDim.x;
-    float amax = 0.f;
-#pragma unroll
-    for (int k = 0; k < kXRegs; ++k) {
-        const float4& v = xr[k];
-        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-        if (!(fabsf(v.x) + fabsf(v.y) + fabsf(v.z) + fabsf(v.w) < INFINITY)) amax = INFINITY;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    __syncthreads();                       // `red` may still be read by an earlier reduction
-    if ((tid & 31) == 0) red[tid >> 5] = amax;
-    __syncthreads();
-    amax = 0.f;
-    for (int w = 0; w < (nt >> 5); ++w) amax = fmaxf(amax, red[w]);
-    finite = amax < INFINITY;
-    int e = 0;
-    if (finite && amax > 0.f) frexpf(amax, &e);          // amax <= 2^e
-    const float scale = finite ? ldexpf(1.f, bits - e) : 0.f;
-#pragma unroll
-    for (int k = 0; k < kXRegs; ++k) {
-        const int i = tid + k * nt;
-        if (i < n4) {                      // n4 is a multiple of 64: whole warps take this branch together
-            const float4& v = xr[k];
-            const int X0 = __float2int_rn(v.x * scale), X1 = __float2int_rn(v.y * scale);
-            const int X2 = __float2int_rn(v.z * scale), X3 = __float2int_rn(v.w * scale);
-            int a[4], b[4], c[4];
-            split_digits(X0, a[0], b[0], c[0]); split_digits(X1, a[1], b[1], c[1]);
-            split_digits(X2, a[2], b[2], c[2]); split_digits(X3, a[3], b[3], c[3]);
-            auto pack = [](const int (&d)[4]) {
-                return (d[0] & 0xFF) | ((d[1] & 0xFF) << 8) | ((d[2] & 0xFF) << 16) | (static_cast<uint32_t>(d[3] & 0xFF) << 24);
-            };
-            reinterpret_cast<uint32_t*>(dig)[i] = pack(a);
-            reinterpret_cast<uint32_t*>(dig + n_in)[i] = pack(b);
-            reinterpret_cast<uint32_t*>(dig + 2 * n_in)[i] = pack(c);
-            int s = X0 + X1 + X2 + X3;     // the 4 lanes of an aligned quad cover one 16-chunk
-            s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
-            s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
-            if ((tid & 3) == 0) xs16[i >> 2] = static_cast<float>(s);
-        }
-    }
     __syncthreads();
     return finite ? ldexpf(1.f, e - bits) : 0.f;
 }

@@ -32,10 +32,15 @@ def _tensor(layout, bits, rows, cols, seed=0):
     return ops.DeviceQT(_Q[layout]("w", "g", w, bits))
 
 
-def gemv(layout, bits, rows, cols, n=1, launches=4):
+def gemv(layout, bits, rows, cols, n=1, launches=4, zero_groups=0.0):
+    """A few plain rwkvq_gemv launches on different tensors (the target of ncu captures);
+    zero_groups: share of the 32-column groups of x that are exactly zero."""
     lib = _lib.load(check_device=True)
     dqs = [_tensor(layout, bits, rows, cols, s) for s in range(launches)]
     x = torch.randn(n, cols, device="cuda")
+    if zero_groups > 0:
+        keep = torch.rand(n, cols // 32, device="cuda") >= zero_groups
+        x = (x.view(n, cols // 32, 32) * keep[..., None]).reshape(n, cols).contiguous()
     y = torch.empty(n, rows, device="cuda")
     for d in dqs:
         _lib.check(lib.rwkvq_gemv(C.byref(d.struct), x.data_ptr(), 0, n, cols, y.data_ptr(), rows, 0, None,
@@ -374,7 +379,7 @@ def prefill(layers=24, recipe="reduction", T=512, batch=1, model="1.5b", reps=3)
     print(f"pp{T} batch {batch} {recipe} {layers} layers: {best:.2f} ms  {batch * T / best * 1e3:.0f} tok/s", flush=True)
 
 
-def time_ring(layout, bits, rows, cols, n=1, ring_bytes=1.5e9, iters=5):
+def time_ring(layout, bits, rows, cols, n=1, ring_bytes=1.5e9, iters=5, zero_groups=0.0):
     lib = _lib.load(check_device=True)
     base = _tensor(layout, bits, rows, cols)
     nb = base.nbytes_file()
@@ -387,6 +392,9 @@ def time_ring(layout, bits, rows, cols, n=1, ring_bytes=1.5e9, iters=5):
         d.struct = ops._descr(d.bufs, d.meta)
         ring.append(d)
     x = torch.randn(n, cols, device="cuda")
+    if zero_groups > 0:          # whole groups of 32 activations exactly zero (relu(k)^2 in the channel mix)
+        keep = torch.rand(n, cols // 32, device="cuda") >= zero_groups
+        x = (x.view(n, cols // 32, 32) * keep[..., None]).reshape(n, cols).contiguous()
     y = torch.empty(n, rows, device="cuda")
 
     def run():
@@ -413,9 +421,17 @@ def time_ring(layout, bits, rows, cols, n=1, ring_bytes=1.5e9, iters=5):
         torch.cuda.synchronize()
         best = min(best, e0.elapsed_time(e1))
     us = best * 1e3 / k
-    print(f"{layout}{bits} [{rows},{cols}] N={n}: {us:8.2f} us/launch {nb / us / 1e3:8.1f} GB/s "
-          f"({nb / 1e6:.2f} MB, ring {k})", flush=True)
+    print(f"{layout}{bits} [{rows},{cols}] N={n}" + (f" {zero_groups:.0%} zero groups" if zero_groups else "") +
+          f": {us:8.2f} us/launch {nb / us / 1e3:8.1f} GB/s ({nb / 1e6:.2f} MB, ring {k})", flush=True)
     return us
+
+
+def sparse_sweep():
+    """The exact zero-group skip of the single-vector GEMV: launch time against the share of
+    32-column groups whose activations are all zero (file bytes / time, so the rate rises)."""
+    for args in [("sb6", 4, 2048, 8192), ("sb6", 5, 65536, 2048), ("sym", 6, 2048, 8192)]:
+        for z in (0.0, 0.35, 0.7):
+            time_ring(*args, zero_groups=z)
 
 
 def sweep():
@@ -492,11 +508,12 @@ def main():
     g = sub.add_parser("gemv")
     g.add_argument("layout"); g.add_argument("bits", type=int); g.add_argument("rows", type=int)
     g.add_argument("cols", type=int); g.add_argument("--n", type=int, default=1)
-    g.add_argument("--launches", type=int, default=4)
+    g.add_argument("--launches", type=int, default=4); g.add_argument("--zero-groups", type=float, default=0.0)
     d = sub.add_parser("decode")
     d.add_argument("--layers", type=int, default=4); d.add_argument("--recipe", default="compression")
     d.add_argument("--steps", type=int, default=3); d.add_argument("--batch", type=int, default=1)
     sub.add_parser("sweep")
+    sub.add_parser("sparse-sweep")
     pf = sub.add_parser("prefill")
     pf.add_argument("--layers", type=int, default=24); pf.add_argument("--recipe", default="reduction")
     pf.add_argument("--T", type=int, default=512); pf.add_argument("--batch", type=int, default=1)
@@ -554,6 +571,9 @@ def main():
     if a.cmd == "gemm-timeline":
         gemm_timeline("sb6", a.bits, a.rows, a.cols, a.M, a.acc_mode)
         return
+    if a.cmd == "sparse-sweep":
+        sparse_sweep()
+        return
     if a.cmd == "gemm-sweep":
         gemm_sweep(a.recipe, acc_mode=a.acc_mode)
         return
@@ -561,7 +581,7 @@ def main():
         tp_chain(a.model, a.recipe, a.exchange)
         return
     if a.cmd == "gemv":
-        gemv(a.layout, a.bits, a.rows, a.cols, a.n, a.launches)
+        gemv(a.layout, a.bits, a.rows, a.cols, a.n, a.launches, a.zero_groups)
     elif a.cmd == "decode":
         decode(a.layers, a.recipe, a.steps, a.batch)
     elif a.cmd == "prefill":

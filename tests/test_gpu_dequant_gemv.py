@@ -426,3 +426,31 @@ def test_c_reader_upload_feeds_the_kernels(cuda_lib, name):
         for s in slabs:
             cuda_lib.rwkvq_file_free_slab(s)
         cuda_lib.rwkvq_file_close(h)
+
+
+@pytest.mark.parametrize("layout,bits", LAYOUTS[:6])
+def test_gemv_skips_all_zero_activation_groups_exactly(cuda_lib, layout, bits):
+    """relu(k)^2 leaves most channel-mix activations exactly zero; the single-vector kernel does not
+    read the codes of a 32-column group whose activations are all zero.  Same bar as the dense
+    case (and the rows of a 2-row call, which run one by one, agree bit for bit with single calls)."""
+    from rwkv_quant_b200.backends.cuda import ops
+    rows, cols = 2048, 8192
+    qt = _synth_linear(layout, bits, rows, cols, seed=17 + bits)
+    dq = ops.DeviceQT(qt)
+    w = _oracle_w(qt).astype(np.float64)
+    rs = np.random.default_rng(5)
+    x = np.maximum(rs.standard_normal((2, cols)), 0.0).astype(np.float32) ** 2       # ~50 % zeros
+    groups = rs.random((2, cols // 32)) < 0.6                                         # + 60 % of the groups entirely zero
+    x = (x.reshape(2, cols // 32, 32) * ~groups[..., None]).reshape(2, cols)
+    x[1, :32 * 200] = 0.0                                                             # a long zero run, whole iterations
+    xt = torch.from_numpy(x).cuda()
+    y = ops.gemv(dq.bufs, dq.meta, xt, 0, None).cpu().numpy()
+    ref = x.astype(np.float64) @ w.T
+    assert relmax(y, ref) <= TOL and np.isfinite(y).all()
+    print(f"{layout}@{bits} zero-group skip: relmax {relmax(y, ref):.2e}")
+    for r in range(2):
+        y1 = ops.gemv(dq.bufs, dq.meta, xt[r:r + 1].contiguous(), 0, None).cpu().numpy()
+        assert np.array_equal(y1[0], y[r])
+    # an all-zero vector gives exact zeros
+    z = ops.gemv(dq.bufs, dq.meta, torch.zeros(1, cols, device="cuda"), 0, None)
+    assert (z == 0).all()
