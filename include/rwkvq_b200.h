@@ -150,7 +150,7 @@ int rwkvq_outlier_tail(const int32_t* row_ptr, const int32_t* cols, const float*
  * GEMV kernels of the reference, which decode each weight once for up to 4 columns and loop
  * over chunks of 4 (GwQuantLinear._gemv_nb / _get_kernel_k3nb, backends/metal/quant_linear_gw.py:
  * 658-744, 850-905; SymQuantLinear._gemv, quant_linear_sym.py:485-516): here one pass serves
- * up to 32 columns (groups of 32 beyond that, walked by one launch).
+ * up to 16 columns per CTA (the token groups of a larger batch run side by side in one launch).
  *   x [N, ldx] fp32 (rows 16-byte aligned, ldx % 4 == 0), y / resid [N, ldy] fp32.
  *   Tensors: sb6 with dev_meta (and dev_planes at 5 / 6 bits), sym (dev_planes at 6 bits),
  *   per-row int8 with cols % 128 == 0; RWKVQ_E_DTYPE otherwise (use rwkvq_gemv).

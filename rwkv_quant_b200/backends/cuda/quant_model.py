@@ -391,10 +391,10 @@ class QuantRWKV7:
 
     def decode_groups(self, batch_size: int) -> int:
         """Stream groups whose launch chains run side by side (see ``Decoder``).  Measured on B200
-        (1.5B, ms per step, one group / two groups): with the default two-term linears 64 streams
-        4.91 / 4.42, 32 streams 3.35 / 3.02, 16 streams 2.21 / 2.61; with RWKVQ_BATCH_FAST=1 one group
-        wins at every size (64 streams: 3.57 on the tcgen05 linears).  More than two groups lose."""
-        return 2 if (batch_size >= 32 and not ops.batch_fast()) else 1
+        (1.5B, ms per step, one group / two groups): 64 streams 4.20 / 4.38, 32 streams 3.02 / 3.03,
+        16 streams 2.13 / 2.54 with the default two-term linears (which walk 16-token tiles inside one
+        launch), 3.57 / 3.8 at 64 streams with RWKVQ_BATCH_FAST=1.  One group is the default."""
+        return 1
 
     @property
     def launches_per_token(self) -> int:

@@ -603,8 +603,14 @@ template <int L>
 int launch_bt_l(BatchArgs& a, int n_mats, int rows, int cols, int N, bool exact, cudaStream_t s) {
     using G = Geo<L>;
     const int n_iters = cols / G::KI;
-    // the two-term kernel works on at most 32 tokens at a time (grid.z walks the groups of a larger batch)
-    const int nt = N <= 8 ? 1 : N <= 16 ? 2 : (N <= 32 || exact) ? 4 : 8;
+    // The two-term kernel works on 16 tokens at a time (grid.z walks the groups of a larger batch): measured
+    // inside the decode graph, two CTAs with 16 tokens each beat one with 32 on every shape (3 MMAs per step
+    // make the 32-token tile MMA-issue bound, and its staged K slice no longer fits unchunked), and for
+    // K >= 8192 one with 8 beats one with 16.
+    int nt = exact ? (N <= 8 || (N <= 16 && cols >= 8192) ? 1 : 2) : N <= 8 ? 1 : N <= 16 ? 2 : N <= 32 ? 4 : 8;
+    const bool forced = g_batch_force_ks > 0 && (g_batch_force_rows == 0 || (g_batch_force_rows == rows && g_batch_force_cols == cols));
+    if (forced && (g_batch_force_ks & 64) && nt > 1) nt /= 2;      // profiling: half the token tile, twice the token groups
+    if (forced && (g_batch_force_ks & 128) && nt > 1) nt /= 2;     // ... and half again
     const int n8 = nt * 8, n_groups = (N + n8 - 1) / n8;
     const int n_tiles = (rows + 15) / 16;
     const int mats = n_mats * n_groups;
@@ -641,8 +647,7 @@ int launch_bt_l(BatchArgs& a, int n_mats, int rows, int cols, int N, bool exact,
         }
     }
     int ks = best_ks, tpc = best_tpc;
-    if (g_batch_force_ks > 0 && n_iters % (g_batch_force_ks & 15) == 0 &&
-        (g_batch_force_rows == 0 || (g_batch_force_rows == rows && g_batch_force_cols == cols))) {
+    if (forced && (g_batch_force_ks & 15) > 0 && n_iters % (g_batch_force_ks & 15) == 0) {
         ks = g_batch_force_ks & 15;
         if (g_batch_force_ks & 16) tpc = 16;
         if (g_batch_force_ks & 32) tpc = 8;

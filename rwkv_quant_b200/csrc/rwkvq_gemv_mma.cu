@@ -56,11 +56,11 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaAr
     const char* xv = a.xk[blockIdx.y] ? static_cast<const char*>(a.xk[blockIdx.y])
                                       : static_cast<const char*>(a.x) + (a.fused ? blockIdx.y * a.ldx * esz : 0);
     bool finite;
-    const float unscale = prepare_x(xv, a.x_dtype, n_in, x_bits<L>(), dig, xs16, red, finite, zflag);
+    const float unscale = prepare_x(xv, a.x_dtype, n_in, x_bits<L>(), dig, xs16, red, finite, a.zero_skip ? zflag : nullptr);
     __syncthreads();
     // exact sparsity skip: groups of 32 columns whose activations are all zero (relu(k)^2 in the channel
     // mix) are not read from the second fetch on
-    zf = zflag;
+    if (a.zero_skip) zf = zflag;
 
     int c_n = 0, buf = 0;
     for (int base = blockIdx.x * WT; base < n_tiles; base += step, buf ^= 1) {
@@ -218,6 +218,7 @@ static int launch_one(MmaArgs& a, int rows, int cols, int n_mats, int KS, cudaSt
     const int units = ((rows + 15) / 16 + WT - 1) / WT;
     const int cap = kResidentCtas / (n_mats * KS) > 0 ? kResidentCtas / (n_mats * KS) : 1;
     a.rows_padded = ((rows + 15) / 16) * 16;
+    a.zero_skip = cols >= 4096;        // rows as long as the channel-mix hidden vector, the one input with exact zeros
     cudaError_t le = launch_pdl(gemv_mma_kernel<L, WK, SPLIT>, dim3(units < cap ? units : cap, n_mats, KS),
                                 dim3(kMmaWarps * 32), smem, s, a);
     if (le != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "gemv_mma: %s", cudaGetErrorString(le));

@@ -47,6 +47,7 @@ struct MmaArgs {
     float* partial;
     unsigned int* counters;
     int rows_padded;
+    int zero_skip;            // leave the codes of all-zero activation groups unread (set for long rows: channel-mix value)
 };
 
 template <bool A_UNSIGNED>
@@ -254,7 +255,7 @@ __device__ __forceinline__ void split_digits(int X, int& d1, int& d2, int& d3) {
 // x is read once: up to kXRegs float4 per thread stay in registers between the max
 // pass and the conversion pass (IN <= 8192 at 256 threads); longer vectors are re-read.
 constexpr int kXRegs = 8;
-// zflag[c / 32] = 1 where all 32 fixed-point activations of the aligned group are zero: the
+// zflag (optional): zflag[c / 32] = 1 where all 32 fixed-point activations of the aligned group are zero: the
 // weights of such a group contribute exactly nothing (integer products, and the block min
 // multiplies the group's sum), so the loader may leave them unread (load_frag).
 __device__ __forceinline__ float prepare_x(const void* x, int dtype, int n_in, int bits, int8_t* dig,
@@ -301,8 +302,10 @@ __device__ __forceinline__ float prepare_x(const void* x, int dtype, int n_in, i
         s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
         if ((tid & 3) == 0) xs16[i >> 2] = static_cast<float>(s);
         // 8 consecutive lanes cover 32 columns (whole warps get here together)
-        const unsigned nz = __ballot_sync(0xFFFFFFFFu, (X0 | X1 | X2 | X3) != 0);
-        if ((tid & 7) == 0) zflag[i >> 3] = ((nz >> (tid & 24)) & 0xFFu) == 0u;
+        if (zflag != nullptr) {
+            const unsigned nz = __ballot_sync(0xFFFFFFFFu, (X0 | X1 | X2 | X3) != 0);
+            if ((tid & 7) == 0) zflag[i >> 3] = ((nz >> (tid & 24)) & 0xFFu) == 0u;
+        }
     };
 #pragma unroll
     for (int k = 0; k < kXRegs; ++k) {
