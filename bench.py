@@ -14,9 +14,12 @@ One JSON line is printed by rank 0:
              timed with CUDA events, max over ranks
   e2e        tokens/s through QuantRWKV7.decoder().step() with the token ids coming from pinned host
              memory and the argmax read back to the host every step
-  roofline   the whole step of one GPU: (file-format weight bytes + WKV state read and written for its
-             streams) / step time against the measured HBM copy bandwidth; `linear_phase` gives the
-             same for the quantized-linear launches alone (6 per layer + head, replayed as a graph)
+  roofline   the dominant kernel: the quantized-linear launches of one step (6 per layer + head) replayed
+             as a graph; algorithmic bytes = their file-format bytes + activation rows, against the
+             measured HBM copy bandwidth; `traffic` = the DRAM bytes of the same launches under ncu
+  step_roofline  the whole step of one GPU: (file-format weight bytes + WKV state read and written for
+             its streams) / step time
+  fast_mode  (N = 1) the same step with RWKVQ_BATCH_FAST=1 arithmetic (single fp16 operands), for comparison
   b1         (N = 1) the single-stream configuration with its own device time, e2e and rooflines
   prefill    (N = 1) pp512 at batch 1 and 16 on a `reduction` build: tokens/s, e2e, FLOP rate against
              the measured bf16 tensor peak
@@ -227,6 +230,10 @@ def linear_phase(model, B, steps, warmup):
 # dram__bytes_read.sum + dram__bytes_write.sum of the quantized-linear launches of one decoded token
 # (1.5B compression, one stream), from the ncu capture summarised under profiles/
 NCU_GEMV_PHASE_DRAM_BYTES_B1 = 828225280 + 342272
+# the same for one step of 64 streams on the default (two-term) small-batch kernels: 24 x 45.60 MB per layer
+# (r/k/v 12.63, output projection 6.11, ffn key 13.19, ffn value 13.68) + 101.84 MB for the head, from a 2-layer
+# capture (profiles/decode_step_b64_b8_launch_list_1p5b_compression.md); traffic grows with the layer count
+NCU_BATCH_PHASE_DRAM_BYTES_B64 = 24 * 45602560 + 101837824
 
 
 def time_decode(model, B, prompt, steps, warmup, sync_all, clock_index=None, groups=None):
@@ -442,13 +449,16 @@ def run_ours(a, rank, world, local_rank):
         "e2e": {"value": total_tokens / t_e2e, "unit": "tok/s", "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 8 * B},
         "gpu_launches": launches,
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "achieved": step_bytes / sec_step / 1e9, "peak": peak, "unit": "GB/s",
-                     "frac": step_bytes / sec_step / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
-                     "what": "whole decode step of one GPU: file-format weight bytes + WKV state read and written "
-                             "for its streams, per step time",
-                     "bytes_per_step": step_bytes, "us_per_step": sec_step * 1e6},
-        "linear_phase": {"bound": "hbm", "achieved": g_bytes / g_sec / 1e9, "peak": peak, "unit": "GB/s",
-                         "frac": g_bytes / g_sec / 1e9 / peak, "traffic": None,
+        "step_roofline": {"bound": "hbm", "achieved": step_bytes / sec_step / 1e9, "peak": peak, "unit": "GB/s",
+                          "frac": step_bytes / sec_step / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
+                          "what": "whole decode step of one GPU: file-format weight bytes + WKV state read and written "
+                                  "for its streams, per step time",
+                          "bytes_per_step": step_bytes, "us_per_step": sec_step * 1e6},
+        "roofline": {"bound": "hbm", "achieved": g_bytes / g_sec / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": g_bytes / g_sec / 1e9 / peak, "peak_kind": peak_kind,
+                         "traffic": NCU_BATCH_PHASE_DRAM_BYTES_B64 if (a.model, a.recipe, B, fast_env) == ("1.5b", "compression", 64, False) else None,
+                         "what": "the dominant kernel (72 % of a 64-stream step in the ncu launch list): file-format bytes of the "
+                                 "quantized linears + their activation rows / time of those launches replayed as one graph",
                          "kernel": (f"row_amax_kernel + {'gemm_tcb_kernel' if (fast_env and B > 32) else 'gemv_batch_kernel'}, "
                                     f"the {g_launches} launches of the quantized linears of one step at "
                                     f"{B} streams" if B > 2 else f"gemv_mma_kernel, {g_launches} launches"),
