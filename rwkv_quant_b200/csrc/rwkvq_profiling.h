@@ -18,7 +18,8 @@ void rwkvq_profiling_gemm_acc_mode(int mode);
 /* With a device buffer of 8 uint64 set, CTA (0,0,0) of every later small-batch launch records
  * global-timer nanoseconds: 0 start, 1 producer done, 2 activations staged, 3 products done,
  * 4 cluster barrier passed, 5 reduced and stored, 6 end.  force_ks > 0 overrides the launcher's choice:
- * low 4 bits the cluster size, +16 groups of 256 rows, +32 groups of 128 rows. */
+ * low 4 bits the cluster size (0: keep the launcher's), +16 groups of 256 rows, +32 groups of 128 rows,
+ * +64 half the token tile (twice the token groups), +128 half again. */
 void rwkvq_profiling_batch_trace(void* buf8, int force_ks);
 /* The same override for tensors of one shape only (rows = 0: every shape); 0 switches it off. */
 void rwkvq_profiling_batch_force(int force_ks, int rows, int cols);
