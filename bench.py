@@ -55,6 +55,7 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the b1 / prefill / big blocks")
+    ap.add_argument("--with-big", action="store_true", help="run the 2.9B 256-stream block at this N too (default: N = 8 only)")
     return ap.parse_args()
 
 
@@ -402,7 +403,7 @@ def run_ours(a, rank, world, local_rank):
         torch.cuda.empty_cache()
         extras["prefill"] = prefill_block(dev, a.model, peaks, peak_kind)
         model = None
-    if not a.no_extras and world == 8:
+    if (not a.no_extras and world == 8) or a.with_big:
         # RWKV-7 2.9B, 256 concurrent streams, 32 per GPU
         del model
         torch.cuda.empty_cache()
