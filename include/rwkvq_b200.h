@@ -145,6 +145,22 @@ int rwkvq_outlier_tail(const int32_t* row_ptr, const int32_t* cols, const float*
                        int x_dtype, int N, int64_t ldx, float* y, int64_t ldy, int epilogue, const float* resid, void* stream);
 
 /*
+ * Block quantizer for the sb6 layout on the device.  Stands behind the reference's host-side search
+ * quantizer (calibration/groupwise.py:207-300 `_gw_one` with 8 blocks of 32 per super-block, as called by
+ * formats/writer.py:236-269 `_make_qt_gw_sb6` for the modes asym_sb6 / asym_sb6_search / asym_sb6_aw).
+ *   w [rows, ldw] fp32 on the device, cols a multiple of 256; bits 4, 5 or 6;
+ *   search != 0: the 8-factor scale search with least-squares refit per block (asym_sb6_search);
+ *   ex2 (optional, [cols] fp32): E[x^2] of the input channels, weights of the search criterion (asym_sb6_aw).
+ * Outputs (device): q [rows, cols] codes 0 .. 2^bits - 1, qs [rows, cols/32] scale codes 1 .. 63,
+ * qm [rows, cols/32] min codes -31 .. 31, d / dm [rows, cols/256] fp16 super-scales: the `parts` of the
+ * reference, which its packers (and rwkv_quant_b200.quantize) turn into the file buffers.
+ * Arithmetic as in the reference (fp32, IEEE division, round-half-to-even); sums over a block run in a
+ * different order than torch's, so a code can differ where a quotient sits on a rounding boundary.
+ */
+int rwkvq_quantize_sb6(const float* w, int64_t ldw, int rows, int cols, int bits, int search, const float* ex2,
+                       uint8_t* q, uint8_t* qs, int8_t* qm, void* d, void* dm, void* stream);
+
+/*
  * The same product for a SMALL BATCH of right-hand sides (decode streams, short verify runs)
  * with every packed weight byte read once for the whole batch.  Stands behind the multi-column
  * GEMV kernels of the reference, which decode each weight once for up to 4 columns and loop

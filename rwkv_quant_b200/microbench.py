@@ -426,6 +426,28 @@ def time_ring(layout, bits, rows, cols, n=1, ring_bytes=1.5e9, iters=5, zero_gro
     return us
 
 
+def quantize_time(rows=10240, cols=2560, reps=5):
+    """rwkvq_quantize_sb6 (scale search + least-squares refit) on one channel-mix matrix of RWKV-7 2.9B:
+    milliseconds per call and weights per second, kernel only and with the bit packing."""
+    from . import quantize
+    w = torch.randn(rows, cols, device="cuda") * 0.02
+    for bits in (4, 5, 6):
+        quantize.quantize_sb6_parts(w, bits)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(); e0.record()
+        for _ in range(reps):
+            quantize.quantize_sb6_parts(w, bits)
+        e1.record(); torch.cuda.synchronize()
+        ms_k = e0.elapsed_time(e1) / reps
+        e0.record()
+        for _ in range(reps):
+            quantize.quantize_sb6("k", "cmix", w, bits)
+        e1.record(); torch.cuda.synchronize()
+        ms_p = e0.elapsed_time(e1) / reps
+        print(f"quantize sb6@{bits} [{rows},{cols}] search: kernel {ms_k:.2f} ms ({rows * cols / ms_k / 1e6:.1f} G weights/s), "
+              f"with packing {ms_p:.2f} ms", flush=True)
+
+
 def sparse_sweep():
     """The exact zero-group skip of the single-vector GEMV: launch time against the share of
     32-column groups whose activations are all zero (file bytes / time, so the rate rises)."""
@@ -514,6 +536,7 @@ def main():
     d.add_argument("--steps", type=int, default=3); d.add_argument("--batch", type=int, default=1)
     sub.add_parser("sweep")
     sub.add_parser("sparse-sweep")
+    sub.add_parser("quantize")
     pf = sub.add_parser("prefill")
     pf.add_argument("--layers", type=int, default=24); pf.add_argument("--recipe", default="reduction")
     pf.add_argument("--T", type=int, default=512); pf.add_argument("--batch", type=int, default=1)
@@ -570,6 +593,9 @@ def main():
         return
     if a.cmd == "gemm-timeline":
         gemm_timeline("sb6", a.bits, a.rows, a.cols, a.M, a.acc_mode)
+        return
+    if a.cmd == "quantize":
+        quantize_time()
         return
     if a.cmd == "sparse-sweep":
         sparse_sweep()
