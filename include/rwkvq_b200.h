@@ -161,6 +161,17 @@ int rwkvq_quantize_sb6(const float* w, int64_t ldw, int rows, int cols, int bits
                        uint8_t* q, uint8_t* qs, int8_t* qm, void* d, void* dm, void* stream);
 
 /*
+ * The same for the symmetric layout (blocks of 16, int8 block-scale codes against one fp16 per 256 weights);
+ * stands behind calibration/groupwise.py:358-473 `_sym_one` as called by formats/writer.py `_make_qt_gw_sym`
+ * (modes sym, sym_aw, sym_plain; outlier fractions are not supported, as in the reference's packed path).
+ *   bits 6 or 8; factors [n_factors] fp32 on the device: the scale factors of the search — the reference's
+ *   19 float32 nodes of torch.linspace(0.7, 1.15, 19), or {1.0} for the plain mode; ex2 as above.
+ * Outputs (device): q [rows, cols] signed codes, qs [rows, cols/16] int8 scale codes, d [rows, cols/256] fp16.
+ */
+int rwkvq_quantize_sym(const float* w, int64_t ldw, int rows, int cols, int bits, const float* factors, int n_factors,
+                       const float* ex2, int8_t* q, int8_t* qs, void* d, void* stream);
+
+/*
  * The same product for a SMALL BATCH of right-hand sides (decode streams, short verify runs)
  * with every packed weight byte read once for the whole batch.  Stands behind the multi-column
  * GEMV kernels of the reference, which decode each weight once for up to 4 columns and loop

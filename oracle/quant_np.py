@@ -1,4 +1,4 @@
-"""CPU oracle of the sb6 block quantizer (test infrastructure: only tests import this).
+"""CPU oracle of the sb6 and sym block quantizers (test infrastructure: only tests import this).
 
 A numpy restatement of the reference's search quantizer for the `sb6` layout,
 `rwkv_quant/calibration/groupwise.py:207-300` (`_gw_one` with sb = 8 and sb_bits = -6 for the
@@ -115,3 +115,44 @@ def unpack_sb6(codes_packed, qsqm, d, dm, *, shape, qh=None, qh2=None):
     qs = oc.sixbit_stream(rec[..., :6], 8).reshape(OUT, IN // 32).astype(np.uint8)
     qm = (oc.sixbit_stream(rec[..., 6:], 8).reshape(OUT, IN // 32).astype(np.int16) - 31).astype(np.int8)
     return q.reshape(OUT, IN), qs, qm
+
+
+def quant_sym(w: np.ndarray, bits: int, factors, ex2: np.ndarray | None = None):
+    """The symmetric layout (blocks of 16, super-blocks of 16 blocks): restates
+    `calibration/groupwise.py:358-473` `_sym_one` without outliers.  `factors`: the float32 nodes the
+    reference searches over (torch.linspace(0.7, 1.15, 19)) or (1.0,) for the plain mode.
+    -> dict(q i8 [OUT, IN], qs i8 [OUT, IN/16], d f16 [OUT, IN/256], deq f32)."""
+    f32 = np.float32
+    w = np.ascontiguousarray(w, dtype=f32)
+    OUT, IN = w.shape
+    assert IN % 256 == 0
+    gs, sb = 16, 16
+    nb = IN // gs
+    wg = w.reshape(OUT, nb, gs)
+    evg = None if ex2 is None else np.maximum(np.asarray(ex2, dtype=f32), f32(1e-12)).reshape(1, nb, gs)
+    qmax = f32(2 ** (bits - 1) - 1)
+    qmin = -qmax - f32(1)
+    base = np.maximum(np.abs(wg).max(axis=2, keepdims=True), f32(1e-12)) / qmax
+    best_s, best_e = base.copy(), None
+    for f in factors:
+        s = base * f32(f)
+        qv = np.clip(np.rint(wg / s), qmin, qmax)
+        e = (wg - qv * s) ** 2
+        err = (e if evg is None else evg * e).sum(axis=2, keepdims=True, dtype=f32)
+        if best_e is None:
+            best_s, best_e = s, err
+        else:
+            b = err < best_e
+            best_s = np.where(b, s, best_s)
+            best_e = np.minimum(best_e, err)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        ssb = best_s.reshape(OUT, nb // sb, sb, 1)
+        d = _h(np.maximum(ssb.max(axis=2, keepdims=True) / f32(127), f32(1e-12)))
+        qs = np.clip(np.rint(ssb / d), -128, 127)
+        scale_q = _h((qs * d).reshape(OUT, nb, 1))
+        nz = np.abs(scale_q) > 0
+        qv = np.clip(np.rint(wg / np.where(nz, scale_q, f32(1))), qmin, qmax)
+        qv = np.where(nz, qv, f32(0))
+    deq = (qv * scale_q).reshape(OUT, IN)
+    return {"q": qv.reshape(OUT, IN).astype(np.int8), "qs": np.nan_to_num(qs, nan=0.0).reshape(OUT, nb).astype(np.int8),
+            "d": d.reshape(OUT, -1).astype(np.float16), "deq": deq.astype(np.float32)}

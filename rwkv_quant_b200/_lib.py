@@ -71,6 +71,8 @@ _PROTOS = {
                                      C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
     "rwkvq_quantize_sb6": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                      C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "rwkvq_quantize_sym": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p,
+                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rwkvq_gemv_batch_workspace_bytes": (C.c_size_t, [C.c_int]),
     "rwkvq_gemv_batch": (C.c_int, [C.POINTER(QTensorStruct), C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_int64,
                                    C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),

@@ -92,3 +92,33 @@ def test_quantize_sb6_refusals(cuda_lib):
         quantize.quantize_sb6_parts(torch.randn(4, 512, device="cuda"), 7)
     with pytest.raises(ValueError):
         quantize.quantize_sb6("k", "cmix", torch.randn(4, 512, device="cuda"), 4, "asym_sb6_aw")
+
+
+@pytest.mark.parametrize("bits,mode", [(6, "sym"), (8, "sym"), (6, "sym_plain"), (8, "sym_aw"), (6, "sym_aw")])
+def test_quantize_sym_matches_oracle(cuda_lib, bits, mode):
+    from rwkv_quant_b200 import quantize
+    from rwkv_quant_b200.backends.cuda import ops
+    g = torch.Generator().manual_seed(bits * 5 + len(mode))
+    w = torch.randn(200, 2048, generator=g) * 0.03
+    w[3] = 0.0                                  # all-zero row: scale codes and codes 0
+    w[5, 10:14] *= 60.0
+    ex2 = (torch.rand(2048, generator=g) ** 2 * 3 + 1e-3) if mode == "sym_aw" else None
+    factors = quantize.sym_factors().tolist() if mode != "sym_plain" else (1.0,)
+    ref = qn.quant_sym(w.numpy(), bits, factors, None if ex2 is None else ex2.numpy())
+    q, qs, d = (t.cpu().numpy() for t in quantize.quantize_sym_parts(w.cuda(), bits, mode != "sym_plain", None if ex2 is None else ex2.cuda()))
+    eq = {"q": (q == ref["q"]).mean(), "qs": (qs == ref["qs"]).mean(), "d": (d == ref["d"]).mean()}
+    print(f"sym@{bits} {mode}: equal fractions", {k: f"{v:.6f}" for k, v in eq.items()})
+    assert eq["q"] >= 0.9995 and eq["qs"] >= 0.999 and eq["d"] >= 0.995
+    qt = quantize.quantize_sym("blocks.0.att.key.weight", "proj", w.cuda(), bits, mode, None if ex2 is None else ex2.cuda())
+    dq = ops.DeviceQT(qt)
+    deq = dq.dequant().cpu().numpy()
+    s = (qs.astype(np.float32).reshape(200, -1, 16) * d.astype(np.float32)[..., None]).astype(np.float16).astype(np.float32)
+    own = q.reshape(200, -1, 16).astype(np.float32) * s.reshape(200, -1, 1)
+    assert np.array_equal(deq, own.reshape(200, 2048))
+    assert (deq[3] == 0).all()
+    e_ref, e_our = float(((ref["deq"] - w.numpy()) ** 2).sum()), float(((deq - w.numpy()) ** 2).sum())
+    assert abs(e_our - e_ref) <= 1e-4 * e_ref
+    x = torch.randn(1, 2048, device="cuda")
+    y = ops.gemv(dq.bufs, dq.meta, x, 0, None).cpu().numpy()
+    yr = x.cpu().numpy().astype(np.float64) @ deq.astype(np.float64).T
+    assert np.abs(y - yr).max() <= 1e-3 * np.abs(yr).max()

@@ -57,3 +57,25 @@ def test_quantizer_oracle_matches_reference_live(bits, search, aw):
     e_ref = float(((ref["deq"].numpy() - w.numpy()) ** 2).sum()), 
     e_our = float(((r["deq"] - w.numpy()) ** 2).sum())
     assert abs(e_our - e_ref[0]) <= 1e-3 * e_ref[0]
+
+
+@pytest.mark.skipif(not os.path.isdir(REF), reason="reference tree not present")
+@pytest.mark.parametrize("bits,search,aw", [(6, True, False), (8, True, False), (6, False, False), (8, True, True)])
+def test_sym_quantizer_oracle_matches_reference_live(bits, search, aw):
+    sys.path.insert(0, REF)
+    try:
+        from rwkv_quant.calibration.groupwise import _SYM_FACTORS, _sym_one
+    finally:
+        sys.path.remove(REF)
+    assert list(_SYM_FACTORS) == torch.linspace(0.7, 1.15, 19).tolist()
+    g = torch.Generator().manual_seed(bits + 3 * search + aw)
+    w = torch.randn(64, 1024, generator=g) * 0.05
+    w[2] = 0.0                                   # an all-zero row: degenerate super-blocks
+    w[4, 16:20] *= 50.0
+    ex2 = (torch.rand(1024, generator=g) ** 2 * 4 + 1e-3) if aw else None
+    ref = _sym_one(w, bits, 16, 16, ex2, search, 0.0, True)
+    r = qn.quant_sym(w.numpy(), bits, _SYM_FACTORS if search else (1.0,), None if ex2 is None else ex2.numpy())
+    assert (r["q"] == ref["q"].numpy()).mean() >= 0.9995
+    assert (r["qs"] == ref["qs"].numpy()).mean() >= 0.999 and (r["d"] == ref["d"].numpy()).mean() >= 0.995
+    e_ref, e_our = float(((ref["deq"].numpy() - w.numpy()) ** 2).sum()), float(((r["deq"] - w.numpy()) ** 2).sum())
+    assert abs(e_our - e_ref) <= 1e-3 * e_ref
