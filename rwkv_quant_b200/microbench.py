@@ -61,6 +61,55 @@ def decode(layers=4, recipe="compression", steps=3, batch=1, model="1.5b"):
     print("ok", dec.next_tokens.tolist())
 
 
+def tp_model_time(model="2.9b", recipe="compression", exchange="p2p", layers=32, steps=8):
+    """Whole-model head-sharded decode (tp_model.TPQuantRWKV7, launches issued from Python) for the
+    ranks of a torchrun launch: milliseconds per single-token step at 1 and 64 streams and per
+    pp512 pass, max over ranks, beside the same calls on one GPU through the same Python path
+    and through the one-call decode step."""
+    import os
+
+    import torch.distributed as dist
+
+    from . import tp, tp_model
+    rank, local = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    ck = synth.build_checkpoint(model, recipe, seed=0, device=dev, n_layer=layers)
+    g = tp.TPGroup(device=dev, exchange=exchange)
+    m = tp_model.TPQuantRWKV7(ck, g, device=dev)
+    ref = QuantRWKV7(ck, device=dev)
+
+    def timed(fn, n):
+        fn()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    for B in (1, 64):
+        tok = torch.randint(1, 60000, (B, 1), device=dev)
+        st_t, st_r, st_c = m.init_state(B), ref.init_state(B), ref._materialize(ref.init_state(B), B)
+        t_tp = timed(lambda: m.forward_stateful(tok, st_t), steps)
+        x1, _ = ref.forward_hidden(tok, st_r)          # same Python path on one GPU
+        t_py = timed(lambda: ref.forward_hidden(tok, st_r), steps)
+        t_c = timed(lambda: ref._decode(tok.reshape(B), st_c), steps)
+        if rank == 0:
+            print(f"tp-model {model} {recipe} {layers} layers x{g.world} ({exchange}), {B} stream(s): {t_tp:.2f} ms per step; "
+                  f"one GPU, same Python path {t_py:.2f} ms, one-call decode step {t_c:.2f} ms", flush=True)
+    idx = torch.randint(1, 60000, (1, 512), device=dev)
+    t_tp = timed(lambda: m.forward_stateful(idx, m.init_state(1), last_only=True), 2)
+    t_1 = timed(lambda: ref.forward_stateful(idx, ref.init_state(1), last_only=True), 2)
+    if rank == 0:
+        print(f"tp-model pp512 batch 1: {t_tp:.1f} ms on {g.world} GPUs, {t_1:.1f} ms on one", flush=True)
+    g.close()
+    dist.destroy_process_group()
+
+
 def tp_chain(model="2.9b", recipe="compression", exchange="p2p", iters=200):
     """Row-split tensor-parallel GEMV chain of one layer (output projection, ffn key, ffn
     value: three exchanges) plus the head, for the ranks of a torchrun launch (one process
@@ -543,6 +592,9 @@ def main():
     tpp = sub.add_parser("tp")
     tpp.add_argument("--model", default="2.9b"); tpp.add_argument("--recipe", default="compression")
     tpp.add_argument("--exchange", default="p2p", choices=["p2p", "nccl", "none"])
+    tm = sub.add_parser("tp-model")
+    tm.add_argument("--model", default="2.9b"); tm.add_argument("--recipe", default="compression")
+    tm.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"]); tm.add_argument("--layers", type=int, default=32)
     go = sub.add_parser("gemm")
     go.add_argument("layout"); go.add_argument("bits", type=int); go.add_argument("rows", type=int)
     go.add_argument("cols", type=int); go.add_argument("--M", type=int, default=8192)
@@ -602,6 +654,9 @@ def main():
         return
     if a.cmd == "gemm-sweep":
         gemm_sweep(a.recipe, acc_mode=a.acc_mode)
+        return
+    if a.cmd == "tp-model":
+        tp_model_time(a.model, a.recipe, a.exchange, a.layers)
         return
     if a.cmd == "tp":
         tp_chain(a.model, a.recipe, a.exchange)

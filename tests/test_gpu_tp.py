@@ -79,3 +79,71 @@ def test_row_split_gemv_two_gpus(tmp_path):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     assert "RANK0_OK" in r.stdout
+
+
+MODEL_WORKER = r'''
+import os, sys, numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from rwkv_quant_b200 import synth, tp, tp_model
+from rwkv_quant_b200.backends.cuda import QuantRWKV7
+rank = int(os.environ["RANK"]); local = int(os.environ["LOCAL_RANK"])
+torch.cuda.set_device(local)
+dev = torch.device("cuda", local)
+dist.init_process_group("nccl", device_id=dev)
+rel = lambda a, b: float((a - b).abs().max() / b.abs().max())
+for recipe in ("compression", "reduction"):
+    # RWKV-7 2.9B widths (D 2560 = 40 heads, FFN 10240), 2 layers, a 4096-row vocabulary
+    ck = synth.build_checkpoint("2.9b", recipe, seed=11, device="cpu", n_layer=2, vocab=4096, keep_on_device=False)
+    ref = QuantRWKV7(ck, device=dev)
+    for exchange in ("p2p", "nccl"):
+        g = tp.TPGroup(device=dev, exchange=exchange)
+        m = tp_model.TPQuantRWKV7(ck, g, device=dev)
+        assert m.n_head_local == 20 and m.blocks[0].Wr.rows == 1280 and m.blocks[0].Wo.cols == 1280
+        idx = torch.from_numpy(np.random.default_rng(5).integers(1, 4000, (2, 9))).to(dev)
+        # prefill of 6 tokens, then 3 single-token steps from the returned (head-sharded) state
+        lo_r, st_r = ref.forward_stateful(idx[:, :6], ref.init_state(2))
+        lo_t, st_t = m.forward_stateful(idx[:, :6], m.init_state(2))
+        errs = [rel(lo_t, lo_r)]
+        for t in range(6, 9):
+            lo_r, st_r = ref.forward_stateful(idx[:, t:t + 1], st_r)
+            lo_t, st_t = m.forward_stateful(idx[:, t:t + 1], st_t)
+            errs.append(rel(lo_t, lo_r))
+        torch.cuda.synchronize(); g.check()
+        assert max(errs) <= 2e-4, (recipe, exchange, errs)
+        # this rank's heads of the WKV state, the replicated shift states
+        for (w_t, ts_t, cs_t), (w_r, ts_r, cs_r) in zip(st_t, st_r):
+            h0 = rank * 20
+            assert (w_t - w_r[:, h0:h0 + 20]).abs().max().item() <= 1e-4 * max(1.0, w_r.abs().max().item())
+            assert rel(ts_t.reshape(2, -1), ts_r.reshape(2, -1)) <= 1e-4 and rel(cs_t.reshape(2, -1), cs_r.reshape(2, -1)) <= 1e-4
+        # every rank holds the same logits bit for bit
+        both = [torch.empty_like(lo_t) for _ in range(2)]
+        dist.all_gather(both, lo_t.contiguous())
+        assert torch.equal(both[0], both[1])
+        if rank == 0: print(f"{recipe} {exchange}: logits relmax vs one GPU {max(errs):.2e}")
+        del m
+        g.close()
+    del ref
+dist.barrier()
+if rank == 0: print("RANK0_OK")
+dist.destroy_process_group()
+'''
+
+
+def test_head_sharded_model_two_gpus(tmp_path):
+    """The whole model split over two GPUs (heads, WKV state, column-split output / ffn.value
+    projections, row-split head) against the single-GPU model: logits over a prefill and three
+    decode steps, final states, and bit-equality of the logits across ranks."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "model_worker.py"
+    script.write_text(MODEL_WORKER)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), ROOT]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-5000:]
+    assert "RANK0_OK" in r.stdout
+    print(r.stdout[-600:])
