@@ -1,5 +1,7 @@
 // Single-vector decode GEMV on the integer tensor-core path: the stand-alone kernel,
 // its launcher and the relayout kernels.  The arithmetic is described in rwkvq_gemv_mma.cuh.
+#include <cstdlib>
+
 #include "rwkvq_gemv_mma.cuh"
 
 namespace rwkvq {
@@ -10,7 +12,9 @@ namespace rwkvq {
 // of the K loop; the activations are prepared once per CTA.  Each warp sees a flat
 // sequence of work items (tile, iteration); the loads of item n+1 are issued
 // before item n is consumed.
-template <int L, int WK, bool SPLIT>      // SPLIT: the K loop is also split across gridDim.z CTAs
+// ZS: the exact zero-group skip (see prepare_x / load_frag), a compile-time variant so that launches
+// without it carry none of its instructions
+template <int L, int WK, bool SPLIT, bool ZS>      // SPLIT: the K loop is also split across gridDim.z CTAs
 __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaArgs a) {
     using G = Geo<L>;
     constexpr int WT = kMmaWarps / WK;
@@ -36,12 +40,14 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaAr
     const int n_items = n_steps * ipt;
     // prefetch side: item counter -> (tile, iteration)
     int i_n = 0, i_tile = blockIdx.x * WT + tl, i_j = 0;
-    Frag<L> nxt{};
+    Frag<L> nxt;
+    if (ZS) nxt = Frag<L>{};               // skipped loads leave the fragment as it was: start from zeros
     const uint8_t* zf = nullptr;           // set once the activations are prepared
     auto fetch_next = [&]() {
         if (i_n < n_items && i_tile < n_tiles) {
             const int r0 = min(i_tile * 16 + g, q.rows - 1), r1 = min(i_tile * 16 + g + 8, q.rows - 1);
-            load_frag<L>(nxt, q, r0, r1, it0 + ks + i_j * WK, t, zf);
+            if (ZS) load_frag<L>(nxt, q, r0, r1, it0 + ks + i_j * WK, t, zf);
+            else load_frag<L>(nxt, q, r0, r1, it0 + ks + i_j * WK, t);
         }
         ++i_n;
         if (++i_j == ipt) { i_j = 0; i_tile += step; }
@@ -56,11 +62,11 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) gemv_mma_kernel(const MmaAr
     const char* xv = a.xk[blockIdx.y] ? static_cast<const char*>(a.xk[blockIdx.y])
                                       : static_cast<const char*>(a.x) + (a.fused ? blockIdx.y * a.ldx * esz : 0);
     bool finite;
-    const float unscale = prepare_x(xv, a.x_dtype, n_in, x_bits<L>(), dig, xs16, red, finite, a.zero_skip ? zflag : nullptr);
+    const float unscale = prepare_x(xv, a.x_dtype, n_in, x_bits<L>(), dig, xs16, red, finite, ZS ? zflag : nullptr);
     __syncthreads();
     // exact sparsity skip: groups of 32 columns whose activations are all zero (relu(k)^2 in the channel
     // mix) are not read from the second fetch on
-    if (a.zero_skip) zf = zflag;
+    if (ZS) zf = zflag;
 
     int c_n = 0, buf = 0;
     for (int base = blockIdx.x * WT; base < n_tiles; base += step, buf ^= 1) {
@@ -197,6 +203,15 @@ int mma_layout_of(const rwkvq_qtensor& t) {
     return -1;
 }
 
+int g_zero_skip = -1;                      // -1: read RWKVQ_ZERO_SKIP from the environment at first use
+static bool zero_skip_enabled() {
+    if (g_zero_skip < 0) {
+        const char* e = getenv("RWKVQ_ZERO_SKIP");
+        g_zero_skip = (e != nullptr && e[0] == '1') ? 1 : 0;
+    }
+    return g_zero_skip == 1;
+}
+
 constexpr int kResidentCtas = 2 * 148;     // 2 CTAs of 256 threads per SM at <= 128 registers
 constexpr int kSplitMaxRows = 4096;        // rows a K-split launch may have (scratch sizing)
 constexpr int kSplitMaxSlices = 4;
@@ -206,23 +221,33 @@ size_t gemv_mma_scratch_bytes() {
     return sizeof(float) * kSplitMaxSlices * kMmaMaxFused * kSplitMaxRows + sizeof(unsigned int) * 1024;
 }
 
-template <int L, int WK, bool SPLIT = false>
-static int launch_one(MmaArgs& a, int rows, int cols, int n_mats, int KS, cudaStream_t s) {
+template <int L, int WK, bool SPLIT, bool ZS>
+static int launch_one_zs(MmaArgs& a, int rows, int cols, int n_mats, int KS, cudaStream_t s) {
     constexpr int WT = kMmaWarps / WK;
     const size_t smem = 3 * static_cast<size_t>(cols) + 4 * (cols / 16) + 2 * kMmaWarps * 16 * 4 + ((cols / 32 + 15) / 16) * 16;
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<L, WK, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<L, WK, SPLIT, ZS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(smem));
         if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "gemv_mma: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
     const int units = ((rows + 15) / 16 + WT - 1) / WT;
     const int cap = kResidentCtas / (n_mats * KS) > 0 ? kResidentCtas / (n_mats * KS) : 1;
     a.rows_padded = ((rows + 15) / 16) * 16;
-    a.zero_skip = cols >= 4096;        // rows as long as the channel-mix hidden vector, the one input with exact zeros
-    cudaError_t le = launch_pdl(gemv_mma_kernel<L, WK, SPLIT>, dim3(units < cap ? units : cap, n_mats, KS),
+    cudaError_t le = launch_pdl(gemv_mma_kernel<L, WK, SPLIT, ZS>, dim3(units < cap ? units : cap, n_mats, KS),
                                 dim3(kMmaWarps * 32), smem, s, a);
     if (le != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "gemv_mma: %s", cudaGetErrorString(le));
     return RWKVQ_OK;
+}
+
+template <int L, int WK, bool SPLIT = false>
+static int launch_one(MmaArgs& a, int rows, int cols, int n_mats, int KS, cudaStream_t s) {
+    // The zero-group skip is opt-in (RWKVQ_ZERO_SKIP=1): on this part a 16-byte hole saves no DRAM traffic
+    // (whole 64-128-byte lines are fetched) and the variant costs ~0.2 us per launch.  When on: rows as long as
+    // the channel-mix hidden vector, the one input with exact zeros, and the layouts whose loader can leave a
+    // group unread.
+    if (zero_skip_enabled() && cols >= 4096 && (L <= ML_SB6_6 || L == ML_SYM6))
+        return launch_one_zs<L, WK, SPLIT, true>(a, rows, cols, n_mats, KS, s);
+    return launch_one_zs<L, WK, SPLIT, false>(a, rows, cols, n_mats, KS, s);
 }
 
 // Work split: a single wave of co-resident CTAs whenever the matrix allows it.
@@ -286,6 +311,8 @@ int launch_gemv_mma(int layout, const rwkvq_qtensor* ts, int n_mats, const void*
 }  // namespace rwkvq
 
 using namespace rwkvq;
+
+extern "C" void rwkvq_profiling_zero_skip(int on) { g_zero_skip = on < 0 ? -1 : (on ? 1 : 0); }
 
 extern "C" {
 

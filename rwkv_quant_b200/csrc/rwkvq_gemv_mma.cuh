@@ -47,7 +47,6 @@ struct MmaArgs {
     float* partial;
     unsigned int* counters;
     int rows_padded;
-    int zero_skip;            // leave the codes of all-zero activation groups unread (set for long rows: channel-mix value)
 };
 
 template <bool A_UNSIGNED>

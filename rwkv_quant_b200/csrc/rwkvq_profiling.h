@@ -30,6 +30,9 @@ void rwkvq_profiling_tcb_force(int force_ks);
 /* Precision of the small-batch linears: 1 single fp16 operands (what RWKVQ_BATCH_FAST=1 selects),
  * 0 two-term operands (the default), -1 read the environment again. */
 void rwkvq_profiling_batch_fast(int fast);
+/* The exact zero-group skip of the single-vector GEMV (what RWKVQ_ZERO_SKIP=1 selects): 1 on, 0 off (the
+ * default), -1 read the environment again. */
+void rwkvq_profiling_zero_skip(int on);
 #ifdef __cplusplus
 }
 #endif

@@ -500,9 +500,13 @@ def quantize_time(rows=10240, cols=2560, reps=5):
 def sparse_sweep():
     """The exact zero-group skip of the single-vector GEMV: launch time against the share of
     32-column groups whose activations are all zero (file bytes / time, so the rate rises)."""
+    sw = _lib.load().rwkvq_profiling_zero_skip      # rwkvq_profiling.h: the skip is opt-in (RWKVQ_ZERO_SKIP=1)
+    sw.restype, sw.argtypes = None, [C.c_int]
+    sw(1)
     for args in [("sb6", 4, 2048, 8192), ("sb6", 5, 65536, 2048), ("sym", 6, 2048, 8192)]:
         for z in (0.0, 0.35, 0.7):
             time_ring(*args, zero_groups=z)
+    sw(-1)
 
 
 def sweep():

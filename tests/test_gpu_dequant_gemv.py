@@ -433,7 +433,21 @@ def test_gemv_skips_all_zero_activation_groups_exactly(cuda_lib, layout, bits):
     """relu(k)^2 leaves most channel-mix activations exactly zero; the single-vector kernel does not
     read the codes of a 32-column group whose activations are all zero.  Same bar as the dense
     case (and the rows of a 2-row call, which run one by one, agree bit for bit with single calls)."""
+    import ctypes as C
     from rwkv_quant_b200.backends.cuda import ops
+    sw = cuda_lib.rwkvq_profiling_zero_skip          # rwkvq_profiling.h: the skip is opt-in (RWKVQ_ZERO_SKIP=1)
+    sw.restype, sw.argtypes = None, [C.c_int]
+    try:
+        sw(1)
+        y_on = _zero_group_case(ops, layout, bits)
+        sw(0)
+        y_off = _zero_group_case(ops, layout, bits)
+    finally:
+        sw(-1)
+    assert np.array_equal(y_on, y_off), "the skip changed a bit of the result"
+
+
+def _zero_group_case(ops, layout, bits):
     rows, cols = 2048, 8192
     qt = _synth_linear(layout, bits, rows, cols, seed=17 + bits)
     dq = ops.DeviceQT(qt)
@@ -454,3 +468,4 @@ def test_gemv_skips_all_zero_activation_groups_exactly(cuda_lib, layout, bits):
     # an all-zero vector gives exact zeros
     z = ops.gemv(dq.bufs, dq.meta, torch.zeros(1, cols, device="cuda"), 0, None)
     assert (z == 0).all()
+    return y
