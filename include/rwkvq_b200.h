@@ -253,14 +253,16 @@ int rwkvq_gemv_t(const rwkvq_qtensor* t, const float* x, int N, int64_t ldx,
 
 /*
  * Up to four LoRA branches for N rows in two launches on the tensor cores:
- *   y_i[n, :] = act_i( x_i[n, :] @ W1_i ) @ W2_i,   W1_i stored [D, r_i], W2_i stored [r_i, D]
+ *   y_i[n, :] = act_i( x_i[n, :] @ W1_i ) @ W2_i,   W1_i stored [D, r_i], W2_i stored [r_i, C]
+ * (C = D, or any multiple of 32 shared by all branches: a column range of the up projections, as a
+ * head-sharded model holds; y_i is [N, C] contiguous)
  * Stands behind QuantTMix._lora for every row count above 2 (backends/metal/quant_model.py:462-526:
  * the decay, in-context rate, gate and value-residual branches; dense fp16 matmuls there).  The
  * matrices are read from their file bytes (asym / per-row int8 / dense bf16) and used in the
  * loader's precision fp16(bf16(w)), which is exact in fp16; x and the rank-space activations enter
  * as fp16 pairs hi + lo (~2^-22 relative), accumulation fp32.  act: 0 none, 1 tanh, 2 sigmoid.
  *   t1_host / t2_host  host arrays of n_br descriptors; xs_host / ys_host host arrays of n_br device
- *   pointers to [N, D] fp32 rows (contiguous, 16-byte aligned); acts_host host array.
+ *   pointers to [N, D] (x) and [N, C] (y) fp32 rows (contiguous, 16-byte aligned); acts_host host array.
  *   Requirements: D % 128 == 0, ranks multiples of 16 up to 512 (RWKVQ_E_SHAPE otherwise: use
  *   rwkvq_gemv_t).  workspace: rwkvq_lora_pair_workspace_bytes(N, max rank) bytes, 16-byte aligned.
  */

@@ -296,20 +296,21 @@ def gemv_batch(dq: "DeviceQT", x: torch.Tensor, epilogue: int = 0, resid: Option
 
 
 def lora_pair_ok(pairs, D: int) -> bool:
-    """Whether ``lora_pair`` serves these (W1 [D, r], W2 [r, D]) tensor pairs."""
-    return D % 128 == 0 and all(a.rows == D and b.cols == D and a.cols == b.rows and a.cols % 16 == 0
+    """Whether ``lora_pair`` serves these (W1 [D, r], W2 [r, C]) tensor pairs (one C for all, a multiple of 32)."""
+    C_out = pairs[0][1].cols
+    return D % 128 == 0 and C_out % 32 == 0 and all(a.rows == D and b.cols == C_out and a.cols == b.rows and a.cols % 16 == 0
                                 and 16 <= a.cols <= 512 and a.outliers is None and b.outliers is None for a, b in pairs)
 
 
 def lora_pair(pairs, xs: Sequence[torch.Tensor], acts: Sequence[int]) -> List[torch.Tensor]:
     """y_i = act_i(x_i @ W1_i) @ W2_i for up to four (W1, W2) pairs of tensors stored [in, out], x_i
-    [N, D] fp32: two tensor-core launches for all branches (act: 0 none, 1 tanh, 2 sigmoid)."""
+    [N, D] fp32 -> y_i [N, C]: two tensor-core launches for all branches (act: 0 none, 1 tanh, 2 sigmoid)."""
     lib = _lib.load()
     n_br = len(pairs)
     xs = [x.float().contiguous() for x in xs]
     _require_cuda(*xs)
     N, D = xs[0].shape
-    ys = [torch.empty((N, D), dtype=torch.float32, device=xs[0].device) for _ in range(n_br)]
+    ys = [torch.empty((N, pairs[0][1].cols), dtype=torch.float32, device=xs[0].device) for _ in range(n_br)]
     t1 = (QTensorStruct * n_br)(*[a.struct for a, _ in pairs])
     t2 = (QTensorStruct * n_br)(*[b.struct for _, b in pairs])
     nws = lib.rwkvq_lora_pair_workspace_bytes(N, max(a.cols for a, _ in pairs))

@@ -270,7 +270,7 @@ class QuantRWKV7:
         # both LoRA products of all branches in two launches of the library's own tensor-core kernels, up
         # to lora_pair_max rows; longer calls (pp512 at batch 16 = 8192 rows) go through a dense fp16 copy
         # and a library GEMM, which is faster there (the own kernels re-stage x per 32 rank columns)
-        pair_kernel = 2 < N <= self.lora_pair_max and ops.lora_pair_ok(pairs, D)
+        pair_kernel = N <= self.lora_pair_max and ops.lora_pair_ok(pairs, D)
         if self.fused_prep and N > 8 and D % 2 == 0:
             # LN1 + shift + 6 lerps, each row written once in the form its consumers read
             mr, mk, mv = self._prep_modes(N, (L.Wr, L.Wk, L.Wv))

@@ -350,12 +350,14 @@ int launch_lmm(LoraMmaArgs& a, int groups, int max_cols, cudaStream_t s) {
 }  // namespace
 
 // Whether the tensor-core pair serves these shapes: D a multiple of 128 (slices of D / 8 columns,
-// whole k16 steps, 128-column output tiles), every rank a multiple of 16 up to 512.
+// whole k16 steps), every rank a multiple of 16 up to 512, and one output width for all branches, a
+// multiple of the 32-column output tiles (D itself, or a rank's share of it in a head-sharded model).
 bool lora_mma_ok(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, int n_br, int D) {
     if (D % 128 != 0) return false;
     for (int i = 0; i < n_br; ++i) {
         const int r = t1[i]->cols;
-        if (t1[i]->rows != D || t2[i]->rows != r || t2[i]->cols != D || r % 16 != 0 || r > 512 || r < 16) return false;
+        if (t1[i]->rows != D || t2[i]->rows != r || r % 16 != 0 || r > 512 || r < 16) return false;
+        if (t2[i]->cols != t2[0]->cols || t2[i]->cols % kLmmUpCols != 0 || t2[i]->cols < kLmmUpCols) return false;
     }
     return true;
 }
@@ -373,7 +375,7 @@ int launch_lora_pair_mma(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* co
         max_cols = t2[i]->cols > max_cols ? t2[i]->cols : max_cols;
         mr = t1[i]->cols > mr ? t1[i]->cols : mr;
     }
-    a.h = h; a.ldx = D; a.ldy = D; a.n_tokens = B; a.n_stride = n_stride; a.max_rank = max_rank; a.n_br = n_br; a.D = D;
+    a.h = h; a.ldx = D; a.ldy = max_cols; a.n_tokens = B; a.n_stride = n_stride; a.max_rank = max_rank; a.n_br = n_br; a.D = D;
     RWKVQ_REQUIRE(mr <= max_rank, RWKVQ_E_SHAPE, "lora_mma: rank %d above the model's max_rank %d", mr, max_rank);
     if (B <= 16) return launch_lmm<1>(a, 1, max_cols, s);
     if (B <= 32) return launch_lmm<2>(a, 1, max_cols, s);
@@ -409,7 +411,7 @@ extern "C" int rwkvq_lora_pair(const rwkvq_qtensor* t1_host, const rwkvq_qtensor
         max_rank = t1_host[i].cols > max_rank ? t1_host[i].cols : max_rank;
     }
     RWKVQ_REQUIRE(lora_mma_ok(t1, t2, n_br, D), RWKVQ_E_SHAPE,
-                  "rwkvq_lora_pair: needs D %% 128 == 0, every rank a multiple of 16 up to 512, W1 [D, r], W2 [r, D]");
+                  "rwkvq_lora_pair: needs D %% 128 == 0, every rank a multiple of 16 up to 512, W1 [D, r], W2 [r, C] with one C %% 32 == 0");
     RWKVQ_REQUIRE(aligned(workspace, 16) && workspace_bytes >= rwkvq_lora_pair_workspace_bytes(N, max_rank), RWKVQ_E_LIMIT,
                   "rwkvq_lora_pair: workspace of %zu bytes, %zu needed (16-byte aligned)", workspace_bytes,
                   rwkvq_lora_pair_workspace_bytes(N, max_rank));

@@ -98,9 +98,15 @@ def tp_model_time(model="2.9b", recipe="compression", exchange="p2p", layers=32,
         x1, _ = ref.forward_hidden(tok, st_r)          # same Python path on one GPU
         t_py = timed(lambda: ref.forward_hidden(tok, st_r), steps)
         t_c = timed(lambda: ref._decode(tok.reshape(B), st_c), steps)
+        dec_t = m.decoder(B, use_graph=True)
+        t_tpg = timed(lambda: dec_t.step(), 4 * steps)
+        dec_1 = ref.decoder(B, use_graph=True, self_feed=True)
+        t_1g = timed(lambda: dec_1.step(), 4 * steps)
+        del dec_t, dec_1
         if rank == 0:
-            print(f"tp-model {model} {recipe} {layers} layers x{g.world} ({exchange}), {B} stream(s): {t_tp:.2f} ms per step; "
-                  f"one GPU, same Python path {t_py:.2f} ms, one-call decode step {t_c:.2f} ms", flush=True)
+            print(f"tp-model {model} {recipe} {layers} layers x{g.world} ({exchange}), {B} stream(s): plain calls {t_tp:.2f} ms per step, "
+                  f"graph replay {t_tpg:.2f} ms; one GPU: same Python path {t_py:.2f} ms, one-call decode step {t_c:.2f} ms, "
+                  f"its graph replay {t_1g:.2f} ms", flush=True)
     idx = torch.randint(1, 60000, (1, 512), device=dev)
     t_tp = timed(lambda: m.forward_stateful(idx, m.init_state(1), last_only=True), 2)
     t_1 = timed(lambda: ref.forward_stateful(idx, ref.init_state(1), last_only=True), 2)

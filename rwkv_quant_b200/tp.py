@@ -115,21 +115,27 @@ class TPGroup:
 
     # ---- the exchange -----------------------------------------------------------------
     @contextlib.contextmanager
-    def graph_capture(self):
+    def graph_capture(self, interleaved: bool = False):
         """Wrap the capture of a CUDA graph that contains exchanges.  Which of a site's two
         destination buffers an exchange writes is chosen by a host counter and therefore frozen into
         the graph: if a graph used a site an odd number of times, every replay would write the same
-        buffer, and a peer one exchange ahead could overwrite it before this rank's consumer has read it
-        (the flags order arrival, not consumption).  On exit this raises unless every site was used an
-        even number of times inside the capture; ``all_gather`` refuses to run under stream capture
-        outside this context."""
+        buffer first and last, and a peer one exchange ahead could overwrite it before this rank's
+        consumer has read it (the flags order arrival, not consumption).  On exit this raises unless
+        every site was used an even number of times inside the capture; ``all_gather`` refuses to run
+        under stream capture outside this context.
+
+        ``interleaved=True`` lifts the even-count rule for graphs in which two consecutive uses of any
+        one site, within a replay and from one replay to the next, are always separated by an exchange
+        of ANOTHER site (the caller's promise; the graph must use at least two sites): a rank can only
+        pass that other exchange once its peer has issued it, which the peer does, in stream order,
+        after consuming the earlier buffer."""
         self._cap = {}
         try:
             yield self
         finally:
             cap, self._cap = self._cap, None
         odd = sorted(k for k, v in cap.items() if v % 2)
-        if odd:
+        if odd and not (interleaved and len(cap) >= 2):
             raise RuntimeError(f"captured graph uses exchange site(s) {odd} an odd number of times: replays would "
                                f"reuse one destination buffer; issue every site an even number of times per graph")
 

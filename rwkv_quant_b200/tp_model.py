@@ -174,8 +174,9 @@ class TPQuantRWKV7(QuantRWKV7):
         H, S = self.n_head_local, self.head_size
         return [(torch.zeros((batch_size, H, S, S), device=self.device), None, None) for _ in range(self.n_layer)]
 
-    def decoder(self, *a, **k):
-        raise NotImplementedError("the CUDA-graph decoder is a single-GPU path; call forward_stateful")
+    def decoder(self, batch_size: int = 1, use_graph: bool = True):
+        """A ``TPDecoder``: one token of ``batch_size`` streams per call, replayed as a CUDA graph."""
+        return TPDecoder(self, batch_size, use_graph)
 
     # ---- exchanges
     def _all_reduce(self, name: str, part: torch.Tensor) -> torch.Tensor:
@@ -202,11 +203,18 @@ class TPQuantRWKV7(QuantRWKV7):
         xs, ts = ops.seq_ln_shift_mix(x, L.ln1[0], L.ln1[1], ts, L.x_mix)              # replicated
         xr, xw, xk, xv, xa, xg = (xs[j].reshape(N, D) for j in range(6))
         r, k, v = self._linear(L.Wr, xr), self._linear(L.Wk, xk), self._linear(L.Wv, xv)   # [N, Dl]: this rank's heads
-        up = lambda dq, t: self._lora_seq(dq, t, 0)
-        y_w = up(L.w2, self._lora_seq(L.w1, xw, 1))
-        y_a = up(L.a2, self._lora_seq(L.a1, xa, 0))
-        g = up(L.g2, self._lora_seq(L.g1, xg, 2))
-        y_v = None if i == 0 else up(L.v2, self._lora_seq(L.v1, xv, 0))
+        pairs = [(L.w1, L.w2), (L.a1, L.a2), (L.g1, L.g2)] + ([(L.v1, L.v2)] if i > 0 else [])
+        if N <= self.lora_pair_max and ops.lora_pair_ok(pairs, D):
+            # down projections full width, up projections onto this rank's channels: two launches for all branches
+            ys = ops.lora_pair(pairs, [xw, xa, xg] + ([xv] if i > 0 else []), [1, 0, 2, 0][:len(pairs)])
+            y_w, y_a, g = ys[:3]
+            y_v = ys[3] if i > 0 else None
+        else:
+            up = lambda dq, t: self._lora_seq(dq, t, 0)
+            y_w = up(L.w2, self._lora_seq(L.w1, xw, 1))
+            y_a = up(L.a2, self._lora_seq(L.a1, xa, 0))
+            g = up(L.g2, self._lora_seq(L.g1, xg, 2))
+            y_v = None if i == 0 else up(L.v2, self._lora_seq(L.v1, xv, 0))
         if i == 0:
             v_first = v
         w, k, v2, na, nb = ops.seq_tmix_pre(k, v, y_w, y_a, y_v, None if i == 0 else v_first, L.w0, L.a0, L.v0,
@@ -234,3 +242,53 @@ class TPQuantRWKV7(QuantRWKV7):
         loc = self._linear(self.head, x.reshape(B * n, self.n_embd).contiguous())       # [B n, V / world]
         logits = self._gather_cols("head", loc)
         return logits.reshape(B, n, self.full_vocab), new_states
+
+
+class TPDecoder:
+    """Greedy single-token steps of ``batch_size`` streams on a ``TPQuantRWKV7``: the whole step of this
+    rank (its launches and its exchanges) captured once and replayed as one CUDA graph, state kept in
+    place.  Every rank of the group must build and step its decoder in lockstep.
+
+    ``step(tokens=None)``: feed ``tokens`` [B] (or the previous step's argmax) and return the next
+    token ids [B] (a tensor of the decoder, overwritten by the next step); ``logits`` [B, V]."""
+
+    def __init__(self, model: TPQuantRWKV7, batch_size: int, use_graph: bool = True):
+        self.m, self.B = model, int(batch_size)
+        dev = model.device
+        self.tokens = torch.ones((self.B, 1), dtype=torch.long, device=dev)
+        self.states = model._materialize(model.init_state(self.B), self.B)
+        self.logits = torch.zeros((self.B, model.full_vocab), dtype=torch.float32, device=dev)
+        self.next_tokens = torch.ones(self.B, dtype=torch.long, device=dev)
+        self.graph = None
+        if use_graph:
+            self._body()                                   # sites, workspaces and library handles exist before the capture
+            torch.cuda.synchronize(dev)
+            for st in self.states:
+                for t in st:
+                    t.zero_()
+            st = torch.cuda.Stream(device=dev)
+            st.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(st):
+                self.graph = torch.cuda.CUDAGraph()
+                # o / v alternate layer by layer and the head exchange closes the step: consecutive uses of one
+                # site always have another site's exchange between them
+                with model.group.graph_capture(interleaved=True), torch.cuda.graph(self.graph, stream=st):
+                    self._body()
+            torch.cuda.current_stream(dev).wait_stream(st)
+
+    def _body(self):
+        logits, new = self.m.forward_stateful(self.tokens, self.states)
+        for old, cur in zip(self.states, new):
+            for o, c in zip(old, cur):
+                if o.data_ptr() != c.data_ptr():
+                    o.copy_(c.reshape(o.shape))
+        self.logits.copy_(logits[:, 0])
+        self.next_tokens.copy_(self.logits.argmax(dim=-1))
+
+    def step(self, tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        self.tokens.copy_((self.next_tokens if tokens is None else tokens).reshape(self.B, 1))
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self._body()
+        return self.next_tokens

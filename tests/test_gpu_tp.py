@@ -120,6 +120,18 @@ for recipe in ("compression", "reduction"):
         dist.all_gather(both, lo_t.contiguous())
         assert torch.equal(both[0], both[1])
         if rank == 0: print(f"{recipe} {exchange}: logits relmax vs one GPU {max(errs):.2e}")
+        # the graph-replayed decoder against plain calls: same tokens, same logits, five steps
+        tok = idx[:, 0]
+        dec = m.decoder(2, use_graph=True)
+        st_e = m.init_state(2)
+        nxt_g = dec.step(tok).clone()
+        for t in range(5):
+            lo_e, st_e = m.forward_stateful((tok if t == 0 else nxt_e).reshape(2, 1), st_e)
+            nxt_e = lo_e[:, 0].argmax(-1)
+            assert torch.equal(nxt_g, nxt_e) and rel(dec.logits, lo_e[:, 0]) <= 1e-6, (recipe, exchange, t)
+            if t < 4: nxt_g = dec.step().clone()
+        torch.cuda.synchronize(); g.check()
+        del dec
         del m
         g.close()
     del ref
