@@ -77,6 +77,18 @@ try:
 except RuntimeError as e:
     assert "odd number" in str(e), e
 l2(l1(x, 1), 2, x)                         # restores the parity of both sites on every rank
+# interleaved graphs (two sites alternating) may use their sites an odd number of times ...
+with g.graph_capture(interleaved=True):
+    l2(l1(x, 1), 2, x)
+l2(l1(x, 1), 2, x)
+# ... a graph with a single site may not
+try:
+    with g.graph_capture(interleaved=True):
+        l1(x, 1)
+    raise SystemExit("one site used once inside an interleaved capture was accepted")
+except RuntimeError as e:
+    assert "odd number" in str(e), e
+l1(x, 1)
 dist.barrier()
 if rank == 0: print("RANK0_OK")
 dist.destroy_process_group()
