@@ -51,22 +51,104 @@ __device__ __forceinline__ void layer_norm_row(float (&x)[PER], int D, const flo
 constexpr int kRowThreads = 256;
 constexpr int kRowPer = 16;      // D <= 4096
 
+// Columns [32 g, 32 g + 32) of row R of an sb6 or sym table as exact fp32 values (the arithmetic of
+// decode_element: separate multiply and add), with every load of the group issued before any use:
+// 16 bytes of codes, the plane words, the scale record.  Requires 32 | cols and the natural alignment
+// of the file buffers (rows of codes are multiples of 16 bytes).
+__device__ __forceinline__ void decode_group32(const QView& t, size_t R, int g, float* out) {
+    if (t.kind == RWKVQ_KIND_SB6) {
+        const int nsb = t.cols >> 8, sbi = g >> 3, j = g & 7;
+        const uint4 cw = *reinterpret_cast<const uint4*>(t.codes + R * (t.cols >> 1) + g * 16);
+        const uint32_t h1 = t.qh ? *reinterpret_cast<const uint32_t*>(t.qh + R * (t.cols >> 3) + g * 4) : 0u;
+        const uint32_t h2 = t.qh2 ? *reinterpret_cast<const uint32_t*>(t.qh2 + R * (t.cols >> 3) + g * 4) : 0u;
+        const uint32_t* mp = reinterpret_cast<const uint32_t*>(t.qsqm + (R * nsb + sbi) * 12);
+        const uint32_t m0 = mp[0], m1 = mp[1], m2 = mp[2];
+        const float d = __half2float(t.d[R * nsb + sbi]), dm = __half2float(t.dm[R * nsb + sbi]);
+        float sc, mn;
+        sb6_scale_min(m0, m1, m2, j, d, dm, sc, mn);
+        const uint32_t w[4] = {cw.x, cw.y, cw.z, cw.w};
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {               // byte k: column k (low nibble), column k + 16 (high nibble)
+            const uint32_t byte = (w[k >> 2] >> (8 * (k & 3))) & 0xFFu;
+            const uint32_t lo = (byte & 0xFu) + 16u * ((h1 >> k) & 1u) + 32u * ((h2 >> k) & 1u);
+            const uint32_t hi = (byte >> 4) + 16u * ((h1 >> (k + 16)) & 1u) + 32u * ((h2 >> (k + 16)) & 1u);
+            out[k] = __fadd_rn(__fmul_rn(static_cast<float>(lo), sc), mn);
+            out[k + 16] = __fadd_rn(__fmul_rn(static_cast<float>(hi), sc), mn);
+        }
+    } else {                                         // sym: two blocks of 16
+        const int nb = t.cols >> 4, nsb = t.cols >> 8;
+        const float d = __half2float(t.d[R * nsb + (g >> 3)]);
+        const uint32_t qs2 = *reinterpret_cast<const unsigned short*>(t.qs + R * nb + 2 * g);
+        float s[2];
+#pragma unroll
+        for (int b2 = 0; b2 < 2; ++b2)
+            s[b2] = half_roundtrip(__fmul_rn(static_cast<float>(static_cast<int8_t>((qs2 >> (8 * b2)) & 0xFFu)), d));
+        if (t.bits == 8) {
+            const uint4* cp = reinterpret_cast<const uint4*>(t.codes + R * t.cols + g * 32);
+            const uint4 c0 = cp[0], c1 = cp[1];
+            const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+                out[k] = __fmul_rn(static_cast<float>(static_cast<int8_t>((w[k >> 2] >> (8 * (k & 3))) & 0xFFu)), s[k >> 4]);
+        } else {
+            const uint4 cw = *reinterpret_cast<const uint4*>(t.codes + R * (t.cols >> 1) + g * 16);
+            const uint32_t h1 = t.qh ? *reinterpret_cast<const uint32_t*>(t.qh + R * (t.cols >> 3) + g * 4) : 0u;
+            const uint32_t h2 = t.qh2 ? *reinterpret_cast<const uint32_t*>(t.qh2 + R * (t.cols >> 3) + g * 4) : 0u;
+            const uint32_t w[4] = {cw.x, cw.y, cw.z, cw.w};
+#pragma unroll
+            for (int b2 = 0; b2 < 2; ++b2)
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {        // block b2, byte k: column k (low nibble), column k + 8 (high nibble)
+                    const uint32_t byte = (w[2 * b2 + (k >> 2)] >> (8 * (k & 3))) & 0xFFu;
+                    const int c_lo = 16 * b2 + k, c_hi = c_lo + 8;
+                    const int lo = static_cast<int>((byte & 0xFu) + 16u * ((h1 >> c_lo) & 1u) + 32u * ((h2 >> c_lo) & 1u)) - 32;
+                    const int hi = static_cast<int>((byte >> 4) + 16u * ((h1 >> c_hi) & 1u) + 32u * ((h2 >> c_hi) & 1u)) - 32;
+                    out[c_lo] = __fmul_rn(static_cast<float>(lo), s[b2]);
+                    out[c_hi] = __fmul_rn(static_cast<float>(hi), s[b2]);
+                }
+        }
+    }
+}
+__device__ __forceinline__ bool group32_ok(const QView& t) {
+    if (t.cols % 256 != 0) return false;
+    if (t.kind == RWKVQ_KIND_SB6) return t.gs == 32 && t.sb == 8;
+    return t.kind == RWKVQ_KIND_SYM && t.gs == 16 && t.sb == 16;
+}
+
 // x[b] = LN0(fp16(bf16(dequant(emb[token[b]])))): one embedding row is decoded from the
-// packed table (quant_model.py:853, 975-976; rounding policy :128-154).
+// packed table (quant_model.py:853, 975-976; rounding policy :128-154).  sb6 / sym tables: one
+// thread per 32 columns decodes its group with all loads in flight at once and hands the row over
+// through shared memory; other layouts: element by element.
 __global__ void __launch_bounds__(kRowThreads) embed_ln0_kernel(QView emb, const long long* tokens,
                                                                const float* ln_w, const float* ln_b,
                                                                float* x, int D) {
     __shared__ float red[kRowThreads / 32];
+    __shared__ float srow[kRowThreads * kRowPer];
     const int b = blockIdx.x;
     pdl_launch_dependents();
     pdl_wait();
     long long tok = __ldcg(tokens + b);
     tok = tok < 0 ? 0 : (tok >= emb.rows ? emb.rows - 1 : tok);
     float v[kRowPer];
+    if (group32_ok(emb)) {
+        for (int g = threadIdx.x; g < D / 32; g += kRowThreads) {
+            float o[32];
+            decode_group32(emb, static_cast<size_t>(tok), g, o);
 #pragma unroll
-    for (int i = 0; i < kRowPer; ++i) {
-        const int d = threadIdx.x + i * kRowThreads;
-        v[i] = (d < D) ? dense_param_rounding(decode_element(emb, static_cast<int>(tok), d)) : 0.f;
+            for (int k = 0; k < 32; ++k) srow[g * 32 + k] = dense_param_rounding(o[k]);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < kRowPer; ++i) {
+            const int d = threadIdx.x + i * kRowThreads;
+            v[i] = (d < D) ? srow[d] : 0.f;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < kRowPer; ++i) {
+            const int d = threadIdx.x + i * kRowThreads;
+            v[i] = (d < D) ? dense_param_rounding(decode_element(emb, static_cast<int>(tok), d)) : 0.f;
+        }
     }
     layer_norm_row<kRowPer>(v, D, ln_w, ln_b, red);
 #pragma unroll
