@@ -849,6 +849,11 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
                 return fail(RWKVQ_E_LAUNCH, "rwkvq_decode_step: fork onto the side stream failed");
             s_lora = lane->stream;
         }
+        // Up to 16 streams the LoRA pair (two dependent launches) is the longer of the two branches: it then
+        // stays on the caller's stream, where its first kernel starts programmatically behind the LayerNorm
+        // and stages its weights while that still runs, and r / k / v take the side stream.
+        cudaStream_t s_rkv = s;
+        if (lane && B <= 16) { s_rkv = lane->stream; s_lora = s; }
         const int ml = mma_layout_of(L.Wr);
         if (B == 1 && ml >= 0 && mma_layout_of(L.Wk) == ml && mma_layout_of(L.Wv) == ml && L.Wk.rows == D &&
             L.Wv.rows == D && L.Wr.rows == D && L.Wk.cols == D && L.Wv.cols == D && L.Wr.cols == D) {
@@ -859,7 +864,7 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
             }
             const rwkvq_qtensor three[3] = {L.Wr, L.Wk, L.Wv};
             const void* x_each[3] = {xr, xk, xv};
-            rc = launch_gemv_mma(ml, three, 3, xr, RWKVQ_F32, D, r, D, RWKVQ_EPI_NONE, nullptr, 1, s, x_each, w.gscratch);
+            rc = launch_gemv_mma(ml, three, 3, xr, RWKVQ_F32, D, r, D, RWKVQ_EPI_NONE, nullptr, 1, s_rkv, x_each, w.gscratch);
             if (rc) return rc;
         } else if (bp && ml >= 0 && mma_layout_of(L.Wk) == ml && mma_layout_of(L.Wv) == ml &&
                    L.Wk.rows == L.Wr.rows && L.Wv.rows == L.Wr.rows && L.Wk.cols == L.Wr.cols && L.Wv.cols == L.Wr.cols) {
@@ -873,17 +878,17 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
             const float* a3[3] = {am, am + 2 * B, am + 3 * B};
             float* y3[3] = {r, k, v};
             if (tcb_pays(B) && gemm_tcb_ok(L.Wr))
-                rc = launch_gemm_tcb(three, 3, x3, h16, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, w.status, s);
+                rc = launch_gemm_tcb(three, 3, x3, h16, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, w.status, s_rkv);
             else
-                rc = launch_gemv_batch(three, 3, x3, h16, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, s);
+                rc = launch_gemv_batch(three, 3, x3, h16, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, s_rkv);
             if (rc) return rc;
         } else {
-            rc = linear(&L.Wr, xr, B, D, r, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream, h16 ? w.xs16 : nullptr, am, nullptr, w.status);
+            rc = linear(&L.Wr, xr, B, D, r, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, s_rkv, h16 ? w.xs16 : nullptr, am, nullptr, w.status);
             if (rc) return rc;
-            rc = linear(&L.Wk, xk, B, D, k, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream,
+            rc = linear(&L.Wk, xk, B, D, k, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, s_rkv,
                         h16 ? w.xs16 + 2 * BD : nullptr, bp ? am + 2 * B : nullptr, nullptr, w.status);
             if (rc) return rc;
-            rc = linear(&L.Wv, xv, B, D, v, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream,
+            rc = linear(&L.Wv, xv, B, D, v, D, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, s_rkv,
                         h16 ? w.xs16 + 3 * BD : nullptr, bp ? am + 3 * B : nullptr, nullptr, w.status);
             if (rc) return rc;
         }
