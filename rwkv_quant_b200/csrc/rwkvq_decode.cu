@@ -160,8 +160,10 @@ __global__ void __launch_bounds__(kRowThreads) embed_ln0_kernel(QView emb, const
 
 // xn = LN(x[b]); prev = shift[b] (zeros for a fresh stream); shift[b] = xn;
 // out[m][b] = xn + (prev - xn) * mix[m]   for m < n_mix   (n_mix = 0: out[0][b] = xn)
-// All loads are issued before the reductions so that their latencies overlap.
-template <int NMIX>
+// All loads are issued before the reductions so that their latencies overlap.  PER: elements per
+// thread (8 serves D <= 2048 and leaves registers for the lerp vectors, which are then loaded with the
+// LayerNorm parameters before the launch wait; 16 serves D <= 4096 and reads them where they are used).
+template <int NMIX, int PER>
 __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* __restrict__ x,
                                                                   const float* __restrict__ ln_w,
                                                                   const float* __restrict__ ln_b,
@@ -182,13 +184,19 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
     __shared__ float red[kRowThreads / 32];
     __shared__ float redm[kRowThreads / 32][NM];
     const int b = blockIdx.x;
-    float v[kRowPer], prev[kRowPer], lw[kRowPer], lb[kRowPer];
+    float v[PER], prev[PER], lw[PER], lb[PER];
+    constexpr bool PRE = PER <= 8 && NMIX > 0;              // lerp vectors in registers
+    float mxr[PRE ? NMIX : 1][PRE ? PER : 1];
     pdl_launch_dependents();
 #pragma unroll
-    for (int i = 0; i < kRowPer; ++i) {          // parameters do not depend on the previous kernel
+    for (int i = 0; i < PER; ++i) {          // parameters do not depend on the previous kernel
         const int d = threadIdx.x + i * kRowThreads;
         lw[i] = d < D ? ln_w[d] : 0.f;
         lb[i] = d < D ? ln_b[d] : 0.f;
+        if (PRE) {
+#pragma unroll
+            for (int m = 0; m < NMIX; ++m) mxr[PRE ? m : 0][PRE ? i : 0] = d < D ? __ldg(mix + m * D + d) : 0.f;
+        }
     }
     pdl_wait();
     if (threadIdx.x == 0) {
@@ -196,7 +204,7 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
         if (zero_b) zero_b[b] = 0.f;
     }
 #pragma unroll
-    for (int i = 0; i < kRowPer; ++i) {
+    for (int i = 0; i < PER; ++i) {
         const int d = threadIdx.x + i * kRowThreads;
         const bool ok = d < D;
         const size_t bd = static_cast<size_t>(b) * D + d;
@@ -205,11 +213,11 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
     }
     float s = 0.f;
 #pragma unroll
-    for (int i = 0; i < kRowPer; ++i) s += v[i];
+    for (int i = 0; i < PER; ++i) s += v[i];
     const float mean = block_sum(s, red) / D;
     float s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < kRowPer; ++i) {
+    for (int i = 0; i < PER; ++i) {
         const float c = (threadIdx.x + i * kRowThreads < D) ? v[i] - mean : 0.f;
         s2 += c * c;
     }
@@ -218,7 +226,7 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
 #pragma unroll
     for (int m = 0; m < NM; ++m) mx[m] = 0.f;
 #pragma unroll
-    for (int i = 0; i < kRowPer; ++i) {
+    for (int i = 0; i < PER; ++i) {
         const int d = threadIdx.x + i * kRowThreads;
         if (d >= D) continue;
         const size_t bd = static_cast<size_t>(b) * D + d;
@@ -228,7 +236,7 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
         shift[bd] = xn;
 #pragma unroll
         for (int m = 0; m < NMIX; ++m) {
-            const float o = xn + xx * __ldg(mix + m * D + d);
+            const float o = xn + xx * (PRE ? mxr[PRE ? m : 0][PRE ? i : 0] : __ldg(mix + m * D + d));
             out[(static_cast<size_t>(m) * B) * D + bd] = o;
             mx[m < NM ? m : 0] = fmaxf(mx[m < NM ? m : 0], fabsf(o));
         }
@@ -264,7 +272,7 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
         if (x16_out == nullptr) return;
         __syncthreads();
 #pragma unroll
-        for (int i = 0; i < kRowPer; ++i) {
+        for (int i = 0; i < PER; ++i) {
             const int d = threadIdx.x + i * kRowThreads;
             if (d >= D) continue;
             const size_t bd = static_cast<size_t>(b) * D + d;
@@ -274,7 +282,7 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
 #pragma unroll
             for (int m = 0; m < NMIX; ++m) {
                 if (!((x16_mask >> m) & 1)) continue;
-                const float o = xn + xx * __ldg(mix + m * D + d);
+                const float o = xn + xx * (PRE ? mxr[PRE ? m : 0][PRE ? i : 0] : __ldg(mix + m * D + d));
                 x16_out[(static_cast<size_t>(m) * B) * D + bd] = __float2half_rn(o * sc_m[m < NM ? m : 0]);
             }
         }
@@ -795,7 +803,7 @@ int rwkvq_seq_layer_norm(const float* x, const float* ln_w, const float* ln_b, f
     RWKVQ_REQUIRE(x && ln_w && ln_b && out, RWKVQ_E_NULL, "rwkvq_seq_layer_norm: null pointer");
     RWKVQ_REQUIRE(n_rows >= 1 && D >= 1 && D <= kRowThreads * kRowPer, RWKVQ_E_SHAPE, "rwkvq_seq_layer_norm: %lld rows of %d (at most %d)",
                   (long long)n_rows, D, kRowThreads * kRowPer);
-    launch_pdl(ln_shift_mix_kernel<0>, dim3(static_cast<unsigned>(n_rows)), dim3(kRowThreads), 0, static_cast<cudaStream_t>(stream), x,
+    launch_pdl(D <= 8 * kRowThreads ? ln_shift_mix_kernel<0, 8> : ln_shift_mix_kernel<0, kRowPer>, dim3(static_cast<unsigned>(n_rows)), dim3(kRowThreads), 0, static_cast<cudaStream_t>(stream), x,
                ln_w, ln_b, static_cast<float*>(nullptr), static_cast<const float*>(nullptr), out, static_cast<int>(n_rows), D,
                static_cast<__half*>(nullptr), static_cast<float*>(nullptr), 0, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
     return check_launch("rwkvq_seq_layer_norm");
@@ -838,7 +846,7 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         float* am = bp ? w.amax : nullptr;
         float *am_og = bp ? w.amax + 6 * B : nullptr, *am_xk = bp ? w.amax + 7 * B : nullptr;
         float *am_h = bp ? w.amax + 8 * B : nullptr;
-        launch_pdl(ln_shift_mix_kernel<6>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln1_w, L.ln1_b, tshift[l], L.x_mix, w.xs, B, D,
+        launch_pdl(D <= 8 * kRowThreads ? ln_shift_mix_kernel<6, 8> : ln_shift_mix_kernel<6, kRowPer>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln1_w, L.ln1_b, tshift[l], L.x_mix, w.xs, B, D,
                    h16 ? w.xs16 : static_cast<__half*>(nullptr), am, 0b001101, am_og, am_h);      // scales of the r, k, v rows
         float *xr = w.xs, *xw = w.xs + BD, *xk = w.xs + 2 * BD, *xv = w.xs + 3 * BD, *xa = w.xs + 4 * BD,
               *xg = w.xs + 5 * BD;
@@ -913,7 +921,7 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         rc = linear(&L.Wo, w.og, B, D, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, w.gemm_ws, stream, nullptr, am_og, nullptr, w.status);
         if (rc) return rc;
         // ---- channel mix
-        launch_pdl(ln_shift_mix_kernel<1>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln2_w, L.ln2_b, cshift[l], L.ffn_x_k, w.xk, B, D,
+        launch_pdl(D <= 8 * kRowThreads ? ln_shift_mix_kernel<1, 8> : ln_shift_mix_kernel<1, kRowPer>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln2_w, L.ln2_b, cshift[l], L.ffn_x_k, w.xk, B, D,
                    h16 ? w.xk16 : static_cast<__half*>(nullptr), am_xk, 1, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
         rc = linear(&L.Wfk, w.xk, B, D, w.hffn, F, RWKVQ_EPI_RELU2, nullptr, w.gscratch, w.gemm_ws, stream, h16 ? w.xk16 : nullptr,
                     am_xk, am_h, w.status);
@@ -922,7 +930,7 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         if (rc) return rc;
     }
     float* am_xo = batch_path(B) ? w.amax + 9 * B : nullptr;
-    launch_pdl(ln_shift_mix_kernel<0>, dim3(B), dim3(kRowThreads), 0, s, w.x, m->lnout_w, m->lnout_b, static_cast<float*>(nullptr), static_cast<const float*>(nullptr), w.xo, B, D,
+    launch_pdl(D <= 8 * kRowThreads ? ln_shift_mix_kernel<0, 8> : ln_shift_mix_kernel<0, kRowPer>, dim3(B), dim3(kRowThreads), 0, s, w.x, m->lnout_w, m->lnout_b, static_cast<float*>(nullptr), static_cast<const float*>(nullptr), w.xo, B, D,
                (am_xo && batch_fast()) ? w.xo16 : static_cast<__half*>(nullptr), am_xo, 1, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
     rc = linear(&m->head, w.xo, B, D, lg, V, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream, (am_xo && batch_fast()) ? w.xo16 : nullptr, am_xo, nullptr, w.status);
     if (rc) return rc;
