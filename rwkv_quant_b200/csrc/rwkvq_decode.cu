@@ -519,17 +519,26 @@ __global__ void __launch_bounds__(256) tmix_core_kernel(const TmixCoreArgs p) {
         h[4 * i] = v4.x; h[4 * i + 1] = v4.y; h[4 * i + 2] = v4.z; h[4 * i + 3] = v4.w;
     }
     pdl_launch_dependents();
-    pdl_wait();            // the state above was written a whole token ago
+    // per-channel parameters of warps 0 and 1 (channel hi * 64 + tid; r_k also for the partner channel of the
+    // final dot product): nothing the kernels before this one write, so they are loaded before the wait
+    float pw0 = 0.f, pa0 = 0.f, pka = 0.f, pkk = 0.f, pv0 = 0.f, prk0 = 0.f, prk1 = 0.f, plw = 0.f, plb = 0.f;
     if (tid < 64) {
         const int c = hi * 64 + tid;
+        pw0 = __ldg(p.w0 + c); pa0 = __ldg(p.a0 + c); pka = __ldg(p.k_a + c); pkk = __ldg(p.k_k + c);
+        if (!p.layer0) pv0 = __ldg(p.v0 + c);
+        prk0 = __ldg(p.r_k + hi * 64 + lane); prk1 = __ldg(p.r_k + hi * 64 + lane + 32);
+        plw = __ldg(p.lnx_w + c); plb = __ldg(p.lnx_b + c);
+    }
+    pdl_wait();            // the state above was written a whole token ago
+    if (tid < 64) {
         const float r = __ldcg(p.r + row + tid), k = __ldcg(p.k + row + tid);
         float v = __ldcg(p.v + row + tid);
-        const float w = expf(-0.606531f * sigmoidf_(__ldcg(p.yw + row + tid) + p.w0[c]));
-        const float av = sigmoidf_(__ldcg(p.ya + row + tid) + p.a0[c]);
-        const float k2 = k * (1.0f + (av - 1.0f) * p.k_a[c]);
+        const float w = expf(-0.606531f * sigmoidf_(__ldcg(p.yw + row + tid) + pw0));
+        const float av = sigmoidf_(__ldcg(p.ya + row + tid) + pa0);
+        const float k2 = k * (1.0f + (av - 1.0f) * pka);
         if (p.layer0) p.v_first[row + tid] = v;
-        else v = v + (__ldcg(p.v_first + row + tid) - v) * sigmoidf_(__ldcg(p.yv + row + tid) + p.v0[c]);
-        const float kk = k * p.k_k[c];
+        else v = v + (__ldcg(p.v_first + row + tid) - v) * sigmoidf_(__ldcg(p.yv + row + tid) + pv0);
+        const float kk = k * pkk;
         sKK[tid] = kk; sAV[tid] = av; sT[tid] = kk * kk;
         sW[tid] = w; sK[tid] = k2; sR[tid] = r; sV[tid] = v; sG[tid] = __ldcg(p.g + row + tid);
     }
@@ -559,17 +568,16 @@ __global__ void __launch_bounds__(256) tmix_core_kernel(const TmixCoreArgs p) {
     if (part == 0) sY[dv] = y;
     __syncthreads();
     if (tid < 64) {            // warps 0 and 1: group norm over the head (two-pass), bonus, gate
-        const int c = hi * 64 + tid;
         const float mean = warp_sum64(sY, lane) / 64.f;
         const float d0 = sY[lane] - mean, d1 = sY[lane + 32] - mean;
-        float var = d0 * d0 + d1 * d1, dp = sR[lane] * sK[lane] * p.r_k[hi * 64 + lane] + sR[lane + 32] * sK[lane + 32] * p.r_k[hi * 64 + lane + 32];
+        float var = d0 * d0 + d1 * d1, dp = sR[lane] * sK[lane] * prk0 + sR[lane + 32] * sK[lane + 32] * prk1;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             var += __shfl_xor_sync(0xFFFFFFFFu, var, o);
             dp += __shfl_xor_sync(0xFFFFFFFFu, dp, o);
         }
         const float nrm = (sY[tid] - mean) * (1.0f / sqrtf(var / 64.f + 64e-5f));
-        const float o = (nrm * p.lnx_w[c] + p.lnx_b[c] + dp * sV[tid]) * sG[tid];
+        const float o = (nrm * plw + plb + dp * sV[tid]) * sG[tid];
         p.og[row + tid] = o;
         if (p.og_amax != nullptr) {          // warps 0 and 1 hold the 64 outputs
             float m = fabsf(o);
