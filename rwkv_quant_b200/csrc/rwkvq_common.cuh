@@ -268,7 +268,8 @@ bool tcb_enabled();
 bool tcb_forced();        // a profiling override asks for the tcgen05 kernel at every batch size
 int launch_gemm_tcb(const rwkvq_qtensor* ts, int n_mats, const void* const* xs, bool half_in, const float* const* scales,
                     int N, long long ldx, float* const* ys, long long ldy, int epilogue, const float* const* resids,
-                    float* const* amax_outs, int* status, cudaStream_t s);
+                    float* const* amax_outs, int* status, cudaStream_t s, bool exact = false,
+                    const void* const* xs_lo = nullptr, const void* const* xs_sum = nullptr);   // exact: two-term operands
 // LoRA pair of the time-mix block for a batch of streams on the tensor cores (rwkvq_lora_mma.cu)
 bool lora_mma_ok(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, int n_br, int D);
 int launch_lora_pair_mma(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, const float* const* xs,

@@ -170,14 +170,19 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
                                                                   float* __restrict__ shift,
                                                                   const float* __restrict__ mix,
                                                                   float* __restrict__ out, int B, int D,
-                                                                  __half* __restrict__ x16_out, float* __restrict__ unscale_out,
-                                                                  int x16_mask,
+                                                                  __half* __restrict__ x16_out, __half* __restrict__ x16lo_out,
+                                                                  __half* __restrict__ xsum_out,
+                                                                  float* __restrict__ unscale_out, int x16_mask,
                                                                   float* __restrict__ zero_a, float* __restrict__ zero_b) {
     // x16_out (optional) [max(NMIX, 1)][B][D] with unscale_out [max(NMIX, 1)][B]: the rows selected by
     // x16_mask also as fp16(out * 2^s), s chosen from the row's max so that no value leaves the fp16
     // range, and 2^-s: the form the single-term small-batch linear reads (half the bytes, no
-    // conversion there).  With unscale_out alone, max|out| of the selected rows goes there instead
-    // (what the two-term small-batch linear wants beside the fp32 rows);
+    // conversion there); x16lo_out with xsum_out (optional; D a multiple of 128): the form the two-term
+    // tcgen05 linear reads: s is then chosen for |out * 2^s| <= 2^9, x16lo_out (same shape) takes
+    // fp16(out * 2^s - x16_out) and xsum_out [max(NMIX, 1)][B][D / 128][8] the sums of out * 2^s over the
+    // four 32-column blocks of every 128 columns, 4 high halves then 4 low halves.  With unscale_out
+    // alone, max|out| of the selected rows goes there instead (what the two-term mma.sync linear wants
+    // beside the fp32 rows);
     // zero_a / zero_b (optional) [B]: slots later kernels of the layer merge their own row maxima
     // into, cleared here for stream b
     constexpr int NM = NMIX > 0 ? NMIX : 1;
@@ -257,14 +262,16 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
                 if ((x16_mask >> threadIdx.x) & 1) unscale_out[threadIdx.x * B + b] = r;
                 return;
             }
-            // |x| * 2^(14 - e) <= 2^14 with max|x| <= 2^e; a non-finite row keeps scale 1 and propagates
+            // |x| * 2^(14 - e) <= 2^14 with max|x| <= 2^e (2^9 for the two-term form, whose block sums must
+            // stay inside the fp16 range); a non-finite row keeps scale 1 and propagates
             float s1 = 1.f, u1 = 1.f;
             if (r > 0.f && r < INFINITY) {
                 int e = 0;
                 frexpf(r, &e);
                 e = max(-100, e);
-                s1 = ldexpf(1.f, 14 - e);
-                u1 = ldexpf(1.f, e - 14);
+                const int top = x16lo_out ? 9 : 14;
+                s1 = ldexpf(1.f, top - e);
+                u1 = ldexpf(1.f, e - top);
             }
             sc_m[threadIdx.x] = s1;
             if ((x16_mask >> threadIdx.x) & 1) unscale_out[threadIdx.x * B + b] = u1;
@@ -277,13 +284,31 @@ __global__ void __launch_bounds__(kRowThreads) ln_shift_mix_kernel(const float* 
             if (d >= D) continue;
             const size_t bd = static_cast<size_t>(b) * D + d;
             const float xn = (v[i] - mean) * inv * lw[i] + lb[i];
-            if (NMIX == 0) { x16_out[bd] = __float2half_rn(xn * sc_m[0]); continue; }
+            // d >= D holds for a whole warp or for none of it (D is a multiple of 32 whenever xsum_out is given)
+            auto emit = [&](int m, float sx) {
+                const size_t o = (static_cast<size_t>(m) * B) * D + bd;
+                const __half hi = __float2half_rn(sx);
+                x16_out[o] = hi;
+                if (x16lo_out == nullptr) return;
+                x16lo_out[o] = __float2half_rn(sx - __half2float(hi));
+                float bs = sx;                                   // the warp holds one block of 32 columns
+#pragma unroll
+                for (int sh = 16; sh > 0; sh >>= 1) bs += __shfl_xor_sync(0xFFFFFFFFu, bs, sh);
+                if ((threadIdx.x & 31) == 0) {
+                    const int blk = d >> 5;
+                    __half* sp = xsum_out + ((static_cast<size_t>(m) * B + b) * (D >> 7) + (blk >> 2)) * 8 + (blk & 3);
+                    const __half sh16 = __float2half_rn(bs);
+                    sp[0] = sh16;
+                    sp[4] = __float2half_rn(bs - __half2float(sh16));
+                }
+            };
+            if (NMIX == 0) { emit(0, xn * sc_m[0]); continue; }
             const float xx = prev[i] - xn;
 #pragma unroll
             for (int m = 0; m < NMIX; ++m) {
                 if (!((x16_mask >> m) & 1)) continue;
                 const float o = xn + xx * (PRE ? mxr[PRE ? m : 0][PRE ? i : 0] : __ldg(mix + m * D + d));
-                x16_out[(static_cast<size_t>(m) * B) * D + bd] = __float2half_rn(o * sc_m[m < NM ? m : 0]);
+                emit(m, o * sc_m[m < NM ? m : 0]);
             }
         }
     }
@@ -641,6 +666,20 @@ inline bool batch_path(int B) { return B > 2 && B <= kBatchMax; }
 // streams on (64 streams: 3.77 against 4.43 ms per step) and loses below (32: 2.87 / 2.68 ms, 8: 2.42 / 2.01 ms):
 // its pass (dependent weight loads -> conversion -> MMA) is longer than a warp-iteration of the mma.sync form
 inline bool tcb_pays(int B) { return batch_fast() && tcb_enabled() && B > 32; }
+// RWKVQ_TCB_EXACT=1 in the environment (read once; off by default): in the default two-term precision the
+// tcgen05 form of the two-term linear (fp16 pairs and block sums from the LayerNorm kernels) serves r / k / v,
+// the ffn key and the head from 33 streams on; the output projection and the ffn value, whose inputs reach
+// the linear as fp32 rows without a known scale, stay on the mma.sync form.  Measured on B200 (1.5B, whole
+// decode step, 64 / 48 / 33 streams): 4.63 / 4.02 / 3.82 ms against 4.04 / 3.76 / 3.60 ms on mma.sync
+// alone, which is why it is not the default.
+int g_tcb_exact = -1;
+inline bool tcx_pays(int B) {
+    if (g_tcb_exact < 0) {
+        const char* e = getenv("RWKVQ_TCB_EXACT");
+        g_tcb_exact = (e != nullptr && e[0] == '1') ? 1 : 0;
+    }
+    return g_tcb_exact == 1 && !batch_fast() && tcb_enabled() && B > 32 && B <= kBatchMax;
+}
 
 
 struct Workspace {
@@ -648,6 +687,8 @@ struct Workspace {
     int* status;             // first word of the workspace: RWKVQ_E_TIMEOUT if a bounded device-side wait of a step ran out
     float* amax;             // [10][B] per-row scale inverses / maxima for the small-batch linears: 6 mix rows, og, xk, hffn, xo
     __half *xs16, *xk16, *xo16;     // fp16 forms of the mix rows, the channel-mix row and the final row
+    __half *xs16lo, *xk16lo, *xo16lo;   // their second terms (two-term tcgen05 linears)
+    __half *xs_sum, *xk_sum, *xo_sum;   // ... and block sums, [rows][B][D / 128][8]
     int n_chunks;
     size_t part_floats;
     size_t bytes;
@@ -674,6 +715,12 @@ Workspace carve(const rwkvq_model& m, int B, void* base) {
     w.xs16 = reinterpret_cast<__half*>(take(3 * b * D));
     w.xk16 = reinterpret_cast<__half*>(take((b * D + 1) / 2));
     w.xo16 = reinterpret_cast<__half*>(take((b * D + 1) / 2));
+    w.xs16lo = reinterpret_cast<__half*>(take(3 * b * D));
+    w.xk16lo = reinterpret_cast<__half*>(take((b * D + 1) / 2));
+    w.xo16lo = reinterpret_cast<__half*>(take((b * D + 1) / 2));
+    w.xs_sum = reinterpret_cast<__half*>(take(6 * b * (D / 32 + 4)));
+    w.xk_sum = reinterpret_cast<__half*>(take(b * (D / 32 + 4)));
+    w.xo_sum = reinterpret_cast<__half*>(take(b * (D / 32 + 4)));
     w.gscratch = take(gemv_mma_scratch_bytes() / sizeof(float));
     w.gemm_ws = take(rwkvq_gemm_workspace_bytes_for(B, static_cast<int>(F > D ? F : D)) / sizeof(float) + 1);
     w.bytes = off;
@@ -684,11 +731,12 @@ Workspace carve(const rwkvq_model& m, int B, void* base) {
 // One quantized linear for B right-hand sides; the single-vector tensor-core kernel gets
 // the K-split scratch, everything else goes through the public entry point.
 // x16 / x_scale: the fp16 form of x with its per-row scale inverses (what the LayerNorm kernels write
-// on the small-batch path), or null with x_scale = max|x| per row for fp32 rows; y_amax: optional
-// slots max|y| per row is merged into.
+// on the small-batch path), or null with x_scale = max|x| per row for fp32 rows; x16lo: the second fp16
+// term of x, which selects the two-term tcgen05 kernel (the caller has checked gemm_tcb_ok); y_amax:
+// optional slots max|y| per row is merged into.
 int linear(const rwkvq_qtensor* t, const float* x, int B, int in, float* y, int out, int epi, const float* resid,
            float* scratch, void* gemm_ws, void* stream, const __half* x16 = nullptr, const float* x_scale = nullptr,
-           float* y_amax = nullptr, int* status = nullptr) {
+           float* y_amax = nullptr, int* status = nullptr, const __half* x16lo = nullptr, const __half* xsum = nullptr) {
     const int ml = mma_layout_of(*t);
     if (B == 1 && ml >= 0) {
         int rc = validate_qtensor(t, "rwkvq_decode_step(linear)");
@@ -704,6 +752,11 @@ int linear(const rwkvq_qtensor* t, const float* x, int B, int in, float* y, int 
         float* ys[1] = {y};
         const float* rs[1] = {resid};
         float* ao[1] = {y_amax};
+        if (x16 && x16lo) {
+            const void* xl[1] = {x16lo};
+            const void* xm[1] = {xsum};
+            return launch_gemm_tcb(t, 1, xs, true, sc, B, in, ys, out, epi, rs, ao, status, static_cast<cudaStream_t>(stream), true, xl, xm);
+        }
         if (tcb_pays(B) && gemm_tcb_ok(*t))
             return launch_gemm_tcb(t, 1, xs, x16 != nullptr, sc, B, in, ys, out, epi, rs, ao, status, static_cast<cudaStream_t>(stream));
         return launch_gemv_batch(t, 1, xs, x16 != nullptr, sc, B, in, ys, out, epi, rs, ao, static_cast<cudaStream_t>(stream));
@@ -794,6 +847,8 @@ int lora_pair(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, co
 
 extern "C" {
 
+void rwkvq_profiling_tcb_exact(int on) { g_tcb_exact = on < 0 ? -1 : (on ? 1 : 0); }      // rwkvq_profiling.h
+
 int rwkvq_seq_embed_ln0(const rwkvq_qtensor* emb, const int64_t* tokens, const float* ln_w, const float* ln_b, float* x,
                         int64_t n_tokens, int D, void* stream) {
     int rc = validate_qtensor(emb, "rwkvq_seq_embed_ln0");
@@ -813,7 +868,8 @@ int rwkvq_seq_layer_norm(const float* x, const float* ln_w, const float* ln_b, f
                   (long long)n_rows, D, kRowThreads * kRowPer);
     launch_pdl(D <= 8 * kRowThreads ? ln_shift_mix_kernel<0, 8> : ln_shift_mix_kernel<0, kRowPer>, dim3(static_cast<unsigned>(n_rows)), dim3(kRowThreads), 0, static_cast<cudaStream_t>(stream), x,
                ln_w, ln_b, static_cast<float*>(nullptr), static_cast<const float*>(nullptr), out, static_cast<int>(n_rows), D,
-               static_cast<__half*>(nullptr), static_cast<float*>(nullptr), 0, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
+               static_cast<__half*>(nullptr), static_cast<__half*>(nullptr), static_cast<__half*>(nullptr), static_cast<float*>(nullptr), 0,
+               static_cast<float*>(nullptr), static_cast<float*>(nullptr));
     return check_launch("rwkvq_seq_layer_norm");
 }
 
@@ -851,11 +907,18 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         // the row maxima feed the small-batch linears: slots 0-5 the six mix rows, 6 og, 7 xk, 8 hffn, 9 xo
         const bool bp = batch_path(B);
         const bool h16 = bp && batch_fast();          // fp16 rows for the single-term kernels; else fp32 rows and their maxima
+        const int ml = mma_layout_of(L.Wr);
+        const bool rkv_fused = ml >= 0 && mma_layout_of(L.Wk) == ml && mma_layout_of(L.Wv) == ml && L.Wk.rows == L.Wr.rows &&
+                               L.Wv.rows == L.Wr.rows && L.Wk.cols == L.Wr.cols && L.Wv.cols == L.Wr.cols;
+        // two-term tcgen05 linears: fp16 pairs of their input rows from the LayerNorm kernels
+        const bool x_rkv = tcx_pays(B) && rkv_fused && gemm_tcb_ok(L.Wr) && gemm_tcb_ok(L.Wk) && gemm_tcb_ok(L.Wv);
+        const bool x_key = tcx_pays(B) && mma_layout_of(L.Wfk) >= 0 && gemm_tcb_ok(L.Wfk);
         float* am = bp ? w.amax : nullptr;
         float *am_og = bp ? w.amax + 6 * B : nullptr, *am_xk = bp ? w.amax + 7 * B : nullptr;
         float *am_h = bp ? w.amax + 8 * B : nullptr;
         launch_pdl(D <= 8 * kRowThreads ? ln_shift_mix_kernel<6, 8> : ln_shift_mix_kernel<6, kRowPer>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln1_w, L.ln1_b, tshift[l], L.x_mix, w.xs, B, D,
-                   h16 ? w.xs16 : static_cast<__half*>(nullptr), am, 0b001101, am_og, am_h);      // scales of the r, k, v rows
+                   (h16 || x_rkv) ? w.xs16 : static_cast<__half*>(nullptr), x_rkv ? w.xs16lo : static_cast<__half*>(nullptr),
+                   x_rkv ? w.xs_sum : static_cast<__half*>(nullptr), am, 0b001101, am_og, am_h);      // scales of the r, k, v rows
         float *xr = w.xs, *xw = w.xs + BD, *xk = w.xs + 2 * BD, *xv = w.xs + 3 * BD, *xa = w.xs + 4 * BD,
               *xg = w.xs + 5 * BD;
         float *r = w.rkv, *k = w.rkv + BD, *v = w.rkv + 2 * BD;
@@ -871,7 +934,6 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         // and stages its weights while that still runs, and r / k / v take the side stream.
         cudaStream_t s_rkv = s;
         if (lane && B <= 16) { s_rkv = lane->stream; s_lora = s; }
-        const int ml = mma_layout_of(L.Wr);
         if (B == 1 && ml >= 0 && mma_layout_of(L.Wk) == ml && mma_layout_of(L.Wv) == ml && L.Wk.rows == D &&
             L.Wv.rows == D && L.Wr.rows == D && L.Wk.cols == D && L.Wv.cols == D && L.Wr.cols == D) {
             // r, k, v in one launch: three matrices, three inputs (rows 0, 2, 3 of xs)
@@ -883,18 +945,22 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
             const void* x_each[3] = {xr, xk, xv};
             rc = launch_gemv_mma(ml, three, 3, xr, RWKVQ_F32, D, r, D, RWKVQ_EPI_NONE, nullptr, 1, s_rkv, x_each, w.gscratch);
             if (rc) return rc;
-        } else if (bp && ml >= 0 && mma_layout_of(L.Wk) == ml && mma_layout_of(L.Wv) == ml &&
-                   L.Wk.rows == L.Wr.rows && L.Wv.rows == L.Wr.rows && L.Wk.cols == L.Wr.cols && L.Wv.cols == L.Wr.cols) {
+        } else if (bp && rkv_fused) {
             for (const rwkvq_qtensor* t : {&L.Wr, &L.Wk, &L.Wv}) {
                 rc = validate_qtensor(t, "rwkvq_decode_step(r/k/v)");
                 if (rc) return rc;
             }
             const rwkvq_qtensor three[3] = {L.Wr, L.Wk, L.Wv};
             const void* x3[3] = {w.xs16, w.xs16 + 2 * BD, w.xs16 + 3 * BD};
-            if (!h16) { x3[0] = xr; x3[1] = xk; x3[2] = xv; }
+            const void* x3lo[3] = {w.xs16lo, w.xs16lo + 2 * BD, w.xs16lo + 3 * BD};
+            const size_t BS = static_cast<size_t>(B) * (D / 128) * 8;     // block sums of one mix row
+            const void* x3sum[3] = {w.xs_sum, w.xs_sum + 2 * BS, w.xs_sum + 3 * BS};
+            if (!h16 && !x_rkv) { x3[0] = xr; x3[1] = xk; x3[2] = xv; }
             const float* a3[3] = {am, am + 2 * B, am + 3 * B};
             float* y3[3] = {r, k, v};
-            if (tcb_pays(B) && gemm_tcb_ok(L.Wr))
+            if (x_rkv)
+                rc = launch_gemm_tcb(three, 3, x3, true, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, w.status, s_rkv, true, x3lo, x3sum);
+            else if (tcb_pays(B) && gemm_tcb_ok(L.Wr))
                 rc = launch_gemm_tcb(three, 3, x3, h16, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, w.status, s_rkv);
             else
                 rc = launch_gemv_batch(three, 3, x3, h16, a3, B, D, y3, D, RWKVQ_EPI_NONE, nullptr, nullptr, s_rkv);
@@ -930,17 +996,22 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         if (rc) return rc;
         // ---- channel mix
         launch_pdl(D <= 8 * kRowThreads ? ln_shift_mix_kernel<1, 8> : ln_shift_mix_kernel<1, kRowPer>, dim3(B), dim3(kRowThreads), 0, s, w.x, L.ln2_w, L.ln2_b, cshift[l], L.ffn_x_k, w.xk, B, D,
-                   h16 ? w.xk16 : static_cast<__half*>(nullptr), am_xk, 1, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
-        rc = linear(&L.Wfk, w.xk, B, D, w.hffn, F, RWKVQ_EPI_RELU2, nullptr, w.gscratch, w.gemm_ws, stream, h16 ? w.xk16 : nullptr,
-                    am_xk, am_h, w.status);
+                   (h16 || x_key) ? w.xk16 : static_cast<__half*>(nullptr), x_key ? w.xk16lo : static_cast<__half*>(nullptr),
+                   x_key ? w.xk_sum : static_cast<__half*>(nullptr), am_xk, 1, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
+        rc = linear(&L.Wfk, w.xk, B, D, w.hffn, F, RWKVQ_EPI_RELU2, nullptr, w.gscratch, w.gemm_ws, stream, (h16 || x_key) ? w.xk16 : nullptr,
+                    am_xk, am_h, w.status, x_key ? w.xk16lo : nullptr, x_key ? w.xk_sum : nullptr);
         if (rc) return rc;
         rc = linear(&L.Wfv, w.hffn, B, F, w.x, D, RWKVQ_EPI_ADD, w.x, w.gscratch, w.gemm_ws, stream, nullptr, am_h, nullptr, w.status);
         if (rc) return rc;
     }
     float* am_xo = batch_path(B) ? w.amax + 9 * B : nullptr;
+    const bool x_head = tcx_pays(B) && mma_layout_of(m->head) >= 0 && gemm_tcb_ok(m->head);
+    const bool xo_h16 = (am_xo && batch_fast()) || x_head;
     launch_pdl(D <= 8 * kRowThreads ? ln_shift_mix_kernel<0, 8> : ln_shift_mix_kernel<0, kRowPer>, dim3(B), dim3(kRowThreads), 0, s, w.x, m->lnout_w, m->lnout_b, static_cast<float*>(nullptr), static_cast<const float*>(nullptr), w.xo, B, D,
-               (am_xo && batch_fast()) ? w.xo16 : static_cast<__half*>(nullptr), am_xo, 1, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
-    rc = linear(&m->head, w.xo, B, D, lg, V, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream, (am_xo && batch_fast()) ? w.xo16 : nullptr, am_xo, nullptr, w.status);
+               xo_h16 ? w.xo16 : static_cast<__half*>(nullptr), x_head ? w.xo16lo : static_cast<__half*>(nullptr),
+               x_head ? w.xo_sum : static_cast<__half*>(nullptr), am_xo, 1, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
+    rc = linear(&m->head, w.xo, B, D, lg, V, RWKVQ_EPI_NONE, nullptr, w.gscratch, w.gemm_ws, stream, xo_h16 ? w.xo16 : nullptr, am_xo, nullptr,
+                w.status, x_head ? w.xo16lo : nullptr, x_head ? w.xo_sum : nullptr);
     if (rc) return rc;
     if (next_tokens) {
         float* pv = w.argv;

@@ -21,6 +21,8 @@
 //     shared memory in rank order, applies the epilogue and stores.
 // Every mbarrier wait is bounded; on expiry the CTA records RWKVQ_E_TIMEOUT in the status word,
 // skips its work, still passes the cluster barriers, frees its tensor memory and returns.
+// A second form of the kernel (template parameter EX, described at the kernel) keeps both operands
+// as two fp16 terms and gives fp32-grade results.
 #include <cooperative_groups.h>
 
 #include <stdlib.h>
@@ -35,8 +37,7 @@ namespace rwkvq {
 
 constexpr int kTbProducers = 256;         // warps 0-7: weights, activations, epilogue
 constexpr int kTbThreads = 288;           // + warp 8: one lane issues the MMAs
-constexpr int kTbPassK = 256;             // columns of a pass: one super-block, four 64-K slabs
-constexpr int kTbSlabs = kTbPassK / kGmK;
+constexpr int kTbSbK = 256;               // columns of a super-block
 constexpr int kTbRP = kGmRows + 4;        // pitch of a partial-sum row
 constexpr int kTbMaxMats = 4;
 extern unsigned long long* g_batch_trace;      // rwkvq_gemv_batch.cu: set by rwkvq_profiling_batch_trace
@@ -46,13 +47,16 @@ struct TcbArgs {
     const float* x[kTbMaxMats];           // [N, ldx] fp32, or null when x16 is given
     const float* amax[kTbMaxMats];        // with x:   [N] max|x| per token
     const __half* x16[kTbMaxMats];        // [N, ldx] fp16 rows = x * 2^s
+    const __half* x16lo[kTbMaxMats];      // two-term kernel with x16: fp16(x * 2^s - x16)
+    const __half* xsum[kTbMaxMats];       // ... and [N, cols / 128][8]: the sums of x * 2^s over the four 32-column blocks
+                                          //     of every 128 columns, 4 high halves then 4 low halves
     const float* unscale[kTbMaxMats];     // with x16: [N] 2^-s
     float* y[kTbMaxMats];                 // [N, ldy]
     const float* resid[kTbMaxMats];
     float* amax_out[kTbMaxMats];          // optional [N]: max|y| per token is merged into it (atomic max; zeroed by the caller)
     long long ldx, ldy;
     int n_tokens, epilogue;
-    int passes;                           // 256-column passes of one CTA's K slice
+    int passes;                           // passes of one CTA's K slice: 256 columns each, 128 in the two-term kernel
     int ks;                               // CTAs along K = cluster size
     int* status;                          // device word: first error code, 0 = ok
     unsigned long long* trace;            // profiling aid (rwkvq_profiling.h): global-timer marks of CTA (0,0,0), or null
@@ -66,15 +70,34 @@ __device__ __forceinline__ void tb_mark(const TcbArgs& a, int slot) {
     }
 }
 
-template <int NT>
+// EX: both operands as two fp16 terms (W: p = fp16(q*s) and its exact rounding error e; x: hi =
+// fp16(x * 2^s) and lo = fp16(x * 2^s - hi)) and three MMAs per K step (e*hi + p*lo + p*hi) into the
+// one accumulator; the block mins, fp16 values by the codec's definition, multiply the per-block
+// sums of the activations in one more MMA per pass (K = the 4 blocks of the pass against their high
+// halves + the same 4 against their low halves, in a small operand pair without swizzle).  The fp32
+// accumulation is then the only rounding that matters (~1e-6 against an fp32 dequantise-and-multiply
+// instead of ~5e-4).  A pass covers 128 columns so that the doubled operands keep the shared-memory
+// footprint of the single-term form; the activations are scaled to at most 2^9 so that a block sum
+// stays inside the fp16 range.
+template <int NT, bool EX>
 __global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int PASSK = EX ? 128 : 256;                        // columns of a pass
+    constexpr int SLABS = PASSK / kGmK;                          // 64-K slabs of a pass: 2 or 4
+    constexpr int ITEMS = PASSK / 32;                            // 32-column items of a row and pass: 4 or 8
+    constexpr int RGRP = kTbProducers / ITEMS;                   // rows one item per thread covers: 64 or 32
+    constexpr int QN = kGmRows / RGRP;                           // items per thread and pass: 2 or 4
     constexpr int SLAB = kGmRows * 128, BSLAB = NT * 128;
     constexpr uint32_t TM_COLS = NT < 32 ? 32 : NT;
     constexpr int RP = kTbRP;
-    unsigned char* a_slabs = smem;                               // [4][SLAB]  weights of the pass
-    unsigned char* b_slabs = smem + kTbSlabs * SLAB;             // [4][BSLAB] activations of the pass
+    unsigned char* a_slabs = smem;                               // [SLABS][SLAB]  weights of the pass (EX: p)
+    unsigned char* e_slabs = a_slabs + SLABS * SLAB;             // EX: [SLABS][SLAB] e
+    unsigned char* b_slabs = a_slabs + (EX ? 2 : 1) * SLABS * SLAB;   // [SLABS][BSLAB] activations of the pass (EX: hi)
+    unsigned char* l_slabs = b_slabs + SLABS * BSLAB;            // EX: [SLABS][BSLAB] lo
+    unsigned char* m_a = l_slabs + SLABS * BSLAB;                // EX: [2][128 rows][16 B] block mins (K 0-3 and again 4-7; K 8-15 zero)
+    unsigned char* m_b = m_a + 2 * kGmRows * 16;                 // EX: [2][NT][16 B] block sums (4 high, 4 low halves; K 8-15 zero)
+    const bool has_min = EX && a.t[blockIdx.y].kind == RWKVQ_KIND_SB6;
     float* part = reinterpret_cast<float*>(a_slabs);             // [NT][RP], over the operands once the MMAs are done
     __shared__ uint64_t bar_full, bar_mma;
     __shared__ uint32_t s_tmem;
@@ -87,7 +110,7 @@ __global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a
     const int ks = a.ks, rank = static_cast<int>(blockIdx.x) % ks, rt = static_cast<int>(blockIdx.x) / ks;
     const int row0 = rt * kGmRows;
     const int n0 = blockIdx.z * NT, nn = min(NT, a.n_tokens - n0);
-    const int np = a.passes, sbk0 = rank * np;
+    const int np = a.passes, pass0 = rank * np;                 // first pass of this CTA, in units of PASSK columns
     const bool is16 = a.x16[blockIdx.y] != nullptr;
 
     tb_mark(a, 0);
@@ -111,32 +134,52 @@ __global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a
             pdl_wait();
             const uint32_t idesc = umma_idesc(NT);
             const uint64_t a_desc0 = umma_desc(smem_addr(a_slabs)), b_desc0 = umma_desc(smem_addr(b_slabs));
+            const uint64_t e_desc0 = umma_desc(smem_addr(e_slabs)), l_desc0 = umma_desc(smem_addr(l_slabs));
+            const uint64_t ma_desc = umma_desc_plain(smem_addr(m_a), kGmRows * 16, 128);
+            const uint64_t mb_desc = umma_desc_plain(smem_addr(m_b), NT * 16, 128);
             bool ok = true;
             for (int p = 0; p < np && ok; ++p) {
                 if (!mbar_wait_bounded(&bar_full, p & 1)) { ok = false; break; }
                 if (s_fail) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
-                for (int sl = 0; sl < kTbSlabs; ++sl) {
+                for (int sl = 0; sl < SLABS; ++sl) {
                     const uint64_t ad = a_desc0 + (static_cast<uint64_t>(sl * SLAB) >> 4);
                     const uint64_t bd = b_desc0 + (static_cast<uint64_t>(sl * BSLAB) >> 4);
+                    const uint64_t ed = e_desc0 + (static_cast<uint64_t>(sl * SLAB) >> 4);
+                    const uint64_t ld = l_desc0 + (static_cast<uint64_t>(sl * BSLAB) >> 4);
 #pragma unroll
-                    for (int k = 0; k < kGmK / 16; ++k)        // 32 bytes further along K per step
-                        umma_f16(tmem, ad + 2 * k, bd + 2 * k, idesc, (p | sl | k) ? 1u : 0u);
+                    for (int k = 0; k < kGmK / 16; ++k) {      // 32 bytes further along K per step
+                        if (EX) {                               // small terms first
+                            umma_f16(tmem, ed + 2 * k, bd + 2 * k, idesc, (p | sl | k) ? 1u : 0u);
+                            umma_f16(tmem, ad + 2 * k, ld + 2 * k, idesc, 1u);
+                            umma_f16(tmem, ad + 2 * k, bd + 2 * k, idesc, 1u);
+                        } else {
+                            umma_f16(tmem, ad + 2 * k, bd + 2 * k, idesc, (p | sl | k) ? 1u : 0u);
+                        }
+                    }
                 }
+                if (has_min) umma_f16(tmem, ma_desc, mb_desc, idesc, 1u);
                 umma_commit(&bar_mma);
             }
             if (!ok) s_fail = 1;
         }
     } else {
         // ------------------------------------------------------------------ producers
-        const int pit = tid & 7, prow = tid >> 3;              // item (32 columns) of the pass, row within a group of 32
-        Packed P[4];
-        auto load_all = [&](int p) {
+        const int pit = tid % ITEMS, prow = tid / ITEMS;       // item (32 columns) of the pass, row within a group of RGRP
+        // packed weights in registers: one pass ahead; the two-term kernel, whose passes are half as
+        // long, two passes ahead (same register count), in two sets used in turn
+        constexpr int AHEAD = EX ? 2 : 1;
+        Packed P0[QN], P1[EX ? QN : 1];
+        // pass p of this CTA: super-block and first item inside it
+        auto sb_of = [&](int p) { return EX ? (pass0 + p) >> 1 : pass0 + p; };
+        auto item_of = [&](int p) { return EX ? ((pass0 + p) & 1) * ITEMS + pit : pit; };
+        auto load_all = [&](int p, Packed* P) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) load_packed(P[q], t, min(row0 + 32 * q + prow, t.rows - 1), sbk0 + p, pit);
+            for (int q = 0; q < QN; ++q) load_packed(P[q], t, min(row0 + RGRP * q + prow, t.rows - 1), sb_of(p), item_of(p));
         };
-        load_all(0);                                            // weights do not depend on the producer of x
+        load_all(0, P0);                                        // weights do not depend on the producer of x
+        if (EX && np > 1) load_all(1, P1);
         pdl_wait();
         tb_mark(a, 2);
         if (tid < NT) {
@@ -150,38 +193,105 @@ __global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a
                     int e = 0;
                     frexpf(am, &e);
                     e = max(-100, e);
-                    s1 = ldexpf(1.f, 14 - e);
-                    u1 = ldexpf(1.f, e - 14);
+                    s1 = ldexpf(1.f, (EX ? 9 : 14) - e);
+                    u1 = ldexpf(1.f, e - (EX ? 9 : 14));
                 }
             }
             s_sc[tid] = s1; s_un[tid] = u1; s_omax[tid] = 0.f;
         }
+        if (has_min) {                                          // the K 8-15 halves of the min operands stay zero
+            for (int i = tid; i < kGmRows + NT; i += kTbProducers)
+                *reinterpret_cast<uint4*>(i < kGmRows ? m_a + kGmRows * 16 + i * 16 : m_b + NT * 16 + (i - kGmRows) * 16) = make_uint4(0, 0, 0, 0);
+        }
         // producers only: named barrier 1 (the issuer warp does not take part)
         asm volatile("bar.sync 1, %0;" ::"n"(kTbProducers) : "memory");
-        constexpr int VPT = NT * 32 / kTbProducers;             // 16-byte activation vectors per thread and pass: 2, 4, 8
-        for (int p = 0; p < np; ++p) {
-            const int kbase = (sbk0 + p) * kTbPassK;
-            uint4 xv[VPT];
+        constexpr int VROW = PASSK / 8;                         // 8-column vectors per token and pass: 32 or 16
+        constexpr int VPT = NT * VROW / kTbProducers;           // ... per thread: 2, 4, 8 (EX: 1, 2, 4)
+        auto do_pass = [&](int p, Packed* P) {
+            const int kbase = (pass0 + p) * PASSK;
+            uint4 xv[VPT], xl[EX ? VPT : 1], sv = make_uint4(0, 0, 0, 0);
+            if (has_min && is16 && tid < nn)
+                sv = __ldcg(reinterpret_cast<const uint4*>(a.xsum[blockIdx.y] + (static_cast<size_t>(n0 + tid) * (t.cols >> 7) + pass0 + p) * 8));
             if (is16) {                                          // requested before the wait and the conversion
                 const __half* xg = a.x16[blockIdx.y] + static_cast<size_t>(n0) * a.ldx + kbase;
+                const __half* xlg = EX ? a.x16lo[blockIdx.y] + static_cast<size_t>(n0) * a.ldx + kbase : nullptr;
 #pragma unroll
                 for (int u = 0; u < VPT; ++u) {
-                    const int idx = tid + u * kTbProducers, n = idx >> 5, k8 = idx & 31;
+                    const int idx = tid + u * kTbProducers, n = idx / VROW, k8 = idx % VROW;
                     xv[u] = n < nn ? __ldcg(reinterpret_cast<const uint4*>(xg + static_cast<size_t>(n) * a.ldx) + k8) : make_uint4(0, 0, 0, 0);
+                    if (EX) xl[u] = n < nn ? __ldcg(reinterpret_cast<const uint4*>(xlg + static_cast<size_t>(n) * a.ldx) + k8) : make_uint4(0, 0, 0, 0);
                 }
             }
             if (p > 0) {                                         // the MMAs of the previous pass have read the operands
                 if (lane == 0 && !s_fail && !mbar_wait_bounded(&bar_mma, (p - 1) & 1)) s_fail = 1;
                 __syncwarp();
             }
-            if (!s_fail) {
+            if (!__any_sync(0xFFFFFFFFu, s_fail != 0)) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) convert_store(P[q], t, 32 * q + prow, pit, pit & 1, a_slabs + (pit >> 1) * SLAB);
+                for (int q = 0; q < QN; ++q) {
+                    if (EX) {
+                        const __half mn = convert_store_pair(P[q], t, RGRP * q + prow, item_of(p), pit & 1, a_slabs + (pit >> 1) * SLAB,
+                                                             e_slabs + (pit >> 1) * SLAB);
+                        if (has_min) {                           // block `pit` of the pass: beside the high and the low sums
+                            __half* mrow = reinterpret_cast<__half*>(m_a + (RGRP * q + prow) * 16);
+                            mrow[pit] = mn;
+                            mrow[4 + pit] = mn;
+                        }
+                    } else {
+                        convert_store(P[q], t, RGRP * q + prow, pit, pit & 1, a_slabs + (pit >> 1) * SLAB);
+                    }
+                }
+                if (has_min && is16 && tid < NT) *reinterpret_cast<uint4*>(m_b + tid * 16) = sv;
                 if (is16) {
 #pragma unroll
                     for (int u = 0; u < VPT; ++u) {
-                        const int idx = tid + u * kTbProducers, n = idx >> 5, k8 = idx & 31;
+                        const int idx = tid + u * kTbProducers, n = idx / VROW, k8 = idx % VROW;
                         *reinterpret_cast<uint4*>(b_slabs + (k8 >> 3) * BSLAB + sw128_offset(n, k8 & 7)) = xv[u];
+                        if (EX) *reinterpret_cast<uint4*>(l_slabs + (k8 >> 3) * BSLAB + sw128_offset(n, k8 & 7)) = xl[u];
+                    }
+                } else if (EX) {
+                    const float* xg = a.x[blockIdx.y] + static_cast<size_t>(n0) * a.ldx + kbase;
+                    constexpr int RV = VPT > 1 ? VPT / 2 : 1;     // vectors per round: half of them in flight at a time
+#pragma unroll
+                    for (int r0 = 0; r0 < VPT; r0 += RV) {
+                        float4 f[RV][2];
+#pragma unroll
+                        for (int u = 0; u < RV; ++u) {
+                            const int idx = tid + (r0 + u) * kTbProducers, n = idx / VROW, k8 = idx % VROW;
+                            const float4* src = reinterpret_cast<const float4*>(xg + static_cast<size_t>(n) * a.ldx) + 2 * k8;
+                            f[u][0] = n < nn ? __ldcg(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            f[u][1] = n < nn ? __ldcg(src + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                        for (int u = 0; u < RV; ++u) {
+                            const int idx = tid + (r0 + u) * kTbProducers, n = idx / VROW, k8 = idx % VROW;
+                            const float s1 = s_sc[n];
+                            const float v[8] = {f[u][0].x * s1, f[u][0].y * s1, f[u][0].z * s1, f[u][0].w * s1,
+                                                f[u][1].x * s1, f[u][1].y * s1, f[u][1].z * s1, f[u][1].w * s1};
+                            uint32_t hw[4], lw[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const __half2 hh = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+                                const float2 hf = __half22float2(hh);
+                                const __half2 ll = __floats2half2_rn(v[2 * j] - hf.x, v[2 * j + 1] - hf.y);
+                                hw[j] = *reinterpret_cast<const uint32_t*>(&hh);
+                                lw[j] = *reinterpret_cast<const uint32_t*>(&ll);
+                            }
+                            const uint32_t off = (k8 >> 3) * BSLAB + sw128_offset(n, k8 & 7);
+                            *reinterpret_cast<uint4*>(b_slabs + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                            *reinterpret_cast<uint4*>(l_slabs + off) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+                            if (has_min) {      // 4 consecutive lanes hold the 32 columns of one block
+                                float bs = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+                                bs += __shfl_xor_sync(0xFFFFFFFFu, bs, 1);
+                                bs += __shfl_xor_sync(0xFFFFFFFFu, bs, 2);
+                                if ((k8 & 3) == 0) {
+                                    __half* srow = reinterpret_cast<__half*>(m_b + n * 16);
+                                    const __half sh = __float2half_rn(bs);
+                                    srow[k8 >> 2] = sh;
+                                    srow[4 + (k8 >> 2)] = __float2half_rn(bs - __half2float(sh));
+                                }
+                            }
+                        }
                     }
                 } else {
                     const float* xg = a.x[blockIdx.y] + static_cast<size_t>(n0) * a.ldx + kbase;
@@ -213,7 +323,15 @@ __global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_full);              // one arrival per warp
             if (p == 0) tb_mark(a, 3);
-            if (p + 1 < np) load_all(p + 1);                    // the registers are free again
+            if (p + AHEAD < np) load_all(p + AHEAD, P);         // the registers are free again
+        };
+        if (EX) {
+            for (int p = 0; p < np; p += 2) {                   // the pass count of the two-term kernel is even
+                do_pass(p, P0);
+                do_pass(p + 1, P1);
+            }
+        } else {
+            for (int p = 0; p < np; ++p) do_pass(p, P0);
         }
         // the accumulator is complete when the last commit has arrived
         if (lane == 0 && !s_fail && !mbar_wait_bounded(&bar_mma, (np - 1) & 1)) s_fail = 1;
@@ -310,16 +428,17 @@ __global__ void __launch_bounds__(kTbThreads, 2) gemm_tcb_kernel(const TcbArgs a
 
 namespace {
 
-template <int NT>
+template <int NT, bool EX>
 int launch_tcb(TcbArgs& a, int n_mats, int n_groups, int row_tiles, cudaStream_t s) {
-    const size_t smem = 1024 + static_cast<size_t>(kTbSlabs) * (kGmRows * 128 + NT * 128);
+    // single-term: four slabs of weights and activations; two-term: two slabs of each of p, e, hi, lo + the min operands
+    const size_t smem = 1024 + static_cast<size_t>(4) * (kGmRows * 128 + NT * 128) + (EX ? 2 * 16 * (kGmRows + NT) : 0);
     static bool configured[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) dev = 0;
     if (dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcb_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcb_kernel<NT, EX>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "rwkvq_gemm_tcb: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        e = cudaFuncSetAttribute(gemm_tcb_kernel<NT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);      // clusters of 16
+        e = cudaFuncSetAttribute(gemm_tcb_kernel<NT, EX>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);      // clusters of 16
         if (e != cudaSuccess) return fail(RWKVQ_E_LIMIT, "rwkvq_gemm_tcb: cluster size attribute: %s", cudaGetErrorString(e));
         if (dev < 64) configured[dev] = true;
     }
@@ -335,7 +454,7 @@ int launch_tcb(TcbArgs& a, int n_mats, int n_groups, int row_tiles, cudaStream_t
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tcb_kernel<NT>, a);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tcb_kernel<NT, EX>, a);
     if (le != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "rwkvq_gemm_tcb: %s", cudaGetErrorString(le));
     return RWKVQ_OK;
 }
@@ -361,10 +480,13 @@ bool gemm_tcb_ok(const rwkvq_qtensor& t) {
     return false;
 }
 
-// Same contract as launch_gemv_batch (rwkvq_common.cuh), plus the device status word.
+// Same contract as launch_gemv_batch (rwkvq_common.cuh), plus the device status word.  `exact`: the
+// two-term kernel; with half_in its rows are scaled to at most 2^9 and it needs xs_lo[k] = fp16(x * 2^s
+// - xs[k]) and xs_sum[k] (TcbArgs::xsum) beside xs[k].
 int launch_gemm_tcb(const rwkvq_qtensor* ts, int n_mats, const void* const* xs, bool half_in, const float* const* scales,
                     int N, long long ldx, float* const* ys, long long ldy, int epilogue, const float* const* resids,
-                    float* const* amax_outs, int* status, cudaStream_t s) {
+                    float* const* amax_outs, int* status, cudaStream_t s, bool exact, const void* const* xs_lo,
+                    const void* const* xs_sum) {
     RWKVQ_REQUIRE(n_mats >= 1 && n_mats <= kTbMaxMats, RWKVQ_E_LIMIT, "rwkvq_gemm_tcb: %d matrices", n_mats);
     TcbArgs a{};
     for (int k = 0; k < n_mats; ++k) {
@@ -375,6 +497,12 @@ int launch_gemm_tcb(const rwkvq_qtensor* ts, int n_mats, const void* const* xs, 
         a.t[k] = make_view(ts[k]);
         if (half_in) { a.x16[k] = static_cast<const __half*>(xs[k]); a.unscale[k] = scales[k]; }
         else { a.x[k] = static_cast<const float*>(xs[k]); a.amax[k] = scales[k]; }
+        if (half_in && exact) {
+            RWKVQ_REQUIRE(xs_lo && xs_lo[k] && aligned(xs_lo[k], 16) && xs_sum && xs_sum[k] && aligned(xs_sum[k], 16), RWKVQ_E_NULL,
+                          "rwkvq_gemm_tcb: the low halves or the block sums of x are missing");
+            a.x16lo[k] = static_cast<const __half*>(xs_lo[k]);
+            a.xsum[k] = static_cast<const __half*>(xs_sum[k]);
+        }
         a.y[k] = ys[k]; a.resid[k] = resids ? resids[k] : nullptr;
         a.amax_out[k] = amax_outs ? amax_outs[k] : nullptr;
         RWKVQ_REQUIRE(epilogue != RWKVQ_EPI_ADD || a.resid[k], RWKVQ_E_NULL, "rwkvq_gemm_tcb: resid is null");
@@ -384,25 +512,32 @@ int launch_gemm_tcb(const rwkvq_qtensor* ts, int n_mats, const void* const* xs, 
     const int rows = ts[0].rows, cols = ts[0].cols;
     const int nt = N <= 16 ? 16 : N <= 32 ? 32 : 64;
     const int n_groups = (N + nt - 1) / nt;
-    const int row_tiles = (rows + kGmRows - 1) / kGmRows, n_sb = cols / kTbPassK;
-    // cluster size: a divisor of the pass count, at most 8; cost model in microseconds: waves of
-    // resident CTAs (two per SM) x (set-up and first loads + passes) + reduction
+    const int row_tiles = (rows + kGmRows - 1) / kGmRows, n_sb = cols / kTbSbK;
+    // cluster size: a divisor of the super-block count, at most 8; cost model in microseconds: waves of
+    // resident CTAs (two per SM) x (set-up and first loads + super-blocks) + reduction
     const int tiles = row_tiles * n_mats * n_groups;
     int best_ks = 1;
     double best = 1e30;
     for (int c = 1; c <= 8; ++c) {
         if (n_sb % c) continue;
         const int waves = (tiles * c + 2 * 148 - 1) / (2 * 148);
-        const double t = waves * (2.5 + 0.9 * (n_sb / c)) + 2.0 + 0.15 * c;
+        const double t = waves * (2.5 + (exact ? 1.8 : 0.9) * (n_sb / c)) + 2.0 + 0.15 * c;
         if (t < best) { best = t; best_ks = c; }
     }
     if (g_tcb_force_ks > 0 && n_sb % g_tcb_force_ks == 0 && g_tcb_force_ks <= 16) best_ks = g_tcb_force_ks;
     a.ks = best_ks;
-    a.passes = n_sb / best_ks;
+    a.passes = n_sb / best_ks * (exact ? 2 : 1);
+    if (exact) {
+        switch (nt) {
+            case 16: return launch_tcb<16, true>(a, n_mats, n_groups, row_tiles, s);
+            case 32: return launch_tcb<32, true>(a, n_mats, n_groups, row_tiles, s);
+            default: return launch_tcb<64, true>(a, n_mats, n_groups, row_tiles, s);
+        }
+    }
     switch (nt) {
-        case 16: return launch_tcb<16>(a, n_mats, n_groups, row_tiles, s);
-        case 32: return launch_tcb<32>(a, n_mats, n_groups, row_tiles, s);
-        default: return launch_tcb<64>(a, n_mats, n_groups, row_tiles, s);
+        case 16: return launch_tcb<16, false>(a, n_mats, n_groups, row_tiles, s);
+        case 32: return launch_tcb<32, false>(a, n_mats, n_groups, row_tiles, s);
+        default: return launch_tcb<64, false>(a, n_mats, n_groups, row_tiles, s);
     }
 }
 

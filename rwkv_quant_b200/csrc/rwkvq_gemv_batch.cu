@@ -776,7 +776,7 @@ extern "C" int rwkvq_gemv_batch(const rwkvq_qtensor* t, const float* x, int N, i
     const float* am[1] = {amax};
     float* ys[1] = {y};
     const float* rs[1] = {resid};
-    rc = tcb ? launch_gemm_tcb(t, 1, xs, false, am, N, ldx, ys, ldy, epilogue, rs, nullptr, status, s)
+    rc = tcb ? launch_gemm_tcb(t, 1, xs, false, am, N, ldx, ys, ldy, epilogue, rs, nullptr, status, s, !batch_fast())
              : launch_gemv_batch(t, 1, xs, false, am, N, ldx, ys, ldy, epilogue, rs, nullptr, s);
     return rc ? rc : check_launch("rwkvq_gemv_batch");
 }

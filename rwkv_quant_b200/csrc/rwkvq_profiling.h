@@ -33,6 +33,10 @@ void rwkvq_profiling_batch_fast(int fast);
 /* The exact zero-group skip of the single-vector GEMV (what RWKVQ_ZERO_SKIP=1 selects): 1 on, 0 off (the
  * default), -1 read the environment again. */
 void rwkvq_profiling_zero_skip(int on);
+/* Decode step above 32 streams in the default precision: 1 runs r / k / v, the ffn key and the head on the
+ * two-term tcgen05 linear (what RWKVQ_TCB_EXACT=1 selects), 0 keeps them on mma.sync (the default), -1 read
+ * the environment again. */
+void rwkvq_profiling_tcb_exact(int on);
 #ifdef __cplusplus
 }
 #endif

@@ -154,12 +154,18 @@ __device__ __forceinline__ void load_packed(Packed& p, const QView& t, int row_g
     }
 }
 
-// 32 weights -> fp16, stored as 4 swizzled 16-byte chunks of row r: chunks 4*half .. +3 of the
-// slab.  `it` = item index inside the super-block (selects the block scales).
-__device__ __forceinline__ void convert_store(const Packed& p, const QView& t, int r, int it, int half,
-                                              unsigned char* a_slab) {
-    uint32_t bytes[8];                             // 32 codes as bytes, column order
-    __half2 s2[2], m2[2], bias;                    // per 16 columns
+// The 32 codes of an item as bytes with their block scales and mins.
+struct ItemCodes {
+    uint32_t bytes[8];                             // column order
+    __half2 s2[2], m2[2], bias;                    // per 16 columns; bias: see bytes_to_half4
+};
+
+// `it` = item index inside the super-block (selects the block scales), `half` = it % 2.
+__device__ __forceinline__ void decode_item(const Packed& p, const QView& t, int it, int half, ItemCodes& c) {
+    uint32_t (&bytes)[8] = c.bytes;
+    __half2 (&s2)[2] = c.s2;
+    __half2 (&m2)[2] = c.m2;
+    __half2& bias = c.bias;
     const uint32_t h = p.h, h2 = p.h2;
     if (t.kind == RWKVQ_KIND_SB6) {
         const uint32_t w[4] = {p.c0.x, p.c0.y, p.c0.z, p.c0.w};
@@ -228,12 +234,59 @@ __device__ __forceinline__ void convert_store(const Packed& p, const QView& t, i
             bias = __float2half2_rn(1056.f);       // stored code = value + 32
         }
     }
+}
+
+// 32 weights -> fp16, stored as 4 swizzled 16-byte chunks of row r: chunks 4*half .. +3 of the slab.
+__device__ __forceinline__ void convert_store(const Packed& p, const QView& t, int r, int it, int half,
+                                              unsigned char* a_slab) {
+    ItemCodes c;
+    decode_item(p, t, it, half, c);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {                  // chunk j: columns 8j .. 8j+7 of the 32
-        const uint2 a = bytes_to_half4(bytes[2 * j], bias, s2[j >> 1], m2[j >> 1]);
-        const uint2 b = bytes_to_half4(bytes[2 * j + 1], bias, s2[j >> 1], m2[j >> 1]);
+        const uint2 a = bytes_to_half4(c.bytes[2 * j], c.bias, c.s2[j >> 1], c.m2[j >> 1]);
+        const uint2 b = bytes_to_half4(c.bytes[2 * j + 1], c.bias, c.s2[j >> 1], c.m2[j >> 1]);
         *reinterpret_cast<uint4*>(a_slab + sw128_offset(r, 4 * half + j)) = make_uint4(a.x, a.y, b.x, b.y);
     }
+}
+
+// 4 code bytes -> the product code * s as TWO fp16 terms: p = fp16(code * s) and the rounding error
+// of that product, which a fused multiply-add recovers exactly (code * s has at most 19 significant
+// bits, p keeps the top 11): p + e = code * s up to the fp16 subnormal quantum (6e-8 absolute).
+__device__ __forceinline__ void bytes_to_half4_pair(uint32_t w, __half2 bias, __half2 s2, uint2& p, uint2& e) {
+    const uint32_t lo = __byte_perm(w, 0x64646464u, 0x4140), hi = __byte_perm(w, 0x64646464u, 0x4342);
+    const __half2 q01 = __hsub2(*reinterpret_cast<const __half2*>(&lo), bias);
+    const __half2 q23 = __hsub2(*reinterpret_cast<const __half2*>(&hi), bias);
+    const __half2 p01 = __hmul2(q01, s2), p23 = __hmul2(q23, s2);
+    const __half2 e01 = __hfma2(q01, s2, __hneg2(p01)), e23 = __hfma2(q23, s2, __hneg2(p23));
+    p = make_uint2(*reinterpret_cast<const uint32_t*>(&p01), *reinterpret_cast<const uint32_t*>(&p23));
+    e = make_uint2(*reinterpret_cast<const uint32_t*>(&e01), *reinterpret_cast<const uint32_t*>(&e23));
+}
+
+// convert_store with the products code * s as two terms: p into a_slab, e into e_slab (same
+// positions).  The block min is NOT folded in: it is returned (an fp16 value by the codec's
+// definition; zero for the layouts without one) and multiplies the block's activation sum instead.
+__device__ __forceinline__ __half convert_store_pair(const Packed& p, const QView& t, int r, int it, int half,
+                                                     unsigned char* a_slab, unsigned char* e_slab) {
+    ItemCodes c;
+    decode_item(p, t, it, half, c);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint2 pa, ea, pb, eb;
+        bytes_to_half4_pair(c.bytes[2 * j], c.bias, c.s2[j >> 1], pa, ea);
+        bytes_to_half4_pair(c.bytes[2 * j + 1], c.bias, c.s2[j >> 1], pb, eb);
+        const uint32_t off = sw128_offset(r, 4 * half + j);
+        *reinterpret_cast<uint4*>(a_slab + off) = make_uint4(pa.x, pa.y, pb.x, pb.y);
+        *reinterpret_cast<uint4*>(e_slab + off) = make_uint4(ea.x, ea.y, eb.x, eb.y);
+    }
+    return __low2half(c.m2[0]);
+}
+
+// Shared-memory matrix descriptor of a K-major operand without swizzle: 8 rows x 16 bytes form a
+// contiguous core matrix; `kstep` bytes lead from one core matrix to the next along K, `mstep`
+// bytes to the next group of 8 rows.
+__device__ __forceinline__ uint64_t umma_desc_plain(uint32_t saddr, uint32_t kstep, uint32_t mstep) {
+    return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(kstep >> 4) << 16) |
+           (static_cast<uint64_t>(mstep >> 4) << 32) | (static_cast<uint64_t>(1) << 46);
 }
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {

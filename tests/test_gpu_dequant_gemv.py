@@ -217,25 +217,25 @@ def test_gemv_wide_dynamic_range_activations(cuda_lib, layout, bits, n):
 BATCH_SHAPES = [(16, 256), (48, 512), (2048, 2048), (100, 2560), (2048, 8192), (1024, 4352), (8192, 2048), (2560, 10240)]
 
 
-@pytest.fixture(params=["two-term", "mma.sync-fast", "tcgen05-fast"])
+@pytest.fixture(params=["two-term", "tcgen05-two-term", "mma.sync-fast", "tcgen05-fast"])
 def batch_kernel(request, cuda_lib):
-    """The three kernels behind rwkvq_gemv_batch: the default two-term mma.sync kernel (both operands
-    as fp16 pairs: fp32-grade results) and, selected by RWKVQ_BATCH_FAST=1 in production and by the
-    library's profiling switches (not part of the C ABI) here, the single-term mma.sync kernel and
-    the tcgen05 kernel (fp16 operands, the arithmetic of the prefill GEMM)."""
+    """The four kernels behind rwkvq_gemv_batch: the two-term kernels (both operands as fp16 pairs:
+    fp32-grade results) on mma.sync and on tcgen05, and, selected by RWKVQ_BATCH_FAST=1 in production
+    and by the library's profiling switches (not part of the C ABI) here, the single-term mma.sync
+    kernel and the single-term tcgen05 kernel (fp16 operands, the arithmetic of the prefill GEMM)."""
     import ctypes as C
     f = cuda_lib.rwkvq_profiling_tcb_force
     f.restype, f.argtypes = None, [C.c_int]
     fast = cuda_lib.rwkvq_profiling_batch_fast
     fast.restype, fast.argtypes = None, [C.c_int]
-    fast(0 if request.param == "two-term" else 1)
-    f(1000 if request.param == "tcgen05-fast" else -1)   # 1000: tcgen05 at every batch size (no valid cluster size: launcher's choice)
+    fast(0 if request.param.endswith("two-term") else 1)
+    f(1000 if request.param.startswith("tcgen05") else -1)   # 1000: tcgen05 at every batch size (no valid cluster size: launcher's choice)
     yield request.param
     f(0)
     fast(-1)
 
 
-BATCH_TOL = {"two-term": 2e-5, "mma.sync-fast": TOL, "tcgen05-fast": TOL}
+BATCH_TOL = {"two-term": 2e-5, "tcgen05-two-term": 2e-5, "mma.sync-fast": TOL, "tcgen05-fast": TOL}
 
 
 @pytest.mark.parametrize("layout,bits", LAYOUTS[:6])
@@ -251,7 +251,7 @@ def test_gemv_batch_matches_oracle(cuda_lib, batch_kernel, layout, bits, rows, c
     qt = _synth_linear(layout, bits, rows, cols, seed=rows + cols + bits)
     dq = ops.DeviceQT(qt)
     assert ops.has_batch_layout(dq)
-    if layout == "rtn" and batch_kernel == "tcgen05-fast":
+    if layout == "rtn" and batch_kernel.startswith("tcgen05"):
         pytest.skip("per-row int8 has no tcgen05 form")
     w = _oracle_w(qt).astype(np.float64)
     worst = 0.0

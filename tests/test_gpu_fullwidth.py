@@ -137,6 +137,44 @@ def test_prefill_then_decode_full_width(build):
     print(f"{name} prefill(37) -> decode(4): last-step logits relmax {err:.2e}")
 
 
+def test_decode_two_term_tcgen05_linears(build, cuda_lib):
+    """The opt-in form of batched decode (RWKVQ_TCB_EXACT=1; here through the library's profiling
+    switch, not part of the C ABI): r / k / v, the ffn key and the head on the two-term tcgen05 linear,
+    fed with fp16 pairs and block sums by the LayerNorm kernels.  64 streams, the oracle follows
+    streams 0 and 63; same tolerance as the default path, and fp32-grade agreement with it."""
+    import ctypes as C
+    model, oracle, name = build
+    hook = cuda_lib.rwkvq_profiling_tcb_exact
+    hook.restype, hook.argtypes = None, [C.c_int]
+    B, n, rows = 64, 4, [0, 63]
+    toks = np.random.default_rng(300).integers(1, 65000, (B, n))
+    ref_st = oracle.init_state(len(rows))
+    ref = []
+    for t in range(n):
+        lo, ref_st = oracle.forward_stateful(toks[rows, t:t + 1], ref_st)
+        ref.append(lo[:, 0])
+    ref = np.stack(ref, 1)
+    tk = torch.from_numpy(toks).cuda()
+    got = {}
+    try:
+        for on in (1, 0):
+            hook(on)
+            dec = model.decoder(B, use_graph=False)
+            out = []
+            for t in range(n):
+                dec.step(tk[:, t])
+                out.append(dec.logits.cpu().numpy())
+            got[on] = np.stack(out, 1)
+            del dec
+    finally:
+        hook(-1)
+    err = relmax(got[1][rows], ref)
+    both = relmax(got[1], got[0])
+    print(f"{name} decode B=64, two-term tcgen05 linears: logits relmax {err:.2e} vs oracle, {both:.2e} vs the mma.sync form")
+    assert np.isfinite(got[1]).all() and err <= TOL, err
+    assert both <= 2e-4, both
+
+
 def test_full_depth_decode_and_prefill(tmp_path, cuda_lib):
     """All 24 layers of the 1.5B compression build (the benchmark's model): rounding that stays
     under the tolerance on 2 layers must not grow past it over the real depth.  Batched decode
