@@ -529,7 +529,10 @@ __device__ __forceinline__ float warp_sum64(const float* v, int lane) {
 }
 
 __global__ void __launch_bounds__(256) tmix_core_kernel(const TmixCoreArgs p) {
-    __shared__ float sKK[64], sAV[64], sW[64], sK[64], sR[64], sV[64], sY[64], sG[64], sT[64];
+    // per-column operands of the state update, written once by warps 0 and 1 and read as float4 by all:
+    // sA = -kk / |kk|, sB = (kk / |kk|) * a_gate, sW decay, sK key, sR receptance
+    __shared__ __align__(16) float sA[64], sB[64], sW[64], sK[64], sR[64];
+    __shared__ float sV[64], sY[64], sG[64], sT[64];
     const int hi = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
     const size_t row = static_cast<size_t>(b) * p.D + hi * 64;
     // the state slice of this thread is requested first: it is the largest load
@@ -564,26 +567,40 @@ __global__ void __launch_bounds__(256) tmix_core_kernel(const TmixCoreArgs p) {
         if (p.layer0) p.v_first[row + tid] = v;
         else v = v + (__ldcg(p.v_first + row + tid) - v) * sigmoidf_(__ldcg(p.yv + row + tid) + pv0);
         const float kk = k * pkk;
-        sKK[tid] = kk; sAV[tid] = av; sT[tid] = kk * kk;
+        sT[tid] = kk * kk;
         sW[tid] = w; sK[tid] = k2; sR[tid] = r; sV[tid] = v; sG[tid] = __ldcg(p.g + row + tid);
+        asm volatile("bar.sync 1, 64;" ::: "memory");        // warps 0 and 1 only: sT is complete
+        // both warps reduce the head-wide sum themselves; a = -kk / |kk|, b = -a * a_gate
+        const float kn = kk * (1.0f / sqrtf(warp_sum64(sT, lane) + 1e-12f));
+        sA[tid] = -kn;
+        sB[tid] = kn * av;
     }
     __syncthreads();
-    // every warp reduces the head-wide sums itself; a = -kk / |kk|, b = -a * a_gate
-    const float inv_n = 1.0f / sqrtf(warp_sum64(sT, lane) + 1e-12f);
     // one WKV-7 step on the thread's 16 state columns
     float sa = 0.f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) sa = fmaf(h[i], -(sKK[16 * (i >> 2) + 4 * part + (i & 3)] * inv_n), sa);
+    for (int i = 0; i < 4; ++i) {
+        const float4 a4 = *reinterpret_cast<const float4*>(sA + 16 * i + 4 * part);
+        sa = fmaf(h[4 * i], a4.x, sa); sa = fmaf(h[4 * i + 1], a4.y, sa);
+        sa = fmaf(h[4 * i + 2], a4.z, sa); sa = fmaf(h[4 * i + 3], a4.w, sa);
+    }
     sa += __shfl_xor_sync(0xFFFFFFFFu, sa, 1);
     sa += __shfl_xor_sync(0xFFFFFFFFu, sa, 2);
     const float vv = sV[dv];
     float y = 0.f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const int dk = 16 * (i >> 2) + 4 * part + (i & 3);
-        const float kn = sKK[dk] * inv_n;
-        h[i] = fmaf(sW[dk], h[i], fmaf(vv, sK[dk], sa * (kn * sAV[dk])));
-        y = fmaf(h[i], sR[dk], y);
+    for (int i = 0; i < 4; ++i) {
+        const int dk = 16 * i + 4 * part;
+        const float4 b4 = *reinterpret_cast<const float4*>(sB + dk), w4 = *reinterpret_cast<const float4*>(sW + dk);
+        const float4 k4 = *reinterpret_cast<const float4*>(sK + dk), r4 = *reinterpret_cast<const float4*>(sR + dk);
+        h[4 * i] = fmaf(w4.x, h[4 * i], fmaf(vv, k4.x, sa * b4.x));
+        y = fmaf(h[4 * i], r4.x, y);
+        h[4 * i + 1] = fmaf(w4.y, h[4 * i + 1], fmaf(vv, k4.y, sa * b4.y));
+        y = fmaf(h[4 * i + 1], r4.y, y);
+        h[4 * i + 2] = fmaf(w4.z, h[4 * i + 2], fmaf(vv, k4.z, sa * b4.z));
+        y = fmaf(h[4 * i + 2], r4.z, y);
+        h[4 * i + 3] = fmaf(w4.w, h[4 * i + 3], fmaf(vv, k4.w, sa * b4.w));
+        y = fmaf(h[4 * i + 3], r4.w, y);
     }
     y += __shfl_xor_sync(0xFFFFFFFFu, y, 1);
     y += __shfl_xor_sync(0xFFFFFFFFu, y, 2);
