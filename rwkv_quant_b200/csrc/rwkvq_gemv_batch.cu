@@ -606,8 +606,13 @@ int launch_bt_l(BatchArgs& a, int n_mats, int rows, int cols, int N, bool exact,
     // The two-term kernel works on 16 tokens at a time (grid.z walks the groups of a larger batch): measured
     // inside the decode graph, two CTAs with 16 tokens each beat one with 32 on every shape (3 MMAs per step
     // make the 32-token tile MMA-issue bound, and its staged K slice no longer fits unchunked), and for
-    // K >= 8192 one with 8 beats one with 16.
-    int nt = exact ? (N <= 8 || (N <= 16 && cols >= 8192) ? 1 : 2) : N <= 8 ? 1 : N <= 16 ? 2 : N <= 32 ? 4 : 8;
+    // K >= 8192 one with 8 beats one with 16.  One exception, measured the same way at 20, 24 and 32 tokens on
+    // the ffn-key shapes of the 1.5B and 2.9B models ([8192, 2048], [10240, 2560]): with at most 32 tokens and
+    // at least twice as many rows as columns ONE CTA with 32 tokens is 1-5 us faster per launch (the output
+    // projection, the ffn value and the head lose with it).
+    const bool tall = rows >= 2 * cols && rows <= 16384;
+    int nt = exact ? (N <= 8 || (N <= 16 && cols >= 8192) ? 1 : (N > 16 && N <= 32 && tall) ? 4 : 2)
+                   : N <= 8 ? 1 : N <= 16 ? 2 : N <= 32 ? 4 : 8;
     const bool forced = g_batch_force_ks > 0 && (g_batch_force_rows == 0 || (g_batch_force_rows == rows && g_batch_force_cols == cols));
     if (forced && (g_batch_force_ks & 64) && nt > 1) nt /= 2;      // profiling: half the token tile, twice the token groups
     if (forced && (g_batch_force_ks & 128) && nt > 1) nt /= 2;     // ... and half again
