@@ -300,10 +300,15 @@ def batch_sweep(recipe="compression", Ns=(8, 64), reps=40, ring=24):
         torch.cuda.empty_cache()
 
 
-def batch_once(layout="sb6", bits=4, rows=8192, cols=2048, n=64, launches=3):
+def batch_once(layout="sb6", bits=4, rows=8192, cols=2048, n=64, launches=3, tcgen05=False):
     """A few plain rwkvq_gemv_batch launches, each on its own tensor (cold weights): the target of
-    ncu captures of the small-batch kernels."""
+    ncu captures of the small-batch kernels.  tcgen05: the tensor-memory form of the kernel (two-term
+    in the default precision) instead of the mma.sync form."""
     lib = _lib.load(check_device=True)
+    if tcgen05:
+        tf = lib.rwkvq_profiling_tcb_force           # rwkvq_profiling.h: not part of the C ABI
+        tf.restype, tf.argtypes = None, [C.c_int]
+        tf(1000)
     dqs = [_tensor(layout, bits, rows, cols, s) for s in range(launches)]
     x = torch.randn(n, cols, device="cuda")
     for d in dqs:
@@ -615,6 +620,7 @@ def main():
     bo = sub.add_parser("batch-once")
     bo.add_argument("layout"); bo.add_argument("bits", type=int); bo.add_argument("rows", type=int)
     bo.add_argument("cols", type=int); bo.add_argument("--n", type=int, default=64); bo.add_argument("--launches", type=int, default=3)
+    bo.add_argument("--tcgen05", action="store_true")
     bt = sub.add_parser("batch-tune")
     bt.add_argument("--layers", type=int, default=4); bt.add_argument("--batch", type=int, default=64)
     bt.add_argument("--recipe", default="compression"); bt.add_argument("--model", default="1.5b")
@@ -645,7 +651,7 @@ def main():
         decode_groups(a.layers, a.batch, a.recipe, a.model)
         return
     if a.cmd == "batch-once":
-        batch_once(a.layout, a.bits, a.rows, a.cols, a.n, a.launches)
+        batch_once(a.layout, a.bits, a.rows, a.cols, a.n, a.launches, a.tcgen05)
         return
     if a.cmd == "batch-tune":
         batch_tune(a.layers, a.batch, a.recipe, a.model)
