@@ -683,19 +683,23 @@ inline bool batch_path(int B) { return B > 2 && B <= kBatchMax; }
 // streams on (64 streams: 3.77 against 4.43 ms per step) and loses below (32: 2.87 / 2.68 ms, 8: 2.42 / 2.01 ms):
 // its pass (dependent weight loads -> conversion -> MMA) is longer than a warp-iteration of the mma.sync form
 inline bool tcb_pays(int B) { return batch_fast() && tcb_enabled() && B > 32; }
-// RWKVQ_TCB_EXACT=1 in the environment (read once; off by default): in the default two-term precision the
-// tcgen05 form of the two-term linear (fp16 pairs and block sums from the LayerNorm kernels) serves r / k / v,
-// the ffn key and the head from 33 streams on; the output projection and the ffn value, whose inputs reach
-// the linear as fp32 rows without a known scale, stay on the mma.sync form.  Measured on B200 (1.5B, whole
-// decode step, 64 / 48 / 33 streams): 4.63 / 4.02 / 3.82 ms against 4.04 / 3.76 / 3.60 ms on mma.sync
-// alone, which is why it is not the default.
-int g_tcb_exact = -1;
-inline bool tcx_pays(int B) {
-    if (g_tcb_exact < 0) {
+// Default (two-term) precision above 32 streams: which linears run on the tcgen05 form of the two-term
+// kernel, fed with fp16 pairs and block sums by the LayerNorm kernels (bit 0 r / k / v, bit 1 ffn key,
+// bit 2 head).  The output projection and the ffn value, whose inputs reach the linear as fp32 rows without
+// a known scale, always stay on the mma.sync form.  Measured on B200 (1.5B, whole decode step, ms, all
+// mma.sync / head only / all three): 33 streams 3.69 / 3.66 / 3.45, 36: 3.72 / 3.69 / 3.47, 40: 3.72 / 3.72 /
+// 3.59, 48: 3.76 / 3.73 / 3.64, 52: 4.02 / 3.96 / 4.20, 56: 4.10 / 4.04 / 4.27, 60: 4.13 / 4.07 / 4.32,
+// 64: 4.05 / 4.00 / 4.27 -- all three up to 48 streams, the head alone from there to 64.
+// RWKVQ_TCB_EXACT in the environment (read once) overrides: 0 none, 1 all three at every such batch.
+int g_tcb_exact = -2;          // -2 environment not read yet, -1 the measured policy, 0 none, 1 all three
+inline int tcx_mask(int B) {
+    if (g_tcb_exact == -2) {
         const char* e = getenv("RWKVQ_TCB_EXACT");
-        g_tcb_exact = (e != nullptr && e[0] == '1') ? 1 : 0;
+        g_tcb_exact = (e == nullptr || (e[0] != '0' && e[0] != '1')) ? -1 : e[0] - '0';
     }
-    return g_tcb_exact == 1 && !batch_fast() && tcb_enabled() && B > 32 && B <= kBatchMax;
+    if (batch_fast() || !tcb_enabled() || B <= 32 || B > kBatchMax || g_tcb_exact == 0) return 0;
+    if (g_tcb_exact == 1) return 7;
+    return B <= 48 ? 7 : B <= 64 ? 4 : 0;
 }
 
 
@@ -864,7 +868,7 @@ int lora_pair(const rwkvq_qtensor* const* t1, const rwkvq_qtensor* const* t2, co
 
 extern "C" {
 
-void rwkvq_profiling_tcb_exact(int on) { g_tcb_exact = on < 0 ? -1 : (on ? 1 : 0); }      // rwkvq_profiling.h
+void rwkvq_profiling_tcb_exact(int on) { g_tcb_exact = on < 0 ? -2 : (on ? 1 : 0); }      // rwkvq_profiling.h
 
 int rwkvq_seq_embed_ln0(const rwkvq_qtensor* emb, const int64_t* tokens, const float* ln_w, const float* ln_b, float* x,
                         int64_t n_tokens, int D, void* stream) {
@@ -928,8 +932,9 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         const bool rkv_fused = ml >= 0 && mma_layout_of(L.Wk) == ml && mma_layout_of(L.Wv) == ml && L.Wk.rows == L.Wr.rows &&
                                L.Wv.rows == L.Wr.rows && L.Wk.cols == L.Wr.cols && L.Wv.cols == L.Wr.cols;
         // two-term tcgen05 linears: fp16 pairs of their input rows from the LayerNorm kernels
-        const bool x_rkv = tcx_pays(B) && rkv_fused && gemm_tcb_ok(L.Wr) && gemm_tcb_ok(L.Wk) && gemm_tcb_ok(L.Wv);
-        const bool x_key = tcx_pays(B) && mma_layout_of(L.Wfk) >= 0 && gemm_tcb_ok(L.Wfk);
+        const int tcx = tcx_mask(B);
+        const bool x_rkv = (tcx & 1) && rkv_fused && gemm_tcb_ok(L.Wr) && gemm_tcb_ok(L.Wk) && gemm_tcb_ok(L.Wv);
+        const bool x_key = (tcx & 2) && mma_layout_of(L.Wfk) >= 0 && gemm_tcb_ok(L.Wfk);
         float* am = bp ? w.amax : nullptr;
         float *am_og = bp ? w.amax + 6 * B : nullptr, *am_xk = bp ? w.amax + 7 * B : nullptr;
         float *am_h = bp ? w.amax + 8 * B : nullptr;
@@ -1022,7 +1027,7 @@ int rwkvq_decode_step(const rwkvq_model* m, int B, const int64_t* tokens, float*
         if (rc) return rc;
     }
     float* am_xo = batch_path(B) ? w.amax + 9 * B : nullptr;
-    const bool x_head = tcx_pays(B) && mma_layout_of(m->head) >= 0 && gemm_tcb_ok(m->head);
+    const bool x_head = (tcx_mask(B) & 4) && mma_layout_of(m->head) >= 0 && gemm_tcb_ok(m->head);
     const bool xo_h16 = (am_xo && batch_fast()) || x_head;
     launch_pdl(D <= 8 * kRowThreads ? ln_shift_mix_kernel<0, 8> : ln_shift_mix_kernel<0, kRowPer>, dim3(B), dim3(kRowThreads), 0, s, w.x, m->lnout_w, m->lnout_b, static_cast<float*>(nullptr), static_cast<const float*>(nullptr), w.xo, B, D,
                xo_h16 ? w.xo16 : static_cast<__half*>(nullptr), x_head ? w.xo16lo : static_cast<__half*>(nullptr),

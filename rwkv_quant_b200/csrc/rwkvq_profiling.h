@@ -34,8 +34,8 @@ void rwkvq_profiling_batch_fast(int fast);
  * default), -1 read the environment again. */
 void rwkvq_profiling_zero_skip(int on);
 /* Decode step above 32 streams in the default precision: 1 runs r / k / v, the ffn key and the head on the
- * two-term tcgen05 linear (what RWKVQ_TCB_EXACT=1 selects), 0 keeps them on mma.sync (the default), -1 read
- * the environment again. */
+ * two-term tcgen05 linear at every such batch (what RWKVQ_TCB_EXACT=1 selects), 0 keeps them on mma.sync
+ * (RWKVQ_TCB_EXACT=0), -1 reads the environment again (unset: the launcher's measured choice by batch size). */
 void rwkvq_profiling_tcb_exact(int on);
 #ifdef __cplusplus
 }

@@ -137,17 +137,20 @@ def test_prefill_then_decode_full_width(build):
     print(f"{name} prefill(37) -> decode(4): last-step logits relmax {err:.2e}")
 
 
-def test_decode_two_term_tcgen05_linears(build, cuda_lib):
-    """The opt-in form of batched decode (RWKVQ_TCB_EXACT=1; here through the library's profiling
-    switch, not part of the C ABI): r / k / v, the ffn key and the head on the two-term tcgen05 linear,
-    fed with fp16 pairs and block sums by the LayerNorm kernels.  64 streams, the oracle follows
-    streams 0 and 63; same tolerance as the default path, and fp32-grade agreement with it."""
+@pytest.mark.parametrize("B", [40, 64])
+def test_decode_two_term_tcgen05_linears(build, cuda_lib, B):
+    """Batched decode above 32 streams runs some linears on the two-term tcgen05 kernel, fed with fp16
+    pairs and block sums by the LayerNorm kernels: r / k / v, the ffn key and the head up to 48 streams,
+    the head alone up to 64 (RWKVQ_TCB_EXACT=1 / 0 force all three / none; here through the library's
+    profiling switch, not part of the C ABI).  With all three forced: the tolerance of the default path
+    against the oracle (streams 0 and B - 1) and fp32-grade agreement with the all-mma.sync step; at 40
+    streams the launcher's own choice must be exactly the forced one."""
     import ctypes as C
     model, oracle, name = build
     hook = cuda_lib.rwkvq_profiling_tcb_exact
     hook.restype, hook.argtypes = None, [C.c_int]
-    B, n, rows = 64, 4, [0, 63]
-    toks = np.random.default_rng(300).integers(1, 65000, (B, n))
+    n, rows = 4, [0, B - 1]
+    toks = np.random.default_rng(300 + B).integers(1, 65000, (B, n))
     ref_st = oracle.init_state(len(rows))
     ref = []
     for t in range(n):
@@ -157,22 +160,28 @@ def test_decode_two_term_tcgen05_linears(build, cuda_lib):
     tk = torch.from_numpy(toks).cuda()
     got = {}
     try:
-        for on in (1, 0):
+        for on in (1, 0, -1):
             hook(on)
             dec = model.decoder(B, use_graph=False)
             out = []
             for t in range(n):
                 dec.step(tk[:, t])
                 out.append(dec.logits.cpu().numpy())
+            dec.check()
             got[on] = np.stack(out, 1)
             del dec
     finally:
         hook(-1)
     err = relmax(got[1][rows], ref)
     both = relmax(got[1], got[0])
-    print(f"{name} decode B=64, two-term tcgen05 linears: logits relmax {err:.2e} vs oracle, {both:.2e} vs the mma.sync form")
+    own = relmax(got[-1][rows], ref)
+    print(f"{name} decode B={B}, two-term tcgen05 linears: logits relmax {err:.2e} vs oracle, {both:.2e} vs the mma.sync form; "
+          f"launcher's choice {own:.2e} vs oracle")
     assert np.isfinite(got[1]).all() and err <= TOL, err
     assert both <= 2e-4, both
+    assert np.isfinite(got[-1]).all() and own <= TOL, own
+    if B == 40:
+        assert np.array_equal(got[-1], got[1])
 
 
 def test_full_depth_decode_and_prefill(tmp_path, cuda_lib):
