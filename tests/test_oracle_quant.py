@@ -14,7 +14,8 @@ import torch
 from oracle import quant_np as qn
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = "/root/reference"
+# the reference checkout: RWKVQ_REFERENCE_DIR, else a directory "reference" beside the repository
+REF = os.environ.get("RWKVQ_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def config1_weights(rows):
