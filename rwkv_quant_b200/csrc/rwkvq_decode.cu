@@ -686,10 +686,13 @@ inline bool tcb_pays(int B) { return batch_fast() && tcb_enabled() && B > 32; }
 // Default (two-term) precision above 32 streams: which linears run on the tcgen05 form of the two-term
 // kernel, fed with fp16 pairs and block sums by the LayerNorm kernels (bit 0 r / k / v, bit 1 ffn key,
 // bit 2 head).  The output projection and the ffn value, whose inputs reach the linear as fp32 rows without
-// a known scale, always stay on the mma.sync form.  Measured on B200 (1.5B, whole decode step, ms, all
-// mma.sync / head only / all three): 33 streams 3.69 / 3.66 / 3.45, 36: 3.72 / 3.69 / 3.47, 40: 3.72 / 3.72 /
-// 3.59, 48: 3.76 / 3.73 / 3.64, 52: 4.02 / 3.96 / 4.20, 56: 4.10 / 4.04 / 4.27, 60: 4.13 / 4.07 / 4.32,
-// 64: 4.05 / 4.00 / 4.27 -- all three up to 48 streams, the head alone from there to 64.
+// a known scale, always stay on the mma.sync form.  Measured on B200 (1.5B, whole decode step, ms):
+//   streams        33    36    40    48    50    52    56    60    64
+//   all mma.sync  3.69  3.72  3.72  3.76  3.92  4.02  4.10  4.13  4.05
+//   head          3.66  3.69  3.72  3.73   -    3.96  4.04  4.07  4.00
+//   r/k/v + head   -    3.70  3.82  3.86  3.80  3.79  3.87  3.92  3.92
+//   all three     3.45  3.47  3.59  3.64  4.14  4.20  4.27  4.32  4.27
+// -> all three up to 48 streams, r / k / v and the head from 49 to 64.
 // RWKVQ_TCB_EXACT in the environment (read once) overrides: 0 none, 1 all three at every such batch.
 int g_tcb_exact = -2;          // -2 environment not read yet, -1 the measured policy, 0 none, 1 all three
 inline int tcx_mask(int B) {
@@ -699,7 +702,7 @@ inline int tcx_mask(int B) {
     }
     if (batch_fast() || !tcb_enabled() || B <= 32 || B > kBatchMax || g_tcb_exact == 0) return 0;
     if (g_tcb_exact == 1) return 7;
-    return B <= 48 ? 7 : B <= 64 ? 4 : 0;
+    return B <= 48 ? 7 : B <= 64 ? 5 : 0;
 }
 
 
