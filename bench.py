@@ -458,10 +458,10 @@ def run_ours(a, rank, world, local_rank):
         "roofline": {"bound": "hbm", "achieved": g_bytes / g_sec / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": g_bytes / g_sec / 1e9 / peak, "peak_kind": peak_kind,
                          "traffic": NCU_BATCH_PHASE_DRAM_BYTES_B64 if (a.model, a.recipe, B, fast_env) == ("1.5b", "compression", 64, False) else None,
-                         "what": "the dominant kernel (the mma.sync small-batch linear: 67 % of a 64-stream step in the ncu launch list, "
-                                 "72 % with the head, which the step itself runs on the tcgen05 form above 48 streams): file-format "
-                                 "bytes of the quantized linears + their activation rows / time of those launches, all through "
-                                 "rwkvq_gemv_batch, replayed as one graph",
+                         "what": "the dominant kernel (the mma.sync small-batch linear: 72 % of a 64-stream step in the ncu launch list "
+                                 "when every linear runs on it, as timed here; the step itself runs r / k / v and the head on the "
+                                 "tcgen05 form above 48 streams): file-format bytes of the quantized linears + their activation "
+                                 "rows / time of those launches, all through rwkvq_gemv_batch, replayed as one graph",
                          "kernel": (f"row_amax_kernel + {'gemm_tcb_kernel' if (fast_env and B > 32) else 'gemv_batch_kernel'}, "
                                     f"the {g_launches} launches of the quantized linears of one step at "
                                     f"{B} streams" if B > 2 else f"gemv_mma_kernel, {g_launches} launches"),
