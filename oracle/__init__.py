@@ -13,4 +13,8 @@ Contents
              rwkv_quant/models/rwkv7_ref.py)
   wkv7_seq.c sequential-order WKV-7 recurrence in plain C (follows the
              prototype kernel in tests/bench_wkv_shared.py)
+  quant_np   numpy restatement of the sb6 and sym block quantizers (follows
+             rwkv_quant/calibration/groupwise.py)
+  wkv7_chunked_np  the same recurrence advanced a chunk of tokens at a time
+             (derivation of a chunked scan; checked against model_np.wkv7_np)
 """
