@@ -390,6 +390,11 @@ size_t rwkvq_decode_workspace_bytes(const rwkvq_model* m_host, int B);
  * (host arrays of device pointers; a fresh stream starts from zeros).
  * logits [B, vocab] fp32 (NULL: kept in the workspace), next_tokens [B] int64 greedy
  * argmax (NULL: skipped), tokens [B] int64 on the device.
+ * Linears: B = 1 the single-vector tensor-core GEMV; 3 <= B <= 256 the weights-once small-batch
+ * kernels in two-term precision (see rwkvq_gemv_batch), of which r / k / v, the ffn key and the head
+ * take the tcgen05 form at 33-48 streams and r / k / v and the head at 49-64 (RWKVQ_TCB_EXACT=0 / 1 in
+ * the environment, read once: none / all three at every B above 32); RWKVQ_BATCH_FAST=1 selects single
+ * fp16 operands instead; larger B the prefill GEMM.
  */
 int rwkvq_decode_step(const rwkvq_model* m_host, int B, const int64_t* tokens,
                       float* const* wkv_host, float* const* tshift_host, float* const* cshift_host,
